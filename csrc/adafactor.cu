@@ -1,0 +1,371 @@
+// Factored Adafactor update (the T5X variant) as a short chain of bandwidth-bound
+// kernels over one parameter [batch, R, C] (batch = stacked-layer / expert dims that the
+// optimizer treats independently):
+//
+//   stats   : rowsum[R] = sum_j (g^2 + eps1), colsum[C] = sum_i (g^2 + eps1), sum p^2
+//   factors : EMA of the two second-moment vectors, then the two factor vectors
+//             (v_row / mean(v_row))^-1/2 and v_col^-1/2
+//   usq     : sum (g * rf_i * cf_j)^2                        (for RMS update clipping)
+//   apply   : p <- (1 - wd) p - lr * scale(p) * u / max(1, rms(u)/thr)   (+ momentum),
+//             also writing the bf16 working copy that the next forward pass reads.
+//
+// The unfactored form (vectors, small matrices) keeps a full second moment and needs
+// two kernels. Scratch (rowsum/colsum/factor vectors/scalars) is provided by the caller
+// and must be zero on entry to `stats`.
+#include "common.cuh"
+
+namespace t5x {
+
+struct AdafactorScalars {  // per batch element, in scratch
+  float psq;   // sum p^2
+  float usq;   // sum u^2
+  float pad0, pad1;
+};
+
+constexpr int kAfThreads = 256;
+constexpr int kAfTileR = 64;
+constexpr int kAfTileC = 512;
+
+template <bool VEC>
+__global__ void __launch_bounds__(kAfThreads)
+    af_stats_kernel(const float* __restrict__ g, const float* __restrict__ p,
+                    float* __restrict__ rowsum, float* __restrict__ colsum,
+                    AdafactorScalars* __restrict__ scal, int R, int C, float eps1) {
+  __shared__ float scol[kAfTileC];
+  __shared__ float red[32];
+  const int b = blockIdx.z;
+  const long long base = static_cast<long long>(b) * R * C;
+  g += base;
+  p += base;
+  rowsum += static_cast<long long>(b) * R;
+  colsum += static_cast<long long>(b) * C;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tile_r = blockIdx.y * kAfTileR, tile_c = blockIdx.x * kAfTileC;
+  for (int i = threadIdx.x; i < kAfTileC; i += kAfThreads) scol[i] = 0.f;
+  __syncthreads();
+  float cacc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) cacc[a][k] = 0.f;
+  float psq = 0.f;
+  for (int rr = 0; rr < kAfTileR / 8; ++rr) {
+    const int row = tile_r + warp * (kAfTileR / 8) + rr;
+    if (row >= R) break;
+    float rs = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+      const int col = tile_c + ch * 128 + lane * 4;
+      if (VEC) {
+        if (col < C) {
+          const float4 gv = *reinterpret_cast<const float4*>(g + static_cast<long long>(row) * C + col);
+          const float4 pv = *reinterpret_cast<const float4*>(p + static_cast<long long>(row) * C + col);
+          const float s0 = gv.x * gv.x + eps1, s1 = gv.y * gv.y + eps1, s2 = gv.z * gv.z + eps1,
+                      s3 = gv.w * gv.w + eps1;
+          rs += (s0 + s1) + (s2 + s3);
+          cacc[ch][0] += s0;
+          cacc[ch][1] += s1;
+          cacc[ch][2] += s2;
+          cacc[ch][3] += s3;
+          psq += pv.x * pv.x + pv.y * pv.y + pv.z * pv.z + pv.w * pv.w;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (col + k < C) {
+            const float gv = g[static_cast<long long>(row) * C + col + k];
+            const float pv = p[static_cast<long long>(row) * C + col + k];
+            const float s = gv * gv + eps1;
+            rs += s;
+            cacc[ch][k] += s;
+            psq += pv * pv;
+          }
+        }
+      }
+    }
+    rs = warp_sum(rs);
+    if (lane == 0) atomicAdd(&rowsum[row], rs);
+  }
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) atomicAdd(&scol[ch * 128 + lane * 4 + k], cacc[ch][k]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < kAfTileC; i += kAfThreads)
+    if (tile_c + i < C) atomicAdd(&colsum[tile_c + i], scol[i]);
+  psq = warp_sum(psq);
+  if (lane == 0) red[warp] = psq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < kAfThreads / 32; ++w) t += red[w];
+    atomicAdd(&scal[b].psq, t);
+  }
+}
+
+// One CTA per batch element. `row_is_normalized`: the vector indexed by matrix rows is the
+// one divided by its mean (T5X "v_row"); otherwise the column-indexed vector is.
+__global__ void __launch_bounds__(1024)
+    af_factors_kernel(float* __restrict__ v_rvec, float* __restrict__ v_cvec,
+                      const float* __restrict__ rowsum, const float* __restrict__ colsum,
+                      float* __restrict__ rf, float* __restrict__ cf, int R, int C, float decay,
+                      int row_is_normalized, int skip_nan) {
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  v_rvec += static_cast<long long>(b) * R;
+  v_cvec += static_cast<long long>(b) * C;
+  rowsum += static_cast<long long>(b) * R;
+  colsum += static_cast<long long>(b) * C;
+  rf += static_cast<long long>(b) * R;
+  cf += static_cast<long long>(b) * C;
+  const float mix = 1.f - decay;
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const float old = v_rvec[i];
+    float nv = decay * old + mix * (rowsum[i] / static_cast<float>(C));
+    if (skip_nan && isnan(nv)) nv = old;
+    v_rvec[i] = nv;
+    if (row_is_normalized) acc += nv;
+  }
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    const float old = v_cvec[i];
+    float nv = decay * old + mix * (colsum[i] / static_cast<float>(R));
+    if (skip_nan && isnan(nv)) nv = old;
+    v_cvec[i] = nv;
+    if (!row_is_normalized) acc += nv;
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+  const float mean = tot / static_cast<float>(row_is_normalized ? R : C);
+  for (int i = threadIdx.x; i < R; i += blockDim.x)
+    rf[i] = row_is_normalized ? rsqrtf(v_rvec[i] / mean) : rsqrtf(v_rvec[i]);
+  for (int i = threadIdx.x; i < C; i += blockDim.x)
+    cf[i] = row_is_normalized ? rsqrtf(v_cvec[i]) : rsqrtf(v_cvec[i] / mean);
+}
+
+__global__ void __launch_bounds__(kAfThreads)
+    af_usq_kernel(const float* __restrict__ g, const float* __restrict__ rf,
+                  const float* __restrict__ cf, AdafactorScalars* __restrict__ scal, int R, int C) {
+  __shared__ float red[32];
+  const int b = blockIdx.y;
+  g += static_cast<long long>(b) * R * C;
+  rf += static_cast<long long>(b) * R;
+  cf += static_cast<long long>(b) * C;
+  const long long n = static_cast<long long>(R) * C;
+  float acc = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(kAfThreads) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * kAfThreads) {
+    const int r = static_cast<int>(i / C), c = static_cast<int>(i - static_cast<long long>(r) * C);
+    const float u = g[i] * rf[r] * cf[c];
+    acc += u * u;
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < kAfThreads / 32; ++w) t += red[w];
+    atomicAdd(&scal[b].usq, t);
+  }
+}
+
+struct AfHyper {
+  float lr, eps2, clip_threshold, weight_decay, beta1, max_param_scale;
+  int multiply_by_parameter_scale, use_clip, use_wd, use_momentum, use_max_scale, skip_nan;
+};
+
+__device__ __forceinline__ float af_update_scale(const AdafactorScalars& s, float n,
+                                                 const AfHyper& h) {
+  float scale = h.lr;
+  if (h.multiply_by_parameter_scale) {
+    float ps = fmaxf(sqrtf(s.psq / n), h.eps2);
+    if (h.use_max_scale) ps = fminf(ps, h.max_param_scale);
+    scale *= ps;
+  }
+  if (h.use_clip) scale /= fmaxf(1.f, sqrtf(s.usq / n) / h.clip_threshold);
+  return scale;
+}
+
+// FACTORED: u = g * rf[r] * cf[c].  !FACTORED: u = g * rsqrt(v) with v already updated.
+template <bool FACTORED>
+__global__ void __launch_bounds__(kAfThreads)
+    af_apply_kernel(float* __restrict__ p, const float* __restrict__ g, const float* __restrict__ rf,
+                    const float* __restrict__ cf, const float* __restrict__ v, float* __restrict__ m,
+                    __nv_bfloat16* __restrict__ p_bf16, long long ld_bf16, long long bf16_batch_stride,
+                    const AdafactorScalars* __restrict__ scal, int R, int C, AfHyper h) {
+  const int b = blockIdx.y;
+  const long long n = static_cast<long long>(R) * C;
+  const long long base = static_cast<long long>(b) * n;
+  const float scale = af_update_scale(scal[b], static_cast<float>(n), h);
+  if (FACTORED) {
+    rf += static_cast<long long>(b) * R;
+    cf += static_cast<long long>(b) * C;
+  }
+  for (long long i = blockIdx.x * static_cast<long long>(kAfThreads) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * kAfThreads) {
+    const int r = static_cast<int>(i / C), c = static_cast<int>(i - static_cast<long long>(r) * C);
+    const float gv = g[base + i];
+    const float u = FACTORED ? gv * rf[r] * cf[c] : gv * rsqrtf(v[base + i]);
+    float sub = scale * u;
+    if (h.use_momentum) {
+      const float old_m = m[base + i];
+      float nm = h.beta1 * old_m + (1.f - h.beta1) * sub;
+      sub = nm;
+      if (h.skip_nan && isnan(nm)) nm = old_m;
+      m[base + i] = nm;
+    }
+    const float old = p[base + i];
+    float np = (h.use_wd ? (1.f - h.weight_decay) * old : old) - sub;
+    if (h.skip_nan && isnan(np)) np = old;
+    p[base + i] = np;
+    if (p_bf16) p_bf16[b * bf16_batch_stride + static_cast<long long>(r) * ld_bf16 + c] = __float2bfloat16(np);
+  }
+}
+
+// Unfactored pass 1: v <- decay v + (1-decay)(g^2+eps1); accumulates sum u^2 and sum p^2.
+__global__ void __launch_bounds__(kAfThreads)
+    af_unfactored_stats_kernel(const float* __restrict__ g, const float* __restrict__ p,
+                               float* __restrict__ v, AdafactorScalars* __restrict__ scal,
+                               long long n, float decay, float eps1, int skip_nan) {
+  __shared__ float red[2][32];
+  const int b = blockIdx.y;
+  const long long base = static_cast<long long>(b) * n;
+  float usq = 0.f, psq = 0.f;
+  const float mix = 1.f - decay;
+  for (long long i = blockIdx.x * static_cast<long long>(kAfThreads) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * kAfThreads) {
+    const float gv = g[base + i], pv = p[base + i], old = v[base + i];
+    float nv = decay * old + mix * (gv * gv + eps1);
+    if (skip_nan && isnan(nv)) nv = old;
+    v[base + i] = nv;
+    const float u = gv * rsqrtf(nv);
+    usq += u * u;
+    psq += pv * pv;
+  }
+  usq = warp_sum(usq);
+  psq = warp_sum(psq);
+  if ((threadIdx.x & 31) == 0) {
+    red[0][threadIdx.x >> 5] = usq;
+    red[1][threadIdx.x >> 5] = psq;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, c = 0.f;
+    for (int w = 0; w < kAfThreads / 32; ++w) {
+      a += red[0][w];
+      c += red[1][w];
+    }
+    atomicAdd(&scal[b].usq, a);
+    atomicAdd(&scal[b].psq, c);
+  }
+}
+
+static inline int af_grid(long long n) {
+  long long blocks = (n + kAfThreads * 4 - 1) / (kAfThreads * 4);
+  long long cap = static_cast<long long>(num_sms()) * 8;
+  return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+}  // namespace t5x
+
+using namespace t5x;
+
+// Scratch layout (floats): [batch*R rowsum][batch*C colsum][batch*R rf][batch*C cf][batch*4 scalars]
+T5X_API long long t5x_adafactor_scratch_floats(int batch, int R, int C) {
+  return 2ll * batch * (static_cast<long long>(R) + C) + 4ll * batch;
+}
+
+// Factored update of p[batch,R,C]. v_rvec[batch,R] is the second-moment vector indexed by
+// matrix rows (mean over columns), v_cvec[batch,C] the one indexed by columns.
+T5X_API int t5x_adafactor_factored(void* p, const void* g, void* v_rvec, void* v_cvec, void* m,
+                                   void* p_bf16, long long ld_bf16, long long bf16_batch_stride,
+                                   void* scratch, int batch, int R, int C, int row_is_normalized,
+                                   float lr, float decay, float eps1, float eps2,
+                                   float clip_threshold, float weight_decay, float beta1,
+                                   float max_param_scale, int flags, void* stream) {
+  if (batch <= 0 || R <= 0 || C <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* s = static_cast<float*>(scratch);
+  float* rowsum = s;
+  float* colsum = rowsum + static_cast<long long>(batch) * R;
+  float* rf = colsum + static_cast<long long>(batch) * C;
+  float* cf = rf + static_cast<long long>(batch) * R;
+  AdafactorScalars* scal = reinterpret_cast<AdafactorScalars*>(cf + static_cast<long long>(batch) * C);
+  cudaMemsetAsync(scratch, 0, t5x_adafactor_scratch_floats(batch, R, C) * sizeof(float), st);
+  AfHyper h;
+  h.lr = lr;
+  h.eps2 = eps2;
+  h.clip_threshold = clip_threshold;
+  h.weight_decay = weight_decay;
+  h.beta1 = beta1;
+  h.max_param_scale = max_param_scale;
+  h.multiply_by_parameter_scale = (flags >> 0) & 1;
+  h.use_clip = (flags >> 1) & 1;
+  h.use_wd = (flags >> 2) & 1;
+  h.use_momentum = (flags >> 3) & 1;
+  h.use_max_scale = (flags >> 4) & 1;
+  h.skip_nan = (flags >> 5) & 1;
+  dim3 sgrid((C + kAfTileC - 1) / kAfTileC, (R + kAfTileR - 1) / kAfTileR, batch);
+  if (C % 4 == 0)
+    af_stats_kernel<true><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
+                                                        static_cast<const float*>(p), rowsum,
+                                                        colsum, scal, R, C, eps1);
+  else
+    af_stats_kernel<false><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
+                                                         static_cast<const float*>(p), rowsum,
+                                                         colsum, scal, R, C, eps1);
+  af_factors_kernel<<<batch, 1024, 0, st>>>(static_cast<float*>(v_rvec), static_cast<float*>(v_cvec),
+                                            rowsum, colsum, rf, cf, R, C, decay, row_is_normalized,
+                                            h.skip_nan);
+  const long long n = static_cast<long long>(R) * C;
+  dim3 egrid(af_grid(n), batch);
+  if (h.use_clip)
+    af_usq_kernel<<<egrid, kAfThreads, 0, st>>>(static_cast<const float*>(g), rf, cf, scal, R, C);
+  af_apply_kernel<true><<<egrid, kAfThreads, 0, st>>>(
+      static_cast<float*>(p), static_cast<const float*>(g), rf, cf, nullptr, static_cast<float*>(m),
+      static_cast<__nv_bfloat16*>(p_bf16), ld_bf16, bf16_batch_stride, scal, R, C, h);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("adafactor_factored: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// Unfactored update of p[batch, R, C] viewed per batch element as R*C numbers (C = bf16 row width).
+// Scratch: batch*4 floats.
+T5X_API int t5x_adafactor_unfactored(void* p, const void* g, void* v, void* m, void* p_bf16,
+                                     long long ld_bf16, long long bf16_batch_stride, void* scratch,
+                                     int batch, int R, int C, float lr, float decay, float eps1,
+                                     float eps2, float clip_threshold, float weight_decay,
+                                     float beta1, float max_param_scale, int flags, void* stream) {
+  if (batch <= 0 || R <= 0 || C <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  AdafactorScalars* scal = static_cast<AdafactorScalars*>(scratch);
+  cudaMemsetAsync(scratch, 0, sizeof(AdafactorScalars) * batch, st);
+  AfHyper h;
+  h.lr = lr;
+  h.eps2 = eps2;
+  h.clip_threshold = clip_threshold;
+  h.weight_decay = weight_decay;
+  h.beta1 = beta1;
+  h.max_param_scale = max_param_scale;
+  h.multiply_by_parameter_scale = (flags >> 0) & 1;
+  h.use_clip = (flags >> 1) & 1;
+  h.use_wd = (flags >> 2) & 1;
+  h.use_momentum = (flags >> 3) & 1;
+  h.use_max_scale = (flags >> 4) & 1;
+  h.skip_nan = (flags >> 5) & 1;
+  const long long n = static_cast<long long>(R) * C;
+  dim3 egrid(af_grid(n), batch);
+  af_unfactored_stats_kernel<<<egrid, kAfThreads, 0, st>>>(
+      static_cast<const float*>(g), static_cast<const float*>(p), static_cast<float*>(v), scal, n,
+      decay, eps1, h.skip_nan);
+  af_apply_kernel<false><<<egrid, kAfThreads, 0, st>>>(
+      static_cast<float*>(p), static_cast<const float*>(g), nullptr, nullptr,
+      static_cast<const float*>(v), static_cast<float*>(m), static_cast<__nv_bfloat16*>(p_bf16),
+      ld_bf16, bf16_batch_stride, scal, R, C, h);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("adafactor_unfactored: %s", cudaGetErrorString(e));
+  return 0;
+}

@@ -1,0 +1,389 @@
+// Bandwidth-bound kernels of the T5 block: RMSNorm forward/backward (with the
+// residual gradient folded in), gated-GELU backward, embedding gather and its
+// scatter-add backward, and fp32->bf16 casts. All are written as grid-stride /
+// persistent loops sized from the SM count, with 16-byte vector accesses.
+#include "common.cuh"
+
+namespace t5x {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+struct alignas(16) Bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const Bf16x8& p, float* f) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ Bf16x8 pack8(const float* f) {
+  Bf16x8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm forward: y = x * rsqrt(mean(x^2) + eps) * scale      (fp32 statistics)
+// One CTA per row at a time (grid-stride over rows). d % 8 == 0.
+// ---------------------------------------------------------------------------
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxVec = 4;  // up to 256*8*4 = 8192 features kept in registers
+
+__global__ void __launch_bounds__(kNormThreads)
+    rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                       __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int rows, int d,
+                       float eps) {
+  __shared__ float red[32];
+  const int nvec = d / 8;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + static_cast<long long>(row) * d);
+    float vals[kNormMaxVec][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        unpack8(xr[v], vals[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    const float tot = block_sum(ss, red);
+    const float rstd = rsqrtf(tot / static_cast<float>(d) + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+    Bf16x8* yr = reinterpret_cast<Bf16x8*>(y + static_cast<long long>(row) * d);
+#pragma unroll
+    for (int i = 0; i < kNormMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        const float4 s0 = reinterpret_cast<const float4*>(scale)[2 * v];
+        const float4 s1 = reinterpret_cast<const float4*>(scale)[2 * v + 1];
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * sc[j];
+        yr[v] = pack8(o);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm backward.
+//   g = dy * scale ;  dx = rstd * (g - x * rstd^2 * mean(g * x)) (+ dres)
+//   dscale[j] += sum_rows dy * x * rstd            (fp32 atomics, one per CTA per feature)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kNormThreads)
+    rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                       const float* __restrict__ scale, const float* __restrict__ rstd_in,
+                       const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dscale, int rows, int d) {
+  __shared__ float red[32];
+  const int nvec = d / 8;
+  float ds_acc[kNormMaxVec][8];
+  float sc[kNormMaxVec][8];
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ds_acc[i][j] = 0.f;
+      sc[i][j] = (v < nvec) ? scale[v * 8 + j] : 0.f;
+    }
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const long long off = static_cast<long long>(row) * d;
+    const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + off);
+    const Bf16x8* dyr = reinterpret_cast<const Bf16x8*>(dy + off);
+    const float rstd = rstd_in[row];
+    float xv[kNormMaxVec][8], gv[kNormMaxVec][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float dyv[8];
+        unpack8(xr[v], xv[i]);
+        unpack8(dyr[v], dyv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ds_acc[i][j] += dyv[j] * xv[i][j] * rstd;
+          gv[i][j] = dyv[j] * sc[i][j];
+          dot += gv[i][j] * xv[i][j];
+        }
+      }
+    }
+    const float tot = block_sum(dot, red);
+    const float c = tot / static_cast<float>(d) * rstd * rstd;
+    Bf16x8* dxr = reinterpret_cast<Bf16x8*>(dx + off);
+    const Bf16x8* rr = dres ? reinterpret_cast<const Bf16x8*>(dres + off) : nullptr;
+#pragma unroll
+    for (int i = 0; i < kNormMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (gv[i][j] - xv[i][j] * c);
+        if (rr) {
+          float r8[8];
+          unpack8(rr[v], r8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r8[j];
+        }
+        dxr[v] = pack8(o);
+      }
+    }
+  }
+  if (dscale) {
+#pragma unroll
+    for (int i = 0; i < kNormMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(&dscale[v * 8 + j], ds_acc[i][j]);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Gated-GELU backward. h = [h0 | h1] with row stride ldh (h1 at column offset `dff`).
+//   in : dg [T, dff] (grad of g = gelu(h0) * h1)
+//   out: h0 <- dg * h1 * gelu'(h0) ; h1 <- dg * gelu(h0) ; dg <- g  (recomputed activation,
+//        needed by the wgrad of the following projection) when write_g is set
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+    gated_gelu_bwd_kernel(__nv_bfloat16* __restrict__ dg, __nv_bfloat16* __restrict__ h, long long rows,
+                          int dff, long long ldh, long long ldg, int write_g) {
+  const int nvec = dff / 8;
+  const long long total = rows * nvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / nvec;
+    const int v = static_cast<int>(i - r * nvec);
+    Bf16x8* p0 = reinterpret_cast<Bf16x8*>(h + r * ldh) + v;
+    Bf16x8* p1 = reinterpret_cast<Bf16x8*>(h + r * ldh + dff) + v;
+    Bf16x8* pg = reinterpret_cast<Bf16x8*>(dg + r * ldg) + v;
+    float a[8], b[8], g[8], o0[8], o1[8], og[8];
+    unpack8(*p0, a);
+    unpack8(*p1, b);
+    unpack8(*pg, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float ge = gelu_tanh(a[j]);
+      o0[j] = g[j] * b[j] * gelu_tanh_grad(a[j]);
+      o1[j] = g[j] * ge;
+      og[j] = ge * b[j];
+    }
+    *p0 = pack8(o0);
+    *p1 = pack8(o1);
+    if (write_g) *pg = pack8(og);
+  }
+}
+
+// Gated-GELU forward on separate pre-activations (used when the GEMM epilogue is not).
+__global__ void __launch_bounds__(256)
+    gated_gelu_fwd_kernel(const __nv_bfloat16* __restrict__ h, __nv_bfloat16* __restrict__ g,
+                          long long rows, int dff, long long ldh, long long ldg) {
+  const int nvec = dff / 8;
+  const long long total = rows * nvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / nvec;
+    const int v = static_cast<int>(i - r * nvec);
+    float a[8], b[8], o[8];
+    unpack8(reinterpret_cast<const Bf16x8*>(h + r * ldh)[v], a);
+    unpack8(reinterpret_cast<const Bf16x8*>(h + r * ldh + dff)[v], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = gelu_tanh(a[j]) * b[j];
+    reinterpret_cast<Bf16x8*>(g + r * ldg)[v] = pack8(o);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Embedding gather (bf16 table) and scatter-add backward into an fp32 gradient.
+// Ids outside [vocab_start, vocab_start + vocab_rows) produce zeros / are skipped:
+// that is the vocab-parallel form (each rank owns a slice of the table).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+    embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                         __nv_bfloat16* __restrict__ out, long long tokens, int d, int vocab_start,
+                         int vocab_rows) {
+  const int nvec = d / 8;
+  const long long total = tokens * nvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / nvec;
+    const int v = static_cast<int>(i - t * nvec);
+    const long long id = ids[t] - vocab_start;
+    Bf16x8 val;
+    if (id >= 0 && id < vocab_rows) {
+      val = reinterpret_cast<const Bf16x8*>(table + id * d)[v];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) val.v[j] = __floats2bfloat162_rn(0.f, 0.f);
+    }
+    reinterpret_cast<Bf16x8*>(out + t * d)[v] = val;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
+                         float* __restrict__ dtable, long long tokens, int d, int vocab_start,
+                         int vocab_rows) {
+  const int nvec = d / 8;
+  const long long total = tokens * nvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / nvec;
+    const int v = static_cast<int>(i - t * nvec);
+    const long long id = ids[t] - vocab_start;
+    if (id < 0 || id >= vocab_rows) continue;
+    float f[8];
+    unpack8(reinterpret_cast<const Bf16x8*>(dout + t * d)[v], f);
+    float* dst = dtable + id * d + v * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(dst + j, f[j]);
+  }
+}
+
+// fp32 -> bf16 cast with independent leading dimensions (to fill slices of fused weights).
+__global__ void __launch_bounds__(256)
+    cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows,
+                         int cols, long long lds, long long ldd) {
+  const int nvec = cols / 4;
+  const long long total = rows * nvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / nvec;
+    const int v = static_cast<int>(i - r * nvec);
+    const float4 f = reinterpret_cast<const float4*>(src + r * lds)[v];
+    __nv_bfloat162 a = __floats2bfloat162_rn(f.x, f.y), b = __floats2bfloat162_rn(f.z, f.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    reinterpret_cast<uint2*>(dst + r * ldd)[v] = u;
+  }
+}
+
+static inline int ew_grid(long long work_items, int threads) {
+  long long blocks = (work_items + threads - 1) / threads;
+  long long cap = static_cast<long long>(num_sms()) * 8;
+  return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+}  // namespace t5x
+
+using namespace t5x;
+
+#define CHECK_LAUNCH(name)                                                           \
+  do {                                                                               \
+    cudaError_t e__ = cudaGetLastError();                                            \
+    if (e__ != cudaSuccess) return set_error(name ": %s", cudaGetErrorString(e__)); \
+  } while (0)
+
+T5X_API int t5x_rmsnorm_fwd(const void* x, const void* scale, void* y, void* rstd, int rows, int d,
+                            float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (d % 8 || d > kNormThreads * 8 * kNormMaxVec)
+    return set_error("rmsnorm: d=%d must be a multiple of 8 and <= %d", d,
+                     kNormThreads * 8 * kNormMaxVec);
+  int grid = rows < num_sms() * 8 ? rows : num_sms() * 8;
+  rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(scale),
+      static_cast<__nv_bfloat16*>(y), static_cast<float*>(rstd), rows, d, eps);
+  CHECK_LAUNCH("rmsnorm_fwd");
+  return 0;
+}
+
+T5X_API int t5x_rmsnorm_bwd(const void* dy, const void* x, const void* scale, const void* rstd,
+                            const void* dres, void* dx, void* dscale, int rows, int d,
+                            void* stream) {
+  if (rows <= 0) return 0;
+  if (d % 8 || d > kNormThreads * 8 * kNormMaxVec)
+    return set_error("rmsnorm: d=%d must be a multiple of 8 and <= %d", d,
+                     kNormThreads * 8 * kNormMaxVec);
+  int grid = rows < num_sms() * 2 ? rows : num_sms() * 2;
+  rmsnorm_bwd_kernel<<<grid, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const float*>(scale), static_cast<const float*>(rstd),
+      static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx),
+      static_cast<float*>(dscale), rows, d);
+  CHECK_LAUNCH("rmsnorm_bwd");
+  return 0;
+}
+
+T5X_API int t5x_gated_gelu_bwd(void* dg, void* h, long long rows, int dff, long long ldh,
+                               long long ldg, int write_g, void* stream) {
+  if (rows <= 0) return 0;
+  if (dff % 8 || ldh % 8 || ldg % 8) return set_error("gated_gelu: sizes must be multiples of 8");
+  gated_gelu_bwd_kernel<<<ew_grid(rows * (dff / 8), 256), 256, 0,
+                          static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(dg), static_cast<__nv_bfloat16*>(h), rows, dff, ldh, ldg, write_g);
+  CHECK_LAUNCH("gated_gelu_bwd");
+  return 0;
+}
+
+T5X_API int t5x_gated_gelu_fwd(const void* h, void* g, long long rows, int dff, long long ldh,
+                               long long ldg, void* stream) {
+  if (rows <= 0) return 0;
+  if (dff % 8 || ldh % 8 || ldg % 8) return set_error("gated_gelu: sizes must be multiples of 8");
+  gated_gelu_fwd_kernel<<<ew_grid(rows * (dff / 8), 256), 256, 0,
+                          static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(g), rows, dff, ldh, ldg);
+  CHECK_LAUNCH("gated_gelu_fwd");
+  return 0;
+}
+
+T5X_API int t5x_embedding_fwd(const void* ids, const void* table, void* out, long long tokens, int d,
+                              int vocab_start, int vocab_rows, void* stream) {
+  if (tokens <= 0) return 0;
+  if (d % 8) return set_error("embedding: d must be a multiple of 8");
+  embedding_fwd_kernel<<<ew_grid(tokens * (d / 8), 256), 256, 0,
+                         static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const long long*>(ids), static_cast<const __nv_bfloat16*>(table),
+      static_cast<__nv_bfloat16*>(out), tokens, d, vocab_start, vocab_rows);
+  CHECK_LAUNCH("embedding_fwd");
+  return 0;
+}
+
+T5X_API int t5x_embedding_bwd(const void* ids, const void* dout, void* dtable, long long tokens,
+                              int d, int vocab_start, int vocab_rows, void* stream) {
+  if (tokens <= 0) return 0;
+  if (d % 8) return set_error("embedding: d must be a multiple of 8");
+  embedding_bwd_kernel<<<ew_grid(tokens * (d / 8), 256), 256, 0,
+                         static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const long long*>(ids), static_cast<const __nv_bfloat16*>(dout),
+      static_cast<float*>(dtable), tokens, d, vocab_start, vocab_rows);
+  CHECK_LAUNCH("embedding_bwd");
+  return 0;
+}
+
+T5X_API int t5x_cast_f32_bf16(const void* src, void* dst, long long rows, int cols, long long lds,
+                              long long ldd, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 4 || lds % 4 || ldd % 4) return set_error("cast: sizes must be multiples of 4");
+  cast_f32_bf16_kernel<<<ew_grid(rows * (cols / 4), 256), 256, 0,
+                         static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(src), static_cast<__nv_bfloat16*>(dst), rows, cols, lds, ldd);
+  CHECK_LAUNCH("cast");
+  return 0;
+}

@@ -1,0 +1,304 @@
+"""Differentiable ops of the T5 block.
+
+On CUDA with bf16 activations every function here runs the hand-written sm_100a
+kernels (tcgen05 GEMMs with fused epilogues, fused RMSNorm, flash attention with
+in-kernel relative-position bias, fused z-loss cross-entropy); anything else (CPU,
+fp32 numerics tests) runs the PyTorch statements in :mod:`t5x_b200.ops.reference`.
+
+Weights are fp32 master parameters. A parameter may carry two attributes managed by
+the train state:
+  * ``bf16``       a bf16 working copy refreshed by the optimizer kernel,
+  * ``main_grad``  an fp32 accumulator; weight gradients are accumulated there directly
+                   by the wgrad GEMM epilogue (``C +=``) instead of being returned.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from t5x_b200.ops import native
+from t5x_b200.ops import reference as ref
+
+
+def _native_ok(x: torch.Tensor) -> bool:
+  return x.is_cuda and x.dtype == torch.bfloat16
+
+
+def compute_weight(p: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+  """The copy of parameter `p` in the compute dtype (cached bf16 copy when attached)."""
+  if dtype == torch.bfloat16:
+    w = getattr(p, "bf16", None)
+    if w is not None:
+      return w
+  return p if p.dtype == dtype else p.to(dtype)
+
+
+def _accumulate_wgrad(weight: torch.Tensor, a_t: torch.Tensor, b: torch.Tensor):
+  """dW = a_t @ b. With a main_grad buffer: accumulate in place and return None."""
+  mg = getattr(weight, "main_grad", None)
+  if mg is not None:
+    first = not getattr(weight, "grad_ready", False)
+    native.gemm(a_t, b, out=mg.view(a_t.shape[0], b.shape[1]), accumulate=not first)
+    weight.grad_ready = True
+    return None
+  return native.gemm(a_t, b, out_dtype=torch.float32).view(weight.shape).to(weight.dtype)
+
+
+class _LinearFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x, weight, residual):
+    k = x.shape[-1]
+    w2 = compute_weight(weight, torch.bfloat16).reshape(k, -1)
+    x2 = x.reshape(-1, k)
+    r2 = residual.reshape(-1, w2.shape[1]) if residual is not None else None
+    y = native.gemm(x2, w2, residual=r2)
+    ctx.save_for_backward(x, weight)
+    ctx.has_res = residual is not None
+    return y.view(*x.shape[:-1], w2.shape[1])
+
+  @staticmethod
+  def backward(ctx, dy):
+    x, weight = ctx.saved_tensors
+    k = x.shape[-1]
+    w2 = compute_weight(weight, torch.bfloat16).reshape(k, -1)
+    dy2 = dy.reshape(-1, w2.shape[1])
+    if not dy2.is_contiguous():
+      dy2 = dy2.contiguous()
+    x2 = x.reshape(-1, k)
+    dx = None
+    if ctx.needs_input_grad[0]:
+      dx = native.gemm(dy2, w2.t()).view(x.shape)
+    dw = None
+    if ctx.needs_input_grad[1]:
+      dw = _accumulate_wgrad(weight, x2.t(), dy2)
+    return dx, dw, (dy if ctx.has_res else None)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor] = None,
+           dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+  """y = x @ W (+ residual). W is [in, out...] (T5X kernel layout); trailing kernel dims are
+  flattened for the contraction and kept flat in the output."""
+  if _native_ok(x):
+    return _LinearFn.apply(x, weight, residual)
+  dt = dtype or x.dtype
+  w = compute_weight(weight, dt).reshape(x.shape[-1], -1)
+  y = x.to(dt) @ w
+  return y if residual is None else y + residual
+
+
+class _RmsNormFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x, scale, eps):
+    xc = x.contiguous()
+    y, rstd = native.rmsnorm_fwd(xc, scale.float(), eps)
+    ctx.save_for_backward(xc, scale, rstd)
+    return y
+
+  @staticmethod
+  def backward(ctx, dy):
+    x, scale, rstd = ctx.saved_tensors
+    mg = getattr(scale, "main_grad", None)
+    if mg is not None:
+      if not getattr(scale, "grad_ready", False):
+        mg.zero_()
+        scale.grad_ready = True
+      dscale_buf, ret = mg, None
+    else:
+      dscale_buf = torch.zeros_like(scale, dtype=torch.float32)
+      ret = dscale_buf
+    dx = native.rmsnorm_bwd(dy.contiguous(), x, scale.float(), rstd, None, dscale_buf)
+    return dx, ret, None
+
+
+def rmsnorm(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+  if _native_ok(x):
+    return _RmsNormFn.apply(x, scale, eps)
+  return ref.rmsnorm(x, scale, eps)
+
+
+class _GatedGeluMlpInFn(torch.autograd.Function):
+  """g = gelu(x @ wi_0) * (x @ wi_1) with the activation fused in the GEMM epilogue."""
+
+  @staticmethod
+  def forward(ctx, x, wi_0, wi_1):
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    w0 = compute_weight(wi_0, torch.bfloat16)
+    w1 = compute_weight(wi_1, torch.bfloat16)
+    dff = w0.shape[1]
+    h = torch.empty((x2.shape[0], 2 * dff), dtype=torch.bfloat16, device=x.device)
+    g = native.gemm(x2, w0, b2=w1, save_h=h)
+    ctx.save_for_backward(x, wi_0, wi_1, h)
+    return g.view(*x.shape[:-1], dff)
+
+  @staticmethod
+  def backward(ctx, dg):
+    x, wi_0, wi_1, h = ctx.saved_tensors
+    k = x.shape[-1]
+    dff = h.shape[1] // 2
+    x2 = x.reshape(-1, k)
+    # The saved pre-activations are overwritten with their gradients (one backward per forward).
+    dh = h
+    native.gated_gelu_bwd_(dg.reshape(-1, dff).contiguous(), dh)  # dh <- [dh0|dh1]
+    w0 = compute_weight(wi_0, torch.bfloat16)
+    w1 = compute_weight(wi_1, torch.bfloat16)
+    dh0, dh1 = dh[:, :dff], dh[:, dff:]
+    dx = None
+    if ctx.needs_input_grad[0]:
+      dx = native.gemm(dh0, w0.t())
+      native.gemm(dh1, w1.t(), out=dx, accumulate=True)
+      dx = dx.view(x.shape)
+    d0 = _accumulate_wgrad(wi_0, x2.t(), dh0) if ctx.needs_input_grad[1] else None
+    d1 = _accumulate_wgrad(wi_1, x2.t(), dh1) if ctx.needs_input_grad[2] else None
+    return dx, d0, d1
+
+
+def gated_gelu_mlp_in(x, wi_0, wi_1, dtype: Optional[torch.dtype] = None):
+  if _native_ok(x):
+    return _GatedGeluMlpInFn.apply(x, wi_0, wi_1)
+  dt = dtype or x.dtype
+  return ref.gelu_tanh(x.to(dt) @ compute_weight(wi_0, dt)) * (x.to(dt) @ compute_weight(wi_1, dt))
+
+
+class _EmbeddingFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, ids, table):
+    ctx.save_for_backward(ids, table)
+    return native.embedding_fwd(ids, compute_weight(table, torch.bfloat16))
+
+  @staticmethod
+  def backward(ctx, dout):
+    ids, table = ctx.saved_tensors
+    mg = getattr(table, "main_grad", None)
+    if mg is not None:
+      if not getattr(table, "grad_ready", False):
+        mg.zero_()
+        table.grad_ready = True
+      native.embedding_bwd_(ids, dout.contiguous(), mg)
+      return None, None
+    dt = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
+    native.embedding_bwd_(ids, dout.contiguous(), dt)
+    return None, dt.to(table.dtype)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+  if table.is_cuda and dtype == torch.bfloat16:
+    return _EmbeddingFn.apply(ids, table)
+  return compute_weight(table, dtype)[ids]
+
+
+# ----------------------------------------------------------------------------
+# Attention
+# ----------------------------------------------------------------------------
+def attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None, bidirectional: bool = True,
+              num_buckets: int = 32, max_distance: int = 128,
+              key_mask: Optional[torch.Tensor] = None, causal: bool = False,
+              q_segment_ids=None, kv_segment_ids=None, extra_mask=None,
+              explicit_bias: Optional[torch.Tensor] = None, q_offset: int = 0,
+              float32_logits: bool = False) -> torch.Tensor:
+  """Multi-head attention without 1/sqrt(d) scaling. q [B,Lq,H,D], k/v [B,Lk,H,D].
+
+  `bias_table` [H, num_buckets] is the T5 relative-position table; on the CUDA path the
+  bias is evaluated inside the kernel and never materialised.
+  """
+  from t5x_b200.ops import attention as attn_ops
+  if (_native_ok(q) and attn_ops.flash_supported(q, k, v, explicit_bias, extra_mask)):
+    return attn_ops.flash_attention(q, k, v, bias_table=bias_table, bidirectional=bidirectional,
+                                    num_buckets=num_buckets, max_distance=max_distance,
+                                    key_mask=key_mask, causal=causal,
+                                    q_segment_ids=q_segment_ids, kv_segment_ids=kv_segment_ids,
+                                    q_offset=q_offset)
+  bias = explicit_bias
+  if bias_table is not None:
+    rb = ref.relative_position_bias(bias_table.float(), q.shape[1], k.shape[1], bidirectional,
+                                    num_buckets, max_distance, q_offset=q_offset)
+    bias = rb if bias is None else bias + rb
+  return ref.attention(q, k, v, bias=bias, key_mask=key_mask, causal=causal,
+                       q_segment_ids=q_segment_ids, kv_segment_ids=kv_segment_ids,
+                       extra_mask=extra_mask,
+                       float32_logits=float32_logits or q.dtype == torch.float32)
+
+
+# ----------------------------------------------------------------------------
+# Cross entropy with z-loss on top of the logits projection
+# ----------------------------------------------------------------------------
+class _LogitsCrossEntropyFn(torch.autograd.Function):
+  """per-token (loss, z_loss, correct) = CE(hidden @ W) without keeping fp32 logits alive
+  beyond this function: logits are produced by the GEMM, reduced, and turned into bf16
+  dlogits in place of a second softmax pass in backward."""
+
+  @staticmethod
+  def forward(ctx, hidden, weight, targets, z_loss, label_smoothing, logits_scale):
+    k = hidden.shape[-1]
+    h2 = hidden.reshape(-1, k)
+    w = compute_weight(weight, torch.bfloat16)
+    if w.shape[0] != k:  # tied embedding [V, d]: logits = h @ E^T
+      w = w.t()
+    vocab = w.shape[1]
+    logits = native.gemm(h2, w, out_dtype=torch.float32, alpha=logits_scale)
+    t2 = targets.reshape(-1)
+    stats, _, arg_idx = native.ce_stats(logits, t2)
+    lse = stats[:, 0] + torch.log(stats[:, 1])
+    conf, low, norm_const = ref.label_smoothing_constants(vocab, label_smoothing)
+    tl = stats[:, 2]
+    soft_dot = conf * tl + low * (stats[:, 3] - tl) if label_smoothing > 0 else tl
+    z = z_loss * lse * lse
+    loss = lse - soft_dot + z - norm_const
+    correct = (arg_idx.long() == t2)
+    ctx.save_for_backward(hidden, weight, t2, lse, logits)
+    ctx.cfg = (z_loss, conf, low, logits_scale)
+    ctx.mark_non_differentiable(correct)
+    return loss.view(targets.shape), z.view(targets.shape), correct.view(targets.shape)
+
+  @staticmethod
+  def backward(ctx, dloss, dz, _dcorrect):
+    hidden, weight, t2, lse, logits = ctx.saved_tensors
+    z_loss, conf, low, logits_scale = ctx.cfg
+    k = hidden.shape[-1]
+    h2 = hidden.reshape(-1, k)
+    w = compute_weight(weight, torch.bfloat16)
+    tied = w.shape[0] != k
+    if tied:
+      w = w.t()
+    # `loss` already contains the z term; a gradient arriving through the separate z output
+    # (metrics only) is ignored, as in the reference's custom VJP (t5x/losses.py:98-124).
+    row_scale = (dloss.reshape(-1).float() * logits_scale).contiguous()
+    dlogits = native.ce_grad(logits, t2, lse, row_scale, z_loss, conf, low)
+    dh = native.gemm(dlogits, w.t()).view(hidden.shape) if ctx.needs_input_grad[0] else None
+    dw = None
+    if ctx.needs_input_grad[1]:
+      if tied:
+        mg = getattr(weight, "main_grad", None)
+        if mg is not None:
+          first = not getattr(weight, "grad_ready", False)
+          native.gemm(dlogits.t(), h2, out=mg, accumulate=not first)
+          weight.grad_ready = True
+        else:
+          dw = native.gemm(dlogits.t(), h2, out_dtype=torch.float32).to(weight.dtype)
+      else:
+        dw = _accumulate_wgrad(weight, h2.t(), dlogits)
+    return dh, dw, None, None, None, None
+
+
+def logits_cross_entropy(hidden, weight, targets, *, z_loss: float = 0.0,
+                         label_smoothing: float = 0.0, logits_scale: float = 1.0,
+                         dtype: Optional[torch.dtype] = None):
+  """Per-token (loss, z_loss, correct) of softmax cross-entropy over `hidden @ weight`.
+
+  The loss includes the z-loss term and subtracts the label-smoothing normalising
+  constant, as `compute_weighted_cross_entropy` does before weighting (t5x/losses.py:132-193).
+  """
+  if _native_ok(hidden):
+    return _LogitsCrossEntropyFn.apply(hidden, weight, targets, z_loss, label_smoothing,
+                                       logits_scale)
+  k = hidden.shape[-1]
+  w = weight.float()
+  if w.shape[0] != k:
+    w = w.t()
+  logits = (hidden.float() @ w) * logits_scale
+  loss, z, _, am = ref.token_cross_entropy(logits, targets, z_loss, label_smoothing)
+  return loss, z, (am == targets)

@@ -1,0 +1,343 @@
+"""ctypes binding of the in-tree sm_100a library (``t5x_b200/lib/libt5x_b200.so``).
+
+The library exports a plain C ABI: device pointers, sizes and a CUDA stream. The
+wrappers here take ``torch`` tensors, check dtypes/contiguity, pass
+``tensor.data_ptr()`` and the current stream, and raise ``NativeError`` with the
+library's message when a call is rejected. On a machine with a GPU a missing
+library is an error (there is no silent fallback); without a GPU the pure
+PyTorch reference ops in :mod:`t5x_b200.ops.reference` are what runs.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Optional
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib",
+                         "libt5x_b200.so")
+_lib = None
+_lock = threading.Lock()
+
+
+class NativeError(RuntimeError):
+  pass
+
+
+class KernelStatusError(RuntimeError):
+  """A kernel gave up on a bounded wait (or flagged non-finite values)."""
+
+
+STATUS_NAMES = {
+    0: "ok", 1: "timeout: TMA producer", 2: "timeout: MMA issuer", 3: "timeout: epilogue",
+    4: "timeout: peer flag", 5: "bad argument", 6: "non-finite value",
+}
+
+c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+def _declare(lib):
+  lib.t5x_last_error.restype = ctypes.c_char_p
+  lib.t5x_read_status.argtypes = [ctypes.POINTER(c_int), c_void_p]
+  lib.t5x_gemm_bf16.argtypes = [
+      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll,
+      c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_ll, c_void_p, c_void_p,
+      c_ll, c_float, c_int, c_void_p]
+  lib.t5x_rmsnorm_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                                  c_void_p]
+  lib.t5x_rmsnorm_bwd.argtypes = [c_void_p] * 7 + [c_int, c_int, c_void_p]
+  lib.t5x_gated_gelu_bwd.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_int, c_void_p]
+  lib.t5x_gated_gelu_fwd.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_void_p]
+  lib.t5x_embedding_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int,
+                                    c_void_p]
+  lib.t5x_embedding_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int,
+                                    c_void_p]
+  lib.t5x_cast_f32_bf16.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_void_p]
+  lib.t5x_ce_stats.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                               c_int, c_ll, c_int, c_void_p]
+  lib.t5x_ce_grad.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                              c_int, c_ll, c_ll, c_int, c_float, c_float, c_float, c_void_p]
+  lib.t5x_adafactor_scratch_floats.restype = c_ll
+  lib.t5x_adafactor_scratch_floats.argtypes = [c_int, c_int, c_int]
+  lib.t5x_adafactor_factored.argtypes = [
+      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_int,
+      c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_float,
+      c_int, c_void_p]
+  lib.t5x_adafactor_unfactored.argtypes = [
+      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_int, c_int, c_int,
+      c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_int, c_void_p]
+  return lib
+
+
+def available() -> bool:
+  """True when the shared library exists (it may still need a GPU to run)."""
+  return os.path.exists(_LIB_PATH)
+
+
+def lib():
+  """Loads the library (building it first if it is missing and nvcc is present)."""
+  global _lib
+  if _lib is not None:
+    return _lib
+  with _lock:
+    if _lib is None:
+      if not os.path.exists(_LIB_PATH):
+        from t5x_b200.ops import build as _build
+        _build.build()
+      _lib = _declare(ctypes.CDLL(_LIB_PATH))
+      _declare_optional(_lib)
+  return _lib
+
+
+def _declare_optional(l):
+  """Entry points added by later source files; declared only when present."""
+  for name, argtypes in _OPTIONAL_SIGNATURES.items():
+    if hasattr(l, name):
+      getattr(l, name).argtypes = argtypes
+
+
+_OPTIONAL_SIGNATURES: dict = {}
+
+
+def register_signature(name: str, argtypes) -> None:
+  _OPTIONAL_SIGNATURES[name] = argtypes
+  if _lib is not None and hasattr(_lib, name):
+    getattr(_lib, name).argtypes = argtypes
+
+
+def use_native(t: torch.Tensor) -> bool:
+  """Native kernels run for CUDA tensors; on a GPU the library is mandatory."""
+  return t.is_cuda
+
+
+def _check(rc: int, what: str) -> None:
+  if rc != 0:
+    raise NativeError(f"{what}: {lib().t5x_last_error().decode()}")
+
+
+def stream_ptr() -> int:
+  return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: Optional[torch.Tensor]) -> int:
+  return 0 if t is None else t.data_ptr()
+
+
+def check_status() -> None:
+  """Synchronises the current stream and raises if a kernel reported a failure."""
+  words = (c_int * 8)()
+  code = lib().t5x_read_status(words, stream_ptr())
+  if code < 0:
+    raise NativeError(lib().t5x_last_error().decode())
+  if code != 0:
+    raise KernelStatusError(
+        f"kernel {words[1]} block {words[2]} reported '{STATUS_NAMES.get(code, code)}' "
+        f"(payload {words[3]}, {words[4]})")
+
+
+# ----------------------------------------------------------------------------
+# GEMM
+# ----------------------------------------------------------------------------
+EPI_PLAIN, EPI_GATED_GELU, EPI_RESIDUAL = 0, 1, 2
+
+
+def _mat_layout(t: torch.Tensor, rows: int, cols: int):
+  """Returns (mn_major, ld, batch_stride) for a [..., rows, cols] operand whose contraction
+  dim is `cols` when K-major. Accepts row-major or its transpose view."""
+  if t.stride(-1) == 1:
+    return 0, t.stride(-2), (t.stride(0) if t.dim() == 3 else 0)
+  if t.stride(-2) == 1:
+    return 1, t.stride(-1), (t.stride(0) if t.dim() == 3 else 0)
+  raise NativeError(f"operand with strides {t.stride()} is neither row- nor column-major")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+         out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
+         residual: Optional[torch.Tensor] = None, b2: Optional[torch.Tensor] = None,
+         save_h: Optional[torch.Tensor] = None, alpha: float = 1.0,
+         max_ctas: int = 0) -> torch.Tensor:
+  """out[..., M, N] (+)= a[..., M, K] @ b[..., K, N]   (bf16 inputs, fp32 accumulation).
+
+  `a` and `b` may be arbitrary 2-D/3-D views whose last two dims are row-major or
+  transposed-row-major (no copy is made: the tensor-core descriptors read either).
+  With `b2` the gated-GELU epilogue runs: out = gelu(a @ b) * (a @ b2); `save_h`
+  ([M, 2N], bf16) then receives the two pre-activations side by side.
+  `residual` adds a bf16 tensor of the output's shape in the epilogue.
+  """
+  assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+  batch = a.shape[0] if a.dim() == 3 else 1
+  M, K = a.shape[-2], a.shape[-1]
+  K2, N = b.shape[-2], b.shape[-1]
+  assert K == K2, (a.shape, b.shape)
+  a_mn, lda, abs_ = _mat_layout(a, M, K)
+  # b as a [K, N] matrix: "K-major" for the kernel means memory [N, K] with K contiguous.
+  if b.stride(-2) == 1:
+    b_mn, ldb = 0, b.stride(-1)
+  elif b.stride(-1) == 1:
+    b_mn, ldb = 1, b.stride(-2)
+  else:
+    raise NativeError(f"b with strides {b.stride()} is neither row- nor column-major")
+  bbs = b.stride(0) if b.dim() == 3 else 0
+  if out is None:
+    shape = (batch, M, N) if a.dim() == 3 else (M, N)
+    out = torch.empty(shape, dtype=out_dtype, device=a.device)
+  assert out.stride(-1) == 1 and out.shape[-2:] == (M, N), (out.shape, out.stride(), M, N)
+  epi = EPI_PLAIN
+  r_ptr, ldr, rbs = 0, 0, 0
+  if residual is not None:
+    assert residual.dtype == torch.bfloat16 and residual.stride(-1) == 1
+    epi = EPI_RESIDUAL
+    r_ptr, ldr = residual.data_ptr(), residual.stride(-2)
+    rbs = residual.stride(0) if residual.dim() == 3 else 0
+  h0 = h1 = 0
+  ldh = 0
+  b2_ptr = 0
+  if b2 is not None:
+    assert b2.stride() == b.stride() and b2.shape == b.shape
+    epi = EPI_GATED_GELU
+    b2_ptr = b2.data_ptr()
+    if save_h is not None:
+      assert save_h.dtype == torch.bfloat16 and save_h.shape[-1] == 2 * N and save_h.stride(-1) == 1
+      h0 = save_h.data_ptr()
+      h1 = h0 + N * 2
+      ldh = save_h.stride(-2)
+  rc = lib().t5x_gemm_bf16(
+      a.data_ptr(), b.data_ptr(), b2_ptr, out.data_ptr(), M, N, K, batch, lda, ldb,
+      out.stride(-2), abs_, bbs, out.stride(0) if out.dim() == 3 else 0, a_mn, b_mn,
+      1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0, epi, r_ptr, ldr, rbs, h0,
+      h1, ldh, alpha, max_ctas, stream_ptr())
+  _check(rc, "gemm")
+  return out
+
+
+# ----------------------------------------------------------------------------
+# Normalisation / activations / embedding
+# ----------------------------------------------------------------------------
+def rmsnorm_fwd(x: torch.Tensor, scale: torch.Tensor, eps: float):
+  d = x.shape[-1]
+  x2 = x.reshape(-1, d)
+  assert x2.is_contiguous() and x.dtype == torch.bfloat16 and scale.dtype == torch.float32
+  y = torch.empty_like(x2)
+  rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+  _check(lib().t5x_rmsnorm_fwd(x2.data_ptr(), scale.data_ptr(), y.data_ptr(), rstd.data_ptr(),
+                               x2.shape[0], d, eps, stream_ptr()), "rmsnorm_fwd")
+  return y.view(x.shape), rstd
+
+
+def rmsnorm_bwd(dy, x, scale, rstd, dres: Optional[torch.Tensor], dscale: torch.Tensor):
+  """Returns dx (+ dres). Accumulates into `dscale` (fp32 [d])."""
+  d = x.shape[-1]
+  dy2, x2 = dy.reshape(-1, d), x.reshape(-1, d)
+  assert dy2.is_contiguous() and x2.is_contiguous()
+  dx = torch.empty_like(x2)
+  dres2 = None
+  if dres is not None:
+    dres2 = dres.reshape(-1, d)
+    assert dres2.is_contiguous()
+  _check(lib().t5x_rmsnorm_bwd(dy2.data_ptr(), x2.data_ptr(), scale.data_ptr(), rstd.data_ptr(),
+                               ptr(dres2), dx.data_ptr(), dscale.data_ptr(), x2.shape[0], d,
+                               stream_ptr()), "rmsnorm_bwd")
+  return dx.view(x.shape)
+
+
+def gated_gelu_bwd_(dg: torch.Tensor, h: torch.Tensor, write_g: bool = False) -> None:
+  """In place: h=[h0|h1] -> [dh0|dh1]; with `write_g`, dg -> g (the recomputed activation)."""
+  dff = dg.shape[-1]
+  dg2, h2 = dg.view(-1, dff), h.view(-1, 2 * dff)
+  _check(lib().t5x_gated_gelu_bwd(dg2.data_ptr(), h2.data_ptr(), dg2.shape[0], dff, h2.stride(0),
+                                  dg2.stride(0), int(write_g), stream_ptr()), "gated_gelu_bwd")
+
+
+def gated_gelu_fwd(h: torch.Tensor) -> torch.Tensor:
+  dff = h.shape[-1] // 2
+  h2 = h.view(-1, 2 * dff)
+  g = torch.empty((h2.shape[0], dff), dtype=h.dtype, device=h.device)
+  _check(lib().t5x_gated_gelu_fwd(h2.data_ptr(), g.data_ptr(), h2.shape[0], dff, h2.stride(0),
+                                  g.stride(0), stream_ptr()), "gated_gelu_fwd")
+  return g.view(*h.shape[:-1], dff)
+
+
+def embedding_fwd(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
+  assert ids.dtype == torch.int64 and table.dtype == torch.bfloat16 and table.is_contiguous()
+  ids_c = ids.contiguous()
+  out = torch.empty((*ids.shape, table.shape[1]), dtype=torch.bfloat16, device=table.device)
+  _check(lib().t5x_embedding_fwd(ids_c.data_ptr(), table.data_ptr(), out.data_ptr(),
+                                 ids_c.numel(), table.shape[1], vocab_start, table.shape[0],
+                                 stream_ptr()), "embedding_fwd")
+  return out
+
+
+def embedding_bwd_(ids: torch.Tensor, dout: torch.Tensor, dtable: torch.Tensor,
+                   vocab_start: int = 0) -> None:
+  assert dtable.dtype == torch.float32 and dtable.is_contiguous() and dout.is_contiguous()
+  ids_c = ids.contiguous()
+  _check(lib().t5x_embedding_bwd(ids_c.data_ptr(), dout.data_ptr(), dtable.data_ptr(),
+                                 ids_c.numel(), dtable.shape[1], vocab_start, dtable.shape[0],
+                                 stream_ptr()), "embedding_bwd")
+
+
+def cast_f32_bf16_(src: torch.Tensor, dst: torch.Tensor) -> None:
+  """dst (bf16, possibly a column slice of a wider matrix) <- src (fp32, 2-D)."""
+  assert src.dtype == torch.float32 and dst.dtype == torch.bfloat16 and src.dim() == 2
+  assert src.stride(1) == 1 and dst.stride(1) == 1 and src.shape == dst.shape
+  _check(lib().t5x_cast_f32_bf16(src.data_ptr(), dst.data_ptr(), src.shape[0], src.shape[1],
+                                 src.stride(0), dst.stride(0), stream_ptr()), "cast")
+
+
+# ----------------------------------------------------------------------------
+# Cross entropy
+# ----------------------------------------------------------------------------
+def ce_stats(logits: torch.Tensor, targets: torch.Tensor, vocab_start: int = 0):
+  rows, v = logits.shape
+  assert logits.stride(1) == 1 and targets.dtype == torch.int64
+  stats = torch.empty((rows, 4), dtype=torch.float32, device=logits.device)
+  arg_val = torch.empty(rows, dtype=torch.float32, device=logits.device)
+  arg_idx = torch.empty(rows, dtype=torch.int32, device=logits.device)
+  _check(lib().t5x_ce_stats(logits.data_ptr(), int(logits.dtype == torch.float32),
+                            targets.data_ptr(), stats.data_ptr(), arg_val.data_ptr(),
+                            arg_idx.data_ptr(), rows, v, logits.stride(0), vocab_start,
+                            stream_ptr()), "ce_stats")
+  return stats, arg_val, arg_idx
+
+
+def ce_grad(logits, targets, lse, row_scale, z_loss, confidence, low_confidence,
+            vocab_start: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+  rows, v = logits.shape
+  if out is None:
+    out = torch.empty((rows, v), dtype=torch.bfloat16, device=logits.device)
+  _check(lib().t5x_ce_grad(logits.data_ptr(), int(logits.dtype == torch.float32),
+                           targets.data_ptr(), lse.data_ptr(), row_scale.data_ptr(),
+                           out.data_ptr(), rows, v, logits.stride(0), out.stride(0), vocab_start,
+                           z_loss, confidence, low_confidence, stream_ptr()), "ce_grad")
+  return out
+
+
+# ----------------------------------------------------------------------------
+# Adafactor
+# ----------------------------------------------------------------------------
+AF_PARAM_SCALE, AF_CLIP, AF_WD, AF_MOMENTUM, AF_MAX_SCALE, AF_SKIP_NAN = 1, 2, 4, 8, 16, 32
+
+
+def adafactor_scratch_floats(batch: int, rows: int, cols: int) -> int:
+  return int(lib().t5x_adafactor_scratch_floats(batch, rows, cols))
+
+
+def adafactor_factored_(p, g, v_rvec, v_cvec, m, p_bf16, scratch, *, batch, rows, cols,
+                        row_is_normalized, lr, decay, eps1, eps2, clip_threshold, weight_decay,
+                        beta1, max_param_scale, flags, ld_bf16=0, bf16_batch_stride=0) -> None:
+  _check(lib().t5x_adafactor_factored(
+      p.data_ptr(), g.data_ptr(), v_rvec.data_ptr(), v_cvec.data_ptr(), ptr(m), ptr(p_bf16),
+      ld_bf16, bf16_batch_stride, scratch.data_ptr(), batch, rows, cols, int(row_is_normalized),
+      lr, decay, eps1, eps2, clip_threshold, weight_decay, beta1, max_param_scale, flags,
+      stream_ptr()), "adafactor_factored")
+
+
+def adafactor_unfactored_(p, g, v, m, p_bf16, scratch, *, batch, rows, cols, lr, decay, eps1, eps2,
+                          clip_threshold, weight_decay, beta1, max_param_scale, flags, ld_bf16=0,
+                          bf16_batch_stride=0) -> None:
+  _check(lib().t5x_adafactor_unfactored(
+      p.data_ptr(), g.data_ptr(), v.data_ptr(), ptr(m), ptr(p_bf16), ld_bf16, bf16_batch_stride,
+      scratch.data_ptr(), batch, rows, cols, lr, decay, eps1, eps2, clip_threshold, weight_decay,
+      beta1, max_param_scale, flags, stream_ptr()), "adafactor_unfactored")
