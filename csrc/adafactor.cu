@@ -19,7 +19,8 @@ namespace t5x {
 struct AdafactorScalars {  // per batch element, in scratch
   float psq;   // sum p^2
   float usq;   // sum u^2
-  float pad0, pad1;
+  float vsum;  // sum of the normalised second-moment vector (T5X "v_row")
+  float pad;
 };
 
 constexpr int kAfThreads = 256;
@@ -103,33 +104,33 @@ __global__ void __launch_bounds__(kAfThreads)
   }
 }
 
-// One CTA per batch element. `row_is_normalized`: the vector indexed by matrix rows is the
-// one divided by its mean (T5X "v_row"); otherwise the column-indexed vector is.
+// EMA of the two second-moment vectors; one CTA per batch element. `row_is_normalized`: the
+// vector indexed by matrix rows is the one divided by its mean (T5X "v_row"); otherwise the
+// column-indexed vector is. row_div / col_div are the GLOBAL column / row counts (the means are
+// over the unsharded dims); the local sums were combined across ranks beforehand if needed.
 __global__ void __launch_bounds__(1024)
-    af_factors_kernel(float* __restrict__ v_rvec, float* __restrict__ v_cvec,
-                      const float* __restrict__ rowsum, const float* __restrict__ colsum,
-                      float* __restrict__ rf, float* __restrict__ cf, int R, int C, float decay,
-                      int row_is_normalized, int skip_nan) {
+    af_ema_kernel(float* __restrict__ v_rvec, float* __restrict__ v_cvec,
+                  const float* __restrict__ rowsum, const float* __restrict__ colsum,
+                  AdafactorScalars* __restrict__ scal, int R, int C, float row_div, float col_div,
+                  float decay, int row_is_normalized, int skip_nan) {
   __shared__ float red[32];
   const int b = blockIdx.x;
   v_rvec += static_cast<long long>(b) * R;
   v_cvec += static_cast<long long>(b) * C;
   rowsum += static_cast<long long>(b) * R;
   colsum += static_cast<long long>(b) * C;
-  rf += static_cast<long long>(b) * R;
-  cf += static_cast<long long>(b) * C;
   const float mix = 1.f - decay;
   float acc = 0.f;
   for (int i = threadIdx.x; i < R; i += blockDim.x) {
     const float old = v_rvec[i];
-    float nv = decay * old + mix * (rowsum[i] / static_cast<float>(C));
+    float nv = decay * old + mix * (rowsum[i] / row_div);
     if (skip_nan && isnan(nv)) nv = old;
     v_rvec[i] = nv;
     if (row_is_normalized) acc += nv;
   }
   for (int i = threadIdx.x; i < C; i += blockDim.x) {
     const float old = v_cvec[i];
-    float nv = decay * old + mix * (colsum[i] / static_cast<float>(R));
+    float nv = decay * old + mix * (colsum[i] / col_div);
     if (skip_nan && isnan(nv)) nv = old;
     v_cvec[i] = nv;
     if (!row_is_normalized) acc += nv;
@@ -137,9 +138,26 @@ __global__ void __launch_bounds__(1024)
   acc = warp_sum(acc);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
   __syncthreads();
-  float tot = 0.f;
-  for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
-  const float mean = tot / static_cast<float>(row_is_normalized ? R : C);
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+    scal[b].vsum = tot;
+  }
+}
+
+// Factor vectors from the updated moments: (v_row / mean(v_row))^-1/2 and v_col^-1/2.
+// norm_count = GLOBAL length of the normalised vector.
+__global__ void __launch_bounds__(1024)
+    af_finalize_kernel(const float* __restrict__ v_rvec, const float* __restrict__ v_cvec,
+                       float* __restrict__ rf, float* __restrict__ cf,
+                       const AdafactorScalars* __restrict__ scal, int R, int C, float norm_count,
+                       int row_is_normalized) {
+  const int b = blockIdx.x;
+  v_rvec += static_cast<long long>(b) * R;
+  v_cvec += static_cast<long long>(b) * C;
+  rf += static_cast<long long>(b) * R;
+  cf += static_cast<long long>(b) * C;
+  const float mean = scal[b].vsum / norm_count;
   for (int i = threadIdx.x; i < R; i += blockDim.x)
     rf[i] = row_is_normalized ? rsqrtf(v_rvec[i] / mean) : rsqrtf(v_rvec[i]);
   for (int i = threadIdx.x; i < C; i += blockDim.x)
@@ -195,11 +213,12 @@ __global__ void __launch_bounds__(kAfThreads)
     af_apply_kernel(float* __restrict__ p, const float* __restrict__ g, const float* __restrict__ rf,
                     const float* __restrict__ cf, const float* __restrict__ v, float* __restrict__ m,
                     __nv_bfloat16* __restrict__ p_bf16, long long ld_bf16, long long bf16_batch_stride,
-                    const AdafactorScalars* __restrict__ scal, int R, int C, AfHyper h) {
+                    const AdafactorScalars* __restrict__ scal, int R, int C, float n_global,
+                    AfHyper h) {
   const int b = blockIdx.y;
   const long long n = static_cast<long long>(R) * C;
   const long long base = static_cast<long long>(b) * n;
-  const float scale = af_update_scale(scal[b], static_cast<float>(n), h);
+  const float scale = af_update_scale(scal[b], n_global, h);
   if (FACTORED) {
     rf += static_cast<long long>(b) * R;
     cf += static_cast<long long>(b) * C;
@@ -278,94 +297,182 @@ T5X_API long long t5x_adafactor_scratch_floats(int batch, int R, int C) {
   return 2ll * batch * (static_cast<long long>(R) + C) + 4ll * batch;
 }
 
-// Factored update of p[batch,R,C]. v_rvec[batch,R] is the second-moment vector indexed by
-// matrix rows (mean over columns), v_cvec[batch,C] the one indexed by columns.
+namespace {
+struct AfScratch {
+  float *rowsum, *colsum, *rf, *cf;
+  AdafactorScalars* scal;
+};
+AfScratch af_split(void* scratch, int batch, int R, int C) {
+  AfScratch a;
+  float* s = static_cast<float*>(scratch);
+  a.rowsum = s;
+  a.colsum = a.rowsum + static_cast<long long>(batch) * R;
+  a.rf = a.colsum + static_cast<long long>(batch) * C;
+  a.cf = a.rf + static_cast<long long>(batch) * R;
+  a.scal = reinterpret_cast<AdafactorScalars*>(a.cf + static_cast<long long>(batch) * C);
+  return a;
+}
+AfHyper af_hyper(float lr, float eps2, float clip_threshold, float weight_decay, float beta1,
+                 float max_param_scale, int flags) {
+  AfHyper h;
+  h.lr = lr;
+  h.eps2 = eps2;
+  h.clip_threshold = clip_threshold;
+  h.weight_decay = weight_decay;
+  h.beta1 = beta1;
+  h.max_param_scale = max_param_scale;
+  h.multiply_by_parameter_scale = (flags >> 0) & 1;
+  h.use_clip = (flags >> 1) & 1;
+  h.use_wd = (flags >> 2) & 1;
+  h.use_momentum = (flags >> 3) & 1;
+  h.use_max_scale = (flags >> 4) & 1;
+  h.skip_nan = (flags >> 5) & 1;
+  return h;
+}
+int af_check(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("%s: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+}  // namespace
+
+// The factored update is split in phases so that a tensor-parallel caller can sum the
+// partial statistics across ranks between them (row sums when columns are sharded, column
+// sums when rows are sharded, and the three scalars). A single-GPU caller uses
+// t5x_adafactor_factored, which runs the phases back to back.
+
+// Phase 1: clears the scratch and accumulates rowsum / colsum / sum p^2 of the local shard.
+T5X_API int t5x_adafactor_stats(const void* p, const void* g, void* scratch, int batch, int R,
+                                int C, float eps1, void* stream) {
+  if (batch <= 0 || R <= 0 || C <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  AfScratch a = af_split(scratch, batch, R, C);
+  cudaMemsetAsync(scratch, 0, t5x_adafactor_scratch_floats(batch, R, C) * sizeof(float), st);
+  dim3 sgrid((C + kAfTileC - 1) / kAfTileC, (R + kAfTileR - 1) / kAfTileR, batch);
+  if (C % 4 == 0)
+    af_stats_kernel<true><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
+                                                        static_cast<const float*>(p), a.rowsum,
+                                                        a.colsum, a.scal, R, C, eps1);
+  else
+    af_stats_kernel<false><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
+                                                         static_cast<const float*>(p), a.rowsum,
+                                                         a.colsum, a.scal, R, C, eps1);
+  return af_check("adafactor_stats");
+}
+
+// Phase 2: EMA of both vectors (global_R / global_C = unsharded dims); leaves the local sum of
+// the normalised vector in scal.vsum.
+T5X_API int t5x_adafactor_ema(void* v_rvec, void* v_cvec, void* scratch, int batch, int R, int C,
+                              int global_R, int global_C, int row_is_normalized, float decay,
+                              int skip_nan, void* stream) {
+  if (batch <= 0) return 0;
+  AfScratch a = af_split(scratch, batch, R, C);
+  af_ema_kernel<<<batch, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float*>(v_rvec), static_cast<float*>(v_cvec), a.rowsum, a.colsum, a.scal, R, C,
+      static_cast<float>(global_C), static_cast<float>(global_R), decay, row_is_normalized,
+      skip_nan);
+  return af_check("adafactor_ema");
+}
+
+// Phase 3: factor vectors, then sum u^2 of the local shard (when clipping is on).
+T5X_API int t5x_adafactor_usq(const void* g, const void* v_rvec, const void* v_cvec, void* scratch,
+                              int batch, int R, int C, int global_R, int global_C,
+                              int row_is_normalized, int use_clip, void* stream) {
+  if (batch <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  AfScratch a = af_split(scratch, batch, R, C);
+  af_finalize_kernel<<<batch, 1024, 0, st>>>(
+      static_cast<const float*>(v_rvec), static_cast<const float*>(v_cvec), a.rf, a.cf, a.scal, R,
+      C, static_cast<float>(row_is_normalized ? global_R : global_C), row_is_normalized);
+  if (use_clip) {
+    dim3 egrid(af_grid(static_cast<long long>(R) * C), batch);
+    af_usq_kernel<<<egrid, kAfThreads, 0, st>>>(static_cast<const float*>(g), a.rf, a.cf, a.scal,
+                                                R, C);
+  }
+  return af_check("adafactor_usq");
+}
+
+// Phase 4: the parameter update. n_global = number of elements of the unsharded parameter
+// (per batch element) over which the two RMS values are taken.
+T5X_API int t5x_adafactor_apply(void* p, const void* g, void* m, void* p_bf16, long long ld_bf16,
+                                long long bf16_batch_stride, void* scratch, int batch, int R, int C,
+                                long long n_global, float lr, float eps2, float clip_threshold,
+                                float weight_decay, float beta1, float max_param_scale, int flags,
+                                void* stream) {
+  if (batch <= 0) return 0;
+  AfScratch a = af_split(scratch, batch, R, C);
+  AfHyper h = af_hyper(lr, eps2, clip_threshold, weight_decay, beta1, max_param_scale, flags);
+  dim3 egrid(af_grid(static_cast<long long>(R) * C), batch);
+  af_apply_kernel<true><<<egrid, kAfThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float*>(p), static_cast<const float*>(g), a.rf, a.cf, nullptr,
+      static_cast<float*>(m), static_cast<__nv_bfloat16*>(p_bf16), ld_bf16, bf16_batch_stride,
+      a.scal, R, C, static_cast<float>(n_global), h);
+  return af_check("adafactor_apply");
+}
+
+// Factored update of p[batch,R,C] on one GPU. v_rvec[batch,R] is the second-moment vector
+// indexed by matrix rows (mean over columns), v_cvec[batch,C] the one indexed by columns.
 T5X_API int t5x_adafactor_factored(void* p, const void* g, void* v_rvec, void* v_cvec, void* m,
                                    void* p_bf16, long long ld_bf16, long long bf16_batch_stride,
                                    void* scratch, int batch, int R, int C, int row_is_normalized,
                                    float lr, float decay, float eps1, float eps2,
                                    float clip_threshold, float weight_decay, float beta1,
                                    float max_param_scale, int flags, void* stream) {
-  if (batch <= 0 || R <= 0 || C <= 0) return 0;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  float* s = static_cast<float*>(scratch);
-  float* rowsum = s;
-  float* colsum = rowsum + static_cast<long long>(batch) * R;
-  float* rf = colsum + static_cast<long long>(batch) * C;
-  float* cf = rf + static_cast<long long>(batch) * R;
-  AdafactorScalars* scal = reinterpret_cast<AdafactorScalars*>(cf + static_cast<long long>(batch) * C);
-  cudaMemsetAsync(scratch, 0, t5x_adafactor_scratch_floats(batch, R, C) * sizeof(float), st);
-  AfHyper h;
-  h.lr = lr;
-  h.eps2 = eps2;
-  h.clip_threshold = clip_threshold;
-  h.weight_decay = weight_decay;
-  h.beta1 = beta1;
-  h.max_param_scale = max_param_scale;
-  h.multiply_by_parameter_scale = (flags >> 0) & 1;
-  h.use_clip = (flags >> 1) & 1;
-  h.use_wd = (flags >> 2) & 1;
-  h.use_momentum = (flags >> 3) & 1;
-  h.use_max_scale = (flags >> 4) & 1;
-  h.skip_nan = (flags >> 5) & 1;
-  dim3 sgrid((C + kAfTileC - 1) / kAfTileC, (R + kAfTileR - 1) / kAfTileR, batch);
-  if (C % 4 == 0)
-    af_stats_kernel<true><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
-                                                        static_cast<const float*>(p), rowsum,
-                                                        colsum, scal, R, C, eps1);
-  else
-    af_stats_kernel<false><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
-                                                         static_cast<const float*>(p), rowsum,
-                                                         colsum, scal, R, C, eps1);
-  af_factors_kernel<<<batch, 1024, 0, st>>>(static_cast<float*>(v_rvec), static_cast<float*>(v_cvec),
-                                            rowsum, colsum, rf, cf, R, C, decay, row_is_normalized,
-                                            h.skip_nan);
-  const long long n = static_cast<long long>(R) * C;
-  dim3 egrid(af_grid(n), batch);
-  if (h.use_clip)
-    af_usq_kernel<<<egrid, kAfThreads, 0, st>>>(static_cast<const float*>(g), rf, cf, scal, R, C);
-  af_apply_kernel<true><<<egrid, kAfThreads, 0, st>>>(
-      static_cast<float*>(p), static_cast<const float*>(g), rf, cf, nullptr, static_cast<float*>(m),
-      static_cast<__nv_bfloat16*>(p_bf16), ld_bf16, bf16_batch_stride, scal, R, C, h);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return set_error("adafactor_factored: %s", cudaGetErrorString(e));
-  return 0;
+  int rc = t5x_adafactor_stats(p, g, scratch, batch, R, C, eps1, stream);
+  if (rc) return rc;
+  rc = t5x_adafactor_ema(v_rvec, v_cvec, scratch, batch, R, C, R, C, row_is_normalized, decay,
+                         (flags >> 5) & 1, stream);
+  if (rc) return rc;
+  rc = t5x_adafactor_usq(g, v_rvec, v_cvec, scratch, batch, R, C, R, C, row_is_normalized,
+                         (flags >> 1) & 1, stream);
+  if (rc) return rc;
+  return t5x_adafactor_apply(p, g, m, p_bf16, ld_bf16, bf16_batch_stride, scratch, batch, R, C,
+                             static_cast<long long>(R) * C, lr, eps2, clip_threshold, weight_decay,
+                             beta1, max_param_scale, flags, stream);
 }
 
-// Unfactored update of p[batch, R, C] viewed per batch element as R*C numbers (C = bf16 row width).
-// Scratch: batch*4 floats.
+// Unfactored: phase 1 (v update, sum u^2, sum p^2 into scratch[batch*4]) and phase 2 (apply).
+T5X_API int t5x_adafactor_unfactored_stats(const void* p, const void* g, void* v, void* scratch,
+                                           int batch, long long n, float decay, float eps1,
+                                           int skip_nan, void* stream) {
+  if (batch <= 0 || n <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaMemsetAsync(scratch, 0, sizeof(AdafactorScalars) * batch, st);
+  dim3 egrid(af_grid(n), batch);
+  af_unfactored_stats_kernel<<<egrid, kAfThreads, 0, st>>>(
+      static_cast<const float*>(g), static_cast<const float*>(p), static_cast<float*>(v),
+      static_cast<AdafactorScalars*>(scratch), n, decay, eps1, skip_nan);
+  return af_check("adafactor_unfactored_stats");
+}
+
+T5X_API int t5x_adafactor_unfactored_apply(void* p, const void* g, const void* v, void* m,
+                                           void* p_bf16, long long ld_bf16,
+                                           long long bf16_batch_stride, void* scratch, int batch,
+                                           int R, int C, long long n_global, float lr, float eps2,
+                                           float clip_threshold, float weight_decay, float beta1,
+                                           float max_param_scale, int flags, void* stream) {
+  if (batch <= 0) return 0;
+  AfHyper h = af_hyper(lr, eps2, clip_threshold, weight_decay, beta1, max_param_scale, flags);
+  dim3 egrid(af_grid(static_cast<long long>(R) * C), batch);
+  af_apply_kernel<false><<<egrid, kAfThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float*>(p), static_cast<const float*>(g), nullptr, nullptr,
+      static_cast<const float*>(v), static_cast<float*>(m), static_cast<__nv_bfloat16*>(p_bf16),
+      ld_bf16, bf16_batch_stride, static_cast<const AdafactorScalars*>(scratch), R, C,
+      static_cast<float>(n_global), h);
+  return af_check("adafactor_unfactored_apply");
+}
+
+// Unfactored update of p[batch, R, C] on one GPU (C = row width of the bf16 copy).
 T5X_API int t5x_adafactor_unfactored(void* p, const void* g, void* v, void* m, void* p_bf16,
                                      long long ld_bf16, long long bf16_batch_stride, void* scratch,
                                      int batch, int R, int C, float lr, float decay, float eps1,
                                      float eps2, float clip_threshold, float weight_decay,
                                      float beta1, float max_param_scale, int flags, void* stream) {
-  if (batch <= 0 || R <= 0 || C <= 0) return 0;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  AdafactorScalars* scal = static_cast<AdafactorScalars*>(scratch);
-  cudaMemsetAsync(scratch, 0, sizeof(AdafactorScalars) * batch, st);
-  AfHyper h;
-  h.lr = lr;
-  h.eps2 = eps2;
-  h.clip_threshold = clip_threshold;
-  h.weight_decay = weight_decay;
-  h.beta1 = beta1;
-  h.max_param_scale = max_param_scale;
-  h.multiply_by_parameter_scale = (flags >> 0) & 1;
-  h.use_clip = (flags >> 1) & 1;
-  h.use_wd = (flags >> 2) & 1;
-  h.use_momentum = (flags >> 3) & 1;
-  h.use_max_scale = (flags >> 4) & 1;
-  h.skip_nan = (flags >> 5) & 1;
   const long long n = static_cast<long long>(R) * C;
-  dim3 egrid(af_grid(n), batch);
-  af_unfactored_stats_kernel<<<egrid, kAfThreads, 0, st>>>(
-      static_cast<const float*>(g), static_cast<const float*>(p), static_cast<float*>(v), scal, n,
-      decay, eps1, h.skip_nan);
-  af_apply_kernel<false><<<egrid, kAfThreads, 0, st>>>(
-      static_cast<float*>(p), static_cast<const float*>(g), nullptr, nullptr,
-      static_cast<const float*>(v), static_cast<float*>(m), static_cast<__nv_bfloat16*>(p_bf16),
-      ld_bf16, bf16_batch_stride, scal, R, C, h);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return set_error("adafactor_unfactored: %s", cudaGetErrorString(e));
-  return 0;
+  int rc = t5x_adafactor_unfactored_stats(p, g, v, scratch, batch, n, decay, eps1, (flags >> 5) & 1,
+                                          stream);
+  if (rc) return rc;
+  return t5x_adafactor_unfactored_apply(p, g, v, m, p_bf16, ld_bf16, bf16_batch_stride, scratch,
+                                        batch, R, C, n, lr, eps2, clip_threshold, weight_decay,
+                                        beta1, max_param_scale, flags, stream);
 }

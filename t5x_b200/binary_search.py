@@ -1,0 +1,73 @@
+"""Top-k / top-p masking (API of t5x/binary_search.py).
+
+The reference finds the per-row cutoff with a 32-step bitwise binary search over the float
+total order, because XLA lacks a cheap partial sort. Here the cutoff comes from a sort /
+top-k on the device; the bit-search helpers are kept with the same contracts for callers
+that use them directly.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+
+
+def int32_bsearch(batch_shape, predicate: Callable[[torch.Tensor], torch.Tensor],
+                  device=None) -> torch.Tensor:
+  """Largest int32 `x` per batch element with predicate(x) true, assuming the predicate is
+  monotone (true up to some threshold) (t5x/binary_search.py:28-71)."""
+  # Decide the sign bit first, then the remaining 31 bits from the top.
+  zero = torch.zeros(batch_shape, dtype=torch.int64, device=device)
+  nonneg = predicate(zero.to(torch.int32))
+  current = torch.where(nonneg, zero, torch.full_like(zero, -(2 ** 31)))
+  for bit in range(30, -1, -1):
+    cand = current + (1 << bit)
+    ok = predicate(cand.to(torch.int32))
+    current = torch.where(ok, cand, current)
+  return current.to(torch.int32)
+
+
+def _monotonic_int32_to_float32(x: torch.Tensor) -> torch.Tensor:
+  x = x.to(torch.int32)
+  flipped = torch.where(x < 0, x ^ 0x7FFFFFFF, x)
+  return flipped.view(torch.float32)
+
+
+def _monotonic_float32_to_int32(x: torch.Tensor) -> torch.Tensor:
+  i = x.to(torch.float32).contiguous().view(torch.int32)
+  return torch.where(i < 0, i ^ 0x7FFFFFFF, i)
+
+
+def float32_bsearch(batch_shape, predicate: Callable[[torch.Tensor], torch.Tensor],
+                    device=None) -> torch.Tensor:
+  """Largest float32 per batch element for which the monotone predicate holds
+  (t5x/binary_search.py:121-164)."""
+  res = int32_bsearch(batch_shape, lambda i: predicate(_monotonic_int32_to_float32(i)),
+                      device=device)
+  return _monotonic_int32_to_float32(res)
+
+
+def topk_mask(x: torch.Tensor, k: int, replace_val) -> torch.Tensor:
+  """Keeps the k largest entries of each row; the rest become `replace_val`. Entries equal
+  to the k-th value are all kept (t5x/binary_search.py:167-227)."""
+  k = min(int(k), x.shape[-1])
+  kth = torch.topk(x, k, dim=-1).values[..., -1:]
+  return torch.where(x >= kth, x, torch.full_like(x, replace_val))
+
+
+def topp_mask(logits: torch.Tensor, p, replace_val) -> torch.Tensor:
+  """Nucleus mask: keeps the smallest set of top logits whose probability mass reaches `p`
+  (entries tied with the cutoff are kept) (t5x/binary_search.py:230-299)."""
+  probs = torch.softmax(logits.float(), dim=-1)
+  sorted_probs, order = torch.sort(probs, dim=-1, descending=True)
+  cum = torch.cumsum(sorted_probs, dim=-1)
+  p_t = torch.as_tensor(p, dtype=torch.float32, device=logits.device)
+  if p_t.dim() > 0:
+    p_t = p_t.reshape(-1, *([1] * (logits.dim() - 1)))
+  # index of the first position where the cumulative mass reaches p
+  reached = (cum >= p_t).float()
+  first = reached.argmax(dim=-1, keepdim=True)
+  none_reached = reached.sum(dim=-1, keepdim=True) == 0
+  first = torch.where(none_reached, torch.full_like(first, logits.shape[-1] - 1), first)
+  cutoff_prob = torch.gather(sorted_probs, -1, first)
+  return torch.where(probs >= cutoff_prob, logits, torch.full_like(logits, replace_val))

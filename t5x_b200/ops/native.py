@@ -68,6 +68,20 @@ def _declare(lib):
   lib.t5x_adafactor_unfactored.argtypes = [
       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_int, c_int, c_int,
       c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_float, c_int, c_void_p]
+  lib.t5x_adafactor_stats.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                      c_void_p]
+  lib.t5x_adafactor_ema.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                    c_int, c_int, c_float, c_int, c_void_p]
+  lib.t5x_adafactor_usq.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                    c_int, c_int, c_int, c_int, c_void_p]
+  lib.t5x_adafactor_apply.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll,
+                                      c_void_p, c_int, c_int, c_int, c_ll, c_float, c_float,
+                                      c_float, c_float, c_float, c_float, c_int, c_void_p]
+  lib.t5x_adafactor_unfactored_stats.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_ll, c_float, c_float, c_int, c_void_p]
+  lib.t5x_adafactor_unfactored_apply.argtypes = [
+      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_int, c_int, c_int,
+      c_ll, c_float, c_float, c_float, c_float, c_float, c_float, c_int, c_void_p]
   return lib
 
 
@@ -341,3 +355,48 @@ def adafactor_unfactored_(p, g, v, m, p_bf16, scratch, *, batch, rows, cols, lr,
       p.data_ptr(), g.data_ptr(), v.data_ptr(), ptr(m), ptr(p_bf16), ld_bf16, bf16_batch_stride,
       scratch.data_ptr(), batch, rows, cols, lr, decay, eps1, eps2, clip_threshold, weight_decay,
       beta1, max_param_scale, flags, stream_ptr()), "adafactor_unfactored")
+
+
+def adafactor_stats_(p, g, scratch, batch, rows, cols, eps1) -> None:
+  _check(lib().t5x_adafactor_stats(p.data_ptr(), g.data_ptr(), scratch.data_ptr(), batch, rows,
+                                   cols, eps1, stream_ptr()), "adafactor_stats")
+
+
+def adafactor_ema_(v_rvec, v_cvec, scratch, batch, rows, cols, global_rows, global_cols,
+                   row_is_normalized, decay, skip_nan) -> None:
+  _check(lib().t5x_adafactor_ema(v_rvec.data_ptr(), v_cvec.data_ptr(), scratch.data_ptr(), batch,
+                                 rows, cols, global_rows, global_cols, int(row_is_normalized),
+                                 decay, int(skip_nan), stream_ptr()), "adafactor_ema")
+
+
+def adafactor_usq_(g, v_rvec, v_cvec, scratch, batch, rows, cols, global_rows, global_cols,
+                   row_is_normalized, use_clip) -> None:
+  _check(lib().t5x_adafactor_usq(g.data_ptr(), v_rvec.data_ptr(), v_cvec.data_ptr(),
+                                 scratch.data_ptr(), batch, rows, cols, global_rows, global_cols,
+                                 int(row_is_normalized), int(use_clip), stream_ptr()),
+         "adafactor_usq")
+
+
+def adafactor_apply_(p, g, m, p_bf16, scratch, batch, rows, cols, n_global, *, lr, eps2,
+                     clip_threshold, weight_decay, beta1, max_param_scale, flags, ld_bf16=0,
+                     bf16_batch_stride=0) -> None:
+  _check(lib().t5x_adafactor_apply(p.data_ptr(), g.data_ptr(), ptr(m), ptr(p_bf16), ld_bf16,
+                                   bf16_batch_stride, scratch.data_ptr(), batch, rows, cols,
+                                   n_global, lr, eps2, clip_threshold, weight_decay, beta1,
+                                   max_param_scale, flags, stream_ptr()), "adafactor_apply")
+
+
+def adafactor_unfactored_stats_(p, g, v, scratch, batch, n, decay, eps1, skip_nan) -> None:
+  _check(lib().t5x_adafactor_unfactored_stats(p.data_ptr(), g.data_ptr(), v.data_ptr(),
+                                              scratch.data_ptr(), batch, n, decay, eps1,
+                                              int(skip_nan), stream_ptr()),
+         "adafactor_unfactored_stats")
+
+
+def adafactor_unfactored_apply_(p, g, v, m, p_bf16, scratch, batch, rows, cols, n_global, *, lr,
+                                eps2, clip_threshold, weight_decay, beta1, max_param_scale, flags,
+                                ld_bf16=0, bf16_batch_stride=0) -> None:
+  _check(lib().t5x_adafactor_unfactored_apply(
+      p.data_ptr(), g.data_ptr(), v.data_ptr(), ptr(m), ptr(p_bf16), ld_bf16, bf16_batch_stride,
+      scratch.data_ptr(), batch, rows, cols, n_global, lr, eps2, clip_threshold, weight_decay,
+      beta1, max_param_scale, flags, stream_ptr()), "adafactor_unfactored_apply")

@@ -144,11 +144,34 @@ def token_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, z_loss: flo
   return loss, z, lse, lf.argmax(-1)
 
 
+_DROPOUT_GENERATORS: dict = {}
+
+
+def set_dropout_seed(seed: Optional[int]) -> None:
+  """Seeds the generators used by `dropout` (one per device); None returns to global RNG."""
+  _DROPOUT_GENERATORS.clear()
+  if seed is not None:
+    _DROPOUT_GENERATORS["seed"] = int(seed)
+
+
+def _dropout_generator(device) -> Optional[torch.Generator]:
+  if "seed" not in _DROPOUT_GENERATORS:
+    return None
+  key = str(device)
+  if key not in _DROPOUT_GENERATORS:
+    g = torch.Generator(device=device)
+    g.manual_seed(_DROPOUT_GENERATORS["seed"])
+    _DROPOUT_GENERATORS[key] = g
+  return _DROPOUT_GENERATORS[key]
+
+
 def dropout(x: torch.Tensor, rate: float, training: bool, broadcast_dims=(),
             generator: Optional[torch.Generator] = None) -> torch.Tensor:
   """Dropout whose mask is shared along `broadcast_dims` (flax nn.Dropout semantics)."""
   if not training or rate == 0.0:
     return x
+  if generator is None:
+    generator = _dropout_generator(x.device)
   shape = list(x.shape)
   for d in broadcast_dims:
     shape[d] = 1
