@@ -357,6 +357,7 @@ T5X_API int t5x_adafactor_stats(const void* p, const void* g, void* scratch, int
     af_stats_kernel<false><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
                                                          static_cast<const float*>(p), a.rowsum,
                                                          a.colsum, a.scal, R, C, eps1);
+  count_launches(1);
   return af_check("adafactor_stats");
 }
 
@@ -371,6 +372,7 @@ T5X_API int t5x_adafactor_ema(void* v_rvec, void* v_cvec, void* scratch, int bat
       static_cast<float*>(v_rvec), static_cast<float*>(v_cvec), a.rowsum, a.colsum, a.scal, R, C,
       static_cast<float>(global_C), static_cast<float>(global_R), decay, row_is_normalized,
       skip_nan);
+  count_launches(1);
   return af_check("adafactor_ema");
 }
 
@@ -389,6 +391,7 @@ T5X_API int t5x_adafactor_usq(const void* g, const void* v_rvec, const void* v_c
     af_usq_kernel<<<egrid, kAfThreads, 0, st>>>(static_cast<const float*>(g), a.rf, a.cf, a.scal,
                                                 R, C);
   }
+  count_launches(use_clip ? 2 : 1);
   return af_check("adafactor_usq");
 }
 
@@ -407,6 +410,7 @@ T5X_API int t5x_adafactor_apply(void* p, const void* g, void* m, void* p_bf16, l
       static_cast<float*>(p), static_cast<const float*>(g), a.rf, a.cf, nullptr,
       static_cast<float*>(m), static_cast<__nv_bfloat16*>(p_bf16), ld_bf16, bf16_batch_stride,
       a.scal, R, C, static_cast<float>(n_global), h);
+  count_launches(1);
   return af_check("adafactor_apply");
 }
 
@@ -442,6 +446,7 @@ T5X_API int t5x_adafactor_unfactored_stats(const void* p, const void* g, void* v
   af_unfactored_stats_kernel<<<egrid, kAfThreads, 0, st>>>(
       static_cast<const float*>(g), static_cast<const float*>(p), static_cast<float*>(v),
       static_cast<AdafactorScalars*>(scratch), n, decay, eps1, skip_nan);
+  count_launches(1);
   return af_check("adafactor_unfactored_stats");
 }
 
@@ -459,6 +464,7 @@ T5X_API int t5x_adafactor_unfactored_apply(void* p, const void* g, const void* v
       static_cast<const float*>(v), static_cast<float*>(m), static_cast<__nv_bfloat16*>(p_bf16),
       ld_bf16, bf16_batch_stride, static_cast<const AdafactorScalars*>(scratch), R, C,
       static_cast<float>(n_global), h);
+  count_launches(1);
   return af_check("adafactor_unfactored_apply");
 }
 

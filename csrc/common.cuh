@@ -278,5 +278,6 @@ const CUtensorMap* get_tensor_map(const void* base, int elem_bytes, int rank, co
                                   const uint64_t* strides_bytes, const uint32_t* box,
                                   int swizzle_128b);
 int* device_status_buffer();  // per-device status words (zero on success)
+void count_launches(int n);     // bookkeeping: kernels launched by this library
 int num_sms();
 }  // namespace t5x

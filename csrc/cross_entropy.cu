@@ -148,6 +148,7 @@ T5X_API int t5x_ce_stats(const void* logits, int logits_fp32, const void* target
         static_cast<const __nv_bfloat16*>(logits), static_cast<const long long*>(targets),
         static_cast<float4*>(stats), static_cast<float*>(arg_val), static_cast<int*>(arg_idx), rows,
         vocab_local, ld, vocab_start);
+  count_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("ce_stats: %s", cudaGetErrorString(e));
   return 0;
@@ -172,6 +173,7 @@ T5X_API int t5x_ce_grad(const void* logits, int logits_fp32, const void* targets
         static_cast<const float*>(lse), static_cast<const float*>(row_scale),
         static_cast<__nv_bfloat16*>(dlogits), rows, vocab_local, ld, ldd, vocab_start, z_loss,
         confidence, low_confidence);
+  count_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("ce_grad: %s", cudaGetErrorString(e));
   return 0;

@@ -296,6 +296,7 @@ using namespace t5x;
 
 #define CHECK_LAUNCH(name)                                                           \
   do {                                                                               \
+    count_launches(1);                                                               \
     cudaError_t e__ = cudaGetLastError();                                            \
     if (e__ != cudaSuccess) return set_error(name ": %s", cudaGetErrorString(e__)); \
   } while (0)

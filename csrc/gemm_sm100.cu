@@ -403,6 +403,7 @@ static int launch_gemm(const CUtensorMap* tA, const CUtensorMap* tB, const CUten
   if (max_ctas > 0) grid = std::min(grid, max_ctas);
   if (grid <= 0) return 0;
   gemm_bf16_kernel<BN, EPI><<<grid, kGemmThreads, S::kTotal, stream>>>(*tA, *tB, *tB2, p);
+  count_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("gemm launch failed: %s", cudaGetErrorString(e));
   return 0;

@@ -1,6 +1,7 @@
 // Host runtime shared by all kernels: error strings, the per-device status
 // buffer that bounded waits report into, device properties and the tensor-map
 // (TMA descriptor) cache.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -146,6 +147,10 @@ static DeviceState& dev_state() {
   return s;
 }
 
+static std::atomic<long long> g_launches{0};
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
+
 int* device_status_buffer() { return dev_state().status; }
 int num_sms() { return dev_state().sms; }
 
@@ -167,6 +172,9 @@ T5X_API int t5x_read_status(int* out, void* stream) {
   if (out) memcpy(out, host, sizeof(host));
   return host[0];
 }
+
+// Number of kernels this library has launched in this process (all devices).
+T5X_API long long t5x_launch_count() { return t5x::launches(); }
 
 T5X_API int t5x_num_sms() { return t5x::num_sms(); }
 T5X_API int t5x_abi_version() { return 1; }

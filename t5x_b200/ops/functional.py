@@ -217,10 +217,45 @@ def attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None, bidirection
     rb = ref.relative_position_bias(bias_table.float(), q.shape[1], k.shape[1], bidirectional,
                                     num_buckets, max_distance, q_offset=q_offset)
     bias = rb if bias is None else bias + rb
+  if q.is_cuda and q.dtype == torch.bfloat16 and not float32_logits:
+    return _library_attention(q, k, v, bias, key_mask, causal, q_segment_ids, kv_segment_ids,
+                              extra_mask)
   return ref.attention(q, k, v, bias=bias, key_mask=key_mask, causal=causal,
                        q_segment_ids=q_segment_ids, kv_segment_ids=kv_segment_ids,
                        extra_mask=extra_mask,
                        float32_logits=float32_logits or q.dtype == torch.float32)
+
+
+def _library_attention(q, k, v, bias, key_mask, causal, q_seg, kv_seg, extra_mask):
+  """Library (torch SDPA) attention for shapes the flash kernels do not cover yet: bias and
+  masks are folded into one additive [B or 1, H or 1, Lq, Lk] tensor."""
+  b, lq, h, d = q.shape
+  lk = k.shape[1]
+  add = None
+  if bias is not None:
+    add = bias.to(q.dtype)
+    add = add[None] if add.dim() == 3 else add
+  mask = None
+  if key_mask is not None:
+    mask = key_mask[:, None, None, :].bool()
+  if causal:
+    cm = (torch.arange(lk, device=q.device)[None, :] <=
+          torch.arange(lq, device=q.device)[:, None] + (lk - lq))[None, None]
+    mask = cm if mask is None else mask & cm
+  if q_seg is not None and kv_seg is not None:
+    sm = q_seg[:, None, :, None] == kv_seg[:, None, None, :]
+    mask = sm if mask is None else mask & sm
+  if extra_mask is not None:
+    mask = extra_mask.bool() if mask is None else mask & extra_mask.bool()
+  if mask is not None:
+    neg = torch.zeros(mask.shape, dtype=q.dtype, device=q.device).masked_fill_(~mask, -1e10)
+    add = neg if add is None else add + neg
+  if add is not None and lk % 8:
+    pad = 8 - lk % 8  # the library kernels want the bias rows 16-byte aligned
+    add = torch.nn.functional.pad(add.expand(-1, -1, lq, lk), (0, pad))[..., :lk]
+  out = torch.nn.functional.scaled_dot_product_attention(
+      q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=add, scale=1.0)
+  return out.transpose(1, 2)
 
 
 # ----------------------------------------------------------------------------

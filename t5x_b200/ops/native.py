@@ -40,6 +40,7 @@ c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlon
 
 def _declare(lib):
   lib.t5x_last_error.restype = ctypes.c_char_p
+  lib.t5x_launch_count.restype = c_ll
   lib.t5x_read_status.argtypes = [ctypes.POINTER(c_int), c_void_p]
   lib.t5x_gemm_bf16.argtypes = [
       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll,
@@ -119,6 +120,11 @@ def register_signature(name: str, argtypes) -> None:
   _OPTIONAL_SIGNATURES[name] = argtypes
   if _lib is not None and hasattr(_lib, name):
     getattr(_lib, name).argtypes = argtypes
+
+
+def launch_count() -> int:
+  """Kernels launched by the native library so far in this process."""
+  return int(lib().t5x_launch_count())
 
 
 def use_native(t: torch.Tensor) -> bool:

@@ -1,0 +1,181 @@
+"""Numerics of every sm_100a kernel against fp32 PyTorch statements of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+  a, b = a.float(), b.float()
+  return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(scope="module")
+def N():
+  from t5x_b200.ops import native
+  assert torch.cuda.is_available()
+  native.lib()
+  return native
+
+
+BF16_TOL = 4e-3
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (128, 256, 64), (256, 256, 128), (384, 512, 320),
+                                   (304, 200, 136), (1000, 264, 72), (2048, 1280, 1024)])
+@pytest.mark.parametrize("ta", [0, 1])
+@pytest.mark.parametrize("tb", [0, 1])
+def test_gemm_layouts(N, shape, ta, tb):
+  M, Nn, K = shape
+  torch.manual_seed(0)
+  A = torch.randn(K, M, device="cuda").bfloat16().t() if ta else torch.randn(M, K, device="cuda").bfloat16()
+  B = torch.randn(Nn, K, device="cuda").bfloat16().t() if tb else torch.randn(K, Nn, device="cuda").bfloat16()
+  C = N.gemm(A, B)
+  N.check_status()
+  assert rel(C, A.float() @ B.float()) < BF16_TOL
+
+
+def test_gemm_epilogues(N):
+  torch.manual_seed(1)
+  M, Nn, K = 512, 384, 256
+  A = torch.randn(M, K, device="cuda").bfloat16()
+  B = (torch.randn(K, Nn, device="cuda") * 0.1).bfloat16()
+  R = torch.randn(M, Nn, device="cuda").bfloat16()
+  ref = A.float() @ B.float()
+  assert rel(N.gemm(A, B, residual=R), ref + R.float()) < BF16_TOL
+  Cf = torch.ones(M, Nn, device="cuda")
+  N.gemm(A, B, out=Cf, accumulate=True)
+  assert rel(Cf, ref + 1) < 1e-5
+  assert rel(N.gemm(A, B, out_dtype=torch.float32), ref) < 1e-5
+  assert rel(N.gemm(A, B, out_dtype=torch.float32, alpha=0.5), 0.5 * ref) < 1e-5
+  W = (torch.randn(K, 2 * Nn, device="cuda") * 0.1).bfloat16()
+  H = torch.empty(M, 2 * Nn, device="cuda", dtype=torch.bfloat16)
+  G = N.gemm(A, W[:, :Nn], b2=W[:, Nn:], save_h=H)
+  h = A.float() @ W.float()
+  assert rel(G, torch.nn.functional.gelu(h[:, :Nn], approximate="tanh") * h[:, Nn:]) < BF16_TOL
+  assert rel(H, h) < BF16_TOL
+  Ab = torch.randn(3, 200, 128, device="cuda").bfloat16()
+  Bb = torch.randn(3, 128, 136, device="cuda").bfloat16()
+  assert rel(N.gemm(Ab, Bb), Ab.float() @ Bb.float()) < BF16_TOL
+  # strided output (a column slice of a wider matrix)
+  wide = torch.zeros(M, 3 * Nn, device="cuda", dtype=torch.bfloat16)
+  N.gemm(A, B, out=wide[:, Nn:2 * Nn])
+  assert rel(wide[:, Nn:2 * Nn], ref) < BF16_TOL and float(wide[:, :Nn].abs().max()) == 0.0
+  N.check_status()
+
+
+def test_rmsnorm(N):
+  torch.manual_seed(2)
+  for T, d in [(1000, 4096), (77, 512), (33, 768)]:
+    x = torch.randn(T, d, device="cuda").bfloat16()
+    sc = torch.rand(d, device="cuda") + 0.5
+    y, rstd = N.rmsnorm_fwd(x, sc, 1e-6)
+    xf = x.float().requires_grad_(True)
+    scp = sc.clone().requires_grad_(True)
+    yr = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-6) * scp
+    assert rel(y, yr) < BF16_TOL
+    dy = torch.randn(T, d, device="cuda").bfloat16()
+    dres = torch.randn(T, d, device="cuda").bfloat16()
+    yr.backward(dy.float())
+    dsc = torch.zeros(d, device="cuda")
+    dx = N.rmsnorm_bwd(dy, x, sc, rstd, dres, dsc)
+    assert rel(dx, xf.grad + dres.float()) < BF16_TOL
+    assert rel(dsc, scp.grad) < 1e-4
+
+
+def test_gated_gelu(N):
+  torch.manual_seed(3)
+  T, dff = 300, 2048
+  h = torch.randn(T, 2 * dff, device="cuda").bfloat16()
+  dg = torch.randn(T, dff, device="cuda").bfloat16()
+  hf = h.float().requires_grad_(True)
+  g = torch.nn.functional.gelu(hf[:, :dff], approximate="tanh") * hf[:, dff:]
+  g.backward(dg.float())
+  assert rel(N.gated_gelu_fwd(h), g) < BF16_TOL
+  hh, dgg = h.clone(), dg.clone()
+  N.gated_gelu_bwd_(dgg, hh, True)
+  assert rel(hh, hf.grad) < BF16_TOL and rel(dgg, g) < BF16_TOL
+
+
+def test_embedding(N):
+  torch.manual_seed(4)
+  V, d = 5000, 512
+  tab = torch.randn(V, d, device="cuda").bfloat16()
+  ids = torch.randint(0, V, (7, 33), device="cuda")
+  assert rel(N.embedding_fwd(ids, tab), tab[ids]) == 0.0
+  dt = torch.zeros(V, d, device="cuda")
+  do = torch.randn(7, 33, d, device="cuda").bfloat16()
+  N.embedding_bwd_(ids, do, dt)
+  ref = torch.zeros(V, d, device="cuda").index_add_(0, ids.view(-1), do.view(-1, d).float())
+  assert rel(dt, ref) < 1e-6
+  # vocab-parallel slice: ids outside [start, start+rows) give zeros
+  part = N.embedding_fwd(ids, tab[1000:3000].contiguous(), vocab_start=1000)
+  own = ((ids >= 1000) & (ids < 3000))[..., None]
+  assert rel(part, tab[ids] * own) == 0.0
+
+
+def test_cross_entropy(N):
+  torch.manual_seed(5)
+  T, V = 300, 32128
+  lg = torch.randn(T, V, device="cuda") * 3
+  tg = torch.randint(0, V, (T,), device="cuda")
+  st, av, ai = N.ce_stats(lg, tg)
+  lse = st[:, 0] + torch.log(st[:, 1])
+  assert rel(lse, torch.logsumexp(lg, -1)) < 1e-6
+  assert rel(st[:, 2], lg.gather(1, tg[:, None]).squeeze()) == 0.0
+  assert bool((ai.long() == lg.argmax(-1)).all())
+  rs = torch.rand(T, device="cuda")
+  dl = N.ce_grad(lg, tg, lse, rs, 1e-4, 1.0, 0.0)
+  lgr = lg.clone().requires_grad_(True)
+  l2 = torch.logsumexp(lgr, -1)
+  ((l2 - lgr.gather(1, tg[:, None]).squeeze() + 1e-4 * l2 * l2) * rs).sum().backward()
+  assert rel(dl, lgr.grad) < BF16_TOL
+
+
+@pytest.mark.parametrize("shape", [(512, 1024, 1), (1024, 512, 0), (300, 260, 1), (130, 32128, 1)])
+def test_adafactor_factored(N, shape):
+  R, C, norm = shape
+  torch.manual_seed(6)
+  p = torch.randn(R, C, device="cuda") * 0.05
+  g = torch.randn(R, C, device="cuda") * 0.01
+  vr = torch.rand(R, device="cuda") * 1e-4
+  vc = torch.rand(C, device="cuda") * 1e-4
+  pb = torch.empty(R, C, device="cuda", dtype=torch.bfloat16)
+  scratch = torch.empty(N.adafactor_scratch_floats(1, R, C), device="cuda")
+  decay, lr = 0.8, 0.01
+  p0, vr0, vc0 = p.clone(), vr.clone(), vc.clone()
+  N.adafactor_factored_(p, g, vr, vc, None, pb, scratch, batch=1, rows=R, cols=C,
+                        row_is_normalized=norm, lr=lr, decay=decay, eps1=1e-30, eps2=1e-3,
+                        clip_threshold=1.0, weight_decay=0.0, beta1=0.0, max_param_scale=0.0,
+                        flags=N.AF_PARAM_SCALE | N.AF_CLIP, ld_bf16=C)
+  gs = g * g + 1e-30
+  nvr = decay * vr0 + (1 - decay) * gs.mean(1)
+  nvc = decay * vc0 + (1 - decay) * gs.mean(0)
+  if norm:
+    rf, cf = (nvr / nvr.mean()) ** -0.5, nvc ** -0.5
+  else:
+    rf, cf = nvr ** -0.5, (nvc / nvc.mean()) ** -0.5
+  u = g * rf[:, None] * cf[None, :]
+  u = u / torch.clamp(u.pow(2).mean().sqrt(), min=1.0)
+  pn = p0 - lr * torch.clamp(p0.pow(2).mean().sqrt(), min=1e-3) * u
+  assert rel(p, pn) < 1e-5 and rel(vr, nvr) < 1e-5 and rel(vc, nvc) < 1e-5
+  assert rel(pb, pn) < BF16_TOL
+  N.check_status()
+
+
+def test_adafactor_unfactored(N):
+  torch.manual_seed(7)
+  n = 5000
+  p = torch.randn(1, n, device="cuda")
+  g = torch.randn(1, n, device="cuda") * 0.1
+  v = torch.rand(1, n, device="cuda") * 1e-3
+  p0, v0 = p.clone(), v.clone()
+  scratch = torch.empty(8, device="cuda")
+  N.adafactor_unfactored_(p, g, v, None, None, scratch, batch=1, rows=1, cols=n, lr=0.01,
+                          decay=0.8, eps1=1e-30, eps2=1e-3, clip_threshold=1.0, weight_decay=0.0,
+                          beta1=0.0, max_param_scale=0.0, flags=N.AF_PARAM_SCALE | N.AF_CLIP)
+  nv = 0.8 * v0 + 0.2 * (g * g + 1e-30)
+  u = g * nv ** -0.5
+  u = u / torch.clamp(u.pow(2).mean().sqrt(), min=1.0)
+  pn = p0 - 0.01 * torch.clamp(p0.pow(2).mean().sqrt(), min=1e-3) * u
+  assert rel(p, pn) < 1e-5 and rel(v, nv) < 1e-5
