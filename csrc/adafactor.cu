@@ -12,7 +12,10 @@
 // The unfactored form (vectors, small matrices) keeps a full second moment and needs
 // two kernels. Scratch (rowsum/colsum/factor vectors/scalars) is provided by the caller
 // and must be zero on entry to `stats`.
+#include <mutex>
+
 #include "common.cuh"
+#include "t5x_b200.h"
 
 namespace t5x {
 
@@ -481,4 +484,112 @@ T5X_API int t5x_adafactor_unfactored(void* p, const void* g, void* v, void* m, v
   return t5x_adafactor_unfactored_apply(p, g, v, m, p_bf16, ld_bf16, bf16_batch_stride, scratch,
                                         batch, R, C, n, lr, eps2, clip_threshold, weight_decay,
                                         beta1, max_param_scale, flags, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of t5x_adafactor_factored (declared in t5x_b200.h).
+//
+// Some hosts of this library may not allocate device memory at the point where they step the
+// optimizer: a caller that has handed the whole device heap to its own pool or arena, one that
+// runs the update from a callback in which cudaMalloc is off limits (it synchronises the
+// device), or a plain C program that links this .so without any tensor library to allocate
+// with. For them the scratch (row/column sums, factor vectors, three scalars per batch
+// element) lives in the fixed device array below instead of a caller-provided buffer.
+// ---------------------------------------------------------------------------------------
+namespace t5x {
+
+constexpr long long kAfStaticScratchFloats = 1ll << 20;  // 4 MiB per GPU that loads this library
+static __device__ __align__(256) float g_af_static_scratch[kAfStaticScratchFloats];
+
+struct AfStaticDevice {
+  float* scratch = nullptr;  // device address of g_af_static_scratch on this device
+  int sms = 0;
+};
+static AfStaticDevice g_af_static[64];
+static std::mutex g_af_static_mu;
+
+// Looks up (once per device, with that device current) the device address of the static array.
+// In host code the array's name is only a handle for the runtime, never a pointer a kernel may
+// receive, so the address has to come from cudaGetSymbolAddress.
+static int af_static_setup(AfStaticDevice** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_error("adafactor_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return set_error("adafactor_static: device %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_af_static_mu);
+  AfStaticDevice& d = g_af_static[dev];
+  if (d.scratch == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_af_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return set_error("adafactor_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || sms <= 0)
+      return set_error("adafactor_static: SM count query: %s", cudaGetErrorString(e));
+    d.sms = sms;
+    d.scratch = static_cast<float*>(ptr);
+  }
+  *out = &d;
+  return 0;
+}
+
+}  // namespace t5x
+
+T5X_API long long t5x_adafactor_factored_static_max_floats() { return t5x::kAfStaticScratchFloats; }
+
+T5X_API int t5x_adafactor_factored_static(void* p, const void* g, void* v_rvec, void* v_cvec,
+                                          void* m, void* p_bf16, long long ld_bf16,
+                                          long long bf16_batch_stride, int batch, int R, int C,
+                                          int row_is_normalized, float lr, float decay, float eps1,
+                                          float eps2, float clip_threshold, float weight_decay,
+                                          float beta1, float max_param_scale, int flags,
+                                          void* stream) {
+  if (batch <= 0 || R <= 0 || C <= 0) return 0;
+  const long long need = t5x_adafactor_scratch_floats(batch, R, C);
+  if (need > kAfStaticScratchFloats)
+    return set_error(
+        "adafactor_static: batch=%d rows=%d cols=%d needs %lld scratch floats but the built-in "
+        "scratch holds %lld; use t5x_adafactor_factored with a caller-provided buffer",
+        batch, R, C, need, kAfStaticScratchFloats);
+  AfStaticDevice* d = nullptr;
+  if (int rc = af_static_setup(&d)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  AfScratch a = af_split(d->scratch, batch, R, C);
+  AfHyper h = af_hyper(lr, eps2, clip_threshold, weight_decay, beta1, max_param_scale, flags);
+  // The array keeps whatever the previous call left: the sums and scalars must start at zero.
+  cudaError_t e = cudaMemsetAsync(d->scratch, 0, need * sizeof(float), st);
+  if (e != cudaSuccess) return set_error("adafactor_static: memset: %s", cudaGetErrorString(e));
+  dim3 sgrid((C + kAfTileC - 1) / kAfTileC, (R + kAfTileR - 1) / kAfTileR, batch);
+  if (C % 4 == 0)
+    af_stats_kernel<true><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
+                                                        static_cast<const float*>(p), a.rowsum,
+                                                        a.colsum, a.scal, R, C, eps1);
+  else
+    af_stats_kernel<false><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
+                                                         static_cast<const float*>(p), a.rowsum,
+                                                         a.colsum, a.scal, R, C, eps1);
+  af_ema_kernel<<<batch, 1024, 0, st>>>(static_cast<float*>(v_rvec), static_cast<float*>(v_cvec),
+                                        a.rowsum, a.colsum, a.scal, R, C, static_cast<float>(C),
+                                        static_cast<float>(R), decay, row_is_normalized, h.skip_nan);
+  af_finalize_kernel<<<batch, 1024, 0, st>>>(
+      static_cast<const float*>(v_rvec), static_cast<const float*>(v_cvec), a.rf, a.cf, a.scal, R,
+      C, static_cast<float>(row_is_normalized ? R : C), row_is_normalized);
+  const long long n = static_cast<long long>(R) * C;
+  long long blocks = (n + kAfThreads * 4 - 1) / (kAfThreads * 4);
+  const long long cap = static_cast<long long>(d->sms) * 8;
+  blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
+  dim3 egrid(static_cast<unsigned>(blocks), batch);
+  int launched = 3;
+  if (h.use_clip) {
+    af_usq_kernel<<<egrid, kAfThreads, 0, st>>>(static_cast<const float*>(g), a.rf, a.cf, a.scal,
+                                                R, C);
+    ++launched;
+  }
+  af_apply_kernel<true><<<egrid, kAfThreads, 0, st>>>(
+      static_cast<float*>(p), static_cast<const float*>(g), a.rf, a.cf, nullptr,
+      static_cast<float*>(m), static_cast<__nv_bfloat16*>(p_bf16), ld_bf16, bf16_batch_stride,
+      a.scal, R, C, static_cast<float>(n), h);
+  count_launches(launched + 1);
+  return af_check("adafactor_factored_static");
 }
