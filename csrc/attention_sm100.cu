@@ -76,7 +76,8 @@ struct FwdSmem {
   static constexpr int kP = kV + 4 * kTile;     // 2 buffers x 2 tiles
   static constexpr int kRel = kP + 4 * kTile;   // (512 + 128) floats
   static constexpr int kStat = kRel + 640 * 4;  // 128 x 2 floats (row max halves), then sums
-  static constexpr int kBars = kStat + 128 * 4 * 4;
+  static constexpr int kKeySeg = kStat + 128 * 4 * 4;  // 512 ints: segment id of key k, -1 = hidden
+  static constexpr int kBars = kKeySeg + 512 * 4;
   static constexpr int kTotal = kBars + 256 + 1024;
 };
 
@@ -92,6 +93,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   uint8_t* sP = smem + FwdSmem::kP;
   float* sRel = reinterpret_cast<float*>(smem + FwdSmem::kRel);
   float* sStat = reinterpret_cast<float*>(smem + FwdSmem::kStat);
+  int* sKeySeg = reinterpret_cast<int*>(smem + FwdSmem::kKeySeg);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FwdSmem::kBars);
   uint64_t* bar_q = bars;           // 1
   uint64_t* bar_k = bars + 1;       // 4
@@ -130,6 +132,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       const int idx = t - 127 - q0 + p.rel_off;
       sRel[t] = (idx >= 0 && idx < p.nrel) ? tab[idx] : 0.f;
     }
+  }
+  // Per-key metadata: segment id (0 when unpacked), -1 for padded / out-of-range keys.
+  for (int k = threadIdx.x; k < 512; k += kAttnThreads) {
+    int sgm = -1;
+    if (k < p.Lk) {
+      const long long off = static_cast<long long>(b) * p.Lk + k;
+      sgm = p.kv_seg ? p.kv_seg[off] : 0;
+      if (p.key_mask && p.key_mask[off] == 0) sgm = -1;
+    }
+    sKeySeg[k] = sgm;
   }
   tc_fence_before();
   __syncthreads();
@@ -192,36 +204,51 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const int qseg = (p.q_seg != nullptr && q < p.Lq) ? p.q_seg[b * p.Lq + q] : 0;
     const int kmax = p.causal ? q + p.causal_off : 0x7fffffff;
-    const uint8_t* kmask = p.key_mask ? p.key_mask + static_cast<long long>(b) * p.Lk : nullptr;
-    const int* kseg = p.kv_seg ? p.kv_seg + static_cast<long long>(b) * p.Lk : nullptr;
+    const bool has_bias = p.rel_bias != nullptr;
     bool ok = true;
-
-    auto logit = [&](float acc, int k) -> float {
-      // k < Lk guaranteed by the caller
-      float s = acc;
-      if (p.rel_bias != nullptr) s += sRel[k - r + 127];
-      bool vis = (k <= kmax);
-      if (kmask) vis = vis && (kmask[k] != 0);
-      if (kseg) vis = vis && (kseg[k] == qseg);
-      return vis ? s : kMaskValue;
-    };
+    // Visibility of this thread's keys, one bit per key: chunk (j, c) covers keys
+    // j*128 + half*64 + c*32 .. +31.  bit set = attend; `inr` = key index < Lk.
+    uint32_t vis[8], inr[8];
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      const int col0 = (ch >> 1) * 128 + half * 64 + (ch & 1) * 32;
+      uint32_t m_vis = 0, m_in = 0;
+      if (col0 < nblk * 128) {
+        for (int i = 0; i < 32; ++i) {
+          const int kk = col0 + i;
+          const int sgm = sKeySeg[kk];
+          const bool in_range = kk < p.Lk;
+          const bool v = (sgm >= 0) && (p.kv_seg == nullptr || sgm == qseg) && (kk <= kmax);
+          m_vis |= (v ? 1u : 0u) << i;
+          m_in |= (in_range ? 1u : 0u) << i;
+        }
+      }
+      vis[ch] = m_vis;
+      inr[ch] = m_in;
+    }
 
     // pass 1: row max
     float m = -3.0e38f;
-    for (int j = 0; j < nblk && ok; ++j) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j >= nblk || !ok) break;
       ok = mbar_wait(&bar_s[j], 0, abort_flag);
       if (!ok) break;
       tc_fence_after();
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         const int col0 = j * 128 + half * 64 + c * 32;
         tmem_ld32(t_row + col0, v);
         tmem_ld_wait();
+        const uint32_t mv = vis[(j << 1) | c], mi = inr[(j << 1) | c];
+        const float* rel = sRel + (col0 - r + 127);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int k = col0 + i;
-          if (k < p.Lk) m = fmaxf(m, logit(__uint_as_float(v[i]), k));
+          float sc = __uint_as_float(v[i]);
+          if (has_bias) sc += rel[i];
+          sc = ((mv >> i) & 1u) ? sc : kMaskValue;
+          if ((mi >> i) & 1u) m = fmaxf(m, sc);
         }
       }
     }
@@ -230,24 +257,29 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     m = fmaxf(sStat[r * 2], sStat[r * 2 + 1]);
     // pass 2: probabilities -> smem (bf16), row sums
     float l = 0.f;
-    for (int j = 0; j < nblk && ok; ++j) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j >= nblk || !ok) break;
       if (j >= 2) {
         ok = mbar_wait(&bar_pv[j - 2], 0, abort_flag);  // P buffer (j&1) is free again
         if (!ok) break;
       }
       uint8_t* ptile = sP + (j & 1) * 2 * FwdSmem::kTile + half * FwdSmem::kTile;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         const int col0 = j * 128 + half * 64 + c * 32;
         tmem_ld32(t_row + col0, v);
         tmem_ld_wait();
+        const uint32_t mv = vis[(j << 1) | c], mi = inr[(j << 1) | c];
+        const float* rel = sRel + (col0 - r + 127);
         float pr[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int k = col0 + i;
-          float e = 0.f;
-          if (k < p.Lk) e = __expf(logit(__uint_as_float(v[i]), k) - m);
+          float sc = __uint_as_float(v[i]);
+          if (has_bias) sc += rel[i];
+          sc = ((mv >> i) & 1u) ? sc : kMaskValue;
+          float e = ((mi >> i) & 1u) ? __expf(sc - m) : 0.f;
           // the PV MMA consumes bf16 probabilities: sum what it will actually see
           e = __bfloat162float(__float2bfloat16(e));
           pr[i] = e;
@@ -498,6 +530,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     bool kvis = k_ok;
     if (p.key_mask && k_ok) kvis = p.key_mask[static_cast<long long>(b) * p.Lk + k] != 0;
     const int kseg = (p.kv_seg && k_ok) ? p.kv_seg[static_cast<long long>(b) * p.Lk + k] : 0;
+    const float inv_lk = 1.f / static_cast<float>(p.Lk);
     bool ok = true;
     for (int i = 0; i < nq && ok; ++i) {
       const int qb = i * 128;
@@ -545,11 +578,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           if (p.kv_seg) vis = vis && (kseg == sQseg[cq]);
           s = vis ? s : kMaskValue;
           float e = (k_ok && q < p.Lq) ? __expf(s - sLse[cq]) : 0.f;
+          // A row with every key masked has lse = -1e10 + log(Lk), which fp32 rounds to -1e10:
+          // its probabilities are uniform over the Lk keys.
+          if (sLse[cq] < -5e9f && k_ok && q < p.Lq) e = inv_lk;
           const float g = e * (__uint_as_float(dpv[x]) - sDelta[cq]);
           pr[x] = e;
           ds[x] = g;
-          // the bias only receives gradient where it was added (unmasked positions)
-          if (p.d_rel_bias != nullptr && vis && g != 0.f) atomicAdd(&sDRel[r - q + lq_pad], g);
+          // masks are additive, so the bias term receives the softmax gradient everywhere
+          if (p.d_rel_bias != nullptr && g != 0.f) atomicAdd(&sDRel[r - q + lq_pad], g);
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -573,7 +609,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         if (q < p.Lq) {
           float* dst = p.dQ + ((static_cast<long long>(b) * p.Lq + q) * p.H + h) * kAttnD + half * 32;
 #pragma unroll
-          for (int x = 0; x < 32; ++x) atomicAdd(dst + x, __uint_as_float(v[x]));
+          for (int x = 0; x < 32; x += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + x),
+                         "f"(__uint_as_float(v[x])), "f"(__uint_as_float(v[x + 1])),
+                         "f"(__uint_as_float(v[x + 2])), "f"(__uint_as_float(v[x + 3]))
+                         : "memory");
         }
       }
       tc_fence_before();

@@ -1,13 +1,110 @@
-"""Flash attention with in-kernel T5 relative-position bias (CUDA path of `functional.attention`)."""
+"""Flash attention with in-kernel T5 relative-position bias (CUDA path of `functional.attention`).
+
+The [heads, buckets] bias table is expanded on the host into a per-relative-offset table
+`rel_bias[h, (k - q) + Lq - 1]` with the oracle's own bucket function (so bucket boundaries are
+bit-identical); the kernels index it by `k - q`, build the masks from per-token metadata and
+never materialise [b, h, q, k] scores. The gradient of the expanded table comes back from the
+backward kernel and autograd folds it into the bucket table.
+"""
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
+
+from t5x_b200.ops import native
+from t5x_b200.ops import reference as ref
+
+c_void_p, c_int, c_ll = native.c_void_p, native.c_int, native.c_ll
+native.register_signature("t5x_attention_fwd", [c_void_p] * 5 + [c_int] * 4 + [c_ll] * 12 +
+                          [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                           c_void_p])
+native.register_signature("t5x_attention_bwd", [c_void_p] * 10 + [c_int] * 4 + [c_ll] * 18 +
+                          [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                           c_int, c_void_p])
+
+MAX_LK = 512
+MAX_LQ = 4096
+
+
+def _strides_ok(t: torch.Tensor) -> bool:
+  return (t.dim() == 4 and t.stride(3) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and
+          t.stride(2) % 8 == 0 and t.data_ptr() % 16 == 0)
 
 
 def flash_supported(q, k, v, explicit_bias, extra_mask) -> bool:
   """True when the sm_100a flash kernels cover this call."""
-  return False
+  return (explicit_bias is None and extra_mask is None and q.shape[-1] == 64 and
+          k.shape[1] <= MAX_LK and q.shape[1] <= MAX_LQ and q.dtype == torch.bfloat16 and
+          k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16)
 
 
-def flash_attention(q, k, v, **kwargs):
-  raise NotImplementedError
+def _sbh(t):
+  return t.stride(0), t.stride(1), t.stride(2)
+
+
+class _FlashAttentionFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, q, k, v, rel_bias, key_mask, q_seg, kv_seg, causal, causal_off, rel_off):
+    q = q if _strides_ok(q) else q.contiguous()
+    k = k if _strides_ok(k) else k.contiguous()
+    v = v if _strides_ok(v) else v.contiguous()
+    B, Lq, H, D = q.shape
+    Lk = k.shape[1]
+    o = torch.empty((B, Lq, H, D), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+    nrel = rel_bias.shape[1] if rel_bias is not None else 0
+    rc = native.lib().t5x_attention_fwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, H, Lq, Lk,
+        *_sbh(q), *_sbh(k), *_sbh(v), *_sbh(o), native.ptr(rel_bias), nrel, rel_off,
+        native.ptr(key_mask), native.ptr(q_seg), native.ptr(kv_seg), int(causal), causal_off,
+        native.stream_ptr())
+    native._check(rc, "attention_fwd")
+    ctx.save_for_backward(q, k, v, o, lse, rel_bias, key_mask, q_seg, kv_seg)
+    ctx.cfg = (causal, causal_off, rel_off)
+    return o
+
+  @staticmethod
+  def backward(ctx, do):
+    q, k, v, o, lse, rel_bias, key_mask, q_seg, kv_seg = ctx.saved_tensors
+    causal, causal_off, rel_off = ctx.cfg
+    B, Lq, H, D = q.shape
+    Lk = k.shape[1]
+    do = do if _strides_ok(do) else do.contiguous()
+    dq32 = torch.zeros((B, Lq, H, D), dtype=torch.float32, device=q.device)
+    dk = torch.empty((B, Lk, H, D), dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty((B, Lk, H, D), dtype=torch.bfloat16, device=q.device)
+    delta = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+    d_rel = torch.zeros_like(rel_bias) if rel_bias is not None else None
+    nrel = rel_bias.shape[1] if rel_bias is not None else 0
+    rc = native.lib().t5x_attention_bwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+        delta.data_ptr(), dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H, Lq, Lk, *_sbh(q),
+        *_sbh(k), *_sbh(v), *_sbh(o), *_sbh(do), *_sbh(dk), native.ptr(rel_bias),
+        native.ptr(d_rel), nrel, rel_off, native.ptr(key_mask), native.ptr(q_seg),
+        native.ptr(kv_seg), int(causal), causal_off, native.stream_ptr())
+    native._check(rc, "attention_bwd")
+    return dq32.to(torch.bfloat16), dk, dv, d_rel, None, None, None, None, None, None
+
+
+def flash_attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None,
+                    bidirectional: bool = True, num_buckets: int = 32, max_distance: int = 128,
+                    key_mask: Optional[torch.Tensor] = None, causal: bool = False,
+                    q_segment_ids=None, kv_segment_ids=None, q_offset: int = 0) -> torch.Tensor:
+  """q [B,Lq,H,64], k/v [B,Lk,H,64] bf16 -> [B,Lq,H,64]."""
+  B, Lq, H, D = q.shape
+  Lk = k.shape[1]
+  rel_bias = None
+  if bias_table is not None:
+    # index t <-> relative position (k - q_pos) = t - (Lq - 1) - q_offset
+    rel = torch.arange(Lq + Lk - 1, device=q.device) - (Lq - 1) - q_offset
+    buckets = ref.relative_position_bucket(rel, bidirectional, num_buckets, max_distance)
+    rel_bias = bias_table.float()[:, buckets].contiguous()
+  km = key_mask.to(torch.uint8).contiguous() if key_mask is not None else None
+  qs = q_segment_ids.to(torch.int32).contiguous() if q_segment_ids is not None else None
+  ks = kv_segment_ids.to(torch.int32).contiguous() if kv_segment_ids is not None else None
+  if qs is None or ks is None:
+    qs = ks = None
+  return _FlashAttentionFn.apply(q, k, v, rel_bias, km, qs, ks, bool(causal),
+                                 (Lk - Lq) if causal else 0, Lq - 1)

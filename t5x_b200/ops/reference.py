@@ -103,7 +103,9 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
   if extra_mask is not None:
     mask = _and(mask, extra_mask.bool())
   if mask is not None:
-    logits = torch.where(mask, logits, torch.full_like(logits, NEG_MASK))
+    # Additive, as in the reference (mask -> bias of 0 / -1e10 that is summed with the logits):
+    # a masked logit equals -1e10 in fp32 and the softmax gradient still reaches q and k.
+    logits = logits + torch.where(mask, 0.0, NEG_MASK).to(logits.dtype)
   probs = torch.softmax(logits.float(), dim=-1).to(v.dtype)
   return torch.einsum("bhqk,bkhd->bqhd", probs, v)
 

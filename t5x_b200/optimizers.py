@@ -41,6 +41,8 @@ def _to_state_dict(x):
   if isinstance(x, Mapping):
     return {k: _to_state_dict(v) for k, v in x.items()}
   if isinstance(x, (list, tuple)):
+    if all(v is None or isinstance(v, (str, tuple)) for v in x):
+      return x  # a tuple of axis names is a leaf
     return {str(i): _to_state_dict(v) for i, v in enumerate(x)}
   return x
 
