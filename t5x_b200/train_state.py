@@ -38,6 +38,15 @@ def _validate_params_axes(params_axes, params):
                        f"{tuple(flat_params[k].shape)}")
 
 
+def _as_tensor(value) -> torch.Tensor:
+  if hasattr(value, "get") and not isinstance(value, Mapping):  # LazyArray
+    value = value.get()
+  arr = np.asarray(value)
+  if arr.dtype.name == "bfloat16":
+    return torch.from_numpy(arr.view(np.int16).copy()).view(torch.bfloat16)
+  return torch.as_tensor(arr)
+
+
 def _copy_into(target, value, path=""):
   """Recursively copies `value` leaves into `target` tensors in place."""
   if isinstance(target, Mapping):
@@ -48,7 +57,7 @@ def _copy_into(target, value, path=""):
                        f"missing {sorted(tk - vk)}, unexpected {sorted(vk - tk)}")
     return {k: _copy_into(target[k], value[k], f"{path}/{k}" if path else k) for k in target}
   if isinstance(target, torch.Tensor):
-    src = value if isinstance(value, torch.Tensor) else torch.as_tensor(np.asarray(value))
+    src = value if isinstance(value, torch.Tensor) else _as_tensor(value)
     if tuple(src.shape) != tuple(target.shape):
       raise ValueError(f"Shape mismatch restoring '{path}': checkpoint {tuple(src.shape)} vs "
                        f"state {tuple(target.shape)}")
