@@ -12,18 +12,26 @@
 // Masked logits take the value -1e10 (not -inf): a fully masked row gives a uniform
 // distribution, exactly like the additive-mask formulation of the reference.
 //
-// Forward : one CTA per (128-query block, head, batch). Lk <= 512 (S fills TMEM's 512 columns).
-// Backward: one CTA per (128-key block, head, batch), looping over query blocks; dQ partial
-//           tiles are added to an fp32 buffer with red.global.add.
+// Forward : one CTA per (head, batch); K and V stay in shared memory while the CTA walks the
+//           128-query blocks; S = Q K^T for the whole key range sits in TMEM (Lk <= 512), the
+//           S MMAs of the next query block are issued as soon as the softmax warps release
+//           the columns. 16 softmax warps (4 threads per row) + 1 warp for TMA and MMA issue.
+// Backward: one CTA per (128-key block, head, batch), looping over query blocks; dK/dV
+//           accumulate in TMEM, dQ partial tiles are added to an fp32 buffer with vector
+//           red.global.add.
 #include "common.cuh"
 
 namespace t5x {
 
 constexpr int kAttnD = 64;
-constexpr int kAttnThreads = 288;  // warps 0-7 softmax/epilogue, warp 8 TMA + MMA issue
+constexpr int kSoftmaxWarps = 16;
+constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
+constexpr int kAttnThreads = kSoftmaxThreads + 32;  // + 1 warp: TMA + MMA issue, TMEM owner
+constexpr int kCtrlWarp = kSoftmaxWarps;
 constexpr int kKernelIdAttnFwd = 2;
 constexpr int kKernelIdAttnBwd = 3;
 constexpr float kMaskValue = -1e10f;
+constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnParams {
   int B, H, Lq, Lk;
@@ -47,22 +55,49 @@ struct AttnParams {
 };
 
 __device__ __forceinline__ void softmax_bar_sync() {
-  asm volatile("bar.sync 1, 256;" ::: "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
 }
 
 // Writes 8 consecutive bf16 (one 16-byte chunk) of row r, chunk c (0..7) of a [128 x 64] K-major
 // 128B-swizzled tile.
 __device__ __forceinline__ void store_swizzled_chunk(uint8_t* tile, int r, int c, const float* v) {
-  __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]);
-  __nv_bfloat162 p1 = __floats2bfloat162_rn(v[2], v[3]);
-  __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]);
-  __nv_bfloat162 p3 = __floats2bfloat162_rn(v[6], v[7]);
   uint4 u;
-  u.x = *reinterpret_cast<uint32_t*>(&p0);
-  u.y = *reinterpret_cast<uint32_t*>(&p1);
-  u.z = *reinterpret_cast<uint32_t*>(&p2);
-  u.w = *reinterpret_cast<uint32_t*>(&p3);
+  u.x = pack_bf16x2(v[0], v[1]);
+  u.y = pack_bf16x2(v[2], v[3]);
+  u.z = pack_bf16x2(v[4], v[5]);
+  u.w = pack_bf16x2(v[6], v[7]);
   *reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = u;
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+// 16 fp32 values -> 16 bf16 written as two 16-byte stores.
+__device__ __forceinline__ void store16_bf16(__nv_bfloat16* dst, const uint32_t (&v)[16], float scale) {
+  uint4 u0, u1;
+  u0.x = pack_bf16x2(__uint_as_float(v[0]) * scale, __uint_as_float(v[1]) * scale);
+  u0.y = pack_bf16x2(__uint_as_float(v[2]) * scale, __uint_as_float(v[3]) * scale);
+  u0.z = pack_bf16x2(__uint_as_float(v[4]) * scale, __uint_as_float(v[5]) * scale);
+  u0.w = pack_bf16x2(__uint_as_float(v[6]) * scale, __uint_as_float(v[7]) * scale);
+  u1.x = pack_bf16x2(__uint_as_float(v[8]) * scale, __uint_as_float(v[9]) * scale);
+  u1.y = pack_bf16x2(__uint_as_float(v[10]) * scale, __uint_as_float(v[11]) * scale);
+  u1.z = pack_bf16x2(__uint_as_float(v[12]) * scale, __uint_as_float(v[13]) * scale);
+  u1.w = pack_bf16x2(__uint_as_float(v[14]) * scale, __uint_as_float(v[15]) * scale);
+  reinterpret_cast<uint4*>(dst)[0] = u0;
+  reinterpret_cast<uint4*>(dst)[1] = u1;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -74,12 +109,13 @@ struct FwdSmem {
   static constexpr int kK = kTile;              // up to 4 tiles
   static constexpr int kV = kK + 4 * kTile;     // up to 4 tiles
   static constexpr int kP = kV + 4 * kTile;     // 2 buffers x 2 tiles
-  static constexpr int kRel = kP + 4 * kTile;   // (512 + 128) floats
-  static constexpr int kStat = kRel + 640 * 4;  // 128 x 2 floats (row max halves), then sums
-  static constexpr int kKeySeg = kStat + 128 * 4 * 4;  // 512 ints: segment id of key k, -1 = hidden
+  static constexpr int kRel = kP + 4 * kTile;   // bias by (k - q): up to 512 + 512 floats
+  static constexpr int kStat = kRel + 1024 * 4; // 128 x 4 floats (row max parts), then sums
+  static constexpr int kKeySeg = kStat + 128 * 4 * 4 * 2;  // 512 ints: segment id of key k, -1 = hidden
   static constexpr int kBars = kKeySeg + 512 * 4;
   static constexpr int kTotal = kBars + 256 + 1024;
 };
+constexpr int kFwdMaxLq = 512;  // sRel covers (k - q) for Lq, Lk <= 512
 
 __global__ void __launch_bounds__(kAttnThreads, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -95,42 +131,46 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   float* sStat = reinterpret_cast<float*>(smem + FwdSmem::kStat);
   int* sKeySeg = reinterpret_cast<int*>(smem + FwdSmem::kKeySeg);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FwdSmem::kBars);
-  uint64_t* bar_q = bars;           // 1
-  uint64_t* bar_k = bars + 1;       // 4
-  uint64_t* bar_v = bars + 5;       // 4
-  uint64_t* bar_s = bars + 9;       // 4  S block ready in TMEM
-  uint64_t* bar_p = bars + 13;      // 4  P block written to smem (8 warp arrivals)
-  uint64_t* bar_pv = bars + 17;     // 4  PV MMA of block j finished (P buffer reusable)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  uint64_t* bar_q = bars;           // Q tile landed (once per query block)
+  uint64_t* bar_kv = bars + 1;      // 4: K_j and V_j landed (once per CTA)
+  uint64_t* bar_s = bars + 5;       // 4: S block j ready in TMEM (once per query block)
+  uint64_t* bar_p = bars + 9;       // 4: P block j written to smem, S block j released
+  uint64_t* bar_pv = bars + 13;     // 4: PV MMA of block j finished (P buffer reusable)
+  uint64_t* bar_qfree = bars + 17;  // all S MMAs of this query block done: Q smem reusable
+  uint64_t* bar_oread = bars + 18;  // O accumulator of this query block has been read out
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * 128, h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int nblk = (p.Lk + 127) / 128;
-  const int o_col = (nblk * 128) & 511;  // TMEM column of the O accumulator (reuses S block 0 when full)
+  const int nq = (p.Lq + 127) / 128;
+  const int lq_pad = nq * 128;
+  const int o_col = (nblk * 128) & 511;  // TMEM column of O (reuses S block 0 when Lk fills TMEM)
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
+    mbar_init(bar_qfree, 1);
+    mbar_init(bar_oread, kSoftmaxWarps);
     for (int j = 0; j < 4; ++j) {
-      mbar_init(&bar_k[j], 1);
-      mbar_init(&bar_v[j], 1);
+      mbar_init(&bar_kv[j], 1);
       mbar_init(&bar_s[j], 1);
-      mbar_init(&bar_p[j], 8);
+      mbar_init(&bar_p[j], kSoftmaxWarps);
       mbar_init(&bar_pv[j], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 8) {
+  if (warp == kCtrlWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  // Relative-position bias for this tile: sRel[t], t = k - r + 127  (r = row within the tile).
+  // Bias by relative offset for this head: sRel[u], u = (k - q) + lq_pad - 1.
   if (p.rel_bias != nullptr) {
     const float* tab = p.rel_bias + static_cast<long long>(h) * p.nrel;
-    for (int t = threadIdx.x; t < nblk * 128 + 128; t += kAttnThreads) {
-      const int idx = t - 127 - q0 + p.rel_off;
-      sRel[t] = (idx >= 0 && idx < p.nrel) ? tab[idx] : 0.f;
+    for (int u = threadIdx.x; u < lq_pad + nblk * 128; u += kAttnThreads) {
+      const int idx = u - (lq_pad - 1) + p.rel_off;
+      sRel[u] = (idx >= 0 && idx < p.nrel) ? tab[idx] : 0.f;
     }
   }
   // Per-key metadata: segment id (0 when unpacked), -1 for padded / out-of-range keys.
@@ -148,48 +188,67 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == kCtrlWarp) {
     if (lane == 0) {
       bool ok = true;
-      // ---- loads ----
       mbar_expect_tx(bar_q, FwdSmem::kTile);
-      tma_load_4d(sQ, &tmQ, bar_q, 0, h, q0, b);
+      tma_load_4d(sQ, &tmQ, bar_q, 0, h, 0, b);
       for (int j = 0; j < nblk; ++j) {
-        mbar_expect_tx(&bar_k[j], FwdSmem::kTile);
-        tma_load_4d(sK + j * FwdSmem::kTile, &tmK, &bar_k[j], 0, h, j * 128, b);
+        mbar_expect_tx(&bar_kv[j], 2 * FwdSmem::kTile);
+        tma_load_4d(sK + j * FwdSmem::kTile, &tmK, &bar_kv[j], 0, h, j * 128, b);
+        tma_load_4d(sV + j * FwdSmem::kTile, &tmV, &bar_kv[j], 0, h, j * 128, b);
       }
-      for (int j = 0; j < nblk; ++j) {
-        mbar_expect_tx(&bar_v[j], FwdSmem::kTile);
-        tma_load_4d(sV + j * FwdSmem::kTile, &tmV, &bar_v[j], 0, h, j * 128, b);
-      }
-      // ---- S_j = Q K_j^T ----
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-      ok = mbar_wait(bar_q, 0, abort_flag);
-      for (int j = 0; j < nblk && ok; ++j) {
-        ok = mbar_wait(&bar_k[j], 0, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + j * FwdSmem::kTile);
-#pragma unroll
-        for (int s = 0; s < 4; ++s)
-          umma_bf16(tmem_base + j * 128, make_smem_desc_sw128(qa + s * 32, 16, 1024),
-                    make_smem_desc_sw128(ka + s * 32, 16, 1024), idesc_s, s != 0);
-        umma_commit(&bar_s[j]);
-      }
-      // ---- O += P_j V_j ----
       const uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);
-      for (int j = 0; j < nblk && ok; ++j) {
-        ok = mbar_wait(&bar_p[j], 0, abort_flag) && mbar_wait(&bar_v[j], 0, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t pa = smem_u32(sP + (j & 1) * 2 * FwdSmem::kTile);
-        const uint32_t va = smem_u32(sV + j * FwdSmem::kTile);
+      const uint32_t qa = smem_u32(sQ);
+      for (int i = 0; i < nq && ok; ++i) {
+        const uint32_t ph = i & 1;
+        // ---- S_j = Q_i K_j^T, as soon as the previous query block released the columns ----
+        ok = mbar_wait(bar_q, ph, abort_flag);
+        for (int j = 0; j < nblk && ok; ++j) {
+          if (i == 0) ok = mbar_wait(&bar_kv[j], 0, abort_flag);
+          if (ok && i > 0) {
+            ok = mbar_wait(&bar_p[j], ph ^ 1, abort_flag);
+            // the O accumulator of the previous block may live in S block 0's columns
+            if (ok && j * 128 == o_col) ok = mbar_wait(bar_oread, ph ^ 1, abort_flag);
+          }
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t ka = smem_u32(sK + j * FwdSmem::kTile);
 #pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma_bf16(tmem_base + o_col,
-                    make_smem_desc_sw128(pa + (s >> 2) * FwdSmem::kTile + (s & 3) * 32, 16, 1024),
-                    make_smem_desc_sw128(va + s * 2048, 8192, 1024), idesc_o, (j | s) != 0);
-        umma_commit(&bar_pv[j]);
+          for (int s = 0; s < 4; ++s)
+            umma_bf16(tmem_base + j * 128, make_smem_desc_sw128(qa + s * 32, 16, 1024),
+                      make_smem_desc_sw128(ka + s * 32, 16, 1024), idesc_s, s != 0);
+          umma_commit(&bar_s[j]);
+        }
+        if (!ok) break;
+        // Q smem is free once the S MMAs are done: prefetch the next query block.
+        if (i + 1 < nq) {
+          umma_commit(bar_qfree);
+          ok = mbar_wait(bar_qfree, ph, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(bar_q, FwdSmem::kTile);
+          tma_load_4d(sQ, &tmQ, bar_q, 0, h, (i + 1) * 128, b);
+        }
+        // ---- O_i += P_j V_j ----
+        if (i > 0 && o_col >= nblk * 128) {
+          // O has its own columns: they must have been read out before being overwritten
+          ok = mbar_wait(bar_oread, ph ^ 1, abort_flag);
+          if (!ok) break;
+        }
+        for (int j = 0; j < nblk && ok; ++j) {
+          ok = mbar_wait(&bar_p[j], ph, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t pa = smem_u32(sP + (j & 1) * 2 * FwdSmem::kTile);
+          const uint32_t va = smem_u32(sV + j * FwdSmem::kTile);
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            umma_bf16(tmem_base + o_col,
+                      make_smem_desc_sw128(pa + (s >> 2) * FwdSmem::kTile + (s & 3) * 32, 16, 1024),
+                      make_smem_desc_sw128(va + s * 2048, 8192, 1024), idesc_o, (j | s) != 0);
+          umma_commit(&bar_pv[j]);
+        }
       }
       if (!ok) {
         report_status(p.status, kStatusTimeoutMma, kKernelIdAttnFwd, blockIdx.x, blockIdx.y);
@@ -198,134 +257,159 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
   } else {
     // ------------------------------ softmax warps ------------------------------
-    const int quarter = warp & 3, half = warp >> 2;
-    const int r = quarter * 32 + lane;  // row of the tile == TMEM lane
-    const int q = q0 + r;
+    const int quarter = warp & 3, part = warp >> 2;  // 4 threads per row, 32 columns each
+    const int r = quarter * 32 + lane;               // row of the tile == TMEM lane
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const int qseg = (p.q_seg != nullptr && q < p.Lq) ? p.q_seg[b * p.Lq + q] : 0;
-    const int kmax = p.causal ? q + p.causal_off : 0x7fffffff;
     const bool has_bias = p.rel_bias != nullptr;
     bool ok = true;
-    // Visibility of this thread's keys, one bit per key: chunk (j, c) covers keys
-    // j*128 + half*64 + c*32 .. +31.  bit set = attend; `inr` = key index < Lk.
-    uint32_t vis[8], inr[8];
-#pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      const int col0 = (ch >> 1) * 128 + half * 64 + (ch & 1) * 32;
-      uint32_t m_vis = 0, m_in = 0;
-      if (col0 < nblk * 128) {
-        for (int i = 0; i < 32; ++i) {
-          const int kk = col0 + i;
-          const int sgm = sKeySeg[kk];
-          const bool in_range = kk < p.Lk;
-          const bool v = (sgm >= 0) && (p.kv_seg == nullptr || sgm == qseg) && (kk <= kmax);
-          m_vis |= (v ? 1u : 0u) << i;
-          m_in |= (in_range ? 1u : 0u) << i;
-        }
-      }
-      vis[ch] = m_vis;
-      inr[ch] = m_in;
-    }
-
-    // pass 1: row max
-    float m = -3.0e38f;
+    // Key-only visibility (padding / key mask) and in-range bits, fixed for the whole CTA.
+    uint32_t kvis[4], inr[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      if (j >= nblk || !ok) break;
-      ok = mbar_wait(&bar_s[j], 0, abort_flag);
+      uint32_t m_vis = 0, m_in = 0;
+      if (j < nblk) {
+        for (int x = 0; x < 32; ++x) {
+          const int kk = j * 128 + part * 32 + x;
+          m_vis |= (sKeySeg[kk] >= 0 ? 1u : 0u) << x;
+          m_in |= (kk < p.Lk ? 1u : 0u) << x;
+        }
+      }
+      kvis[j] = m_vis;
+      inr[j] = m_in;
+    }
+    for (int i = 0; i < nq && ok; ++i) {
+      const uint32_t ph = i & 1;
+      const int q = i * 128 + r;
+      const int qseg = (p.q_seg != nullptr && q < p.Lq) ? p.q_seg[b * p.Lq + q] : 0;
+      const int kmax = p.causal ? q + p.causal_off : 0x7fffffff;
+      // Visibility bits of this thread's keys: chunk j covers keys j*128 + part*32 .. +31.
+      uint32_t vis[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t mvis = kvis[j];
+        if (p.causal) {
+          const int n = kmax - (j * 128 + part * 32) + 1;  // number of leading visible keys
+          mvis &= n >= 32 ? 0xffffffffu : (n <= 0 ? 0u : ((1u << n) - 1u));
+        }
+        if (p.kv_seg != nullptr && j < nblk) {
+          uint32_t ms = 0;
+          for (int x = 0; x < 32; ++x)
+            ms |= (sKeySeg[j * 128 + part * 32 + x] == qseg ? 1u : 0u) << x;
+          mvis &= ms;
+        }
+        vis[j] = mvis;
+      }
+      // ---- pass 1: row max ----
+      float m = -3.0e38f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j >= nblk || !ok) break;
+        ok = mbar_wait(&bar_s[j], ph, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t v[32];
+        const int col0 = j * 128 + part * 32;
+        tmem_ld32(t_row + col0, v);
+        tmem_ld_wait();
+        const float* rel = sRel + (col0 - q + lq_pad - 1);
+        if (vis[j] == 0xffffffffu) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            float sc = __uint_as_float(v[x]);
+            if (has_bias) sc += rel[x];
+            m = fmaxf(m, sc);
+          }
+        } else {
+          const uint32_t mv = vis[j], mi = inr[j];
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            float sc = __uint_as_float(v[x]);
+            if (has_bias) sc += rel[x];
+            sc = ((mv >> x) & 1u) ? sc : kMaskValue;
+            if ((mi >> x) & 1u) m = fmaxf(m, sc);
+          }
+        }
+      }
+      sStat[r * 4 + part] = m;
+      softmax_bar_sync();
+      m = fmaxf(fmaxf(sStat[r * 4], sStat[r * 4 + 1]), fmaxf(sStat[r * 4 + 2], sStat[r * 4 + 3]));
+      const float m2 = m * kLog2e;
+      // ---- pass 2: probabilities -> smem (bf16), row sums ----
+      float l = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j >= nblk || !ok) break;
+        // P buffer (j & 1) was last read by the PV MMA of block j-2 (this query block) or of
+        // the last block with the same parity of the previous query block.
+        if (j >= 2) {
+          ok = mbar_wait(&bar_pv[j - 2], ph, abort_flag);
+        } else if (i > 0) {
+          const int jp = ((nblk - 1 - j) & ~1) + j;  // last block index with parity j
+          if (jp < nblk) ok = mbar_wait(&bar_pv[jp], ph ^ 1, abort_flag);
+        }
+        if (!ok) break;
+        uint8_t* ptile = sP + (j & 1) * 2 * FwdSmem::kTile + (part >> 1) * FwdSmem::kTile;
+        uint32_t v[32];
+        const int col0 = j * 128 + part * 32;
+        tmem_ld32(t_row + col0, v);
+        tmem_ld_wait();
+        const float* rel = sRel + (col0 - q + lq_pad - 1);
+        float pr[32];
+        if (vis[j] == 0xffffffffu) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            float sc = __uint_as_float(v[x]);
+            if (has_bias) sc += rel[x];
+            const float e = exp2f(fmaf(sc, kLog2e, -m2));
+            pr[x] = e;
+            l += e;
+          }
+        } else {
+          const uint32_t mv = vis[j], mi = inr[j];
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            float sc = __uint_as_float(v[x]);
+            if (has_bias) sc += rel[x];
+            sc = ((mv >> x) & 1u) ? sc : kMaskValue;
+            // subtract first: a fully masked row has sc == m == -1e10 and must give exp2(0)
+            const float e = ((mi >> x) & 1u) ? exp2f((sc - m) * kLog2e) : 0.f;
+            pr[x] = e;
+            l += e;
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) store_swizzled_chunk(ptile, r, (part & 1) * 4 + g, pr + g * 8);
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_p[j]);
+      }
+      sStat[512 + r * 4 + part] = l;
+      softmax_bar_sync();
+      l = (sStat[512 + r * 4] + sStat[512 + r * 4 + 1]) + (sStat[512 + r * 4 + 2] + sStat[512 + r * 4 + 3]);
+      // ---- epilogue: O / l (each of the 4 threads of a row writes 16 of the 64 columns) ----
+      if (ok) ok = mbar_wait(&bar_pv[nblk - 1], ph, abort_flag);
       if (!ok) break;
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        const int col0 = j * 128 + half * 64 + c * 32;
-        tmem_ld32(t_row + col0, v);
+      {
+        uint32_t v[16];
+        tmem_ld16(t_row + o_col + part * 16, v);
         tmem_ld_wait();
-        const uint32_t mv = vis[(j << 1) | c], mi = inr[(j << 1) | c];
-        const float* rel = sRel + (col0 - r + 127);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float sc = __uint_as_float(v[i]);
-          if (has_bias) sc += rel[i];
-          sc = ((mv >> i) & 1u) ? sc : kMaskValue;
-          if ((mi >> i) & 1u) m = fmaxf(m, sc);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_oread);
+        if (q < p.Lq) {
+          __nv_bfloat16* dst =
+              p.O + b * p.o_sb + static_cast<long long>(q) * p.o_sl + h * p.o_sh + part * 16;
+          store16_bf16(dst, v, 1.f / l);
+          if (part == 0 && p.lse != nullptr)
+            p.lse[(static_cast<long long>(b) * p.H + h) * p.Lq + q] = m + __logf(l);
         }
       }
+      // sStat is rewritten by the next query block only after everyone read the sums
+      softmax_bar_sync();
     }
-    sStat[r * 2 + half] = m;
-    softmax_bar_sync();
-    m = fmaxf(sStat[r * 2], sStat[r * 2 + 1]);
-    // pass 2: probabilities -> smem (bf16), row sums
-    float l = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (j >= nblk || !ok) break;
-      if (j >= 2) {
-        ok = mbar_wait(&bar_pv[j - 2], 0, abort_flag);  // P buffer (j&1) is free again
-        if (!ok) break;
-      }
-      uint8_t* ptile = sP + (j & 1) * 2 * FwdSmem::kTile + half * FwdSmem::kTile;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        const int col0 = j * 128 + half * 64 + c * 32;
-        tmem_ld32(t_row + col0, v);
-        tmem_ld_wait();
-        const uint32_t mv = vis[(j << 1) | c], mi = inr[(j << 1) | c];
-        const float* rel = sRel + (col0 - r + 127);
-        float pr[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float sc = __uint_as_float(v[i]);
-          if (has_bias) sc += rel[i];
-          sc = ((mv >> i) & 1u) ? sc : kMaskValue;
-          float e = ((mi >> i) & 1u) ? __expf(sc - m) : 0.f;
-          // the PV MMA consumes bf16 probabilities: sum what it will actually see
-          e = __bfloat162float(__float2bfloat16(e));
-          pr[i] = e;
-          l += e;
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) store_swizzled_chunk(ptile, r, c * 4 + g, pr + g * 8);
-      }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_p[j]);
-    }
-    sStat[256 + r * 2 + half] = l;
-    softmax_bar_sync();
-    l = sStat[256 + r * 2] + sStat[256 + r * 2 + 1];
-    // epilogue: O / l
-    if (ok) ok = mbar_wait(&bar_pv[nblk - 1], 0, abort_flag);
-    if (ok) {
-      tc_fence_after();
-      uint32_t v[32];
-      tmem_ld32(t_row + o_col + half * 32, v);
-      tmem_ld_wait();
-      if (q < p.Lq) {
-        const float inv = 1.f / l;
-        float o[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * inv;
-        __nv_bfloat16* dst = p.O + b * p.o_sb + static_cast<long long>(q) * p.o_sl + h * p.o_sh + half * 32;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          __nv_bfloat162 a0 = __floats2bfloat162_rn(o[g * 8], o[g * 8 + 1]);
-          __nv_bfloat162 a1 = __floats2bfloat162_rn(o[g * 8 + 2], o[g * 8 + 3]);
-          __nv_bfloat162 a2 = __floats2bfloat162_rn(o[g * 8 + 4], o[g * 8 + 5]);
-          __nv_bfloat162 a3 = __floats2bfloat162_rn(o[g * 8 + 6], o[g * 8 + 7]);
-          uint4 u;
-          u.x = *reinterpret_cast<uint32_t*>(&a0);
-          u.y = *reinterpret_cast<uint32_t*>(&a1);
-          u.z = *reinterpret_cast<uint32_t*>(&a2);
-          u.w = *reinterpret_cast<uint32_t*>(&a3);
-          reinterpret_cast<uint4*>(dst)[g] = u;
-        }
-        if (half == 0 && p.lse != nullptr)
-          p.lse[(static_cast<long long>(b) * p.H + h) * p.Lq + q] = m + __logf(l);
-      }
-    } else if (lane == 0) {
+    if (!ok && lane == 0) {
       report_status(p.status, kStatusTimeoutEpilogue, kKernelIdAttnFwd, blockIdx.x, blockIdx.y);
       *abort_flag = 1;
     }
@@ -334,7 +418,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     for (int it = 0; it < 2000; ++it) __nanosleep(1000);
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kCtrlWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -376,9 +460,9 @@ struct BwdSmem {
   static constexpr int kDO = 4 * kTile;       // 2 stages
   static constexpr int kPT = 6 * kTile;       // P^T : 2 tiles (128 keys x 128 queries)
   static constexpr int kDST = 8 * kTile;      // dS^T: 2 tiles
-  static constexpr int kVec = 10 * kTile;     // lse[128], delta[128], qseg[128] (ints)
-  static constexpr int kRel = kVec + 3 * 128 * 4;   // bias by rel for the (i, j) pair: 256 floats
-  static constexpr int kDRel = kRel + 256 * 4;      // d bias by rel accumulators: (Lq_pad + 128) floats
+  static constexpr int kVec = 10 * kTile;     // 2 stages x {lse[128], delta[128], qseg[128]}
+  static constexpr int kRel = kVec + 2 * 3 * 128 * 4;   // bias by rel for the (i, j) pair: 2 x 256 floats
+  static constexpr int kDRel = kRel + 2 * 256 * 4;      // d bias by rel accumulators: (Lq_pad + 128) floats
   static constexpr int kBars = kDRel + (4096 + 128) * 4;
   static constexpr int kTotal = kBars + 256 + 1024;
 };
@@ -396,19 +480,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   uint8_t* sDO = smem + BwdSmem::kDO;
   uint8_t* sPT = smem + BwdSmem::kPT;
   uint8_t* sDST = smem + BwdSmem::kDST;
-  float* sLse = reinterpret_cast<float*>(smem + BwdSmem::kVec);
-  float* sDelta = sLse + 128;
-  int* sQseg = reinterpret_cast<int*>(sDelta + 128);
-  float* sRel = reinterpret_cast<float*>(smem + BwdSmem::kRel);
+  float* sVec = reinterpret_cast<float*>(smem + BwdSmem::kVec);
+  float* sRelAll = reinterpret_cast<float*>(smem + BwdSmem::kRel);
   float* sDRel = reinterpret_cast<float*>(smem + BwdSmem::kDRel);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::kBars);
   uint64_t* bar_kv = bars;          // 1
   uint64_t* bar_qdo = bars + 1;     // 2 (full, per stage)
   uint64_t* bar_free = bars + 3;    // 2 (stage consumed by the MMAs)
   uint64_t* bar_s = bars + 5;       // S^T and dP^T ready
-  uint64_t* bar_p = bars + 6;       // P^T / dS^T written (8 warp arrivals)
-  uint64_t* bar_dq = bars + 7;      // dQ partial ready (also: P^T/dS^T smem and stage are free)
-  uint64_t* bar_dq_read = bars + 8; // dQ partial consumed (8 warp arrivals)
+  uint64_t* bar_p = bars + 6;       // P^T / dS^T written, S^T / dP^T released
+  uint64_t* bar_dq = bars + 7;      // dQ partial ready (also: P^T/dS^T smem consumed)
+  uint64_t* bar_dq_read = bars + 8; // dQ partial consumed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -426,13 +508,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       mbar_init(&bar_free[s], 1);
     }
     mbar_init(bar_s, 1);
-    mbar_init(bar_p, 8);
+    mbar_init(bar_p, kSoftmaxWarps);
     mbar_init(bar_dq, 1);
-    mbar_init(bar_dq_read, 8);
+    mbar_init(bar_dq_read, kSoftmaxWarps);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 8) {
+  if (warp == kCtrlWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -443,33 +525,26 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == kCtrlWarp) {
     if (lane == 0) {
       bool ok = true;
       mbar_expect_tx(bar_kv, 2 * BwdSmem::kTile);
       tma_load_4d(sK, &tmK, bar_kv, 0, h, k0, b);
       tma_load_4d(sV, &tmV, bar_kv, 0, h, k0, b);
-      // prefetch the first two query blocks
       for (int i = 0; i < nq && i < 2; ++i) {
         mbar_expect_tx(&bar_qdo[i], 2 * BwdSmem::kTile);
         tma_load_4d(sQ + i * BwdSmem::kTile, &tmQ, &bar_qdo[i], 0, h, i * 128, b);
         tma_load_4d(sDO + i * BwdSmem::kTile, &tmDO, &bar_qdo[i], 0, h, i * 128, b);
       }
-      ok = mbar_wait(bar_kv, 0, abort_flag);
       const uint32_t idesc_kq = make_idesc_bf16(128, 128, 0, 0);   // [keys x queries], K = d
       const uint32_t idesc_kd = make_idesc_bf16(128, 64, 0, 1);    // [keys x d], K = queries (B MN-major)
       const uint32_t idesc_qd = make_idesc_bf16(128, 64, 1, 1);    // [queries x d], A and B MN-major
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
       const uint32_t pta = smem_u32(sPT), dsta = smem_u32(sDST);
-      for (int i = 0; i < nq && ok; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
-        ok = mbar_wait(&bar_qdo[st], ph, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t qa = smem_u32(sQ + st * BwdSmem::kTile);
-        const uint32_t doa = smem_u32(sDO + st * BwdSmem::kTile);
-        // S^T = K Q^T ; dP^T = V dO^T
+
+      auto issue_scores = [&](int i) {  // S^T = K Q_i^T ; dP^T = V dO_i^T
+        const uint32_t qa = smem_u32(sQ + (i & 1) * BwdSmem::kTile);
+        const uint32_t doa = smem_u32(sDO + (i & 1) * BwdSmem::kTile);
 #pragma unroll
         for (int s = 0; s < 4; ++s)
           umma_bf16(tmem_base + cS, make_smem_desc_sw128(ka + s * 32, 16, 1024),
@@ -479,13 +554,21 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           umma_bf16(tmem_base + cDP, make_smem_desc_sw128(va + s * 32, 16, 1024),
                     make_smem_desc_sw128(doa + s * 32, 16, 1024), idesc_kq, s != 0);
         umma_commit(bar_s);
-        // wait for P^T / dS^T
+      };
+
+      ok = mbar_wait(bar_kv, 0, abort_flag) && mbar_wait(&bar_qdo[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+      }
+      for (int i = 0; i < nq && ok; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        const uint32_t qa = smem_u32(sQ + st * BwdSmem::kTile);
+        const uint32_t doa = smem_u32(sDO + st * BwdSmem::kTile);
         ok = mbar_wait(bar_p, i & 1, abort_flag);
+        if (ok && i > 0) ok = mbar_wait(bar_dq_read, (i - 1) & 1, abort_flag);
         if (!ok) break;
-        if (i > 0) {
-          ok = mbar_wait(bar_dq_read, (i - 1) & 1, abort_flag);  // previous dQ tile has been read
-          if (!ok) break;
-        }
         tc_fence_after();
         // dV += P^T dO ; dK += dS^T Q ; dQ_i = dS K
 #pragma unroll
@@ -506,6 +589,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
                     make_smem_desc_sw128(ka + s * 2048, 8192, 1024), idesc_qd, s != 0);
         umma_commit(bar_dq);
         umma_commit(&bar_free[st]);
+        // Scores of the next query block right behind: S^T / dP^T columns were released by bar_p.
+        if (i + 1 < nq) {
+          ok = mbar_wait(&bar_qdo[(i + 1) & 1], ((i + 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(i + 1);
+        }
         // refill this stage with query block i + 2
         if (i + 2 < nq) {
           ok = mbar_wait(&bar_free[st], ph, abort_flag);
@@ -522,8 +612,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
   } else {
     // ------------------------------ softmax / gradient warps ------------------------------
-    const int quarter = warp & 3, half = warp >> 2;
-    const int r = quarter * 32 + lane;  // key row of the tile == TMEM lane
+    const int quarter = warp & 3, part = warp >> 2;  // 4 threads per key row, 32 queries each
+    const int r = quarter * 32 + lane;               // key row of the tile == TMEM lane
     const int k = k0 + r;
     const bool k_ok = k < p.Lk;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -531,118 +621,142 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     if (p.key_mask && k_ok) kvis = p.key_mask[static_cast<long long>(b) * p.Lk + k] != 0;
     const int kseg = (p.kv_seg && k_ok) ? p.kv_seg[static_cast<long long>(b) * p.Lk + k] : 0;
     const float inv_lk = 1.f / static_cast<float>(p.Lk);
+    const bool has_bias = p.rel_bias != nullptr;
+    const bool simple_mask = !p.causal && p.kv_seg == nullptr;
     bool ok = true;
+
+    auto load_vectors = [&](int i) {
+      // per-query vectors of block i into stage (i & 1); all softmax threads cooperate
+      float* sLse = sVec + (i & 1) * 384;
+      float* sDelta = sLse + 128;
+      int* sQseg = reinterpret_cast<int*>(sDelta + 128);
+      float* sRel = sRelAll + (i & 1) * 256;
+      const int qb = i * 128;
+      const int t = threadIdx.x;
+      if (t < 128) {
+        const int q = qb + t;
+        const long long off = (static_cast<long long>(b) * p.H + h) * p.Lq + q;
+        sLse[t] = (q < p.Lq) ? p.lse[off] * kLog2e : 0.f;
+        sDelta[t] = (q < p.Lq) ? p.delta[off] : 0.f;
+        sQseg[t] = (p.q_seg && q < p.Lq) ? p.q_seg[static_cast<long long>(b) * p.Lq + q] : 0;
+      } else if (t < 128 + 255 && has_bias) {
+        // rel = k - q over the pair: index u = r - c + 127 in [0, 255)
+        const int u = t - 128;
+        const float* tab = p.rel_bias + static_cast<long long>(h) * p.nrel;
+        const int idx = (k0 - qb) + (u - 127) + p.rel_off;
+        sRel[u] = (idx >= 0 && idx < p.nrel) ? tab[idx] : 0.f;
+      }
+    };
+
+    load_vectors(0);
+    softmax_bar_sync();
     for (int i = 0; i < nq && ok; ++i) {
       const int qb = i * 128;
-      // per-query vectors for this block (all 256 threads cooperate)
-      {
-        const int t = threadIdx.x;
-        if (t < 128) {
-          const int q = qb + t;
-          const long long off = (static_cast<long long>(b) * p.H + h) * p.Lq + q;
-          sLse[t] = (q < p.Lq) ? p.lse[off] : 0.f;
-          sDelta[t] = (q < p.Lq) ? p.delta[off] : 0.f;
-          sQseg[t] = (p.q_seg && q < p.Lq) ? p.q_seg[static_cast<long long>(b) * p.Lq + q] : 0;
-        }
-        if (p.rel_bias != nullptr) {
-          // rel = k - q over the pair: index u = r - c + 127 in [0, 255)
-          const float* tab = p.rel_bias + static_cast<long long>(h) * p.nrel;
-          if (t < 255) {
-            const int idx = (k0 - qb) + (t - 127) + p.rel_off;
-            sRel[t] = (idx >= 0 && idx < p.nrel) ? tab[idx] : 0.f;
-          }
+      const float* sLse = sVec + (i & 1) * 384;
+      const float* sDelta = sLse + 128;
+      const int* sQseg = reinterpret_cast<const int*>(sDelta + 128);
+      const float* sRel = sRelAll + (i & 1) * 256;
+      if (i + 1 < nq) load_vectors(i + 1);  // other stage; consumed after the sync at the loop end
+      const int col0 = part * 32;  // query column within the block
+      // visibility of (this key, queries col0..col0+31)
+      uint32_t mv;
+      if (simple_mask) {
+        mv = kvis ? 0xffffffffu : 0u;
+      } else {
+        mv = 0;
+        for (int x = 0; x < 32; ++x) {
+          const int q = qb + col0 + x;
+          bool v = kvis;
+          if (p.causal) v = v && (k <= q + p.causal_off);
+          if (p.kv_seg) v = v && (kseg == sQseg[col0 + x]);
+          mv |= (v ? 1u : 0u) << x;
         }
       }
-      softmax_bar_sync();
       ok = mbar_wait(bar_s, i & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      uint8_t* pt_tile = sPT + half * BwdSmem::kTile;
-      uint8_t* dst_tile = sDST + half * BwdSmem::kTile;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32], dpv[32];
-        const int col0 = half * 64 + c * 32;  // query column within the block
-        tmem_ld32(t_row + cS + col0, sv);
-        tmem_ld32(t_row + cDP + col0, dpv);
-        tmem_ld_wait();
-        float pr[32], ds[32];
+      uint32_t sv[32], dpv[32];
+      tmem_ld32(t_row + cS + col0, sv);
+      tmem_ld32(t_row + cDP + col0, dpv);
+      tmem_ld_wait();
+      float pr[32], ds[32];
+      const float* rel = sRel + (r - col0 + 127);
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          const int cq = col0 + x;
-          const int q = qb + cq;
-          float s = __uint_as_float(sv[x]);
-          if (p.rel_bias != nullptr) s += sRel[r - cq + 127];
-          bool vis = kvis;
-          if (p.causal) vis = vis && (k <= q + p.causal_off);
-          if (p.kv_seg) vis = vis && (kseg == sQseg[cq]);
-          s = vis ? s : kMaskValue;
-          float e = (k_ok && q < p.Lq) ? __expf(s - sLse[cq]) : 0.f;
-          // A row with every key masked has lse = -1e10 + log(Lk), which fp32 rounds to -1e10:
-          // its probabilities are uniform over the Lk keys.
-          if (sLse[cq] < -5e9f && k_ok && q < p.Lq) e = inv_lk;
-          const float g = e * (__uint_as_float(dpv[x]) - sDelta[cq]);
-          pr[x] = e;
-          ds[x] = g;
-          // masks are additive, so the bias term receives the softmax gradient everywhere
-          if (p.d_rel_bias != nullptr && g != 0.f) atomicAdd(&sDRel[r - q + lq_pad], g);
-        }
+      for (int x = 0; x < 32; ++x) {
+        const int cq = col0 + x;
+        float s = __uint_as_float(sv[x]);
+        if (has_bias) s += rel[-x];
+        s = ((mv >> x) & 1u) ? s : kMaskValue;
+        const float lse2 = sLse[cq];
+        float e = exp2f(fmaf(s, kLog2e, -lse2));
+        // A row with every key masked has lse = -1e10 + log(Lk), which fp32 rounds to -1e10:
+        // its probabilities are uniform over the Lk keys.
+        if (lse2 < -5e9f) e = inv_lk;
+        if (!k_ok || qb + cq >= p.Lq) e = 0.f;
+        const float g = e * (__uint_as_float(dpv[x]) - sDelta[cq]);
+        pr[x] = e;
+        ds[x] = g;
+      }
+      if (p.d_rel_bias != nullptr) {
+        // masks are additive, so the bias term receives the softmax gradient everywhere
+        float* acc = sDRel + (r - qb - col0 + lq_pad);
+#pragma unroll
+        for (int x = 0; x < 32; ++x)
+          if (ds[x] != 0.f) atomicAdd(acc - x, ds[x]);
+      }
+      {
+        uint8_t* pt_tile = sPT + (part >> 1) * BwdSmem::kTile;
+        uint8_t* dst_tile = sDST + (part >> 1) * BwdSmem::kTile;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          store_swizzled_chunk(pt_tile, r, c * 4 + g, pr + g * 8);
-          store_swizzled_chunk(dst_tile, r, c * 4 + g, ds + g * 8);
+          store_swizzled_chunk(pt_tile, r, (part & 1) * 4 + g, pr + g * 8);
+          store_swizzled_chunk(dst_tile, r, (part & 1) * 4 + g, ds + g * 8);
         }
       }
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p);
-      // dQ partial: rows are queries here (TMEM lane = query within the block)
+      // dQ partial: rows are queries here (TMEM lane = query within the block); 16 columns each
       ok = mbar_wait(bar_dq, i & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
       {
-        uint32_t v[32];
-        tmem_ld32(t_row + cDQ + half * 32, v);
+        uint32_t v[16];
+        tmem_ld16(t_row + cDQ + part * 16, v);
         tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_dq_read);
         const int q = qb + r;
         if (q < p.Lq) {
-          float* dst = p.dQ + ((static_cast<long long>(b) * p.Lq + q) * p.H + h) * kAttnD + half * 32;
+          float* dst = p.dQ + ((static_cast<long long>(b) * p.Lq + q) * p.H + h) * kAttnD + part * 16;
 #pragma unroll
-          for (int x = 0; x < 32; x += 4)
+          for (int x = 0; x < 16; x += 4)
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + x),
                          "f"(__uint_as_float(v[x])), "f"(__uint_as_float(v[x + 1])),
                          "f"(__uint_as_float(v[x + 2])), "f"(__uint_as_float(v[x + 3]))
                          : "memory");
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_dq_read);
-      softmax_bar_sync();  // sLse/sDelta/sRel are rewritten at the top of the next iteration
+      softmax_bar_sync();  // the vectors of block i+1 are complete; those of block i are dead
     }
     if (ok) {
       // dK, dV accumulators are complete once the last bar_dq fired (same commit group).
-      uint32_t vk[32], vv[32];
-      tmem_ld32(t_row + cDK + half * 32, vk);
-      tmem_ld32(t_row + cDV + half * 32, vv);
+      uint32_t vk[16], vv[16];
+      tmem_ld16(t_row + cDK + part * 16, vk);
+      tmem_ld16(t_row + cDV + part * 16, vv);
       tmem_ld_wait();
       if (k_ok) {
-        __nv_bfloat16* dk = p.dK + b * p.dk_sb + static_cast<long long>(k) * p.dk_sl + h * p.dk_sh + half * 32;
-        __nv_bfloat16* dv = p.dV + b * p.dk_sb + static_cast<long long>(k) * p.dk_sl + h * p.dk_sh + half * 32;
-#pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          *reinterpret_cast<__nv_bfloat162*>(dk + x) =
-              __floats2bfloat162_rn(__uint_as_float(vk[x]), __uint_as_float(vk[x + 1]));
-          *reinterpret_cast<__nv_bfloat162*>(dv + x) =
-              __floats2bfloat162_rn(__uint_as_float(vv[x]), __uint_as_float(vv[x + 1]));
-        }
+        const long long off = b * p.dk_sb + static_cast<long long>(k) * p.dk_sl + h * p.dk_sh + part * 16;
+        store16_bf16(p.dK + off, vk, 1.f);
+        store16_bf16(p.dV + off, vv, 1.f);
       }
       softmax_bar_sync();
       if (p.d_rel_bias != nullptr) {
         // sDRel[t] holds sum dS over (k - q) = k0 + t - lq_pad for this key block
         float* out = p.d_rel_bias + static_cast<long long>(h) * p.nrel;
-        for (int t = threadIdx.x; t < lq_pad + 128; t += 256) {
+        for (int t = threadIdx.x; t < lq_pad + 128; t += kSoftmaxThreads) {
           const float g = sDRel[t];
           if (g != 0.f) {
             const int idx = k0 + (t - lq_pad) + p.rel_off;  // (k - q) + rel_off
@@ -659,7 +773,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     for (int it = 0; it < 2000; ++it) __nanosleep(1000);
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kCtrlWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -690,6 +804,8 @@ T5X_API int t5x_attention_fwd(const void* q, const void* k, const void* v, void*
                               int causal, int causal_off, void* stream) {
   if (B <= 0 || H <= 0 || Lq <= 0 || Lk <= 0) return 0;
   if (Lk > 512) return set_error("attention_fwd: Lk=%d > 512 is not covered by this kernel", Lk);
+  if (Lq > kFwdMaxLq && rel_bias != nullptr)
+    return set_error("attention_fwd: Lq=%d > %d with a relative bias is not covered", Lq, kFwdMaxLq);
   const CUtensorMap* tq = bhld_map(q, B, Lq, H, q_sb, q_sl, q_sh);
   const CUtensorMap* tk = bhld_map(k, B, Lk, H, k_sb, k_sl, k_sh);
   const CUtensorMap* tv = bhld_map(v, B, Lk, H, v_sb, v_sl, v_sh);
@@ -715,7 +831,7 @@ T5X_API int t5x_attention_fwd(const void* q, const void* k, const void* v, void*
     if (e != cudaSuccess) return set_error("attention_fwd attr: %s", cudaGetErrorString(e));
     attr_set[dev] = true;
   }
-  dim3 grid((Lq + 127) / 128, H, B);
+  dim3 grid(H, B);
   attn_fwd_kernel<<<grid, kAttnThreads, FwdSmem::kTotal, static_cast<cudaStream_t>(stream)>>>(
       *tq, *tk, *tv, p);
   count_launches(1);

@@ -24,7 +24,7 @@ native.register_signature("t5x_attention_bwd", [c_void_p] * 10 + [c_int] * 4 + [
                            c_int, c_void_p])
 
 MAX_LK = 512
-MAX_LQ = 4096
+MAX_LQ = 512
 
 
 def _strides_ok(t: torch.Tensor) -> bool:
@@ -88,6 +88,23 @@ class _FlashAttentionFn(torch.autograd.Function):
     return dq32.to(torch.bfloat16), dk, dv, d_rel, None, None, None, None, None, None
 
 
+_BUCKET_CACHE: dict = {}
+
+
+def _rel_buckets(Lq, Lk, q_offset, bidirectional, num_buckets, max_distance, device):
+  """Bucket index for every relative offset of an [Lq, Lk] attention: entry t stands for
+  (k - q_pos) = t - (Lq - 1) - q_offset. Cached: it depends on the shapes only."""
+  key = (Lq, Lk, q_offset, bool(bidirectional), num_buckets, max_distance, str(device))
+  b = _BUCKET_CACHE.get(key)
+  if b is None:
+    rel = torch.arange(Lq + Lk - 1, device=device) - (Lq - 1) - q_offset
+    b = ref.relative_position_bucket(rel, bidirectional, num_buckets, max_distance)
+    if len(_BUCKET_CACHE) > 256:
+      _BUCKET_CACHE.clear()
+    _BUCKET_CACHE[key] = b
+  return b
+
+
 def flash_attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None,
                     bidirectional: bool = True, num_buckets: int = 32, max_distance: int = 128,
                     key_mask: Optional[torch.Tensor] = None, causal: bool = False,
@@ -97,10 +114,8 @@ def flash_attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None,
   Lk = k.shape[1]
   rel_bias = None
   if bias_table is not None:
-    # index t <-> relative position (k - q_pos) = t - (Lq - 1) - q_offset
-    rel = torch.arange(Lq + Lk - 1, device=q.device) - (Lq - 1) - q_offset
-    buckets = ref.relative_position_bucket(rel, bidirectional, num_buckets, max_distance)
-    rel_bias = bias_table.float()[:, buckets].contiguous()
+    rel_bias = bias_table.float()[:, _rel_buckets(Lq, Lk, q_offset, bidirectional, num_buckets,
+                                                  max_distance, q.device)].contiguous()
   km = key_mask.to(torch.uint8).contiguous() if key_mask is not None else None
   qs = q_segment_ids.to(torch.int32).contiguous() if q_segment_ids is not None else None
   ks = kv_segment_ids.to(torch.int32).contiguous() if kv_segment_ids is not None else None
