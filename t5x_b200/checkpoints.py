@@ -423,11 +423,14 @@ class Checkpointer:
         is_leaf=lambda x: not isinstance(x, Mapping) or isinstance(x, _ParameterInfo))
     flat_fallback = state_utils.flatten_state_dict(fallback_state or {})
     missing = [k for k in flat_target if k not in flat_ckpt and k not in flat_fallback]
-    extra = [k for k in flat_ckpt if k not in flat_target]
-    if missing or extra:
-      raise ValueError(
-          "The target dict keys and state dict keys do not match: missing from checkpoint "
-          f"{sorted(missing)}; not in the model {sorted(extra)}")
+    if missing:
+      raise ValueError("The target dict keys and state dict keys do not match, target dict "
+                       f"contains keys {sorted(missing)} which are not present in the checkpoint")
+    # Checkpoint entries the target has no slot for (e.g. optimizer slots when restoring for
+    # inference) are left unread.
+    for k in flat_ckpt:
+      if k not in flat_target:
+        logging.debug("Not restoring key from ckpt: %s", k)
     restored = {}
     for name, tgt in flat_target.items():
       if name not in flat_ckpt:
@@ -687,7 +690,8 @@ class OrbaxCheckpointManagerInterface:
                force_keep_period: Optional[int] = None,
                metric_name_to_monitor: Optional[str] = None, metric_mode: str = "max",
                keep_checkpoints_without_metrics: bool = True):
-    self._directory = os.fspath(directory)
+    # A manager built only to restore (evaluation, inference) has no directory of its own.
+    self._directory = os.fspath(directory) if directory is not None else ""
     self._period = period or 1
     self._checkpoint_steps = set(checkpoint_steps or ())
     kwargs = dict(keep=keep, save_dtype=save_dtype or np.float32, restore_dtype=restore_dtype,

@@ -184,9 +184,18 @@ def get_dataset(mixture_or_task_name, task_feature_lengths, feature_converter, d
 def _span_corruption_source(split, shard_info, seed, sequence_length=None, **_):
   sl = sequence_length or {"inputs": 512, "targets": 114}
   off = {"train": 0, "validation": 1_000_003, "test": 2_000_003}.get(split, 0)
-  return synthetic.span_corruption_stream(seed + off, sl["inputs"], sl["targets"],
-                                          shard_id=shard_info.index,
-                                          num_shards=shard_info.num_shards)
+  stream = synthetic.span_corruption_stream(seed + off, sl["inputs"], sl["targets"],
+                                            shard_id=shard_info.index,
+                                            num_shards=shard_info.num_shards)
+  if split == "train":
+    return stream
+  # held-out splits are finite so that evaluation and batch inference terminate
+  import itertools
+  per_shard = -(-_HELD_OUT_EXAMPLES // shard_info.num_shards)
+  return itertools.islice(stream, per_shard)
+
+
+_HELD_OUT_EXAMPLES = 64
 
 
 def _token_accuracy(targets, predictions):
@@ -200,7 +209,8 @@ def register_synthetic_tasks(vocab_size: int = 32128) -> None:
   feats = {"inputs": Feature(vocab), "targets": Feature(vocab)}
   for name in ("synthetic_span_corruption", "c4_v220_span_corruption"):
     if name not in TaskRegistry:
-      TaskRegistry.add(name, _span_corruption_source, feats, metric_fns=[_token_accuracy])
+      TaskRegistry.add(name, _span_corruption_source, feats, metric_fns=[_token_accuracy],
+                       splits=("train", "validation", "test"))
 
 
 register_synthetic_tasks()

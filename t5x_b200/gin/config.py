@@ -587,6 +587,16 @@ def parse_config_file(path: str, skip_unknown: bool = False, _relative_to=None) 
     parse_config(f.read(), skip_unknown=skip_unknown, _filename=real)
 
 
+_MAIN_MODULE = None
+
+
+def set_main_module(module) -> None:
+  """The object that `import __main__ as x` binds in config files. Entry points that are called
+  as functions (rather than run as scripts) register themselves here."""
+  global _MAIN_MODULE
+  _MAIN_MODULE = module
+
+
 def _do_import(stmt: str, imports: Dict[str, Any], skip_unknown: bool):
   m = re.match(r"from\s+([\w.]+)\s+import\s+(\w+)(?:\s+as\s+(\w+))?$", stmt)
   try:
@@ -606,7 +616,7 @@ def _do_import(stmt: str, imports: Dict[str, Any], skip_unknown: bool):
     mod, alias = m.groups()
     if mod == "__main__":
       import sys
-      obj = sys.modules["__main__"]
+      obj = _MAIN_MODULE if _MAIN_MODULE is not None else sys.modules["__main__"]
     else:
       obj = _import_module(mod)
     if alias:
