@@ -350,7 +350,12 @@ class EncoderDecoderModel(BaseTransformerModel):
 
 
 def remove_prefix(sequence: torch.Tensor, prefix_length: torch.Tensor) -> torch.Tensor:
-  """Shifts each row left by its prefix length, zero-filling (t5x/models.py:1248-1282)."""
+  """Shifts each row left by its prefix length, zero-filling (t5x/models.py:1248-1282).
+  `sequence` is [batch, len] or [batch, num_decodes, len]."""
+  if sequence.dim() == 3:
+    b, n, l = sequence.shape
+    out = remove_prefix(sequence.reshape(b * n, l), prefix_length.repeat_interleave(n))
+    return out.view(b, n, l)
   b, l = sequence.shape
   idx = torch.arange(l, device=sequence.device)[None, :] + prefix_length[:, None].long()
   valid = idx < l

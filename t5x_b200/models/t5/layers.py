@@ -401,8 +401,13 @@ class MultiHeadDotProductAttention(nn.Module):
         # Per-example cache positions (prefix-LM prefill paths).
         rows = torch.arange(b, device=q.device)
         il = idx.long()
-        cache["cached_key"][rows, il] = k[:, 0]
-        cache["cached_value"][rows, il] = v[:, 0]
+        # A row already at the end of its buffer keeps stepping until the whole batch is done;
+        # its write is dropped (the one-hot update of the reference is all-zero there).
+        inb = (il < max_len)[:, None, None]
+        ic = il.clamp(max=max_len - 1)
+        cache["cached_key"][rows, ic] = torch.where(inb, k[:, 0], cache["cached_key"][rows, ic])
+        cache["cached_value"][rows, ic] = torch.where(inb, v[:, 0],
+                                                      cache["cached_value"][rows, ic])
         key_mask = pos[None, :] <= il[:, None]
         cache["cache_index"] = idx + 1
         k, v = cache["cached_key"], cache["cached_value"]
