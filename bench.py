@@ -129,6 +129,10 @@ def main() -> None:
   ap.add_argument("--targets-length", type=int, default=114)
   ap.add_argument("--microbatches", type=int, default=0)
   ap.add_argument("--skip-e2e", action="store_true")
+  ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                  help="dp: data parallel with the optimizer sharded over replicas (gradient "
+                       "reduction and weight broadcast fused into the Adafactor kernels over "
+                       "NVLink peer memory); tp: tensor parallel over all GPUs")
   args = ap.parse_args()
 
   if args.impl == "reference":
@@ -154,7 +158,10 @@ def main() -> None:
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local_rank)
   pstate.init_distributed("nccl")
-  st = pstate.setup_mesh(model_size=world)
+  st = pstate.setup_mesh(model_size=world if args.parallelism == "tp" else 1)
+  data_shards = 1 if args.parallelism == "tp" else world
+  if args.batch % data_shards:
+    raise SystemExit(f"--batch {args.batch} is not divisible by {data_shards} data shards")
   dev = st.device
   rank = st.rank
 
@@ -176,10 +183,12 @@ def main() -> None:
   trainer = trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, n_micro)
   n_params = sum(int(np.prod(getattr(p, "global_shape", p.shape))) for p in module.parameters())
 
-  # Every tensor-parallel rank consumes the same global batch (data axis = 1).
+  # Tensor-parallel ranks all consume the global batch; data-parallel ranks each take a shard.
+  from t5x_b200.data.dataset import ShardInfo
   lengths = {"inputs": args.inputs_length, "targets": args.targets_length}
   ds = data.get_dataset("synthetic_span_corruption", lengths, fc.EncDecFeatureConverter(pack=False),
-                        seed=0, batch_size=args.batch, num_epochs=None)
+                        seed=0, batch_size=args.batch // data_shards, num_epochs=None,
+                        shard_info=ShardInfo(st.rank % data_shards, data_shards))
 
   def pin(batch):
     out = {}
@@ -286,7 +295,9 @@ def main() -> None:
         "config": {"model": f"t5.1.1-{args.model}", "params": n_params,
                    "global_batch": args.batch, "seq_len": args.inputs_length + args.targets_length,
                    "inputs_length": args.inputs_length, "targets_length": args.targets_length,
-                   "parallelism": f"data1 x model{world}", "optimizer": "adafactor",
+                   "parallelism": (f"data1 x model{world}" if args.parallelism == "tp" else
+                                   f"data{world} x model1, optimizer sharded over data"),
+                   "optimizer": "adafactor",
                    "num_microbatches": n_micro,
                    "l2": "no explicit flush: every step streams the full weights, gradients and "
                          "activations (tens of GB), far larger than the 126 MB L2",

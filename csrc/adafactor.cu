@@ -14,17 +14,11 @@
 // and must be zero on entry to `stats`.
 #include <mutex>
 
+#include "adafactor_common.cuh"
 #include "common.cuh"
 #include "t5x_b200.h"
 
 namespace t5x {
-
-struct AdafactorScalars {  // per batch element, in scratch
-  float psq;   // sum p^2
-  float usq;   // sum u^2
-  float vsum;  // sum of the normalised second-moment vector (T5X "v_row")
-  float pad;
-};
 
 constexpr int kAfThreads = 256;
 constexpr int kAfTileR = 64;
@@ -193,23 +187,6 @@ __global__ void __launch_bounds__(kAfThreads)
   }
 }
 
-struct AfHyper {
-  float lr, eps2, clip_threshold, weight_decay, beta1, max_param_scale;
-  int multiply_by_parameter_scale, use_clip, use_wd, use_momentum, use_max_scale, skip_nan;
-};
-
-__device__ __forceinline__ float af_update_scale(const AdafactorScalars& s, float n,
-                                                 const AfHyper& h) {
-  float scale = h.lr;
-  if (h.multiply_by_parameter_scale) {
-    float ps = fmaxf(sqrtf(s.psq / n), h.eps2);
-    if (h.use_max_scale) ps = fminf(ps, h.max_param_scale);
-    scale *= ps;
-  }
-  if (h.use_clip) scale /= fmaxf(1.f, sqrtf(s.usq / n) / h.clip_threshold);
-  return scale;
-}
-
 // FACTORED: u = g * rf[r] * cf[c].  !FACTORED: u = g * rsqrt(v) with v already updated.
 template <bool FACTORED>
 __global__ void __launch_bounds__(kAfThreads)
@@ -314,23 +291,6 @@ AfScratch af_split(void* scratch, int batch, int R, int C) {
   a.cf = a.rf + static_cast<long long>(batch) * R;
   a.scal = reinterpret_cast<AdafactorScalars*>(a.cf + static_cast<long long>(batch) * C);
   return a;
-}
-AfHyper af_hyper(float lr, float eps2, float clip_threshold, float weight_decay, float beta1,
-                 float max_param_scale, int flags) {
-  AfHyper h;
-  h.lr = lr;
-  h.eps2 = eps2;
-  h.clip_threshold = clip_threshold;
-  h.weight_decay = weight_decay;
-  h.beta1 = beta1;
-  h.max_param_scale = max_param_scale;
-  h.multiply_by_parameter_scale = (flags >> 0) & 1;
-  h.use_clip = (flags >> 1) & 1;
-  h.use_wd = (flags >> 2) & 1;
-  h.use_momentum = (flags >> 3) & 1;
-  h.use_max_scale = (flags >> 4) & 1;
-  h.skip_nan = (flags >> 5) & 1;
-  return h;
 }
 int af_check(const char* what) {
   cudaError_t e = cudaGetLastError();

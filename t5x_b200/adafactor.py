@@ -244,11 +244,49 @@ class Adafactor(OptimizerDef):
     mbps = hp.multiply_by_parameter_scale
     if isinstance(mbps, HParamMap):
       mbps = mbps[path]
-    if self._try_native(param, state, grad, path, lr, decay, bool(mbps), weight_decay_rate,
-                        averaging_dims, factored_dims):
+    zinfo = getattr(param, "zero", None)
+    if zinfo is not None and self._fused_sharded_ok(param, state, grad, averaging_dims,
+                                                    factored_dims):
+      # gradient reduction and weight broadcast happen inside the update kernels
+      done = self._try_native(param, state, grad, path, lr, decay, bool(mbps),
+                              weight_decay_rate, averaging_dims, factored_dims, zinfo=zinfo)
+      assert done
       return param, state
-    return self._apply_torch(param, state, grad, lr, decay, bool(mbps), weight_decay_rate,
-                             averaging_dims, factored_dims)
+    if zinfo is not None:
+      from t5x_b200.ops import comm
+      comm.peer_reduce_f32_(grad, zinfo.grad_ptrs(), zinfo.numel)
+    if not self._try_native(param, state, grad, path, lr, decay, bool(mbps), weight_decay_rate,
+                            averaging_dims, factored_dims):
+      self._apply_torch(param, state, grad, lr, decay, bool(mbps), weight_decay_rate,
+                        averaging_dims, factored_dims)
+    if zinfo is not None:
+      comm.peer_push_bf16_(zinfo.bf16_ptrs(), param.bf16, zinfo.numel, skip_rank=zinfo.ctx.rank)
+    return param, state
+
+  def _fused_sharded_ok(self, param, state, grad, averaging_dims, factored_dims) -> bool:
+    """True when the NVLink-fused kernels cover this parameter: a factored [batch, R, C]
+    fp32 matrix with C % 4 == 0 that is not also tensor-parallel sharded."""
+    if factored_dims is None or param.dtype != torch.float32 or not param.is_contiguous():
+      return False
+    st = pstate.get()
+    if getattr(param, "shard_dim", None) is not None and st.model_size > 1:
+      return False
+    if self.hyper_params.beta1 is not None and self.dtype_momentum != torch.float32:
+      return False
+    nd = param.dim()
+    batch_dims = tuple(i for i in range(nd) if i not in averaging_dims)
+    nb = len(batch_dims)
+    if batch_dims != tuple(range(nb)):
+      return False
+    d1, d0 = factored_dims
+    rest = tuple(range(nb, nd))
+    if tuple(d1) + tuple(d0) == rest:
+      col_dims = d0
+    elif tuple(d0) + tuple(d1) == rest:
+      col_dims = d1
+    else:
+      return False
+    return int(np.prod([param.shape[d] for d in col_dims])) % 4 == 0
 
   # PyTorch statement (any rank, any rule). Sharded dims are reduced over the model axis.
   def _apply_torch(self, param, state, grad, lr, decay, mbps, weight_decay_rate,
@@ -335,7 +373,7 @@ class Adafactor(OptimizerDef):
 
   # Fused CUDA path for fp32 parameters laid out [batch..., rows, cols].
   def _try_native(self, param, state, grad, path, lr, decay, mbps, weight_decay_rate,
-                  averaging_dims, factored_dims) -> bool:
+                  averaging_dims, factored_dims, zinfo=None) -> bool:
     if not (param.is_cuda and param.dtype == torch.float32 and grad.dtype == torch.float32 and
             param.is_contiguous() and grad.is_contiguous()):
       return False
@@ -423,7 +461,12 @@ class Adafactor(OptimizerDef):
         ld_bf16 = bf.stride(-2)
         bbs = bf.stride(0) if nb == 1 else 0
     scratch = _scratch(param.device, native.adafactor_scratch_floats(batch, R, C))
-    native.adafactor_stats_(param, grad, scratch, batch, R, C, hp.epsilon1)
+    if zinfo is not None:
+      from t5x_b200.ops import comm
+      comm.dist_adafactor_stats_(param, zinfo.grad_ptrs(), grad, scratch, batch, R, C,
+                                 hp.epsilon1)
+    else:
+      native.adafactor_stats_(param, grad, scratch, batch, R, C, hp.epsilon1)
     rows_sharded = sharded and shard_dim in row_dims
     cols_sharded = sharded and shard_dim in col_dims
     o_row, o_col = 0, batch * R
@@ -449,8 +492,12 @@ class Adafactor(OptimizerDef):
       us = scratch[o_scal:o_scal + 4 * batch].view(batch, 4)[:, 1].contiguous()
       dist.all_reduce(us, group=st.model_group)
       scratch[o_scal:o_scal + 4 * batch].view(batch, 4)[:, 1] = us
-    native.adafactor_apply_(param, grad, m, bf, scratch, batch, R, C, n_global, ld_bf16=ld_bf16,
-                            bf16_batch_stride=bbs, **common)
+    if zinfo is not None:
+      comm.dist_adafactor_apply_(param, grad, m, zinfo.bf16_ptrs(), scratch, batch, R, C,
+                                 n_global, **common)
+    else:
+      native.adafactor_apply_(param, grad, m, bf, scratch, batch, R, C, n_global,
+                              ld_bf16=ld_bf16, bf16_batch_stride=bbs, **common)
     return True
 
   def apply_gradient(self, hyper_params, params, state, grads):
@@ -479,6 +526,9 @@ class Adafactor(OptimizerDef):
         for k in flat_p:
           flat_g[k].mul_(scale.to(flat_g[k].dtype))
       for k, p in flat_p.items():
+        zinfo = getattr(p, "zero", None)
+        if zinfo is not None and not zinfo.mine:
+          continue  # its owner updates it and pushes the new bf16 weights here
         self.apply_param_gradient(step, hyper_params, p, flat_s[k], flat_g[k], k)
     finally:
       self.hyper_params = saved_hp

@@ -1,0 +1,149 @@
+"""Optimizer sharding over the data axis by parameter ownership.
+
+With D data-parallel replicas, every parameter has one owner rank. All ranks hold the bf16
+working weights and accumulate full fp32 gradients locally; at the end of a step the owner of
+a parameter
+
+  1. pulls the D gradient copies over NVLink and sums them inside the optimizer's first pass
+     (`t5x_dist_adafactor_stats`), so the reduce-scatter is never a separate collective,
+  2. runs the rest of the update on its own fp32 master copy and optimizer slots, and
+  3. stores the new bf16 weights straight into every replica's working copy from the update
+     kernel (`t5x_dist_adafactor_apply`), so there is no separate all-gather either.
+
+Two stream-ordered barriers bracket the update: one after backward (all gradient copies are
+complete) and one after the update (all pushes have landed, and nobody is still reading this
+rank's gradients). fp32 master weights and optimizer slots of parameters a rank does not own go
+stale during training; `sync_replicas()` refreshes them from the owners and is called whenever
+the state leaves the training loop (end of `Trainer.train`, checkpointing, evaluation of
+weight metrics).
+
+This is the reference's "2-D parameter partitioning" (optimizer state sharded over the data
+axis, t5x/partitioning.py:615-676) restated for one process per GPU with peer memory.
+"""
+from __future__ import annotations
+
+import logging
+from typing import Dict, List, Mapping, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from t5x_b200.parallel import state as pstate
+
+_ALIGN = 128  # elements; keeps every parameter's offset 256-byte aligned in both buffers
+
+
+class ZeroInfo:
+  """Per-parameter record: where it lives in the symmetric buffers and who updates it."""
+  __slots__ = ("ctx", "offset", "numel", "owner")
+
+  def __init__(self, ctx, offset: int, numel: int, owner: int):
+    self.ctx, self.offset, self.numel, self.owner = ctx, offset, numel, owner
+
+  @property
+  def mine(self) -> bool:
+    return self.owner == self.ctx.rank
+
+  def grad_ptrs(self):
+    return self.ctx.grads.ptrs_at(self.offset)
+
+  def bf16_ptrs(self):
+    return self.ctx.weights.ptrs_at(self.offset)
+
+
+def assign_owners(sizes: Mapping[str, int], world: int) -> Dict[str, int]:
+  """Largest-first greedy balancing of parameter sizes over ranks; deterministic."""
+  load = [0] * world
+  owners = {}
+  for name in sorted(sizes, key=lambda k: (-sizes[k], k)):
+    r = min(range(world), key=lambda i: (load[i], i))
+    owners[name] = r
+    load[r] += sizes[name]
+  return owners
+
+
+class ZeroContext:
+  """Symmetric gradient / weight buffers for a flat {name: fp32 parameter} mapping."""
+
+  def __init__(self, params_flat: Mapping[str, torch.Tensor], group=None):
+    from t5x_b200.ops import comm
+    st = pstate.get()
+    self.group = group if group is not None else (st.data_group or dist.group.WORLD)
+    self.rank = dist.get_rank(self.group)
+    self.world = dist.get_world_size(self.group)
+    names = [k for k, p in params_flat.items()
+             if isinstance(p, torch.Tensor) and p.is_cuda and p.dtype == torch.float32]
+    sizes = {k: int(params_flat[k].numel()) for k in names}
+    self.owners = assign_owners(sizes, self.world)
+    offset = 0
+    self.infos: Dict[str, ZeroInfo] = {}
+    for k in names:
+      self.infos[k] = ZeroInfo(self, offset, sizes[k], self.owners[k])
+      offset += -(-sizes[k] // _ALIGN) * _ALIGN
+    self.total = max(offset, _ALIGN)
+    device = params_flat[names[0]].device
+    self.grads = comm.SymmetricBuffer(self.total, torch.float32, self.group, device)
+    self.weights = comm.SymmetricBuffer(self.total, torch.bfloat16, self.group, device)
+    for k in names:
+      p, info = params_flat[k], self.infos[k]
+      g = self.grads.tensor[info.offset:info.offset + info.numel].view(p.shape)
+      w = self.weights.tensor[info.offset:info.offset + info.numel].view(p.shape)
+      old = getattr(p, "bf16", None)
+      w.copy_(old if old is not None else p.detach())
+      g.zero_()
+      p.bf16, p.main_grad, p.grad_ready, p.zero = w, g, False, info
+    self.params = {k: params_flat[k] for k in names}
+    torch.cuda.synchronize(device)
+    dist.barrier(group=self.group)
+    owned = sum(sizes[k] for k in names if self.owners[k] == self.rank)
+    logging.info("optimizer sharding: rank %d/%d owns %.1f M of %.1f M parameters", self.rank,
+                 self.world, owned / 1e6, sum(sizes.values()) / 1e6)
+
+  # -- step protocol -------------------------------------------------------------------------
+  def gradients_complete(self) -> None:
+    """Barrier after the last backward pass: every rank's gradient copy is final."""
+    self.grads.barrier(channel=0)
+
+  def update_complete(self) -> None:
+    """Barrier after the update: all weight pushes have landed and no rank still reads
+    another's gradients."""
+    self.grads.barrier(channel=1)
+
+  def sync_replicas(self, optimizer_state=None) -> None:
+    """Refreshes fp32 master weights (and optimizer slots) on non-owners from the owners."""
+    ranks = dist.get_process_group_ranks(self.group)
+    for k, p in self.params.items():
+      dist.broadcast(p.data, src=ranks[self.owners[k]], group=self.group)
+    if optimizer_state is not None:
+      from t5x_b200.utils import tree as tree_utils
+      flat = tree_utils.flatten_dict(optimizer_state)
+      by_param = {}
+      for path, v in flat.items():
+        if isinstance(v, torch.Tensor) and v.is_cuda:
+          by_param.setdefault(path[:-1], []).append(v)
+      for k in self.params:
+        for v in by_param.get(tuple(k) if not isinstance(k, tuple) else k, []):
+          dist.broadcast(v, src=ranks[self.owners[k]], group=self.group)
+
+
+_ACTIVE: Optional[ZeroContext] = None
+
+
+def active() -> Optional[ZeroContext]:
+  return _ACTIVE
+
+
+def enable(params_flat: Mapping[str, torch.Tensor], group=None) -> Optional[ZeroContext]:
+  """Shards the optimizer over the data axis if it has more than one replica on GPUs."""
+  global _ACTIVE
+  st = pstate.get()
+  if not dist.is_initialized() or st.data_size <= 1 or st.device.type != "cuda":
+    return None
+  _ACTIVE = ZeroContext(params_flat, group)
+  return _ACTIVE
+
+
+def disable() -> None:
+  global _ACTIVE
+  _ACTIVE = None

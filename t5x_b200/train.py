@@ -203,6 +203,8 @@ def train(*, model: models.BaseModel, train_dataset_cfg: utils.DatasetConfig,
 
   def _save(force=True):
     tick = time.time()
+    if hasattr(trainer, "sync_replicas"):
+      trainer.sync_replicas()
     fns = checkpoint_cfg.save.state_transformation_fns if checkpoint_cfg.save else ()
     checkpoint_manager.save(trainer.train_state, fns, force=force)
     checkpoint_manager.wait_until_finished()
@@ -294,6 +296,8 @@ def train(*, model: models.BaseModel, train_dataset_cfg: utils.DatasetConfig,
   finally:
     if gc_period:
       gc.enable()
+    if hasattr(trainer, "sync_replicas"):
+      trainer.sync_replicas()
     if old_handler is not None:
       signal.signal(signal.SIGTERM, old_handler)
     trainer.train_metrics_manager.flush()

@@ -287,7 +287,13 @@ def reduce_gradients_over_data_axis(grads_flat: Mapping[str, torch.Tensor], para
     for k, g in grads_flat.items():
       if getattr(params_flat[k], "expert_sharded", False):
         continue
+      if getattr(params_flat[k], "zero", None) is not None:
+        continue  # summed by its owner inside the optimizer kernels
       dist.all_reduce(g, group=st.data_group)
+  from t5x_b200.parallel import zero
+  ctx = zero.active()
+  if ctx is not None:
+    ctx.gradients_complete()
 
 
 # ----------------------------------------------------------------------------
@@ -323,7 +329,36 @@ def accumulate_grads_microbatched(model, train_state, batch: BatchType, dropout_
     metrics = m if metrics is None else merge_metrics(metrics, m)
   grads = _collect_grads(flat)
   reduce_gradients_over_data_axis(grads, flat)
+  metrics = reduce_metrics_over_data_axis(metrics)
   return tree_utils.unflatten_dict(grads), metrics, None
+
+
+_SUMMED_METRIC_FIELDS = ("total", "count", "numerator")
+
+
+def reduce_metrics_over_data_axis(metrics: MetricMapType) -> MetricMapType:
+  """Sums the per-example accumulators of model metrics over the data-parallel replicas, so
+  that every rank reports the metrics of the global batch (one small all-reduce per step)."""
+  st = pstate.get()
+  if metrics is None or st.data_size * st.expert_size <= 1 or st.data_group is None \
+      or not dist.is_initialized():
+    return metrics
+  slots = []
+  for name in sorted(metrics):
+    m = metrics[name]
+    for f in _SUMMED_METRIC_FIELDS:
+      v = getattr(m, f, None)
+      if v is not None:
+        slots.append((name, f, v))
+  if not slots:
+    return metrics
+  vec = torch.stack([torch.as_tensor(v, device=st.device).double().reshape(()) for _, _, v in slots])
+  dist.all_reduce(vec, group=st.data_group)
+  out = dict(metrics)
+  for i, (name, f, v) in enumerate(slots):
+    dtype = v.dtype if isinstance(v, torch.Tensor) else torch.float32
+    out[name] = out[name].replace(**{f: vec[i].to(dtype)})
+  return out
 
 
 def apply_grads(train_state, grad_accum, metrics: MetricMapType, learning_rate,
@@ -337,6 +372,10 @@ def apply_grads(train_state, grad_accum, metrics: MetricMapType, learning_rate,
   with torch.no_grad():
     new_train_state = train_state.apply_gradient(grad_accum, learning_rate=learning_rate,
                                                  **(other_state_variables or {}))
+    from t5x_b200.parallel import zero
+    ctx = zero.active()
+    if ctx is not None:
+      ctx.update_complete()
   metrics = dict(metrics)
   metrics["learning_rate"] = metrics_lib.AveragePerStep(total=torch.as_tensor(learning_rate))
   metrics["learning_rate/current"] = metrics_lib.LastValue(value=torch.as_tensor(learning_rate))
@@ -442,8 +481,20 @@ class BaseTrainer(abc.ABC):
       if torch.cuda.is_available():
         torch.cuda.nvtx.range_pop()
       metrics = metrics_update if metrics is None else merge_metrics(metrics, metrics_update)
+    self._replicas_stale = True
     return self.train_metrics_manager.write_metrics_summary(metrics, start_step + num_steps,
                                                             num_steps)
+
+  def sync_replicas(self) -> None:
+    """With the optimizer sharded over the data axis, brings every replica's fp32 master
+    weights and optimizer slots up to date with their owners. Callers invoke it whenever the
+    state leaves the training loop (checkpointing, returning the final state); forward passes
+    do not need it because they read the bf16 working weights, which are always current."""
+    from t5x_b200.parallel import zero
+    ctx = zero.active()
+    if ctx is not None and getattr(self, "_replicas_stale", False):
+      ctx.sync_replicas(getattr(self.train_state, "param_states", None))
+    self._replicas_stale = False
 
   def compile_train(self, batch) -> None:
     """Warms up the train step's kernels and allocator pools (no-op on the CPU path): the
@@ -514,8 +565,29 @@ class Trainer(BaseTrainer):
                      eval_names=eval_names, summary_dir=summary_dir,
                      train_state_axes=train_state_axes, rng=rng)
     if hasattr(train_state, "params"):
+      # Sharding allocates the working weights and gradient accumulators itself (in memory
+      # that all replicas map); only parameters it does not cover get private buffers.
+      self._maybe_shard_optimizer(train_state, weight_metrics_computer)
       attach_compute_buffers(train_state.params,
                              bf16_copy=self._device.type == "cuda", main_grad=True)
+
+  def _maybe_shard_optimizer(self, train_state, weight_metrics_computer) -> None:
+    """Shards the optimizer over the data axis (see `t5x_b200.parallel.zero`) when there is
+    more than one replica on GPUs and nothing needs the fully reduced gradient on every
+    rank (weight metrics, global-norm clipping). `T5X_B200_OPTIMIZER_SHARDING=0` keeps the
+    plain all-reduce."""
+    from t5x_b200 import adafactor
+    from t5x_b200.parallel import zero
+    st = pstate.get()
+    if (os.environ.get("T5X_B200_OPTIMIZER_SHARDING", "1") == "0" or st.data_size <= 1 or
+        st.expert_size > 1 or self._device.type != "cuda" or weight_metrics_computer is not None):
+      return
+    opt_def = getattr(getattr(train_state, "_optimizer", None), "optimizer_def", None)
+    if not isinstance(opt_def, adafactor.Adafactor):
+      return
+    if opt_def.hyper_params.global_norm_clip_threshold:
+      return
+    zero.enable(tree_utils.flatten_dict(train_state.params), st.data_group)
 
   def _train_step(self, train_state, batch, step_num):
     step = int(step_num)

@@ -1,0 +1,120 @@
+"""Child process of the multi-GPU tests: one rank per GPU, launched by torchrun.
+
+  torchrun --nproc-per-node N tests/multi_gpu_worker.py <case> <out_dir>
+
+Each case writes `<out_dir>/rank<r>.json` with what the parent test asserts on.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from t5x_b200.parallel import state as pstate  # noqa: E402
+
+
+def _setup():
+  local = int(os.environ.get("LOCAL_RANK", "0"))
+  torch.cuda.set_device(local)
+  pstate.init_distributed("nccl")
+  return pstate.setup_mesh(model_size=1)
+
+
+def case_collectives(out):
+  """peer_reduce / peer_push / barrier against torch.distributed results."""
+  from t5x_b200.ops import comm, native
+  st = _setup()
+  n = 1_000_003
+  buf = comm.SymmetricBuffer(n, torch.float32)
+  g = torch.Generator(device="cuda").manual_seed(100 + st.rank)
+  buf.tensor.copy_(torch.randn(n, device="cuda", generator=g))
+  expect = buf.tensor.clone()
+  dist.all_reduce(expect)
+  buf.barrier(0)
+  dst = torch.empty(n, device="cuda")
+  comm.peer_reduce_f32_(dst, buf.ptrs_at(0), n)
+  buf.barrier(1)
+  err_reduce = float((dst - expect).abs().max())
+  # push: rank r broadcasts its slice [r*k, (r+1)*k) of a bf16 buffer to everyone
+  k = 4099
+  wb = comm.SymmetricBuffer(k * st.world_size, torch.bfloat16)
+  wb.tensor.zero_()
+  src = torch.full((k,), float(st.rank + 1), device="cuda", dtype=torch.bfloat16)
+  wb.barrier(0)
+  comm.peer_push_bf16_(wb.ptrs_at(st.rank * k), src, k)
+  wb.barrier(1)
+  native.check_status()
+  got = wb.tensor.float().view(st.world_size, k)
+  ok_push = all(bool((got[r] == r + 1).all()) for r in range(st.world_size))
+  json.dump({"err_reduce": err_reduce, "ok_push": ok_push}, out)
+
+
+def _tiny_trainer(n_micro=2):
+  from t5x_b200 import adafactor, models, train_state as ts_lib, trainer as trainer_lib
+  from t5x_b200.data import vocabularies
+  from t5x_b200.models.t5 import network
+  from t5x_b200.utils import schedules
+  st = pstate.get()
+  cfg = network.T5Config(vocab_size=512, dtype="bfloat16", emb_dim=128, num_heads=2,
+                         num_encoder_layers=2, num_decoder_layers=2, head_dim=64, mlp_dim=256,
+                         mlp_activations=("gelu", "linear"), dropout_rate=0.0)
+  torch.manual_seed(7)
+  module = network.Transformer(cfg, device=st.device)
+  vocab = vocabularies.PassThroughVocabulary(512)
+  opt = adafactor.Adafactor(decay_rate=0.8, step_offset=0,
+                            logical_factor_rules=adafactor.standard_logical_factor_rules())
+  model = models.EncoderDecoderModel(module, vocab, vocab, opt, z_loss=1e-4)
+  state = ts_lib.FlaxOptimTrainState.create(opt, model.get_initial_variables(None, None))
+  lr_fn = schedules.create_learning_rate_scheduler("constant", 0.01, 0)
+  return trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, n_micro), module
+
+
+def _batches(rank, world, steps, per_rank=8):
+  g = torch.Generator().manual_seed(3)
+  out = []
+  for _ in range(steps):
+    enc = torch.randint(1, 512, (per_rank * world, 128), generator=g)
+    dec = torch.randint(1, 512, (per_rank * world, 128), generator=g)
+    sl = slice(rank * per_rank, (rank + 1) * per_rank)
+    dec_in = torch.cat([torch.zeros(per_rank * world, 1, dtype=torch.long), dec[:, :-1]], 1)
+    out.append({"encoder_input_tokens": enc[sl], "decoder_input_tokens": dec_in[sl],
+                "decoder_target_tokens": dec[sl],
+                "decoder_loss_weights": torch.ones(per_rank, 128)})
+  return out
+
+
+def case_train(out):
+  """Three train steps of a small model; the parent compares the sharded-optimizer run with
+  the all-reduce run (T5X_B200_OPTIMIZER_SHARDING=0)."""
+  from t5x_b200.ops import native
+  from t5x_b200.parallel import zero
+  st = _setup()
+  trainer, module = _tiny_trainer()
+  batches = _batches(st.rank, st.world_size, 3)
+  summary = trainer.train(iter(batches), 3, start_step=0).result()
+  trainer.sync_replicas()
+  native.check_status()
+  torch.cuda.synchronize()
+  flat = torch.cat([p.detach().float().reshape(-1) for p in module.parameters()])
+  bf = torch.cat([p.bf16.float().reshape(-1) for p in module.parameters()])
+  json.dump({"loss": float(summary["loss"].value), "sharded": zero.active() is not None,
+             "param_sum": float(flat.double().sum()), "param_abs": float(flat.double().abs().sum()),
+             "bf16_abs": float(bf.double().abs().sum()),
+             "first": flat[:8].tolist()}, out)
+  trainer.close()
+
+
+CASES = {"collectives": case_collectives, "train": case_train}
+
+if __name__ == "__main__":
+  case, out_dir = sys.argv[1], sys.argv[2]
+  rank = int(os.environ.get("RANK", "0"))
+  with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
+    CASES[case](f)
+  if dist.is_initialized():
+    dist.barrier()
+    dist.destroy_process_group()
