@@ -296,7 +296,8 @@ def main() -> None:
                    "global_batch": args.batch, "seq_len": args.inputs_length + args.targets_length,
                    "inputs_length": args.inputs_length, "targets_length": args.targets_length,
                    "parallelism": (f"data1 x model{world}" if args.parallelism == "tp" else
-                                   f"data{world} x model1, optimizer sharded over data"),
+                                   f"data{world} x model1" +
+                                   (", optimizer sharded over data" if world > 1 else "")),
                    "optimizer": "adafactor",
                    "num_microbatches": n_micro,
                    "l2": "no explicit flush: every step streams the full weights, gradients and "

@@ -1,0 +1,183 @@
+// Pieces shared by the one-CTA and the CTA-pair GEMM kernels: problem description, row
+// load/store helpers and the epilogue of one accumulator tile.
+#pragma once
+#include "common.cuh"
+
+namespace t5x {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+constexpr int kKernelIdGemm = 1;
+
+enum GemmEpilogue : int { kEpiPlain = 0, kEpiGatedGelu = 1, kEpiResidual = 2 };
+
+struct GemmParams {
+  int M, N, K, batch;
+  int a_mn, b_mn;
+  int out_fp32, accumulate;
+  void* C;
+  long long ldc, c_batch_stride;  // elements
+  const __nv_bfloat16* R;         // residual (bf16), same shape as C
+  long long ldr, r_batch_stride;
+  __nv_bfloat16* H0;  // gated-GELU: optional copies of the two pre-activations
+  __nv_bfloat16* H1;
+  long long ldh;
+  float alpha;
+  int tiles_m, tiles_n;
+  int* status;
+};
+
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const float* v, int n_valid,
+                                               bool vec_ok) {
+  if (vec_ok && n_valid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(v[i * 8 + 0], v[i * 8 + 1]);
+      __nv_bfloat162 p1 = __floats2bfloat162_rn(v[i * 8 + 2], v[i * 8 + 3]);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(v[i * 8 + 4], v[i * 8 + 5]);
+      __nv_bfloat162 p3 = __floats2bfloat162_rn(v[i * 8 + 6], v[i * 8 + 7]);
+      uint4 u;
+      u.x = *reinterpret_cast<uint32_t*>(&p0);
+      u.y = *reinterpret_cast<uint32_t*>(&p1);
+      u.z = *reinterpret_cast<uint32_t*>(&p2);
+      u.w = *reinterpret_cast<uint32_t*>(&p3);
+      reinterpret_cast<uint4*>(dst)[i] = u;
+    }
+  } else {
+    for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = __float2bfloat16(v[i]);
+  }
+}
+
+__device__ __forceinline__ void load_row_bf16(const __nv_bfloat16* src, float* v, int n_valid,
+                                              bool vec_ok) {
+  if (vec_ok && n_valid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 u = reinterpret_cast<const uint4*>(src)[i];
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(p[j]);
+        v[i * 8 + j * 2] = f.x;
+        v[i * 8 + j * 2 + 1] = f.y;
+      }
+    }
+  } else {
+    for (int i = 0; i < 32; ++i) v[i] = (i < n_valid) ? __bfloat162float(src[i]) : 0.f;
+  }
+}
+
+// Tile order: groups of kRasterGroup row tiles are walked column by column, so that the tiles
+// in flight at one time (one per SM or SM pair) share a few A row blocks and a few B column
+// blocks instead of one A block and every B block; the operands of a wave then fit in L2.
+constexpr int kRasterGroup = 8;
+__device__ __forceinline__ void gemm_tile_coords(const GemmParams& p, int tile, int tiles_per_batch,
+                                                 int& b, int& mt, int& nt) {
+  b = tile / tiles_per_batch;
+  const int rem = tile - b * tiles_per_batch;
+  const int per_group = kRasterGroup * p.tiles_n;
+  const int g = rem / per_group;
+  const int first_m = g * kRasterGroup;
+  const int gsz = min(kRasterGroup, p.tiles_m - first_m);
+  const int r = rem - g * per_group;
+  nt = r / gsz;
+  mt = first_m + (r - nt * gsz);
+}
+
+// Epilogue of one 128-row accumulator tile held in TMEM columns [t_cols, t_cols + BN): the
+// calling warp owns lane quarter q (rows m0 + 32q .. +31), `c_vec_ok` says whether 16-byte
+// stores to C are legal.
+template <int BN, int EPI>
+__device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t t_row, int m0,
+                                                   int n0, int b, int q, int lane,
+                                                   bool c_vec_ok) {
+  const int row = m0 + q * 32 + lane;
+  const bool row_ok = row < p.M;
+
+  if (EPI == kEpiGatedGelu) {
+    constexpr int kHalf = BN / 2;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.c_batch_stride +
+                         static_cast<long long>(row) * p.ldc;
+#pragma unroll 1
+    for (int c = 0; c < kHalf / 32; ++c) {
+      uint32_t r0[32], r1[32];
+      tmem_ld32(t_row + c * 32, r0);
+      tmem_ld32(t_row + kHalf + c * 32, r1);
+      tmem_ld_wait();
+      const int col = n0 + c * 32;
+      const int n_valid = p.N - col;
+      if (row_ok && n_valid > 0) {
+        float g[32], h0[32], h1[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          h0[i] = __uint_as_float(r0[i]);
+          h1[i] = __uint_as_float(r1[i]);
+          g[i] = gelu_tanh(h0[i]) * h1[i];
+        }
+        store_row_bf16(out + col, g, n_valid, c_vec_ok);
+        if (p.H0 != nullptr) {
+          const bool hv = (p.ldh % 8 == 0);
+          store_row_bf16(p.H0 + static_cast<long long>(row) * p.ldh + col, h0, n_valid, hv);
+          store_row_bf16(p.H1 + static_cast<long long>(row) * p.ldh + col, h1, n_valid, hv);
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld32(t_row + c * 32, r);
+      tmem_ld_wait();
+      const int col = n0 + c * 32;
+      const int n_valid = p.N - col;
+      if (row_ok && n_valid > 0) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        if (EPI == kEpiResidual) {
+          float rr[32];
+          const bool rv = (p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+          load_row_bf16(p.R + b * p.r_batch_stride + static_cast<long long>(row) * p.ldr + col,
+                        rr, n_valid, rv);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += rr[i];
+        }
+        if (p.out_fp32) {
+          float* out = reinterpret_cast<float*>(p.C) + b * p.c_batch_stride +
+                       static_cast<long long>(row) * p.ldc + col;
+          const bool fv = (p.ldc % 4 == 0) && n_valid >= 32;
+          if (fv) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float4 o = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+              if (p.accumulate) {
+                float4 old = reinterpret_cast<float4*>(out)[i];
+                o.x += old.x;
+                o.y += old.y;
+                o.z += old.z;
+                o.w += old.w;
+              }
+              reinterpret_cast<float4*>(out)[i] = o;
+            }
+          } else {
+            for (int i = 0; i < 32 && i < n_valid; ++i)
+              out[i] = p.accumulate ? out[i] + v[i] : v[i];
+          }
+        } else {
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.c_batch_stride +
+                               static_cast<long long>(row) * p.ldc + col;
+          if (p.accumulate) {
+            float old[32];
+            load_row_bf16(out, old, n_valid, c_vec_ok);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += old[i];
+          }
+          store_row_bf16(out, v, n_valid, c_vec_ok);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace t5x

@@ -1,0 +1,269 @@
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2): one 256 x 256 output tile per pair.
+//
+// Why pairs: with one CTA per tile a 128 x 256 tile stages (128 + 256) x 64 operand elements
+// per 64-deep k block, and the shared memory of one SM has to absorb those TMA writes while the
+// tensor core reads them back; that traffic, not the MMA rate, bounds the one-CTA kernel.
+// A pair computes 256 x 256 with each CTA staging only its own 128 rows of A and its own 128
+// columns of B (the tensor cores of both SMs read both B halves), a third less shared-memory
+// traffic per FLOP.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer (both CTAs, own halves), warp 1 = MMA
+// issuer (even CTA only; owns the TMEM allocation in both), warps 2..5 = epilogue of the
+// CTA's own 128 accumulator rows. Barriers: `full` lives in the even CTA and counts the bytes
+// of both CTAs' loads; `empty` and `tmem_full` exist in both CTAs and are signalled by one
+// tcgen05.commit addressed to both; `tmem_empty` lives in the even CTA and collects the
+// arrivals of all eight epilogue warps. Every wait is bounded and TMA loads never use
+// cluster multicast.
+#include <algorithm>
+
+#include "gemm_common.cuh"
+
+namespace t5x {
+
+constexpr int kPairBN = 256;
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = kBM * kBK * 2;           // 128 rows of A
+constexpr int kPairBBytes = (kPairBN / 2) * kBK * 2;  // 128 columns of B
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
+constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + 1024 + 1024;
+constexpr int kKernelIdGemmPair = 2;
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+  constexpr int BN = kPairBN;
+  constexpr int kStages = kPairStages;
+  constexpr int kTileN = (EPI == kEpiGatedGelu) ? BN / 2 : BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + kStages * kPairABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kPairStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* tmem_full = bars + 2 * kStages;
+  uint64_t* tmem_empty = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = even CTA (issues the MMAs)
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if (EPI == kEpiGatedGelu) tma_prefetch_desc(&tmB2);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;  // tiles_m counts 256-row tiles here
+  const int total_tiles = tiles_per_batch * p.batch;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        int b, mt, nt;
+        gemm_tile_coords(p, tile, tiles_per_batch, b, mt, nt);
+        const int m0 = mt * (2 * kBM) + static_cast<int>(cta) * kBM;
+        const int n_tile = nt * kTileN;
+        // this CTA's 128 B columns: its half of the tile, or (gated) the same 128 columns of
+        // wi_0 for the even CTA and of wi_1 for the odd one
+        const int n0 = (EPI == kEpiGatedGelu) ? n_tile : n_tile + static_cast<int>(cta) * (BN / 2);
+        const CUtensorMap* tb = (EPI == kEpiGatedGelu && cta == 1) ? &tmB2 : &tmB;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+            report_status(p.status, kStatusTimeoutProducer, kKernelIdGemmPair, tile, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          if (cta == 0) mbar_expect_tx(&full[stage], 2 * kPairStageBytes);
+          const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
+          uint8_t* a_dst = sA + stage * kPairABytes;
+          uint8_t* b_dst = sB + stage * kPairBBytes;
+          const int k0 = kb * kBK;
+          if (!p.a_mn) {
+            tma_load_3d_pair(a_dst, &tmA, bar, k0, m0, b);  // box {64 k, 128 m, 1}
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)  // box {64 m, 64 k, 1}
+              tma_load_3d_pair(a_dst + j * 8192, &tmA, bar, m0 + 64 * j, k0, b);
+          }
+          if (!p.b_mn) {
+            tma_load_3d_pair(b_dst, tb, bar, k0, n0, b);  // box {64 k, 128 n, 1}
+          } else {
+#pragma unroll
+            for (int j = 0; j < (BN / 2) / 64; ++j)  // box {64 n, 64 k, 1}
+              tma_load_3d_pair(b_dst + j * 8192, tb, bar, n0 + 64 * j, k0, b);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA) ------------------------------
+    if (lane == 0 && cta == 0) {
+      const uint32_t idesc = make_idesc_bf16(2 * kBM, BN, p.a_mn, p.b_mn);
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u;
+      const uint32_t b_kstep = p.b_mn ? 2048u : 32u;
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u;
+      const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) {
+          report_status(p.status, kStatusTimeoutMma, kKernelIdGemmPair, tile, -1);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            report_status(p.status, kStatusTimeoutMma, kKernelIdGemmPair, tile, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * kPairABytes);
+          const uint32_t b_addr = smem_u32(sB + stage * kPairBBytes);
+#pragma unroll
+          for (int s = 0; s < kBK / 16; ++s) {
+            const uint64_t ad = make_smem_desc_sw128(a_addr + s * a_kstep, a_lbo, 1024);
+            const uint64_t bd = make_smem_desc_sw128(b_addr + s * b_kstep, b_lbo, 1024);
+            umma_bf16_pair(d_tmem, ad, bd, idesc, (kb | s) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage], 0x3);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit_pair(&tmem_full[acc], 0x3);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (own 128 rows) ------------------------------
+    const int q = warp & 3;
+    int local = 0;
+    bool ok = true;
+    const bool c_vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const uint32_t drained = mapa_shared(smem_u32(&tmem_empty[0]), 0);
+    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      int b, mt, nt;
+      gemm_tile_coords(p, tile, tiles_per_batch, b, mt, nt);
+      const int m0 = mt * (2 * kBM) + static_cast<int>(cta) * kBM;
+      const int n0 = nt * kTileN;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) {
+        if (lane == 0) report_status(p.status, kStatusTimeoutEpilogue, kKernelIdGemmPair, tile, 0);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(drained + acc * 8);
+    }
+  }
+
+  // Teardown: neither CTA may leave (or free TMEM) while its partner can still read its
+  // shared memory, signal its barriers or write its accumulators.
+  __syncwarp();
+  if (*abort_flag && warp == 0 && lane == 0) {
+    for (int it = 0; it < 2000; ++it) __nanosleep(1000);  // ~2 ms for copies in flight to land
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+template <int EPI>
+static int launch_pair(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tB2,
+                       GemmParams& p, int max_ctas, cudaStream_t stream) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kPairSmemTotal);
+    if (e != cudaSuccess) return set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_set[dev] = true;
+  }
+  const int total = p.tiles_m * p.tiles_n * p.batch;
+  int pairs = num_sms() / 2;
+  if (max_ctas > 0) pairs = std::min(pairs, std::max(1, max_ctas / 2));
+  pairs = std::max(1, std::min(pairs, total));
+  gemm_pair_kernel<EPI><<<2 * pairs, kGemmThreads, kPairSmemTotal, stream>>>(*tA, *tB, *tB2, p);
+  count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("gemm_pair launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// Called by t5x_gemm_bf16 for problems large enough to fill CTA pairs. `p.tiles_m` must count
+// 256-row tiles; the tensor maps are the same as for the one-CTA kernel with BN = 128-column
+// (K-major) or 64-column (MN-major) B boxes.
+int launch_gemm_pair(int epilogue, const CUtensorMap* tA, const CUtensorMap* tB,
+                     const CUtensorMap* tB2, GemmParams& p, int max_ctas, cudaStream_t stream) {
+  switch (epilogue) {
+    case kEpiPlain:
+      return launch_pair<kEpiPlain>(tA, tB, tB2, p, max_ctas, stream);
+    case kEpiGatedGelu:
+      return launch_pair<kEpiGatedGelu>(tA, tB, tB2, p, max_ctas, stream);
+    case kEpiResidual:
+      return launch_pair<kEpiResidual>(tA, tB, tB2, p, max_ctas, stream);
+    default:
+      return set_error("gemm_pair: unknown epilogue %d", epilogue);
+  }
+}
+
+}  // namespace t5x

@@ -18,32 +18,9 @@
 // h0/h1 for the backward pass).
 #include <algorithm>
 
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace t5x {
-
-constexpr int kBM = 128;
-constexpr int kBK = 64;
-constexpr int kGemmThreads = 192;
-constexpr int kKernelIdGemm = 1;
-
-enum GemmEpilogue : int { kEpiPlain = 0, kEpiGatedGelu = 1, kEpiResidual = 2 };
-
-struct GemmParams {
-  int M, N, K, batch;
-  int a_mn, b_mn;
-  int out_fp32, accumulate;
-  void* C;
-  long long ldc, c_batch_stride;  // elements
-  const __nv_bfloat16* R;         // residual (bf16), same shape as C
-  long long ldr, r_batch_stride;
-  __nv_bfloat16* H0;  // gated-GELU: optional copies of the two pre-activations
-  __nv_bfloat16* H1;
-  long long ldh;
-  float alpha;
-  int tiles_m, tiles_n;
-  int* status;
-};
 
 template <int BN>
 struct GemmSmem {
@@ -54,46 +31,6 @@ struct GemmSmem {
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 align slack
 };
-
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const float* v, int n_valid,
-                                               bool vec_ok) {
-  if (vec_ok && n_valid >= 32) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __nv_bfloat162 p0 = __floats2bfloat162_rn(v[i * 8 + 0], v[i * 8 + 1]);
-      __nv_bfloat162 p1 = __floats2bfloat162_rn(v[i * 8 + 2], v[i * 8 + 3]);
-      __nv_bfloat162 p2 = __floats2bfloat162_rn(v[i * 8 + 4], v[i * 8 + 5]);
-      __nv_bfloat162 p3 = __floats2bfloat162_rn(v[i * 8 + 6], v[i * 8 + 7]);
-      uint4 u;
-      u.x = *reinterpret_cast<uint32_t*>(&p0);
-      u.y = *reinterpret_cast<uint32_t*>(&p1);
-      u.z = *reinterpret_cast<uint32_t*>(&p2);
-      u.w = *reinterpret_cast<uint32_t*>(&p3);
-      reinterpret_cast<uint4*>(dst)[i] = u;
-    }
-  } else {
-    for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = __float2bfloat16(v[i]);
-  }
-}
-
-__device__ __forceinline__ void load_row_bf16(const __nv_bfloat16* src, float* v, int n_valid,
-                                              bool vec_ok) {
-  if (vec_ok && n_valid >= 32) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint4 u = reinterpret_cast<const uint4*>(src)[i];
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __bfloat1622float2(p[j]);
-        v[i * 8 + j * 2] = f.x;
-        v[i * 8 + j * 2 + 1] = f.y;
-      }
-    }
-  } else {
-    for (int i = 0; i < 32; ++i) v[i] = (i < n_valid) ? __bfloat162float(src[i]) : 0.f;
-  }
-}
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -155,10 +92,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int b = tile / tiles_per_batch;
-        const int rem = tile - b * tiles_per_batch;
-        const int m0 = (rem / p.tiles_n) * kBM;
-        const int n0 = (rem % p.tiles_n) * kTileN;
+        int b, mt, nt;
+        gemm_tile_coords(p, tile, tiles_per_batch, b, mt, nt);
+        const int m0 = mt * kBM;
+        const int n0 = nt * kTileN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             report_status(p.status, kStatusTimeoutProducer, kKernelIdGemm, tile, kb);
@@ -267,10 +204,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      const int b = tile / tiles_per_batch;
-      const int rem = tile - b * tiles_per_batch;
-      const int m0 = (rem / p.tiles_n) * kBM;
-      const int n0 = (rem % p.tiles_n) * kTileN;
+      int b, mt, nt;
+      gemm_tile_coords(p, tile, tiles_per_batch, b, mt, nt);
+      const int m0 = mt * kBM;
+      const int n0 = nt * kTileN;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) {
         if (lane == 0) report_status(p.status, kStatusTimeoutEpilogue, kKernelIdGemm, tile, 0);
         *abort_flag = 1;
@@ -278,93 +215,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         break;
       }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-
-      if (EPI == kEpiGatedGelu) {
-        constexpr int kHalf = BN / 2;
-        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.c_batch_stride +
-                             static_cast<long long>(row) * p.ldc;
-#pragma unroll 1
-        for (int c = 0; c < kHalf / 32; ++c) {
-          uint32_t r0[32], r1[32];
-          tmem_ld32(t_row + c * 32, r0);
-          tmem_ld32(t_row + kHalf + c * 32, r1);
-          tmem_ld_wait();
-          const int col = n0 + c * 32;
-          const int n_valid = p.N - col;
-          if (row_ok && n_valid > 0) {
-            float g[32], h0[32], h1[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              h0[i] = __uint_as_float(r0[i]);
-              h1[i] = __uint_as_float(r1[i]);
-              g[i] = gelu_tanh(h0[i]) * h1[i];
-            }
-            store_row_bf16(out + col, g, n_valid, c_vec_ok);
-            if (p.H0 != nullptr) {
-              const bool hv = (p.ldh % 8 == 0);
-              store_row_bf16(p.H0 + static_cast<long long>(row) * p.ldh + col, h0, n_valid, hv);
-              store_row_bf16(p.H1 + static_cast<long long>(row) * p.ldh + col, h1, n_valid, hv);
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(t_row + c * 32, r);
-          tmem_ld_wait();
-          const int col = n0 + c * 32;
-          const int n_valid = p.N - col;
-          if (row_ok && n_valid > 0) {
-            float v[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-            if (EPI == kEpiResidual) {
-              float rr[32];
-              const bool rv = (p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
-              load_row_bf16(p.R + b * p.r_batch_stride + static_cast<long long>(row) * p.ldr + col,
-                            rr, n_valid, rv);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] += rr[i];
-            }
-            if (p.out_fp32) {
-              float* out = reinterpret_cast<float*>(p.C) + b * p.c_batch_stride +
-                           static_cast<long long>(row) * p.ldc + col;
-              const bool fv = (p.ldc % 4 == 0) && n_valid >= 32;
-              if (fv) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  float4 o = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
-                  if (p.accumulate) {
-                    float4 old = reinterpret_cast<float4*>(out)[i];
-                    o.x += old.x;
-                    o.y += old.y;
-                    o.z += old.z;
-                    o.w += old.w;
-                  }
-                  reinterpret_cast<float4*>(out)[i] = o;
-                }
-              } else {
-                for (int i = 0; i < 32 && i < n_valid; ++i)
-                  out[i] = p.accumulate ? out[i] + v[i] : v[i];
-              }
-            } else {
-              __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.c_batch_stride +
-                                   static_cast<long long>(row) * p.ldc + col;
-              if (p.accumulate) {
-                float old[32];
-                load_row_bf16(out, old, n_valid, c_vec_ok);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] += old[i];
-              }
-              store_row_bf16(out, v, n_valid, c_vec_ok);
-            }
-          }
-        }
-      }
+      gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
@@ -443,6 +295,29 @@ static const CUtensorMap* operand_map(const void* ptr, int mn_major, long long r
 // epilogue: 0 plain, 1 gated-GELU (B and B2 are wi_0 / wi_1; N is the width of each),
 //           2 residual add (R bf16).
 // Returns 0 on success; a negative value with t5x_last_error() set otherwise.
+namespace t5x {
+int launch_gemm_pair(int epilogue, const CUtensorMap* tA, const CUtensorMap* tB,
+                     const CUtensorMap* tB2, GemmParams& p, int max_ctas, cudaStream_t stream);
+
+// 0 = never use CTA pairs, 1 = when the shape suits them (default), 2 = always.
+// Read once from T5X_GEMM_PAIR; t5x_gemm_set_pair_mode overrides it.
+static int g_pair_mode = -1;
+static int gemm_pair_mode() {
+  if (g_pair_mode < 0) {
+    const char* e = getenv("T5X_GEMM_PAIR");
+    g_pair_mode = e ? atoi(e) : 1;
+    if (g_pair_mode < 0 || g_pair_mode > 2) g_pair_mode = 1;
+  }
+  return g_pair_mode;
+}
+}  // namespace t5x
+
+T5X_API int t5x_gemm_set_pair_mode(int mode) {
+  if (mode < 0 || mode > 2) return t5x::set_error("gemm pair mode must be 0, 1 or 2");
+  t5x::g_pair_mode = mode;
+  return 0;
+}
+
 T5X_API int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C, int M, int N,
                           int K, int batch, long long lda, long long ldb, long long ldc,
                           long long a_batch_stride, long long b_batch_stride,
@@ -482,26 +357,46 @@ T5X_API int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C,
   const CUtensorMap* tB = operand_map(B, b_mn_major, N, K, ldb, b_batch_stride, batch, 128);
   if (!tA || !tB) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int sms = num_sms();
+  auto waves_eff = [&](long long tiles, int units) {
+    long long waves = (tiles + units - 1) / units;
+    return static_cast<double>(tiles) / static_cast<double>(waves * units);
+  };
+  // CTA pairs (256 x 256 tiles, a third less shared-memory traffic per FLOP) when the problem
+  // has at least one full pair tile and pairs fill the machine about as well as single CTAs.
+  const int pair_tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
+  const int pair_mode = gemm_pair_mode();
 
   if (epilogue == kEpiGatedGelu) {
     if (out_fp32 || accumulate) return set_error("gated-GELU epilogue writes bf16 without accumulate");
     const CUtensorMap* tB2 = operand_map(B2, b_mn_major, N, K, ldb, b_batch_stride, batch, 128);
     if (!tB2) return -1;
     p.tiles_n = (N + 127) / 128;
+    const double e1 = waves_eff(1ll * p.tiles_m * p.tiles_n * batch, sms);
+    const double e2 = waves_eff(1ll * pair_tiles_m * p.tiles_n * batch, sms / 2);
+    if (pair_mode == 2 || (pair_mode == 1 && M >= 2 * kBM && e2 * 1.2 >= e1)) {
+      p.tiles_m = pair_tiles_m;
+      return launch_gemm_pair(kEpiGatedGelu, tA, tB, tB2, p, max_ctas, st);
+    }
     return launch_gemm<256, kEpiGatedGelu>(tA, tB, tB2, p, max_ctas, st);
   }
   // Tile width: 256 unless N is small or 128-wide tiles fill the SMs markedly better.
-  const int sms = num_sms();
-  auto waves_eff = [&](int bn) {
-    long long tiles = 1ll * p.tiles_m * ((N + bn - 1) / bn) * batch;
-    long long waves = (tiles + sms - 1) / sms;
-    return static_cast<double>(tiles) / static_cast<double>(waves * sms);
-  };
+  const double e128 = waves_eff(1ll * p.tiles_m * ((N + 127) / 128) * batch, sms);
+  const double e256 = waves_eff(1ll * p.tiles_m * ((N + 255) / 256) * batch, sms);
   int bn = 256;
-  if (N <= 128 || waves_eff(128) > waves_eff(256) * 1.15) bn = 128;
+  if (N <= 128 || e128 > e256 * 1.15) bn = 128;
+  if (epilogue == kEpiResidual && R == nullptr) return set_error("residual epilogue needs R");
+  {
+    const double e1 = bn == 256 ? e256 : e128 / 1.15;
+    const double e2 = waves_eff(1ll * pair_tiles_m * ((N + 255) / 256) * batch, sms / 2);
+    if (pair_mode == 2 || (pair_mode == 1 && M >= 2 * kBM && N >= 256 && e2 * 1.2 >= e1)) {
+      p.tiles_m = pair_tiles_m;
+      p.tiles_n = (N + 255) / 256;
+      return launch_gemm_pair(epilogue, tA, tB, tB, p, max_ctas, st);
+    }
+  }
   p.tiles_n = (N + bn - 1) / bn;
   if (epilogue == kEpiResidual) {
-    if (R == nullptr) return set_error("residual epilogue needs R");
     return bn == 256 ? launch_gemm<256, kEpiResidual>(tA, tB, tB, p, max_ctas, st)
                      : launch_gemm<128, kEpiResidual>(tA, tB, tB, p, max_ctas, st);
   }

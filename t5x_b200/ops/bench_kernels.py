@@ -1,0 +1,114 @@
+"""Micro-benchmarks of the native kernels against the library ops they replace.
+
+  python -m t5x_b200.ops.bench_kernels gemm [--pair 0|1|2]
+  python -m t5x_b200.ops.bench_kernels attention
+
+Timing: CUDA events on the launching stream after 3 warm-up calls; between timed calls a
+256 MB buffer is overwritten so that operands do not stay in L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from t5x_b200.ops import native
+
+_FLUSH = None
+
+
+def _flush_l2():
+  global _FLUSH
+  if _FLUSH is None:
+    _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+  _FLUSH.fill_(1)
+
+
+def time_ms(fn, iters: int = 10, warmup: int = 3) -> float:
+  for _ in range(warmup):
+    fn()
+  torch.cuda.synchronize()
+  total = 0.0
+  for _ in range(iters):
+    _flush_l2()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    total += e0.elapsed_time(e1)
+  return total / iters
+
+
+# (M, N, K, a transposed, b transposed): the XXL train step's dense shapes for one 16-sequence
+# microbatch (8192 encoder / 1824 decoder tokens), forward, dgrad and wgrad forms.
+GEMM_SHAPES = [
+    (8192, 4096, 4096, 0, 0), (8192, 10240, 4096, 0, 0), (8192, 4096, 10240, 0, 0),
+    (8192, 4096, 4096, 0, 1), (4096, 10240, 8192, 1, 0), (4096, 4096, 8192, 1, 0),
+    (1824, 4096, 4096, 0, 0), (1824, 10240, 4096, 0, 0), (4096, 4096, 1824, 1, 0),
+    (1824, 32128, 4096, 0, 0), (4096, 4096, 4096, 0, 0), (16384, 8192, 8192, 0, 0),
+]
+
+
+def bench_gemm(pair_modes=(0, 1)):
+  rows = []
+  for (M, N, K, ta, tb) in GEMM_SHAPES:
+    A = (torch.randn(K, M, device="cuda").bfloat16().t() if ta
+         else torch.randn(M, K, device="cuda").bfloat16())
+    B = (torch.randn(N, K, device="cuda").bfloat16().t() if tb
+         else torch.randn(K, N, device="cuda").bfloat16())
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    flops = 2.0 * M * N * K
+    row = {"M": M, "N": N, "K": K, "ta": ta, "tb": tb}
+    for mode in pair_modes:
+      native.gemm_set_pair_mode(mode)
+      ms = time_ms(lambda: native.gemm(A, B, out=out))
+      row[f"ours_pair{mode}_tflops"] = round(flops / ms / 1e9, 1)
+    native.gemm_set_pair_mode(1)
+    native.check_status()
+    ms = time_ms(lambda: torch.matmul(A, B, out=out))
+    row["cublas_tflops"] = round(flops / ms / 1e9, 1)
+    rows.append(row)
+    print(json.dumps(row), flush=True)
+  return rows
+
+
+def bench_attention():
+  from t5x_b200.ops import attention as attn
+  rows = []
+  for (b, h, lq, lk) in [(16, 64, 512, 512), (16, 64, 114, 512), (16, 64, 114, 114)]:
+    q = torch.randn(b, lq, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(b, lk, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(b, lk, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    table = torch.randn(h, 32, device="cuda")
+    fwd = lambda: attn.flash_attention(q, k, v, bias_table=table, bidirectional=True)
+    ms_f = time_ms(fwd)
+    o = fwd()
+    do = torch.randn_like(o)
+    ms_fb = time_ms(lambda: torch.autograd.grad(fwd(), (q, k, v), do))
+    flops = 4.0 * b * h * lq * lk * 64
+    row = {"b": b, "h": h, "lq": lq, "lk": lk, "fwd_ms": round(ms_f, 3),
+           "fwd_tflops": round(flops / ms_f / 1e9, 1), "fwd_bwd_ms": round(ms_fb, 3)}
+    qs, ks, vs = (t.detach().transpose(1, 2) for t in (q, k, v))
+    row["sdpa_fwd_ms_no_bias"] = round(time_ms(
+        lambda: torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, scale=1.0)), 3)
+    rows.append(row)
+    print(json.dumps(row), flush=True)
+  native.check_status()
+  return rows
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("what", choices=["gemm", "attention"])
+  ap.add_argument("--pair", type=int, nargs="*", default=[0, 1])
+  args = ap.parse_args()
+  if args.what == "gemm":
+    bench_gemm(tuple(args.pair))
+  else:
+    bench_attention()
+
+
+if __name__ == "__main__":
+  main()

@@ -235,6 +235,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None
 # ----------------------------------------------------------------------------
 # Normalisation / activations / embedding
 # ----------------------------------------------------------------------------
+def gemm_set_pair_mode(mode: int) -> None:
+  """0: one CTA per tile always; 1: CTA pairs (256 x 256 tiles) where the shape suits them
+  (default); 2: CTA pairs always."""
+  l = lib()
+  l.t5x_gemm_set_pair_mode.argtypes = [c_int]
+  _check(l.t5x_gemm_set_pair_mode(mode), "gemm_set_pair_mode")
+
+
 def rmsnorm_fwd(x: torch.Tensor, scale: torch.Tensor, eps: float):
   d = x.shape[-1]
   x2 = x.reshape(-1, d)

@@ -35,6 +35,53 @@ def test_gemm_layouts(N, shape, ta, tb):
   assert rel(C, A.float() @ B.float()) < BF16_TOL
 
 
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 256), (384, 512, 320),
+                                   (304, 200, 136), (1000, 264, 72), (2048, 1280, 1024),
+                                   (4096, 4096, 512)])
+@pytest.mark.parametrize("ta", [0, 1])
+@pytest.mark.parametrize("tb", [0, 1])
+def test_gemm_cta_pairs(N, shape, ta, tb):
+  """The cta_group::2 kernel (forced on) against fp32 matmul, all operand layouts."""
+  M, Nn, K = shape
+  torch.manual_seed(0)
+  A = torch.randn(K, M, device="cuda").bfloat16().t() if ta else torch.randn(M, K, device="cuda").bfloat16()
+  B = torch.randn(Nn, K, device="cuda").bfloat16().t() if tb else torch.randn(K, Nn, device="cuda").bfloat16()
+  N.gemm_set_pair_mode(2)
+  try:
+    C = N.gemm(A, B)
+    N.check_status()
+  finally:
+    N.gemm_set_pair_mode(1)
+  assert rel(C, A.float() @ B.float()) < BF16_TOL
+
+
+def test_gemm_cta_pairs_epilogues(N):
+  torch.manual_seed(1)
+  M, Nn, K = 768, 640, 256
+  A = torch.randn(M, K, device="cuda").bfloat16()
+  B = (torch.randn(K, Nn, device="cuda") * 0.1).bfloat16()
+  R = torch.randn(M, Nn, device="cuda").bfloat16()
+  ref = A.float() @ B.float()
+  N.gemm_set_pair_mode(2)
+  try:
+    assert rel(N.gemm(A, B, residual=R), ref + R.float()) < BF16_TOL
+    Cf = torch.ones(M, Nn, device="cuda")
+    N.gemm(A, B, out=Cf, accumulate=True)
+    assert rel(Cf, ref + 1) < 1e-5
+    W = (torch.randn(K, 2 * Nn, device="cuda") * 0.1).bfloat16()
+    H = torch.empty(M, 2 * Nn, device="cuda", dtype=torch.bfloat16)
+    G = N.gemm(A, W[:, :Nn], b2=W[:, Nn:], save_h=H)
+    h = A.float() @ W.float()
+    assert rel(G, torch.nn.functional.gelu(h[:, :Nn], approximate="tanh") * h[:, Nn:]) < BF16_TOL
+    assert rel(H, h) < BF16_TOL
+    Ab = torch.randn(3, 520, 128, device="cuda").bfloat16()
+    Bb = torch.randn(3, 128, 264, device="cuda").bfloat16()
+    assert rel(N.gemm(Ab, Bb), Ab.float() @ Bb.float()) < BF16_TOL
+    N.check_status()
+  finally:
+    N.gemm_set_pair_mode(1)
+
+
 def test_gemm_epilogues(N):
   torch.manual_seed(1)
   M, Nn, K = 512, 384, 256
