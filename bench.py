@@ -129,6 +129,8 @@ def main() -> None:
   ap.add_argument("--targets-length", type=int, default=114)
   ap.add_argument("--microbatches", type=int, default=0)
   ap.add_argument("--skip-e2e", action="store_true")
+  ap.add_argument("--mode", default="train", choices=["train", "decode"],
+                  help="train: T5.1.1-XXL train step (default); decode: T5.1.1-XL beam decode")
   ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
                   help="dp: data parallel with the optimizer sharded over replicas (gradient "
                        "reduction and weight broadcast fused into the Adafactor kernels over "
@@ -137,6 +139,10 @@ def main() -> None:
 
   if args.impl == "reference":
     reference_arm(args)
+    return
+  if args.mode == "decode":
+    import bench_decode
+    bench_decode.run(args, ClockSampler)
     return
 
   import numpy as np

@@ -262,6 +262,140 @@ __global__ void __launch_bounds__(kAfThreads)
   }
 }
 
+// Tiled forms of the two element-wise factored passes: a CTA covers kAfRowsPerCta rows x 1024
+// columns, a thread 4 adjacent columns of each row, so the row / column factors are indexed
+// without a division per element and loads are 16 bytes wide when C % 4 == 0.
+constexpr int kAfRowsPerCta = 32;
+constexpr int kAfColsPerCta = kAfThreads * 4;
+
+template <bool VEC>
+__global__ void __launch_bounds__(kAfThreads)
+    af_usq_tiled_kernel(const float* __restrict__ g, const float* __restrict__ rf,
+                        const float* __restrict__ cf, AdafactorScalars* __restrict__ scal, int R,
+                        int C) {
+  __shared__ float red[kAfThreads / 32];
+  const int b = blockIdx.z;
+  g += static_cast<long long>(b) * R * C;
+  rf += static_cast<long long>(b) * R;
+  cf += static_cast<long long>(b) * C;
+  const int r0 = blockIdx.y * kAfRowsPerCta;
+  const int col = blockIdx.x * kAfColsPerCta + threadIdx.x * 4;
+  const int rows = min(kAfRowsPerCta, R - r0);
+  float acc = 0.f;
+  if (col < C) {
+    float c[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) c[k] = (col + k < C) ? cf[col + k] : 0.f;
+    for (int rr = 0; rr < rows; ++rr) {
+      const float* gp = g + static_cast<long long>(r0 + rr) * C + col;
+      const float rv = rf[r0 + rr];
+      float v[4];
+      if (VEC) {
+        const float4 t = *reinterpret_cast<const float4*>(gp);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = (col + k < C) ? gp[k] : 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float u = v[k] * rv * c[k];
+        acc += u * u;
+      }
+    }
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAfThreads / 32; ++w) t += red[w];
+    atomicAdd(&scal[b].usq, t);
+  }
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kAfThreads)
+    af_apply_tiled_kernel(float* __restrict__ p, const float* __restrict__ g,
+                          const float* __restrict__ rf, const float* __restrict__ cf,
+                          float* __restrict__ m, __nv_bfloat16* __restrict__ p_bf16,
+                          long long ld_bf16, long long bf16_batch_stride,
+                          const AdafactorScalars* __restrict__ scal, int R, int C, float n_global,
+                          AfHyper h) {
+  const int b = blockIdx.z;
+  const long long base = static_cast<long long>(b) * R * C;
+  const int r0 = blockIdx.y * kAfRowsPerCta;
+  const int col = blockIdx.x * kAfColsPerCta + threadIdx.x * 4;
+  if (col >= C) return;
+  const float scale = af_update_scale(scal[b], n_global, h);
+  rf += static_cast<long long>(b) * R;
+  cf += static_cast<long long>(b) * C;
+  float c[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) c[k] = (col + k < C) ? cf[col + k] : 0.f;
+  const int nk = min(4, C - col);
+  const int rows = min(kAfRowsPerCta, R - r0);
+  const bool bf_vec = VEC && p_bf16 != nullptr && (ld_bf16 % 4 == 0) &&
+                      (bf16_batch_stride % 4 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(p_bf16) & 7) == 0);
+  for (int rr = 0; rr < rows; ++rr) {
+    const long long off = base + static_cast<long long>(r0 + rr) * C + col;
+    const float rv = rf[r0 + rr] * scale;
+    float gv[4], ov[4], nv[4];
+    if (VEC) {
+      const float4 t = *reinterpret_cast<const float4*>(g + off);
+      const float4 o = *reinterpret_cast<const float4*>(p + off);
+      gv[0] = t.x; gv[1] = t.y; gv[2] = t.z; gv[3] = t.w;
+      ov[0] = o.x; ov[1] = o.y; ov[2] = o.z; ov[3] = o.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        gv[k] = k < nk ? g[off + k] : 0.f;
+        ov[k] = k < nk ? p[off + k] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float sub = gv[k] * rv * c[k];
+      if (h.use_momentum && k < nk) {
+        const float old_m = m[off + k];
+        float nm = h.beta1 * old_m + (1.f - h.beta1) * sub;
+        sub = nm;
+        if (h.skip_nan && isnan(nm)) nm = old_m;
+        m[off + k] = nm;
+      }
+      float np = (h.use_wd ? (1.f - h.weight_decay) * ov[k] : ov[k]) - sub;
+      if (h.skip_nan && isnan(np)) np = ov[k];
+      nv[k] = np;
+    }
+    if (VEC) {
+      *reinterpret_cast<float4*>(p + off) = make_float4(nv[0], nv[1], nv[2], nv[3]);
+    } else {
+      for (int k = 0; k < nk; ++k) p[off + k] = nv[k];
+    }
+    if (p_bf16 != nullptr) {
+      __nv_bfloat16* o = p_bf16 + b * bf16_batch_stride +
+                         static_cast<long long>(r0 + rr) * ld_bf16 + col;
+      if (bf_vec) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(nv[0], nv[1]);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(nv[2], nv[3]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(o) = packed;
+      } else {
+        for (int k = 0; k < nk; ++k) o[k] = __float2bfloat16(nv[k]);
+      }
+    }
+  }
+}
+
+static inline dim3 af_tiled_grid(int batch, int R, int C) {
+  return dim3((C + kAfColsPerCta - 1) / kAfColsPerCta, (R + kAfRowsPerCta - 1) / kAfRowsPerCta,
+              batch);
+}
+
 static inline int af_grid(long long n) {
   long long blocks = (n + kAfThreads * 4 - 1) / (kAfThreads * 4);
   long long cap = static_cast<long long>(num_sms()) * 8;
@@ -350,9 +484,13 @@ T5X_API int t5x_adafactor_usq(const void* g, const void* v_rvec, const void* v_c
       static_cast<const float*>(v_rvec), static_cast<const float*>(v_cvec), a.rf, a.cf, a.scal, R,
       C, static_cast<float>(row_is_normalized ? global_R : global_C), row_is_normalized);
   if (use_clip) {
-    dim3 egrid(af_grid(static_cast<long long>(R) * C), batch);
-    af_usq_kernel<<<egrid, kAfThreads, 0, st>>>(static_cast<const float*>(g), a.rf, a.cf, a.scal,
-                                                R, C);
+    const dim3 tgrid = af_tiled_grid(batch, R, C);
+    if (C % 4 == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0)
+      af_usq_tiled_kernel<true><<<tgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g), a.rf,
+                                                              a.cf, a.scal, R, C);
+    else
+      af_usq_tiled_kernel<false><<<tgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g), a.rf,
+                                                               a.cf, a.scal, R, C);
   }
   count_launches(use_clip ? 2 : 1);
   return af_check("adafactor_usq");
@@ -368,11 +506,19 @@ T5X_API int t5x_adafactor_apply(void* p, const void* g, void* m, void* p_bf16, l
   if (batch <= 0) return 0;
   AfScratch a = af_split(scratch, batch, R, C);
   AfHyper h = af_hyper(lr, eps2, clip_threshold, weight_decay, beta1, max_param_scale, flags);
-  dim3 egrid(af_grid(static_cast<long long>(R) * C), batch);
-  af_apply_kernel<true><<<egrid, kAfThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<float*>(p), static_cast<const float*>(g), a.rf, a.cf, nullptr,
-      static_cast<float*>(m), static_cast<__nv_bfloat16*>(p_bf16), ld_bf16, bf16_batch_stride,
-      a.scal, R, C, static_cast<float>(n_global), h);
+  const dim3 tgrid = af_tiled_grid(batch, R, C);
+  const bool vec = C % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+  if (vec)
+    af_apply_tiled_kernel<true><<<tgrid, kAfThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<float*>(p), static_cast<const float*>(g), a.rf, a.cf, static_cast<float*>(m),
+        static_cast<__nv_bfloat16*>(p_bf16), ld_bf16, bf16_batch_stride, a.scal, R, C,
+        static_cast<float>(n_global), h);
+  else
+    af_apply_tiled_kernel<false><<<tgrid, kAfThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<float*>(p), static_cast<const float*>(g), a.rf, a.cf, static_cast<float*>(m),
+        static_cast<__nv_bfloat16*>(p_bf16), ld_bf16, bf16_batch_stride, a.scal, R, C,
+        static_cast<float>(n_global), h);
   count_launches(1);
   return af_check("adafactor_apply");
 }

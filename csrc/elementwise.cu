@@ -388,3 +388,51 @@ T5X_API int t5x_cast_f32_bf16(const void* src, void* dst, long long rows, int co
   CHECK_LAUNCH("cast");
   return 0;
 }
+
+
+// dst[i] = bf16(src[i] (+ residual[i])): finishes a split-K GEMM whose partial products were
+// added into an fp32 workspace.
+namespace t5x {
+__global__ void __launch_bounds__(256)
+    f32_to_bf16_residual_kernel(const float* __restrict__ src, const __nv_bfloat16* __restrict__ res,
+                                __nv_bfloat16* __restrict__ dst, long long n4) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += stride) {
+    float4 a = reinterpret_cast<const float4*>(src)[i];
+    if (res != nullptr) {
+      const uint2 r = reinterpret_cast<const uint2*>(res)[i];
+      const float2 r0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+      const float2 r1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+      a.x += r0.x;
+      a.y += r0.y;
+      a.z += r1.x;
+      a.w += r1.y;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(dst)[i] = o;
+  }
+}
+}  // namespace t5x
+
+// n must be a multiple of 4; all pointers 16-byte (src) / 8-byte (res, dst) aligned.
+T5X_API int t5x_f32_to_bf16_residual(const void* src, const void* residual, void* dst,
+                                     long long n, void* stream) {
+  if (n <= 0) return 0;
+  if (n % 4) return t5x::set_error("f32_to_bf16_residual: n must be a multiple of 4");
+  const long long n4 = n / 4;
+  long long blocks = (n4 + 255) / 256;
+  const long long cap = static_cast<long long>(t5x::num_sms()) * 8;
+  if (blocks > cap) blocks = cap;
+  t5x::f32_to_bf16_residual_kernel<<<static_cast<int>(blocks), 256, 0,
+                                     static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(src), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<__nv_bfloat16*>(dst), n4);
+  t5x::count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return t5x::set_error("f32_to_bf16_residual: %s", cudaGetErrorString(e));
+  return 0;
+}

@@ -151,6 +151,10 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               float4 o = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+              if (p.accumulate == 2) {  // several CTAs (split K) add into the same tile
+                atomicAdd(reinterpret_cast<float4*>(out) + i, o);
+                continue;
+              }
               if (p.accumulate) {
                 float4 old = reinterpret_cast<float4*>(out)[i];
                 o.x += old.x;
@@ -161,8 +165,12 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
               reinterpret_cast<float4*>(out)[i] = o;
             }
           } else {
-            for (int i = 0; i < 32 && i < n_valid; ++i)
-              out[i] = p.accumulate ? out[i] + v[i] : v[i];
+            for (int i = 0; i < 32 && i < n_valid; ++i) {
+              if (p.accumulate == 2)
+                atomicAdd(out + i, v[i]);
+              else
+                out[i] = p.accumulate ? out[i] + v[i] : v[i];
+            }
           }
         } else {
           __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.c_batch_stride +

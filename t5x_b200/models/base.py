@@ -291,6 +291,13 @@ class EncoderDecoderModel(BaseTransformerModel):
       decoder_prompt_inputs = decoder_input_tokens * (decoder_input_tokens != eos)
     else:
       decoder_prompt_inputs = torch.zeros_like(decoder_input_tokens)
+    fast = self._graph_decoder(params, decoder_input_tokens, num_decodes, eos, decoder_params,
+                               rng, prompt_with_targets)
+    if fast is not None:
+      decodes, scores = fast.decode(encoder_input_tokens)
+      if return_all_decodes:
+        return decodes, {"scores": scores}
+      return decodes[:, -1, :], {"scores": scores[:, -1]}
     with torch.no_grad():
       encoded_inputs = call_module(self.module, params, "encode", encoder_input_tokens,
                                    enable_dropout=False)
@@ -321,6 +328,31 @@ class EncoderDecoderModel(BaseTransformerModel):
     if return_all_decodes:
       return decodes, {"scores": scores}
     return decodes[:, -1, :], {"scores": scores[:, -1]}
+
+  def _graph_decoder(self, params, decoder_input_tokens, num_decodes, eos, decoder_params, rng,
+                     prompt_with_targets):
+    """The CUDA-graph beam decoder when it covers this call (bf16 T5 network on a GPU, beam
+    search without a prompt and with default search options), else None."""
+    import os
+    if prompt_with_targets or rng is not None or os.environ.get("T5X_B200_GRAPH_DECODE") == "0":
+      return None
+    if params is not None and not _owns(self.module, params):
+      return None
+    extra = set(decoder_params or {}) - {"eos_id", "alpha"}
+    if extra:
+      return None
+    from t5x_b200 import decoding_fast
+    if not decoding_fast.supported(self.module, decoder_input_tokens, self._decode_fn):
+      return None
+    dp = decoder_params or {}
+    key = (decoder_input_tokens.shape[0], num_decodes, decoder_input_tokens.shape[1],
+           dp.get("eos_id", eos), dp.get("alpha", 0.6))
+    cache = self.__dict__.setdefault("_graph_decoders", {})
+    if key not in cache:
+      cache.clear()  # one set of static buffers at a time
+      cache[key] = decoding_fast.GraphBeamDecoder(self.module, key[0], key[1], key[2], key[3],
+                                                  alpha=key[4])
+    return cache[key]
 
   def score_batch(self, params, batch, return_intermediates: bool = False):
     """Sequence log-likelihoods (t5x/models.py:760-812)."""

@@ -235,6 +235,38 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None
 # ----------------------------------------------------------------------------
 # Normalisation / activations / embedding
 # ----------------------------------------------------------------------------
+def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, *,
+                residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+  """out[M, N] (bf16) = a[M, K] @ b[K, N] (+ residual) with K cut into `splits` slices whose
+  partial products are added atomically into an fp32 workspace. For skinny problems (decode
+  steps: M of a few hundred rows) this puts `splits` times more CTAs on the weight stream
+  than one CTA per output tile would."""
+  M, K = a.shape
+  N = b.shape[1]
+  assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.stride(1) == 1
+  assert b.stride(1) == 1, "b must be row-major [K, N]"
+  if splits <= 1 or K % splits or (K // splits) % 64 or N % 4:
+    return gemm(a, b, out=out, residual=residual)
+  ks = K // splits
+  ws = workspace if workspace is not None else torch.empty(M, N, dtype=torch.float32,
+                                                           device=a.device)
+  ws = ws.view(-1)[:M * N].view(M, N)
+  ws.zero_()
+  rc = lib().t5x_gemm_bf16(
+      a.data_ptr(), b.data_ptr(), 0, ws.data_ptr(), M, N, ks, splits, a.stride(0), b.stride(0), N,
+      ks, ks * b.stride(0), 0, 0, 1, 1, 2, EPI_PLAIN, 0, 0, 0, 0, 0, 0, 1.0, 0, stream_ptr())
+  _check(rc, "gemm_splitk")
+  if out is None:
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+  assert out.is_contiguous() and (residual is None or residual.is_contiguous())
+  l = lib()
+  l.t5x_f32_to_bf16_residual.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_void_p]
+  _check(l.t5x_f32_to_bf16_residual(ws.data_ptr(), ptr(residual), out.data_ptr(), M * N,
+                                    stream_ptr()), "f32_to_bf16_residual")
+  return out
+
+
 def gemm_set_pair_mode(mode: int) -> None:
   """0: one CTA per tile always; 1: CTA pairs (256 x 256 tiles) where the shape suits them
   (default); 2: CTA pairs always."""
