@@ -88,6 +88,44 @@ def linear(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tenso
   return y if residual is None else y + residual
 
 
+class _BatchedLinearFn(torch.autograd.Function):
+  """y[e] = x[e] @ w[e] for stacked expert kernels (one batched GEMM each way)."""
+
+  @staticmethod
+  def forward(ctx, x, weight):
+    w = compute_weight(weight, torch.bfloat16)
+    ctx.save_for_backward(x, weight)
+    return native.gemm(x.contiguous(), w)
+
+  @staticmethod
+  def backward(ctx, dy):
+    x, weight = ctx.saved_tensors
+    w = compute_weight(weight, torch.bfloat16)
+    dy = dy.contiguous()
+    dx = dw = None
+    if ctx.needs_input_grad[0]:
+      dx = native.gemm(dy, w.transpose(1, 2))
+    if ctx.needs_input_grad[1]:
+      mg = getattr(weight, "main_grad", None)
+      xt = x.contiguous().transpose(1, 2)
+      if mg is not None:
+        first = not getattr(weight, "grad_ready", False)
+        native.gemm(xt, dy, out=mg, accumulate=not first)
+        weight.grad_ready = True
+      else:
+        dw = native.gemm(xt, dy, out_dtype=torch.float32).to(weight.dtype)
+    return dx, dw
+
+
+def batched_linear(x: torch.Tensor, weight: torch.Tensor,
+                   dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+  """x [E, N, in] @ weight [E, in, out] -> [E, N, out]."""
+  if _native_ok(x):
+    return _BatchedLinearFn.apply(x, weight)
+  dt = dtype or x.dtype
+  return torch.bmm(x.to(dt), compute_weight(weight, dt))
+
+
 class _RmsNormFn(torch.autograd.Function):
 
   @staticmethod
