@@ -309,9 +309,16 @@ class MoeLayer(nn.Module):
     route, metrics = self.router(tokens, cap, enable_dropout)
     _COLLECTED.append(metrics)
     flat_slot = _flat_slots(route["expert_index"], route["slot"], cap)
-    x = _Dispatch.apply(tokens, flat_slot, self.num_experts, cap)
-    y = self.expert(x)
-    out = _Combine.apply(y, flat_slot, route["gate"].to(self.dtype), self.num_experts, cap)
+    from t5x_b200.ops import moe as moe_ops
+    if moe_ops.enabled(tokens):
+      # NVLink path: rows are pushed into / pulled from the owners' buffers by the kernels
+      x = moe_ops.FusedDispatch.apply(tokens, flat_slot, self.num_experts, cap)
+      y = self.expert(x)
+      out = moe_ops.FusedCombine.apply(y, flat_slot, route["gate"], self.num_experts, cap)
+    else:
+      x = _Dispatch.apply(tokens, flat_slot, self.num_experts, cap)
+      y = self.expert(x)
+      out = _Combine.apply(y, flat_slot, route["gate"].to(self.dtype), self.num_experts, cap)
     out = out.view(b, l, d).to(inputs.dtype)
     out = ref.dropout(out, self.dropout_rate, enable_dropout, broadcast_dims=(-2,)) \
         if self.dropout_rate > 0 else out

@@ -626,7 +626,9 @@ def _do_import(stmt: str, imports: Dict[str, Any], skip_unknown: bool):
       imports.setdefault(mod.split(".")[0], _import_module(mod.split(".")[0]))
   except ImportError as e:
     target = stmt.split()[1]
-    if skip_unknown or target.startswith(OPTIONAL_IMPORT_PREFIXES):
+    optional = any(target == p.rstrip(".") or target.startswith(p.rstrip(".") + ".")
+                   for p in OPTIONAL_IMPORT_PREFIXES)
+    if skip_unknown or optional:
       logging.info("gin: ignoring unavailable import '%s' (%s)", stmt, e)
       return
     raise

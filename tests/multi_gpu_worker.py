@@ -108,7 +108,47 @@ def case_train(out):
   trainer.close()
 
 
-CASES = {"collectives": case_collectives, "train": case_train}
+def case_moe(out):
+  """Loss and gradients of an expert-parallel MoE model; the parent compares the NVLink-fused
+  dispatch/combine with the all_to_all path (T5X_B200_MOE_FUSED=0)."""
+  from t5x_b200 import adafactor, trainer as trainer_lib
+  from t5x_b200.contrib.moe import adafactor_utils, models as moe_models, network as moe_network
+  from t5x_b200.data import vocabularies
+  from t5x_b200.models import base
+  from t5x_b200.ops import native
+  local = int(os.environ.get("LOCAL_RANK", "0"))
+  torch.cuda.set_device(local)
+  pstate.init_distributed("nccl")
+  st = pstate.setup_mesh(model_size=1, expert_size=int(os.environ["WORLD_SIZE"]))
+  cfg = moe_network.MoeT5Config(vocab_size=512, dtype="bfloat16", emb_dim=128, num_heads=2,
+                                head_dim=64, mlp_dim=256, num_encoder_layers=2,
+                                num_decoder_layers=2, dropout_rate=0.0,
+                                mlp_activations=("gelu", "linear"), num_experts=4,
+                                num_selected_experts=2, train_capacity_factor=2.0)
+  torch.manual_seed(11)
+  module = moe_network.Transformer(cfg, device=st.device)
+  vocab = vocabularies.PassThroughVocabulary(512)
+  opt = adafactor.Adafactor(logical_factor_rules=adafactor_utils.logical_factor_rules())
+  model = moe_models.MoeEncoderDecoderModel(module, vocab, vocab, opt, aux_loss_factor=0.01,
+                                            router_z_loss_factor=0.001)
+  trainer_lib.attach_compute_buffers(base.module_param_tree(module), bf16_copy=True,
+                                     main_grad=True)
+  batch = {k: v.to(st.device) for k, v in _batches(st.rank, st.world_size, 1)[0].items()}
+  loss, _ = model.loss_fn(None, batch, None)
+  loss.backward()
+  native.check_status()
+  torch.cuda.synchronize()
+  wi = module.encoder.layers_1.mlp.expert.wi_0.kernel
+  wo = module.decoder.layers_1.mlp.expert.wo.kernel
+  router = module.encoder.layers_1.mlp.router.router_weights.w.kernel
+  dense = module.encoder.layers_0.mlp.wi_0.kernel
+  g = lambda p: (p.main_grad if getattr(p, "grad_ready", False) else p.grad).float()
+  json.dump({"loss": float(loss), "wi": float(g(wi).abs().sum()), "wo": float(g(wo).abs().sum()),
+             "router": float(g(router).abs().sum()), "dense": float(g(dense).abs().sum()),
+             "wi_first": g(wi).reshape(-1)[:6].tolist()}, out)
+
+
+CASES = {"collectives": case_collectives, "train": case_train, "moe": case_moe}
 
 if __name__ == "__main__":
   case, out_dir = sys.argv[1], sys.argv[2]

@@ -71,3 +71,15 @@ def test_barrier_gives_up_when_a_peer_never_arrives():
   # the context is still usable and the status is cleared
   assert float(torch.ones(4, device="cuda").sum()) == 4.0
   native.check_status()
+
+
+def test_moe_fused_exchange_matches_all_to_all(tmp_path):
+  _need_two()
+  fused = _run_ranks("moe", tmp_path / "f")
+  plain = _run_ranks("moe", tmp_path / "p", env={"T5X_B200_MOE_FUSED": "0"})
+  for a, b in zip(fused, plain):
+    assert a["loss"] == pytest.approx(b["loss"], rel=2e-3)
+    for key in ("wi", "wo", "router", "dense"):
+      assert a[key] == pytest.approx(b[key], rel=2e-2), key
+    for x, y in zip(a["wi_first"], b["wi_first"]):
+      assert x == pytest.approx(y, rel=5e-2, abs=1e-3)

@@ -93,3 +93,24 @@ def test_main_dispatch_dry_run_and_precompile(tmp_path):
       "--gin.TASK_FEATURE_LENGTHS={'inputs': 8, 'targets': 8}",
       "--gin.network.T5Config.vocab_size=32128"])
   assert "gemm fwd" in open(os.path.join(model_dir, "launch_plan.txt")).read()
+
+
+def test_moe_pretrain_from_gin(tmp_path):
+  """Switch-style model through the MoE run config: MoE partitioner, MoE trainer, expert
+  metrics in the training summary."""
+  model_dir = str(tmp_path / "moe")
+  tiny = ["--gin.moe_network.MoeT5Config.emb_dim=8", "--gin.moe_network.MoeT5Config.mlp_dim=16",
+          "--gin.moe_network.MoeT5Config.num_heads=2", "--gin.moe_network.MoeT5Config.head_dim=4",
+          "--gin.moe_network.MoeT5Config.num_encoder_layers=2",
+          "--gin.moe_network.MoeT5Config.num_decoder_layers=2", "--gin.NUM_EXPERTS=4",
+          "--gin.NUM_EXPERT_PARTITIONS=1"]
+  train_lib.main(["--gin_file=t5x/contrib/moe/configs/models/switch_base.gin",
+                  "--gin_file=t5x/contrib/moe/configs/runs/pretrain.gin"] + VOCAB + tiny + [
+      f'--gin.MODEL_DIR="{model_dir}"', f'--gin.MIXTURE_OR_TASK_NAME="{TASK}"',
+      "--gin.USE_CACHED_TASKS=False", "--gin.TRAIN_STEPS=2", "--gin.BATCH_SIZE=8",
+      "--gin.TASK_FEATURE_LENGTHS={'inputs': 8, 'targets': 8}",
+      "--gin.train_script.train.eval_period=2", "--gin.train_script.train.eval_steps=1",
+      "--gin.utils.SaveCheckpointConfig.period=2", "--gin.train_script.train.random_seed=0"])
+  assert checkpoints.all_steps(model_dir) == [0, 2]
+  info = open(os.path.join(model_dir, "model-info.txt")).read()
+  assert "mlp/expert/wi_0/kernel" in info and "router_weights" in info
