@@ -147,7 +147,17 @@ def _zeros_like_tree(params):
   return {k: torch.zeros_like(v, dtype=torch.float32) for k, v in params.items()}
 
 
+# Learning rate handed in by the caller of `Optimizer.apply_gradient(learning_rate=...)` for the
+# duration of one OptaxWrapper update; transformations built with `learning_rate=None` use it.
+_STEP_LEARNING_RATE = [None]
+
+
 def _lr(learning_rate, count):
+  if learning_rate is None:
+    if _STEP_LEARNING_RATE[0] is None:
+      raise ValueError("This optimizer was built with learning_rate=None: pass "
+                       "`learning_rate=` to apply_gradient (the trainer does).")
+    return float(_STEP_LEARNING_RATE[0])
   return learning_rate(count) if callable(learning_rate) else learning_rate
 
 
@@ -482,13 +492,23 @@ class OptaxWrapper(OptimizerDef):
       return node
     return conv(state)
 
+  def update_hyper_params(self, **hyper_param_overrides):
+    """The wrapped transformation owns its hyper-parameters (a learning rate given at
+    construction, possibly a schedule, wins); only a `learning_rate` override is kept, for
+    transformations that were built with `learning_rate=None` (t5x/optimizers.py:493-500)."""
+    return {"learning_rate": hyper_param_overrides.get("learning_rate")}
+
   def apply_gradient(self, hyper_params, params, state, grads):
     flat_p = tree_utils.flatten_dict(params)
     flat_g = {k: v.float() for k, v in tree_utils.flatten_dict(grads).items()}
     opt_state = self._flat(state.param_states, flat_p.keys())
+    _STEP_LEARNING_RATE[0] = (hyper_params or {}).get("learning_rate")
     with torch.no_grad():
-      updates, new_opt_state = self.optax_optimizer.update(
-          flat_g, opt_state, {k: v.detach() for k, v in flat_p.items()})
+      try:
+        updates, new_opt_state = self.optax_optimizer.update(
+            flat_g, opt_state, {k: v.detach() for k, v in flat_p.items()})
+      finally:
+        _STEP_LEARNING_RATE[0] = None
       for k, p in flat_p.items():
         p.add_(updates[k].to(p.dtype))
         bf = getattr(p, "bf16", None)
