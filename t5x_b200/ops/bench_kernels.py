@@ -99,13 +99,48 @@ def bench_attention():
   return rows
 
 
+def gemm_one(m: int, n: int, k: int, iters: int, pair: int):
+  """A few launches of one GEMM shape (the small case for profiler captures)."""
+  a = torch.randn(m, k, device="cuda").bfloat16()
+  b = torch.randn(k, n, device="cuda").bfloat16()
+  out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+  native.gemm_set_pair_mode(pair)
+  ms = time_ms(lambda: native.gemm(a, b, out=out), iters=iters, warmup=2)
+  native.check_status()
+  print(json.dumps({"M": m, "N": n, "K": k, "pair": pair, "ms": round(ms, 4),
+                    "tflops": round(2.0 * m * n * k / ms / 1e9, 1)}))
+
+
+def attention_one(b: int, h: int, lq: int, lk: int, iters: int):
+  """A few forward + backward launches of one attention shape."""
+  from t5x_b200.ops import attention as attn
+  q = torch.randn(b, lq, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+  k = torch.randn(b, lk, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+  v = torch.randn(b, lk, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+  table = torch.randn(h, 32, device="cuda")
+  do = torch.randn(b, lq, h, 64, device="cuda", dtype=torch.bfloat16)
+  fn = lambda: torch.autograd.grad(
+      attn.flash_attention(q, k, v, bias_table=table, bidirectional=True), (q, k, v), do)
+  ms = time_ms(fn, iters=iters, warmup=2)
+  native.check_status()
+  print(json.dumps({"b": b, "h": h, "lq": lq, "lk": lk, "fwd_bwd_ms": round(ms, 4)}))
+
+
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("what", choices=["gemm", "attention"])
+  ap.add_argument("what", choices=["gemm", "attention", "gemm-one", "attention-one"])
   ap.add_argument("--pair", type=int, nargs="*", default=[0, 1])
+  ap.add_argument("--shape", type=int, nargs="*", default=[])
+  ap.add_argument("--iters", type=int, default=3)
   args = ap.parse_args()
   if args.what == "gemm":
     bench_gemm(tuple(args.pair))
+  elif args.what == "gemm-one":
+    m, n, k = args.shape or [8192, 8192, 4096]
+    gemm_one(m, n, k, args.iters, args.pair[0] if args.pair else 1)
+  elif args.what == "attention-one":
+    b, h, lq, lk = args.shape or [16, 64, 512, 512]
+    attention_one(b, h, lq, lk, args.iters)
   else:
     bench_attention()
 
