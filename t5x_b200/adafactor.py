@@ -529,6 +529,8 @@ class Adafactor(OptimizerDef):
         zinfo = getattr(p, "zero", None)
         if zinfo is not None and not zinfo.mine:
           continue  # its owner updates it and pushes the new bf16 weights here
+        if zinfo is not None and k in getattr(zinfo.ctx, "done_this_step", ()):
+          continue  # already updated while the backward pass was running
         self.apply_param_gradient(step, hyper_params, p, flat_s[k], flat_g[k], k)
     finally:
       self.hyper_params = saved_hp

@@ -100,9 +100,73 @@ class ZeroContext:
     logging.info("optimizer sharding: rank %d/%d owns %.1f M of %.1f M parameters", self.rank,
                  self.world, owned / 1e6, sum(sizes.values()) / 1e6)
 
+  # -- overlap with backward ----------------------------------------------------------------
+  # During the last microbatch of a step, the parameters of a transformer layer are final as
+  # soon as that layer's backward has been issued. A backward hook on every `layers_N` module
+  # then lets a side stream wait for the main stream (CUDA event), meet the other ranks at a
+  # barrier, and run the owner's fused reduce + update + weight push for that layer while the
+  # main stream continues with the backward pass of the layers below.
+  def attach_overlap(self, module: torch.nn.Module, optimizer_def, state_of) -> None:
+    """`state_of(name)` returns the optimizer slots of parameter `name` ('/'-joined)."""
+    import re
+    self._opt_def = optimizer_def
+    self._state_of = state_of
+    self._side = torch.cuda.Stream(device=self.grads.tensor.device)
+    self._overlap = None          # (step, hyper_params) while the last microbatch runs
+    self.done_this_step = set()
+    self._buckets = {}
+    by_id = {id(p): k for k, p in self.params.items()}
+    for mod_name, mod in module.named_modules():
+      if not re.fullmatch(r"(.*\.)?layers_\d+", mod_name):
+        continue
+      names = [by_id[id(p)] for p in mod.parameters(recurse=True) if id(p) in by_id]
+      if not names:
+        continue
+      self._buckets[mod_name] = names
+      mod.register_full_backward_hook(
+          lambda m, gin, gout, bucket=mod_name: self._bucket_ready(bucket))
+
+  def begin_overlap(self, step: int, hyper_params) -> None:
+    if getattr(self, "_side", None) is not None:
+      self._overlap = (int(step), hyper_params)
+      self.done_this_step = set()
+
+  def end_overlap(self) -> None:
+    if getattr(self, "_side", None) is not None:
+      self._overlap = None
+      torch.cuda.current_stream().wait_stream(self._side)
+
+  def _bucket_ready(self, bucket: str) -> None:
+    if self._overlap is None:
+      return
+    step, hp = self._overlap
+    # only parameters whose whole gradient went through the native accumulate path are final
+    names = [k for k in self._buckets[bucket]
+             if getattr(self.params[k], "grad_ready", False) and self.params[k].grad is None]
+    if not names:
+      return
+    main = torch.cuda.current_stream()
+    ev = torch.cuda.Event()
+    ev.record(main)
+    with torch.cuda.stream(self._side):
+      self._side.wait_event(ev)
+      self.grads.barrier(channel=2)   # every rank has issued this layer's backward
+      saved = self._opt_def.hyper_params
+      self._opt_def.hyper_params = hp
+      try:
+        with torch.no_grad():
+          for k in names:
+            p = self.params[k]
+            if p.zero.mine:
+              self._opt_def.apply_param_gradient(step, hp, p, self._state_of(k), p.main_grad, k)
+      finally:
+        self._opt_def.hyper_params = saved
+    self.done_this_step.update(names)
+
   # -- step protocol -------------------------------------------------------------------------
   def gradients_complete(self) -> None:
     """Barrier after the last backward pass: every rank's gradient copy is final."""
+    self.end_overlap()
     self.grads.barrier(channel=0)
 
   def update_complete(self) -> None:

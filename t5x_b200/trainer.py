@@ -312,7 +312,7 @@ def _slice_batch(batch, i: int, n: int):
 
 def accumulate_grads_microbatched(model, train_state, batch: BatchType, dropout_rng: int,
                                   num_microbatches: Optional[int],
-                                  data_partition_spec=None):
+                                  data_partition_spec=None, learning_rate=None):
   """Gradients (fp32, summed over microbatches) and merged metrics
   (t5x/trainer.py:704-852)."""
   params = train_state.params
@@ -320,10 +320,19 @@ def accumulate_grads_microbatched(model, train_state, batch: BatchType, dropout_
   _begin_step(flat)
   n = num_microbatches if num_microbatches and num_microbatches > 1 else 1
   metrics = None
+  from t5x_b200.parallel import zero
+  ctx = zero.active()
   for i in range(n):
     mb = batch if n == 1 else _slice_batch(batch, i, n)
     rng = None if dropout_rng is None else fold_in_seed(dropout_rng, i)
     loss, m = model.loss_fn(params, mb, rng)
+    if ctx is not None and i == n - 1 and learning_rate is not None and \
+        hasattr(train_state, "_optimizer"):
+      # gradients become final layer by layer during this backward pass: let the owners
+      # start their fused reduce + update while the pass is still running
+      opt = train_state._optimizer
+      ctx.begin_overlap(int(train_state.step), opt.optimizer_def.update_hyper_params(
+          learning_rate=learning_rate))
     loss.backward()
     _fold_autograd_grads(flat)
     metrics = m if metrics is None else merge_metrics(metrics, m)
@@ -393,7 +402,8 @@ def eval_step(model, train_state, batch: BatchType) -> MetricMapType:
 def train_with_lr(train_state, batch, learning_rate, dropout_rng, model, num_microbatches,
                   weight_metrics_computer=None, data_partition_spec=None):
   grad_accum, metrics, mutables = accumulate_grads_microbatched(
-      model, train_state, batch, dropout_rng, num_microbatches, data_partition_spec)
+      model, train_state, batch, dropout_rng, num_microbatches, data_partition_spec,
+      learning_rate=learning_rate)
   return apply_grads(train_state, grad_accum, metrics, learning_rate, weight_metrics_computer)
 
 
@@ -587,7 +597,12 @@ class Trainer(BaseTrainer):
       return
     if opt_def.hyper_params.global_norm_clip_threshold:
       return
-    zero.enable(tree_utils.flatten_dict(train_state.params), st.data_group)
+    ctx = zero.enable(tree_utils.flatten_dict(train_state.params), st.data_group)
+    module = getattr(self._model, "module", None)
+    if ctx is not None and module is not None and \
+        os.environ.get("T5X_B200_OVERLAP_GRAD_EXCHANGE", "1") != "0":
+      slots = tree_utils.flatten_dict(train_state.param_states, is_leaf=adafactor._is_state_leaf)
+      ctx.attach_overlap(module, opt_def, lambda name: slots[name])
 
   def _train_step(self, train_state, batch, step_num):
     step = int(step_num)

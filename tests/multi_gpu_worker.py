@@ -101,7 +101,9 @@ def case_train(out):
   torch.cuda.synchronize()
   flat = torch.cat([p.detach().float().reshape(-1) for p in module.parameters()])
   bf = torch.cat([p.bf16.float().reshape(-1) for p in module.parameters()])
-  json.dump({"loss": float(summary["loss"].value), "sharded": zero.active() is not None,
+  ctx = zero.active()
+  json.dump({"loss": float(summary["loss"].value), "sharded": ctx is not None,
+             "overlapped": len(getattr(ctx, "done_this_step", ())),
              "param_sum": float(flat.double().sum()), "param_abs": float(flat.double().abs().sum()),
              "bf16_abs": float(bf.double().abs().sum()),
              "first": flat[:8].tolist()}, out)

@@ -46,6 +46,8 @@ def test_sharded_optimizer_matches_all_reduce(tmp_path):
   sharded = _run_ranks("train", tmp_path / "z")
   plain = _run_ranks("train", tmp_path / "p", env={"T5X_B200_OPTIMIZER_SHARDING": "0"})
   assert all(r["sharded"] for r in sharded) and not any(r["sharded"] for r in plain)
+  # the layers' updates ran during the backward pass of the last microbatch
+  assert all(r["overlapped"] > 0 for r in sharded)
   # replicas agree with each other, and the two gradient-reduction routes agree
   for run in (sharded, plain):
     assert abs(run[0]["param_sum"] - run[1]["param_sum"]) <= 1e-6 * run[0]["param_abs"]
