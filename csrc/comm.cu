@@ -110,49 +110,107 @@ constexpr int kDsThreads = 256;
 constexpr int kDsTileR = 32;
 constexpr int kDsTileC = 1024;  // 256 threads x float4
 
+// Tile walk shared by the two kernels below: CTAs stride over (batch, row tile, column tile).
+// The grid is capped (t5x_comm_set_max_ctas) so that these NVLink-latency-bound kernels leave
+// room on every SM for the GEMMs of the backward pass they overlap with.
+struct DsTiles {
+  int x;               // column tiles per row tile
+  int per_batch;       // tiles per batch entry
+  long long total;
+};
+
+static int g_comm_max_ctas = 0;  // 0: two per SM
+
+static inline DsTiles ds_tiles(int batch, int R, int C) {
+  DsTiles t;
+  t.x = (C + kDsTileC - 1) / kDsTileC;
+  t.per_batch = t.x * ((R + kDsTileR - 1) / kDsTileR);
+  t.total = static_cast<long long>(t.per_batch) * batch;
+  return t;
+}
+
+static inline int ds_grid(const DsTiles& t) {
+  const long long cap = g_comm_max_ctas > 0 ? g_comm_max_ctas : 2LL * num_sms();
+  return static_cast<int>(t.total < cap ? (t.total < 1 ? 1 : t.total) : cap);
+}
+
 // Adafactor phase 1 over the gradient summed across ranks. CTA tile: kDsTileR rows x
 // kDsTileC columns; a thread owns 4 adjacent columns and walks the rows, so column sums stay
 // in registers and row sums need one block reduction per row. Requires C % 4 == 0.
+template <int W>  // number of ranks known at compile time, or 0 for any `world`
 __global__ void __launch_bounds__(kDsThreads)
     dist_stats_kernel(PeerF32 grads, int world, float* __restrict__ g_out,
                       const float* __restrict__ p, float* __restrict__ rowsum,
                       float* __restrict__ colsum, AdafactorScalars* __restrict__ scal, int R, int C,
-                      float eps1) {
+                      float eps1, DsTiles tiles) {
   __shared__ float srow[kDsTileR][kDsThreads / 32];
   __shared__ float spsq[kDsThreads / 32];
-  const int b = blockIdx.z;
-  const long long base = static_cast<long long>(b) * R * C;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int r0 = blockIdx.y * kDsTileR;
-  const int col = blockIdx.x * kDsTileC + threadIdx.x * 4;
+  for (long long tile = blockIdx.x; tile < tiles.total; tile += gridDim.x) {
+  const int b = static_cast<int>(tile / tiles.per_batch);
+  const int in_b = static_cast<int>(tile - static_cast<long long>(b) * tiles.per_batch);
+  const long long base = static_cast<long long>(b) * R * C;
+  const int r0 = (in_b / tiles.x) * kDsTileR;
+  const int col = (in_b % tiles.x) * kDsTileC + threadIdx.x * 4;
   const bool active = col < C;
   float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f, psq = 0.f;
   const int rows = min(kDsTileR, R - r0);
-  for (int rr = 0; rr < rows; ++rr) {
-    float rs = 0.f;
-    if (active) {
-      const long long off = base + static_cast<long long>(r0 + rr) * C + col;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int d = 0; d < world; ++d) {
-        const float4 v = *reinterpret_cast<const float4*>(grads.p[d] + off);
-        acc.x += v.x;
-        acc.y += v.y;
-        acc.z += v.z;
-        acc.w += v.w;
+  // All loads of RU rows (W gradient copies and the parameter each) are issued before the
+  // first use, so a thread keeps RU * (W + 1) 16-byte requests in flight over NVLink / HBM.
+  constexpr int RU = W == 0 ? 1 : (W <= 2 ? 4 : 2);
+  constexpr int WN = W == 0 ? 1 : W;
+  for (int rr = 0; rr < rows; rr += RU) {
+    float4 v[RU][WN], pv[RU];
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      const bool on = active && rr + u < rows;
+      const long long off = base + static_cast<long long>(r0 + rr + u) * C + col;
+      pv[u] = on ? *reinterpret_cast<const float4*>(p + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (W == 0) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (on)
+          for (int d = 0; d < world; ++d) {
+            const float4 t = *reinterpret_cast<const float4*>(grads.p[d] + off);
+            acc.x += t.x;
+            acc.y += t.y;
+            acc.z += t.z;
+            acc.w += t.w;
+          }
+        v[u][0] = acc;
+      } else {
+#pragma unroll
+        for (int d = 0; d < WN; ++d)
+          v[u][d] = on ? *reinterpret_cast<const float4*>(grads.p[d] + off)
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      *reinterpret_cast<float4*>(g_out + off) = acc;
-      const float4 pv = *reinterpret_cast<const float4*>(p + off);
-      const float s0 = acc.x * acc.x + eps1, s1 = acc.y * acc.y + eps1,
-                  s2 = acc.z * acc.z + eps1, s3 = acc.w * acc.w + eps1;
-      c0 += s0;
-      c1 += s1;
-      c2 += s2;
-      c3 += s3;
-      rs = (s0 + s1) + (s2 + s3);
-      psq += pv.x * pv.x + pv.y * pv.y + pv.z * pv.z + pv.w * pv.w;
     }
-    rs = warp_sum(rs);
-    if (lane == 0) srow[rr][warp] = rs;
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      const bool on = active && rr + u < rows;
+      float4 acc = v[u][0];
+#pragma unroll
+      for (int d = 1; d < WN; ++d) {
+        acc.x += v[u][d].x;
+        acc.y += v[u][d].y;
+        acc.z += v[u][d].z;
+        acc.w += v[u][d].w;
+      }
+      float rs = 0.f;
+      if (on) {
+        const long long off = base + static_cast<long long>(r0 + rr + u) * C + col;
+        *reinterpret_cast<float4*>(g_out + off) = acc;
+        const float s0 = acc.x * acc.x + eps1, s1 = acc.y * acc.y + eps1,
+                    s2 = acc.z * acc.z + eps1, s3 = acc.w * acc.w + eps1;
+        c0 += s0;
+        c1 += s1;
+        c2 += s2;
+        c3 += s3;
+        rs = (s0 + s1) + (s2 + s3);
+        psq += pv[u].x * pv[u].x + pv[u].y * pv[u].y + pv[u].z * pv[u].z + pv[u].w * pv[u].w;
+      }
+      rs = warp_sum(rs);
+      if (lane == 0 && rr + u < rows) srow[rr + u][warp] = rs;
+    }
   }
   psq = warp_sum(psq);
   if (lane == 0) spsq[warp] = psq;
@@ -176,6 +234,8 @@ __global__ void __launch_bounds__(kDsThreads)
     for (int w = 0; w < kDsThreads / 32; ++w) t += spsq[w];
     atomicAdd(&scal[b].psq, t);
   }
+  __syncthreads();  // srow / spsq are reused by the next tile
+  }
 }
 
 // Factored parameter update with the bf16 result stored to every rank. Same tiling as
@@ -185,19 +245,21 @@ __global__ void __launch_bounds__(kDsThreads)
                       const float* __restrict__ rf, const float* __restrict__ cf,
                       float* __restrict__ m, PeerBf16 out, int world,
                       const AdafactorScalars* __restrict__ scal, int R, int C, float n_global,
-                      AfHyper h) {
-  const int b = blockIdx.z;
+                      AfHyper h, DsTiles tiles) {
+  for (long long tile = blockIdx.x; tile < tiles.total; tile += gridDim.x) {
+  const int b = static_cast<int>(tile / tiles.per_batch);
+  const int in_b = static_cast<int>(tile - static_cast<long long>(b) * tiles.per_batch);
   const long long base = static_cast<long long>(b) * R * C;
-  const int r0 = blockIdx.y * kDsTileR;
-  const int col = blockIdx.x * kDsTileC + threadIdx.x * 4;
-  if (col >= C) return;
+  const int r0 = (in_b / tiles.x) * kDsTileR;
+  const int col = (in_b % tiles.x) * kDsTileC + threadIdx.x * 4;
+  if (col >= C) continue;
   const float scale = af_update_scale(scal[b], n_global, h);
   const float4 cfv = *reinterpret_cast<const float4*>(cf + static_cast<long long>(b) * C + col);
-  rf += static_cast<long long>(b) * R;
+  const float* rfb = rf + static_cast<long long>(b) * R;
   const int rows = min(kDsTileR, R - r0);
   for (int rr = 0; rr < rows; ++rr) {
     const long long off = base + static_cast<long long>(r0 + rr) * C + col;
-    const float rfv = rf[r0 + rr] * scale;
+    const float rfv = rfb[r0 + rr] * scale;
     const float4 gv = *reinterpret_cast<const float4*>(g + off);
     const float4 old = *reinterpret_cast<const float4*>(p + off);
     float sub[4] = {gv.x * rfv * cfv.x, gv.y * rfv * cfv.y, gv.z * rfv * cfv.z,
@@ -229,6 +291,7 @@ __global__ void __launch_bounds__(kDsThreads)
     packed.x = *reinterpret_cast<uint32_t*>(&lo);
     packed.y = *reinterpret_cast<uint32_t*>(&hi);
     for (int d = 0; d < world; ++d) *reinterpret_cast<uint2*>(out.p[d] + off) = packed;
+  }
   }
 }
 
@@ -298,6 +361,9 @@ T5X_API int t5x_peer_push_bf16(void* const* dsts, const void* src, int world, in
   return comm_check("peer_push_bf16");
 }
 
+// Upper bound on the grid of the NVLink-fused optimizer kernels (0 restores two CTAs per SM).
+T5X_API void t5x_comm_set_max_ctas(int max_ctas) { g_comm_max_ctas = max_ctas < 0 ? 0 : max_ctas; }
+
 // Adafactor phase 1 with the gradient summed over `world` ranks' copies (grads[d], same
 // layout as g_out, which receives the sum and may be this rank's own copy). Clears `scratch`
 // like t5x_adafactor_stats. Requires C % 4 == 0 and 16-byte aligned pointers.
@@ -315,10 +381,13 @@ T5X_API int t5x_dist_adafactor_stats(const void* p, const void* const* grads, in
   float* colsum = rowsum + static_cast<long long>(batch) * R;
   AdafactorScalars* scal = reinterpret_cast<AdafactorScalars*>(
       s + 2ll * batch * (static_cast<long long>(R) + C));
-  dim3 grid((C + kDsTileC - 1) / kDsTileC, (R + kDsTileR - 1) / kDsTileR, batch);
-  dist_stats_kernel<<<grid, kDsThreads, 0, st>>>(ps, world, static_cast<float*>(g_out),
-                                                 static_cast<const float*>(p), rowsum, colsum,
-                                                 scal, R, C, eps1);
+  const DsTiles tiles = ds_tiles(batch, R, C);
+  auto kernel = world == 2 ? dist_stats_kernel<2>
+              : world == 4 ? dist_stats_kernel<4>
+              : world == 8 ? dist_stats_kernel<8> : dist_stats_kernel<0>;
+  kernel<<<ds_grid(tiles), kDsThreads, 0, st>>>(
+      ps, world, static_cast<float*>(g_out), static_cast<const float*>(p), rowsum, colsum, scal,
+      R, C, eps1, tiles);
   count_launches(1);
   return comm_check("dist_adafactor_stats");
 }
@@ -339,10 +408,10 @@ T5X_API int t5x_dist_adafactor_apply(void* p, const void* g, void* m, void* cons
   float* cf = rf + static_cast<long long>(batch) * R;
   AdafactorScalars* scal = reinterpret_cast<AdafactorScalars*>(cf + static_cast<long long>(batch) * C);
   AfHyper h = af_hyper(lr, eps2, clip_threshold, weight_decay, beta1, max_param_scale, flags);
-  dim3 grid((C + kDsTileC - 1) / kDsTileC, (R + kDsTileR - 1) / kDsTileR, batch);
-  dist_apply_kernel<<<grid, kDsThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  const DsTiles tiles = ds_tiles(batch, R, C);
+  dist_apply_kernel<<<ds_grid(tiles), kDsThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<float*>(p), static_cast<const float*>(g), rf, cf, static_cast<float*>(m), po,
-      world, scal, R, C, static_cast<float>(n_global), h);
+      world, scal, R, C, static_cast<float>(n_global), h, tiles);
   count_launches(1);
   return comm_check("dist_adafactor_apply");
 }

@@ -32,6 +32,8 @@ native.register_signature("t5x_dist_adafactor_apply",
                            c_ll, c_float, c_float, c_float, c_float, c_float, c_float, c_int,
                            c_void_p])
 
+native.register_signature("t5x_comm_set_max_ctas", [c_int])
+
 MAX_PEERS = 16
 # Polls (64 ns apart at least) a barrier waits before it gives up: about two seconds.
 DEFAULT_SPIN_LIMIT = 1 << 24
@@ -112,3 +114,9 @@ def dist_adafactor_apply_(p, g, m, bf16_ptrs, scratch, batch, rows, cols, n_glob
       p.data_ptr(), g.data_ptr(), native.ptr(m), bf16_ptrs, len(bf16_ptrs), scratch.data_ptr(),
       batch, rows, cols, n_global, lr, eps2, clip_threshold, weight_decay, beta1,
       max_param_scale, flags, native.stream_ptr()), "dist_adafactor_apply")
+
+
+def set_max_ctas(max_ctas: int) -> None:
+  """Caps the grid of the NVLink-fused optimizer kernels (0: two CTAs per SM), so that they
+  leave room for the GEMMs they overlap with."""
+  native.lib().t5x_comm_set_max_ctas(int(max_ctas))

@@ -23,6 +23,7 @@ axis, t5x/partitioning.py:615-676) restated for one process per GPU with peer me
 from __future__ import annotations
 
 import logging
+import os
 from typing import Dict, List, Mapping, Optional
 
 import numpy as np
@@ -112,10 +113,15 @@ class ZeroContext:
     self._opt_def = optimizer_def
     self._state_of = state_of
     self._side = torch.cuda.Stream(device=self.grads.tensor.device)
+    if os.environ.get("T5X_B200_COMM_MAX_CTAS"):
+      from t5x_b200.ops import comm
+      comm.set_max_ctas(int(os.environ["T5X_B200_COMM_MAX_CTAS"]))
     self._overlap = None          # (step, hyper_params) while the last microbatch runs
     self.done_this_step = set()
     self._buckets = {}
     by_id = {id(p): k for k, p in self.params.items()}
+    taken = set()
+    stacks = set()
     for mod_name, mod in module.named_modules():
       if not re.fullmatch(r"(.*\.)?layers_\d+", mod_name):
         continue
@@ -123,8 +129,29 @@ class ZeroContext:
       if not names:
         continue
       self._buckets[mod_name] = names
+      taken.update(names)
+      stacks.add(mod_name.rpartition(".")[0])
       mod.register_full_backward_hook(
           lambda m, gin, gout, bucket=mod_name: self._bucket_ready(bucket))
+    # What a layer stack owns besides its layers (final norm, output projection, position
+    # biases) is final once the gradient with respect to the stack's input exists. A stack
+    # whose inputs need no gradient (token ids) fires its hook early, with no input gradient:
+    # `_bucket_ready` ignores that call. Parameters shared between stacks wait for the end.
+    uses = {}
+    for stack in stacks:
+      if stack:
+        for p in module.get_submodule(stack).parameters(recurse=True):
+          uses[id(p)] = uses.get(id(p), 0) + 1
+    for stack in sorted(s for s in stacks if s):
+      mod = module.get_submodule(stack)
+      names = [by_id[id(p)] for p in mod.parameters(recurse=True)
+               if id(p) in by_id and by_id[id(p)] not in taken and uses[id(p)] == 1]
+      if not names:
+        continue
+      self._buckets[stack] = names
+      mod.register_full_backward_hook(
+          lambda m, gin, gout, bucket=stack: self._bucket_ready(
+              bucket, has_input_grad=any(g is not None for g in gin)))
 
   def begin_overlap(self, step: int, hyper_params) -> None:
     if getattr(self, "_side", None) is not None:
@@ -136,8 +163,8 @@ class ZeroContext:
       self._overlap = None
       torch.cuda.current_stream().wait_stream(self._side)
 
-  def _bucket_ready(self, bucket: str) -> None:
-    if self._overlap is None:
+  def _bucket_ready(self, bucket: str, has_input_grad: bool = True) -> None:
+    if self._overlap is None or not has_input_grad:
       return
     step, hp = self._overlap
     # only parameters whose whole gradient went through the native accumulate path are final
