@@ -25,7 +25,26 @@ struct GemmParams {
   long long ldh;
   float alpha;
   int tiles_m, tiles_n;
+  int mt_rot;  // the row-tile walk starts at this tile (tensor-parallel kernels); 0 otherwise
   int* status;
+};
+
+// Tensor-parallel extensions of the CTA-pair GEMM. The rows of A (all-gather) or of C
+// (reduce-scatter) are split evenly over `world` ranks, `rows_per_rank` consecutive rows each.
+enum GemmTpMode : int { kTpNone = 0, kTpAllGather = 1, kTpReduceScatter = 2 };
+constexpr int kTpMaxPeers = 16;
+struct GemmTp {
+  int world, rank, rows_per_rank;
+  // all-gather -> GEMM: A is this rank's [M, K] buffer; block r of it is pulled from
+  // a_src[r] (rank r's buffer as mapped here, same layout) by the copy warps while the tensor
+  // cores work on blocks that are already here. flags[r] counts the pieces of block r landed.
+  const uint8_t* a_src[kTpMaxPeers];
+  uint8_t* a_dst;
+  long long block_bytes;
+  unsigned int* flags;
+  // GEMM -> reduce-scatter: rows of block r are stored to c_dst[r] ([rows_per_rank, ldc] bf16,
+  // this rank's slot of rank r's inbox as mapped here) instead of C.
+  __nv_bfloat16* c_dst[kTpMaxPeers];
 };
 
 __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const float* v, int n_valid,
@@ -83,17 +102,27 @@ __device__ __forceinline__ void gemm_tile_coords(const GemmParams& p, int tile, 
   const int r = rem - g * per_group;
   nt = r / gsz;
   mt = first_m + (r - nt * gsz);
+  if (p.mt_rot) {
+    mt += p.mt_rot;
+    if (mt >= p.tiles_m) mt -= p.tiles_m;
+  }
 }
 
 // Epilogue of one 128-row accumulator tile held in TMEM columns [t_cols, t_cols + BN): the
 // calling warp owns lane quarter q (rows m0 + 32q .. +31), `c_vec_ok` says whether 16-byte
 // stores to C are legal.
-template <int BN, int EPI>
+template <int BN, int EPI, bool RS = false>
 __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t t_row, int m0,
                                                    int n0, int b, int q, int lane,
-                                                   bool c_vec_ok) {
+                                                   bool c_vec_ok, const GemmTp* tp = nullptr) {
   const int row = m0 + q * 32 + lane;
   const bool row_ok = row < p.M;
+  // reduce-scatter: this row lives in its owner's inbox (peer memory unless the owner is us)
+  __nv_bfloat16* rs_row = nullptr;
+  if (RS && row_ok) {
+    const int owner = row / tp->rows_per_rank;
+    rs_row = tp->c_dst[owner] + static_cast<long long>(row - owner * tp->rows_per_rank) * p.ldc;
+  }
 
   if (EPI == kEpiGatedGelu) {
     constexpr int kHalf = BN / 2;
@@ -172,6 +201,8 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
                 out[i] = p.accumulate ? out[i] + v[i] : v[i];
             }
           }
+        } else if (RS) {
+          store_row_bf16(rs_row + col, v, n_valid, c_vec_ok);
         } else {
           __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.c_batch_stride +
                                static_cast<long long>(row) * p.ldc + col;

@@ -28,10 +28,34 @@ constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
 constexpr int kPairSmemTotal = kPairStages * kPairStageBytes + 1024 + 1024;
 constexpr int kKernelIdGemmPair = 2;
 
-template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+// Tensor-parallel variants (MODE != kTpNone) of the same kernel:
+//
+//  kTpAllGather     A's row blocks live on `world` ranks. A seventh warp per CTA pulls the
+//                   other ranks' blocks into this rank's A buffer with bulk copies staged
+//                   through shared memory (peer memory -> shared -> local memory, never a
+//                   multicast load) and counts landed pieces in flags[r]; the TMA producer
+//                   waits (bounded) for the blocks its tile needs. The row-tile walk starts
+//                   at this rank's own block, so the tensor cores work while NVLink delivers.
+//  kTpReduceScatter the epilogue stores each bf16 row of the partial product into the inbox
+//                   of the rank that owns the row (peer memory over NVLink); the walk starts
+//                   at the next rank's block and ends with this rank's own.
+constexpr int kTpPiece = 8192;   // bytes per bulk copy
+constexpr int kTpSlots = 3;      // staging slots per CTA
+constexpr int kTpStageBytes = kTpPiece * kTpSlots;
+constexpr int kTpFlagLimit = 1 << 22;  // polls (>= 64 ns apart) before a flag wait gives up
+
+template <int MODE>
+constexpr int pair_threads() { return MODE == kTpAllGather ? kGemmThreads + 32 : kGemmThreads; }
+template <int MODE>
+constexpr int pair_smem() {
+  return MODE == kTpAllGather ? kPairSmemTotal + kTpStageBytes : kPairSmemTotal;
+}
+
+template <int EPI, int MODE = kTpNone>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>(), 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+                     const __grid_constant__ CUtensorMap tmB2, const GemmParams p,
+                     const __grid_constant__ GemmTp tp) {
   constexpr int BN = kPairBN;
   constexpr int kStages = kPairStages;
   constexpr int kTileN = (EPI == kEpiGatedGelu) ? BN / 2 : BN;
@@ -48,6 +72,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   uint64_t* tmem_empty = bars + 2 * kStages + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* copy_full = bars + 2 * kStages + 8;                    // kTpSlots barriers
+  uint8_t* staging = smem + kStages * kPairStageBytes + 1024;      // kTpSlots x kTpPiece
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -64,6 +90,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       mbar_init(&tmem_full[a], 1);
       mbar_init(&tmem_empty[a], 8);
     }
+    if (MODE == kTpAllGather)
+      for (int a = 0; a < kTpSlots; ++a) mbar_init(&copy_full[a], 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -91,6 +119,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t landed = 0;  // ranks whose block is known to be here
+      const uint32_t pieces_per_block =
+          MODE == kTpAllGather ? static_cast<uint32_t>((tp.block_bytes + kTpPiece - 1) / kTpPiece) : 0;
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
         int b, mt, nt;
         gemm_tile_coords(p, tile, tiles_per_batch, b, mt, nt);
@@ -100,6 +131,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         // wi_0 for the even CTA and of wi_1 for the odd one
         const int n0 = (EPI == kEpiGatedGelu) ? n_tile : n_tile + static_cast<int>(cta) * (BN / 2);
         const CUtensorMap* tb = (EPI == kEpiGatedGelu && cta == 1) ? &tmB2 : &tmB;
+        if (MODE == kTpAllGather && m0 < p.M) {
+          // the rows of this CTA's A tile: wait for the blocks of other ranks among them
+          const int r_lo = m0 / tp.rows_per_rank;
+          const int r_hi = min(m0 + kBM - 1, p.M - 1) / tp.rows_per_rank;
+          for (int r = r_lo; r <= r_hi && ok; ++r) {
+            if (r == tp.rank || ((landed >> r) & 1u)) continue;
+            bool here = false;
+            for (int it = 0; it < kTpFlagLimit; ++it) {
+              if (ld_acquire_gpu(&tp.flags[r]) >= pieces_per_block) {
+                here = true;
+                break;
+              }
+              if (*abort_flag) break;
+              __nanosleep(64);
+            }
+            if (!here) {
+              report_status(p.status, kStatusTimeoutPeerFlag, kKernelIdGemmPair, tile, r);
+              *abort_flag = 1;
+              ok = false;
+            }
+            landed |= 1u << r;
+          }
+          if (!ok) break;
+          fence_proxy_async_all();  // the bulk stores that wrote A, before this TMA reads it
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             report_status(p.status, kStatusTimeoutProducer, kKernelIdGemmPair, tile, kb);
@@ -181,6 +237,69 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         if (ok) umma_commit_pair(&tmem_full[acc], 0x3);
       }
     }
+  } else if (MODE == kTpAllGather && warp == 6) {
+    // ------------------------------ all-gather copy warp ------------------------------
+    // Pieces of kTpPiece bytes of the other ranks' blocks, in ring order from the next rank,
+    // are dealt round-robin to the CTAs. Each goes peer memory -> staging slot (bulk load on
+    // an mbarrier) -> this rank's A (bulk store); flags[r] is raised once the stores of a few
+    // pieces are complete.
+    if (lane == 0 && tp.world > 1) {
+      const long long ppb = (tp.block_bytes + kTpPiece - 1) / kTpPiece;
+      const long long total = ppb * (tp.world - 1);
+      long long g_issue = blockIdx.x, g_done = blockIdx.x;
+      int n_issue = 0, n_done = 0;
+      int pub_rank = -1;
+      uint32_t pub_count = 0;
+      bool ok = true;
+      auto publish = [&]() {
+        if (pub_count) {
+          bulk_store_wait_all();
+          fence_proxy_async_all();
+          red_release_gpu_add(&tp.flags[pub_rank], pub_count);
+          pub_count = 0;
+        }
+      };
+      while (g_done < total && ok) {
+        while (g_issue < total && n_issue - n_done < kTpSlots) {
+          const int r = (tp.rank + 1 + static_cast<int>(g_issue / ppb)) % tp.world;
+          const long long off = (g_issue % ppb) * kTpPiece;
+          const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long long>(kTpPiece),
+                                                           tp.block_bytes - off));
+          const int slot = n_issue % kTpSlots;
+          mbar_expect_tx(&copy_full[slot], bytes);
+          bulk_load(staging + slot * kTpPiece, tp.a_src[r] + r * tp.block_bytes + off, bytes,
+                    &copy_full[slot]);
+          ++n_issue;
+          g_issue += gridDim.x;
+        }
+        const int r = (tp.rank + 1 + static_cast<int>(g_done / ppb)) % tp.world;
+        const long long off = (g_done % ppb) * kTpPiece;
+        const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long long>(kTpPiece),
+                                                         tp.block_bytes - off));
+        const int slot = n_done % kTpSlots;
+        if (!mbar_wait(&copy_full[slot], (n_done / kTpSlots) & 1, abort_flag)) {
+          report_status(p.status, kStatusTimeoutPeerFlag, kKernelIdGemmPair, -2, r);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        if (r != pub_rank) {
+          publish();
+          pub_rank = r;
+        }
+        bulk_store(tp.a_dst + r * tp.block_bytes + off, staging + slot * kTpPiece, bytes);
+        bulk_store_wait_read();  // the slot may be refilled
+        ++pub_count;
+        ++n_done;
+        g_done += gridDim.x;
+        if (pub_count == 4) publish();
+      }
+      publish();
+      if (!ok) {
+        // loads still in flight target this CTA's shared memory: give them time to land
+        for (int it = 0; it < 2000; ++it) __nanosleep(1000);
+      }
+    }
   } else {
     // ------------------------------ epilogue (own 128 rows) ------------------------------
     const int q = warp & 3;
@@ -203,7 +322,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok);
+      gemm_epilogue_tile<BN, EPI, MODE == kTpReduceScatter>(p, t_row, m0, n0, b, q, lane, c_vec_ok,
+                                                            &tp);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(drained + acc * 8);
@@ -225,16 +345,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   }
 }
 
-template <int EPI>
+template <int EPI, int MODE>
 static int launch_pair(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tB2,
-                       GemmParams& p, int max_ctas, cudaStream_t stream) {
+                       GemmParams& p, const GemmTp& tp, int max_ctas, cudaStream_t stream) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<EPI>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<EPI, MODE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kPairSmemTotal);
+                                         pair_smem<MODE>());
     if (e != cudaSuccess) return set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set[dev] = true;
   }
@@ -242,27 +362,52 @@ static int launch_pair(const CUtensorMap* tA, const CUtensorMap* tB, const CUten
   int pairs = num_sms() / 2;
   if (max_ctas > 0) pairs = std::min(pairs, std::max(1, max_ctas / 2));
   pairs = std::max(1, std::min(pairs, total));
-  gemm_pair_kernel<EPI><<<2 * pairs, kGemmThreads, kPairSmemTotal, stream>>>(*tA, *tB, *tB2, p);
+  gemm_pair_kernel<EPI, MODE><<<2 * pairs, pair_threads<MODE>(), pair_smem<MODE>(), stream>>>(
+      *tA, *tB, *tB2, p, tp);
   count_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("gemm_pair launch: %s", cudaGetErrorString(e));
   return 0;
 }
 
-// Called by t5x_gemm_bf16 for problems large enough to fill CTA pairs. `p.tiles_m` must count
-// 256-row tiles; the tensor maps are the same as for the one-CTA kernel with BN = 128-column
-// (K-major) or 64-column (MN-major) B boxes.
-int launch_gemm_pair(int epilogue, const CUtensorMap* tA, const CUtensorMap* tB,
-                     const CUtensorMap* tB2, GemmParams& p, int max_ctas, cudaStream_t stream) {
+template <int MODE>
+static int launch_pair_mode(int epilogue, const CUtensorMap* tA, const CUtensorMap* tB,
+                            const CUtensorMap* tB2, GemmParams& p, const GemmTp& tp, int max_ctas,
+                            cudaStream_t stream) {
   switch (epilogue) {
     case kEpiPlain:
-      return launch_pair<kEpiPlain>(tA, tB, tB2, p, max_ctas, stream);
+      return launch_pair<kEpiPlain, MODE>(tA, tB, tB2, p, tp, max_ctas, stream);
     case kEpiGatedGelu:
-      return launch_pair<kEpiGatedGelu>(tA, tB, tB2, p, max_ctas, stream);
+      if (MODE == kTpReduceScatter) break;
+      return launch_pair<kEpiGatedGelu, MODE == kTpReduceScatter ? kTpNone : MODE>(
+          tA, tB, tB2, p, tp, max_ctas, stream);
     case kEpiResidual:
-      return launch_pair<kEpiResidual>(tA, tB, tB2, p, max_ctas, stream);
+      if (MODE == kTpAllGather) break;
+      return launch_pair<kEpiResidual, MODE == kTpAllGather ? kTpNone : MODE>(
+          tA, tB, tB2, p, tp, max_ctas, stream);
     default:
-      return set_error("gemm_pair: unknown epilogue %d", epilogue);
+      break;
+  }
+  return set_error("gemm_pair: epilogue %d is not available in tensor-parallel mode %d", epilogue,
+                   MODE);
+}
+
+// Called by t5x_gemm_bf16 for problems large enough to fill CTA pairs. `p.tiles_m` must count
+// 256-row tiles; the tensor maps are the same as for the one-CTA kernel with BN = 128-column
+// (K-major) or 64-column (MN-major) B boxes. `tp` is null for a plain GEMM.
+int launch_gemm_pair(int epilogue, const CUtensorMap* tA, const CUtensorMap* tB,
+                     const CUtensorMap* tB2, GemmParams& p, int max_ctas, cudaStream_t stream,
+                     const GemmTp* tp, int tp_mode) {
+  static const GemmTp none = {};
+  switch (tp == nullptr ? kTpNone : tp_mode) {
+    case kTpNone:
+      return launch_pair_mode<kTpNone>(epilogue, tA, tB, tB2, p, none, max_ctas, stream);
+    case kTpAllGather:
+      return launch_pair_mode<kTpAllGather>(epilogue, tA, tB, tB2, p, *tp, max_ctas, stream);
+    case kTpReduceScatter:
+      return launch_pair_mode<kTpReduceScatter>(epilogue, tA, tB, tB2, p, *tp, max_ctas, stream);
+    default:
+      return set_error("gemm_pair: unknown tensor-parallel mode %d", tp_mode);
   }
 }
 

@@ -297,7 +297,8 @@ static const CUtensorMap* operand_map(const void* ptr, int mn_major, long long r
 // Returns 0 on success; a negative value with t5x_last_error() set otherwise.
 namespace t5x {
 int launch_gemm_pair(int epilogue, const CUtensorMap* tA, const CUtensorMap* tB,
-                     const CUtensorMap* tB2, GemmParams& p, int max_ctas, cudaStream_t stream);
+                     const CUtensorMap* tB2, GemmParams& p, int max_ctas, cudaStream_t stream,
+                     const GemmTp* tp = nullptr, int tp_mode = 0);
 
 // 0 = never use CTA pairs, 1 = when the shape suits them (default), 2 = always.
 // Read once from T5X_GEMM_PAIR; t5x_gemm_set_pair_mode overrides it.
@@ -318,14 +319,14 @@ T5X_API int t5x_gemm_set_pair_mode(int mode) {
   return 0;
 }
 
-T5X_API int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C, int M, int N,
-                          int K, int batch, long long lda, long long ldb, long long ldc,
-                          long long a_batch_stride, long long b_batch_stride,
-                          long long c_batch_stride, int a_mn_major, int b_mn_major, int out_fp32,
-                          int accumulate, int epilogue, const void* R, long long ldr,
-                          long long r_batch_stride, void* H0, void* H1, long long ldh, float alpha,
-                          int max_ctas, void* stream) {
-  using namespace t5x;
+namespace t5x {
+static int gemm_impl(const void* A, const void* B, const void* B2, void* C, int M, int N,
+                     int K, int batch, long long lda, long long ldb, long long ldc,
+                     long long a_batch_stride, long long b_batch_stride,
+                     long long c_batch_stride, int a_mn_major, int b_mn_major, int out_fp32,
+                     int accumulate, int epilogue, const void* R, long long ldr,
+                     long long r_batch_stride, void* H0, void* H1, long long ldh, float alpha,
+                     int max_ctas, void* stream, const GemmTp* tp, int tp_mode) {
   if (M <= 0 || N <= 0 || batch <= 0) return 0;
   if (K <= 0) return set_error("gemm: K must be positive");
   if (lda % 8 || ldb % 8) return set_error("gemm: lda/ldb must be multiples of 8 elements");
@@ -352,6 +353,7 @@ T5X_API int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C,
   p.alpha = alpha;
   p.status = device_status_buffer();
   p.tiles_m = (M + kBM - 1) / kBM;
+  p.mt_rot = 0;
 
   const CUtensorMap* tA = operand_map(A, a_mn_major, M, K, lda, a_batch_stride, batch, 128);
   const CUtensorMap* tB = operand_map(B, b_mn_major, N, K, ldb, b_batch_stride, batch, 128);
@@ -366,6 +368,25 @@ T5X_API int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C,
   // has at least one full pair tile and pairs fill the machine about as well as single CTAs.
   const int pair_tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
   const int pair_mode = gemm_pair_mode();
+
+  if (tp != nullptr) {
+    // tensor-parallel kernels exist for CTA pairs only; the walk over row tiles is rotated so
+    // that an all-gather starts with this rank's rows and a reduce-scatter ends with them
+    if (batch != 1 || out_fp32 || accumulate)
+      return set_error("tensor-parallel gemm: batch 1, bf16 output, no accumulate");
+    if (epilogue == kEpiResidual && R == nullptr) return set_error("residual epilogue needs R");
+    const CUtensorMap* tB2 = tB;
+    if (epilogue == kEpiGatedGelu) {
+      tB2 = operand_map(B2, b_mn_major, N, K, ldb, b_batch_stride, batch, 128);
+      if (!tB2) return -1;
+    }
+    p.tiles_m = pair_tiles_m;
+    p.tiles_n = epilogue == kEpiGatedGelu ? (N + 127) / 128 : (N + 255) / 256;
+    const int first = tp_mode == kTpAllGather ? tp->rank : (tp->rank + 1) % tp->world;
+    p.mt_rot = static_cast<int>((static_cast<long long>(first) * tp->rows_per_rank) / (2 * kBM));
+    if (p.mt_rot >= p.tiles_m) p.mt_rot = 0;
+    return launch_gemm_pair(epilogue, tA, tB, tB2, p, max_ctas, st, tp, tp_mode);
+  }
 
   if (epilogue == kEpiGatedGelu) {
     if (out_fp32 || accumulate) return set_error("gated-GELU epilogue writes bf16 without accumulate");
@@ -402,4 +423,74 @@ T5X_API int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C,
   }
   return bn == 256 ? launch_gemm<256, kEpiPlain>(tA, tB, tB, p, max_ctas, st)
                    : launch_gemm<128, kEpiPlain>(tA, tB, tB, p, max_ctas, st);
+}
+}  // namespace t5x
+
+T5X_API int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C, int M, int N,
+                          int K, int batch, long long lda, long long ldb, long long ldc,
+                          long long a_batch_stride, long long b_batch_stride,
+                          long long c_batch_stride, int a_mn_major, int b_mn_major, int out_fp32,
+                          int accumulate, int epilogue, const void* R, long long ldr,
+                          long long r_batch_stride, void* H0, void* H1, long long ldh, float alpha,
+                          int max_ctas, void* stream) {
+  return t5x::gemm_impl(A, B, B2, C, M, N, K, batch, lda, ldb, ldc, a_batch_stride,
+                        b_batch_stride, c_batch_stride, a_mn_major, b_mn_major, out_fp32,
+                        accumulate, epilogue, R, ldr, r_batch_stride, H0, H1, ldh, alpha, max_ctas,
+                        stream, nullptr, 0);
+}
+
+// All-gather -> GEMM in one kernel. A is this rank's [M, K] bf16 buffer (row-major, lda == K)
+// whose block `rank` (rows_per_rank rows) is already filled; a_peers[r] is rank r's buffer of
+// the same layout as mapped into this process. The kernel pulls the other blocks over NVLink
+// while it multiplies, so A is complete (and reusable) when it returns. `flags`: `world`
+// uint32 in this GPU's memory, cleared here. epilogue 0 (C = A @ B) or 1 (gated GELU).
+T5X_API int t5x_gemm_allgather_bf16(void* A, const void* const* a_peers, int world, int rank,
+                                    int rows_per_rank, void* flags, const void* B, const void* B2,
+                                    void* C, int M, int N, int K, long long ldb, long long ldc,
+                                    int b_mn_major, int epilogue, void* H0, void* H1,
+                                    long long ldh, void* stream) {
+  using namespace t5x;
+  if (world < 1 || world > kTpMaxPeers || rank < 0 || rank >= world ||
+      static_cast<long long>(rows_per_rank) * world != M || (K % 8))
+    return set_error("gemm_allgather: bad world/rank/rows (%d/%d/%d for M=%d)", world, rank,
+                     rows_per_rank, M);
+  GemmTp tp = {};
+  tp.world = world;
+  tp.rank = rank;
+  tp.rows_per_rank = rows_per_rank;
+  tp.block_bytes = static_cast<long long>(rows_per_rank) * K * 2;
+  for (int r = 0; r < world; ++r) tp.a_src[r] = static_cast<const uint8_t*>(a_peers[r]);
+  tp.a_dst = static_cast<uint8_t*>(A);
+  tp.flags = static_cast<unsigned int*>(flags);
+  cudaMemsetAsync(flags, 0, sizeof(unsigned int) * world, static_cast<cudaStream_t>(stream));
+  return gemm_impl(A, B, B2, C, M, N, K, 1, K, ldb, ldc, 0, 0, 0, 0, b_mn_major, 0, 0, epilogue,
+                   nullptr, 0, 0, H0, H1, ldh, 1.f, 0, stream, &tp, kTpAllGather);
+}
+
+// GEMM -> reduce-scatter in one kernel: the bf16 partial product A @ B (+ R) of this rank is
+// stored row block by row block into the owners' inboxes: c_peers[r] is this rank's slot
+// ([rows_per_rank, ldc]) of rank r's inbox as mapped into this process. The owners sum their
+// slots after a barrier. epilogue 0 or 2 (adds the local bf16 [M, N] matrix R first).
+T5X_API int t5x_gemm_reducescatter_bf16(const void* A, const void* B, void* const* c_peers,
+                                        int world, int rank, int rows_per_rank, int M, int N, int K,
+                                        long long lda, long long ldb, long long ldc,
+                                        int a_mn_major, int b_mn_major, const void* R,
+                                        long long ldr, void* stream) {
+  using namespace t5x;
+  if (world < 1 || world > kTpMaxPeers || rank < 0 || rank >= world ||
+      static_cast<long long>(rows_per_rank) * world != M || (ldc % 8))
+    return set_error("gemm_reducescatter: bad world/rank/rows (%d/%d/%d for M=%d)", world, rank,
+                     rows_per_rank, M);
+  GemmTp tp = {};
+  tp.world = world;
+  tp.rank = rank;
+  tp.rows_per_rank = rows_per_rank;
+  for (int r = 0; r < world; ++r) {
+    if (reinterpret_cast<uintptr_t>(c_peers[r]) & 15)
+      return set_error("gemm_reducescatter: inbox pointers must be 16-byte aligned");
+    tp.c_dst[r] = static_cast<__nv_bfloat16*>(c_peers[r]);
+  }
+  return gemm_impl(A, B, nullptr, nullptr, M, N, K, 1, lda, ldb, ldc, 0, 0, 0, a_mn_major,
+                   b_mn_major, 0, 0, R ? kEpiResidual : kEpiPlain, R, ldr, 0, nullptr, nullptr, 0,
+                   1.f, 0, stream, &tp, kTpReduceScatter);
 }

@@ -429,6 +429,37 @@ class MultiHeadDotProductAttention(nn.Module):
                      enable_dropout, beams_per_kv=beams_per_kv)
     return self._project_out(x, b, lq, residual)
 
+  def forward_sp(self, h_sp: torch.Tensor, x_sp: torch.Tensor, batch: int, lq: int, *,
+                 kv_full: Optional[torch.Tensor] = None, bias_table=None,
+                 bidirectional: bool = True, num_buckets: int = 32, max_distance: int = 128,
+                 key_mask=None, causal: bool = False, q_segment_ids=None,
+                 kv_segment_ids=None) -> torch.Tensor:
+    """Row-sharded ("sequence parallel") form under tensor parallelism: `h_sp` / `x_sp` are
+    this rank's rows of the normed input and of the residual stream ([batch * lq / T, emb]).
+    The q/k/v projections gather the rows inside their GEMM kernel and the output projection
+    scatters its partial sums from its epilogue (see `t5x_b200.parallel.tp_fused`); returns
+    this rank's rows of the new residual stream. `kv_full` (cross-attention) is the replicated
+    [batch, lk, emb] encoder output."""
+    from t5x_b200.parallel import tp_fused
+    if self.scale_attn_logits:
+      h_sp = h_sp / math.sqrt(self.head_dim)
+    hd = (self.local_heads, self.head_dim)
+    if kv_full is None:
+      q, k, v = tp_fused.all_gather_linears(
+          h_sp, [self.query.kernel, self.key.kernel, self.value.kernel])
+      lk = lq
+    else:
+      (q,) = tp_fused.all_gather_linears(h_sp, [self.query.kernel])
+      lk = kv_full.shape[1]
+      k, v = self.key(kv_full), self.value(kv_full)
+    q = q.view(batch, lq, *hd)
+    k = k.view(batch, lk, *hd)
+    v = v.view(batch, lk, *hd)
+    x = self._attend(q, k, v, bias_table, bidirectional, num_buckets, max_distance, key_mask,
+                     causal, q_segment_ids, kv_segment_ids, None, None, 0, False)
+    x = x.reshape(batch * lq, self.local_heads * self.head_dim)
+    return tp_fused.linear_reduce_scatter(x, self.out.kernel, x_sp)
+
   def _project_out(self, x, b, lq, residual):
     x = x.reshape(b, lq, self.local_heads * self.head_dim)
     st = pstate.get()
@@ -502,6 +533,26 @@ class MlpBlock(nn.Module):
         setattr(self, f"wi_{i}", DenseGeneral(emb_dim, intermediate_dim, ("embed", "mlp"), init,
                                               dtype, 1, device))
     self.wo = DenseGeneral(intermediate_dim, emb_dim, ("mlp", "embed"), init, dtype, 0, device)
+
+  def forward_sp(self, h_sp: torch.Tensor, x_sp: torch.Tensor) -> torch.Tensor:
+    """Row-sharded form under tensor parallelism (no dropout): wi gathers the rows inside its
+    GEMM kernel, wo scatters its partial sums from its epilogue; returns this rank's rows of
+    the new residual stream."""
+    from t5x_b200.parallel import tp_fused
+    h_sp = h_sp.to(self.dtype)
+    if self.activations == ("gelu", "linear"):
+      g = tp_fused.all_gather_gated_gelu(h_sp, self.wi_0.kernel, self.wi_1.kernel)
+    elif len(self.activations) == 1:
+      (g,) = tp_fused.all_gather_linears(h_sp, [self.wi.kernel])
+      g = ref.ACTIVATIONS[self.activations[0]](g)
+    else:
+      hs = tp_fused.all_gather_linears(
+          h_sp, [getattr(self, f"wi_{i}").kernel for i in range(len(self.activations))])
+      g = None
+      for act, h in zip(self.activations, hs):
+        h = ref.ACTIVATIONS[act](h)
+        g = h if g is None else g * h
+    return tp_fused.linear_reduce_scatter(g, self.wo.kernel, x_sp)
 
   def forward(self, inputs: torch.Tensor, residual: Optional[torch.Tensor] = None,
               enable_dropout: bool = False) -> torch.Tensor:

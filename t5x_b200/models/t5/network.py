@@ -22,6 +22,7 @@ from t5x_b200.models.t5 import layers
 from t5x_b200.ops import functional as F
 from t5x_b200.ops import reference as ref
 from t5x_b200.parallel import state as pstate
+from t5x_b200.parallel import tp_fused
 from t5x_b200.parallel import tp
 
 
@@ -86,6 +87,24 @@ class EncoderLayer(nn.Module):
     else:
       x = self.mlp(h, residual=x)
     return x
+
+  def forward_sp(self, x_sp, batch, length, *, bias_table, key_mask, segment_ids=None):
+    """Row-sharded residual stream under fused tensor parallelism (no dropout)."""
+    c = self.config
+    _mark_partial(self.pre_attention_layer_norm, self.pre_mlp_layer_norm)
+    h = self.pre_attention_layer_norm(x_sp)
+    x_sp = self.attention.forward_sp(
+        h, x_sp, batch, length, bias_table=bias_table, bidirectional=True,
+        num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance, key_mask=key_mask,
+        q_segment_ids=segment_ids, kv_segment_ids=segment_ids)
+    return self.mlp.forward_sp(self.pre_mlp_layer_norm(x_sp), x_sp)
+
+
+def _mark_partial(*norms) -> None:
+  """Norm scales applied to row-sharded activations get gradients that cover this rank's
+  rows only; the trainer sums them over the model axis."""
+  for n in norms:
+    n.scale.sp_partial_grad = True
 
 
 class DecoderLayer(nn.Module):
@@ -155,6 +174,25 @@ class DecoderLayer(nn.Module):
       x = self.mlp(h, residual=x)
     return x
 
+  def forward_sp(self, x_sp, encoded, batch, length, *, bias_table, decoder_key_mask,
+                 encoder_key_mask, decoder_segment_ids=None, encoder_segment_ids=None):
+    """Row-sharded residual stream under fused tensor parallelism (training, no dropout);
+    `encoded` is the replicated encoder output."""
+    c = self.config
+    _mark_partial(self.pre_self_attention_layer_norm, self.pre_cross_attention_layer_norm,
+                  self.pre_mlp_layer_norm)
+    h = self.pre_self_attention_layer_norm(x_sp)
+    x_sp = self.self_attention.forward_sp(
+        h, x_sp, batch, length, bias_table=bias_table, bidirectional=False,
+        num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance,
+        key_mask=decoder_key_mask, causal=True, q_segment_ids=decoder_segment_ids,
+        kv_segment_ids=decoder_segment_ids)
+    h = self.pre_cross_attention_layer_norm(x_sp)
+    x_sp = self.encoder_decoder_attention.forward_sp(
+        h, x_sp, batch, length, kv_full=encoded, key_mask=encoder_key_mask,
+        q_segment_ids=decoder_segment_ids, kv_segment_ids=encoder_segment_ids)
+    return self.mlp.forward_sp(self.pre_mlp_layer_norm(x_sp), x_sp)
+
 
 class Encoder(nn.Module):
   """Embedding (shared) -> dropout -> layers -> final norm -> dropout (network.py:182-219)."""
@@ -174,6 +212,16 @@ class Encoder(nn.Module):
     c = self.config
     key_mask = encoder_input_tokens > 0
     x = self._shared[0](encoder_input_tokens.long())
+    b, l, d = x.shape
+    if tp_fused.usable(x, b * l) and not (enable_dropout and c.dropout_rate > 0):
+      # row-sharded residual stream; collectives inside the GEMM kernels
+      x_sp = tp_fused.scatter_rows(x.reshape(b * l, d))
+      for i in range(c.num_encoder_layers):
+        x_sp = getattr(self, f"layers_{i}").forward_sp(
+            x_sp, b, l, bias_table=self.relpos_bias.rel_embedding, key_mask=key_mask,
+            segment_ids=encoder_segment_ids)
+      _mark_partial(self.encoder_norm)
+      return tp_fused.gather_rows(self.encoder_norm(x_sp), partial_grads=True).view(b, l, d)
     x = _dropout(x, c.dropout_rate, enable_dropout)
     for i in range(c.num_encoder_layers):
       x = getattr(self, f"layers_{i}")(x, bias_table=self.relpos_bias.rel_embedding,
@@ -217,6 +265,18 @@ class Decoder(nn.Module):
     """Final-norm hidden states [batch, len, emb] (what the logits projection consumes)."""
     c = self.config
     y = self._shared[0](decoder_input_tokens.long())
+    b, l, d = y.shape
+    if (tp_fused.usable(y, b * l) and not decode and cache is None and
+        not (enable_dropout and c.dropout_rate > 0)):
+      y_sp = tp_fused.scatter_rows(y.reshape(b * l, d))
+      for i in range(c.num_decoder_layers):
+        y_sp = getattr(self, f"layers_{i}").forward_sp(
+            y_sp, encoded, b, l, bias_table=self.relpos_bias.rel_embedding,
+            decoder_key_mask=decoder_key_mask, encoder_key_mask=encoder_key_mask,
+            decoder_segment_ids=decoder_segment_ids, encoder_segment_ids=encoder_segment_ids)
+      _mark_partial(self.decoder_norm)
+      # the vocabulary-parallel loss hands back a gradient already summed over the model axis
+      return tp_fused.gather_rows(self.decoder_norm(y_sp), partial_grads=False).view(b, l, d)
     y = _dropout(y, c.dropout_rate, enable_dropout)
     for i in range(c.num_decoder_layers):
       y = getattr(self, f"layers_{i}")(

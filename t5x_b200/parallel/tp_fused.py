@@ -1,0 +1,439 @@
+"""Tensor parallelism with the collectives inside the GEMM kernels.
+
+The reference shards `heads`, `mlp` and `vocab` over the 'model' mesh axis and lets the
+compiler place an all-reduce after every row-parallel projection
+(t5x/partitioning.py:564-573). Here the residual stream is instead kept row-sharded
+(each model rank holds `M / T` consecutive rows of the `[batch * length, d_model]`
+activations, "sequence parallel"), which turns every all-reduce into a reduce-scatter after
+the row-parallel projection and an all-gather before the next column-parallel one, and both
+run inside the tensor-core kernels:
+
+  all_gather_linears      the column-parallel projections (q/k/v, wi_0/wi_1, logits): the
+                          kernel pulls the other ranks' row blocks over NVLink into a local
+                          buffer while its tensor cores work on the blocks already there
+                          (`t5x_gemm_allgather_bf16`); the gathered rows are kept for the
+                          weight gradient.
+  linear_reduce_scatter   the row-parallel projections (attention out, wo): the epilogue of
+                          the GEMM stores each row of the partial product into the inbox of the
+                          rank that owns the row (`t5x_gemm_reducescatter_bf16`); the owner adds
+                          its `T` inbox slots in fp32.
+
+Backward of one is the other. Buffers that peers read or write live in one symmetric-memory
+arena per model group; flag barriers through its signal pads order the accesses: before a rank
+reuses bytes that peers read (or writes into a peer's inbox) every rank has finished the
+kernels that touched them.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from t5x_b200.parallel import state as pstate
+
+_ALIGN = 1024
+
+
+class _Block:
+  """A byte range of the arena; returns itself to the free list when dropped."""
+
+  def __init__(self, arena, offset: int, size: int):
+    self.arena, self.offset, self.size = arena, offset, size
+
+  def tensor(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
+    n = 1
+    for s in shape:
+      n *= int(s)
+    nbytes = n * torch.empty((), dtype=dtype).element_size()
+    assert nbytes <= self.size
+    return self.arena.buf.tensor[self.offset:self.offset + nbytes].view(dtype).view(*shape)
+
+  def peer_ptrs(self, extra_bytes: int = 0) -> List[int]:
+    return [p + self.offset + extra_bytes for p in self.arena.buf.peer_ptrs]
+
+  def release(self) -> None:
+    if self.arena is not None:
+      self.arena._free(self.offset, self.size)
+      self.arena = None
+
+  def __del__(self):
+    self.release()
+
+
+class _Inbox:
+  """The reduce-scatter inbox as [T, M / T, N] bf16 on every rank."""
+
+  def __init__(self, arena, buf):
+    self.arena, self.buf = arena, buf
+
+  def tensor(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
+    n = 1
+    for s in shape:
+      n *= int(s)
+    return self.buf.tensor[:n * 2].view(dtype).view(*shape)
+
+  def peer_ptrs(self, extra_bytes: int = 0) -> List[int]:
+    return [p + extra_bytes for p in self.buf.peer_ptrs]
+
+
+class SymmetricArena:
+  """One symmetric allocation per model group with a first-fit allocator. Every rank runs the
+  same program, so every rank hands out the same offsets and a peer's copy of a block is at
+  the same offset of the peer's mapping."""
+
+  def __init__(self, nbytes: int, group):
+    from t5x_b200.ops import comm
+    self.buf = comm.SymmetricBuffer(int(nbytes), torch.uint8, group)
+    self.rank, self.world = self.buf.rank, self.buf.world
+    self.free = [(0, int(nbytes))]
+    self.flags = torch.zeros(64, dtype=torch.int32, device=self.buf.tensor.device)
+    # True while a kernel that reads peers' memory has been enqueued since the last barrier:
+    # the next reuse of arena bytes must wait for every rank to get past it.
+    self.dirty = False
+    # The inbox of the reduce-scatter kernels is a buffer of its own (peers write it, only
+    # this rank reads it). True while this rank's sum over it is not yet ordered before the
+    # peers' next writes by a barrier.
+    self._inbox = None
+    self.inbox_busy = False
+    self._group = group
+
+  def alloc(self, nbytes: int) -> _Block:
+    size = -(-int(nbytes) // _ALIGN) * _ALIGN
+    for i, (off, sz) in enumerate(self.free):
+      if sz >= size:
+        if sz == size:
+          del self.free[i]
+        else:
+          self.free[i] = (off + size, sz - size)
+        return _Block(self, off, size)
+    raise RuntimeError(
+        f"tensor-parallel arena exhausted ({size} bytes wanted); raise T5X_B200_TP_ARENA_GB")
+
+  def _free(self, offset: int, size: int) -> None:
+    self.free.append((offset, size))
+    self.free.sort()
+    merged = []
+    for off, sz in self.free:
+      if merged and merged[-1][0] + merged[-1][1] == off:
+        merged[-1] = (merged[-1][0], merged[-1][1] + sz)
+      else:
+        merged.append((off, sz))
+    self.free = merged
+
+  def inbox(self, nbytes: int) -> "_Inbox":
+    if self._inbox is None or self._inbox.tensor.numel() < nbytes:
+      from t5x_b200.ops import comm
+      self.barrier()  # nobody is still writing the buffer being replaced
+      self._inbox = comm.SymmetricBuffer(int(nbytes), torch.uint8, self._group)
+    return _Inbox(self, self._inbox)
+
+  def barrier(self) -> None:
+    self.buf.barrier(channel=0)
+    self.dirty = False
+    self.inbox_busy = False
+
+  def settle(self) -> None:
+    """Barrier only if a peer-touching kernel is still unordered against what comes next."""
+    if self.dirty:
+      self.barrier()
+
+
+_ARENA: Optional[SymmetricArena] = None
+
+
+def arena() -> SymmetricArena:
+  global _ARENA
+  if _ARENA is None:
+    st = pstate.get()
+    gb = float(os.environ.get("T5X_B200_TP_ARENA_GB", "12"))
+    _ARENA = SymmetricArena(int(gb * (1 << 30)), st.model_group)
+  return _ARENA
+
+
+def enabled() -> bool:
+  """Fused tensor-parallel kernels run on GPUs when the model axis has more than one rank
+  (`T5X_B200_TP_FUSED=0` keeps the all-reduce form of `t5x_b200.parallel.tp`)."""
+  st = pstate.get()
+  return (st.model_size > 1 and st.device.type == "cuda" and dist.is_initialized() and
+          os.environ.get("T5X_B200_TP_FUSED", "1") != "0")
+
+
+# ---- kernel wrappers ----------------------------------------------------------------------
+def _native():
+  from t5x_b200.ops import native
+  import ctypes
+  if not getattr(_native, "_registered", False):
+    vp, ci, ll = native.c_void_p, native.c_int, native.c_ll
+    pp = ctypes.POINTER(vp)
+    native.register_signature(
+        "t5x_gemm_allgather_bf16",
+        [vp, pp, ci, ci, ci, vp, vp, vp, vp, ci, ci, ci, ll, ll, ci, ci, vp, vp, ll, vp])
+    native.register_signature(
+        "t5x_gemm_reducescatter_bf16",
+        [vp, vp, pp, ci, ci, ci, ci, ci, ci, ll, ll, ll, ci, ci, vp, ll, vp])
+    _native._registered = True
+  return native
+
+
+def _ptr_array(ptrs: Sequence[int]):
+  from t5x_b200.ops import comm
+  return comm._ptr_array(ptrs)
+
+
+def _b_layout(b: torch.Tensor):
+  """(mn_major, ld) of b as the [K, N] operand of the kernel."""
+  if b.stride(-2) == 1:
+    return 0, b.stride(-1)
+  if b.stride(-1) == 1:
+    return 1, b.stride(-2)
+  raise ValueError(f"b with strides {b.stride()} is neither row- nor column-major")
+
+
+def gemm_allgather(block: _Block, M: int, K: int, b: torch.Tensor, *,
+                   b2: Optional[torch.Tensor] = None, save_h: Optional[torch.Tensor] = None
+                   ) -> torch.Tensor:
+  """C [M, N] = A @ b (or gelu(A @ b) * (A @ b2)), where A [M, K] is `block` of the arena on
+  every rank and only this rank's row block of it is filled on entry; the rest arrives from
+  the peers inside the kernel. On return (in stream order) `block` holds all of A."""
+  native = _native()
+  ar = block.arena
+  N = b.shape[1]
+  b_mn, ldb = _b_layout(b)
+  out = torch.empty((M, N), dtype=torch.bfloat16, device=b.device)
+  h0 = h1 = ldh = 0
+  if b2 is not None:
+    assert b2.stride() == b.stride() and b2.shape == b.shape
+    if save_h is not None:
+      h0 = save_h.data_ptr()
+      h1 = h0 + N * 2
+      ldh = save_h.stride(0)
+  a = block.tensor((M, K))
+  native._check(native.lib().t5x_gemm_allgather_bf16(
+      a.data_ptr(), _ptr_array(block.peer_ptrs()), ar.world, ar.rank, M // ar.world,
+      ar.flags.data_ptr(), b.data_ptr(), native.ptr(b2), out.data_ptr(), M, N, K, ldb,
+      out.stride(0), b_mn, 1 if b2 is not None else 0, h0, h1, ldh, native.stream_ptr()),
+      "gemm_allgather")
+  ar.dirty = True
+  return out
+
+
+def gemm_reducescatter(a: torch.Tensor, b: torch.Tensor, inbox: _Inbox, *,
+                       residual: Optional[torch.Tensor] = None) -> None:
+  """Stores the bf16 partial product a [M, K] @ b [K, N] (+ residual [M, N]) of this rank
+  into slot `rank` of the owners' inboxes (`inbox`: [T, M / T, N] bf16 on every rank)."""
+  native = _native()
+  ar = inbox.arena
+  M, K = a.shape
+  N = b.shape[1]
+  a_mn, lda, _ = native._mat_layout(a, M, K)
+  b_mn, ldb = _b_layout(b)
+  rows = M // ar.world
+  slot = ar.rank * rows * N * 2
+  r_ptr = ldr = 0
+  if residual is not None:
+    assert residual.dtype == torch.bfloat16 and residual.stride(1) == 1
+    r_ptr, ldr = residual.data_ptr(), residual.stride(0)
+  native._check(native.lib().t5x_gemm_reducescatter_bf16(
+      a.data_ptr(), b.data_ptr(), _ptr_array(inbox.peer_ptrs(slot)), ar.world, ar.rank, rows, M,
+      N, K, lda, ldb, N, a_mn, b_mn, r_ptr, ldr, native.stream_ptr()), "gemm_reducescatter")
+
+
+# ---- building blocks ----------------------------------------------------------------------
+def _gather_block(rows: torch.Tensor) -> _Block:
+  """An arena block shaped [M, K] whose block of this rank holds `rows` ([M / T, K]), with
+  every rank past the point where its own rows are in place."""
+  ar = arena()
+  m, k = rows.shape
+  ar.settle()  # peers may still be reading the bytes this block reuses
+  blk = ar.alloc(m * ar.world * k * 2)
+  blk.tensor((m * ar.world, k))[ar.rank * m:(ar.rank + 1) * m].copy_(rows)
+  ar.barrier()
+  return blk
+
+
+def _reduce_scatter(a: torch.Tensor, b: torch.Tensor, residual: Optional[torch.Tensor] = None
+                    ) -> torch.Tensor:
+  """fp32 [M / T, N]: this rank's rows of the sum over ranks of a @ b (+ residual)."""
+  ar = arena()
+  M, N = a.shape[0], b.shape[1]
+  m = M // ar.world
+  inbox = ar.inbox(M * N * 2)
+  if ar.inbox_busy:
+    ar.barrier()  # every rank has finished summing what the inbox held before
+  gemm_reducescatter(a, b, inbox, residual=residual)
+  ar.barrier()  # every rank's rows have landed
+  out = torch.sum(inbox.tensor((ar.world, m, N)), dim=0, dtype=torch.float32)
+  ar.inbox_busy = True
+  return out
+
+
+def _weight2d(w: torch.Tensor, k: int) -> torch.Tensor:
+  from t5x_b200.ops import functional as F
+  return F.compute_weight(w, torch.bfloat16).reshape(k, -1)
+
+
+class _AllGatherLinearsFn(torch.autograd.Function):
+  """(h_sp [M/T, K]; W_0.. [K, N_i]) -> y_i [M, N_i] = allgather(h_sp) @ W_i. With `gated`,
+  the single output is gelu(A @ W_0) * (A @ W_1)."""
+
+  @staticmethod
+  def forward(ctx, h_sp, gated, *weights):
+    from t5x_b200.ops import native
+    ar = arena()
+    m, k = h_sp.shape
+    M = m * ar.world
+    blk = _gather_block(h_sp)
+    ws = [_weight2d(w, k) for w in weights]
+    ctx.h = None
+    if gated:
+      ctx.h = torch.empty((M, 2 * ws[0].shape[1]), dtype=torch.bfloat16, device=h_sp.device)
+      outs = [gemm_allgather(blk, M, k, ws[0], b2=ws[1], save_h=ctx.h)]
+    else:
+      outs = [gemm_allgather(blk, M, k, ws[0])]
+      a_full = blk.tensor((M, k))
+      outs += [native.gemm(a_full, w) for w in ws[1:]]
+    ctx.blk, ctx.weights, ctx.gated, ctx.shape = blk, weights, gated, (M, k)
+    return tuple(outs)
+
+  @staticmethod
+  def backward(ctx, *douts):
+    from t5x_b200.ops import functional as F, native
+    M, k = ctx.shape
+    blk, weights = ctx.blk, ctx.weights
+    a_full = blk.tensor((M, k))
+    ws = [_weight2d(w, k) for w in weights]
+    if ctx.gated:
+      dff = ws[0].shape[1]
+      dh = ctx.h
+      native.gated_gelu_bwd_(douts[0].reshape(M, dff).contiguous(), dh)
+      dys = [dh[:, :dff], dh[:, dff:]]
+    else:
+      dys = [None if d is None else d.reshape(M, -1).contiguous() for d in douts]
+    dws = []
+    for i, (w, dy) in enumerate(zip(weights, dys)):
+      need = ctx.needs_input_grad[2 + i] and dy is not None
+      dws.append(F._accumulate_wgrad(w, a_full.t(), dy) if need else None)
+    blk.release()
+    ctx.blk = ctx.h = None
+    dh_sp = None
+    if ctx.needs_input_grad[0]:
+      live = [(dy, w) for dy, w in zip(dys, ws) if dy is not None]
+      partial = None
+      for dy, w in live[:-1]:
+        if partial is None:
+          partial = native.gemm(dy, w.t())
+        else:
+          native.gemm(dy, w.t(), out=partial, accumulate=True)
+      dy, w = live[-1]
+      dh_sp = _reduce_scatter(dy, w.t(), residual=partial).to(torch.bfloat16)
+    return (dh_sp, None) + tuple(dws)
+
+
+class _LinearReduceScatterFn(torch.autograd.Function):
+  """(a [M, K_local]; W [K_local, N]; residual_sp [M/T, N]) -> this rank's rows of
+  sum_ranks(a @ W) + residual_sp."""
+
+  @staticmethod
+  def forward(ctx, a, weight, residual_sp):
+    k = a.shape[-1]
+    a2 = a.reshape(-1, k)
+    w2 = _weight2d(weight, k)
+    y = _reduce_scatter(a2, w2)
+    if residual_sp is not None:
+      y += residual_sp
+    ctx.save_for_backward(a, weight)
+    ctx.has_res = residual_sp is not None
+    return y.to(torch.bfloat16)
+
+  @staticmethod
+  def backward(ctx, dy_sp):
+    from t5x_b200.ops import functional as F
+    a, weight = ctx.saved_tensors
+    k = a.shape[-1]
+    a2 = a.reshape(-1, k)
+    w2 = _weight2d(weight, k)
+    M, N = a2.shape[0], w2.shape[1]
+    blk = _gather_block(dy_sp.contiguous())
+    da = gemm_allgather(blk, M, N, w2.t()).view(a.shape)
+    dw = None
+    if ctx.needs_input_grad[1]:
+      dw = F._accumulate_wgrad(weight, a2.t(), blk.tensor((M, N)))
+    blk.release()
+    return da, dw, (dy_sp if ctx.has_res else None)
+
+
+def all_gather_linears(h_sp: torch.Tensor, weights: Sequence[torch.Tensor]) -> List[torch.Tensor]:
+  """Column-parallel projections of row-sharded activations: [allgather(h_sp) @ W for W]."""
+  return list(_AllGatherLinearsFn.apply(h_sp.contiguous(), False, *weights))
+
+
+def all_gather_gated_gelu(h_sp: torch.Tensor, wi_0: torch.Tensor, wi_1: torch.Tensor
+                          ) -> torch.Tensor:
+  """gelu(A @ wi_0) * (A @ wi_1) with A = allgather(h_sp)."""
+  return _AllGatherLinearsFn.apply(h_sp.contiguous(), True, wi_0, wi_1)[0]
+
+
+def linear_reduce_scatter(a: torch.Tensor, weight: torch.Tensor,
+                          residual_sp: Optional[torch.Tensor] = None) -> torch.Tensor:
+  """Row-parallel projection: this rank's rows of sum_ranks(a @ W) (+ residual_sp)."""
+  return _LinearReduceScatterFn.apply(a, weight, residual_sp)
+
+
+# ---- entering and leaving the row-sharded region (NCCL; once per layer stack) --------------
+class _ScatterRowsFn(torch.autograd.Function):
+  """Replicated [M, d] -> this rank's rows. Backward all-gathers the row gradients."""
+
+  @staticmethod
+  def forward(ctx, x):
+    st = pstate.get()
+    m = x.shape[0] // st.model_size
+    return x[st.model_rank * m:(st.model_rank + 1) * m].contiguous()
+
+  @staticmethod
+  def backward(ctx, g):
+    st = pstate.get()
+    out = torch.empty((g.shape[0] * st.model_size,) + tuple(g.shape[1:]), dtype=g.dtype,
+                      device=g.device)
+    dist.all_gather_into_tensor(out, g.contiguous(), group=st.model_group)
+    return out
+
+
+class _GatherRowsFn(torch.autograd.Function):
+  """Row-sharded [M/T, d] -> replicated [M, d]. With `partial_grads` the consumers are
+  model-sharded and leave partial sums as gradients, which backward reduce-scatters;
+  otherwise the gradient arrives already summed and backward keeps this rank's rows."""
+
+  @staticmethod
+  def forward(ctx, x_sp, partial_grads):
+    st = pstate.get()
+    ctx.partial_grads = partial_grads
+    out = torch.empty((x_sp.shape[0] * st.model_size,) + tuple(x_sp.shape[1:]), dtype=x_sp.dtype,
+                      device=x_sp.device)
+    dist.all_gather_into_tensor(out, x_sp.contiguous(), group=st.model_group)
+    return out
+
+  @staticmethod
+  def backward(ctx, g):
+    st = pstate.get()
+    m = g.shape[0] // st.model_size
+    if not ctx.partial_grads:
+      return g[st.model_rank * m:(st.model_rank + 1) * m].contiguous(), None
+    out = torch.empty((m,) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
+    dist.reduce_scatter_tensor(out, g.contiguous(), group=st.model_group)
+    return out, None
+
+
+def scatter_rows(x: torch.Tensor) -> torch.Tensor:
+  return _ScatterRowsFn.apply(x)
+
+
+def gather_rows(x_sp: torch.Tensor, partial_grads: bool) -> torch.Tensor:
+  return _GatherRowsFn.apply(x_sp, partial_grads)
+
+
+def usable(x: torch.Tensor, rows: int) -> bool:
+  """The fused path covers bf16 CUDA activations whose rows divide evenly over the ranks."""
+  st = pstate.get()
+  return (enabled() and x.is_cuda and x.dtype == torch.bfloat16 and rows % st.model_size == 0)

@@ -276,6 +276,25 @@ def _fold_autograd_grads(params_flat) -> None:
     p.grad = None
 
 
+def reduce_partial_gradients_over_model_axis(grads_flat, params_flat) -> None:
+  """Replicated parameters applied to row-sharded activations (the norm scales of the fused
+  tensor-parallel path, marked `sp_partial_grad`) hold the gradient of this rank's rows only:
+  sums them over the model axis in one all-reduce."""
+  st = pstate.get()
+  if st.model_size <= 1 or st.model_group is None:
+    return
+  keys = [k for k, p in params_flat.items() if getattr(p, "sp_partial_grad", False)]
+  if not keys:
+    return
+  flat = torch.cat([grads_flat[k].reshape(-1) for k in keys])
+  dist.all_reduce(flat, group=st.model_group)
+  off = 0
+  for k in keys:
+    n = grads_flat[k].numel()
+    grads_flat[k].copy_(flat[off:off + n].view_as(grads_flat[k]))
+    off += n
+
+
 def reduce_gradients_over_data_axis(grads_flat: Mapping[str, torch.Tensor], params_flat) -> None:
   """Sum of gradients over data-parallel replicas (losses are sums, not means, so the global
   gradient is the sum; t5x/trainer.py:815-828). Expert-sharded parameters are reduced over
@@ -337,6 +356,7 @@ def accumulate_grads_microbatched(model, train_state, batch: BatchType, dropout_
     _fold_autograd_grads(flat)
     metrics = m if metrics is None else merge_metrics(metrics, m)
   grads = _collect_grads(flat)
+  reduce_partial_gradients_over_model_axis(grads, flat)
   reduce_gradients_over_data_axis(grads, flat)
   metrics = reduce_metrics_over_data_axis(metrics)
   return tree_utils.unflatten_dict(grads), metrics, None

@@ -150,7 +150,86 @@ def case_moe(out):
              "wi_first": g(wi).reshape(-1)[:6].tolist()}, out)
 
 
-CASES = {"collectives": case_collectives, "train": case_train, "moe": case_moe}
+def _setup_tp():
+  local = int(os.environ.get("LOCAL_RANK", "0"))
+  torch.cuda.set_device(local)
+  pstate.init_distributed("nccl")
+  return pstate.setup_mesh(model_size=int(os.environ["WORLD_SIZE"]))
+
+
+def case_tp_ops(out):
+  """all-gather -> GEMM and GEMM -> reduce-scatter (forward and backward) against fp32
+  PyTorch on the gathered operands."""
+  from t5x_b200.ops import native
+  from t5x_b200.parallel import tp_fused
+  st = _setup_tp()
+  T, r = st.model_size, st.model_rank
+  res = {}
+  for name, (m, k, n) in {"even": (512, 256, 384), "ragged": (228, 192, 320)}.items():
+    g = torch.Generator(device="cuda").manual_seed(50)
+    h_all = torch.randn(T * m, k, device="cuda", generator=g).to(torch.bfloat16)
+    ws = [(torch.randn(k, n, device="cuda", generator=g) * 0.05) for _ in range(3)]
+    wo = torch.randn(T * n, k, device="cuda", generator=g) * 0.05     # row-parallel [T*n, k]
+    dy_all = torch.randn(T * m, k, device="cuda", generator=g).to(torch.bfloat16)
+    res_sp = torch.randn(T * m, k, device="cuda", generator=g).to(torch.bfloat16)
+    sl = slice(r * m, (r + 1) * m)
+    # --- fused: y = RS( gated(AG(h) @ w0, @ w1) ... ) chain: q = AG(h)@w2 ; z = RS(q @ wo_r) + res
+    h_sp = h_all[sl].clone().requires_grad_(True)
+    wp = [torch.nn.Parameter(w.clone()) for w in ws]
+    wo_r = torch.nn.Parameter(wo[r * n:(r + 1) * n].clone())
+    q0, q1, q2 = tp_fused.all_gather_linears(h_sp, wp)
+    gg = tp_fused.all_gather_gated_gelu(h_sp, wp[0], wp[1])
+    mix = (q0 + q1 * 0.5 + q2 * 0.25 + gg).to(torch.bfloat16)
+    z = tp_fused.linear_reduce_scatter(mix, wo_r, res_sp[sl])
+    z.backward(dy_all[sl])
+    native.check_status()
+    for w in wp:  # the same weights on every rank here: total gradient = sum of the ranks'
+      dist.all_reduce(w.grad)
+    # --- reference (fp32, whole problem on every rank)
+    hf = h_all.float().requires_grad_(True)
+    wf = [w.to(torch.bfloat16).float().requires_grad_(True) for w in ws]
+    wof = wo.to(torch.bfloat16).float().requires_grad_(True)
+    gelu = lambda t: 0.5 * t * (1 + torch.tanh(0.7978845608028654 * (t + 0.044715 * t ** 3)))
+    # every rank has the same column-parallel weights here, so the sum over ranks of the
+    # row-parallel products is mix @ sum_r wo_r
+    mixf = hf @ wf[0] + 0.5 * (hf @ wf[1]) + 0.25 * (hf @ wf[2]) + gelu(hf @ wf[0]) * (hf @ wf[1])
+    zf = sum(mixf @ wof[i * n:(i + 1) * n] for i in range(T)) + res_sp.float()
+    zf.backward(dy_all.float())
+    scale = float(zf.abs().max())
+    res[name] = {
+        "z": float((z.float() - zf[sl]).abs().max()) / scale,
+        "dh": float((h_sp.grad.float() - hf.grad[sl]).abs().max()) / float(hf.grad.abs().max()),
+        "dw0": float((wp[0].grad.float() - wf[0].grad).abs().max()) / float(wf[0].grad.abs().max()),
+        "dw2": float((wp[2].grad.float() - wf[2].grad).abs().max()) / float(wf[2].grad.abs().max()),
+        "dwo": float((wo_r.grad.float() - wof.grad[r * n:(r + 1) * n]).abs().max()) /
+               float(wof.grad.abs().max()),
+    }
+  torch.cuda.synchronize()
+  json.dump(res, out)
+
+
+def case_tp_train(out):
+  """Three train steps of a small tensor-parallel model; the parent compares the fused
+  kernels with the all-reduce form (T5X_B200_TP_FUSED=0)."""
+  from t5x_b200.ops import native
+  from t5x_b200.parallel import tp_fused
+  st = _setup_tp()
+  trainer, module = _tiny_trainer()
+  batches = _batches(0, 1, 3)   # model ranks all see the same batch
+  summary = trainer.train(iter(batches), 3, start_step=0).result()
+  native.check_status()
+  torch.cuda.synchronize()
+  flat = torch.cat([p.detach().float().reshape(-1) for p in module.parameters()])
+  json.dump({"loss": float(summary["loss"].value), "fused": tp_fused.enabled(),
+             "param_abs": float(flat.double().abs().sum()),
+             "first": flat[:8].tolist(),
+             "norm": module.encoder.layers_1.pre_mlp_layer_norm.scale.detach().float()[:6].tolist()},
+            out)
+  trainer.close()
+
+
+CASES = {"collectives": case_collectives, "train": case_train, "moe": case_moe,
+         "tp_ops": case_tp_ops, "tp_train": case_tp_train}
 
 if __name__ == "__main__":
   case, out_dir = sys.argv[1], sys.argv[2]

@@ -85,3 +85,25 @@ def test_moe_fused_exchange_matches_all_to_all(tmp_path):
       assert a[key] == pytest.approx(b[key], rel=2e-2), key
     for x, y in zip(a["wi_first"], b["wi_first"]):
       assert x == pytest.approx(y, rel=5e-2, abs=1e-3)
+
+
+def test_fused_tensor_parallel_gemms(tmp_path):
+  _need_two()
+  for res in _run_ranks("tp_ops", tmp_path):
+    for name, errs in res.items():
+      for what, e in errs.items():
+        assert e < 3e-2, (name, what, e)
+
+
+def test_fused_tensor_parallel_training_matches_all_reduce(tmp_path):
+  _need_two()
+  fused = _run_ranks("tp_train", tmp_path / "f")
+  plain = _run_ranks("tp_train", tmp_path / "p", env={"T5X_B200_TP_FUSED": "0"})
+  assert all(r["fused"] for r in fused) and not any(r["fused"] for r in plain)
+  a, b = fused[0], plain[0]
+  assert fused[0]["loss"] == pytest.approx(fused[1]["loss"], rel=1e-6)
+  assert a["loss"] == pytest.approx(b["loss"], rel=5e-3)
+  for x, y in zip(a["norm"], b["norm"]):
+    assert x == pytest.approx(y, rel=1e-2, abs=1e-3)
+  for x, y in zip(a["first"], b["first"]):
+    assert x == pytest.approx(y, rel=2e-2, abs=2e-3)
