@@ -184,7 +184,9 @@ def main() -> None:
   model = models.EncoderDecoderModel(module, vocab, vocab, opt, z_loss=1e-4,
                                      loss_normalizing_factor=None)
   state = ts_lib.FlaxOptimTrainState.create(opt, model.get_initial_variables(None, None))
-  n_micro = args.microbatches or default_microbatches(args.model, world)
+  # tensor-parallel ranks all work on the same microbatch: 32 sequences at a time for XXL
+  n_micro = args.microbatches or (default_microbatches(args.model, 2) if args.parallelism == "tp"
+                                  else default_microbatches(args.model, world))
   lr_fn = schedules.create_learning_rate_scheduler("constant * rsqrt_decay", 1.0, 10000)
   trainer = trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, n_micro)
   n_params = sum(int(np.prod(getattr(p, "global_shape", p.shape))) for p in module.parameters())

@@ -436,3 +436,63 @@ T5X_API int t5x_f32_to_bf16_residual(const void* src, const void* residual, void
   if (e != cudaSuccess) return t5x::set_error("f32_to_bf16_residual: %s", cudaGetErrorString(e));
   return 0;
 }
+
+// dst[i] = bf16(sum over s of slots[s * n + i] (+ residual[i])) with fp32 accumulation: the
+// owner's side of the tensor-parallel reduce-scatter (`slots` is its inbox, one slot per rank).
+namespace t5x {
+__global__ void __launch_bounds__(256)
+    slot_sum_bf16_kernel(const __nv_bfloat16* __restrict__ slots, int num_slots, long long n8,
+                         const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ dst) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += stride) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (res != nullptr) {
+      const uint4 u = reinterpret_cast<const uint4*>(res)[i];
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p[j]);
+        acc[2 * j] = f.x;
+        acc[2 * j + 1] = f.y;
+      }
+    }
+    for (int s = 0; s < num_slots; ++s) {
+      const uint4 u = reinterpret_cast<const uint4*>(slots)[s * n8 + i];
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    reinterpret_cast<uint4*>(dst)[i] = o;
+  }
+}
+}  // namespace t5x
+
+// n (elements per slot) must be a multiple of 8; pointers 16-byte aligned.
+T5X_API int t5x_slot_sum_bf16(const void* slots, int num_slots, long long n, const void* residual,
+                              void* dst, void* stream) {
+  using namespace t5x;
+  if (n <= 0) return 0;
+  if (n % 8 || num_slots < 1) return set_error("slot_sum_bf16: n must be a multiple of 8");
+  const long long n8 = n / 8;
+  long long blocks = (n8 + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms()) * 8;
+  if (blocks > cap) blocks = cap;
+  slot_sum_bf16_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(slots), num_slots, n8,
+      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(dst));
+  count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("slot_sum_bf16: %s", cudaGetErrorString(e));
+  return 0;
+}

@@ -111,18 +111,12 @@ __device__ __forceinline__ void gemm_tile_coords(const GemmParams& p, int tile, 
 // Epilogue of one 128-row accumulator tile held in TMEM columns [t_cols, t_cols + BN): the
 // calling warp owns lane quarter q (rows m0 + 32q .. +31), `c_vec_ok` says whether 16-byte
 // stores to C are legal.
-template <int BN, int EPI, bool RS = false>
+template <int BN, int EPI>
 __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t t_row, int m0,
                                                    int n0, int b, int q, int lane,
-                                                   bool c_vec_ok, const GemmTp* tp = nullptr) {
+                                                   bool c_vec_ok) {
   const int row = m0 + q * 32 + lane;
   const bool row_ok = row < p.M;
-  // reduce-scatter: this row lives in its owner's inbox (peer memory unless the owner is us)
-  __nv_bfloat16* rs_row = nullptr;
-  if (RS && row_ok) {
-    const int owner = row / tp->rows_per_rank;
-    rs_row = tp->c_dst[owner] + static_cast<long long>(row - owner * tp->rows_per_rank) * p.ldc;
-  }
 
   if (EPI == kEpiGatedGelu) {
     constexpr int kHalf = BN / 2;
@@ -201,8 +195,6 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
                 out[i] = p.accumulate ? out[i] + v[i] : v[i];
             }
           }
-        } else if (RS) {
-          store_row_bf16(rs_row + col, v, n_valid, c_vec_ok);
         } else {
           __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.c_batch_stride +
                                static_cast<long long>(row) * p.ldc + col;
@@ -216,6 +208,77 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
         }
       }
     }
+  }
+}
+
+// Reduce-scatter epilogue of one 128-row accumulator tile: each row of the bf16 partial product
+// (+ local residual) goes to the inbox of the rank that owns the row, mostly peer memory. A
+// lane holds one row of the accumulator, so storing straight from registers would send 16-byte
+// pieces of 32 different rows per instruction; over NVLink that is one small packet each.
+// Instead 128 columns at a time are staged in shared memory (`stage`: 8 KB of this warp, 16-byte
+// chunks XOR-swizzled by row so that neither side has bank conflicts) and written out as
+// 256-byte row segments, two rows per warp instruction. Requires N % 8 == 0 and ldc % 8 == 0.
+constexpr int kRsGroupCols = 128;
+constexpr int kRsStageBytesPerWarp = 32 * kRsGroupCols * 2;
+template <int BN, int EPI>
+__device__ __forceinline__ void gemm_epilogue_tile_rs(const GemmParams& p, const GemmTp& tp,
+                                                      uint32_t t_row, int m0, int n0, int q,
+                                                      int lane, uint8_t* stage) {
+  const int row = m0 + q * 32 + lane;
+  const bool row_ok = row < p.M;
+#pragma unroll 1
+  for (int g = 0; g < BN / kRsGroupCols; ++g) {
+    const int gcol = n0 + g * kRsGroupCols;
+#pragma unroll 1
+    for (int c = 0; c < kRsGroupCols / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld32(t_row + g * kRsGroupCols + c * 32, r);
+      tmem_ld_wait();
+      const int col = gcol + c * 32;
+      const int n_valid = p.N - col;
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+      if (EPI == kEpiResidual && row_ok && n_valid > 0) {
+        float rr[32];
+        const bool rv = (p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+        load_row_bf16(p.R + static_cast<long long>(row) * p.ldr + col, rr, n_valid, rv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += rr[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {  // four 16-byte chunks of this lane's row
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[i * 8 + 0], v[i * 8 + 1]);
+        __nv_bfloat162 p1 = __floats2bfloat162_rn(v[i * 8 + 2], v[i * 8 + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[i * 8 + 4], v[i * 8 + 5]);
+        __nv_bfloat162 p3 = __floats2bfloat162_rn(v[i * 8 + 6], v[i * 8 + 7]);
+        uint4 u;
+        u.x = *reinterpret_cast<uint32_t*>(&p0);
+        u.y = *reinterpret_cast<uint32_t*>(&p1);
+        u.z = *reinterpret_cast<uint32_t*>(&p2);
+        u.w = *reinterpret_cast<uint32_t*>(&p3);
+        const int chunk = (c * 4 + i) ^ (lane & 15);
+        *reinterpret_cast<uint4*>(stage + lane * (kRsGroupCols * 2) + chunk * 16) = u;
+      }
+    }
+    __syncwarp();
+    // 16 instructions, each: lanes 0-15 one row, lanes 16-31 the next, 16 bytes per lane
+    const int chunk = lane & 15;
+    const int ccol = gcol + chunk * 8;
+#pragma unroll 4
+    for (int it = 0; it < 16; ++it) {
+      const int rloc = it * 2 + (lane >> 4);
+      const int grow = m0 + q * 32 + rloc;
+      if (grow < p.M && ccol < p.N) {
+        const uint4 u = *reinterpret_cast<const uint4*>(stage + rloc * (kRsGroupCols * 2) +
+                                                        ((chunk ^ (rloc & 15)) * 16));
+        const int owner = grow / tp.rows_per_rank;
+        __nv_bfloat16* dst = tp.c_dst[owner] +
+                             static_cast<long long>(grow - owner * tp.rows_per_rank) * p.ldc + ccol;
+        *reinterpret_cast<uint4*>(dst) = u;
+      }
+    }
+    __syncwarp();
   }
 }
 

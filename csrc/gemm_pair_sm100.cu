@@ -48,8 +48,11 @@ template <int MODE>
 constexpr int pair_threads() { return MODE == kTpAllGather ? kGemmThreads + 32 : kGemmThreads; }
 template <int MODE>
 constexpr int pair_smem() {
-  return MODE == kTpAllGather ? kPairSmemTotal + kTpStageBytes : kPairSmemTotal;
+  return MODE == kTpAllGather       ? kPairSmemTotal + kTpStageBytes
+         : MODE == kTpReduceScatter ? kPairSmemTotal + 4 * kRsStageBytesPerWarp
+                                    : kPairSmemTotal;
 }
+static_assert(kPairSmemTotal + 4 * kRsStageBytesPerWarp <= 232448, "shared memory per CTA");
 
 template <int EPI, int MODE = kTpNone>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>(), 1)
@@ -322,8 +325,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
       }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      gemm_epilogue_tile<BN, EPI, MODE == kTpReduceScatter>(p, t_row, m0, n0, b, q, lane, c_vec_ok,
-                                                            &tp);
+      if (MODE == kTpReduceScatter)
+        gemm_epilogue_tile_rs<BN, EPI>(p, tp, t_row, m0, n0, q, lane,
+                                       staging + (warp - 2) * kRsStageBytesPerWarp);
+      else
+        gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(drained + acc * 8);

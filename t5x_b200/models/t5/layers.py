@@ -241,8 +241,8 @@ class LayerNorm(nn.Module):
     self.dtype = canonical_dtype(dtype)
     self.scale = param_with_axes((features,), ones_init, ("embed",), device=device)
 
-  def forward(self, x: torch.Tensor) -> torch.Tensor:
-    return F.rmsnorm(x.to(self.dtype), self.scale, self.epsilon)
+  def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return F.rmsnorm(x.to(self.dtype), self.scale, self.epsilon, out=out)
 
 
 class Embed(nn.Module):
@@ -430,7 +430,7 @@ class MultiHeadDotProductAttention(nn.Module):
     return self._project_out(x, b, lq, residual)
 
   def forward_sp(self, h_sp: torch.Tensor, x_sp: torch.Tensor, batch: int, lq: int, *,
-                 kv_full: Optional[torch.Tensor] = None, bias_table=None,
+                 kv_full: Optional[torch.Tensor] = None, h_block=None, bias_table=None,
                  bidirectional: bool = True, num_buckets: int = 32, max_distance: int = 128,
                  key_mask=None, causal: bool = False, q_segment_ids=None,
                  kv_segment_ids=None) -> torch.Tensor:
@@ -442,14 +442,14 @@ class MultiHeadDotProductAttention(nn.Module):
     [batch, lk, emb] encoder output."""
     from t5x_b200.parallel import tp_fused
     if self.scale_attn_logits:
-      h_sp = h_sp / math.sqrt(self.head_dim)
+      h_sp, h_block = h_sp / math.sqrt(self.head_dim), None
     hd = (self.local_heads, self.head_dim)
     if kv_full is None:
       q, k, v = tp_fused.all_gather_linears(
-          h_sp, [self.query.kernel, self.key.kernel, self.value.kernel])
+          h_sp, [self.query.kernel, self.key.kernel, self.value.kernel], block=h_block)
       lk = lq
     else:
-      (q,) = tp_fused.all_gather_linears(h_sp, [self.query.kernel])
+      (q,) = tp_fused.all_gather_linears(h_sp, [self.query.kernel], block=h_block)
       lk = kv_full.shape[1]
       k, v = self.key(kv_full), self.value(kv_full)
     q = q.view(batch, lq, *hd)
@@ -534,20 +534,20 @@ class MlpBlock(nn.Module):
                                               dtype, 1, device))
     self.wo = DenseGeneral(intermediate_dim, emb_dim, ("mlp", "embed"), init, dtype, 0, device)
 
-  def forward_sp(self, h_sp: torch.Tensor, x_sp: torch.Tensor) -> torch.Tensor:
+  def forward_sp(self, h_sp: torch.Tensor, x_sp: torch.Tensor, h_block=None) -> torch.Tensor:
     """Row-sharded form under tensor parallelism (no dropout): wi gathers the rows inside its
     GEMM kernel, wo scatters its partial sums from its epilogue; returns this rank's rows of
-    the new residual stream."""
+    the new residual stream. `h_block`: the arena block `h_sp` was written into, if any."""
     from t5x_b200.parallel import tp_fused
-    h_sp = h_sp.to(self.dtype)
     if self.activations == ("gelu", "linear"):
-      g = tp_fused.all_gather_gated_gelu(h_sp, self.wi_0.kernel, self.wi_1.kernel)
+      g = tp_fused.all_gather_gated_gelu(h_sp, self.wi_0.kernel, self.wi_1.kernel, block=h_block)
     elif len(self.activations) == 1:
-      (g,) = tp_fused.all_gather_linears(h_sp, [self.wi.kernel])
+      (g,) = tp_fused.all_gather_linears(h_sp, [self.wi.kernel], block=h_block)
       g = ref.ACTIVATIONS[self.activations[0]](g)
     else:
       hs = tp_fused.all_gather_linears(
-          h_sp, [getattr(self, f"wi_{i}").kernel for i in range(len(self.activations))])
+          h_sp, [getattr(self, f"wi_{i}").kernel for i in range(len(self.activations))],
+          block=h_block)
       g = None
       for act, h in zip(self.activations, hs):
         h = ref.ACTIVATIONS[act](h)

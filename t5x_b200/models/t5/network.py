@@ -92,12 +92,15 @@ class EncoderLayer(nn.Module):
     """Row-sharded residual stream under fused tensor parallelism (no dropout)."""
     c = self.config
     _mark_partial(self.pre_attention_layer_norm, self.pre_mlp_layer_norm)
-    h = self.pre_attention_layer_norm(x_sp)
+    # each norm writes straight into this rank's rows of the buffer the next GEMM gathers
+    blk, dst = tp_fused.rows_buffer(*x_sp.shape)
+    h = self.pre_attention_layer_norm(x_sp, out=dst)
     x_sp = self.attention.forward_sp(
-        h, x_sp, batch, length, bias_table=bias_table, bidirectional=True,
+        h, x_sp, batch, length, h_block=blk, bias_table=bias_table, bidirectional=True,
         num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance, key_mask=key_mask,
         q_segment_ids=segment_ids, kv_segment_ids=segment_ids)
-    return self.mlp.forward_sp(self.pre_mlp_layer_norm(x_sp), x_sp)
+    blk, dst = tp_fused.rows_buffer(*x_sp.shape)
+    return self.mlp.forward_sp(self.pre_mlp_layer_norm(x_sp, out=dst), x_sp, h_block=blk)
 
 
 def _mark_partial(*norms) -> None:
@@ -181,17 +184,20 @@ class DecoderLayer(nn.Module):
     c = self.config
     _mark_partial(self.pre_self_attention_layer_norm, self.pre_cross_attention_layer_norm,
                   self.pre_mlp_layer_norm)
-    h = self.pre_self_attention_layer_norm(x_sp)
+    blk, dst = tp_fused.rows_buffer(*x_sp.shape)
+    h = self.pre_self_attention_layer_norm(x_sp, out=dst)
     x_sp = self.self_attention.forward_sp(
-        h, x_sp, batch, length, bias_table=bias_table, bidirectional=False,
+        h, x_sp, batch, length, h_block=blk, bias_table=bias_table, bidirectional=False,
         num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance,
         key_mask=decoder_key_mask, causal=True, q_segment_ids=decoder_segment_ids,
         kv_segment_ids=decoder_segment_ids)
-    h = self.pre_cross_attention_layer_norm(x_sp)
+    blk, dst = tp_fused.rows_buffer(*x_sp.shape)
+    h = self.pre_cross_attention_layer_norm(x_sp, out=dst)
     x_sp = self.encoder_decoder_attention.forward_sp(
-        h, x_sp, batch, length, kv_full=encoded, key_mask=encoder_key_mask,
+        h, x_sp, batch, length, kv_full=encoded, h_block=blk, key_mask=encoder_key_mask,
         q_segment_ids=decoder_segment_ids, kv_segment_ids=encoder_segment_ids)
-    return self.mlp.forward_sp(self.pre_mlp_layer_norm(x_sp), x_sp)
+    blk, dst = tp_fused.rows_buffer(*x_sp.shape)
+    return self.mlp.forward_sp(self.pre_mlp_layer_norm(x_sp, out=dst), x_sp, h_block=blk)
 
 
 class Encoder(nn.Module):

@@ -129,9 +129,9 @@ def batched_linear(x: torch.Tensor, weight: torch.Tensor,
 class _RmsNormFn(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, x, scale, eps):
+  def forward(ctx, x, scale, eps, out=None):
     xc = x.contiguous()
-    y, rstd = native.rmsnorm_fwd(xc, scale.float(), eps)
+    y, rstd = native.rmsnorm_fwd(xc, scale.float(), eps, out=out)
     ctx.save_for_backward(xc, scale, rstd)
     return y
 
@@ -148,12 +148,14 @@ class _RmsNormFn(torch.autograd.Function):
       dscale_buf = torch.zeros_like(scale, dtype=torch.float32)
       ret = dscale_buf
     dx = native.rmsnorm_bwd(dy.contiguous(), x, scale.float(), rstd, None, dscale_buf)
-    return dx, ret, None
+    return dx, ret, None, None
 
 
-def rmsnorm(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+def rmsnorm(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+  """`out` (CUDA path only): a bf16 buffer of x's shape that receives the result."""
   if _native_ok(x):
-    return _RmsNormFn.apply(x, scale, eps)
+    return _RmsNormFn.apply(x, scale, eps, out)
   return ref.rmsnorm(x, scale, eps)
 
 

@@ -275,11 +275,14 @@ def gemm_set_pair_mode(mode: int) -> None:
   _check(l.t5x_gemm_set_pair_mode(mode), "gemm_set_pair_mode")
 
 
-def rmsnorm_fwd(x: torch.Tensor, scale: torch.Tensor, eps: float):
+def rmsnorm_fwd(x: torch.Tensor, scale: torch.Tensor, eps: float,
+                out: Optional[torch.Tensor] = None):
   d = x.shape[-1]
   x2 = x.reshape(-1, d)
   assert x2.is_contiguous() and x.dtype == torch.bfloat16 and scale.dtype == torch.float32
-  y = torch.empty_like(x2)
+  if out is not None:
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() == x2.numel()
+  y = torch.empty_like(x2) if out is None else out.view(x2.shape)
   rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
   _check(lib().t5x_rmsnorm_fwd(x2.data_ptr(), scale.data_ptr(), y.data_ptr(), rstd.data_ptr(),
                                x2.shape[0], d, eps, stream_ptr()), "rmsnorm_fwd")

@@ -48,7 +48,9 @@ class _Block:
       n *= int(s)
     nbytes = n * torch.empty((), dtype=dtype).element_size()
     assert nbytes <= self.size
-    return self.arena.buf.tensor[self.offset:self.offset + nbytes].view(dtype).view(*shape)
+    # `.data`: a tensor of its own for autograd's version counting (kernels and other views
+    # write the arena all the time)
+    return self.arena.buf.tensor[self.offset:self.offset + nbytes].view(dtype).view(*shape).data
 
   def peer_ptrs(self, extra_bytes: int = 0) -> List[int]:
     return [p + self.offset + extra_bytes for p in self.arena.buf.peer_ptrs]
@@ -72,7 +74,7 @@ class _Inbox:
     n = 1
     for s in shape:
       n *= int(s)
-    return self.buf.tensor[:n * 2].view(dtype).view(*shape)
+    return self.buf.tensor[:n * 2].view(dtype).view(*shape).data
 
   def peer_ptrs(self, extra_bytes: int = 0) -> List[int]:
     return [p + extra_bytes for p in self.buf.peer_ptrs]
@@ -170,6 +172,7 @@ def _native():
     native.register_signature(
         "t5x_gemm_allgather_bf16",
         [vp, pp, ci, ci, ci, vp, vp, vp, vp, ci, ci, ci, ll, ll, ci, ci, vp, vp, ll, vp])
+    native.register_signature("t5x_slot_sum_bf16", [vp, ci, ll, vp, vp, vp])
     native.register_signature(
         "t5x_gemm_reducescatter_bf16",
         [vp, vp, pp, ci, ci, ci, ci, ci, ci, ll, ll, ll, ci, ci, vp, ll, vp])
@@ -241,21 +244,35 @@ def gemm_reducescatter(a: torch.Tensor, b: torch.Tensor, inbox: _Inbox, *,
 
 
 # ---- building blocks ----------------------------------------------------------------------
-def _gather_block(rows: torch.Tensor) -> _Block:
-  """An arena block shaped [M, K] whose block of this rank holds `rows` ([M / T, K]), with
-  every rank past the point where its own rows are in place."""
+def rows_buffer(m: int, k: int):
+  """(block, dst): an arena block for a gathered [m * T, k] bf16 matrix and the view of this
+  rank's rows of it. A producer that writes its [m, k] result into `dst` saves the copy that
+  `all_gather_linears(..., block=None)` would make."""
   ar = arena()
-  m, k = rows.shape
   ar.settle()  # peers may still be reading the bytes this block reuses
   blk = ar.alloc(m * ar.world * k * 2)
-  blk.tensor((m * ar.world, k))[ar.rank * m:(ar.rank + 1) * m].copy_(rows)
+  return blk, blk.tensor((m * ar.world, k))[ar.rank * m:(ar.rank + 1) * m]
+
+
+def _gather_block(rows: torch.Tensor, blk: Optional[_Block] = None) -> _Block:
+  """An arena block shaped [M, K] whose block of this rank holds `rows` ([M / T, K]), with
+  every rank past the point where its own rows are in place. `blk`: the block `rows` already
+  lives in (see `rows_buffer`)."""
+  ar = arena()
+  m, k = rows.shape
+  if blk is None:
+    blk, dst = rows_buffer(m, k)
+    dst.copy_(rows)
   ar.barrier()
   return blk
 
 
-def _reduce_scatter(a: torch.Tensor, b: torch.Tensor, residual: Optional[torch.Tensor] = None
-                    ) -> torch.Tensor:
-  """fp32 [M / T, N]: this rank's rows of the sum over ranks of a @ b (+ residual)."""
+def _reduce_scatter(a: torch.Tensor, b: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                    add_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+  """bf16 [M / T, N]: this rank's rows of the sum over ranks of (a @ b + residual), plus
+  `add_rows` ([M / T, N], this rank's rows of a replicated-sum term such as the residual
+  stream). The sum over the inbox slots is taken in fp32."""
+  native = _native()
   ar = arena()
   M, N = a.shape[0], b.shape[1]
   m = M // ar.world
@@ -264,7 +281,12 @@ def _reduce_scatter(a: torch.Tensor, b: torch.Tensor, residual: Optional[torch.T
     ar.barrier()  # every rank has finished summing what the inbox held before
   gemm_reducescatter(a, b, inbox, residual=residual)
   ar.barrier()  # every rank's rows have landed
-  out = torch.sum(inbox.tensor((ar.world, m, N)), dim=0, dtype=torch.float32)
+  out = torch.empty((m, N), dtype=torch.bfloat16, device=a.device)
+  if add_rows is not None:
+    assert add_rows.dtype == torch.bfloat16 and add_rows.is_contiguous()
+  native._check(native.lib().t5x_slot_sum_bf16(
+      inbox.tensor((ar.world, m, N)).data_ptr(), ar.world, m * N, native.ptr(add_rows),
+      out.data_ptr(), native.stream_ptr()), "slot_sum_bf16")
   ar.inbox_busy = True
   return out
 
@@ -279,12 +301,12 @@ class _AllGatherLinearsFn(torch.autograd.Function):
   the single output is gelu(A @ W_0) * (A @ W_1)."""
 
   @staticmethod
-  def forward(ctx, h_sp, gated, *weights):
+  def forward(ctx, h_sp, gated, blk, *weights):
     from t5x_b200.ops import native
     ar = arena()
     m, k = h_sp.shape
     M = m * ar.world
-    blk = _gather_block(h_sp)
+    blk = _gather_block(h_sp, blk)
     ws = [_weight2d(w, k) for w in weights]
     ctx.h = None
     if gated:
@@ -313,7 +335,7 @@ class _AllGatherLinearsFn(torch.autograd.Function):
       dys = [None if d is None else d.reshape(M, -1).contiguous() for d in douts]
     dws = []
     for i, (w, dy) in enumerate(zip(weights, dys)):
-      need = ctx.needs_input_grad[2 + i] and dy is not None
+      need = ctx.needs_input_grad[3 + i] and dy is not None
       dws.append(F._accumulate_wgrad(w, a_full.t(), dy) if need else None)
     blk.release()
     ctx.blk = ctx.h = None
@@ -327,8 +349,8 @@ class _AllGatherLinearsFn(torch.autograd.Function):
         else:
           native.gemm(dy, w.t(), out=partial, accumulate=True)
       dy, w = live[-1]
-      dh_sp = _reduce_scatter(dy, w.t(), residual=partial).to(torch.bfloat16)
-    return (dh_sp, None) + tuple(dws)
+      dh_sp = _reduce_scatter(dy, w.t(), residual=partial)
+    return (dh_sp, None, None) + tuple(dws)
 
 
 class _LinearReduceScatterFn(torch.autograd.Function):
@@ -340,12 +362,10 @@ class _LinearReduceScatterFn(torch.autograd.Function):
     k = a.shape[-1]
     a2 = a.reshape(-1, k)
     w2 = _weight2d(weight, k)
-    y = _reduce_scatter(a2, w2)
-    if residual_sp is not None:
-      y += residual_sp
+    y = _reduce_scatter(a2, w2, add_rows=None if residual_sp is None else residual_sp.contiguous())
     ctx.save_for_backward(a, weight)
     ctx.has_res = residual_sp is not None
-    return y.to(torch.bfloat16)
+    return y
 
   @staticmethod
   def backward(ctx, dy_sp):
@@ -364,15 +384,17 @@ class _LinearReduceScatterFn(torch.autograd.Function):
     return da, dw, (dy_sp if ctx.has_res else None)
 
 
-def all_gather_linears(h_sp: torch.Tensor, weights: Sequence[torch.Tensor]) -> List[torch.Tensor]:
-  """Column-parallel projections of row-sharded activations: [allgather(h_sp) @ W for W]."""
-  return list(_AllGatherLinearsFn.apply(h_sp.contiguous(), False, *weights))
+def all_gather_linears(h_sp: torch.Tensor, weights: Sequence[torch.Tensor],
+                       block: Optional[_Block] = None) -> List[torch.Tensor]:
+  """Column-parallel projections of row-sharded activations: [allgather(h_sp) @ W for W].
+  `block`: the `rows_buffer` block whose `dst` view `h_sp` is."""
+  return list(_AllGatherLinearsFn.apply(h_sp.contiguous(), False, block, *weights))
 
 
-def all_gather_gated_gelu(h_sp: torch.Tensor, wi_0: torch.Tensor, wi_1: torch.Tensor
-                          ) -> torch.Tensor:
+def all_gather_gated_gelu(h_sp: torch.Tensor, wi_0: torch.Tensor, wi_1: torch.Tensor,
+                          block: Optional[_Block] = None) -> torch.Tensor:
   """gelu(A @ wi_0) * (A @ wi_1) with A = allgather(h_sp)."""
-  return _AllGatherLinearsFn.apply(h_sp.contiguous(), True, wi_0, wi_1)[0]
+  return _AllGatherLinearsFn.apply(h_sp.contiguous(), True, block, wi_0, wi_1)[0]
 
 
 def linear_reduce_scatter(a: torch.Tensor, weight: torch.Tensor,
