@@ -675,44 +675,72 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       ok = mbar_wait(bar_s, i & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[32], dpv[32];
-      tmem_ld32(t_row + cS + col0, sv);
-      tmem_ld32(t_row + cDP + col0, dpv);
-      tmem_ld_wait();
-      float pr[32], ds[32];
+      // 16 columns (queries) at a time keeps the working set in registers: scores and dP of
+      // the chunk, its per-query statistics, and the packed bf16 results.
       const float* rel = sRel + (r - col0 + 127);
+      const bool interior = simple_mask && k0 + 128 <= p.Lk && qb + 128 <= p.Lq;
+      // interior tile with a key-only mask: the mask is one additive constant per thread
+      // (-1e10 absorbs any score: |s| is far below the fp32 spacing at 1e10)
+      const float madd = kvis ? 0.f : kMaskValue;
+      uint8_t* pt_tile = sPT + (part >> 1) * BwdSmem::kTile;
+      uint8_t* dst_tile = sDST + (part >> 1) * BwdSmem::kTile;
+      // Bias gradient: dS[key r][query c] belongs to bin (r - c). Within the warp's 32 x 32
+      // block the sums along diagonals are formed in registers: a running sum moves one lane up
+      // per column, so it follows its diagonal; lane 31 holds a finished diagonal at each
+      // column and the other lanes finish after the last one. 63 shared-memory atomics per
+      // warp instead of 1024. (Masks are additive, so the bias receives dS everywhere.)
+      const bool want_drel = p.d_rel_bias != nullptr;
+      float* bins = sDRel + (quarter * 32 - qb - col0 + lq_pad);  // bins[lane - x]
+      float run = 0.f;
 #pragma unroll
-      for (int x = 0; x < 32; ++x) {
-        const int cq = col0 + x;
-        float s = __uint_as_float(sv[x]);
-        if (has_bias) s += rel[-x];
-        s = ((mv >> x) & 1u) ? s : kMaskValue;
-        const float lse2 = sLse[cq];
-        float e = exp2f(fmaf(s, kLog2e, -lse2));
-        // A row with every key masked has lse = -1e10 + log(Lk), which fp32 rounds to -1e10:
-        // its probabilities are uniform over the Lk keys.
-        if (lse2 < -5e9f) e = inv_lk;
-        if (!k_ok || qb + cq >= p.Lq) e = 0.f;
-        const float g = e * (__uint_as_float(dpv[x]) - sDelta[cq]);
-        pr[x] = e;
-        ds[x] = g;
-      }
-      if (p.d_rel_bias != nullptr) {
-        // masks are additive, so the bias term receives the softmax gradient everywhere
-        float* acc = sDRel + (r - qb - col0 + lq_pad);
+      for (int hc = 0; hc < 2; ++hc) {
+        uint32_t sv[16], dpv[16];
+        tmem_ld16(t_row + cS + col0 + hc * 16, sv);
+        tmem_ld16(t_row + cDP + col0 + hc * 16, dpv);
+        tmem_ld_wait();
+        float lse_c[16], del_c[16];
 #pragma unroll
-        for (int x = 0; x < 32; ++x)
-          if (ds[x] != 0.f) atomicAdd(acc - x, ds[x]);
-      }
-      {
-        uint8_t* pt_tile = sPT + (part >> 1) * BwdSmem::kTile;
-        uint8_t* dst_tile = sDST + (part >> 1) * BwdSmem::kTile;
+        for (int g = 0; g < 4; ++g) {  // 16-byte broadcast loads of the per-query statistics
+          const float4 a = reinterpret_cast<const float4*>(sLse + col0 + hc * 16)[g];
+          const float4 d = reinterpret_cast<const float4*>(sDelta + col0 + hc * 16)[g];
+          lse_c[4 * g] = a.x, lse_c[4 * g + 1] = a.y, lse_c[4 * g + 2] = a.z, lse_c[4 * g + 3] = a.w;
+          del_c[4 * g] = d.x, del_c[4 * g + 1] = d.y, del_c[4 * g + 2] = d.z, del_c[4 * g + 3] = d.w;
+        }
+        float pr[16], ds[16];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          store_swizzled_chunk(pt_tile, r, (part & 1) * 4 + g, pr + g * 8);
-          store_swizzled_chunk(dst_tile, r, (part & 1) * 4 + g, ds + g * 8);
+        for (int x = 0; x < 16; ++x) {
+          const int xx = hc * 16 + x;
+          float s = __uint_as_float(sv[x]);
+          if (has_bias) s += rel[-xx];
+          if (interior) {
+            s = fmaxf(s + madd, kMaskValue);
+          } else {
+            s = ((mv >> xx) & 1u) ? s : kMaskValue;
+          }
+          float e = exp2f(fmaf(s, kLog2e, -lse_c[x]));
+          // A row with every key masked has lse = -1e10 + log(Lk), which fp32 rounds to -1e10:
+          // its probabilities are uniform over the Lk keys.
+          if (lse_c[x] < -5e9f) e = inv_lk;
+          if (!interior && (!k_ok || qb + col0 + xx >= p.Lq)) e = 0.f;
+          pr[x] = e;
+          ds[x] = e * (__uint_as_float(dpv[x]) - del_c[x]);
+        }
+        if (want_drel) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            run += ds[x];
+            if (lane == 31) atomicAdd(bins + (31 - hc * 16 - x), run);
+            run = __shfl_up_sync(0xffffffffu, run, 1);
+            if (lane == 0) run = 0.f;
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          store_swizzled_chunk(pt_tile, r, (part & 1) * 4 + hc * 2 + g, pr + g * 8);
+          store_swizzled_chunk(dst_tile, r, (part & 1) * 4 + hc * 2 + g, ds + g * 8);
         }
       }
+      if (want_drel && lane != 0) atomicAdd(bins + (lane - 32), run);
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
