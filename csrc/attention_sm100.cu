@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (j >= nblk || !ok) break;
-        ok = mbar_wait(&bar_s[j], ph, abort_flag);
+        ok = mbar_wait_relaxed(&bar_s[j], ph, abort_flag);
         if (!ok) break;
         tc_fence_after();
         uint32_t v[32];
@@ -342,10 +342,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         // P buffer (j & 1) was last read by the PV MMA of block j-2 (this query block) or of
         // the last block with the same parity of the previous query block.
         if (j >= 2) {
-          ok = mbar_wait(&bar_pv[j - 2], ph, abort_flag);
+          ok = mbar_wait_relaxed(&bar_pv[j - 2], ph, abort_flag);
         } else if (i > 0) {
           const int jp = ((nblk - 1 - j) & ~1) + j;  // last block index with parity j
-          if (jp < nblk) ok = mbar_wait(&bar_pv[jp], ph ^ 1, abort_flag);
+          if (jp < nblk) ok = mbar_wait_relaxed(&bar_pv[jp], ph ^ 1, abort_flag);
         }
         if (!ok) break;
         uint8_t* ptile = sP + (j & 1) * 2 * FwdSmem::kTile + (part >> 1) * FwdSmem::kTile;
@@ -388,7 +388,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       softmax_bar_sync();
       l = (sStat[512 + r * 4] + sStat[512 + r * 4 + 1]) + (sStat[512 + r * 4 + 2] + sStat[512 + r * 4 + 3]);
       // ---- epilogue: O / l (each of the 4 threads of a row writes 16 of the 64 columns) ----
-      if (ok) ok = mbar_wait(&bar_pv[nblk - 1], ph, abort_flag);
+      if (ok) ok = mbar_wait_relaxed(&bar_pv[nblk - 1], ph, abort_flag);
       if (!ok) break;
       tc_fence_after();
       {
@@ -672,7 +672,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           mv |= (v ? 1u : 0u) << x;
         }
       }
-      ok = mbar_wait(bar_s, i & 1, abort_flag);
+      ok = mbar_wait_relaxed(bar_s, i & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
       // 16 columns (queries) at a time keeps the working set in registers: scores and dP of
@@ -685,13 +685,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       uint8_t* pt_tile = sPT + (part >> 1) * BwdSmem::kTile;
       uint8_t* dst_tile = sDST + (part >> 1) * BwdSmem::kTile;
       // Bias gradient: dS[key r][query c] belongs to bin (r - c). Within the warp's 32 x 32
-      // block the sums along diagonals are formed in registers: a running sum moves one lane up
-      // per column, so it follows its diagonal; lane 31 holds a finished diagonal at each
-      // column and the other lanes finish after the last one. 63 shared-memory atomics per
-      // warp instead of 1024. (Masks are additive, so the bias receives dS everywhere.)
+      // block (lane = key row, x = query column) lane L collects diagonal L and diagonal L - 32:
+      // at column x it fetches the value of lane (L + x) mod 32, which lies on diagonal L when
+      // L + x < 32 and on diagonal L - 32 otherwise. The 32 shuffles are independent of each
+      // other, and the block costs two shared-memory atomics per lane instead of 32. (Masks
+      // are additive, so the bias receives dS everywhere.)
       const bool want_drel = p.d_rel_bias != nullptr;
       float* bins = sDRel + (quarter * 32 - qb - col0 + lq_pad);  // bins[lane - x]
-      float run = 0.f;
+      float diag_pos = 0.f, diag_neg = 0.f;
 #pragma unroll
       for (int hc = 0; hc < 2; ++hc) {
         uint32_t sv[16], dpv[16];
@@ -728,10 +729,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         if (want_drel) {
 #pragma unroll
           for (int x = 0; x < 16; ++x) {
-            run += ds[x];
-            if (lane == 31) atomicAdd(bins + (31 - hc * 16 - x), run);
-            run = __shfl_up_sync(0xffffffffu, run, 1);
-            if (lane == 0) run = 0.f;
+            const int xx = hc * 16 + x;
+            const float v = __shfl_sync(0xffffffffu, ds[x], (lane + xx) & 31);
+            if (lane + xx < 32) {
+              diag_pos += v;
+            } else {
+              diag_neg += v;
+            }
           }
         }
 #pragma unroll
@@ -740,13 +744,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           store_swizzled_chunk(dst_tile, r, (part & 1) * 4 + hc * 2 + g, ds + g * 8);
         }
       }
-      if (want_drel && lane != 0) atomicAdd(bins + (lane - 32), run);
+      if (want_drel) {
+        atomicAdd(bins + lane, diag_pos);
+        if (lane != 0) atomicAdd(bins + (lane - 32), diag_neg);
+      }
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p);
       // dQ partial: rows are queries here (TMEM lane = query within the block); 16 columns each
-      ok = mbar_wait(bar_dq, i & 1, abort_flag);
+      ok = mbar_wait_relaxed(bar_dq, i & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
       {

@@ -100,6 +100,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   return false;
 }
 
+// The same for many waiting warps (the softmax warps of the attention kernels): after a few
+// immediate polls the warp sleeps between polls, so that the waiters leave the issue slots and
+// the shared-memory port to the one warp that feeds the tensor cores.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity,
+                                                  volatile int* abort_flag) {
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (it >= 4) __nanosleep(40);
+    if ((it & 0xff) == 0xff && *abort_flag) return false;
+  }
+  return false;
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
