@@ -491,7 +491,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   uint64_t* bar_p = bars + 6;       // P^T / dS^T written, S^T / dP^T released
   uint64_t* bar_dq = bars + 7;      // dQ partial ready (also: P^T/dS^T smem consumed)
   uint64_t* bar_dq_read = bars + 8; // dQ partial consumed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* bar_sfree = bars + 9;   // S^T / dP^T columns read into registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -499,7 +500,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   const int nq = (p.Lq + 127) / 128;
   const int lq_pad = nq * 128;
   // TMEM columns
-  constexpr int cS = 0, cDP = 128, cDQ = 256, cDK = 320, cDV = 384;
+  // dQ partial tiles alternate between two 64-column buffers, so that the tile of query block
+  // i is read out while the MMAs of block i + 1 run.
+  constexpr int cS = 0, cDP = 128, cDQ = 256, cDK = 384, cDV = 448;
 
   if (threadIdx.x == 0) {
     mbar_init(bar_kv, 1);
@@ -511,6 +514,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     mbar_init(bar_p, kSoftmaxWarps);
     mbar_init(bar_dq, 1);
     mbar_init(bar_dq_read, kSoftmaxWarps);
+    mbar_init(bar_sfree, kSoftmaxWarps);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -561,13 +565,24 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         tc_fence_after();
         issue_scores(0);
       }
+      // Order per query block i: the scores of block i + 1 are issued as soon as the softmax
+      // warps hold those of block i in registers (bar_sfree), so they are computed while the
+      // warps do their arithmetic; the gradient MMAs of block i follow when P^T / dS^T are in
+      // shared memory (bar_p).
       for (int i = 0; i < nq && ok; ++i) {
         const int st = i & 1;
         const uint32_t ph = (i >> 1) & 1;
         const uint32_t qa = smem_u32(sQ + st * BwdSmem::kTile);
         const uint32_t doa = smem_u32(sDO + st * BwdSmem::kTile);
-        ok = mbar_wait(bar_p, i & 1, abort_flag);
-        if (ok && i > 0) ok = mbar_wait(bar_dq_read, (i - 1) & 1, abort_flag);
+        ok = mbar_wait(bar_sfree, i & 1, abort_flag);
+        if (ok && i + 1 < nq) {
+          ok = mbar_wait(&bar_qdo[(i + 1) & 1], ((i + 1) >> 1) & 1, abort_flag);
+          if (ok) {
+            tc_fence_after();
+            issue_scores(i + 1);
+          }
+        }
+        if (ok) ok = mbar_wait(bar_p, i & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         // dV += P^T dO ; dK += dS^T Q ; dQ_i = dS K
@@ -585,16 +600,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         // are kTile apart (LBO), 8-key groups 1024 B apart (SBO); K advances 16 keys = 2048 B.
 #pragma unroll
         for (int s = 0; s < 8; ++s)
-          umma_bf16(tmem_base + cDQ, make_smem_desc_sw128(dsta + s * 2048, BwdSmem::kTile, 1024),
+          umma_bf16(tmem_base + cDQ + (i & 1) * 64,
+                    make_smem_desc_sw128(dsta + s * 2048, BwdSmem::kTile, 1024),
                     make_smem_desc_sw128(ka + s * 2048, 8192, 1024), idesc_qd, s != 0);
         umma_commit(bar_dq);
         umma_commit(&bar_free[st]);
-        // Scores of the next query block right behind: S^T / dP^T columns were released by bar_p.
-        if (i + 1 < nq) {
-          ok = mbar_wait(&bar_qdo[(i + 1) & 1], ((i + 1) >> 1) & 1, abort_flag);
+        // The softmax warps read dQ_{i-1} right after they signalled bar_p for block i; once
+        // they have, its buffer is free for dQ_{i+1}. (Waiting here, not before the next
+        // block's MMAs, keeps at most one completion of bar_dq_read ahead of this wait.)
+        if (i >= 1 && i + 1 < nq) {
+          ok = mbar_wait(bar_dq_read, (i - 1) & 1, abort_flag);
           if (!ok) break;
-          tc_fence_after();
-          issue_scores(i + 1);
         }
         // refill this stage with query block i + 2
         if (i + 2 < nq) {
@@ -625,30 +641,67 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     const bool simple_mask = !p.causal && p.kv_seg == nullptr;
     bool ok = true;
 
-    auto load_vectors = [&](int i) {
-      // per-query vectors of block i into stage (i & 1); all softmax threads cooperate
-      float* sLse = sVec + (i & 1) * 384;
-      float* sDelta = sLse + 128;
-      int* sQseg = reinterpret_cast<int*>(sDelta + 128);
-      float* sRel = sRelAll + (i & 1) * 256;
+    // Per-query vectors of block i go to stage (i & 1) of shared memory; all softmax threads
+    // cooperate (thread t < 128: lse, delta and segment id of query t; the next 255 threads:
+    // the bias by relative position over the (key block, query block) pair, index
+    // u = r - c + 127). `fetch` issues the global loads early, `publish` stores them after the
+    // arithmetic of the current block, so their latency is off the critical path.
+    float pf_a = 0.f, pf_b = 0.f;
+    int pf_c = 0;
+    auto fetch_vectors = [&](int i) {
       const int qb = i * 128;
       const int t = threadIdx.x;
       if (t < 128) {
         const int q = qb + t;
         const long long off = (static_cast<long long>(b) * p.H + h) * p.Lq + q;
-        sLse[t] = (q < p.Lq) ? p.lse[off] * kLog2e : 0.f;
-        sDelta[t] = (q < p.Lq) ? p.delta[off] : 0.f;
-        sQseg[t] = (p.q_seg && q < p.Lq) ? p.q_seg[static_cast<long long>(b) * p.Lq + q] : 0;
+        pf_a = (q < p.Lq) ? p.lse[off] * kLog2e : 0.f;
+        pf_b = (q < p.Lq) ? p.delta[off] : 0.f;
+        pf_c = (p.q_seg && q < p.Lq) ? p.q_seg[static_cast<long long>(b) * p.Lq + q] : 0;
       } else if (t < 128 + 255 && has_bias) {
-        // rel = k - q over the pair: index u = r - c + 127 in [0, 255)
         const int u = t - 128;
         const float* tab = p.rel_bias + static_cast<long long>(h) * p.nrel;
         const int idx = (k0 - qb) + (u - 127) + p.rel_off;
-        sRel[u] = (idx >= 0 && idx < p.nrel) ? tab[idx] : 0.f;
+        pf_a = (idx >= 0 && idx < p.nrel) ? tab[idx] : 0.f;
+      }
+    };
+    auto publish_vectors = [&](int i) {
+      float* sLse = sVec + (i & 1) * 384;
+      float* sDelta = sLse + 128;
+      int* sQseg = reinterpret_cast<int*>(sDelta + 128);
+      float* sRel = sRelAll + (i & 1) * 256;
+      const int t = threadIdx.x;
+      if (t < 128) {
+        sLse[t] = pf_a;
+        sDelta[t] = pf_b;
+        sQseg[t] = pf_c;
+      } else if (t < 128 + 255 && has_bias) {
+        sRel[t - 128] = pf_a;
       }
     };
 
-    load_vectors(0);
+    auto read_dq = [&](int blk, bool release) {
+      uint32_t v[16];
+      tmem_ld16(t_row + cDQ + (blk & 1) * 64 + part * 16, v);
+      tmem_ld_wait();
+      if (release) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_dq_read);
+      }
+      const int q = blk * 128 + r;
+      if (q < p.Lq) {
+        float* dst = p.dQ + ((static_cast<long long>(b) * p.Lq + q) * p.H + h) * kAttnD + part * 16;
+#pragma unroll
+        for (int x = 0; x < 16; x += 4)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + x),
+                       "f"(__uint_as_float(v[x])), "f"(__uint_as_float(v[x + 1])),
+                       "f"(__uint_as_float(v[x + 2])), "f"(__uint_as_float(v[x + 3]))
+                       : "memory");
+      }
+    };
+
+    fetch_vectors(0);
+    publish_vectors(0);
     softmax_bar_sync();
     for (int i = 0; i < nq && ok; ++i) {
       const int qb = i * 128;
@@ -656,7 +709,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       const float* sDelta = sLse + 128;
       const int* sQseg = reinterpret_cast<const int*>(sDelta + 128);
       const float* sRel = sRelAll + (i & 1) * 256;
-      if (i + 1 < nq) load_vectors(i + 1);  // other stage; consumed after the sync at the loop end
+      if (i + 1 < nq) fetch_vectors(i + 1);  // published before the sync at the loop end
       const int col0 = part * 32;  // query column within the block
       // visibility of (this key, queries col0..col0+31)
       uint32_t mv;
@@ -699,6 +752,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         tmem_ld16(t_row + cS + col0 + hc * 16, sv);
         tmem_ld16(t_row + cDP + col0 + hc * 16, dpv);
         tmem_ld_wait();
+        if (hc == 1) {
+          // all of S^T / dP^T of this block is in registers: the scores of the next block may
+          // overwrite the columns while the arithmetic below runs
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_sfree);
+        }
         float lse_c[16], del_c[16];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {  // 16-byte broadcast loads of the per-query statistics
@@ -738,6 +798,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             }
           }
         }
+        if (hc == 0 && i > 0) {
+          // the gradient MMAs of block i - 1 still read P^T / dS^T; they also produce dQ_{i-1}
+          ok = mbar_wait_relaxed(bar_dq, (i - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+        }
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
           store_swizzled_chunk(pt_tile, r, (part & 1) * 4 + hc * 2 + g, pr + g * 8);
@@ -752,29 +818,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p);
-      // dQ partial: rows are queries here (TMEM lane = query within the block); 16 columns each
-      ok = mbar_wait_relaxed(bar_dq, i & 1, abort_flag);
       if (!ok) break;
-      tc_fence_after();
-      {
-        uint32_t v[16];
-        tmem_ld16(t_row + cDQ + part * 16, v);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_dq_read);
-        const int q = qb + r;
-        if (q < p.Lq) {
-          float* dst = p.dQ + ((static_cast<long long>(b) * p.Lq + q) * p.H + h) * kAttnD + part * 16;
-#pragma unroll
-          for (int x = 0; x < 16; x += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + x),
-                         "f"(__uint_as_float(v[x])), "f"(__uint_as_float(v[x + 1])),
-                         "f"(__uint_as_float(v[x + 2])), "f"(__uint_as_float(v[x + 3]))
-                         : "memory");
-        }
-      }
+      // dQ partial of the previous block (its MMAs were waited for above), while the MMAs of
+      // this block run: rows are queries here (TMEM lane = query within the block), 16 columns
+      // per thread.
+      if (i > 0) read_dq(i - 1, true);
+      if (i + 1 < nq) publish_vectors(i + 1);  // other stage than the one block i used
       softmax_bar_sync();  // the vectors of block i+1 are complete; those of block i are dead
+    }
+    if (ok) {
+      ok = mbar_wait_relaxed(bar_dq, (nq - 1) & 1, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        read_dq(nq - 1, false);
+      }
     }
     if (ok) {
       // dK, dV accumulators are complete once the last bar_dq fired (same commit group).
