@@ -142,3 +142,41 @@ def test_restore_model_from_tf_checkpoint(tmp_path):
   for k, want in flat.items():
     got = tree_utils.flatten_dict(restored.params)[k].detach().numpy()
     np.testing.assert_array_equal(got, want)
+
+
+def test_convert_tf_checkpoint_script(tmp_path):
+  """The conversion script writes a native checkpoint that restores the TF values."""
+  from t5x_b200 import checkpoints, partitioning
+  from t5x_b200.scripts import convert_tf_checkpoint as script
+  cfg = network.T5Config(vocab_size=64, emb_dim=16, num_heads=2, head_dim=8, mlp_dim=32,
+                         num_encoder_layers=2, num_decoder_layers=2, dropout_rate=0.0,
+                         mlp_activations=("gelu", "linear"))
+  torch.manual_seed(0)
+  src = network.Transformer(cfg)
+  flat = {k: v.detach().numpy() for k, v in tree_utils.flatten_dict(
+      models.module_param_tree(src)).items()}
+  v = vocabularies.PassThroughVocabulary(64)
+  torch.manual_seed(1)
+  model = models.EncoderDecoderModel(network.Transformer(cfg), v, v, adafactor.Adafactor())
+  state = ts.FlaxOptimTrainState.create(model.optimizer_def,
+                                        model.get_initial_variables(None, None))
+  tensors = _tf_names(flat)
+  slots = tree_utils.flatten_dict(state.param_states)
+  for key in flat:
+    for tf_name in _tf_names({key: flat[key]}):
+      if tuple(slots[f"{key}/v"].shape) != (1,):
+        tensors[tf_name + "_slot_v"] = np.full(slots[f"{key}/v"].shape, 0.5, np.float32)
+      else:
+        tensors[tf_name + "_slot_vr"] = np.full(slots[f"{key}/v_row"].shape, 0.25, np.float32)
+        tensors[tf_name + "_slot_vc"] = np.full(slots[f"{key}/v_col"].shape, 0.75, np.float32)
+  tensors["global_step"] = np.asarray(77, np.int64)
+  prefix = str(tmp_path / "tf" / "model.ckpt-77")
+  tf_bundle.write_bundle(prefix, tensors)
+  out_dir = str(tmp_path / "native")
+  script.convert_checkpoint(model, prefix, out_dir)
+  ck = checkpoints.Checkpointer(state, partitioning.PjitPartitioner(1), out_dir)
+  assert ck.all_steps() == [77]
+  restored = ck.restore(step=77)
+  for k, want in flat.items():
+    got = tree_utils.flatten_dict(restored.params)[k].detach().numpy()
+    np.testing.assert_array_equal(got, want)
