@@ -89,45 +89,56 @@ __global__ void __launch_bounds__(kNormThreads)
 // ---------------------------------------------------------------------------
 // RMSNorm backward.
 //   g = dy * scale ;  dx = rstd * (g - x * rstd^2 * mean(g * x)) (+ dres)
-//   dscale[j] += sum_rows dy * x * rstd            (fp32 atomics, one per CTA per feature)
+//   dscale[j] += sum_rows dy * x * rstd            (per-CTA partial sums, then one reduction)
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kNormThreads)
+// NV = 16-byte vectors per thread (d <= 2048 * NV). Operands stay packed (bf16) in registers
+// between the two passes over a row and the scale is re-read from L1, so that four CTAs fit an
+// SM for d <= 4096: the kernel is bound by how many rows are in flight. The per-feature sums
+// for dscale are kept in registers over the CTA's rows and written to `partial`
+// ([gridDim.x, d], plain stores); rmsnorm_dscale_reduce_kernel adds them up.
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 4 : 2)
     rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                        const float* __restrict__ scale, const float* __restrict__ rstd_in,
                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
-                       float* __restrict__ dscale, int rows, int d) {
+                       float* __restrict__ partial, int rows, int d) {
   __shared__ float red[32];
   const int nvec = d / 8;
-  float ds_acc[kNormMaxVec][8];
-  float sc[kNormMaxVec][8];
+  float ds_acc[NV][8];
 #pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
-    const int v = threadIdx.x + i * kNormThreads;
+  for (int i = 0; i < NV; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      ds_acc[i][j] = 0.f;
-      sc[i][j] = (v < nvec) ? scale[v * 8 + j] : 0.f;
-    }
-  }
+    for (int j = 0; j < 8; ++j) ds_acc[i][j] = 0.f;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const long long off = static_cast<long long>(row) * d;
     const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + off);
     const Bf16x8* dyr = reinterpret_cast<const Bf16x8*>(dy + off);
-    const float rstd = rstd_in[row];
-    float xv[kNormMaxVec][8], gv[kNormMaxVec][8];
-    float dot = 0.f;
+    Bf16x8 xp[NV], dyp[NV];
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {  // all loads of the row before the first use
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
-        float dyv[8];
-        unpack8(xr[v], xv[i]);
-        unpack8(dyr[v], dyv);
+        xp[i] = xr[v];
+        dyp[i] = dyr[v];
+      }
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float xv[8], dyv[8];
+        unpack8(xp[i], xv);
+        unpack8(dyp[i], dyv);
+        const float4 s0 = reinterpret_cast<const float4*>(scale)[2 * v];
+        const float4 s1 = reinterpret_cast<const float4*>(scale)[2 * v + 1];
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          ds_acc[i][j] += dyv[j] * xv[i][j] * rstd;
-          gv[i][j] = dyv[j] * sc[i][j];
-          dot += gv[i][j] * xv[i][j];
+          const float t = dyv[j] * xv[j];
+          ds_acc[i][j] += t * rstd;
+          dot += t * sc[j];
         }
       }
     }
@@ -136,12 +147,17 @@ __global__ void __launch_bounds__(kNormThreads)
     Bf16x8* dxr = reinterpret_cast<Bf16x8*>(dx + off);
     const Bf16x8* rr = dres ? reinterpret_cast<const Bf16x8*>(dres + off) : nullptr;
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
-        float o[8];
+        float xv[8], dyv[8], o[8];
+        unpack8(xp[i], xv);
+        unpack8(dyp[i], dyv);
+        const float4 s0 = reinterpret_cast<const float4*>(scale)[2 * v];
+        const float4 s1 = reinterpret_cast<const float4*>(scale)[2 * v + 1];
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (gv[i][j] - xv[i][j] * c);
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (dyv[j] * sc[j] - xv[j] * c);
         if (rr) {
           float r8[8];
           unpack8(rr[v], r8);
@@ -152,16 +168,37 @@ __global__ void __launch_bounds__(kNormThreads)
       }
     }
   }
-  if (dscale) {
+  if (partial) {
+    float* out = partial + static_cast<long long>(blockIdx.x) * d;
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) atomicAdd(&dscale[v * 8 + j], ds_acc[i][j]);
+        reinterpret_cast<float4*>(out)[2 * v] =
+            make_float4(ds_acc[i][0], ds_acc[i][1], ds_acc[i][2], ds_acc[i][3]);
+        reinterpret_cast<float4*>(out)[2 * v + 1] =
+            make_float4(ds_acc[i][4], ds_acc[i][5], ds_acc[i][6], ds_acc[i][7]);
       }
     }
   }
+}
+
+// dscale[j] += sum over the CTAs of partial[cta][j]
+__global__ void __launch_bounds__(256)
+    rmsnorm_dscale_reduce_kernel(const float* __restrict__ partial, int parts, int d,
+                                 float* __restrict__ dscale) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= d) return;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int p = 0;
+  for (; p + 3 < parts; p += 4) {
+    a0 += partial[static_cast<long long>(p) * d + j];
+    a1 += partial[static_cast<long long>(p + 1) * d + j];
+    a2 += partial[static_cast<long long>(p + 2) * d + j];
+    a3 += partial[static_cast<long long>(p + 3) * d + j];
+  }
+  for (; p < parts; ++p) a0 += partial[static_cast<long long>(p) * d + j];
+  dscale[j] += (a0 + a1) + (a2 + a3);
 }
 
 // ---------------------------------------------------------------------------
@@ -322,12 +359,37 @@ T5X_API int t5x_rmsnorm_bwd(const void* dy, const void* x, const void* scale, co
   if (d % 8 || d > kNormThreads * 8 * kNormMaxVec)
     return set_error("rmsnorm: d=%d must be a multiple of 8 and <= %d", d,
                      kNormThreads * 8 * kNormMaxVec);
-  int grid = rows < num_sms() * 2 ? rows : num_sms() * 2;
-  rmsnorm_bwd_kernel<<<grid, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-      static_cast<const float*>(scale), static_cast<const float*>(rstd),
-      static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx),
-      static_cast<float*>(dscale), rows, d);
+  // Workspace for the per-CTA dscale sums: one buffer per device, allocated at the first call
+  // (so not under stream capture) and shared by all calls: backward passes on one stream.
+  constexpr int kMaxParts = 1024;
+  static float* ws[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dscale != nullptr && ws[dev] == nullptr) {
+    if (cudaMalloc(&ws[dev], sizeof(float) * kMaxParts * kNormThreads * 8 * kNormMaxVec) !=
+        cudaSuccess)
+      return set_error("rmsnorm_bwd: workspace allocation failed");
+  }
+  const int nv = d <= 2048 ? 1 : (d <= 4096 ? 2 : 4);
+  int grid = num_sms() * (nv <= 2 ? 4 : 2);
+  if (grid > rows) grid = rows;
+  if (grid > kMaxParts) grid = kMaxParts;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = dscale != nullptr ? ws[dev] : nullptr;
+  auto launch = [&](auto kernel) {
+    kernel<<<grid, kNormThreads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+        static_cast<const float*>(scale), static_cast<const float*>(rstd),
+        static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), partial, rows, d);
+  };
+  if (nv == 1) launch(rmsnorm_bwd_kernel<1>);
+  else if (nv == 2) launch(rmsnorm_bwd_kernel<2>);
+  else launch(rmsnorm_bwd_kernel<4>);
+  if (dscale != nullptr) {
+    count_launches(1);
+    rmsnorm_dscale_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, grid, d,
+                                                                  static_cast<float*>(dscale));
+  }
   CHECK_LAUNCH("rmsnorm_bwd");
   return 0;
 }

@@ -241,7 +241,11 @@ class LayerNorm(nn.Module):
     self.dtype = canonical_dtype(dtype)
     self.scale = param_with_axes((features,), ones_init, ("embed",), device=device)
 
-  def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+  def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+              with_residual: bool = False):
+    """`with_residual`: returns (x, norm(x)); pass the first element on as the residual."""
+    if with_residual:
+      return F.residual_rmsnorm(x.to(self.dtype), self.scale, self.epsilon, out=out)
     return F.rmsnorm(x.to(self.dtype), self.scale, self.epsilon, out=out)
 
 

@@ -69,7 +69,7 @@ class EncoderLayer(nn.Module):
   def forward(self, x, *, bias_table, key_mask, segment_ids=None, enable_dropout=False):
     c = self.config
     drop = enable_dropout and c.dropout_rate > 0
-    h = self.pre_attention_layer_norm(x)
+    x, h = self.pre_attention_layer_norm(x, with_residual=True)
     if drop:
       a = self.attention(h, h, bias_table=bias_table, bidirectional=True,
                          num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance,
@@ -81,7 +81,7 @@ class EncoderLayer(nn.Module):
                          num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance,
                          key_mask=key_mask, q_segment_ids=segment_ids, kv_segment_ids=segment_ids,
                          residual=x)
-    h = self.pre_mlp_layer_norm(x)
+    x, h = self.pre_mlp_layer_norm(x, with_residual=True)
     if drop:
       x = x + _dropout(self.mlp(h, enable_dropout=True), c.dropout_rate, True)
     else:
@@ -94,13 +94,14 @@ class EncoderLayer(nn.Module):
     _mark_partial(self.pre_attention_layer_norm, self.pre_mlp_layer_norm)
     # each norm writes straight into this rank's rows of the buffer the next GEMM gathers
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
-    h = self.pre_attention_layer_norm(x_sp, out=dst)
+    x_sp, h = self.pre_attention_layer_norm(x_sp, out=dst, with_residual=True)
     x_sp = self.attention.forward_sp(
         h, x_sp, batch, length, h_block=blk, bias_table=bias_table, bidirectional=True,
         num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance, key_mask=key_mask,
         q_segment_ids=segment_ids, kv_segment_ids=segment_ids)
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
-    return self.mlp.forward_sp(self.pre_mlp_layer_norm(x_sp, out=dst), x_sp, h_block=blk)
+    x_sp, h = self.pre_mlp_layer_norm(x_sp, out=dst, with_residual=True)
+    return self.mlp.forward_sp(h, x_sp, h_block=blk)
 
 
 def _mark_partial(*norms) -> None:
@@ -135,7 +136,7 @@ class DecoderLayer(nn.Module):
     c = self.config
     drop = enable_dropout and c.dropout_rate > 0
     rate = c.dropout_rate
-    h = self.pre_self_attention_layer_norm(x)
+    x, h = self.pre_self_attention_layer_norm(x, with_residual=True)
     self_kwargs = dict(bias_table=bias_table, bidirectional=False,
                        num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance)
     if decode:
@@ -151,7 +152,7 @@ class DecoderLayer(nn.Module):
       x = self.self_attention(h, h, key_mask=decoder_key_mask, causal=True,
                               q_segment_ids=decoder_segment_ids,
                               kv_segment_ids=decoder_segment_ids, residual=x, **self_kwargs)
-    h = self.pre_cross_attention_layer_norm(x)
+    x, h = self.pre_cross_attention_layer_norm(x, with_residual=True)
     if decode:
       cross = cache["encoder_decoder_attention"]
       if "cross_key" not in cross:
@@ -170,7 +171,7 @@ class DecoderLayer(nn.Module):
       x = self.encoder_decoder_attention(h, encoded, key_mask=encoder_key_mask,
                                          q_segment_ids=decoder_segment_ids,
                                          kv_segment_ids=encoder_segment_ids, residual=x)
-    h = self.pre_mlp_layer_norm(x)
+    x, h = self.pre_mlp_layer_norm(x, with_residual=True)
     if drop:
       x = x + _dropout(self.mlp(h, enable_dropout=True), rate, True)
     else:
@@ -185,19 +186,20 @@ class DecoderLayer(nn.Module):
     _mark_partial(self.pre_self_attention_layer_norm, self.pre_cross_attention_layer_norm,
                   self.pre_mlp_layer_norm)
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
-    h = self.pre_self_attention_layer_norm(x_sp, out=dst)
+    x_sp, h = self.pre_self_attention_layer_norm(x_sp, out=dst, with_residual=True)
     x_sp = self.self_attention.forward_sp(
         h, x_sp, batch, length, h_block=blk, bias_table=bias_table, bidirectional=False,
         num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance,
         key_mask=decoder_key_mask, causal=True, q_segment_ids=decoder_segment_ids,
         kv_segment_ids=decoder_segment_ids)
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
-    h = self.pre_cross_attention_layer_norm(x_sp, out=dst)
+    x_sp, h = self.pre_cross_attention_layer_norm(x_sp, out=dst, with_residual=True)
     x_sp = self.encoder_decoder_attention.forward_sp(
         h, x_sp, batch, length, kv_full=encoded, h_block=blk, key_mask=encoder_key_mask,
         q_segment_ids=decoder_segment_ids, kv_segment_ids=encoder_segment_ids)
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
-    return self.mlp.forward_sp(self.pre_mlp_layer_norm(x_sp, out=dst), x_sp, h_block=blk)
+    x_sp, h = self.pre_mlp_layer_norm(x_sp, out=dst, with_residual=True)
+    return self.mlp.forward_sp(h, x_sp, h_block=blk)
 
 
 class Encoder(nn.Module):

@@ -151,6 +151,47 @@ class _RmsNormFn(torch.autograd.Function):
     return dx, ret, None, None
 
 
+class _ResidualRmsNormFn(torch.autograd.Function):
+  """x -> (x, rmsnorm(x)): the first output is the residual branch. Its gradient is added to
+  the norm's input gradient inside the backward kernel instead of by a separate elementwise
+  add over the activations."""
+
+  @staticmethod
+  def forward(ctx, x, scale, eps, out=None):
+    xc = x.contiguous()
+    y, rstd = native.rmsnorm_fwd(xc, scale.float(), eps, out=out)
+    ctx.save_for_backward(xc, scale, rstd)
+    return x.view_as(x), y
+
+  @staticmethod
+  def backward(ctx, dres, dy):
+    x, scale, rstd = ctx.saved_tensors
+    if dy is None:
+      return dres, None, None, None
+    mg = getattr(scale, "main_grad", None)
+    if mg is not None:
+      if not getattr(scale, "grad_ready", False):
+        mg.zero_()
+        scale.grad_ready = True
+      dscale_buf, ret = mg, None
+    else:
+      dscale_buf = torch.zeros_like(scale, dtype=torch.float32)
+      ret = dscale_buf
+    if dres is not None:
+      dres = dres.to(torch.bfloat16).contiguous()
+    dx = native.rmsnorm_bwd(dy.contiguous(), x, scale.float(), rstd, dres, dscale_buf)
+    return dx, ret, None, None
+
+
+def residual_rmsnorm(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6,
+                     out: Optional[torch.Tensor] = None):
+  """(x, rmsnorm(x)); use the first element as the residual input of the block the norm
+  feeds, so that the two gradient paths into x meet inside the norm's backward kernel."""
+  if _native_ok(x):
+    return _ResidualRmsNormFn.apply(x, scale, eps, out)
+  return x, ref.rmsnorm(x, scale, eps)
+
+
 def rmsnorm(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6,
             out: Optional[torch.Tensor] = None) -> torch.Tensor:
   """`out` (CUDA path only): a bf16 buffer of x's shape that receives the result."""
