@@ -433,22 +433,50 @@ __global__ void __launch_bounds__(256)
                       float* __restrict__ delta, int B, int H, int Lq, long long do_sb,
                       long long do_sl, long long do_sh, long long o_sb, long long o_sl,
                       long long o_sh) {
-  // one warp per (b, q, h): 64 elements -> 2 per lane
+  // eight lanes per (b, q, h): 64 elements -> one 16-byte load per lane and tensor; four items
+  // in flight per thread. Requires 16-byte aligned rows (strides multiples of 8 elements).
   const long long total = static_cast<long long>(B) * Lq * H;
-  const int lane = threadIdx.x & 31;
-  for (long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; w < total;
-       w += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
-    const int hh = static_cast<int>(w % H);
-    const long long t = w / H;
-    const int q = static_cast<int>(t % Lq);
-    const int bb = static_cast<int>(t / Lq);
-    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(
-        dO + bb * do_sb + static_cast<long long>(q) * do_sl + hh * do_sh + lane * 2);
-    const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(
-        O + bb * o_sb + static_cast<long long>(q) * o_sl + hh * o_sh + lane * 2);
-    const float2 fa = __bfloat1622float2(a), fc = __bfloat1622float2(c);
-    float s = warp_sum(fa.x * fc.x + fa.y * fc.y);
-    if (lane == 0) delta[(static_cast<long long>(bb) * H + hh) * Lq + q] = s;
+  const int sub = threadIdx.x & 7;
+  const long long first = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 3;
+  const long long stride = (static_cast<long long>(gridDim.x) * blockDim.x) >> 3;
+  // the four 8-lane groups of a warp leave the loop together (the shuffles use the full mask)
+  const int group = (threadIdx.x & 31) >> 3;
+  for (long long w0 = first; w0 - group < total; w0 += 4 * stride) {
+    uint4 a[4], c[4];
+    long long out[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long w = w0 + u * stride;
+      out[u] = -1;
+      if (w < total) {
+        const int hh = static_cast<int>(w % H);
+        const long long t = w / H;
+        const int q = static_cast<int>(t % Lq);
+        const int bb = static_cast<int>(t / Lq);
+        a[u] = *reinterpret_cast<const uint4*>(dO + bb * do_sb + static_cast<long long>(q) * do_sl +
+                                               hh * do_sh + sub * 8);
+        c[u] = *reinterpret_cast<const uint4*>(O + bb * o_sb + static_cast<long long>(q) * o_sl +
+                                               hh * o_sh + sub * 8);
+        out[u] = (static_cast<long long>(bb) * H + hh) * Lq + q;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float s = 0.f;
+      if (out[u] >= 0) {
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a[u]);
+        const __nv_bfloat162* pc = reinterpret_cast<const __nv_bfloat162*>(&c[u]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fa = __bfloat1622float2(pa[j]), fc = __bfloat1622float2(pc[j]);
+          s += fa.x * fc.x + fa.y * fc.y;
+        }
+      }
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      if (sub == 0 && out[u] >= 0) delta[out[u]] = s;
+    }
   }
 }
 
@@ -952,8 +980,10 @@ T5X_API int t5x_attention_bwd(const void* q, const void* k, const void* v, const
   const CUtensorMap* tdo = bhld_map(d_o, B, Lq, H, do_sb, do_sl, do_sh);
   if (!tq || !tk || !tv || !tdo) return -1;
   {
-    long long warps = static_cast<long long>(B) * Lq * H;
-    long long blocks = (warps * 32 + 255) / 256;
+    if ((do_sb | do_sl | do_sh | o_sb | o_sl | o_sh) & 7)
+      return set_error("attention_bwd: dO / O strides must be multiples of 8 elements");
+    long long items = static_cast<long long>(B) * Lq * H;
+    long long blocks = (items * 8 / 4 + 255) / 256;
     long long cap = static_cast<long long>(num_sms()) * 8;
     attn_delta_kernel<<<static_cast<int>(blocks > cap ? cap : blocks), 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(o),

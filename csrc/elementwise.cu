@@ -183,22 +183,31 @@ __global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 4 : 2)
   }
 }
 
-// dscale[j] += sum over the CTAs of partial[cta][j]
+// dscale[j] += sum over the CTAs of partial[cta][j]. One CTA per 32 features: 8 warps split the
+// `parts` rows between them (each load is one 128-byte line), then add up through shared memory.
 __global__ void __launch_bounds__(256)
     rmsnorm_dscale_reduce_kernel(const float* __restrict__ partial, int parts, int d,
                                  float* __restrict__ dscale) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= d) return;
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  int p = 0;
-  for (; p + 3 < parts; p += 4) {
-    a0 += partial[static_cast<long long>(p) * d + j];
-    a1 += partial[static_cast<long long>(p + 1) * d + j];
-    a2 += partial[static_cast<long long>(p + 2) * d + j];
-    a3 += partial[static_cast<long long>(p + 3) * d + j];
+  __shared__ float red[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + lane;
+  float a0 = 0.f, a1 = 0.f;
+  if (j < d) {
+    int p = warp;
+    for (; p + 8 < parts; p += 16) {
+      a0 += partial[static_cast<long long>(p) * d + j];
+      a1 += partial[static_cast<long long>(p + 8) * d + j];
+    }
+    if (p < parts) a0 += partial[static_cast<long long>(p) * d + j];
   }
-  for (; p < parts; ++p) a0 += partial[static_cast<long long>(p) * d + j];
-  dscale[j] += (a0 + a1) + (a2 + a3);
+  red[warp][lane] = a0 + a1;
+  __syncthreads();
+  if (warp == 0 && j < d) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][lane];
+    dscale[j] += t;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -387,7 +396,7 @@ T5X_API int t5x_rmsnorm_bwd(const void* dy, const void* x, const void* scale, co
   else launch(rmsnorm_bwd_kernel<4>);
   if (dscale != nullptr) {
     count_launches(1);
-    rmsnorm_dscale_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, grid, d,
+    rmsnorm_dscale_reduce_kernel<<<(d + 31) / 32, 256, 0, st>>>(partial, grid, d,
                                                                   static_cast<float*>(dscale));
   }
   CHECK_LAUNCH("rmsnorm_bwd");
