@@ -123,7 +123,9 @@ def main() -> None:
   ap.add_argument("--steps", type=int, default=3)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-  ap.add_argument("--model", default="xxl", choices=sorted(MODEL_SIZES))
+  ap.add_argument("--model", default="xxl", choices=sorted(MODEL_SIZES) + ["switch-base"],
+                  help="a T5.1.1 size, or switch-base: T5.1.1-Base with every other FFN replaced "
+                       "by 8 top-1 experts, expert-parallel over all ranks")
   ap.add_argument("--batch", type=int, default=128)
   ap.add_argument("--inputs-length", type=int, default=512)
   ap.add_argument("--targets-length", type=int, default=114)
@@ -164,31 +166,53 @@ def main() -> None:
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local_rank)
   pstate.init_distributed("nccl")
-  st = pstate.setup_mesh(model_size=world if args.parallelism == "tp" else 1)
+  moe = args.model == "switch-base"
+  if moe and (args.parallelism == "tp" or 8 % world):
+    raise SystemExit("switch-base runs expert-parallel on 1, 2, 4 or 8 GPUs")
+  st = pstate.setup_mesh(model_size=world if args.parallelism == "tp" else 1,
+                         expert_size=world if moe else 1)
   data_shards = 1 if args.parallelism == "tp" else world
   if args.batch % data_shards:
     raise SystemExit(f"--batch {args.batch} is not divisible by {data_shards} data shards")
   dev = st.device
   rank = st.rank
 
-  emb, heads, layers, head_dim, mlp = MODEL_SIZES[args.model]
-  cfg = network.T5Config(vocab_size=32128, dtype="bfloat16", emb_dim=emb, num_heads=heads,
-                         num_encoder_layers=layers, num_decoder_layers=layers, head_dim=head_dim,
-                         mlp_dim=mlp, mlp_activations=("gelu", "linear"), dropout_rate=0.0,
-                         logits_via_embedding=False)
+  emb, heads, layers, head_dim, mlp = MODEL_SIZES["base" if moe else args.model]
+  common = dict(vocab_size=32128, dtype="bfloat16", emb_dim=emb, num_heads=heads,
+                num_encoder_layers=layers, num_decoder_layers=layers, head_dim=head_dim,
+                mlp_dim=mlp, mlp_activations=("gelu", "linear"), dropout_rate=0.0,
+                logits_via_embedding=False)
   torch.manual_seed(1234)
-  module = network.Transformer(cfg, device=dev)
   vocab = vocabularies.PassThroughVocabulary(32128)
-  opt = adafactor.Adafactor(decay_rate=0.8, step_offset=0,
-                            logical_factor_rules=adafactor.standard_logical_factor_rules())
-  model = models.EncoderDecoderModel(module, vocab, vocab, opt, z_loss=1e-4,
-                                     loss_normalizing_factor=None)
+  if moe:
+    from t5x_b200.contrib.moe import adafactor_utils, models as moe_models, network as moe_network
+    cfg = moe_network.MoeT5Config(num_experts=8, num_selected_experts=1,
+                                  train_capacity_factor=1.25, sparse_layout="every_other",
+                                  **common)
+    module = moe_network.Transformer(cfg, device=dev)
+    opt = adafactor.Adafactor(decay_rate=0.8, step_offset=0,
+                              logical_factor_rules=adafactor_utils.logical_factor_rules())
+    model = moe_models.MoeEncoderDecoderModel(module, vocab, vocab, opt, z_loss=1e-4,
+                                              loss_normalizing_factor=None, aux_loss_factor=1e-2,
+                                              router_z_loss_factor=1e-3)
+  else:
+    cfg = network.T5Config(**common)
+    module = network.Transformer(cfg, device=dev)
+    opt = adafactor.Adafactor(decay_rate=0.8, step_offset=0,
+                              logical_factor_rules=adafactor.standard_logical_factor_rules())
+    model = models.EncoderDecoderModel(module, vocab, vocab, opt, z_loss=1e-4,
+                                       loss_normalizing_factor=None)
   state = ts_lib.FlaxOptimTrainState.create(opt, model.get_initial_variables(None, None))
   # tensor-parallel ranks all work on the same microbatch: 32 sequences at a time for XXL
   n_micro = args.microbatches or (default_microbatches(args.model, 2) if args.parallelism == "tp"
                                   else default_microbatches(args.model, world))
   lr_fn = schedules.create_learning_rate_scheduler("constant * rsqrt_decay", 1.0, 10000)
-  trainer = trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, n_micro)
+  if moe:
+    from t5x_b200.contrib.moe import trainer as moe_trainer
+    trainer = moe_trainer.MoeTrainer(model, state, None, [], None, None, 0, lr_fn, n_micro,
+                                     num_expert_partitions=world)
+  else:
+    trainer = trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, n_micro)
   n_params = sum(int(np.prod(getattr(p, "global_shape", p.shape))) for p in module.parameters())
 
   # Tensor-parallel ranks all consume the global batch; data-parallel ranks each take a shard.
@@ -293,18 +317,22 @@ def main() -> None:
 
   if rank == 0:
     out = {
-        "metric": f"T5.1.1-{args.model.upper()} train tokens/s",
+        "metric": ("Switch-Base-8 train tokens/s" if moe else
+                   f"T5.1.1-{args.model.upper()} train tokens/s"),
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong",
-        "vs_baseline": value / (BASELINE_TOKENS_PER_S_PER_GPU * world),
+        # the published figure is for XXL; other models have none
+        "vs_baseline": (value / (BASELINE_TOKENS_PER_S_PER_GPU * world)
+                        if args.model == "xxl" else None),
         "dtype": "bf16", "data": "synthetic span-corruption tokens, random-init weights",
         "impl": "ours",
-        "config": {"model": f"t5.1.1-{args.model}", "params": n_params,
+        "config": {"model": "switch-base-8" if moe else f"t5.1.1-{args.model}", "params": n_params,
                    "global_batch": args.batch, "seq_len": args.inputs_length + args.targets_length,
                    "inputs_length": args.inputs_length, "targets_length": args.targets_length,
-                   "parallelism": (f"data1 x model{world}" if args.parallelism == "tp" else
-                                   f"data{world} x model1" +
+                   "parallelism": (f"expert{world} (tokens data-parallel over the same ranks)"
+                                   if moe else f"data1 x model{world}"
+                                   if args.parallelism == "tp" else f"data{world} x model1" +
                                    (", optimizer sharded over data" if world > 1 else "")),
                    "optimizer": "adafactor",
                    "num_microbatches": n_micro,
