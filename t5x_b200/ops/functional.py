@@ -39,7 +39,12 @@ def _accumulate_wgrad(weight: torch.Tensor, a_t: torch.Tensor, b: torch.Tensor):
   mg = getattr(weight, "main_grad", None)
   if mg is not None:
     first = not getattr(weight, "grad_ready", False)
-    native.gemm(a_t, b, out=mg.view(a_t.shape[0], b.shape[1]), accumulate=not first)
+    out = mg.view(a_t.shape[0], b.shape[1])
+    splits = native.wgrad_splits(a_t.shape[0], b.shape[1], a_t.shape[1])
+    if splits > 1 and out.is_contiguous():
+      native.gemm_splitk_accumulate(a_t, b, out, splits, accumulate=not first)
+    else:
+      native.gemm(a_t, b, out=out, accumulate=not first)
     weight.grad_ready = True
     return None
   return native.gemm(a_t, b, out_dtype=torch.float32).view(weight.shape).to(weight.dtype)

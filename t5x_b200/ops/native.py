@@ -267,6 +267,45 @@ def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, *,
   return out
 
 
+def wgrad_splits(M: int, N: int, K: int) -> int:
+  """How many K slices a weight-gradient GEMM [M, K] @ [K, N] should be cut into: 1 unless
+  the output has too few tiles to occupy the SMs and K is long (small models: a 768 x 768
+  gradient over 131072 tokens is 18 output tiles)."""
+  tiles = -(-M // 128) * -(-N // 256)
+  sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+  if tiles * 2 > sms or K < 8192:
+    return 1
+  splits = min(sms // tiles, K // 2048)
+  while splits > 1 and (K % splits or (K // splits) % 64):
+    splits -= 1
+  return max(1, splits)
+
+
+def gemm_splitk_accumulate(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, splits: int,
+                           accumulate: bool) -> torch.Tensor:
+  """out[M, N] (fp32) (+)= a[M, K] @ b[K, N] with K cut into `splits` slices whose products
+  are added atomically into `out` (cleared first unless `accumulate`). Operand layouts as in
+  `gemm`."""
+  assert out.dtype == torch.float32 and out.is_contiguous()
+  M, K = a.shape
+  N = b.shape[1]
+  ks = K // splits
+  a_mn, lda, _ = _mat_layout(a, M, K)
+  if b.stride(-2) == 1:
+    b_mn, ldb = 0, b.stride(-1)
+  else:
+    b_mn, ldb = 1, b.stride(-2)
+  a_step = ks * lda if a_mn else ks       # elements between consecutive K slices
+  b_step = ks * ldb if b_mn else ks
+  if not accumulate:
+    out.zero_()
+  rc = lib().t5x_gemm_bf16(
+      a.data_ptr(), b.data_ptr(), 0, out.data_ptr(), M, N, ks, splits, lda, ldb, N, a_step,
+      b_step, 0, a_mn, b_mn, 1, 2, EPI_PLAIN, 0, 0, 0, 0, 0, 0, 1.0, 0, stream_ptr())
+  _check(rc, "gemm_splitk_accumulate")
+  return out
+
+
 def gemm_set_pair_mode(mode: int) -> None:
   """0: one CTA per tile always; 1: CTA pairs (256 x 256 tiles) where the shape suits them
   (default); 2: CTA pairs always."""

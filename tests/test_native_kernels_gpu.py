@@ -226,3 +226,23 @@ def test_adafactor_unfactored(N):
   u = u / torch.clamp(u.pow(2).mean().sqrt(), min=1.0)
   pn = p0 - 0.01 * torch.clamp(p0.pow(2).mean().sqrt(), min=1e-3) * u
   assert rel(p, pn) < 1e-5 and rel(v, nv) < 1e-5
+
+
+@pytest.mark.parametrize("shape", [(768, 768, 16384), (768, 2048, 8192), (320, 200, 12288)])
+def test_weight_gradient_split_k(N, shape):
+  """dW (+)= x^T dy with K cut into slices that add into the fp32 output atomically."""
+  M, Nn, K = shape
+  torch.manual_seed(0)
+  x = torch.randn(K, M, device="cuda").to(torch.bfloat16)       # activations [tokens, in]
+  dy = torch.randn(K, Nn, device="cuda").to(torch.bfloat16)     # [tokens, out]
+  splits = N.wgrad_splits(M, Nn, K)
+  assert splits > 1
+  want = x.float().t() @ dy.float()
+  out = torch.full((M, Nn), 7.0, device="cuda")
+  N.gemm_splitk_accumulate(x.t(), dy, out, splits, accumulate=False)
+  assert rel(out, want) < BF16_TOL
+  N.gemm_splitk_accumulate(x.t(), dy, out, splits, accumulate=True)
+  assert rel(out, 2 * want) < BF16_TOL
+  # large outputs keep the single-pass kernel
+  assert N.wgrad_splits(4096, 4096, 8192) == 1
+  N.check_status()
