@@ -211,6 +211,148 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---------------------------------------------------------------------------
+// RMSNorm for narrow rows (d <= 1024): one warp per row, eight rows per CTA, reductions by
+// shuffles only. With one CTA per row most of its 256 threads would idle (d = 768 is 96
+// 16-byte vectors) and every row would cost three block barriers.
+// ---------------------------------------------------------------------------
+constexpr int kNormWarpMaxVec = 4;  // 32 lanes x 4 vectors x 8 = 1024 features
+
+__global__ void __launch_bounds__(kNormThreads)
+    rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                            __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int rows,
+                            int d, float eps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = d / 8;
+  const int wpb = kNormThreads / 32;
+  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
+    const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + static_cast<long long>(row) * d);
+    float vals[kNormWarpMaxVec][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormWarpMaxVec; ++i) {
+      const int v = lane + i * 32;
+      if (v < nvec) {
+        unpack8(xr[v], vals[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / static_cast<float>(d) + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    Bf16x8* yr = reinterpret_cast<Bf16x8*>(y + static_cast<long long>(row) * d);
+#pragma unroll
+    for (int i = 0; i < kNormWarpMaxVec; ++i) {
+      const int v = lane + i * 32;
+      if (v < nvec) {
+        const float4 s0 = reinterpret_cast<const float4*>(scale)[2 * v];
+        const float4 s1 = reinterpret_cast<const float4*>(scale)[2 * v + 1];
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * sc[j];
+        yr[v] = pack8(o);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kNormThreads)
+    rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                            const float* __restrict__ scale, const float* __restrict__ rstd_in,
+                            const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                            float* __restrict__ partial, int rows, int d) {
+  __shared__ float sacc[kNormThreads / 32][kNormWarpMaxVec * 32 * 8 / 4];  // one quarter at a time
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = d / 8;
+  const int wpb = kNormThreads / 32;
+  float ds_acc[kNormWarpMaxVec][8];
+#pragma unroll
+  for (int i = 0; i < kNormWarpMaxVec; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ds_acc[i][j] = 0.f;
+  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
+    const long long off = static_cast<long long>(row) * d;
+    const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + off);
+    const Bf16x8* dyr = reinterpret_cast<const Bf16x8*>(dy + off);
+    Bf16x8 xp[kNormWarpMaxVec], dyp[kNormWarpMaxVec];
+#pragma unroll
+    for (int i = 0; i < kNormWarpMaxVec; ++i) {
+      const int v = lane + i * 32;
+      if (v < nvec) {
+        xp[i] = xr[v];
+        dyp[i] = dyr[v];
+      }
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormWarpMaxVec; ++i) {
+      const int v = lane + i * 32;
+      if (v < nvec) {
+        float xv[8], dyv[8];
+        unpack8(xp[i], xv);
+        unpack8(dyp[i], dyv);
+        const float4 s0 = reinterpret_cast<const float4*>(scale)[2 * v];
+        const float4 s1 = reinterpret_cast<const float4*>(scale)[2 * v + 1];
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float t = dyv[j] * xv[j];
+          ds_acc[i][j] += t * rstd;
+          dot += t * sc[j];
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    const float c = dot / static_cast<float>(d) * rstd * rstd;
+    Bf16x8* dxr = reinterpret_cast<Bf16x8*>(dx + off);
+    const Bf16x8* rr = dres ? reinterpret_cast<const Bf16x8*>(dres + off) : nullptr;
+#pragma unroll
+    for (int i = 0; i < kNormWarpMaxVec; ++i) {
+      const int v = lane + i * 32;
+      if (v < nvec) {
+        float xv[8], dyv[8], o[8];
+        unpack8(xp[i], xv);
+        unpack8(dyp[i], dyv);
+        const float4 s0 = reinterpret_cast<const float4*>(scale)[2 * v];
+        const float4 s1 = reinterpret_cast<const float4*>(scale)[2 * v + 1];
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (dyv[j] * sc[j] - xv[j] * c);
+        if (rr) {
+          float r8[8];
+          unpack8(rr[v], r8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r8[j];
+        }
+        dxr[v] = pack8(o);
+      }
+    }
+  }
+  if (partial) {
+    // the eight warps hold sums for the same features: add them through shared memory, one
+    // vector slot (32 lanes x 8 features) at a time
+    float* out = partial + static_cast<long long>(blockIdx.x) * d;
+#pragma unroll
+    for (int i = 0; i < kNormWarpMaxVec; ++i) {
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sacc[warp][lane * 8 + j] = ds_acc[i][j];
+      __syncthreads();
+      const int f = threadIdx.x;  // feature within the slot: 256 per slot
+      const int col = i * 256 + f;
+      if (col < d) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNormThreads / 32; ++w) t += sacc[w][f];
+        out[col] = t;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Gated-GELU backward. h = [h0 | h1] with row stride ldh (h1 at column offset `dff`).
 //   in : dg [T, dff] (grad of g = gelu(h0) * h1)
 //   out: h0 <- dg * h1 * gelu'(h0) ; h1 <- dg * gelu(h0) ; dg <- g  (recomputed activation,
@@ -353,6 +495,16 @@ T5X_API int t5x_rmsnorm_fwd(const void* x, const void* scale, void* y, void* rst
   if (d % 8 || d > kNormThreads * 8 * kNormMaxVec)
     return set_error("rmsnorm: d=%d must be a multiple of 8 and <= %d", d,
                      kNormThreads * 8 * kNormMaxVec);
+  if (d <= kNormWarpMaxVec * 32 * 8) {  // narrow rows: one warp per row
+    const int wpb = kNormThreads / 32;
+    int blocks = (rows + wpb - 1) / wpb;
+    if (blocks > num_sms() * 8) blocks = num_sms() * 8;
+    rmsnorm_fwd_warp_kernel<<<blocks, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(scale),
+        static_cast<__nv_bfloat16*>(y), static_cast<float*>(rstd), rows, d, eps);
+    CHECK_LAUNCH("rmsnorm_fwd");
+    return 0;
+  }
   int grid = rows < num_sms() * 8 ? rows : num_sms() * 8;
   rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(scale),
@@ -391,7 +543,13 @@ T5X_API int t5x_rmsnorm_bwd(const void* dy, const void* x, const void* scale, co
         static_cast<const float*>(scale), static_cast<const float*>(rstd),
         static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), partial, rows, d);
   };
-  if (nv == 1) launch(rmsnorm_bwd_kernel<1>);
+  if (d <= kNormWarpMaxVec * 32 * 8) {  // narrow rows: one warp per row, eight rows per CTA
+    const int wpb = kNormThreads / 32;
+    grid = (rows + wpb - 1) / wpb;
+    if (grid > num_sms() * 4) grid = num_sms() * 4;
+    if (grid > kMaxParts) grid = kMaxParts;
+    launch(rmsnorm_bwd_warp_kernel);
+  } else if (nv == 1) launch(rmsnorm_bwd_kernel<1>);
   else if (nv == 2) launch(rmsnorm_bwd_kernel<2>);
   else launch(rmsnorm_bwd_kernel<4>);
   if (dscale != nullptr) {

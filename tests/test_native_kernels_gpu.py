@@ -113,7 +113,7 @@ def test_gemm_epilogues(N):
 
 def test_rmsnorm(N):
   torch.manual_seed(2)
-  for T, d in [(1000, 4096), (77, 512), (33, 768)]:
+  for T, d in [(1000, 4096), (77, 512), (33, 768), (5000, 768), (300, 1024), (64, 2048), (40, 8192)]:
     x = torch.randn(T, d, device="cuda").bfloat16()
     sc = torch.rand(d, device="cuda") + 0.5
     y, rstd = N.rmsnorm_fwd(x, sc, 1e-6)
