@@ -95,3 +95,32 @@ def test_two_way_tensor_parallel_matches_single(tmp_path):
     a, b = got["params"][n], p.detach()
     assert a.shape == b.shape, n
     assert torch.allclose(a, b, rtol=2e-3, atol=2e-5), (n, (a - b).abs().max().item())
+
+
+def test_symmetric_arena_allocator_is_deterministic_and_coalesces():
+  """The first-fit allocator of the fused tensor-parallel path: every rank runs the same
+  sequence, so offsets must depend on the sequence only; freed neighbours merge again."""
+  from t5x_b200.parallel import tp_fused
+  ar = object.__new__(tp_fused.SymmetricArena)
+  ar.free = [(0, 1 << 20)]
+  a = ar.alloc(1000)          # rounded up to the 1024-byte granule
+  b = ar.alloc(5000)
+  c = ar.alloc(1024)
+  assert (a.offset, a.size) == (0, 1024)
+  assert (b.offset, b.size) == (1024, 5120)
+  assert c.offset == 6144
+  b.release()
+  d = ar.alloc(2048)          # first fit: the hole left by b
+  assert d.offset == 1024
+  e = ar.alloc(4096)          # does not fit the remaining 3072-byte hole
+  assert e.offset == 7168
+  for blk in (a, c, d, e):
+    blk.release()
+  assert ar.free == [(0, 1 << 20)]
+  b.release()                 # releasing twice is a no-op
+  assert ar.free == [(0, 1 << 20)]
+  f = ar.alloc(1 << 20)
+  with pytest.raises(RuntimeError, match="arena exhausted"):
+    ar.alloc(1)
+  del f                       # dropping the block returns it
+  assert ar.free == [(0, 1 << 20)]
