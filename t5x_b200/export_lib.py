@@ -56,6 +56,36 @@ def create_preprocessor(output_features: Mapping[str, Any],
   return preprocess
 
 
+def create_preprocessor_from_task(model=None, task_feature_lengths: Mapping[str, int] = None,
+                                  task_name: str = None, serialized_examples: bool = True,
+                                  run_precache: bool = False, **_) -> Callable:
+  """Serving preprocessor that takes whole examples of a registered task instead of bare
+  input strings (role of t5x/export_lib.py `create_preprocessor_from_task`): each request is
+  a feature dictionary (a JSON string of one when `serialized_examples`) whose text features
+  are tokenised with the task's vocabularies and trimmed to `task_feature_lengths`."""
+  from t5x_b200.data import tasks as tasks_lib
+  features = tasks_lib.get_mixture_or_task(task_name).output_features
+
+  def preprocess(items: Sequence[Any]) -> List[dict]:
+    out = []
+    for item in items:
+      if serialized_examples and isinstance(item, (str, bytes)):
+        item = json.loads(item)
+      ex = {}
+      for name, feat in features.items():
+        value = item.get(name, [] if name != "inputs" else "")
+        ids = list(feat.vocabulary.encode(value)) if isinstance(value, str) else list(value)
+        limit = (task_feature_lengths or {}).get(name)
+        if getattr(feat, "add_eos", True) and name == "inputs":
+          ids = (ids[:limit - 1] if limit else ids) + [feat.vocabulary.eos_id]
+        ex[name] = np.asarray(ids[:limit] if limit else ids, np.int32)
+      ex.setdefault("targets", np.zeros((0,), np.int32))
+      out.append(ex)
+    return out
+
+  return preprocess
+
+
 def create_postprocessor(vocab, inference_mode: str = "predict", tokenized_outputs: bool = False,
                          output_feature_names: Optional[Sequence[str]] = None) -> Callable:
   def postprocess(values, aux=None):
@@ -161,7 +191,8 @@ def save(*, model: models.BaseTransformerModel, inference_mode: str,
          task_feature_lengths: Mapping[str, int] = None, batch_size: Optional[int] = None,
          output_dir: str = None, model_name: str = "model", warmup_examples=None,
          tokenized_inputs: bool = False, tokenized_outputs: bool = False,
-         export_dtype: str = "bfloat16", version: Optional[int] = None, **_):
+         export_dtype: str = "bfloat16", version: Optional[int] = None,
+         mixture_or_task_name: Optional[str] = None, **_):
   """Restores the checkpoint and writes the inference bundle; returns its directory."""
   partitioner = partitioner or partitioning.PjitPartitioner(num_partitions=1)
   bs = batch_size or 1
@@ -189,6 +220,7 @@ def save(*, model: models.BaseTransformerModel, inference_mode: str,
                "batch_size": batch_size, "dtype": export_dtype,
                "step": int(utils.get_local_data(state.step)),
                "tokenized_inputs": tokenized_inputs, "tokenized_outputs": tokenized_outputs,
+               "mixture_or_task_name": mixture_or_task_name,
                "polymorphic_shapes": create_polymorphic_shapes_fn(input_shapes)}, f, indent=1)
   write_warmup_example_fn(bs, bundle, model_name,
                           input_texts=warmup_examples or ("hello world",))
@@ -218,7 +250,10 @@ def load(bundle_dir: str, model: models.BaseTransformerModel,
   if output_features is None:
     output_features = {"inputs": tasks_lib.Feature(model.input_vocabulary),
                        "targets": tasks_lib.Feature(model.output_vocabulary)}
-  pre = create_preprocessor(output_features, lengths, sig.get("tokenized_inputs", False))
+  if sig.get("mixture_or_task_name"):
+    pre = create_preprocessor_from_task(model, lengths, sig["mixture_or_task_name"])
+  else:
+    pre = create_preprocessor(output_features, lengths, sig.get("tokenized_inputs", False))
   fn = create_inference_function(model=model, inference_mode=sig["inference_mode"])
   post = create_postprocessor(model.output_vocabulary, sig["inference_mode"],
                               sig.get("tokenized_outputs", False))

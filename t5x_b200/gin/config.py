@@ -44,7 +44,7 @@ MODULE_ALIASES = {
     "t5x.contrib.moe": "t5x_b200.contrib.moe",
     "t5x.contrib.calm": "t5x_b200.contrib.calm",
     "seqio": "t5x_b200.data.seqio_api",
-    "optax": "t5x_b200.optimizers",
+    "optax": "t5x_b200.optax_api",
 }
 # Imports that only register datasets / are unavailable offline: ignored when missing.
 OPTIONAL_IMPORT_PREFIXES = ("t5.", "t5", "tensorflow", "tensorflow_datasets", "flaxformer",
@@ -406,7 +406,7 @@ def _split_binding_key(key: str):
 _TOKEN = re.compile(r"""
     (?P<ws>\s+)
   | (?P<str>(?:[rRbBuU]{0,2})(?:'''(?:\\.|[^\\])*?'''|\"\"\"(?:\\.|[^\\])*?\"\"\"|'(?:\\.|[^'\\\n])*'|"(?:\\.|[^"\\\n])*"))
-  | (?P<num>[+-]?(?:0[xX][0-9a-fA-F]+|(?:\d+\.\d*|\.\d+|\d+)(?:[eE][+-]?\d+)?j?))
+  | (?P<num>[+-]?(?:0[xX][0-9a-fA-F]+|(?:\d[\d_]*\.[\d_]*|\.\d[\d_]*|\d[\d_]*)(?:[eE][+-]?\d+)?j?))
   | (?P<ref>@[A-Za-z_][\w./]*(?:\(\))?)
   | (?P<macro>%[A-Za-z_][\w.]*)
   | (?P<name>[A-Za-z_][\w.]*)

@@ -50,3 +50,59 @@ def test_run_file_parses(path):
   files = ["t5x/examples/t5/t5_1_1/tiny.gin", path]
   gin.parse_config_files_and_bindings(files, ["DROPOUT_RATE = 0.0"], finalize_config=False)
   assert gin.query_parameter("partitioning.PjitPartitioner.num_partitions") == 1
+
+
+def _main_module_for(path):
+  from t5x_b200 import eval as eval_lib, infer, precompile, train
+  base = os.path.basename(path)
+  if "eval" in base and "train_eval" not in base:
+    return eval_lib
+  if "infer" in base:
+    return infer
+  if "precompile" in base:
+    return precompile
+  return train
+
+
+# Every other shipped file: the GPU-contrib tree, scalable_t5 / uMT5, the example runs and the
+# MoE run files. Model files need DROPOUT_RATE; run files and examples parse on top of the
+# model they include (or of a tiny model when they are pure run files).
+_COVERED = set(MODEL_FILES) | set(RUN_FILES)
+OTHER_FILES = sorted(p for p in glob.glob(os.path.join(PKG, "**", "*.gin"), recursive=True)
+                     if p not in _COVERED)
+
+
+@pytest.mark.parametrize("path", OTHER_FILES, ids=lambda p: os.path.relpath(p, PKG))
+def test_every_other_gin_file_parses(path):
+  rel = os.path.relpath(path, PKG)
+  gin.set_main_module(_main_module_for(path))
+  text = open(path).read()
+  files = [path]
+  pure_run = ("/runs/" in rel.replace(os.sep, "/") and "umt5" not in rel)
+  fragment = any(s in rel for s in ("umt5/architectures", "umt5/optimizer", "umt5/vocab",
+                                    "umt5/runs", "adamw_opt", "local_tiny", "encdec_common"))
+  if fragment:
+    # fragments are meant to be included next to a model: check them in such a composition
+    model = ("t5x/examples/scalable_t5/mt5/small.gin" if "scalable_t5" in rel
+             else "t5x/examples/t5/t5_1_1/tiny.gin")
+    run = "t5x/configs/runs/pretrain.gin" if "finetuning_common" not in rel else None
+    files = [model] + ([run] if run and "umt5/runs" not in rel else []) + [path]
+    if "umt5/architectures" in rel:
+      files.append("t5x/examples/scalable_t5/umt5/vocab.gin")
+  elif pure_run:
+    model = ("t5x/contrib/moe/configs/models/switch_base.gin" if "contrib/moe" in rel
+             else "t5x/examples/t5/t5_1_1/tiny.gin")
+    files = [model, path]
+  gin.parse_config_files_and_bindings(files, ["DROPOUT_RATE = 0.0"], finalize_config=False)
+  assert "include" in text or "=" in text
+
+
+def test_optax_names_bind_gradient_transformations():
+  from t5x_b200 import optimizers
+  gin.parse_config_files_and_bindings(
+      ["t5x/examples/t5/t5_1_1/tiny.gin", "t5x/contrib/gpu/t5/t5_1_1/adamw_opt.gin"],
+      ["DROPOUT_RATE = 0.0"], finalize_config=False)
+  from t5x_b200.gin import config as gin_config
+  opt = gin_config._materialize(gin.query_parameter("%OPTIMIZER"))
+  assert isinstance(opt, optimizers.OptaxWrapper)
+  assert gin.query_parameter("network.T5Config.scale_attn_logits") is True
