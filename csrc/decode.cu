@@ -176,7 +176,7 @@ constexpr int kCrossThreads = kCrossWarps * 32;
 constexpr int kCrossMaxKeys = 1024;
 
 template <int BEAMS>
-__global__ void __launch_bounds__(kCrossThreads)
+__global__ void __launch_bounds__(kCrossThreads, BEAMS <= 4 ? 4 : 2)
     decode_cross_attention_kernel(const __nv_bfloat16* __restrict__ q,  // [B*beams, H, 64]
                                   const __nv_bfloat16* __restrict__ k,  // [B, H, Lk, 64]
                                   const __nv_bfloat16* __restrict__ v,
