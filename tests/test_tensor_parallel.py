@@ -124,3 +124,44 @@ def test_symmetric_arena_allocator_is_deterministic_and_coalesces():
     ar.alloc(1)
   del f                       # dropping the block returns it
   assert ar.free == [(0, 1 << 20)]
+
+
+def test_owner_assignment_balances_and_is_deterministic():
+  from t5x_b200.parallel import zero
+  sizes = {"a": 100, "b": 90, "c": 50, "d": 40, "e": 10, "f": 10}
+  owners = zero.assign_owners(sizes, 2)
+  assert owners == zero.assign_owners(dict(reversed(list(sizes.items()))), 2)
+  load = [sum(sizes[k] for k, r in owners.items() if r == rank) for rank in range(2)]
+  assert sorted(load) == [150, 150]
+  assert set(zero.assign_owners(sizes, 8).values()) <= set(range(8))
+  assert zero.assign_owners({}, 4) == {}
+
+
+def _partial_grad_worker(rank, world, port, out_path):
+  sys.path.insert(0, ROOT)
+  os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                    WORLD_SIZE=str(world))
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  from t5x_b200 import trainer as trainer_lib
+  from t5x_b200.parallel import state as pstate
+  pstate.setup_mesh(model_size=world, device=torch.device("cpu"))
+  # two "norm scales" that saw this rank's rows only, one ordinary replicated parameter
+  params = {"n1": torch.nn.Parameter(torch.zeros(4)), "n2": torch.nn.Parameter(torch.zeros(3)),
+            "w": torch.nn.Parameter(torch.zeros(2))}
+  params["n1"].sp_partial_grad = True
+  params["n2"].sp_partial_grad = True
+  grads = {"n1": torch.full((4,), float(rank + 1)), "n2": torch.arange(3.0) * (rank + 1),
+           "w": torch.full((2,), 5.0)}
+  trainer_lib.reduce_partial_gradients_over_model_axis(grads, params)
+  torch.save({k: v.clone() for k, v in grads.items()}, f"{out_path}.{rank}")
+  dist.destroy_process_group()
+
+
+def test_partial_gradients_of_row_sharded_norms_are_summed_over_the_model_axis(tmp_path):
+  out = str(tmp_path / "g")
+  mp.spawn(_partial_grad_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+  for rank in range(2):
+    g = torch.load(f"{out}.{rank}")
+    assert g["n1"].tolist() == [3.0] * 4              # 1 + 2
+    assert g["n2"].tolist() == [0.0, 3.0, 6.0]
+    assert g["w"].tolist() == [5.0, 5.0]              # untouched
