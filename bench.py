@@ -159,6 +159,10 @@ def main() -> None:
   from t5x_b200.parallel import state as pstate
   from t5x_b200.utils import schedules
 
+  # NCCL only carries barriers, the metrics all-reduce and (tensor-parallel runs) two gathers
+  # per step here; the in-switch reduction buys nothing for those, and with it off a rank that
+  # dies cannot raise NVLink faults on its peers' GPUs. An explicit setting wins.
+  os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
   world = int(os.environ.get("WORLD_SIZE", "1"))
   if world != args.gpus:
     raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun "

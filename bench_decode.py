@@ -29,6 +29,7 @@ def run(args, ClockSampler) -> None:
   from t5x_b200.ops import native
   from t5x_b200.parallel import state as pstate
 
+  os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # NCCL only synchronises ranks here
   world = int(os.environ.get("WORLD_SIZE", "1"))
   if world != args.gpus:
     raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
