@@ -525,11 +525,13 @@ class Adafactor(OptimizerDef):
         scale = thr * torch.minimum(torch.tensor(1.0 / thr, device=gn.device), 1.0 / gn)
         for k in flat_p:
           flat_g[k].mul_(scale.to(flat_g[k].dtype))
+      from t5x_b200.parallel import zero
+      done = zero.done_this_step()
       for k, p in flat_p.items():
         zinfo = getattr(p, "zero", None)
         if zinfo is not None and not zinfo.mine:
           continue  # its owner updates it and pushes the new bf16 weights here
-        if zinfo is not None and k in getattr(zinfo.ctx, "done_this_step", ()):
+        if k in done:
           continue  # already updated while the backward pass was running
         self.apply_param_gradient(step, hyper_params, p, flat_s[k], flat_g[k], k)
     finally:

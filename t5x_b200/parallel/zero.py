@@ -218,7 +218,93 @@ class ZeroContext:
           dist.broadcast(v, src=ranks[self.owners[k]], group=self.group)
 
 
+class LocalUpdateOverlap:
+  """The single-replica form of the overlap above: no gradients to exchange, but the
+  optimizer update of a transformer layer (memory-bound) can still run on a side stream as
+  soon as that layer's backward has been issued in the last microbatch, under the GEMMs
+  (compute-bound) of the layers below."""
+
+  def __init__(self, params_flat: Mapping[str, torch.Tensor], module: torch.nn.Module,
+               optimizer_def, state_of):
+    import re
+    self.params = {k: p for k, p in params_flat.items()
+                   if isinstance(p, torch.Tensor) and p.is_cuda and p.dtype == torch.float32}
+    self._opt_def, self._state_of = optimizer_def, state_of
+    device = next(iter(self.params.values())).device
+    self._side = torch.cuda.Stream(device=device)
+    self._overlap = None
+    self.done_this_step = set()
+    self._buckets = {}
+    by_id = {id(p): k for k, p in self.params.items()}
+    for mod_name, mod in module.named_modules():
+      if not re.fullmatch(r"(.*\.)?layers_\d+", mod_name):
+        continue
+      names = [by_id[id(p)] for p in mod.parameters(recurse=True) if id(p) in by_id]
+      if names:
+        self._buckets[mod_name] = names
+        mod.register_full_backward_hook(
+            lambda m, gin, gout, bucket=mod_name: self._bucket_ready(bucket))
+
+  def begin_overlap(self, step: int, hyper_params) -> None:
+    self._overlap = (int(step), hyper_params)
+    self.done_this_step = set()
+
+  def end_overlap(self) -> None:
+    self._overlap = None
+    torch.cuda.current_stream().wait_stream(self._side)
+
+  def _bucket_ready(self, bucket: str) -> None:
+    if self._overlap is None:
+      return
+    step, hp = self._overlap
+    names = [k for k in self._buckets[bucket]
+             if getattr(self.params[k], "grad_ready", False) and self.params[k].grad is None
+             and getattr(self.params[k], "main_grad", None) is not None]
+    if not names:
+      return
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream())
+    with torch.cuda.stream(self._side):
+      self._side.wait_event(ev)
+      saved = self._opt_def.hyper_params
+      self._opt_def.hyper_params = hp
+      try:
+        with torch.no_grad():
+          for k in names:
+            p = self.params[k]
+            self._opt_def.apply_param_gradient(step, hp, p, self._state_of(k), p.main_grad, k)
+      finally:
+        self._opt_def.hyper_params = saved
+    self.done_this_step.update(names)
+
+
 _ACTIVE: Optional[ZeroContext] = None
+_LOCAL: Optional[LocalUpdateOverlap] = None
+
+
+def enable_local_overlap(params_flat, module, optimizer_def, state_of) -> LocalUpdateOverlap:
+  global _LOCAL
+  _LOCAL = LocalUpdateOverlap(params_flat, module, optimizer_def, state_of)
+  return _LOCAL
+
+
+def disable_local_overlap() -> None:
+  global _LOCAL
+  _LOCAL = None
+
+
+def overlap_controller():
+  """Whoever runs optimizer updates under the last backward pass: the sharded-optimizer
+  context, the single-replica overlap, or None."""
+  if _ACTIVE is not None and getattr(_ACTIVE, "_side", None) is not None:
+    return _ACTIVE
+  return _LOCAL
+
+
+def done_this_step():
+  """Names of the parameters already updated during the current step's backward pass."""
+  ctl = overlap_controller()
+  return ctl.done_this_step if ctl is not None else ()
 
 
 def active() -> Optional[ZeroContext]:
@@ -236,5 +322,6 @@ def enable(params_flat: Mapping[str, torch.Tensor], group=None) -> Optional[Zero
 
 
 def disable() -> None:
-  global _ACTIVE
+  global _ACTIVE, _LOCAL
   _ACTIVE = None
+  _LOCAL = None

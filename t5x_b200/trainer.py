@@ -340,7 +340,7 @@ def accumulate_grads_microbatched(model, train_state, batch: BatchType, dropout_
   n = num_microbatches if num_microbatches and num_microbatches > 1 else 1
   metrics = None
   from t5x_b200.parallel import zero
-  ctx = zero.active()
+  ctx = zero.overlap_controller()
   for i in range(n):
     mb = batch if n == 1 else _slice_batch(batch, i, n)
     rng = None if dropout_rng is None else fold_in_seed(dropout_rng, i)
@@ -355,6 +355,8 @@ def accumulate_grads_microbatched(model, train_state, batch: BatchType, dropout_
     loss.backward()
     _fold_autograd_grads(flat)
     metrics = m if metrics is None else merge_metrics(metrics, m)
+  if ctx is not None:
+    ctx.end_overlap()  # updates issued under the last backward pass are ordered before what follows
   grads = _collect_grads(flat)
   reduce_partial_gradients_over_model_axis(grads, flat)
   reduce_gradients_over_data_axis(grads, flat)
@@ -597,9 +599,17 @@ class Trainer(BaseTrainer):
     if hasattr(train_state, "params"):
       # Sharding allocates the working weights and gradient accumulators itself (in memory
       # that all replicas map); only parameters it does not cover get private buffers.
+      self._local_overlap_args = None
       self._maybe_shard_optimizer(train_state, weight_metrics_computer)
       attach_compute_buffers(train_state.params,
                              bf16_copy=self._device.type == "cuda", main_grad=True)
+      if self._local_overlap_args is not None:
+        from t5x_b200 import adafactor
+        from t5x_b200.parallel import zero
+        ts, opt_def = self._local_overlap_args
+        slots = tree_utils.flatten_dict(ts.param_states, is_leaf=adafactor._is_state_leaf)
+        zero.enable_local_overlap(tree_utils.flatten_dict(ts.params), self._model.module,
+                                  opt_def, lambda name: slots[name])
 
   def _maybe_shard_optimizer(self, train_state, weight_metrics_computer) -> None:
     """Shards the optimizer over the data axis (see `t5x_b200.parallel.zero`) when there is
@@ -608,14 +618,21 @@ class Trainer(BaseTrainer):
     plain all-reduce."""
     from t5x_b200 import adafactor
     from t5x_b200.parallel import zero
+    zero.disable_local_overlap()  # a previous trainer's registration does not apply to this one
     st = pstate.get()
-    if (os.environ.get("T5X_B200_OPTIMIZER_SHARDING", "1") == "0" or st.data_size <= 1 or
-        st.expert_size > 1 or self._device.type != "cuda" or weight_metrics_computer is not None):
-      return
     opt_def = getattr(getattr(train_state, "_optimizer", None), "optimizer_def", None)
-    if not isinstance(opt_def, adafactor.Adafactor):
+    if (self._device.type != "cuda" or weight_metrics_computer is not None or
+        not isinstance(opt_def, adafactor.Adafactor) or
+        opt_def.hyper_params.global_norm_clip_threshold):
       return
-    if opt_def.hyper_params.global_norm_clip_threshold:
+    if st.world_size == 1 and getattr(self._model, "module", None) is not None and \
+        os.environ.get("T5X_B200_OVERLAP_GRAD_EXCHANGE", "1") != "0":
+      # one replica: nothing to exchange, but each layer's update can still run under the
+      # backward pass of the layers below it (registered after the buffers are attached)
+      self._local_overlap_args = (train_state, opt_def)
+      return
+    if (os.environ.get("T5X_B200_OPTIMIZER_SHARDING", "1") == "0" or st.data_size <= 1 or
+        st.expert_size > 1):
       return
     ctx = zero.enable(tree_utils.flatten_dict(train_state.params), st.data_group)
     module = getattr(self._model, "module", None)
