@@ -339,13 +339,31 @@ __global__ void __launch_bounds__(kAfThreads)
   const bool bf_vec = VEC && p_bf16 != nullptr && (ld_bf16 % 4 == 0) &&
                       (bf16_batch_stride % 4 == 0) &&
                       ((reinterpret_cast<uintptr_t>(p_bf16) & 7) == 0);
-  for (int rr = 0; rr < rows; ++rr) {
+  // Four rows per trip with all eight 16-byte loads issued before the first use: the kernel
+  // is bound by how many bytes each thread keeps in flight.
+  constexpr int kRowUnroll = 4;
+  for (int r4 = 0; r4 < rows; r4 += kRowUnroll) {
+    float4 tg[kRowUnroll], to[kRowUnroll];
+    if (VEC) {
+#pragma unroll
+      for (int u = 0; u < kRowUnroll; ++u) {
+        if (r4 + u < rows) {
+          const long long off = base + static_cast<long long>(r0 + r4 + u) * C + col;
+          tg[u] = *reinterpret_cast<const float4*>(g + off);
+          to[u] = *reinterpret_cast<const float4*>(p + off);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; ++u) {
+    const int rr = r4 + u;
+    if (rr >= rows) break;
     const long long off = base + static_cast<long long>(r0 + rr) * C + col;
     const float rv = rf[r0 + rr] * scale;
     float gv[4], ov[4], nv[4];
     if (VEC) {
-      const float4 t = *reinterpret_cast<const float4*>(g + off);
-      const float4 o = *reinterpret_cast<const float4*>(p + off);
+      const float4 t = tg[u];
+      const float4 o = to[u];
       gv[0] = t.x; gv[1] = t.y; gv[2] = t.z; gv[3] = t.w;
       ov[0] = o.x; ov[1] = o.y; ov[2] = o.z; ov[3] = o.w;
     } else {
@@ -387,6 +405,7 @@ __global__ void __launch_bounds__(kAfThreads)
       } else {
         for (int k = 0; k < nk; ++k) o[k] = __float2bfloat16(nv[k]);
       }
+    }
     }
   }
 }

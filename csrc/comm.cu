@@ -257,11 +257,26 @@ __global__ void __launch_bounds__(kDsThreads)
   const float4 cfv = *reinterpret_cast<const float4*>(cf + static_cast<long long>(b) * C + col);
   const float* rfb = rf + static_cast<long long>(b) * R;
   const int rows = min(kDsTileR, R - r0);
-  for (int rr = 0; rr < rows; ++rr) {
+  // four rows per trip, all eight 16-byte loads issued before the first use
+  constexpr int kRowUnroll = 4;
+  for (int r4 = 0; r4 < rows; r4 += kRowUnroll) {
+  float4 tg[kRowUnroll], to[kRowUnroll];
+#pragma unroll
+  for (int u = 0; u < kRowUnroll; ++u) {
+    if (r4 + u < rows) {
+      const long long off = base + static_cast<long long>(r0 + r4 + u) * C + col;
+      tg[u] = *reinterpret_cast<const float4*>(g + off);
+      to[u] = *reinterpret_cast<const float4*>(p + off);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kRowUnroll; ++u) {
+    const int rr = r4 + u;
+    if (rr >= rows) break;
     const long long off = base + static_cast<long long>(r0 + rr) * C + col;
     const float rfv = rfb[r0 + rr] * scale;
-    const float4 gv = *reinterpret_cast<const float4*>(g + off);
-    const float4 old = *reinterpret_cast<const float4*>(p + off);
+    const float4 gv = tg[u];
+    const float4 old = to[u];
     float sub[4] = {gv.x * rfv * cfv.x, gv.y * rfv * cfv.y, gv.z * rfv * cfv.z,
                     gv.w * rfv * cfv.w};
     const float ov[4] = {old.x, old.y, old.z, old.w};
@@ -291,6 +306,7 @@ __global__ void __launch_bounds__(kDsThreads)
     packed.x = *reinterpret_cast<uint32_t*>(&lo);
     packed.y = *reinterpret_cast<uint32_t*>(&hi);
     for (int d = 0; d < world; ++d) *reinterpret_cast<uint2*>(out.p[d] + off) = packed;
+  }
   }
   }
 }
