@@ -47,6 +47,39 @@ __global__ void __launch_bounds__(kAfThreads)
 #pragma unroll
     for (int k = 0; k < 4; ++k) cacc[a][k] = 0.f;
   float psq = 0.f;
+  if (VEC && tile_r + kAfTileR <= R && tile_c + kAfTileC <= C) {
+    // interior tile: two rows per trip, their sixteen 16-byte loads issued before the first use
+    for (int rr = 0; rr < kAfTileR / 8; rr += 2) {
+      const int row = tile_r + warp * (kAfTileR / 8) + rr;
+      float4 gq[2][4], pq[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const long long off = static_cast<long long>(row + u) * C + tile_c + ch * 128 + lane * 4;
+          gq[u][ch] = *reinterpret_cast<const float4*>(g + off);
+          pq[u][ch] = *reinterpret_cast<const float4*>(p + off);
+        }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        float rs = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const float4 gv = gq[u][ch], pv = pq[u][ch];
+          const float s0 = gv.x * gv.x + eps1, s1 = gv.y * gv.y + eps1, s2 = gv.z * gv.z + eps1,
+                      s3 = gv.w * gv.w + eps1;
+          rs += (s0 + s1) + (s2 + s3);
+          cacc[ch][0] += s0;
+          cacc[ch][1] += s1;
+          cacc[ch][2] += s2;
+          cacc[ch][3] += s3;
+          psq += pv.x * pv.x + pv.y * pv.y + pv.z * pv.z + pv.w * pv.w;
+        }
+        rs = warp_sum(rs);
+        if (lane == 0) atomicAdd(&rowsum[row + u], rs);
+      }
+    }
+  } else
   for (int rr = 0; rr < kAfTileR / 8; ++rr) {
     const int row = tile_r + warp * (kAfTileR / 8) + rr;
     if (row >= R) break;
