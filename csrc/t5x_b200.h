@@ -60,6 +60,54 @@ int t5x_adafactor_factored_static(void* p, const void* g, void* v_rvec, void* v_
                                   float weight_decay, float beta1, float max_param_scale,
                                   int flags, void* stream);
 
+/* ---- GEMM (tcgen05): C[batch, M, N] (+)= alpha * A[batch, M, K] @ B[batch, K, N] ----
+ * bf16 operands, fp32 accumulation; leading dimensions and batch strides in elements.
+ * a_mn_major / b_mn_major: 0 = the contraction dim is contiguous, 1 = the M (N) dim is.
+ * out_fp32: C is fp32 (else bf16); accumulate: 0 store, 1 add to C, 2 add atomically (several
+ * K slices as batches into one C). epilogue: 0 plain, 1 gated GELU (C = gelu(A B) * (A B2),
+ * optional copies of both products in H0 / H1), 2 add the bf16 matrix R. */
+int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C, int M, int N, int K,
+                  int batch, long long lda, long long ldb, long long ldc,
+                  long long a_batch_stride, long long b_batch_stride, long long c_batch_stride,
+                  int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int epilogue,
+                  const void* R, long long ldr, long long r_batch_stride, void* H0, void* H1,
+                  long long ldh, float alpha, int max_ctas, void* stream);
+
+/* ---- tensor parallelism with the collective inside the GEMM kernel ----
+ * The M rows are split evenly over `world` ranks (rows_per_rank each). Peer pointers are the
+ * other ranks' buffers as mapped into this process (symmetric memory).
+ *
+ * all-gather -> GEMM: A is this rank's [M, K] buffer with only block `rank` filled; the kernel
+ * pulls block r from a_peers[r] (same layout) while it multiplies; `flags`: `world` uint32 of
+ * this GPU's memory. A barrier over the ranks must separate the writes of the blocks from
+ * this call. epilogue 0 or 1.
+ *
+ * GEMM -> reduce-scatter: the bf16 partial product (+ R) is stored row block by row block to
+ * c_peers[r], this rank's slot [rows_per_rank, ldc] of rank r's inbox; after a barrier the
+ * owner adds its `world` slots with t5x_slot_sum_bf16. */
+int t5x_gemm_allgather_bf16(void* A, const void* const* a_peers, int world, int rank,
+                            int rows_per_rank, void* flags, const void* B, const void* B2,
+                            void* C, int M, int N, int K, long long ldb, long long ldc,
+                            int b_mn_major, int epilogue, void* H0, void* H1, long long ldh,
+                            void* stream);
+int t5x_gemm_reducescatter_bf16(const void* A, const void* B, void* const* c_peers, int world,
+                                int rank, int rows_per_rank, int M, int N, int K, long long lda,
+                                long long ldb, long long ldc, int a_mn_major, int b_mn_major,
+                                const void* R, long long ldr, void* stream);
+int t5x_slot_sum_bf16(const void* slots, int num_slots, long long n, const void* residual,
+                      void* dst, void* stream);
+
+/* Stream-ordered barrier over `world` ranks through signal pads (one per rank, as mapped
+ * here; (channel + 1) * 16 uint32 each, zero at start). `epoch` >= 1 and increasing per
+ * channel. A rank that never arrives makes the wait give up after `spin_limit` polls and
+ * records a status (t5x_read_status) instead of hanging. */
+int t5x_comm_barrier(const void* const* pads, int rank, int world, int channel,
+                     unsigned int epoch, unsigned long long spin_limit, void* stream);
+
+/* Synchronises `stream` and copies the device status words (kernel id, reason, indices) to
+ * `words[8]`; returns the reason code (0 = none) and clears it. */
+int t5x_read_status(int* words, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
