@@ -350,10 +350,10 @@ class MultiHeadDotProductAttention(nn.Module):
 
   def project_kv(self, inputs_kv: torch.Tensor):
     b, lk, _ = inputs_kv.shape
-    kv_in = tp.copy_to_model_parallel(inputs_kv)
-    k = self.key(kv_in).view(b, lk, self.local_heads, self.head_dim)
-    v = self.value(kv_in).view(b, lk, self.local_heads, self.head_dim)
-    return k, v
+    kv_in = tp.copy_to_model_parallel(inputs_kv).to(self.dtype)
+    k, v = F.multi_linear(kv_in, [self.key.kernel, self.value.kernel], dtype=self.dtype)
+    return (k.view(b, lk, self.local_heads, self.head_dim),
+            v.view(b, lk, self.local_heads, self.head_dim))
 
   def forward(self, inputs_q: torch.Tensor, inputs_kv: Optional[torch.Tensor], *,
               bias_table: Optional[torch.Tensor] = None, bidirectional: bool = True,
@@ -367,13 +367,23 @@ class MultiHeadDotProductAttention(nn.Module):
               beams_per_kv: int = 1) -> torch.Tensor:
     b, lq, _ = inputs_q.shape
     q_in = tp.copy_to_model_parallel(inputs_q)
-    if self.scale_attn_logits:
-      q_in = q_in / math.sqrt(self.head_dim)
-    q = self.query(q_in).view(b, lq, self.local_heads, self.head_dim)
-    if precomputed_kv is not None:
-      k, v = precomputed_kv
+    if (precomputed_kv is None and inputs_kv is inputs_q and not self.scale_attn_logits):
+      # self-attention: the three projections share their input, and one backward builds its
+      # gradient by accumulating GEMMs
+      q, k, v = F.multi_linear(q_in.to(self.dtype),
+                               [self.query.kernel, self.key.kernel, self.value.kernel],
+                               dtype=self.dtype)
+      q = q.view(b, lq, self.local_heads, self.head_dim)
+      k = k.view(b, lq, self.local_heads, self.head_dim)
+      v = v.view(b, lq, self.local_heads, self.head_dim)
     else:
-      k, v = self.project_kv(inputs_kv)
+      if self.scale_attn_logits:
+        q_in = q_in / math.sqrt(self.head_dim)
+      q = self.query(q_in).view(b, lq, self.local_heads, self.head_dim)
+      if precomputed_kv is not None:
+        k, v = precomputed_kv
+      else:
+        k, v = self.project_kv(inputs_kv)
     q_offset = 0
     if cache is not None and prefill:
       # Fill the cache with the prompt's keys/values in one pass.

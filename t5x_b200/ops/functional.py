@@ -81,6 +81,55 @@ class _LinearFn(torch.autograd.Function):
     return dx, dw, (dy if ctx.has_res else None)
 
 
+class _MultiLinearFn(torch.autograd.Function):
+  """(x @ W_0, x @ W_1, ...) for projections that share their input (q/k/v, cross k/v). In
+  backward the input gradient is built by accumulating GEMMs (dx = dy_0 W_0^T, then
+  dx += dy_i W_i^T in the epilogue), not by separate GEMMs whose results autograd would add
+  with elementwise kernels over the activations."""
+
+  @staticmethod
+  def forward(ctx, x, *weights):
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    outs = []
+    for w in weights:
+      w2 = compute_weight(w, torch.bfloat16).reshape(k, -1)
+      outs.append(native.gemm(x2, w2).view(*x.shape[:-1], w2.shape[1]))
+    ctx.save_for_backward(x, *weights)
+    return tuple(outs)
+
+  @staticmethod
+  def backward(ctx, *dys):
+    x, *weights = ctx.saved_tensors
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    dx = None
+    dws = []
+    for i, (w, dy) in enumerate(zip(weights, dys)):
+      if dy is None:
+        dws.append(None)
+        continue
+      w2 = compute_weight(w, torch.bfloat16).reshape(k, -1)
+      dy2 = dy.reshape(-1, w2.shape[1])
+      if not dy2.is_contiguous():
+        dy2 = dy2.contiguous()
+      if ctx.needs_input_grad[0]:
+        if dx is None:
+          dx = native.gemm(dy2, w2.t())
+        else:
+          native.gemm(dy2, w2.t(), out=dx, accumulate=True)
+      dws.append(_accumulate_wgrad(w, x2.t(), dy2) if ctx.needs_input_grad[1 + i] else None)
+    return (None if dx is None else dx.view(x.shape),) + tuple(dws)
+
+
+def multi_linear(x: torch.Tensor, weights: Sequence[torch.Tensor],
+                 dtype: Optional[torch.dtype] = None):
+  """[x @ W for W in weights] with one fused backward for the shared input."""
+  if _native_ok(x):
+    return list(_MultiLinearFn.apply(x, *weights))
+  return [linear(x, w, dtype=dtype) for w in weights]
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor] = None,
            dtype: Optional[torch.dtype] = None) -> torch.Tensor:
   """y = x @ W (+ residual). W is [in, out...] (T5X kernel layout); trailing kernel dims are
