@@ -483,6 +483,23 @@ int af_check(const char* what) {
   if (e != cudaSuccess) return set_error("%s: %s", what, cudaGetErrorString(e));
   return 0;
 }
+// 16-byte loads of the statistics kernel need p and g on 16-byte boundaries as well as C % 4 == 0.
+static bool af_stats_vec_ok(const void* p, const void* g, int C) {
+  return C % 4 == 0 && ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15) == 0;
+}
+
+// Pointers every factored update dereferences on the device; `m` only with the momentum flag.
+static int af_validate(const char* what, const void* p, const void* g, const void* v_rvec,
+                       const void* v_cvec, const void* m, int flags) {
+  if (p == nullptr || g == nullptr) return set_error("%s: p and g must not be null", what);
+  if (v_rvec == nullptr || v_cvec == nullptr)
+    return set_error("%s: v_rvec and v_cvec must not be null", what);
+  if ((flags & 8) && m == nullptr)
+    return set_error("%s: the momentum flag (8) is set but m is null", what);
+  if (((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 3) != 0)
+    return set_error("%s: p and g must be 4-byte aligned", what);
+  return 0;
+}
 }  // namespace
 
 // The factored update is split in phases so that a tensor-parallel caller can sum the
@@ -498,7 +515,8 @@ T5X_API int t5x_adafactor_stats(const void* p, const void* g, void* scratch, int
   AfScratch a = af_split(scratch, batch, R, C);
   cudaMemsetAsync(scratch, 0, t5x_adafactor_scratch_floats(batch, R, C) * sizeof(float), st);
   dim3 sgrid((C + kAfTileC - 1) / kAfTileC, (R + kAfTileR - 1) / kAfTileR, batch);
-  if (C % 4 == 0)
+  if (p == nullptr || g == nullptr) return set_error("adafactor_stats: p and g must not be null");
+  if (af_stats_vec_ok(p, g, C))
     af_stats_kernel<true><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
                                                         static_cast<const float*>(p), a.rowsum,
                                                         a.colsum, a.scal, R, C, eps1);
@@ -583,7 +601,11 @@ T5X_API int t5x_adafactor_factored(void* p, const void* g, void* v_rvec, void* v
                                    float lr, float decay, float eps1, float eps2,
                                    float clip_threshold, float weight_decay, float beta1,
                                    float max_param_scale, int flags, void* stream) {
-  int rc = t5x_adafactor_stats(p, g, scratch, batch, R, C, eps1, stream);
+  if (batch <= 0 || R <= 0 || C <= 0) return 0;
+  int rc = af_validate("adafactor_factored", p, g, v_rvec, v_cvec, m, flags);
+  if (rc) return rc;
+  if (scratch == nullptr) return set_error("adafactor_factored: scratch must not be null");
+  rc = t5x_adafactor_stats(p, g, scratch, batch, R, C, eps1, stream);
   if (rc) return rc;
   rc = t5x_adafactor_ema(v_rvec, v_cvec, scratch, batch, R, C, R, C, row_is_normalized, decay,
                          (flags >> 5) & 1, stream);
@@ -710,6 +732,7 @@ T5X_API int t5x_adafactor_factored_static(void* p, const void* g, void* v_rvec, 
         "adafactor_static: batch=%d rows=%d cols=%d needs %lld scratch floats but the built-in "
         "scratch holds %lld; use t5x_adafactor_factored with a caller-provided buffer",
         batch, R, C, need, kAfStaticScratchFloats);
+  if (int rc = af_validate("adafactor_static", p, g, v_rvec, v_cvec, m, flags)) return rc;
   AfStaticDevice* d = nullptr;
   if (int rc = af_static_setup(&d)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -719,7 +742,7 @@ T5X_API int t5x_adafactor_factored_static(void* p, const void* g, void* v_rvec, 
   cudaError_t e = cudaMemsetAsync(d->scratch, 0, need * sizeof(float), st);
   if (e != cudaSuccess) return set_error("adafactor_static: memset: %s", cudaGetErrorString(e));
   dim3 sgrid((C + kAfTileC - 1) / kAfTileC, (R + kAfTileR - 1) / kAfTileR, batch);
-  if (C % 4 == 0)
+  if (af_stats_vec_ok(p, g, C))
     af_stats_kernel<true><<<sgrid, kAfThreads, 0, st>>>(static_cast<const float*>(g),
                                                         static_cast<const float*>(p), a.rowsum,
                                                         a.colsum, a.scal, R, C, eps1);

@@ -173,6 +173,19 @@ T5X_API int t5x_read_status(int* out, void* stream) {
   return host[0];
 }
 
+// Enqueues, on `stream`, a copy of the status words to `host_dst` (kStatusWords ints of pinned
+// host memory) and returns at once. The caller reads `host_dst` after an event recorded behind
+// this call has completed; the words are not cleared. A training loop uses this to notice a
+// kernel that gave up on a wait without stalling its launch queue.
+T5X_API int t5x_status_copy_async(int* host_dst, void* stream) {
+  if (host_dst == nullptr) return t5x::set_error("status copy: null destination");
+  int* s = t5x::device_status_buffer();
+  if (cudaMemcpyAsync(host_dst, s, t5x::kStatusWords * sizeof(int), cudaMemcpyDeviceToHost,
+                      static_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return t5x::set_error("status copy failed: %s", cudaGetErrorString(cudaGetLastError()));
+  return 0;
+}
+
 // Number of kernels this library has launched in this process (all devices).
 T5X_API long long t5x_launch_count() { return t5x::launches(); }
 

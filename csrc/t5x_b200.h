@@ -20,7 +20,9 @@ long long t5x_adafactor_scratch_floats(int batch, int rows, int cols);
  * v_cvec[batch, cols] are the second-moment vectors, m an optional momentum buffer, p_bf16 an
  * optional bf16 copy of the updated parameter. `flags` is a bit set: 1 multiply by parameter
  * scale, 2 RMS clipping, 4 weight decay, 8 momentum, 16 cap the parameter scale, 32 skip NaN
- * updates. */
+ * updates. p, g, v_rvec and v_cvec must not be null and m must not be null when flag 8 is
+ * set (the call is rejected otherwise); p and g need only 4-byte alignment (16-byte aligned
+ * pointers with cols % 4 == 0 take the faster 16-byte loads). */
 int t5x_adafactor_factored(void* p, const void* g, void* v_rvec, void* v_cvec, void* m,
                            void* p_bf16, long long ld_bf16, long long bf16_batch_stride,
                            void* scratch, int batch, int rows, int cols, int row_is_normalized,
@@ -107,6 +109,11 @@ int t5x_comm_barrier(const void* const* pads, int rank, int world, int channel,
 /* Synchronises `stream` and copies the device status words (kernel id, reason, indices) to
  * `words[8]`; returns the reason code (0 = none) and clears it. */
 int t5x_read_status(int* words, void* stream);
+
+/* The same words copied to `host_dst` (8 ints of pinned host memory) by an asynchronous copy
+ * enqueued on `stream`; nothing is synchronised or cleared. Read `host_dst` once an event
+ * recorded after this call has completed. */
+int t5x_status_copy_async(int* host_dst, void* stream);
 
 #ifdef __cplusplus
 }

@@ -140,4 +140,19 @@ def get_loss_normalizing_factor_and_weights(
     output = loss_weights.sum()
   else:
     raise ValueError(f"Unsupported value of loss_normalizing_factor: {loss_normalizing_factor}")
-  return output, loss_weights
+  return _sum_over_data_replicas(output), loss_weights
+
+
+def _sum_over_data_replicas(factor):
+  """A factor derived from the batch counts the GLOBAL batch: the reference evaluates it
+  inside the partitioned step over all replicas' examples (t5x/losses.py:278-356 under
+  t5x/trainer.py:745-852), and gradients are summed over replicas afterwards. Each rank sees
+  only its shard here, so the per-shard counts are added over the data (and expert) axis."""
+  import torch.distributed as dist
+  from t5x_b200.parallel import state as pstate
+  st = pstate.get()
+  if st.data_size * st.expert_size <= 1 or st.data_group is None or not dist.is_initialized():
+    return factor
+  t = torch.as_tensor(factor, dtype=torch.float32, device=st.device).detach().clone().reshape(1)
+  dist.all_reduce(t, group=st.data_group)
+  return t[0]

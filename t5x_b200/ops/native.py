@@ -157,6 +157,47 @@ def check_status() -> None:
         f"(payload {words[3]}, {words[4]})")
 
 
+def _raise_status(words) -> None:
+  code = int(words[0])
+  raise KernelStatusError(
+      f"kernel {int(words[1])} block {int(words[2])} reported '{STATUS_NAMES.get(code, code)}' "
+      f"(payload {int(words[3])}, {int(words[4])})")
+
+
+class StatusPoller:
+  """Watches the device status words from inside a training loop without stalling it.
+
+  `poll()` looks at the copy enqueued by an earlier `poll()` if that copy has completed
+  (raising `KernelStatusError` when a kernel gave up on a bounded wait: a peer that never
+  raised its flag, a barrier that ran out) and enqueues the next copy behind the work launched
+  so far. A failure is therefore reported one or two steps after it happened, and the host
+  never waits for the GPU. `check()` is the blocking form for points where the state leaves
+  the loop (checkpoints, the end of training)."""
+
+  def __init__(self):
+    self._host = torch.zeros(8, dtype=torch.int32).pin_memory()
+    self._event = None
+
+  def poll(self) -> None:
+    if self._event is not None:
+      if not self._event.query():
+        return
+      if int(self._host[0]) != 0:
+        words = self._host.clone()
+        self._event = None
+        check_status()  # synchronises and clears the device words
+        _raise_status(words)
+    l = lib()
+    l.t5x_status_copy_async.argtypes = [c_void_p, c_void_p]
+    _check(l.t5x_status_copy_async(self._host.data_ptr(), stream_ptr()), "status_copy_async")
+    self._event = torch.cuda.Event()
+    self._event.record()
+
+  def check(self) -> None:
+    self._event = None
+    check_status()
+
+
 # ----------------------------------------------------------------------------
 # GEMM
 # ----------------------------------------------------------------------------

@@ -37,10 +37,15 @@ _ALIGN = 1024
 
 
 class _Block:
-  """A byte range of the arena; returns itself to the free list when dropped."""
+  """A byte range of the arena. Blocks go back to the free list only at points that every
+  rank reaches in the same order: an explicit `release()` (end of the autograd function that
+  owns the block) or the arena's `end_step()`. Object lifetime plays no part: a block that is
+  merely dropped stays allocated until the end of the step, so ranks whose garbage collectors
+  run at different times still hand out identical offsets."""
 
   def __init__(self, arena, offset: int, size: int):
     self.arena, self.offset, self.size = arena, offset, size
+    self.generation = arena.generation
 
   def tensor(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
     n = 1
@@ -56,12 +61,9 @@ class _Block:
     return [p + self.offset + extra_bytes for p in self.arena.buf.peer_ptrs]
 
   def release(self) -> None:
-    if self.arena is not None:
-      self.arena._free(self.offset, self.size)
-      self.arena = None
-
-  def __del__(self):
-    self.release()
+    ar, self.arena = self.arena, None
+    if ar is not None and self.generation == ar.generation:
+      ar._free(self.offset, self.size)
 
 
 class _Inbox:
@@ -89,7 +91,10 @@ class SymmetricArena:
     from t5x_b200.ops import comm
     self.buf = comm.SymmetricBuffer(int(nbytes), torch.uint8, group)
     self.rank, self.world = self.buf.rank, self.buf.world
-    self.free = [(0, int(nbytes))]
+    self.nbytes = int(nbytes)
+    self.free = [(0, self.nbytes)]
+    self.generation = 0   # bumped by end_step(); blocks of older generations are void
+    self.allocations = 0  # blocks handed out so far (cross-checked over ranks in debug runs)
     self.flags = torch.zeros(64, dtype=torch.int32, device=self.buf.tensor.device)
     # True while a kernel that reads peers' memory has been enqueued since the last barrier:
     # the next reuse of arena bytes must wait for every rank to get past it.
@@ -109,6 +114,7 @@ class SymmetricArena:
           del self.free[i]
         else:
           self.free[i] = (off + size, sz - size)
+        self.allocations += 1
         return _Block(self, off, size)
     raise RuntimeError(
         f"tensor-parallel arena exhausted ({size} bytes wanted); raise T5X_B200_TP_ARENA_GB")
@@ -123,6 +129,24 @@ class SymmetricArena:
       else:
         merged.append((off, sz))
     self.free = merged
+
+  def end_step(self) -> None:
+    """Called by the trainer between steps, when no activation of the step is alive any more:
+    every block still allocated (dropped without `release()`, or kept by an exception path) is
+    voided and the whole arena is free again. With `T5X_B200_TP_ARENA_CHECK=1` the ranks also
+    compare how many blocks they have handed out; a difference means their programs diverged
+    and peers would read each other's bytes at the wrong offsets."""
+    self.settle()
+    self.generation += 1
+    self.free = [(0, self.nbytes)]
+    if os.environ.get("T5X_B200_TP_ARENA_CHECK", "0") == "1" and dist.is_initialized():
+      mine = torch.tensor([self.allocations], dtype=torch.int64, device=self.buf.tensor.device)
+      every = [torch.zeros_like(mine) for _ in range(self.world)]
+      dist.all_gather(every, mine, group=self._group)
+      counts = [int(t) for t in every]
+      if len(set(counts)) != 1:
+        raise RuntimeError(f"tensor-parallel arena: ranks handed out {counts} blocks; their "
+                           "allocation sequences differ")
 
   def inbox(self, nbytes: int) -> "_Inbox":
     if self._inbox is None or self._inbox.tensor.numel() < nbytes:
@@ -317,6 +341,11 @@ class _AllGatherLinearsFn(torch.autograd.Function):
       a_full = blk.tensor((M, k))
       outs += [native.gemm(a_full, w) for w in ws[1:]]
     ctx.blk, ctx.weights, ctx.gated, ctx.shape = blk, weights, gated, (M, k)
+    if not any(ctx.needs_input_grad):
+      # no backward will come for this block: give the bytes back here (the next user of
+      # them waits at the arena's barrier for the peers that still read them)
+      blk.release()
+      ctx.blk = ctx.h = None
     return tuple(outs)
 
   @staticmethod

@@ -167,9 +167,7 @@ class ZeroContext:
     if self._overlap is None or not has_input_grad:
       return
     step, hp = self._overlap
-    # only parameters whose whole gradient went through the native accumulate path are final
-    names = [k for k in self._buckets[bucket]
-             if getattr(self.params[k], "grad_ready", False) and self.params[k].grad is None]
+    names = self._final_names(bucket)
     if not names:
       return
     main = torch.cuda.current_stream()
@@ -189,6 +187,24 @@ class ZeroContext:
       finally:
         self._opt_def.hyper_params = saved
     self.done_this_step.update(names)
+
+  def _final_names(self, bucket: str) -> List[str]:
+    """Parameters of `bucket` whose gradient is final once the bucket's backward has been
+    issued: the whole gradient went through the native accumulate path, and no reduction
+    over another mesh axis is still owed. Norm scales applied to row-sharded activations
+    (`sp_partial_grad`) hold only this model rank's rows until the model-axis sum that runs
+    after the backward pass; updating them here would let the model ranks apply different
+    updates to a replicated parameter, so they take the ordinary path after that sum."""
+    partial_pending = pstate.get().model_size > 1
+    out = []
+    for k in self._buckets[bucket]:
+      p = self.params[k]
+      if not getattr(p, "grad_ready", False) or p.grad is not None:
+        continue
+      if partial_pending and getattr(p, "sp_partial_grad", False):
+        continue
+      out.append(k)
+    return out
 
   # -- step protocol -------------------------------------------------------------------------
   def gradients_complete(self) -> None:

@@ -512,10 +512,36 @@ class BaseTrainer(abc.ABC):
         self.train_state, metrics_update = self._train_step(self.train_state, batch, step_num)
       if torch.cuda.is_available():
         torch.cuda.nvtx.range_pop()
+      self._after_step()
       metrics = metrics_update if metrics is None else merge_metrics(metrics, metrics_update)
     self._replicas_stale = True
     return self.train_metrics_manager.write_metrics_summary(metrics, start_step + num_steps,
                                                             num_steps)
+
+  def _after_step(self) -> None:
+    """Between steps: (1) look, without waiting for the GPU, at the device status words.
+    Every cross-GPU wait in the kernels (barriers, the flags of the fused gather/scatter
+    GEMMs) gives up after a bounded number of polls and records why; the kernels behind it
+    would then run on incomplete gradients, weights or inbox rows, so the run stops with a
+    `KernelStatusError` instead of training on them. (2) Return all bytes of the
+    tensor-parallel arena, at a point every rank reaches in the same order."""
+    if self._device.type != "cuda":
+      return
+    from t5x_b200.parallel import tp_fused
+    if tp_fused._ARENA is not None:
+      tp_fused._ARENA.end_step()
+    if getattr(self, "_status_poller", None) is None:
+      from t5x_b200.ops import native
+      self._status_poller = native.StatusPoller()
+    self._status_poller.poll()
+
+  def check_kernel_status(self) -> None:
+    """Blocking form of the status check, for points where the state leaves the loop."""
+    if self._device.type == "cuda":
+      if getattr(self, "_status_poller", None) is None:
+        from t5x_b200.ops import native
+        self._status_poller = native.StatusPoller()
+      self._status_poller.check()
 
   def sync_replicas(self) -> None:
     """With the optimizer sharded over the data axis, brings every replica's fp32 master
@@ -523,6 +549,7 @@ class BaseTrainer(abc.ABC):
     state leaves the training loop (checkpointing, returning the final state); forward passes
     do not need it because they read the bf16 working weights, which are always current."""
     from t5x_b200.parallel import zero
+    self.check_kernel_status()  # a checkpoint must not be written from a step that gave up
     ctx = zero.active()
     if ctx is not None and getattr(self, "_replicas_stale", False):
       ctx.sync_replicas(getattr(self.train_state, "param_states", None))

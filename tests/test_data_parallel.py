@@ -1,0 +1,125 @@
+"""Data-parallel (data axis) paths on CPU ranks over gloo.
+
+  * a batch-derived loss normalising factor counts the global batch, so two replicas with half
+    the batch each reproduce the single-process loss and update;
+  * the sharded optimizer's overlapped update leaves out parameters whose gradient still owes
+    a sum over the model axis.
+"""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+  s = socket.socket()
+  s.bind(("127.0.0.1", 0))
+  p = s.getsockname()[1]
+  s.close()
+  return p
+
+
+def _build(loss_normalizing_factor, seed=0):
+  from t5x_b200 import adafactor, models
+  from t5x_b200.data import vocabularies
+  from t5x_b200.models.t5 import network
+  cfg = network.T5Config(vocab_size=256, dtype="float32", emb_dim=128, num_heads=2,
+                         num_encoder_layers=1, num_decoder_layers=1, head_dim=32, mlp_dim=256,
+                         mlp_activations=("gelu", "linear"), dropout_rate=0.0)
+  module = network.Transformer(cfg)
+  vocab = vocabularies.PassThroughVocabulary(256)
+  opt = adafactor.Adafactor(decay_rate=0.8, step_offset=0,
+                            logical_factor_rules=adafactor.standard_logical_factor_rules())
+  model = models.EncoderDecoderModel(module, vocab, vocab, opt, z_loss=1e-4,
+                                     loss_normalizing_factor=loss_normalizing_factor)
+  model.get_initial_variables(seed, None)
+  return model
+
+
+def _batch():
+  """Four examples with different numbers of real target tokens, so that a per-shard count
+  differs from the global one."""
+  g = torch.Generator().manual_seed(5)
+  enc = torch.randint(3, 250, (4, 16), generator=g)
+  tgt = torch.randint(3, 250, (4, 10), generator=g)
+  for row, n in enumerate((10, 3, 7, 5)):
+    tgt[row, n:] = 0
+  dec_in = torch.cat([torch.zeros(4, 1, dtype=torch.long), tgt[:, :-1]], 1)
+  return {"encoder_input_tokens": enc, "decoder_target_tokens": tgt,
+          "decoder_input_tokens": dec_in, "decoder_loss_weights": (tgt > 0).float()}
+
+
+def _step(model, batch):
+  from t5x_b200 import train_state as ts_lib, trainer as trainer_lib
+  from t5x_b200.models import base
+  state = ts_lib.FlaxOptimTrainState.create(
+      model.optimizer_def, {"params": base.module_param_tree(model.module),
+                            "params_axes": base.module_param_axes(model.module)})
+  tr = trainer_lib.Trainer(model, state, None, [], None, None, 0, lambda s: 0.01, 1)
+  _, metrics = tr._train_step(state, batch, 0)
+  tr.close()
+  return metrics
+
+
+def _dp_worker(rank, world, port, factor, out_path):
+  sys.path.insert(0, ROOT)
+  os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                    WORLD_SIZE=str(world))
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  from t5x_b200.parallel import state as pstate
+  pstate.setup_mesh(model_size=1, device=torch.device("cpu"))
+  model = _build(factor)
+  full = _batch()
+  n = full["encoder_input_tokens"].shape[0] // world
+  shard = {k: v[rank * n:(rank + 1) * n] for k, v in full.items()}
+  metrics = _step(model, shard)
+  if rank == 0:
+    torch.save({"loss": float(metrics["loss"].total),
+                "params": {k: p.detach().clone() for k, p in model.module.named_parameters()}},
+               out_path)
+  dist.barrier()
+  dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("factor", ["NUM_REAL_TARGET_TOKENS", "NUM_TOTAL_TARGET_TOKENS",
+                                    "AVERAGE_PER_SEQUENCE"])
+def test_special_loss_normalizing_factor_counts_the_global_batch(tmp_path, factor):
+  out = str(tmp_path / "dp.pt")
+  mp.spawn(_dp_worker, args=(2, _free_port(), factor, out), nprocs=2, join=True)
+  got = torch.load(out)
+  model = _build(factor)
+  metrics = _step(model, _batch())
+  want = float(metrics["loss"].total)
+  assert abs(got["loss"] - want) / abs(want) < 1e-5, (got["loss"], want)
+  for n, p in model.module.named_parameters():
+    a, b = got["params"][n], p.detach()
+    assert torch.allclose(a, b, rtol=2e-4, atol=2e-6), (n, (a - b).abs().max().item())
+
+
+def test_overlapped_update_skips_parameters_that_owe_a_model_axis_sum():
+  """On a data x model mesh the norm scales of the row-sharded residual stream hold partial
+  gradients until the model-axis all-reduce after backward; the per-layer update that runs
+  under the backward pass must leave them to the ordinary path."""
+  from t5x_b200.parallel import state as pstate, zero
+
+  def param(ready=True, partial=False):
+    p = torch.nn.Parameter(torch.zeros(4))
+    p.grad_ready = ready
+    if partial:
+      p.sp_partial_grad = True
+    return p
+
+  ctx = object.__new__(zero.ZeroContext)
+  ctx.params = {"w": param(), "scale": param(partial=True), "late": param(ready=False)}
+  ctx._buckets = {"layers_0": ["w", "scale", "late"]}
+  st = pstate.get()
+  st.model_size = 1
+  assert ctx._final_names("layers_0") == ["w", "scale"]
+  st.model_size = 2
+  assert ctx._final_names("layers_0") == ["w"]

@@ -102,7 +102,8 @@ def test_symmetric_arena_allocator_is_deterministic_and_coalesces():
   sequence, so offsets must depend on the sequence only; freed neighbours merge again."""
   from t5x_b200.parallel import tp_fused
   ar = object.__new__(tp_fused.SymmetricArena)
-  ar.free = [(0, 1 << 20)]
+  ar.nbytes, ar.free, ar.generation, ar.allocations = 1 << 20, [(0, 1 << 20)], 0, 0
+  ar.dirty, ar.world = False, 1
   a = ar.alloc(1000)          # rounded up to the 1024-byte granule
   b = ar.alloc(5000)
   c = ar.alloc(1024)
@@ -122,7 +123,13 @@ def test_symmetric_arena_allocator_is_deterministic_and_coalesces():
   f = ar.alloc(1 << 20)
   with pytest.raises(RuntimeError, match="arena exhausted"):
     ar.alloc(1)
-  del f                       # dropping the block returns it
+  del f                       # dropping a block frees nothing: object lifetime differs by rank
+  assert ar.free == []
+  ar.end_step()               # the step boundary voids whatever is still allocated
+  assert ar.free == [(0, 1 << 20)] and ar.allocations == 6
+  h = ar.alloc(4096)
+  ar.end_step()
+  h.release()                 # a block of an earlier step is void: nothing is freed twice
   assert ar.free == [(0, 1 << 20)]
 
 
