@@ -57,27 +57,25 @@ RestoreStateTransformationFn = Callable[..., Mapping[str, Any]]
 
 
 def _choose_chunk_shape(write_shape: Sequence[int], target_elements: int):
-  """Largest chunk shape with <= target_elements that evenly divides `write_shape`, found by
-  greedily shrinking the currently largest dimension (t5x/checkpoints.py:103-157)."""
-  assert target_elements >= 1
-  rank = len(write_shape)
-  dim_factors = [[i for i in range(1, size + 1) if size % i == 0] for size in write_shape]
+  """Chunk shape of an array written as `write_shape`: every chunk extent divides its
+  dimension, the chunk holds at most `target_elements` values, and it is reached from the
+  whole array by repeatedly stepping the widest remaining extent (the first one on a tie)
+  down to its next smaller divisor. This walk fixes the on-disk chunk grid, so that files
+  written here are chunked like the reference's (t5x/checkpoints.py:103-157)."""
+  if target_elements < 1:
+    raise ValueError("target_elements must be at least 1")
+  chunk = [int(n) for n in write_shape]
 
-  def total():
-    t = 1
-    for i in range(rank):
-      t *= dim_factors[i][-1]
-    return t
+  def step_down(extent: int, full: int) -> int:
+    for cand in range(extent - 1, 0, -1):
+      if full % cand == 0:
+        return cand
+    raise AssertionError("extent 1 has no smaller divisor")
 
-  while total() > target_elements:
-    dim_to_reduce, dim_to_reduce_size = -1, 1
-    for i in range(rank):
-      size = dim_factors[i][-1]
-      if size > dim_to_reduce_size:
-        dim_to_reduce_size, dim_to_reduce = size, i
-    assert dim_to_reduce_size > 1
-    dim_factors[dim_to_reduce].pop()
-  return [dim_factors[i][-1] for i in range(rank)]
+  while int(np.prod(chunk, dtype=np.int64)) > target_elements:
+    widest = max(range(len(chunk)), key=lambda i: (chunk[i], -i))
+    chunk[widest] = step_down(chunk[widest], int(write_shape[widest]))
+  return chunk
 
 
 @dataclasses.dataclass

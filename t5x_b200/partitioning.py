@@ -162,55 +162,58 @@ class LocalChunkInfo:
 
 
 class LocalChunker:
-  """Which slice of a sharded global array this host holds, and its replica index among
-  hosts holding the same slice (t5x/partitioning.py:424-542)."""
+  """Answers, for this process, "which block of a sharded global array is mine, and which
+  copy of that block am I?" (the role of t5x/partitioning.py:424-542).
+
+  Along every mesh axis the devices of one process form one chunk; `num_chunks[axis]` is how
+  many such chunks the axis has and `chunk_ids[axis]` which of them this process is. A block
+  index over several mesh axes, and the replica index over the axes an array is NOT sharded
+  on, are both mixed-radix numbers in those digits, most significant axis first."""
 
   def __init__(self, global_mesh: Mesh):
     self.global_mesh = global_mesh
-    local_mesh = global_mesh.local_mesh
-    host_location = global_mesh.coords()
-    self.num_chunks = collections.OrderedDict()
-    self.chunk_ids = collections.OrderedDict()
+    per_process = global_mesh.local_mesh.shape
+    here = global_mesh.coords()
     self.mesh_axes = list(global_mesh.shape.keys())
-    for mesh_axis in self.mesh_axes:
-      num_devices_per_chunk = local_mesh.shape[mesh_axis]
-      self.num_chunks[mesh_axis] = global_mesh.shape[mesh_axis] // num_devices_per_chunk
-      self.chunk_ids[mesh_axis] = host_location[mesh_axis] // num_devices_per_chunk
+    self.num_chunks = collections.OrderedDict(
+        (a, global_mesh.shape[a] // per_process[a]) for a in self.mesh_axes)
+    self.chunk_ids = collections.OrderedDict(
+        (a, here[a] // per_process[a]) for a in self.mesh_axes)
+
+  def _mixed_radix(self, axes) -> Tuple[int, int]:
+    """(value, radix product) of this process's chunk digits along `axes`, in that order."""
+    value, span = 0, 1
+    for a in axes:
+      value = value * self.num_chunks[a] + self.chunk_ids[a]
+      span *= self.num_chunks[a]
+    return value, span
+
+  @staticmethod
+  def _as_axes(spec) -> Tuple[str, ...]:
+    if not spec:
+      return ()
+    return (spec,) if isinstance(spec, str) else tuple(a for a in spec if a)
 
   def get_local_chunk_info(self, global_shape: Tuple[int, ...],
                            mesh_axes: Sequence[Optional[str]]) -> LocalChunkInfo:
-    local_slice = [slice(None) for _ in global_shape]
-    sharded_mesh_axes = set()
-    for i, (mesh_axis, size) in enumerate(zip(mesh_axes, global_shape)):
-      if not mesh_axis:
+    block, used = [], set()
+    for extent, spec in zip(global_shape, mesh_axes):
+      axes = self._as_axes(spec)
+      if not axes:
+        block.append(slice(None))
         continue
-      axes = (mesh_axis,) if isinstance(mesh_axis, str) else tuple(mesh_axis)
-      sharded_mesh_axes.update(axes)
-      chunk_id, num = 0, 1
-      for a in axes:
-        chunk_id = chunk_id * self.num_chunks[a] + self.chunk_ids[a]
-        num *= self.num_chunks[a]
-      chunk_size = size // num
-      local_slice[i] = slice(chunk_id * chunk_size, (chunk_id + 1) * chunk_size)
-    return LocalChunkInfo(tuple(local_slice), self.get_replica_id(sharded_mesh_axes))
+      used.update(axes)
+      index, count = self._mixed_radix(axes)
+      width = extent // count
+      block.append(slice(index * width, (index + 1) * width))
+    return LocalChunkInfo(tuple(block), self.get_replica_id(used))
 
   def get_shard_id(self, sharded_mesh_axes: Union[str, Set[Optional[str]], Sequence]) -> int:
-    if isinstance(sharded_mesh_axes, str):
-      sharded_mesh_axes = (sharded_mesh_axes,)
-    shard_id = 0
-    for mesh_axis in sharded_mesh_axes:
-      shard_id = shard_id * self.num_chunks[mesh_axis] + self.chunk_ids[mesh_axis]
-    return shard_id
+    return self._mixed_radix(self._as_axes(sharded_mesh_axes))[0]
 
   def get_replica_id(self, sharded_mesh_axes: Union[str, Set[Optional[str]], Sequence]) -> int:
-    if isinstance(sharded_mesh_axes, str):
-      sharded_mesh_axes = (sharded_mesh_axes,)
-    replica_id = 0
-    for mesh_axis in self.mesh_axes:
-      if mesh_axis in sharded_mesh_axes:
-        continue
-      replica_id = replica_id * self.num_chunks[mesh_axis] + self.chunk_ids[mesh_axis]
-    return replica_id
+    sharded = set(self._as_axes(sharded_mesh_axes))
+    return self._mixed_radix([a for a in self.mesh_axes if a not in sharded])[0]
 
 
 # ----------------------------------------------------------------------------

@@ -700,85 +700,76 @@ class BaseAction(abc.ABC):
 ActionMapType = Mapping[ActionMode, Sequence[BaseAction]]
 
 
-def _scalar_value(m):
+def _monitored_value(metrics_by_task, task: str, metric: str) -> Optional[float]:
+  """The float behind metrics_by_task[task][metric], or None (with a warning naming what is
+  missing) when the task, the metric or a scalar value is not there."""
+  per_task = metrics_by_task.get(task)
+  if per_task is None:
+    logging.warning("action: no metrics for task %r (tasks present: %s)", task,
+                    sorted(metrics_by_task))
+    return None
+  if metric not in per_task:
+    logging.warning("action: task %r reports no metric %r", task, metric)
+    return None
+  m = per_task[metric]
   if isinstance(m, metric_writers.Scalar):
     return metric_writers.to_float(m)
   if isinstance(m, (float, int)):
     return float(m)
+  logging.warning("action: metric %r of task %r is a %s, not a scalar", metric, task,
+                  type(m).__name__)
   return None
 
 
-def _lookup(action, metrics_by_task, task, metric):
-  if task not in metrics_by_task:
-    logging.warning("Monitoring task: %s does not exist in all task metrics. Available tasks "
-                    "are : %s", task, list(metrics_by_task.keys()))
-    return None
-  if metric not in metrics_by_task[task]:
-    logging.warning("Metric : %s does not exist in metrics for task : %s", metric, task)
-    return None
-  v = _scalar_value(metrics_by_task[task][metric])
-  if v is None:
-    logging.warning("Metric %s does not have Scalar type. Found %s.", metric,
-                    type(metrics_by_task[task][metric]))
-  return v
-
-
 class EarlyStoppingAction(BaseAction):
-  """Stops when the monitored metric has not improved `patience` times in a row
-  (t5x/trainer.py:1100-1228)."""
+  """Asks to stop once the monitored metric has gone `patience` evaluations without getting
+  better (the behaviour of t5x/trainer.py:1100-1228).
+
+  A sliding window holds the last `patience` values. "Better" means lower for mode 'min' and
+  higher for 'max', by more than `atol + rtol * |previous|`. Training stops when no value in
+  the full window improved on the one before it."""
 
   def __init__(self, metric: Tuple[str, str], mode: str, patience: int = 3, atol: float = 0.0,
                rtol: float = 0.0):
+    if mode not in ("min", "max"):
+      raise ValueError(f"mode must be 'min' or 'max', got {mode!r}")
+    if atol < 0 or rtol < 0:
+      raise ValueError("atol and rtol must be >= 0")
     self._task, self._metric = metric
-    if mode not in ["min", "max"]:
-      raise ValueError('mode must be in ["min", "max"]')
-    self._mode = mode
-    if atol < 0:
-      raise ValueError("atol must be greater equal than 0")
-    if rtol < 0:
-      raise ValueError("rtol must be greater equal than 0")
+    self._sign = 1.0 if mode == "min" else -1.0  # compare sign * value, always minimising
     self._atol, self._rtol = atol, rtol
     self._patience = patience
-    self._metric_history = []
+    import collections
+    self._window = collections.deque(maxlen=patience)
 
-  def _compare_fn(self, current, previous):
-    delta = self._atol + self._rtol * abs(previous)
-    if self._mode == "max":
-      delta *= -1
-    if self._mode == "min":
-      return current >= previous - delta
-    return current <= previous - delta
+  def _stalled(self, now: float, before: float) -> bool:
+    tolerance = self._atol + self._rtol * abs(before)
+    return self._sign * now >= self._sign * before - tolerance
 
   def run(self, train_state, metrics_by_task) -> bool:
-    v = _lookup(self, metrics_by_task, self._task, self._metric)
-    if v is None:
+    value = _monitored_value(metrics_by_task, self._task, self._metric)
+    if value is None:
       return False
-    self._metric_history.append(v)
-    if len(self._metric_history) < self._patience:
+    self._window.append(value)
+    if len(self._window) < self._patience:
       return False
-    if all(self._compare_fn(self._metric_history[i + 1], self._metric_history[i])
-           for i in range(self._patience - 1)):
-      logging.warning("Requested `stop_training`: metric %s for task %s has not improved for %s "
-                      "iterations; history %s", self._metric, self._task, self._patience,
-                      self._metric_history)
+    values = list(self._window)
+    if all(self._stalled(b, a) for a, b in zip(values, values[1:])):
+      logging.warning("early stopping: %s of task %s did not improve over the last %d "
+                      "evaluations (%s)", self._metric, self._task, self._patience, values)
       return True
-    self._metric_history.pop(0)
     return False
 
 
 class TerminateOnNanAction(BaseAction):
-  """Stops when the monitored metric is NaN or Inf (t5x/trainer.py:1231-1285)."""
+  """Asks to stop when the monitored metric is not finite (t5x/trainer.py:1231-1285)."""
 
   def __init__(self, task: str, metric: str = "loss"):
-    self._task = task
-    self._metric = metric
+    self._task, self._metric = task, metric
 
   def run(self, train_state, metrics_by_task) -> bool:
-    v = _lookup(self, metrics_by_task, self._task, self._metric)
-    if v is None:
+    value = _monitored_value(metrics_by_task, self._task, self._metric)
+    if value is None or np.isfinite(value):
       return False
-    if np.isnan(v) or np.isinf(v):
-      logging.warning("Requested `stop_training`: NaN encountered in metric for task : %s",
-                      self._task)
-      return True
-    return False
+    logging.warning("terminate on NaN: %s of task %s is %s", self._metric, self._task, value)
+    return True
