@@ -1,9 +1,9 @@
 """Top-k / top-p masking (API of t5x/binary_search.py).
 
 The reference finds the per-row cutoff with a 32-step bitwise binary search over the float
-total order, because XLA lacks a cheap partial sort. Here the cutoff comes from a sort /
-top-k on the device; the bit-search helpers are kept with the same contracts for callers
-that use them directly.
+total order, because XLA lacks a cheap partial sort. On CUDA the cutoff comes from a four-pass
+radix select inside one kernel (csrc/beam.cu); on the CPU from a sort / top-k. The bit-search
+helpers are kept with the same contracts for callers that use them directly.
 """
 from __future__ import annotations
 
@@ -51,6 +51,9 @@ def topk_mask(x: torch.Tensor, k: int, replace_val) -> torch.Tensor:
   """Keeps the k largest entries of each row; the rest become `replace_val`. Entries equal
   to the k-th value are all kept (t5x/binary_search.py:167-227)."""
   k = min(int(k), x.shape[-1])
+  if x.is_cuda and x.dtype == torch.float32 and k >= 1:
+    from t5x_b200.ops import native
+    return native.topk_topp_mask(x, k, None, float(replace_val))
   kth = torch.topk(x, k, dim=-1).values[..., -1:]
   return torch.where(x >= kth, x, torch.full_like(x, replace_val))
 
@@ -58,6 +61,12 @@ def topk_mask(x: torch.Tensor, k: int, replace_val) -> torch.Tensor:
 def topp_mask(logits: torch.Tensor, p, replace_val) -> torch.Tensor:
   """Nucleus mask: keeps the smallest set of top logits whose probability mass reaches `p`
   (entries tied with the cutoff are kept) (t5x/binary_search.py:230-299)."""
+  if logits.is_cuda and logits.dtype == torch.float32:
+    from t5x_b200.ops import native
+    p_arg = p if not isinstance(p, torch.Tensor) else (
+        p.reshape(-1).expand(logits.reshape(-1, logits.shape[-1]).shape[0]) if p.dim() > 0
+        else float(p))
+    return native.topk_topp_mask(logits, 0, p_arg, float(replace_val))
   probs = torch.softmax(logits.float(), dim=-1)
   sorted_probs, order = torch.sort(probs, dim=-1, descending=True)
   cum = torch.cumsum(sorted_probs, dim=-1)

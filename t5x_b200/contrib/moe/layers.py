@@ -86,6 +86,50 @@ class RouterWeights(nn.Module):
                                     device=device)
 
 
+class _FusedRouterFn(torch.autograd.Function):
+  """The whole tokens-choose router as native kernels (csrc/router.cu): fp32 logits, softmax,
+  top-k, capacity positions in token order (first choices before second choices), the two
+  losses and the usage metrics in three launches; backward in two. Differentiable outputs:
+  the gates (zero where a choice lost its slot), the load-balancing loss and the z-loss."""
+
+  @staticmethod
+  def forward(ctx, tokens, w, k, capacity):
+    from t5x_b200.ops import native
+    wc = w.detach().float().contiguous()
+    fwd = native.moe_router_fwd(tokens, wc, k, capacity)
+    ctx.save_for_backward(tokens, wc)
+    ctx.fwd, ctx.cfg, ctx.w_dtype = fwd, (k, capacity), w.dtype
+    m = fwd["metrics"]
+    index, flat_slot = fwd["index"], fwd["flat_slot"]
+    ctx.mark_non_differentiable(index, flat_slot, m)
+    return fwd["gate"], m[0].clone(), m[1].clone(), index, flat_slot, m
+
+  @staticmethod
+  def backward(ctx, dgate, daux, dz, _di, _ds, _dm):
+    from t5x_b200.ops import native
+    tokens, wc = ctx.saved_tensors
+    k, capacity = ctx.cfg
+    zero = torch.zeros((), dtype=torch.float32, device=tokens.device)
+    coef = torch.stack([zero if daux is None else daux.float().reshape(()),
+                        zero if dz is None else dz.float().reshape(())])
+    if dgate is None:
+      dgate = torch.zeros_like(ctx.fwd["gate"])
+    dx, dw = native.moe_router_bwd(tokens, wc, k, capacity, ctx.fwd, dgate, coef,
+                                   need_dx=ctx.needs_input_grad[0])
+    ctx.fwd = None
+    return dx, dw.to(ctx.w_dtype), None, None
+
+
+def fused_router_usable(tokens: torch.Tensor, num_experts: int, k: int) -> bool:
+  import os
+  from t5x_b200.ops import native
+  if os.environ.get("T5X_B200_MOE_FUSED_ROUTER", "1") == "0":
+    return False
+  return (tokens.is_cuda and tokens.dtype == torch.bfloat16 and tokens.dim() == 2 and
+          num_experts <= native.ROUTER_MAX_EXPERTS and k <= native.ROUTER_MAX_CHOICES and
+          (num_experts * tokens.shape[1] + 9 * tokens.shape[1]) * 4 <= 190 * 1024)
+
+
 class TokensChooseRouter(nn.Module):
   """Every token picks its top-k experts; an expert keeps the first `capacity` tokens that
   picked it (all first choices are placed before any second choice)."""
@@ -101,8 +145,16 @@ class TokensChooseRouter(nn.Module):
   def forward(self, tokens: torch.Tensor, capacity: int, enable_dropout: bool = False):
     """tokens [T, d] -> dict(expert_index [T,k], slot [T,k] (−1 = dropped), gate [T,k],
     plus the two losses and the three usage metrics)."""
+    jitter = enable_dropout and self.jitter_noise > 0
+    if not jitter and fused_router_usable(tokens, self.num_experts, self.k):
+      gate, aux, z, index, flat_slot, m = _FusedRouterFn.apply(
+          tokens.contiguous(), self.router_weights.w.kernel, self.k, capacity)
+      metrics = {"auxiliary_loss": aux, "router_z_loss": z,
+                 "fraction_tokens_left_behind": m[2], "expert_usage": m[3],
+                 "router_confidence": m[4]}
+      return {"expert_index": index, "flat_slot": flat_slot, "gate": gate}, metrics
     x = tokens.float()
-    if enable_dropout and self.jitter_noise > 0:
+    if jitter:
       x = x * torch.empty_like(x).uniform_(1.0 - self.jitter_noise, 1.0 + self.jitter_noise)
     logits = x @ self.router_weights.w.kernel.float()
     probs = torch.softmax(logits, dim=-1)
@@ -127,7 +179,8 @@ class TokensChooseRouter(nn.Module):
         "expert_usage": kept.float().sum() / float(e * capacity),
         "router_confidence": (gate * kept.float()).sum() / dispatched_somewhere.clamp(min=1.0),
     }
-    return {"expert_index": index, "slot": slot, "gate": gate * kept.to(gate.dtype)}, metrics
+    return {"expert_index": index, "slot": slot, "gate": gate * kept.to(gate.dtype),
+            "flat_slot": _flat_slots(index, slot, capacity)}, metrics
 
 
 # ----------------------------------------------------------------------------
@@ -311,7 +364,7 @@ class MoeLayer(nn.Module):
     cap = expert_capacity(b * l, self.num_experts, cf, self.k, self.min_expert_capacity)
     route, metrics = self.router(tokens, cap, enable_dropout)
     _COLLECTED.append(metrics)
-    flat_slot = _flat_slots(route["expert_index"], route["slot"], cap)
+    flat_slot = route["flat_slot"]
     from t5x_b200.ops import moe as moe_ops
     if moe_ops.enabled(tokens):
       # NVLink path: rows are pushed into / pulled from the owners' buffers by the kernels
@@ -319,6 +372,7 @@ class MoeLayer(nn.Module):
       y = self.expert(x)
       out = moe_ops.FusedCombine.apply(y, flat_slot, route["gate"], self.num_experts, cap)
     else:
+      flat_slot = flat_slot.long()
       x = _Dispatch.apply(tokens, flat_slot, self.num_experts, cap)
       y = self.expert(x)
       out = _Combine.apply(y, flat_slot, route["gate"].to(self.dtype), self.num_experts, cap)

@@ -438,6 +438,22 @@ def _temperature_sample_single_trial(inputs, cache, tokens_to_logits, eos_id, ge
          else torch.full((batch_size,), max_decode_len, dtype=torch.int64, device=device))
   scalar_index = initial_index is None
 
+  # On CUDA one kernel per step does the scaling, the top-k / top-p cut-off (radix select),
+  # the draw (Gumbel noise from a counter-based generator keyed by this call's nonce and the
+  # step) and the log-probability; the tensor-op statements below are the CPU path.
+  native_nonce = None
+  if device.type == "cuda":
+    from t5x_b200.ops import native as _native
+    if gen is not None:
+      native_nonce = int(torch.randint(0, 2 ** 62, (1,), generator=gen, device=gen.device).item())
+    else:
+      native_nonce = int(torch.empty((), dtype=torch.int64).random_().item())
+
+  def native_sample(logits, temp, step):
+    return _native.sample_tokens(logits.contiguous(), temperature=temp, topk=topk or 0,
+                                 topp=topp or 0.0, rescale_log_probs=rescale_log_probs,
+                                 seed=native_nonce, stream_id=step)
+
   def nonzero_temp(logits, temp):
     scaled = logits / torch.clamp(temp, min=MIN_TEMPERATURE)
     if topk:
@@ -467,7 +483,11 @@ def _temperature_sample_single_trial(inputs, cache, tokens_to_logits, eos_id, ge
     logits = logits.float()
     if logit_callback_fn is not None:
       logits = logit_callback_fn(logits, state)
-    if temperature_t.dim() == 1:
+    if native_nonce is not None and logits.dim() == 2:
+      temp = (temperature_t.repeat_interleave(num_decodes) if temperature_t.dim() == 1
+              else float(temperature_t))
+      next_token, next_log_prob = native_sample(logits, temp, int(state.step))
+    elif temperature_t.dim() == 1:
       temp_rows = temperature_t.repeat_interleave(num_decodes)[:, None]
       nt_a, lp_a = nonzero_temp(logits, temp_rows)
       nt_b, lp_b = zero_temp(logits)

@@ -146,6 +146,7 @@ class GraphBeamDecoder:
     self.positions = torch.arange(self.L, device=dev)
     self.min_brevity = float(decoding.brevity_penalty(alpha, self.L))
     self.graph: Optional[torch.cuda.CUDAGraph] = None
+    self._beam_scratch = None
 
   # ------------------------------------------------------------------------------------------
   def _reset(self):
@@ -218,6 +219,21 @@ class GraphBeamDecoder:
                               residual=residual, workspace=self._ws)
 
   def _beam_step(self, flat_logits: torch.Tensor) -> None:
+    """One step of the search state update. Beam widths 1, 2, 4 and 8 run the two native
+    kernels of csrc/beam.cu (log-softmax partials + candidate selection, then all of the
+    bookkeeping per example); other widths run the same algorithm as tensor ops."""
+    if self.k in (1, 2, 4, 8) and flat_logits.dtype == torch.float32:
+      if self._beam_scratch is None:
+        self._beam_scratch = native.BeamStepScratch(self.b, self.k, flat_logits.shape[1], self.dev)
+      native.beam_step(flat_logits, batch=self.b, beams=self.k, eos_id=self.eos,
+                       alpha=self.alpha, min_brevity=self.min_brevity, live_lp=self.live_lp,
+                       live_seqs=self.live_seqs, fin_seqs=self.fin_seqs,
+                       fin_scores=self.fin_scores, fin_flags=self.fin_flags, ancestry=self.anc,
+                       cur=self.cur, terminated=self.terminated, scratch=self._beam_scratch)
+      return
+    self._beam_step_tensor_ops(flat_logits)
+
+  def _beam_step_tensor_ops(self, flat_logits: torch.Tensor) -> None:
     b, k, L = self.b, self.k, self.L
     ci = self.cur.long()
     logits = flat_logits.view(b, k, -1)

@@ -41,7 +41,29 @@ class T5Config(t5_network.T5Config):
 
 def _maybe_remat(fn, policy: str, training: bool):
   if policy == "full" and training and torch.is_grad_enabled():
-    return lambda *a, **kw: torch.utils.checkpoint.checkpoint(fn, *a, use_reentrant=False, **kw)
+    from t5x_b200.ops import reference as ref
+
+    def rematerialised(*a, **kw):
+      # The recomputation in backward must draw the dropout masks of the first pass: every
+      # dropout call is numbered, so the block remembers the number it started at and the
+      # second pass counts from there again (and leaves the counter where it found it).
+      first_site = ref.dropout_site_state()
+      passes = [0]
+
+      def block(*ba, **bkw):
+        passes[0] += 1
+        if passes[0] == 1:
+          return fn(*ba, **bkw)
+        resume = ref.dropout_site_state()
+        ref.set_dropout_site_state(first_site)
+        try:
+          return fn(*ba, **bkw)
+        finally:
+          ref.set_dropout_site_state(resume)
+
+      return torch.utils.checkpoint.checkpoint(block, *a, use_reentrant=False, **kw)
+
+    return rematerialised
   if policy not in (None, "none", "minimal", "full"):
     raise ValueError(f"unknown remat_policy {policy!r}")
   return fn

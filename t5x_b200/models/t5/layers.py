@@ -311,6 +311,15 @@ class RelativePositionBiases(nn.Module):
     return b[None]
 
 
+def sp_output_dropout(y_sp: torch.Tensor, rate: float, seq_len: int) -> torch.Tensor:
+  """Dropout (mask shared along the sequence) of this rank's rows of a row-sharded
+  [batch * seq_len, emb] activation: the rows' global indices select the mask, so the ranks
+  together apply exactly the mask one rank holding all rows would."""
+  st = pstate.get()
+  return F.dropout(y_sp, rate, True, broadcast_dims=(-2,), seq_len=seq_len,
+                   row_offset=st.model_rank * y_sp.shape[0])
+
+
 class MultiHeadDotProductAttention(nn.Module):
   """Multi-head attention with q/k/v/out projections (layers.py:132-346).
 
@@ -447,7 +456,7 @@ class MultiHeadDotProductAttention(nn.Module):
                  kv_full: Optional[torch.Tensor] = None, h_block=None, bias_table=None,
                  bidirectional: bool = True, num_buckets: int = 32, max_distance: int = 128,
                  key_mask=None, causal: bool = False, q_segment_ids=None,
-                 kv_segment_ids=None) -> torch.Tensor:
+                 kv_segment_ids=None, dropout_rate: float = 0.0) -> torch.Tensor:
     """Row-sharded ("sequence parallel") form under tensor parallelism: `h_sp` / `x_sp` are
     this rank's rows of the normed input and of the residual stream ([batch * lq / T, emb]).
     The q/k/v projections gather the rows inside their GEMM kernel and the output projection
@@ -470,8 +479,11 @@ class MultiHeadDotProductAttention(nn.Module):
     k = k.view(batch, lk, *hd)
     v = v.view(batch, lk, *hd)
     x = self._attend(q, k, v, bias_table, bidirectional, num_buckets, max_distance, key_mask,
-                     causal, q_segment_ids, kv_segment_ids, None, None, 0, False)
+                     causal, q_segment_ids, kv_segment_ids, None, None, 0, dropout_rate > 0.0)
     x = x.reshape(batch * lq, self.local_heads * self.head_dim)
+    if dropout_rate > 0.0:
+      return x_sp + sp_output_dropout(tp_fused.linear_reduce_scatter(x, self.out.kernel, None),
+                                      dropout_rate, lq)
     return tp_fused.linear_reduce_scatter(x, self.out.kernel, x_sp)
 
   def _project_out(self, x, b, lq, residual):
@@ -492,7 +504,15 @@ class MultiHeadDotProductAttention(nn.Module):
       qg = q.view(b0, beams_per_kv * lq, h, d)
       out = F.attention(qg, k, v, key_mask=key_mask, float32_logits=self.float32_logits)
       return out.reshape(bb, lq, h, d)
-    if per_example_bias is not None or (enable_dropout and self.dropout_rate > 0.0):
+    drop = enable_dropout and self.dropout_rate > 0.0
+    if drop and per_example_bias is None and q.is_cuda and q.dtype == torch.bfloat16:
+      from t5x_b200.ops import attention as attn_ops
+      if attn_ops.flash_supported(q, k, v, explicit_bias, extra_mask):
+        # the dropout mask of the attention weights is shared along the query axis, so it can
+        # be applied to the rows of v instead and the flash kernel runs unchanged
+        v = F.attention_value_dropout(v, self.dropout_rate, True)
+        drop = False
+    if per_example_bias is not None or drop:
       dt = torch.float32 if self.float32_logits else q.dtype
       logits = torch.einsum("bqhd,bkhd->bhqk", q.to(dt), k.to(dt))
       if per_example_bias is not None:
@@ -548,10 +568,13 @@ class MlpBlock(nn.Module):
                                               dtype, 1, device))
     self.wo = DenseGeneral(intermediate_dim, emb_dim, ("mlp", "embed"), init, dtype, 0, device)
 
-  def forward_sp(self, h_sp: torch.Tensor, x_sp: torch.Tensor, h_block=None) -> torch.Tensor:
-    """Row-sharded form under tensor parallelism (no dropout): wi gathers the rows inside its
-    GEMM kernel, wo scatters its partial sums from its epilogue; returns this rank's rows of
-    the new residual stream. `h_block`: the arena block `h_sp` was written into, if any."""
+  def forward_sp(self, h_sp: torch.Tensor, x_sp: torch.Tensor, h_block=None, *,
+                 seq_len: Optional[int] = None, dropout_rate: float = 0.0) -> torch.Tensor:
+    """Row-sharded form under tensor parallelism: wi gathers the rows inside its GEMM kernel,
+    wo scatters its partial sums from its epilogue; returns this rank's rows of the new
+    residual stream. `h_block`: the arena block `h_sp` was written into, if any. With
+    `dropout_rate` > 0 (training) the intermediate and the block output are dropped out with
+    masks shared along the `seq_len` positions of a sequence."""
     from t5x_b200.parallel import tp_fused
     if self.activations == ("gelu", "linear"):
       g = tp_fused.all_gather_gated_gelu(h_sp, self.wi_0.kernel, self.wi_1.kernel, block=h_block)
@@ -566,6 +589,11 @@ class MlpBlock(nn.Module):
       for act, h in zip(self.activations, hs):
         h = ref.ACTIVATIONS[act](h)
         g = h if g is None else g * h
+    if dropout_rate > 0.0:
+      g = F.dropout(g, self.dropout_rate, True, broadcast_dims=(-2,), seq_len=seq_len,
+                    sharded=True)
+      return x_sp + sp_output_dropout(tp_fused.linear_reduce_scatter(g, self.wo.kernel, None),
+                                      dropout_rate, seq_len)
     return tp_fused.linear_reduce_scatter(g, self.wo.kernel, x_sp)
 
   def forward(self, inputs: torch.Tensor, residual: Optional[torch.Tensor] = None,
@@ -580,7 +608,8 @@ class MlpBlock(nn.Module):
       for i, act in enumerate(self.activations):
         h = ref.ACTIVATIONS[act](getattr(self, f"wi_{i}")(x_in))
         x = h if x is None else x * h
-    x = ref.dropout(x, self.dropout_rate, enable_dropout, broadcast_dims=(-2,))
+    x = F.dropout(x, self.dropout_rate, enable_dropout, broadcast_dims=(-2,),
+                  sharded=pstate.get().model_size > 1)
     st = pstate.get()
     if st.model_size == 1:
       return self.wo(x, residual=residual)

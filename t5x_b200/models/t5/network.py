@@ -47,8 +47,8 @@ class T5Config:
   relpos_max_distance: int = 128
 
 
-def _dropout(x, rate, enable, broadcast=True):
-  return ref.dropout(x, rate, enable, broadcast_dims=(-2,) if broadcast else ())
+def _dropout(x, rate, enable, broadcast=True, **kw):
+  return F.dropout(x, rate, enable, broadcast_dims=(-2,) if broadcast else (), **kw)
 
 
 class EncoderLayer(nn.Module):
@@ -88,9 +88,11 @@ class EncoderLayer(nn.Module):
       x = self.mlp(h, residual=x)
     return x
 
-  def forward_sp(self, x_sp, batch, length, *, bias_table, key_mask, segment_ids=None):
-    """Row-sharded residual stream under fused tensor parallelism (no dropout)."""
+  def forward_sp(self, x_sp, batch, length, *, bias_table, key_mask, segment_ids=None,
+                 enable_dropout=False):
+    """Row-sharded residual stream under fused tensor parallelism."""
     c = self.config
+    rate = c.dropout_rate if enable_dropout else 0.0
     _mark_partial(self.pre_attention_layer_norm, self.pre_mlp_layer_norm)
     # each norm writes straight into this rank's rows of the buffer the next GEMM gathers
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
@@ -98,10 +100,15 @@ class EncoderLayer(nn.Module):
     x_sp = self.attention.forward_sp(
         h, x_sp, batch, length, h_block=blk, bias_table=bias_table, bidirectional=True,
         num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance, key_mask=key_mask,
-        q_segment_ids=segment_ids, kv_segment_ids=segment_ids)
+        q_segment_ids=segment_ids, kv_segment_ids=segment_ids, dropout_rate=rate)
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
     x_sp, h = self.pre_mlp_layer_norm(x_sp, out=dst, with_residual=True)
-    return self.mlp.forward_sp(h, x_sp, h_block=blk)
+    return self.mlp.forward_sp(h, x_sp, h_block=blk, seq_len=length, dropout_rate=rate)
+
+
+def _sp_dropout_ok(x, c, enable_dropout) -> bool:
+  """The row-sharded path handles dropout through the in-kernel masks (CUDA, bf16)."""
+  return not (enable_dropout and c.dropout_rate > 0) or (x.is_cuda and x.dtype == torch.bfloat16)
 
 
 def _mark_partial(*norms) -> None:
@@ -179,10 +186,12 @@ class DecoderLayer(nn.Module):
     return x
 
   def forward_sp(self, x_sp, encoded, batch, length, *, bias_table, decoder_key_mask,
-                 encoder_key_mask, decoder_segment_ids=None, encoder_segment_ids=None):
-    """Row-sharded residual stream under fused tensor parallelism (training, no dropout);
-    `encoded` is the replicated encoder output."""
+                 encoder_key_mask, decoder_segment_ids=None, encoder_segment_ids=None,
+                 enable_dropout=False):
+    """Row-sharded residual stream under fused tensor parallelism (training); `encoded` is the
+    replicated encoder output."""
     c = self.config
+    rate = c.dropout_rate if enable_dropout else 0.0
     _mark_partial(self.pre_self_attention_layer_norm, self.pre_cross_attention_layer_norm,
                   self.pre_mlp_layer_norm)
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
@@ -191,15 +200,16 @@ class DecoderLayer(nn.Module):
         h, x_sp, batch, length, h_block=blk, bias_table=bias_table, bidirectional=False,
         num_buckets=c.relpos_num_buckets, max_distance=c.relpos_max_distance,
         key_mask=decoder_key_mask, causal=True, q_segment_ids=decoder_segment_ids,
-        kv_segment_ids=decoder_segment_ids)
+        kv_segment_ids=decoder_segment_ids, dropout_rate=rate)
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
     x_sp, h = self.pre_cross_attention_layer_norm(x_sp, out=dst, with_residual=True)
     x_sp = self.encoder_decoder_attention.forward_sp(
         h, x_sp, batch, length, kv_full=encoded, h_block=blk, key_mask=encoder_key_mask,
-        q_segment_ids=decoder_segment_ids, kv_segment_ids=encoder_segment_ids)
+        q_segment_ids=decoder_segment_ids, kv_segment_ids=encoder_segment_ids,
+        dropout_rate=rate)
     blk, dst = tp_fused.rows_buffer(*x_sp.shape)
     x_sp, h = self.pre_mlp_layer_norm(x_sp, out=dst, with_residual=True)
-    return self.mlp.forward_sp(h, x_sp, h_block=blk)
+    return self.mlp.forward_sp(h, x_sp, h_block=blk, seq_len=length, dropout_rate=rate)
 
 
 class Encoder(nn.Module):
@@ -221,15 +231,22 @@ class Encoder(nn.Module):
     key_mask = encoder_input_tokens > 0
     x = self._shared[0](encoder_input_tokens.long())
     b, l, d = x.shape
-    if tp_fused.usable(x, b * l) and not (enable_dropout and c.dropout_rate > 0):
+    if tp_fused.usable(x, b * l) and _sp_dropout_ok(x, c, enable_dropout):
       # row-sharded residual stream; collectives inside the GEMM kernels
+      drop = enable_dropout and c.dropout_rate > 0
       x_sp = tp_fused.scatter_rows(x.reshape(b * l, d))
+      if drop:
+        x_sp = layers.sp_output_dropout(x_sp, c.dropout_rate, l)
       for i in range(c.num_encoder_layers):
         x_sp = getattr(self, f"layers_{i}").forward_sp(
             x_sp, b, l, bias_table=self.relpos_bias.rel_embedding, key_mask=key_mask,
-            segment_ids=encoder_segment_ids)
+            segment_ids=encoder_segment_ids, enable_dropout=drop)
       _mark_partial(self.encoder_norm)
-      return tp_fused.gather_rows(self.encoder_norm(x_sp), partial_grads=True).view(b, l, d)
+      y_sp = self.encoder_norm(x_sp)
+      if drop:  # the mask after the final norm is not shared along the sequence
+        y_sp = F.dropout(y_sp, c.dropout_rate, True,
+                         row_offset=pstate.get().model_rank * y_sp.shape[0])
+      return tp_fused.gather_rows(y_sp, partial_grads=True).view(b, l, d)
     x = _dropout(x, c.dropout_rate, enable_dropout)
     for i in range(c.num_encoder_layers):
       x = getattr(self, f"layers_{i}")(x, bias_table=self.relpos_bias.rel_embedding,
@@ -275,16 +292,23 @@ class Decoder(nn.Module):
     y = self._shared[0](decoder_input_tokens.long())
     b, l, d = y.shape
     if (tp_fused.usable(y, b * l) and not decode and cache is None and
-        not (enable_dropout and c.dropout_rate > 0)):
+        _sp_dropout_ok(y, c, enable_dropout)):
+      drop = enable_dropout and c.dropout_rate > 0
       y_sp = tp_fused.scatter_rows(y.reshape(b * l, d))
+      if drop:
+        y_sp = layers.sp_output_dropout(y_sp, c.dropout_rate, l)
       for i in range(c.num_decoder_layers):
         y_sp = getattr(self, f"layers_{i}").forward_sp(
             y_sp, encoded, b, l, bias_table=self.relpos_bias.rel_embedding,
             decoder_key_mask=decoder_key_mask, encoder_key_mask=encoder_key_mask,
-            decoder_segment_ids=decoder_segment_ids, encoder_segment_ids=encoder_segment_ids)
+            decoder_segment_ids=decoder_segment_ids, encoder_segment_ids=encoder_segment_ids,
+            enable_dropout=drop)
       _mark_partial(self.decoder_norm)
+      y_sp = self.decoder_norm(y_sp)
+      if drop:
+        y_sp = layers.sp_output_dropout(y_sp, c.dropout_rate, l)
       # the vocabulary-parallel loss hands back a gradient already summed over the model axis
-      return tp_fused.gather_rows(self.decoder_norm(y_sp), partial_grads=False).view(b, l, d)
+      return tp_fused.gather_rows(y_sp, partial_grads=False).view(b, l, d)
     y = _dropout(y, c.dropout_rate, enable_dropout)
     for i in range(c.num_decoder_layers):
       y = getattr(self, f"layers_{i}")(

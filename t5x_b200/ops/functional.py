@@ -327,6 +327,80 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, dtype: torch.dtype) -> tor
 
 
 # ----------------------------------------------------------------------------
+# Dropout
+# ----------------------------------------------------------------------------
+class _DropoutFn(torch.autograd.Function):
+  """x * mask / keep with the mask drawn inside the kernel from (seed, site, key); backward
+  runs the same kernel on the gradient."""
+
+  @staticmethod
+  def forward(ctx, x, rate, seed, site, group_rows, col_group, row_offset):
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+      x2 = x2.contiguous()
+    ctx.cfg = (rate, seed, site, group_rows, col_group, row_offset)
+    y = native.dropout_rows(x2, rate, seed, site, group_rows=group_rows, col_group=col_group,
+                            row_offset=row_offset)
+    return y.view(x.shape)
+
+  @staticmethod
+  def backward(ctx, dy):
+    rate, seed, site, group_rows, col_group, row_offset = ctx.cfg
+    d2 = dy.reshape(-1, dy.shape[-1])
+    if d2.stride(-1) != 1:
+      d2 = d2.contiguous()
+    dx = native.dropout_rows(d2, rate, seed, site, group_rows=group_rows, col_group=col_group,
+                             row_offset=row_offset)
+    return dx.view(dy.shape), None, None, None, None, None, None
+
+
+def _dropout_seed_and_site(sharded: bool):
+  seed = ref.dropout_seed()
+  if seed is None:  # no step seed: one from the host generator (no device synchronisation)
+    seed = int(torch.empty((), dtype=torch.int64).random_().item())
+  site = ref.next_dropout_site()
+  if sharded:
+    # activations whose columns are split over the model axis: every rank draws its own mask
+    from t5x_b200.parallel import state as pstate
+    site = (site & 0xFFFFFF) | ((pstate.get().model_rank & 0xFF) << 24)
+  return seed, site
+
+
+def dropout(x: torch.Tensor, rate: float, training: bool, broadcast_dims=(), *,
+            seq_len: Optional[int] = None, row_offset: int = 0,
+            sharded: bool = False) -> torch.Tensor:
+  """Dropout whose mask is shared along `broadcast_dims` (`()` or `(-2,)`, the length axis of
+  [batch, length, features]; t5x/examples/t5/network.py:76-78). On CUDA with bf16 the mask is
+  drawn inside the kernel. For a 2-D block of rows of a row-sharded [batch * length, features]
+  activation pass `seq_len` (the length) and `row_offset` (global index of the block's first
+  row): the block then gets the mask the whole tensor would get. `sharded`: the feature axis is
+  split over the model axis, so ranks draw independent masks."""
+  if not training or rate == 0.0:
+    return x
+  bd = tuple(broadcast_dims)
+  if _native_ok(x) and bd in ((), (-2,)):
+    seed, site = _dropout_seed_and_site(sharded)
+    if bd == (-2,):
+      group_rows = int(seq_len if seq_len is not None else x.shape[-2])
+    else:
+      group_rows = 1
+    return _DropoutFn.apply(x, float(rate), seed, site, group_rows, 1, int(row_offset))
+  return ref.dropout(x, rate, training, broadcast_dims=broadcast_dims)
+
+
+def attention_value_dropout(v: torch.Tensor, rate: float, training: bool) -> torch.Tensor:
+  """Attention-weight dropout with the mask shared along the query axis
+  (t5x/examples/t5/layers.py:115-126) restated on the values: with one keep decision per
+  (batch, head, key), sum_k (w[q, k] m[k]) v[k] = sum_k w[q, k] (m[k] v[k]), so scaling the rows
+  of v [batch, keys, heads, dim] gives the same result and the attention kernel needs no mask
+  input. CUDA bf16 only (callers fall back to explicit weights elsewhere)."""
+  if not training or rate == 0.0:
+    return v
+  seed, site = _dropout_seed_and_site(sharded=True)
+  return _DropoutFn.apply(v, float(rate), seed, site, 1, int(v.shape[-1]), 0)
+
+
+# ----------------------------------------------------------------------------
 # Attention
 # ----------------------------------------------------------------------------
 def attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None, bidirectional: bool = True,

@@ -529,3 +529,173 @@ def adafactor_unfactored_apply_(p, g, v, m, p_bf16, scratch, batch, rows, cols, 
       p.data_ptr(), g.data_ptr(), v.data_ptr(), ptr(m), ptr(p_bf16), ld_bf16, bf16_batch_stride,
       scratch.data_ptr(), batch, rows, cols, n_global, lr, eps2, clip_threshold, weight_decay,
       beta1, max_param_scale, flags, stream_ptr()), "adafactor_unfactored_apply")
+
+
+# ----------------------------------------------------------------------------
+# Dropout (in-kernel counter-based mask)
+# ----------------------------------------------------------------------------
+c_ull, c_uint = ctypes.c_ulonglong, ctypes.c_uint
+register_signature("t5x_dropout_bf16", [c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_ll, c_int,
+                                        c_int, c_ull, c_uint, c_float, c_void_p])
+register_signature("t5x_dropout_keep_host", [c_ull, c_uint, c_ull, c_float])
+
+
+def dropout_rows(x: torch.Tensor, rate: float, seed: int, stream_id: int, *, group_rows: int,
+                 col_group: int, row_offset: int = 0, out: Optional[torch.Tensor] = None
+                 ) -> torch.Tensor:
+  """out[r, c] = x[r, c] * keep(key) / (1 - rate) for a 2-D bf16 view x [R, C] with
+  key = ((r + row_offset) // group_rows) * ceil(C / col_group) + c // col_group. The mask is a
+  pure function of (seed, stream_id, key), so calling this again on a gradient with the same
+  three numbers applies the mask of the forward pass."""
+  assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1
+  if out is None:
+    out = torch.empty_like(x)
+  assert out.shape == x.shape and out.stride(1) == 1
+  _check(lib().t5x_dropout_bf16(x.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1],
+                                x.stride(0), out.stride(0), row_offset, group_rows, col_group,
+                                seed & ((1 << 64) - 1), stream_id & 0xFFFFFFFF, float(rate),
+                                stream_ptr()), "dropout")
+  return out
+
+
+def dropout_keep_host(seed: int, stream_id: int, key: int, rate: float) -> bool:
+  """The device generator's keep decision for one key, evaluated on the host."""
+  return bool(lib().t5x_dropout_keep_host(seed & ((1 << 64) - 1), stream_id & 0xFFFFFFFF,
+                                          int(key), float(rate)))
+
+
+# ----------------------------------------------------------------------------
+# Beam search step, sampling, top-k / top-p masks
+# ----------------------------------------------------------------------------
+register_signature("t5x_beam_chunks", [c_int])
+register_signature("t5x_beam_step", [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_float,
+                                     c_float] + [c_void_p] * 13)
+register_signature("t5x_sample_tokens", [c_void_p, c_ll, c_int, c_int, c_void_p, c_float, c_int,
+                                         c_void_p, c_float, c_int, c_ull, c_uint, c_void_p,
+                                         c_void_p, c_void_p])
+register_signature("t5x_topk_topp_mask", [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int,
+                                          c_void_p, c_float, c_float, c_void_p])
+
+
+class BeamStepScratch:
+  """Device scratch of `beam_step` for a fixed (batch, beams, vocab)."""
+
+  def __init__(self, batch: int, beams: int, vocab: int, device):
+    s = int(lib().t5x_beam_chunks(vocab))
+    rows = batch * beams
+    self.f = torch.empty(rows * s * (2 + 2 * beams), dtype=torch.float32, device=device)
+    self.i = torch.empty(rows * s * 2 * beams, dtype=torch.int32, device=device)
+    self.flags = torch.zeros(batch, dtype=torch.uint8, device=device)
+    self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def beam_step(logits: torch.Tensor, *, batch: int, beams: int, eos_id: int, alpha: float,
+              min_brevity: float, live_lp, live_seqs, fin_seqs, fin_scores, fin_flags, ancestry,
+              cur, terminated, scratch: BeamStepScratch) -> None:
+  """One beam-search step in place (see csrc/beam.cu): `logits` [batch * beams, V] fp32 are
+  the logits of the tokens at position `cur` (device int32 scalar, advanced by the call)."""
+  assert logits.dtype == torch.float32 and logits.stride(1) == 1
+  assert live_seqs.dtype == torch.int64 and fin_seqs.dtype == torch.int64
+  assert ancestry.dtype == torch.int32 and cur.dtype == torch.int32
+  assert fin_flags.dtype == torch.bool and terminated.dtype == torch.bool
+  for t in (live_lp, live_seqs, fin_seqs, fin_scores, fin_flags, ancestry):
+    assert t.is_contiguous()
+  _check(lib().t5x_beam_step(
+      logits.data_ptr(), logits.stride(0), batch, beams, live_seqs.shape[2], logits.shape[1],
+      eos_id, float(alpha), float(min_brevity), live_lp.data_ptr(), live_seqs.data_ptr(),
+      fin_seqs.data_ptr(), fin_scores.data_ptr(), fin_flags.data_ptr(), ancestry.data_ptr(),
+      cur.data_ptr(), terminated.data_ptr(), scratch.f.data_ptr(), scratch.i.data_ptr(),
+      scratch.flags.data_ptr(), scratch.ticket.data_ptr(), stream_ptr()), "beam_step")
+
+
+def _row_array(v, rows: int, device):
+  """(device pointer or 0, scalar) for a value that is either a Python number or per row."""
+  if isinstance(v, torch.Tensor) and v.dim() > 0:
+    t = v.to(device=device, dtype=torch.float32).reshape(-1).contiguous()
+    assert t.numel() == rows
+    return t, 0.0
+  return None, float(v)
+
+
+def sample_tokens(logits: torch.Tensor, *, temperature, topk: int, topp, rescale_log_probs: bool,
+                  seed: int, stream_id: int):
+  """(tokens int64 [rows], log_probs fp32 [rows]) drawn from logits [rows, V] fp32 with
+  temperature scaling and a top-k or top-p mask (one kernel; csrc/beam.cu)."""
+  assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+  rows, v = logits.shape
+  t_arr, t_s = _row_array(temperature, rows, logits.device)
+  p_arr, p_s = _row_array(topp if topp else 0.0, rows, logits.device)
+  tokens = torch.empty(rows, dtype=torch.int64, device=logits.device)
+  lps = torch.empty(rows, dtype=torch.float32, device=logits.device)
+  _check(lib().t5x_sample_tokens(
+      logits.data_ptr(), logits.stride(0), rows, v, ptr(t_arr), t_s, int(topk or 0), ptr(p_arr),
+      p_s, int(bool(rescale_log_probs)), seed & ((1 << 64) - 1), stream_id & 0xFFFFFFFF,
+      tokens.data_ptr(), lps.data_ptr(), stream_ptr()), "sample_tokens")
+  return tokens, lps
+
+
+def topk_topp_mask(logits: torch.Tensor, topk: int, topp, replace_val: float) -> torch.Tensor:
+  """logits with everything outside the top-k / top-p set replaced by `replace_val`."""
+  x = logits.reshape(-1, logits.shape[-1])
+  x = x if (x.dtype == torch.float32 and x.stride(1) == 1) else x.float().contiguous()
+  out = torch.empty_like(x)
+  p_arr, p_s = _row_array(topp if topp is not None else 0.0, x.shape[0], x.device)
+  _check(lib().t5x_topk_topp_mask(x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0),
+                                  x.shape[0], x.shape[1], int(topk or 0), ptr(p_arr), p_s,
+                                  float(replace_val), stream_ptr()), "topk_topp_mask")
+  return out.view(logits.shape)
+
+
+# ----------------------------------------------------------------------------
+# Mixture-of-experts router
+# ----------------------------------------------------------------------------
+register_signature("t5x_moe_router_parts", [c_int])
+register_signature("t5x_moe_router_fwd", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int,
+                                          c_int] + [c_void_p] * 9)
+register_signature("t5x_moe_router_bwd", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int,
+                                          c_int] + [c_void_p] * 9 + [c_ll, c_void_p, c_void_p])
+
+ROUTER_MAX_EXPERTS, ROUTER_MAX_CHOICES = 64, 4
+
+
+def moe_router_fwd(x: torch.Tensor, w: torch.Tensor, k: int, capacity: int):
+  """x [T, d] bf16, w [d, E] fp32 -> dict of probs [T, E], lse [T], index [T, k] (int32),
+  gate [T, k] (zero for choices that lost their slot), flat_slot [T, k] (int32, -1 = dropped),
+  stats [E, 4], metrics [8] (auxiliary_loss, router_z_loss, fraction_tokens_left_behind,
+  expert_usage, router_confidence, tokens dispatched)."""
+  assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+  assert w.dtype == torch.float32 and w.is_contiguous()
+  t, d = x.shape
+  e = w.shape[1]
+  dev = x.device
+  parts = int(lib().t5x_moe_router_parts(t))
+  f32, i32 = dict(dtype=torch.float32, device=dev), dict(dtype=torch.int32, device=dev)
+  out = dict(probs=torch.empty(t, e, **f32), lse=torch.empty(t, **f32),
+             index=torch.empty(t, k, **i32), gate=torch.empty(t, k, **f32),
+             flat_slot=torch.empty(t, k, **i32), stats=torch.empty(e, 4, **f32),
+             metrics=torch.zeros(8, **f32))
+  part = torch.empty(parts, 1 + e, **f32)
+  _check(lib().t5x_moe_router_fwd(
+      x.data_ptr(), x.stride(0), w.data_ptr(), t, d, e, k, capacity, out["probs"].data_ptr(),
+      out["lse"].data_ptr(), out["index"].data_ptr(), out["gate"].data_ptr(),
+      out["flat_slot"].data_ptr(), out["stats"].data_ptr(), out["metrics"].data_ptr(),
+      part.data_ptr(), stream_ptr()), "moe_router_fwd")
+  return out
+
+
+def moe_router_bwd(x, w, k: int, capacity: int, fwd: dict, dgate: torch.Tensor,
+                   coef: torch.Tensor, need_dx: bool = True):
+  """(dx [T, d] bf16 or None, dw [d, E] fp32) from the gate gradients [T, k] and
+  coef = [d loss / d auxiliary_loss, d loss / d router_z_loss] (device fp32)."""
+  t, d = x.shape
+  e = w.shape[1]
+  dlogits = torch.empty(t, e, dtype=torch.float32, device=x.device)
+  dx = torch.empty(t, d, dtype=torch.bfloat16, device=x.device) if need_dx else None
+  dw = torch.empty(d, e, dtype=torch.float32, device=x.device)
+  dgate = dgate.float().contiguous()
+  _check(lib().t5x_moe_router_bwd(
+      x.data_ptr(), x.stride(0), w.data_ptr(), t, d, e, k, capacity, fwd["probs"].data_ptr(),
+      fwd["lse"].data_ptr(), fwd["index"].data_ptr(), fwd["flat_slot"].data_ptr(),
+      dgate.data_ptr(), fwd["stats"].data_ptr(), coef.data_ptr(), dlogits.data_ptr(), ptr(dx),
+      d, dw.data_ptr(), stream_ptr()), "moe_router_bwd")
+  return dx, dw

@@ -150,10 +150,38 @@ _DROPOUT_GENERATORS: dict = {}
 
 
 def set_dropout_seed(seed: Optional[int]) -> None:
-  """Seeds the generators used by `dropout` (one per device); None returns to global RNG."""
+  """Seeds the generators used by `dropout` (one per device); None returns to global RNG.
+  Also restarts the numbering of dropout sites used by the in-kernel masks."""
   _DROPOUT_GENERATORS.clear()
+  _DROPOUT_SITE[0] = 0
   if seed is not None:
     _DROPOUT_GENERATORS["seed"] = int(seed)
+
+
+_DROPOUT_SITE = [0]
+
+
+def dropout_seed() -> Optional[int]:
+  """The seed set by `set_dropout_seed`, or None."""
+  return _DROPOUT_GENERATORS.get("seed")
+
+
+def next_dropout_site() -> int:
+  """A number that is different for every dropout call since the last `set_dropout_seed`:
+  together with the seed it names the mask of that call (the in-kernel generator is keyed by
+  (seed, site, element))."""
+  _DROPOUT_SITE[0] += 1
+  return _DROPOUT_SITE[0]
+
+
+def dropout_site_state() -> int:
+  return _DROPOUT_SITE[0]
+
+
+def set_dropout_site_state(n: int) -> None:
+  """Restores the site counter (recomputation of a checkpointed block must draw the masks of
+  its first pass)."""
+  _DROPOUT_SITE[0] = int(n)
 
 
 def _dropout_generator(device) -> Optional[torch.Generator]:
