@@ -1,0 +1,302 @@
+"""Same-box comparator: the benchmark's train step written as plain PyTorch.
+
+`bench.py --impl library` runs T5.1.1 (same architecture, batch, sequence lengths, optimizer and
+microbatching as the headline benchmark) with library kernels only: cuBLAS through
+`torch.matmul` under bf16 autocast, `scaled_dot_product_attention` with the relative-position
+bias and padding mask as an additive mask, eager elementwise ops, an Adafactor written with
+tensor ops, and NCCL `all_reduce` for the gradients when there is more than one GPU. Nothing of
+the `t5x_b200` package is imported: this is the "PyTorch + cuBLAS + NCCL" baseline the fused
+kernels are measured against, and the stand-in for the reference's own JAX build, which cannot
+run on this box.
+
+The math follows the reference model definition (t5x/examples/t5/network.py,
+t5x/examples/t5/layers.py: pre-norm blocks, RMS norm without bias, gated-GELU MLP, bucketed
+relative-position bias shared per stack, no 1/sqrt(d) scaling, untied logits) and
+t5x/adafactor.py (factored second moments, update clipping, parameter-scaled learning rate).
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+
+def _bucket(rel, bidirectional, num_buckets=32, max_distance=128):
+  ret = torch.zeros_like(rel)
+  n = -rel
+  if bidirectional:
+    num_buckets //= 2
+    ret = ret + (n < 0).long() * num_buckets
+    n = n.abs()
+  else:
+    n = n.clamp(min=0)
+  max_exact = num_buckets // 2
+  large = max_exact + (torch.log(n.float() / max_exact + 1e-7) /
+                       math.log(max_distance / max_exact) * (num_buckets - max_exact)).long()
+  large = large.clamp(max=num_buckets - 1)
+  return ret + torch.where(n < max_exact, n, large)
+
+
+def _relpos_bias(table, lq, lk, bidirectional):
+  """[1, H, lq, lk] from the [H, buckets] table."""
+  dev = table.device
+  rel = torch.arange(lk, device=dev)[None, :] - torch.arange(lq, device=dev)[:, None]
+  return table[:, _bucket(rel, bidirectional)][None]
+
+
+def _rmsnorm(x, scale):
+  xf = x.float()
+  return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * scale).to(torch.bfloat16)
+
+
+class LibraryT5(torch.nn.Module):
+
+  def __init__(self, vocab, d, heads, layers, head_dim, ff, device):
+    super().__init__()
+    self.h, self.dk, self.layers = heads, head_dim, layers
+    inner = heads * head_dim
+
+    def w(*shape, std):
+      return torch.nn.Parameter(torch.randn(*shape, device=device) * std)
+
+    self.emb = w(vocab, d, std=1.0)
+    self.logits = w(d, vocab, std=d ** -0.5)
+    self.enc_rel, self.dec_rel = w(heads, 32, std=0.1), w(heads, 32, std=0.1)
+    self.enc_final = torch.nn.Parameter(torch.ones(d, device=device))
+    self.dec_final = torch.nn.Parameter(torch.ones(d, device=device))
+
+    def attn():
+      return torch.nn.ParameterDict(dict(
+          q=w(d, inner, std=(d * head_dim) ** -0.5), k=w(d, inner, std=d ** -0.5),
+          v=w(d, inner, std=d ** -0.5), o=w(inner, d, std=inner ** -0.5)))
+
+    def mlp():
+      return torch.nn.ParameterDict(dict(wi0=w(d, ff, std=d ** -0.5), wi1=w(d, ff, std=d ** -0.5),
+                                         wo=w(ff, d, std=ff ** -0.5)))
+
+    def ln():
+      return torch.nn.Parameter(torch.ones(d, device=device))
+
+    self.enc = torch.nn.ModuleList([torch.nn.ModuleDict(dict(
+        attn=attn(), mlp=mlp(), ln=torch.nn.ParameterDict(dict(a=ln(), m=ln()))))
+        for _ in range(layers)])
+    self.dec = torch.nn.ModuleList([torch.nn.ModuleDict(dict(
+        attn=attn(), cross=attn(), mlp=mlp(),
+        ln=torch.nn.ParameterDict(dict(a=ln(), c=ln(), m=ln())))) for _ in range(layers)])
+
+  def _attend(self, p, xq, xkv, mask):
+    b, lq, _ = xq.shape
+    lk = xkv.shape[1]
+    q = (xq @ p["q"]).view(b, lq, self.h, self.dk).transpose(1, 2)
+    k = (xkv @ p["k"]).view(b, lk, self.h, self.dk).transpose(1, 2)
+    v = (xkv @ p["v"]).view(b, lk, self.h, self.dk).transpose(1, 2)
+    o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, scale=1.0)
+    return o.transpose(1, 2).reshape(b, lq, self.h * self.dk) @ p["o"]
+
+  @staticmethod
+  def _mlp(p, x):
+    return (F.gelu(x @ p["wi0"], approximate="tanh") * (x @ p["wi1"])) @ p["wo"]
+
+  def forward(self, enc_tokens, dec_in, dec_targets, weights, z_loss=1e-4):
+    neg = -1e10
+    le, ld = enc_tokens.shape[1], dec_in.shape[1]
+    enc_pad = (enc_tokens > 0)[:, None, None, :]
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+      enc_mask = (_relpos_bias(self.enc_rel, le, le, True) +
+                  torch.where(enc_pad, 0.0, neg)).to(torch.bfloat16)
+      x = self.emb[enc_tokens].to(torch.bfloat16)
+      for ly in self.enc:
+        h = _rmsnorm(x, ly["ln"]["a"])
+        x = x + self._attend(ly["attn"], h, h, enc_mask)
+        x = x + self._mlp(ly["mlp"], _rmsnorm(x, ly["ln"]["m"]))
+      encoded = _rmsnorm(x, self.enc_final)
+      causal = torch.ones(ld, ld, dtype=torch.bool, device=x.device).tril()[None, None]
+      dec_pad = (dec_targets > 0)[:, None, None, :]
+      self_mask = (_relpos_bias(self.dec_rel, ld, ld, False) +
+                   torch.where(causal & dec_pad, 0.0, neg)).to(torch.bfloat16)
+      cross_mask = torch.where(enc_pad, 0.0, neg).to(torch.bfloat16).expand(-1, -1, ld, -1)
+      y = self.emb[dec_in].to(torch.bfloat16)
+      for ly in self.dec:
+        h = _rmsnorm(y, ly["ln"]["a"])
+        y = y + self._attend(ly["attn"], h, h, self_mask)
+        y = y + self._attend(ly["cross"], _rmsnorm(y, ly["ln"]["c"]), encoded, cross_mask)
+        y = y + self._mlp(ly["mlp"], _rmsnorm(y, ly["ln"]["m"]))
+      y = _rmsnorm(y, self.dec_final)
+      logits = (y @ self.logits).float()
+    lse = torch.logsumexp(logits, -1)
+    tgt = logits.gather(-1, dec_targets[..., None]).squeeze(-1)
+    return ((lse - tgt + z_loss * lse * lse) * weights).sum()
+
+
+class LibraryAdafactor:
+  """Factored Adafactor with tensor ops (t5x/adafactor.py:464-578; decay 0.8 exponent schedule,
+  update clipping 1.0, learning rate times parameter RMS)."""
+
+  def __init__(self, params, decay_rate=0.8, eps1=1e-30, eps2=1e-3, clip=1.0):
+    self.params = list(params)
+    self.decay_rate, self.eps1, self.eps2, self.clip = decay_rate, eps1, eps2, clip
+    self.state = []
+    for p in self.params:
+      if p.dim() == 2 and min(p.shape) >= 128:
+        self.state.append((torch.zeros(p.shape[0], device=p.device),
+                           torch.zeros(p.shape[1], device=p.device)))
+      else:
+        self.state.append((torch.zeros_like(p),))
+    self.step_no = 0
+
+  @torch.no_grad()
+  def step(self, lr):
+    t = self.step_no + 1.0
+    beta2 = 1.0 - t ** (-self.decay_rate)
+    for p, st in zip(self.params, self.state):
+      g = p.grad
+      g2 = g * g + self.eps1
+      if len(st) == 2:
+        vr, vc = st
+        vr.mul_(beta2).add_(g2.mean(1), alpha=1 - beta2)
+        vc.mul_(beta2).add_(g2.mean(0), alpha=1 - beta2)
+        u = g * torch.rsqrt(vr / vr.mean())[:, None] * torch.rsqrt(vc)[None, :]
+      else:
+        st[0].mul_(beta2).add_(g2, alpha=1 - beta2)
+        u = g * torch.rsqrt(st[0])
+      u = u / torch.clamp(u.pow(2).mean().sqrt() / self.clip, min=1.0)
+      scale = torch.clamp(p.pow(2).mean().sqrt(), min=self.eps2)
+      p.sub_(u * (lr * scale))
+      p.grad = None
+    self.step_no += 1
+
+
+def _span_corruption_batch(rng, batch, le, ld, vocab=32128):
+  """Synthetic span-corruption tokens: uniform ids in [3, 32000), about 15 % noise in spans of
+  mean length 3 replaced by descending sentinels, EOS = 1, padding = 0."""
+  import numpy as np
+  enc = np.zeros((batch, le), np.int64)
+  tgt = np.zeros((batch, ld), np.int64)
+  for b in range(batch):
+    raw = rng.integers(3, 32000, size=le + 60)
+    inp, out, sentinel, i = [], [], 32099, 0
+    while i < len(raw) and len(inp) < le - 1:
+      if rng.random() < 0.05:
+        span = max(1, int(rng.poisson(3)))
+        inp.append(sentinel)
+        out.append(sentinel)
+        out.extend(raw[i:i + span].tolist())
+        sentinel -= 1
+        i += span
+      else:
+        inp.append(int(raw[i]))
+        i += 1
+    inp, out = inp[:le - 1] + [1], out[:ld - 1] + [1]
+    enc[b, :len(inp)] = inp
+    tgt[b, :len(out)] = out
+  dec_in = np.concatenate([np.zeros((batch, 1), np.int64), tgt[:, :-1]], 1)
+  return {"enc": enc, "dec_in": dec_in, "tgt": tgt, "w": (tgt > 0).astype("float32")}
+
+
+def run(args, ClockSampler, model_sizes, default_microbatches, baseline_tok_s_per_gpu) -> None:
+  import numpy as np
+  os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  rank = int(os.environ.get("RANK", "0"))
+  local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+  torch.cuda.set_device(local_rank)
+  dev = torch.device("cuda", local_rank)
+  if world > 1:
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl")
+  if args.model not in model_sizes:
+    raise SystemExit("--impl library covers the dense T5.1.1 sizes")
+  d, heads, layers, head_dim, ff = model_sizes[args.model]
+  torch.manual_seed(1234)
+  model = LibraryT5(32128, d, heads, layers, head_dim, ff, dev)
+  opt = LibraryAdafactor(model.parameters())
+  n_params = sum(p.numel() for p in model.parameters())
+  per_rank = args.batch // world
+  # half the microbatch of the headline run: autograd keeps fp32 gradients, bf16 weight casts
+  # and unfused activations alive, which needs the room
+  n_micro = args.microbatches or min(per_rank, 2 * default_microbatches(args.model, world))
+  rng = np.random.default_rng(100 + rank)
+  host = []
+  for _ in range(4):
+    b = _span_corruption_batch(rng, per_rank, args.inputs_length, args.targets_length)
+    host.append({k: torch.from_numpy(v).pin_memory() for k, v in b.items()})
+  resident = [{k: v.to(dev) for k, v in b.items()} for b in host]
+  tokens_per_step = args.batch * (args.inputs_length + args.targets_length)
+
+  def step(batch, i):
+    m = per_rank // n_micro
+    total = torch.zeros((), device=dev)
+    for j in range(n_micro):
+      sl = slice(j * m, (j + 1) * m)
+      loss = model(batch["enc"][sl], batch["dec_in"][sl], batch["tgt"][sl], batch["w"][sl])
+      loss.backward()
+      total += loss.detach()
+    if world > 1:
+      for p in model.parameters():
+        dist.all_reduce(p.grad)
+      dist.all_reduce(total)
+    opt.step(1.0 / math.sqrt(max(i, 10000)))
+    return total
+
+  def sync():
+    if world > 1:
+      dist.barrier()
+    torch.cuda.synchronize()
+
+  def timed(batches, copy):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    last = None
+    for i in range(args.steps):
+      b = batches[i % 4]
+      if copy:
+        b = {k: v.to(dev, non_blocking=True) for k, v in b.items()}
+      last = step(b, i)
+      if copy:
+        last = float(last)  # device -> host read of the step's loss
+    e1.record()
+    sync()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0]) / args.steps, float(last)
+
+  for i in range(args.warmup):
+    step(resident[i % 4], i)
+  sampler = ClockSampler(local_rank)
+  sampler.start()
+  ms, loss = timed(resident, copy=False)
+  clocks = sampler.stop()
+  e_ms, _ = timed(host, copy=True)
+  value = tokens_per_step / (ms / 1e3)
+  if rank == 0:
+    print(json.dumps({
+        "metric": f"T5.1.1-{args.model.upper()} train tokens/s", "value": value,
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / (baseline_tok_s_per_gpu * world) if args.model == "xxl" else None,
+        "dtype": "bf16", "data": "synthetic span-corruption tokens, random-init weights",
+        "impl": "library",
+        "config": {"model": f"t5.1.1-{args.model}", "params": n_params,
+                   "global_batch": args.batch,
+                   "seq_len": args.inputs_length + args.targets_length,
+                   "parallelism": f"data{world} x model1, gradients all-reduced with NCCL",
+                   "optimizer": "adafactor (tensor ops)", "num_microbatches": n_micro,
+                   "kernels": "cuBLAS via torch.matmul under bf16 autocast, "
+                              "scaled_dot_product_attention with an additive bias, eager "
+                              "elementwise ops; none of this repository's kernels",
+                   "l2": "no explicit flush: every step streams tens of GB"},
+        "clocks": clocks,
+        "e2e": {"value": tokens_per_step / (e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e_ms,
+                "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in host[0].values()),
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": 0, "final_loss": loss,
+        "peak_memory_gb": torch.cuda.max_memory_allocated() / 2 ** 30}))
+  if world > 1:
+    dist.barrier()
+    dist.destroy_process_group()

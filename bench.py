@@ -1,15 +1,29 @@
-"""Headline benchmark: T5.1.1-XXL training tokens/s (synthetic span corruption, bf16, Adafactor).
+"""Headline benchmark: T5.1.1-XXL training tokens/s (synthetic span corruption, bf16, Adafactor),
+with the XL beam-decode tokens/s as a second record in the same JSON line.
 
   python bench.py --gpus N --steps K --warmup W            (N=1)
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
       --master-port P bench.py --gpus N --steps K --warmup W
 
-One process per GPU; the mesh is data=1 x model=N (tensor parallel over heads / mlp / vocab),
-global batch 128, inputs 512 / targets 114, as the named configuration prescribes. Prints one
-JSON line on rank 0. `value` is device-timed (CUDA events, max over ranks) over K full train
-steps with device-resident batches; `e2e` repeats the measurement through the public Trainer
-API with a pinned-host -> device copy of every batch and a device -> host read of the step's
-metrics inside the timed region. `--impl reference` reports why the reference cannot run here.
+One process per GPU, global batch 128, inputs 512 / targets 114. Rank 0 prints one JSON line:
+
+  value / e2e    the train step on the default layout: data parallel over the N GPUs with the
+                 optimizer sharded over the replicas (mesh data=N x model=1). `value` is
+                 device-timed (CUDA events, max over ranks) over K steps with device-resident
+                 batches; `e2e` repeats it through the public Trainer API with a pinned-host ->
+                 device copy of every batch and a device -> host read of the step's metrics
+                 inside the timed region.
+  named_mesh     (N > 1) the same step on the mesh the named configuration prescribes,
+                 data=1 x model=N: tensor parallel over heads / mlp / vocab with the all-gather
+                 and reduce-scatter inside the GEMM kernels (3 warm-up + 5..8 timed steps).
+  selfcheck      (N > 1) errors of the fused multi-GPU kernels against library collectives,
+                 measured on this box right before the timed regions; the run fails if one
+                 exceeds its tolerance.
+  decode         T5.1.1-XL beam search (beam 4, batch 64, 512 encoder tokens, 128 steps).
+
+`--impl reference` reports why the reference cannot run here; `--impl library` runs the same
+train step as plain PyTorch (cuBLAS matmuls, library attention, NCCL all-reduce, none of this
+repository's kernels): the same-box comparator.
 """
 from __future__ import annotations
 
@@ -117,69 +131,61 @@ def default_microbatches(model: str, n_gpus: int) -> int:
   return 1
 
 
-def main() -> None:
-  ap = argparse.ArgumentParser()
-  ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=3)
-  ap.add_argument("--warmup", type=int, default=3)
-  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-  ap.add_argument("--model", default="xxl", choices=sorted(MODEL_SIZES) + ["switch-base"],
-                  help="a T5.1.1 size, or switch-base: T5.1.1-Base with every other FFN replaced "
-                       "by 8 top-1 experts, expert-parallel over all ranks")
-  ap.add_argument("--batch", type=int, default=128)
-  ap.add_argument("--inputs-length", type=int, default=512)
-  ap.add_argument("--targets-length", type=int, default=114)
-  ap.add_argument("--microbatches", type=int, default=0)
-  ap.add_argument("--skip-e2e", action="store_true")
-  ap.add_argument("--mode", default="train", choices=["train", "decode"],
-                  help="train: T5.1.1-XXL train step (default); decode: T5.1.1-XL beam decode")
-  ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
-                  help="dp: data parallel with the optimizer sharded over replicas (gradient "
-                       "reduction and weight broadcast fused into the Adafactor kernels over "
-                       "NVLink peer memory); tp: tensor parallel over all GPUs")
-  args = ap.parse_args()
-
-  if args.impl == "reference":
-    reference_arm(args)
-    return
-  if args.mode == "decode":
-    import bench_decode
-    bench_decode.run(args, ClockSampler)
-    return
-
-  import numpy as np
+def _sync_all(world: int) -> None:
   import torch
   import torch.distributed as dist
+  if world > 1:
+    dist.barrier()
+  torch.cuda.synchronize()
+
+
+def _max_over_ranks(ms: float, world: int, dev) -> float:
+  import torch
+  import torch.distributed as dist
+  t = torch.tensor([ms], dtype=torch.float64, device=dev)
+  if world > 1:
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+  return float(t[0])
+
+
+def _teardown() -> None:
+  """Drops everything a finished phase left on the device before the next phase builds its
+  own model on another mesh."""
+  import gc
+  import torch
+  from t5x_b200.parallel import tp_fused, zero
+  zero.disable()
+  tp_fused._ARENA = None
+  gc.collect()
+  torch.cuda.empty_cache()
+  torch.cuda.reset_peak_memory_stats()
+
+
+def measure_train(args, parallelism: str, steps: int, warmup: int, with_e2e: bool) -> dict:
+  """Builds the model on the mesh of `parallelism` ("dp": data=N; "tp": model=N), runs
+  `warmup` + `steps` train steps and returns the record of the timed ones."""
+  import numpy as np
+  import torch
 
   from t5x_b200 import adafactor, data, models, train_state as ts_lib, trainer as trainer_lib
   from t5x_b200.data import feature_converters as fc, vocabularies
-  from t5x_b200.data.dataset import PrefetchIterator
+  from t5x_b200.data.dataset import PrefetchIterator, ShardInfo
   from t5x_b200.models.t5 import network
   from t5x_b200.ops import native
   from t5x_b200.parallel import state as pstate
   from t5x_b200.utils import schedules
 
-  # NCCL only carries barriers, the metrics all-reduce and (tensor-parallel runs) two gathers
-  # per step here; the in-switch reduction buys nothing for those, and with it off a rank that
-  # dies cannot raise NVLink faults on its peers' GPUs. An explicit setting wins.
-  os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
   world = int(os.environ.get("WORLD_SIZE", "1"))
-  if world != args.gpus:
-    raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun "
-                     f"--nproc-per-node {args.gpus}")
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-  torch.cuda.set_device(local_rank)
-  pstate.init_distributed("nccl")
   moe = args.model == "switch-base"
-  if moe and (args.parallelism == "tp" or 8 % world):
+  if moe and (parallelism == "tp" or 8 % world):
     raise SystemExit("switch-base runs expert-parallel on 1, 2, 4 or 8 GPUs")
-  st = pstate.setup_mesh(model_size=world if args.parallelism == "tp" else 1,
+  st = pstate.setup_mesh(model_size=world if parallelism == "tp" else 1,
                          expert_size=world if moe else 1)
-  data_shards = 1 if args.parallelism == "tp" else world
+  data_shards = 1 if parallelism == "tp" else world
   if args.batch % data_shards:
     raise SystemExit(f"--batch {args.batch} is not divisible by {data_shards} data shards")
-  dev = st.device
-  rank = st.rank
+  dev, rank = st.device, st.rank
 
   emb, heads, layers, head_dim, mlp = MODEL_SIZES["base" if moe else args.model]
   common = dict(vocab_size=32128, dtype="bfloat16", emb_dim=emb, num_heads=heads,
@@ -208,7 +214,7 @@ def main() -> None:
                                        loss_normalizing_factor=None)
   state = ts_lib.FlaxOptimTrainState.create(opt, model.get_initial_variables(None, None))
   # tensor-parallel ranks all work on the same microbatch: 32 sequences at a time for XXL
-  n_micro = args.microbatches or (default_microbatches(args.model, 2) if args.parallelism == "tp"
+  n_micro = args.microbatches or (default_microbatches(args.model, 2) if parallelism == "tp"
                                   else default_microbatches(args.model, world))
   lr_fn = schedules.create_learning_rate_scheduler("constant * rsqrt_decay", 1.0, 10000)
   if moe:
@@ -220,32 +226,21 @@ def main() -> None:
   n_params = sum(int(np.prod(getattr(p, "global_shape", p.shape))) for p in module.parameters())
 
   # Tensor-parallel ranks all consume the global batch; data-parallel ranks each take a shard.
-  from t5x_b200.data.dataset import ShardInfo
   lengths = {"inputs": args.inputs_length, "targets": args.targets_length}
   ds = data.get_dataset("synthetic_span_corruption", lengths, fc.EncDecFeatureConverter(pack=False),
                         seed=0, batch_size=args.batch // data_shards, num_epochs=None,
                         shard_info=ShardInfo(st.rank % data_shards, data_shards))
 
   def pin(batch):
-    out = {}
-    for k, v in batch.items():
-      t = torch.from_numpy(np.ascontiguousarray(v).astype(np.int64))
-      out[k] = t.pin_memory()
-    return out
+    return {k: torch.from_numpy(np.ascontiguousarray(v).astype(np.int64)).pin_memory()
+            for k, v in batch.items()}
 
   host_iter = PrefetchIterator(iter(ds), depth=4, transform=pin)
-  total_steps = args.warmup + args.steps
-  h2d_bytes = 0
   tokens_per_step = args.batch * (args.inputs_length + args.targets_length)
-
-  def sync_all():
-    if world > 1:
-      dist.barrier()
-    torch.cuda.synchronize()
 
   # ---- device-timed region: batches already resident on the device -----------------------
   resident = []
-  for _ in range(min(4, max(1, total_steps))):
+  for _ in range(min(4, max(1, warmup + steps))):
     hb = next(host_iter)
     resident.append({k: v.to(dev, non_blocking=True) for k, v in hb.items()})
   torch.cuda.synchronize()
@@ -258,94 +253,187 @@ def main() -> None:
 
   rit = resident_iter()
   step_no = 0
-  for _ in range(args.warmup):
+  for _ in range(warmup):
     trainer.train(rit, 1, start_step=step_no)
     step_no += 1
   native.check_status()
-  sync_all()
+  _sync_all(world)
   sampler = ClockSampler(local_rank)
   sampler.start()
   launches0 = native.launch_count()
-  e0 = torch.cuda.Event(enable_timing=True)
-  e1 = torch.cuda.Event(enable_timing=True)
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   e0.record()
   futures = []
-  for _ in range(args.steps):
+  for _ in range(steps):
     futures.append(trainer.train(rit, 1, start_step=step_no))
     step_no += 1
   e1.record()
-  sync_all()
+  _sync_all(world)
   ms = e0.elapsed_time(e1)
   launches = native.launch_count() - launches0
   clocks = sampler.stop()
   native.check_status()
-  summary = futures[-1].result()
-  last_loss = float(summary["loss"].value)
-  t = torch.tensor([ms], dtype=torch.float64, device=dev)
-  if world > 1:
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-  ms_per_step = float(t[0]) / args.steps
+  last_loss = float(futures[-1].result()["loss"].value)
+  ms_per_step = _max_over_ranks(ms, world, dev) / steps
   value = tokens_per_step / (ms_per_step / 1e3)
 
   # ---- end-to-end through the public API: H2D of inputs and D2H of metrics every step ----
   e2e = None
-  if not args.skip_e2e:
+  if with_e2e:
     def e2e_iter():
       while True:
         yield next(host_iter)
     eit = e2e_iter()
     d2h_bytes = 0
-    for _ in range(1):
-      trainer.train(eit, 1, start_step=step_no).result()
-      step_no += 1
-    sync_all()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
+    trainer.train(eit, 1, start_step=step_no).result()
+    step_no += 1
+    _sync_all(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
       s = trainer.train(eit, 1, start_step=step_no).result()   # waits for and reads the metrics
       step_no += 1
       d2h_bytes = 4 * len(s)
     e1.record()
-    sync_all()
-    ems = e0.elapsed_time(e1)
-    t = torch.tensor([ems], dtype=torch.float64, device=dev)
-    if world > 1:
-      dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e_ms = float(t[0]) / args.steps
+    _sync_all(world)
+    e_ms = _max_over_ranks(e0.elapsed_time(e1), world, dev) / steps
     h2d_bytes = sum(v.numel() * v.element_size() for v in resident[0].values())
     e2e = {"value": tokens_per_step / (e_ms / 1e3), "unit": "tokens/s",
            "ms_per_step": e_ms, "h2d_bytes_per_step": h2d_bytes,
            "d2h_bytes_per_step": d2h_bytes}
   trainer.close()
+  peak_gb = torch.cuda.max_memory_allocated() / 2 ** 30
+  host_iter.close() if hasattr(host_iter, "close") else None
+  del trainer, state, model, module, resident, futures
+  _teardown()
 
+  if moe:
+    layout = f"expert{world} (tokens data-parallel over the same ranks)"
+  elif parallelism == "tp":
+    layout = f"data1 x model{world}" + (
+        " (all-gather / reduce-scatter inside the GEMM kernels, row-sharded residual stream)"
+        if world > 1 else "")
+  else:
+    layout = f"data{world} x model1" + (", optimizer sharded over data" if world > 1 else "")
+  return {
+      "metric": ("Switch-Base-8 train tokens/s" if moe else
+                 f"T5.1.1-{args.model.upper()} train tokens/s"),
+      "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+      "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+      "scaling": "strong",
+      # the published figure is for XXL; other models have none
+      "vs_baseline": (value / (BASELINE_TOKENS_PER_S_PER_GPU * world)
+                      if args.model == "xxl" else None),
+      "dtype": "bf16", "data": "synthetic span-corruption tokens, random-init weights",
+      "impl": "ours",
+      "config": {"model": "switch-base-8" if moe else f"t5.1.1-{args.model}", "params": n_params,
+                 "global_batch": args.batch, "seq_len": args.inputs_length + args.targets_length,
+                 "inputs_length": args.inputs_length, "targets_length": args.targets_length,
+                 "parallelism": layout, "optimizer": "adafactor", "num_microbatches": n_micro,
+                 "l2": "no explicit flush: every step streams the full weights, gradients and "
+                       "activations (tens of GB), far larger than the 126 MB L2",
+                 "baseline_note": "vs_baseline divides by the reference's published A100 figure "
+                                  "scaled per GPU (1346 seq/s * 640 tok / 512 GPUs = 1682.5 tok/s/GPU)"},
+      "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": last_loss,
+      "peak_memory_gb": peak_gb,
+  }
+
+
+def run_selfcheck(world: int) -> dict:
+  """Errors of the fused multi-GPU kernels against library collectives on this box; each
+  family is checked on the mesh it serves. Raises if a tolerance is exceeded."""
+  from t5x_b200.parallel import selfcheck, state as pstate
+  out = {}
+  pstate.setup_mesh(model_size=1)
+  out.update(selfcheck.run(["dp"]))
+  _teardown()
+  pstate.setup_mesh(model_size=world)
+  out.update(selfcheck.run(["tp"]))
+  _teardown()
+  pstate.setup_mesh(model_size=1, expert_size=world)
+  out.update(selfcheck.run(["moe"]))
+  _teardown()
+  out["tolerance"] = 2e-2
+  return out
+
+
+def main() -> None:
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=3)
+  ap.add_argument("--warmup", type=int, default=3)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"])
+  ap.add_argument("--model", default="xxl", choices=sorted(MODEL_SIZES) + ["switch-base"],
+                  help="a T5.1.1 size, or switch-base: T5.1.1-Base with every other FFN replaced "
+                       "by 8 top-1 experts, expert-parallel over all ranks")
+  ap.add_argument("--batch", type=int, default=128)
+  ap.add_argument("--inputs-length", type=int, default=512)
+  ap.add_argument("--targets-length", type=int, default=114)
+  ap.add_argument("--microbatches", type=int, default=0)
+  ap.add_argument("--skip-e2e", action="store_true")
+  ap.add_argument("--skip-extras", action="store_true",
+                  help="only the headline train measurement: no self-check, named-mesh or decode "
+                       "records")
+  ap.add_argument("--mode", default="train", choices=["train", "decode"],
+                  help="train: T5.1.1-XXL train step (default); decode: T5.1.1-XL beam decode")
+  ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                  help="dp: data parallel with the optimizer sharded over replicas (gradient "
+                       "reduction and weight broadcast fused into the Adafactor kernels over "
+                       "NVLink peer memory); tp: tensor parallel over all GPUs")
+  args = ap.parse_args()
+
+  if args.impl == "reference":
+    reference_arm(args)
+    return
+  if args.impl == "library":
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    import library_t5
+    library_t5.run(args, ClockSampler, MODEL_SIZES, default_microbatches,
+                   BASELINE_TOKENS_PER_S_PER_GPU)
+    return
+  if args.mode == "decode":
+    import bench_decode
+    bench_decode.run(args, ClockSampler)
+    return
+
+  import torch
+  import torch.distributed as dist
+
+  from t5x_b200.parallel import state as pstate
+
+  # NCCL only carries barriers, the metrics all-reduce and (tensor-parallel runs) two gathers
+  # per step here; the in-switch reduction buys nothing for those, and with it off a rank that
+  # dies cannot raise NVLink faults on its peers' GPUs. An explicit setting wins.
+  os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  if world != args.gpus:
+    raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun "
+                     f"--nproc-per-node {args.gpus}")
+  torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+  pstate.init_distributed("nccl")
+  rank = int(os.environ.get("RANK", "0"))
+  extras = not args.skip_extras and args.model == "xxl"
+
+  selfcheck = None
+  if extras and world > 1:
+    selfcheck = run_selfcheck(world)
+  out = measure_train(args, args.parallelism, args.steps, args.warmup, not args.skip_e2e)
+  if selfcheck is not None:
+    out["selfcheck"] = selfcheck
+  if extras and world > 1 and args.parallelism == "dp":
+    nm = measure_train(args, "tp", min(max(args.steps, 5), 8), 3, not args.skip_e2e)
+    out["named_mesh"] = {k: nm[k] for k in ("value", "unit", "ms_per_step", "steps", "warmup",
+                                            "e2e", "clocks", "gpu_launches", "final_loss",
+                                            "peak_memory_gb")}
+    out["named_mesh"]["parallelism"] = nm["config"]["parallelism"]
+    out["named_mesh"]["num_microbatches"] = nm["config"]["num_microbatches"]
+  if extras:
+    import bench_decode
+    dec = bench_decode.measure(world, min(max(args.steps, 3), 5), 3, ClockSampler)
+    out["decode"] = {k: dec[k] for k in ("metric", "value", "unit", "ms_per_step", "steps",
+                                         "warmup", "e2e", "clocks", "gpu_launches", "config",
+                                         "peak_memory_gb")}
   if rank == 0:
-    out = {
-        "metric": ("Switch-Base-8 train tokens/s" if moe else
-                   f"T5.1.1-{args.model.upper()} train tokens/s"),
-        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong",
-        # the published figure is for XXL; other models have none
-        "vs_baseline": (value / (BASELINE_TOKENS_PER_S_PER_GPU * world)
-                        if args.model == "xxl" else None),
-        "dtype": "bf16", "data": "synthetic span-corruption tokens, random-init weights",
-        "impl": "ours",
-        "config": {"model": "switch-base-8" if moe else f"t5.1.1-{args.model}", "params": n_params,
-                   "global_batch": args.batch, "seq_len": args.inputs_length + args.targets_length,
-                   "inputs_length": args.inputs_length, "targets_length": args.targets_length,
-                   "parallelism": (f"expert{world} (tokens data-parallel over the same ranks)"
-                                   if moe else f"data1 x model{world}"
-                                   if args.parallelism == "tp" else f"data{world} x model1" +
-                                   (", optimizer sharded over data" if world > 1 else "")),
-                   "optimizer": "adafactor",
-                   "num_microbatches": n_micro,
-                   "l2": "no explicit flush: every step streams the full weights, gradients and "
-                         "activations (tens of GB), far larger than the 126 MB L2",
-                   "baseline_note": "vs_baseline divides by the reference's published A100 figure "
-                                    "scaled per GPU (1346 seq/s * 640 tok / 512 GPUs = 1682.5 tok/s/GPU)"},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": last_loss,
-    }
     print(json.dumps(out))
   if world > 1:
     dist.barrier()

@@ -18,7 +18,19 @@ BATCH, ENC_LEN, DEC_LEN, BEAMS, ALPHA = 64, 512, 128, 4, 0.6
 
 
 def run(args, ClockSampler) -> None:
-  import numpy as np
+  """`bench.py --mode decode`: prints the decode measurement as the JSON line."""
+  import torch.distributed as dist
+  out = measure(args.gpus, args.steps, args.warmup, ClockSampler)
+  if int(os.environ.get("RANK", "0")) == 0:
+    print(json.dumps(out))
+  if dist.is_initialized():
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def measure(gpus: int, steps: int, warmup: int, ClockSampler) -> dict:
+  """Builds the XL model, times `steps` decodes of the batch (device-timed and end to end) and
+  returns the result record (the same on every rank)."""
   import torch
   import torch.distributed as dist
 
@@ -31,8 +43,8 @@ def run(args, ClockSampler) -> None:
 
   os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # NCCL only synchronises ranks here
   world = int(os.environ.get("WORLD_SIZE", "1"))
-  if world != args.gpus:
-    raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+  if world != gpus:
+    raise SystemExit(f"--gpus {gpus} but WORLD_SIZE={world}")
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local_rank)
   pstate.init_distributed("nccl")
@@ -74,7 +86,7 @@ def run(args, ClockSampler) -> None:
     torch.cuda.synchronize()
 
   resident = [h.to(dev) for h in host_inputs]
-  for i in range(args.warmup):
+  for i in range(warmup):
     decode(resident[i % 4])
   native.check_status()
   sync_all()
@@ -85,7 +97,7 @@ def run(args, ClockSampler) -> None:
   replays0 = gd0.replays if gd0 is not None else 0
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   e0.record()
-  for i in range(args.steps):
+  for i in range(steps):
     out, aux = decode(resident[i % 4])
   e1.record()
   sync_all()
@@ -100,7 +112,7 @@ def run(args, ClockSampler) -> None:
   t = torch.tensor([ms], dtype=torch.float64, device=dev)
   if world > 1:
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-  ms_per_decode = float(t[0]) / args.steps
+  ms_per_decode = float(t[0]) / steps
   tokens = BATCH * DEC_LEN
   value = tokens / (ms_per_decode / 1e3)
 
@@ -109,7 +121,7 @@ def run(args, ClockSampler) -> None:
   sync_all()
   e0.record()
   d2h = 0
-  for i in range(args.steps):
+  for i in range(steps):
     enc_dev = host_inputs[i % 4].to(dev, non_blocking=True)
     out, aux = decode(enc_dev)
     out_h, sc_h = out.cpu(), aux["scores"].cpu()
@@ -119,27 +131,26 @@ def run(args, ClockSampler) -> None:
   t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
   if world > 1:
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-  e_ms = float(t[0]) / args.steps
+  e_ms = float(t[0]) / steps
   h2d = host_inputs[0].numel() * host_inputs[0].element_size()
-  if rank == 0:
-    print(json.dumps({
-        "metric": "T5.1.1-XL beam-decode tokens/s", "value": value, "unit": "tokens/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_decode, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16",
-        "data": "uniform random encoder tokens, random-init weights", "impl": "ours",
-        "config": {"model": "t5.1.1-xl", "params": n_params, "global_batch": BATCH,
-                   "seq_len": ENC_LEN, "decode_steps": DEC_LEN, "beam": BEAMS, "alpha": ALPHA,
-                   "parallelism": f"data{world} x model1 (replicated weights, batch split)",
-                   "step": "one timed step = one full decode of the batch (encoder pass, 128 "
-                           "decoder steps with KV cache, beam bookkeeping); tokens = batch x 128",
-                   "l2": "no explicit flush: each decoder step streams 3.3 GB of decoder "
-                         "weights plus the key/value caches, far larger than the 126 MB L2"},
-        "clocks": clocks,
-        "e2e": {"value": tokens / (e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e_ms,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches, "graph_replays_in_timed_region": graph_replays,
-    }))
-  if world > 1:
-    dist.barrier()
-    dist.destroy_process_group()
+  peak_gb = torch.cuda.max_memory_allocated() / 2 ** 30
+  del model, module
+  return {
+      "metric": "T5.1.1-XL beam-decode tokens/s", "value": value, "unit": "tokens/s",
+      "n_gpus": world, "steps": steps, "warmup": warmup,
+      "ms_per_step": ms_per_decode, "higher_is_better": True, "scaling": "strong",
+      "vs_baseline": None, "dtype": "bf16",
+      "data": "uniform random encoder tokens, random-init weights", "impl": "ours",
+      "config": {"model": "t5.1.1-xl", "params": n_params, "global_batch": BATCH,
+                 "seq_len": ENC_LEN, "decode_steps": DEC_LEN, "beam": BEAMS, "alpha": ALPHA,
+                 "parallelism": f"data{world} x model1 (replicated weights, batch split)",
+                 "step": "one timed step = one full decode of the batch (encoder pass, 128 "
+                         "decoder steps with KV cache, beam bookkeeping); tokens = batch x 128",
+                 "l2": "no explicit flush: each decoder step streams 3.3 GB of decoder "
+                       "weights plus the key/value caches, far larger than the 126 MB L2"},
+      "clocks": clocks,
+      "e2e": {"value": tokens / (e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e_ms,
+              "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+      "gpu_launches": launches, "graph_replays_in_timed_region": graph_replays,
+      "peak_memory_gb": peak_gb,
+  }

@@ -18,8 +18,7 @@
 //   router_final_kernel   one CTA: the two losses and the three usage metrics.
 //   router_bwd_kernel     a warp per token: gradient of the logits from the gate gradients and
 //                         the two losses, and of the tokens (dlogits . W^T).
-//   router_dw_kernel      gradient of W: each CTA owns 32 input features and walks all tokens,
-//                         summing in a fixed order.
+//   router_dw_*_kernel    gradient of W: per-tile partial sums, then a fixed-order sum over tiles.
 #include <float.h>
 
 #include "common.cuh"
@@ -296,39 +295,71 @@ __global__ void __launch_bounds__(kRtThreads)
   }
 }
 
-// dw[c, e] = sum_t x[t, c] * dlogits[t, e]; a CTA owns 32 features, 8 token lanes each.
-__global__ void __launch_bounds__(256)
-    router_dw_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
-                     const float* __restrict__ dlogits, const RouterDims dm,
-                     float* __restrict__ dw) {
-  __shared__ float red[8][32];
-  const int cl = threadIdx.x & 31, tl = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + cl;
+// dw[c, e] = sum_t x[t, c] * dlogits[t, e] in two deterministic stages: every CTA reduces a
+// tile of kDwTile tokens into part[tile, c, e] (a thread owns feature columns, the tile's dlogits
+// sit in shared memory), then a second kernel adds the tiles in order.
+constexpr int kDwTile = 512;
+constexpr int kDwThreads = 256;
+constexpr int kDwMaxColsPerThread = 4;  // d <= 1024 per pass over the tile
+
+__global__ void __launch_bounds__(kDwThreads)
+    router_dw_partial_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                             const float* __restrict__ dlogits, const RouterDims dm,
+                             float* __restrict__ part /* [tiles, d, E] */) {
+  __shared__ __align__(16) float dl[kDwTile * 8];
+  const int tile = blockIdx.x;
+  const int t0 = tile * kDwTile, nt = min(kDwTile, dm.T - t0);
+  float* out = part + static_cast<long long>(tile) * dm.d * dm.E;
   for (int e0 = 0; e0 < dm.E; e0 += 8) {
-    float acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    if (c < dm.d) {
-      for (int t = tl; t < dm.T; t += 8) {
-        const float xv = __bfloat162float(x[static_cast<long long>(t) * ldx + c]);
-        const float* dl = dlogits + static_cast<long long>(t) * dm.E + e0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (e0 + j < dm.E) acc[j] = fmaf(xv, dl[j], acc[j]);
-      }
+    const int ne = min(8, dm.E - e0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * 8; i += kDwThreads) {
+      const int t = i >> 3, j = i & 7;
+      dl[i] = j < ne ? dlogits[static_cast<long long>(t0 + t) * dm.E + e0 + j] : 0.f;
     }
+    __syncthreads();
+    for (int c0 = 0; c0 < dm.d; c0 += kDwThreads * kDwMaxColsPerThread) {
+      float acc[kDwMaxColsPerThread][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      red[tl][cl] = acc[j];
-      __syncthreads();
-      if (tl == 0 && c < dm.d && e0 + j < dm.E) {
-        float s = 0.f;
-        for (int q = 0; q < 8; ++q) s += red[q][cl];
-        dw[static_cast<long long>(c) * dm.E + e0 + j] = s;
+      for (int q = 0; q < kDwMaxColsPerThread; ++q)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[q][j] = 0.f;
+      for (int t = 0; t < nt; ++t) {
+        const __nv_bfloat16* row = x + static_cast<long long>(t0 + t) * ldx + c0;
+        const float4 a = *reinterpret_cast<const float4*>(dl + t * 8);
+        const float4 b = *reinterpret_cast<const float4*>(dl + t * 8 + 4);
+#pragma unroll
+        for (int q = 0; q < kDwMaxColsPerThread; ++q) {
+          const int c = c0 + q * kDwThreads + threadIdx.x;
+          const float xv = c < dm.d ? __bfloat162float(row[q * kDwThreads + threadIdx.x]) : 0.f;
+          acc[q][0] = fmaf(xv, a.x, acc[q][0]);
+          acc[q][1] = fmaf(xv, a.y, acc[q][1]);
+          acc[q][2] = fmaf(xv, a.z, acc[q][2]);
+          acc[q][3] = fmaf(xv, a.w, acc[q][3]);
+          acc[q][4] = fmaf(xv, b.x, acc[q][4]);
+          acc[q][5] = fmaf(xv, b.y, acc[q][5]);
+          acc[q][6] = fmaf(xv, b.z, acc[q][6]);
+          acc[q][7] = fmaf(xv, b.w, acc[q][7]);
+        }
       }
-      __syncthreads();
+#pragma unroll
+      for (int q = 0; q < kDwMaxColsPerThread; ++q) {
+        const int c = c0 + q * kDwThreads + threadIdx.x;
+        if (c < dm.d)
+          for (int j = 0; j < ne; ++j) out[static_cast<long long>(c) * dm.E + e0 + j] = acc[q][j];
+      }
     }
   }
+}
+
+__global__ void __launch_bounds__(256)
+    router_dw_reduce_kernel(const float* __restrict__ part, int tiles, int n,
+                            float* __restrict__ dw) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = 0.f;
+  for (int t = 0; t < tiles; ++t) s += part[static_cast<long long>(t) * n + i];
+  dw[i] = s;
 }
 
 static int router_check(const RouterDims& dm, size_t smem) {
@@ -349,6 +380,8 @@ T5X_API int t5x_moe_router_parts(int T) {
   const int cap = 2 * t5x::num_sms();
   return want < cap ? (want < 1 ? 1 : want) : cap;
 }
+
+T5X_API int t5x_moe_router_dw_tiles(int T) { return (T + t5x::kDwTile - 1) / t5x::kDwTile; }
 
 // Forward. x [T, d] bf16 (row stride ldx), w [d, E] fp32. Outputs: probs [T, E], lse [T],
 // index [T, k] int32, gate [T, k] fp32 (zero where the choice lost its slot), flat_slot [T, k]
@@ -395,12 +428,12 @@ T5X_API int t5x_moe_router_fwd(const void* x, long long ldx, const void* w, int 
 
 // Backward. dgate [T, k] (gradient of the returned gates), coef [2] device floats (gradients of
 // the auxiliary and z losses). Writes dlogits [T, E] (scratch), dx [T, d] bf16 (may be null)
-// and dw [d, E] fp32.
+// and dw [d, E] fp32; dw_part: scratch of t5x_moe_router_dw_tiles(T) * d * E floats.
 T5X_API int t5x_moe_router_bwd(const void* x, long long ldx, const void* w, int T, int d, int E,
                                int k, int capacity, const void* probs, const void* lse,
                                const void* index, const void* flat_slot, const void* dgate,
                                const void* stats, const void* coef, void* dlogits, void* dx,
-                               long long lddx, void* dw, void* stream) {
+                               long long lddx, void* dw, void* dw_part, void* stream) {
   using namespace t5x;
   RouterDims dm = {T, d, E, k, capacity};
   const size_t smem = (static_cast<size_t>(E) * d + kRtWarps * E) * 4;
@@ -413,10 +446,13 @@ T5X_API int t5x_moe_router_bwd(const void* x, long long ldx, const void* w, int 
       static_cast<const float*>(dgate), static_cast<const float*>(stats),
       static_cast<const float*>(coef), static_cast<const float*>(w), dm,
       static_cast<float*>(dlogits), static_cast<__nv_bfloat16*>(dx), lddx);
-  router_dw_kernel<<<(d + 31) / 32, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx,
-                                                 static_cast<const float*>(dlogits), dm,
-                                                 static_cast<float*>(dw));
-  count_launches(2);
+  const int tiles = (T + kDwTile - 1) / kDwTile;
+  router_dw_partial_kernel<<<tiles, kDwThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx,
+                                                        static_cast<const float*>(dlogits), dm,
+                                                        static_cast<float*>(dw_part));
+  router_dw_reduce_kernel<<<(d * E + 255) / 256, 256, 0, st>>>(
+      static_cast<const float*>(dw_part), tiles, d * E, static_cast<float*>(dw));
+  count_launches(3);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("router_bwd launch: %s", cudaGetErrorString(e));
   return 0;

@@ -24,8 +24,9 @@ native.register_signature("t5x_moe_gather", [c_void_p, c_void_p, c_void_p, c_voi
 
 
 def enabled(tokens: torch.Tensor) -> bool:
-  st = pstate.get()
-  return (tokens.is_cuda and tokens.dtype == torch.bfloat16 and st.expert_size > 1 and
+  """The scatter / gather kernels serve any expert-parallel size, one rank included (the
+  "peers" are then this GPU's own buffers and no barrier is needed)."""
+  return (tokens.is_cuda and tokens.dtype == torch.bfloat16 and
           tokens.shape[-1] % 8 == 0 and os.environ.get("T5X_B200_MOE_FUSED", "1") != "0")
 
 
@@ -53,37 +54,47 @@ class MoeExchange:
 _EXCHANGES = {}
 
 
-def exchange_for(group) -> MoeExchange:
+def exchange_for(group) -> Optional[MoeExchange]:
+  if group is None:  # one expert-parallel rank: no shared buffers
+    return None
   key = id(group)
   if key not in _EXCHANGES:
     _EXCHANGES[key] = MoeExchange(group)
   return _EXCHANGES[key]
 
 
-def _scatter(rows, scale, flat_slot, buf: comm.SymmetricBuffer, capacity, e_local):
+def _scatter(rows, scale, flat_slot, ptrs, capacity, e_local):
+  """`ptrs`: ctypes array of every expert-parallel rank's buffer address."""
   st = pstate.get()
   t, d = rows.shape
   native._check(native.lib().t5x_moe_scatter(
-      rows.data_ptr(), native.ptr(scale), flat_slot.data_ptr(), buf.ptrs_at(0), t,
+      rows.data_ptr(), native.ptr(scale), flat_slot.data_ptr(), ptrs, t,
       flat_slot.shape[1], capacity, e_local, st.expert_size, st.expert_rank, d,
       native.stream_ptr()), "moe_scatter")
 
 
-def _gather(out, dw, dout, w, flat_slot, buf: comm.SymmetricBuffer, capacity, e_local, t, d):
+def _gather(out, dw, dout, w, flat_slot, ptrs, capacity, e_local, t, d):
   st = pstate.get()
   native._check(native.lib().t5x_moe_gather(
       native.ptr(out), native.ptr(dw), native.ptr(dout), native.ptr(w), flat_slot.data_ptr(),
-      buf.ptrs_at(0), t, flat_slot.shape[1], capacity, e_local, st.expert_size, st.expert_rank,
+      ptrs, t, flat_slot.shape[1], capacity, e_local, st.expert_size, st.expert_rank,
       d, native.stream_ptr()), "moe_gather")
 
 
-def _push(ex: MoeExchange, rows, scale, flat_slot, capacity, e_local, ep, d) -> torch.Tensor:
+def _push(ex: Optional[MoeExchange], rows, scale, flat_slot, capacity, e_local, ep,
+          d) -> torch.Tensor:
   """rows -> owners' inboxes; returns this rank's received [E_local, EP * C, d] (a copy)."""
   n = e_local * ep * capacity * d
+  if ep == 1:
+    # one rank: the "inbox" is a fresh local buffer that is returned as it is
+    buf = torch.zeros(n, dtype=torch.bfloat16, device=rows.device)
+    _scatter(rows.contiguous(), scale, flat_slot, comm._ptr_array([buf.data_ptr()]), capacity,
+             e_local)
+    return buf.view(e_local, capacity, d)
   ex.ensure(n, rows.device)
   ex.inbox.tensor[:n].zero_()       # unused slots must read as zero rows
   ex.barrier(0)                     # everyone has cleared before anyone writes
-  _scatter(rows.contiguous(), scale, flat_slot, ex.inbox, capacity, e_local)
+  _scatter(rows.contiguous(), scale, flat_slot, ex.inbox.ptrs_at(0), capacity, e_local)
   ex.barrier(1)                     # all rows have landed
   return ex.inbox.tensor[:n].view(e_local, ep * capacity, d).clone()
 
@@ -91,10 +102,15 @@ def _push(ex: MoeExchange, rows, scale, flat_slot, capacity, e_local, ep, d) -> 
 def _pull(ex: MoeExchange, local, out, dw, dout, w, flat_slot, capacity, e_local, ep, t, d):
   """Publishes `local` [E_local, EP * C, d] in the outbox and reads this rank's rows back."""
   n = e_local * ep * capacity * d
+  if ep == 1:
+    local = local.contiguous()
+    _gather(out, dw, dout, w, flat_slot, comm._ptr_array([local.data_ptr()]), capacity, e_local,
+            t, d)
+    return
   ex.ensure(n, local.device)
   ex.outbox.tensor[:n].copy_(local.reshape(-1))
   ex.barrier(2)                     # every outbox is published
-  _gather(out, dw, dout, w, flat_slot, ex.outbox, capacity, e_local, t, d)
+  _gather(out, dw, dout, w, flat_slot, ex.outbox.ptrs_at(0), capacity, e_local, t, d)
   ex.barrier(3)                     # nobody still reads an outbox that is about to change
 
 

@@ -653,7 +653,9 @@ register_signature("t5x_moe_router_parts", [c_int])
 register_signature("t5x_moe_router_fwd", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int,
                                           c_int] + [c_void_p] * 9)
 register_signature("t5x_moe_router_bwd", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int,
-                                          c_int] + [c_void_p] * 9 + [c_ll, c_void_p, c_void_p])
+                                          c_int] + [c_void_p] * 9 + [c_ll, c_void_p, c_void_p,
+                                                                     c_void_p])
+register_signature("t5x_moe_router_dw_tiles", [c_int])
 
 ROUTER_MAX_EXPERTS, ROUTER_MAX_CHOICES = 64, 4
 
@@ -693,9 +695,11 @@ def moe_router_bwd(x, w, k: int, capacity: int, fwd: dict, dgate: torch.Tensor,
   dx = torch.empty(t, d, dtype=torch.bfloat16, device=x.device) if need_dx else None
   dw = torch.empty(d, e, dtype=torch.float32, device=x.device)
   dgate = dgate.float().contiguous()
+  dw_part = torch.empty(int(lib().t5x_moe_router_dw_tiles(t)) * d * e, dtype=torch.float32,
+                        device=x.device)
   _check(lib().t5x_moe_router_bwd(
       x.data_ptr(), x.stride(0), w.data_ptr(), t, d, e, k, capacity, fwd["probs"].data_ptr(),
       fwd["lse"].data_ptr(), fwd["index"].data_ptr(), fwd["flat_slot"].data_ptr(),
       dgate.data_ptr(), fwd["stats"].data_ptr(), coef.data_ptr(), dlogits.data_ptr(), ptr(dx),
-      d, dw.data_ptr(), stream_ptr()), "moe_router_bwd")
+      d, dw.data_ptr(), dw_part.data_ptr(), stream_ptr()), "moe_router_bwd")
   return dx, dw
