@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import concurrent.futures
 import dataclasses
+from zlib import error as zlib_error
 import functools
 import logging
 import os
@@ -145,9 +146,15 @@ def _np_dtype(d) -> Optional[np.dtype]:
 
 
 def _sync_global_devices(name: str) -> None:
-  """Barrier over all ranks (multihost_utils.sync_global_devices in the reference)."""
-  if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-    dist.barrier()
+  """Barrier over all ranks between the phases of a save (multihost_utils.sync_global_devices in
+  the reference). It runs on the host with a timeout: a rank that crashed before reaching
+  `name` turns into a `HostSyncError` on the others, not into a save that never returns."""
+  pstate.host_barrier(name)
+
+
+class CheckpointReadError(ValueError):
+  """A checkpoint exists but cannot be read (index file missing or damaged, an array chunk
+  missing or truncated)."""
 
 
 def _broadcast_int_from_rank0(value: int) -> int:
@@ -240,6 +247,17 @@ class Checkpointer:
         checkpoint_utils.remove_dataset_checkpoint(get_checkpoint_dir(self.checkpoints_dir, step),
                                                    _TRAIN_DS_PREFIX)
 
+  def _remove_stale_tmp_dirs(self, keep: Optional[str] = None):
+    """`checkpoint_<step>.tmp-<timestamp>` directories are saves that never reached their final
+    rename (the job died mid-save). Step discovery ignores them; the next save removes them."""
+    import glob
+    import shutil
+    pattern = os.path.join(self.checkpoints_dir, f"{get_checkpoint_prefix()}_*.tmp-*")
+    for path in glob.glob(pattern):
+      if path != keep and os.path.isdir(path):
+        logging.warning("Removing unfinished checkpoint directory %s", path)
+        shutil.rmtree(path, ignore_errors=True)
+
   def _remove_old_checkpoints(self):
     if self.keep:
       steps = self.all_steps()
@@ -306,6 +324,7 @@ class Checkpointer:
       return
     logging.info("Saving checkpoint for step %d to %s", step, tmp_dir)
     if _rank() == 0:
+      self._remove_stale_tmp_dirs(keep=tmp_dir)
       os.makedirs(tmp_dir, exist_ok=True)
     _sync_global_devices(f"checkpointer:make_dir:{tmp_dir}")
     written = self._write_state_to_tensorstore(tmp_dir, train_state, concurrent_gb,
@@ -404,11 +423,16 @@ class Checkpointer:
     else:
       ckpt_dir = os.path.dirname(ckpt_path)
     if not os.path.exists(ckpt_path) or os.path.isdir(ckpt_path):
-      raise ValueError(f"Path is not a valid T5X checkpoint: {ckpt_path}")
+      raise CheckpointReadError(f"Path is not a valid T5X checkpoint: {ckpt_path}")
     logging.info("Restoring from checkpoint: %s", ckpt_path)
-    with open(ckpt_path, "rb") as fp:
-      raw = fp.read()
-    ckpt_contents = msgpack_io.msgpack_restore(raw)
+    try:
+      with open(ckpt_path, "rb") as fp:
+        raw = fp.read()
+      ckpt_contents = msgpack_io.msgpack_restore(raw)
+      if not isinstance(ckpt_contents, Mapping) or "optimizer" not in ckpt_contents:
+        raise ValueError("no 'optimizer' entry")
+    except Exception as e:
+      raise CheckpointReadError(f"Checkpoint index {ckpt_path} is damaged: {e}") from e
     ckpt_state_dict = self._get_optimizer_state_dict(ckpt_contents, state_transformation_fns)
     written_infos = self._parameter_infos
     target_sd = self._train_state.state_dict()
@@ -435,8 +459,16 @@ class Checkpointer:
         restored[name] = flat_fallback[name]
         logging.warning("Initializing param=%s from fallback state", name)
         continue
-      restored[name] = self._read_leaf(name, flat_ckpt[name], tgt, flat_info.get(name), ckpt_dir,
-                                       ckpt_contents.get("version", VERSION), lazy_parameters)
+      try:
+        restored[name] = self._read_leaf(name, flat_ckpt[name], tgt, flat_info.get(name),
+                                         ckpt_dir, ckpt_contents.get("version", VERSION),
+                                         lazy_parameters)
+      except (OSError, EOFError, KeyError, zlib_error, ValueError) as e:
+        if isinstance(e, CheckpointReadError):
+          raise
+        raise CheckpointReadError(
+            f"Array {'/'.join(map(str, name))} of checkpoint {ckpt_dir} cannot be read "
+            f"({type(e).__name__}: {e})") from e
     state_dict = tree_utils.unflatten_dict(restored)
     if self._dataset_iterator is not None and self._dataset_ckpt_name:
       ds_path = os.path.join(ckpt_dir, self._dataset_ckpt_name)

@@ -46,8 +46,9 @@ def get() -> ParallelState:
 
 
 def reset() -> None:
-  global _STATE
+  global _STATE, _CONTROL_GROUP
   _STATE = ParallelState()
+  _CONTROL_GROUP = None
 
 
 def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) -> None:
@@ -61,6 +62,64 @@ def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) ->
   if backend == "nccl":
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
   dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=timeout_s))
+
+
+# ----------------------------------------------------------------------------
+# Host-side control plane
+# ----------------------------------------------------------------------------
+class HostSyncError(RuntimeError):
+  """A host-level barrier or agreement between ranks did not complete in time: some rank
+  crashed, hung or never reached the named point."""
+
+
+_CONTROL_GROUP = None
+
+
+def control_group():
+  """A gloo group over all ranks for host-level synchronisation (checkpoint phases, stop and
+  preemption flags: the role of the coordination service behind
+  jax.experimental.multihost_utils). It involves no GPU work, so a rank that died cannot park
+  the others inside a device collective: its absence shows up as a timeout error on the host.
+  Created on first use; with a gloo default group that group itself serves."""
+  global _CONTROL_GROUP
+  if not dist.is_initialized() or dist.get_world_size() <= 1:
+    return None
+  if _CONTROL_GROUP is None:
+    if dist.get_backend() == "gloo":
+      _CONTROL_GROUP = dist.group.WORLD
+    else:
+      _CONTROL_GROUP = dist.new_group(backend="gloo")
+  return _CONTROL_GROUP
+
+
+def host_sync_timeout_s() -> float:
+  return float(os.environ.get("T5X_B200_HOST_SYNC_TIMEOUT_S", "1800"))
+
+
+def host_barrier(name: str, timeout_s: Optional[float] = None) -> None:
+  """Barrier over all ranks on the host. If a rank does not arrive within `timeout_s`
+  (default `T5X_B200_HOST_SYNC_TIMEOUT_S`, 30 minutes) every waiting rank raises
+  `HostSyncError` naming the barrier instead of waiting forever."""
+  group = control_group()
+  if group is None:
+    return
+  import datetime
+  t = host_sync_timeout_s() if timeout_s is None else float(timeout_s)
+  try:
+    dist.monitored_barrier(group=group, timeout=datetime.timedelta(seconds=t))
+  except RuntimeError as e:
+    raise HostSyncError(f"host barrier '{name}' did not complete within {t:.0f} s on rank "
+                        f"{dist.get_rank()}: {e}") from e
+
+
+def host_any(flag: bool) -> bool:
+  """True on every rank if `flag` is true on any rank (one small gloo all-reduce)."""
+  group = control_group()
+  if group is None:
+    return bool(flag)
+  t = torch.tensor([1 if flag else 0], dtype=torch.int32)
+  dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+  return bool(int(t[0]))
 
 
 def setup_mesh(model_size: int = 1, expert_size: int = 1,

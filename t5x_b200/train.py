@@ -213,7 +213,9 @@ def train(*, model: models.BaseModel, train_dataset_cfg: utils.DatasetConfig,
 
   # Emergency checkpoint on SIGTERM (preemption).
   def _on_sigterm(signum, frame):
-    raise trainer_lib.PreemptionError("received SIGTERM")
+    # only a flag: the trainer raises PreemptionError at the next step boundary, on all ranks
+    logging.warning("SIGTERM received: stopping at the next step boundary.")
+    trainer.request_preemption()
   old_handler = None
   if threading_is_main():
     old_handler = signal.signal(signal.SIGTERM, _on_sigterm)

@@ -502,6 +502,7 @@ class BaseTrainer(abc.ABC):
     self.train_metrics_manager.start_duration_timer(block_on=self.train_state)
     last_log = time.time()
     for step_num in range(start_step, start_step + num_steps):
+      self._check_preemption()
       if time.time() - last_log > 10.0:
         logging.info("Training: step %d", step_num)
         last_log = time.time()
@@ -517,6 +518,20 @@ class BaseTrainer(abc.ABC):
     self._replicas_stale = True
     return self.train_metrics_manager.write_metrics_summary(metrics, start_step + num_steps,
                                                             num_steps)
+
+  def request_preemption(self) -> None:
+    """Called from a signal handler: asks the loop to stop at the next step boundary. The
+    handler must not raise by itself: an exception in the middle of a step would leave the
+    parameters half updated (the optimizer kernels work in place)."""
+    self._preemption_requested = True
+
+  def _check_preemption(self) -> None:
+    """Between steps: raises `PreemptionError` on every rank as soon as any rank has been asked
+    to stop, so that all of them write the emergency checkpoint for the same step (the role of
+    `multihost_utils.reached_preemption_sync_point`, t5x/train.py:660-666)."""
+    if pstate.host_any(getattr(self, "_preemption_requested", False)):
+      self._preemption_requested = False
+      raise PreemptionError("stop requested (SIGTERM)")
 
   def _after_step(self) -> None:
     """Between steps: (1) look, without waiting for the GPU, at the device status words.

@@ -110,9 +110,9 @@ def _dist_on() -> bool:
 
 
 def sync_global_devices(name: str) -> None:
-  """Barrier across all ranks (t5x/utils.py:760-769)."""
-  if _dist_on():
-    dist.barrier()
+  """Barrier across all ranks (t5x/utils.py:760-769), on the host and with a timeout: see
+  `parallel.state.host_barrier`."""
+  pstate.host_barrier(name)
 
 
 def broadcast_one_to_all(value, is_source: Optional[bool] = None):
@@ -289,11 +289,40 @@ def restore(checkpoint_manager, paths: Sequence[str], restore_cfg: RestoreCheckp
             fallback_state=None):
   """Restores one train state (or a list for several paths) (t5x/utils.py:469-526)."""
   fns = restore_cfg.state_transformation_fns
+
+  def one(path):
+    # When the newest checkpoint of a run directory is asked for and it turns out to be
+    # unreadable (the job was killed while a later process was still flushing it, a disk
+    # filled up), fall back to the one before it rather than refuse to resume. All ranks take
+    # the decision together: a rank whose shards happened to be intact follows the others.
+    from t5x_b200 import checkpoints
+    candidates = [path]
+    if getattr(restore_cfg, "mode", None) == "latest" and os.path.isdir(path):
+      from t5x_b200 import checkpoints_utils
+      try:
+        parent, step = checkpoints_utils.get_step_from_checkpoint_dir(path)
+        candidates += [checkpoints_utils.get_checkpoint_dir(parent, s)
+                       for s in reversed(checkpoints_utils.all_steps(parent)) if s < step]
+      except ValueError:
+        pass
+    last_error = None
+    for cand in candidates:
+      state, error = None, None
+      try:
+        state = checkpoint_manager.restore(path=cand, fallback_state=fallback_state,
+                                           state_transformation_fns=fns)
+      except checkpoints.CheckpointReadError as e:
+        error = e
+      if not pstate.host_any(error is not None):
+        return state
+      last_error = error or last_error
+      logging.warning("Checkpoint %s is unreadable on some rank (%s); trying the previous one.",
+                      cand, error)
+    raise last_error or checkpoints.CheckpointReadError(f"no readable checkpoint at {path}")
+
   if len(paths) == 1:
-    return checkpoint_manager.restore(path=paths[0], fallback_state=fallback_state,
-                                      state_transformation_fns=fns)
-  return [checkpoint_manager.restore(path=p, fallback_state=fallback_state,
-                                     state_transformation_fns=fns) for p in paths]
+    return one(paths[0])
+  return [one(p) for p in paths]
 
 
 def create_checkpoint_manager_and_restore(train_state_initializer: TrainStateInitializer,
