@@ -144,6 +144,10 @@ __device__ __forceinline__ void bulk_store_wait_read() {
 __device__ __forceinline__ void bulk_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
+// all of this thread's bulk stores except the most recent one are complete
+__device__ __forceinline__ void bulk_store_wait_all_but_last() {
+  asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_all() {
   asm volatile("fence.proxy.async;" ::: "memory");
 }

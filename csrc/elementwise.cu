@@ -669,9 +669,37 @@ T5X_API int t5x_f32_to_bf16_residual(const void* src, const void* residual, void
 // dst[i] = bf16(sum over s of slots[s * n + i] (+ residual[i])) with fp32 accumulation: the
 // owner's side of the tensor-parallel reduce-scatter (`slots` is its inbox, one slot per rank).
 namespace t5x {
+struct SlotSumWait {
+  const unsigned int* sig;  // this rank's "scattered" words, one per rank; null: no wait
+  int world, rank;
+  unsigned int epoch;
+  int* status;
+};
+constexpr int kSlotSumSpinLimit = 1 << 24;  // polls >= 64 ns apart: 1-3 s
+
 __global__ void __launch_bounds__(256)
     slot_sum_bf16_kernel(const __nv_bfloat16* __restrict__ slots, int num_slots, long long n8,
-                         const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ dst) {
+                         const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ dst,
+                         const SlotSumWait w) {
+  if (w.sig != nullptr) {
+    // every peer's reduce-scatter GEMM has performed all its stores into this rank's inbox
+    if (threadIdx.x < w.world && threadIdx.x != w.rank) {
+      const unsigned int* word = w.sig + threadIdx.x;
+      bool here = false;
+      for (int it = 0; it < kSlotSumSpinLimit; ++it) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+        if (static_cast<int>(v - w.epoch) >= 0) {
+          here = true;
+          break;
+        }
+        __nanosleep(64);
+      }
+      if (!here) report_status(w.status, kStatusTimeoutPeerFlag, 41, threadIdx.x,
+                               static_cast<int>(w.epoch));
+    }
+    __syncthreads();
+  }
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
        i += stride) {
@@ -719,9 +747,37 @@ T5X_API int t5x_slot_sum_bf16(const void* slots, int num_slots, long long n, con
   if (blocks > cap) blocks = cap;
   slot_sum_bf16_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(slots), num_slots, n8,
-      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(dst));
+      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(dst),
+      SlotSumWait{nullptr, 0, 0, 0u, nullptr});
   count_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("slot_sum_bf16: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// The same sum, preceded (inside the kernel) by a bounded wait until every other rank's
+// reduce-scatter GEMM of epoch `epoch` has raised its "scattered" signal: `sig` points at this
+// rank's `world` signal words of that kind. Takes the place of a barrier kernel between the
+// GEMM and the sum.
+T5X_API int t5x_slot_sum_wait_bf16(const void* slots, int num_slots, long long n,
+                                   const void* residual, void* dst, const void* sig, int world,
+                                   int rank, unsigned int epoch, void* stream) {
+  using namespace t5x;
+  if (n <= 0) return 0;
+  if (n % 8 || num_slots < 1) return set_error("slot_sum_wait_bf16: n must be a multiple of 8");
+  if (sig == nullptr || world < 1 || world > 256 || rank < 0 || rank >= world)
+    return set_error("slot_sum_wait_bf16: bad signal arguments");
+  const long long n8 = n / 8;
+  long long blocks = (n8 + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms()) * 8;
+  if (blocks > cap) blocks = cap;
+  slot_sum_bf16_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(slots), num_slots, n8,
+      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(dst),
+      SlotSumWait{static_cast<const unsigned int*>(sig), world, rank, epoch,
+                  device_status_buffer()});
+  count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("slot_sum_wait_bf16: %s", cudaGetErrorString(e));
   return 0;
 }

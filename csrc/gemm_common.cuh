@@ -31,21 +31,55 @@ struct GemmParams {
 
 // Tensor-parallel extensions of the CTA-pair GEMM. The rows of A (all-gather) or of C
 // (reduce-scatter) are split evenly over `world` ranks, `rows_per_rank` consecutive rows each.
+//
+// Ordering between ranks needs no separate barrier kernel. Every rank owns a small array of
+// signal words in memory that all ranks map; word [kind][r] is written only by rank r, with an
+// epoch number that grows by one per call (all ranks make the same calls in the same order).
+//   kTpSigRowsReady  rank r's own rows of the A buffer are in place (written by the kernel that
+//                    precedes the all-gather GEMM on r's stream). Raised by r's all-gather GEMM
+//                    as it starts; awaited by the copy warps before they pull from r.
+//   kTpSigScattered  every store of rank r's reduce-scatter GEMM into the inboxes has been
+//                    performed. Raised by the last CTA of that GEMM; awaited by the kernel that
+//                    sums the inbox slots.
+// Waits compare epochs by signed distance (wrap-safe), are bounded, and report a status.
 enum GemmTpMode : int { kTpNone = 0, kTpAllGather = 1, kTpReduceScatter = 2 };
 constexpr int kTpMaxPeers = 16;
+constexpr int kTpSigRowsReady = 0;
+constexpr int kTpSigScattered = 1;
+constexpr int kTpSigWords = 2 * kTpMaxPeers;
+constexpr int kTpGroupRows = 128;  // rows of A whose arrival is tracked by one counter
 struct GemmTp {
   int world, rank, rows_per_rank;
   // all-gather -> GEMM: A is this rank's [M, K] buffer; block r of it is pulled from
   // a_src[r] (rank r's buffer as mapped here, same layout) by the copy warps while the tensor
-  // cores work on blocks that are already here. flags[r] counts the pieces of block r landed.
+  // cores work on blocks that are already here. flags[r * groups_per_block + g] counts the
+  // pieces landed in row group g (kTpGroupRows rows) of block r; the last CTA to leave the
+  // kernel clears them again.
   const uint8_t* a_src[kTpMaxPeers];
   uint8_t* a_dst;
   long long block_bytes;
+  long long group_bytes;
+  int groups_per_block;
   unsigned int* flags;
   // GEMM -> reduce-scatter: rows of block r are stored to c_dst[r] ([rows_per_rank, ldc] bf16,
   // this rank's slot of rank r's inbox as mapped here) instead of C.
   __nv_bfloat16* c_dst[kTpMaxPeers];
+  // signal words: this rank's own array and the peers' arrays as mapped here; `epoch` is what
+  // this call raises and waits for; `exit_count` counts CTAs that have finished (device word).
+  unsigned int* sig_local;
+  unsigned int* sig_peer[kTpMaxPeers];
+  unsigned int epoch;
+  unsigned int* exit_count;
 };
+
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* addr, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* addr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const float* v, int n_valid,
                                                bool vec_ok) {

@@ -33,16 +33,22 @@ constexpr int kKernelIdGemmPair = 2;
 //  kTpAllGather     A's row blocks live on `world` ranks. A seventh warp per CTA pulls the
 //                   other ranks' blocks into this rank's A buffer with bulk copies staged
 //                   through shared memory (peer memory -> shared -> local memory, never a
-//                   multicast load) and counts landed pieces in flags[r]; the TMA producer
-//                   waits (bounded) for the blocks its tile needs. The row-tile walk starts
-//                   at this rank's own block, so the tensor cores work while NVLink delivers.
+//                   multicast load) and counts landed pieces per group of 128 rows; the TMA
+//                   producer waits (bounded) only for the row groups its tile reads. The
+//                   row-tile walk starts at this rank's own block and follows the order in
+//                   which the copy warps pull, so the tensor cores work while NVLink delivers.
+//                   The kernel raises this rank's "rows ready" signal as it starts and the copy
+//                   warps wait for a peer's signal before they read from it, so no barrier
+//                   kernel is needed in front; the last CTA to leave clears the counters.
 //  kTpReduceScatter the epilogue stores each bf16 row of the partial product into the inbox
 //                   of the rank that owns the row (peer memory over NVLink); the walk starts
-//                   at the next rank's block and ends with this rank's own.
+//                   at the next rank's block and ends with this rank's own. The last CTA to
+//                   leave raises this rank's "scattered" signal on every peer, which the
+//                   kernel that sums the inbox slots waits for.
 constexpr int kTpPiece = 8192;   // bytes per bulk copy
 constexpr int kTpSlots = 3;      // staging slots per CTA
 constexpr int kTpStageBytes = kTpPiece * kTpSlots;
-constexpr int kTpFlagLimit = 1 << 22;  // polls (>= 64 ns apart) before a flag wait gives up
+constexpr int kTpFlagLimit = 1 << 24;  // polls (>= 64 ns apart) before a flag wait gives up: 1-3 s
 
 template <int MODE>
 constexpr int pair_threads() { return MODE == kTpAllGather ? kGemmThreads + 32 : kGemmThreads; }
@@ -122,9 +128,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      uint32_t landed = 0;  // ranks whose block is known to be here
-      const uint32_t pieces_per_block =
-          MODE == kTpAllGather ? static_cast<uint32_t>((tp.block_bytes + kTpPiece - 1) / kTpPiece) : 0;
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
         int b, mt, nt;
         gemm_tile_coords(p, tile, tiles_per_batch, b, mt, nt);
@@ -135,26 +138,37 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
         const int n0 = (EPI == kEpiGatedGelu) ? n_tile : n_tile + static_cast<int>(cta) * (BN / 2);
         const CUtensorMap* tb = (EPI == kEpiGatedGelu && cta == 1) ? &tmB2 : &tmB;
         if (MODE == kTpAllGather && m0 < p.M) {
-          // the rows of this CTA's A tile: wait for the blocks of other ranks among them
+          // the rows of this CTA's A tile: wait for the row groups of other ranks among them
+          const int m_end = min(m0 + kBM, p.M);  // exclusive
+          const long long row_bytes = static_cast<long long>(p.K) * 2;
           const int r_lo = m0 / tp.rows_per_rank;
-          const int r_hi = min(m0 + kBM - 1, p.M - 1) / tp.rows_per_rank;
+          const int r_hi = (m_end - 1) / tp.rows_per_rank;
           for (int r = r_lo; r <= r_hi && ok; ++r) {
-            if (r == tp.rank || ((landed >> r) & 1u)) continue;
-            bool here = false;
-            for (int it = 0; it < kTpFlagLimit; ++it) {
-              if (ld_acquire_gpu(&tp.flags[r]) >= pieces_per_block) {
-                here = true;
-                break;
+            if (r == tp.rank) continue;
+            const int b0 = r * tp.rows_per_rank;
+            const long long lo = static_cast<long long>(max(m0, b0) - b0) * row_bytes;
+            const long long hi =
+                static_cast<long long>(min(m_end, b0 + tp.rows_per_rank) - b0) * row_bytes - 1;
+            for (int g = static_cast<int>(lo / tp.group_bytes);
+                 g <= static_cast<int>(hi / tp.group_bytes) && ok; ++g) {
+              const long long gbytes = min(tp.group_bytes, tp.block_bytes - g * tp.group_bytes);
+              const uint32_t need = static_cast<uint32_t>((gbytes + kTpPiece - 1) / kTpPiece);
+              const unsigned int* flag = &tp.flags[r * tp.groups_per_block + g];
+              bool here = false;
+              for (int it = 0; it < kTpFlagLimit; ++it) {
+                if (ld_acquire_gpu(flag) >= need) {
+                  here = true;
+                  break;
+                }
+                if (*abort_flag) break;
+                __nanosleep(64);
               }
-              if (*abort_flag) break;
-              __nanosleep(64);
+              if (!here) {
+                report_status(p.status, kStatusTimeoutPeerFlag, kKernelIdGemmPair, tile, r);
+                *abort_flag = 1;
+                ok = false;
+              }
             }
-            if (!here) {
-              report_status(p.status, kStatusTimeoutPeerFlag, kKernelIdGemmPair, tile, r);
-              *abort_flag = 1;
-              ok = false;
-            }
-            landed |= 1u << r;
           }
           if (!ok) break;
           fence_proxy_async_all();  // the bulk stores that wrote A, before this TMA reads it
@@ -247,24 +261,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
     // an mbarrier) -> this rank's A (bulk store); flags[r] is raised once the stores of a few
     // pieces are complete.
     if (lane == 0 && tp.world > 1) {
+      if (blockIdx.x == 0) {
+        // this rank's own rows were written by the kernel before this one: tell the peers
+        for (int r = 0; r < tp.world; ++r)
+          if (r != tp.rank)
+            st_release_sys_u32(tp.sig_peer[r] + kTpSigRowsReady * kTpMaxPeers + tp.rank, tp.epoch);
+      }
       const long long ppb = (tp.block_bytes + kTpPiece - 1) / kTpPiece;
       const long long total = ppb * (tp.world - 1);
       long long g_issue = blockIdx.x, g_done = blockIdx.x;
       int n_issue = 0, n_done = 0;
-      int pub_rank = -1;
-      uint32_t pub_count = 0;
+      uint32_t ready = 1u << tp.rank;  // peers whose rows are known to be in place
+      int pend_flag = -1;              // counter the stored-but-unpublished pieces belong to
+      uint32_t pend_count = 0;
       bool ok = true;
-      auto publish = [&]() {
-        if (pub_count) {
-          bulk_store_wait_all();
-          fence_proxy_async_all();
-          red_release_gpu_add(&tp.flags[pub_rank], pub_count);
-          pub_count = 0;
-        }
-      };
       while (g_done < total && ok) {
-        while (g_issue < total && n_issue - n_done < kTpSlots) {
+        while (g_issue < total && n_issue - n_done < kTpSlots && ok) {
           const int r = (tp.rank + 1 + static_cast<int>(g_issue / ppb)) % tp.world;
+          if (!((ready >> r) & 1u)) {
+            const unsigned int* sig = tp.sig_local + kTpSigRowsReady * kTpMaxPeers + r;
+            bool here = false;
+            for (int it = 0; it < kTpFlagLimit; ++it) {
+              if (static_cast<int32_t>(ld_acquire_sys_u32(sig) - tp.epoch) >= 0) {
+                here = true;
+                break;
+              }
+              if (*abort_flag) break;
+              __nanosleep(64);
+            }
+            if (!here) {
+              report_status(p.status, kStatusTimeoutPeerFlag, kKernelIdGemmPair, -3, r);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            ready |= 1u << r;
+          }
           const long long off = (g_issue % ppb) * kTpPiece;
           const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long long>(kTpPiece),
                                                            tp.block_bytes - off));
@@ -275,6 +307,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
           ++n_issue;
           g_issue += gridDim.x;
         }
+        if (!ok || n_done == n_issue) break;
         const int r = (tp.rank + 1 + static_cast<int>(g_done / ppb)) % tp.world;
         const long long off = (g_done % ppb) * kTpPiece;
         const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long long>(kTpPiece),
@@ -286,18 +319,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
           ok = false;
           break;
         }
-        if (r != pub_rank) {
-          publish();
-          pub_rank = r;
-        }
         bulk_store(tp.a_dst + r * tp.block_bytes + off, staging + slot * kTpPiece, bytes);
         bulk_store_wait_read();  // the slot may be refilled
-        ++pub_count;
+        const int flag = r * tp.groups_per_block + static_cast<int>(off / tp.group_bytes);
+        if (pend_count && pend_flag != flag) {
+          // pieces of another row group: publish them once all stores but the one just issued
+          // are complete
+          bulk_store_wait_all_but_last();
+          fence_proxy_async_all();
+          red_release_gpu_add(&tp.flags[pend_flag], pend_count);
+          pend_count = 0;
+        }
+        pend_flag = flag;
+        ++pend_count;
         ++n_done;
         g_done += gridDim.x;
-        if (pub_count == 4) publish();
+        if (pend_count == 4) {
+          bulk_store_wait_all();
+          fence_proxy_async_all();
+          red_release_gpu_add(&tp.flags[pend_flag], pend_count);
+          pend_count = 0;
+        }
       }
-      publish();
+      if (pend_count) {
+        bulk_store_wait_all();
+        fence_proxy_async_all();
+        red_release_gpu_add(&tp.flags[pend_flag], pend_count);
+      }
       if (!ok) {
         // loads still in flight target this CTA's shared memory: give them time to land
         for (int it = 0; it < 2000; ++it) __nanosleep(1000);
@@ -334,6 +382,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(drained + acc * 8);
     }
+    if (MODE == kTpReduceScatter) __threadfence_system();  // this thread's inbox stores
   }
 
   // Teardown: neither CTA may leave (or free TMEM) while its partner can still read its
@@ -345,6 +394,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();
+  if (MODE != kTpNone && threadIdx.x == 0 && tp.world > 1) {
+    // The last CTA to get here speaks for the whole kernel: it clears the arrival counters
+    // for the next all-gather, or tells the peers that this rank's scatter is complete.
+    __threadfence_system();
+    const unsigned int arrived = atomicAdd(tp.exit_count, 1u);
+    if (arrived == gridDim.x - 1) {
+      __threadfence_system();
+      if (MODE == kTpAllGather) {
+        const int n = tp.world * tp.groups_per_block;
+        for (int i = 0; i < n; ++i) tp.flags[i] = 0u;
+      } else {
+        for (int r = 0; r < tp.world; ++r)
+          if (r != tp.rank)
+            st_release_sys_u32(tp.sig_peer[r] + kTpSigScattered * kTpMaxPeers + tp.rank, tp.epoch);
+      }
+      *tp.exit_count = 0u;
+      __threadfence();
+    }
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, 512);

@@ -439,43 +439,73 @@ T5X_API int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C,
                         stream, nullptr, 0);
 }
 
+namespace t5x {
+static int tp_signals(GemmTp& tp, void* sig_local, void* const* sig_peers, unsigned int epoch,
+                      void* exit_count, const char* what) {
+  if (sig_local == nullptr || sig_peers == nullptr || exit_count == nullptr)
+    return set_error("%s: signal words are required", what);
+  tp.sig_local = static_cast<unsigned int*>(sig_local);
+  for (int r = 0; r < tp.world; ++r) tp.sig_peer[r] = static_cast<unsigned int*>(sig_peers[r]);
+  tp.epoch = epoch;
+  tp.exit_count = static_cast<unsigned int*>(exit_count);
+  return 0;
+}
+}  // namespace t5x
+
+// Number of arrival counters (uint32, zero before the first call) an all-gather GEMM over
+// `world` ranks with `rows_per_rank` rows each uses.
+T5X_API int t5x_gemm_allgather_flag_words(int world, int rows_per_rank) {
+  return world * ((rows_per_rank + t5x::kTpGroupRows - 1) / t5x::kTpGroupRows);
+}
+
 // All-gather -> GEMM in one kernel. A is this rank's [M, K] bf16 buffer (row-major, lda == K)
 // whose block `rank` (rows_per_rank rows) is already filled; a_peers[r] is rank r's buffer of
 // the same layout as mapped into this process. The kernel pulls the other blocks over NVLink
-// while it multiplies, so A is complete (and reusable) when it returns. `flags`: `world`
-// uint32 in this GPU's memory, cleared here. epilogue 0 (C = A @ B) or 1 (gated GELU).
+// while it multiplies, so A is complete (and reusable) when it returns. No barrier is needed in
+// front of the call: the kernel raises this rank's "rows ready" signal (epoch `epoch`, one
+// more than in the previous call of either tensor-parallel GEMM on this group) and waits for
+// each peer's before it reads from it. `flags`: t5x_gemm_allgather_flag_words counters of this
+// GPU's memory, zero on entry and again on exit. sig_local / sig_peers: 32 uint32 per rank in
+// memory every rank maps (zero at start); exit_count: one zeroed uint32 of this GPU.
+// epilogue 0 (C = A @ B) or 1 (gated GELU). K must be a multiple of 32.
 T5X_API int t5x_gemm_allgather_bf16(void* A, const void* const* a_peers, int world, int rank,
                                     int rows_per_rank, void* flags, const void* B, const void* B2,
                                     void* C, int M, int N, int K, long long ldb, long long ldc,
                                     int b_mn_major, int epilogue, void* H0, void* H1,
-                                    long long ldh, void* stream) {
+                                    long long ldh, void* sig_local, void* const* sig_peers,
+                                    unsigned int epoch, void* exit_count, void* stream) {
   using namespace t5x;
   if (world < 1 || world > kTpMaxPeers || rank < 0 || rank >= world ||
-      static_cast<long long>(rows_per_rank) * world != M || (K % 8))
-    return set_error("gemm_allgather: bad world/rank/rows (%d/%d/%d for M=%d)", world, rank,
-                     rows_per_rank, M);
+      static_cast<long long>(rows_per_rank) * world != M || (K % 32))
+    return set_error("gemm_allgather: bad world/rank/rows (%d/%d/%d for M=%d) or K=%d not a "
+                     "multiple of 32", world, rank, rows_per_rank, M, K);
   GemmTp tp = {};
   tp.world = world;
   tp.rank = rank;
   tp.rows_per_rank = rows_per_rank;
   tp.block_bytes = static_cast<long long>(rows_per_rank) * K * 2;
+  tp.group_bytes = static_cast<long long>(kTpGroupRows) * K * 2;
+  tp.groups_per_block = (rows_per_rank + kTpGroupRows - 1) / kTpGroupRows;
   for (int r = 0; r < world; ++r) tp.a_src[r] = static_cast<const uint8_t*>(a_peers[r]);
   tp.a_dst = static_cast<uint8_t*>(A);
   tp.flags = static_cast<unsigned int*>(flags);
-  cudaMemsetAsync(flags, 0, sizeof(unsigned int) * world, static_cast<cudaStream_t>(stream));
+  if (int rc = tp_signals(tp, sig_local, sig_peers, epoch, exit_count, "gemm_allgather")) return rc;
   return gemm_impl(A, B, B2, C, M, N, K, 1, K, ldb, ldc, 0, 0, 0, 0, b_mn_major, 0, 0, epilogue,
                    nullptr, 0, 0, H0, H1, ldh, 1.f, 0, stream, &tp, kTpAllGather);
 }
 
 // GEMM -> reduce-scatter in one kernel: the bf16 partial product A @ B (+ R) of this rank is
 // stored row block by row block into the owners' inboxes: c_peers[r] is this rank's slot
-// ([rows_per_rank, ldc]) of rank r's inbox as mapped into this process. The owners sum their
-// slots after a barrier. epilogue 0 or 2 (adds the local bf16 [M, N] matrix R first).
+// ([rows_per_rank, ldc]) of rank r's inbox as mapped into this process. When its last store
+// has been performed the kernel raises this rank's "scattered" signal (epoch `epoch`) on every
+// peer; the owners sum their slots with t5x_slot_sum_wait_bf16, which waits for those signals.
+// epilogue 0 or 2 (adds the local bf16 [M, N] matrix R first).
 T5X_API int t5x_gemm_reducescatter_bf16(const void* A, const void* B, void* const* c_peers,
                                         int world, int rank, int rows_per_rank, int M, int N, int K,
                                         long long lda, long long ldb, long long ldc,
                                         int a_mn_major, int b_mn_major, const void* R,
-                                        long long ldr, void* stream) {
+                                        long long ldr, void* sig_local, void* const* sig_peers,
+                                        unsigned int epoch, void* exit_count, void* stream) {
   using namespace t5x;
   if (world < 1 || world > kTpMaxPeers || rank < 0 || rank >= world ||
       static_cast<long long>(rows_per_rank) * world != M || (ldc % 8))
@@ -490,6 +520,8 @@ T5X_API int t5x_gemm_reducescatter_bf16(const void* A, const void* B, void* cons
       return set_error("gemm_reducescatter: inbox pointers must be 16-byte aligned");
     tp.c_dst[r] = static_cast<__nv_bfloat16*>(c_peers[r]);
   }
+  if (int rc = tp_signals(tp, sig_local, sig_peers, epoch, exit_count, "gemm_reducescatter"))
+    return rc;
   return gemm_impl(A, B, nullptr, nullptr, M, N, K, 1, lda, ldb, ldc, 0, 0, 0, a_mn_major,
                    b_mn_major, 0, 0, R ? kEpiResidual : kEpiPlain, R, ldr, 0, nullptr, nullptr, 0,
                    1.f, 0, stream, &tp, kTpReduceScatter);

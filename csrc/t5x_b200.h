@@ -79,25 +79,40 @@ int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C, int M, 
  * The M rows are split evenly over `world` ranks (rows_per_rank each). Peer pointers are the
  * other ranks' buffers as mapped into this process (symmetric memory).
  *
+ * Ordering between ranks is carried by signal words instead of barrier kernels: every rank
+ * owns 32 uint32 (zero at start) that all ranks map (sig_local = this rank's own,
+ * sig_peers[r] = rank r's as mapped here), and every call of either GEMM takes an `epoch` one
+ * larger than the previous call on the group; all ranks make the same calls in the same order.
+ * exit_count: one zeroed uint32 of this GPU's memory shared by both GEMMs.
+ *
  * all-gather -> GEMM: A is this rank's [M, K] buffer with only block `rank` filled; the kernel
- * pulls block r from a_peers[r] (same layout) while it multiplies; `flags`: `world` uint32 of
- * this GPU's memory. A barrier over the ranks must separate the writes of the blocks from
- * this call. epilogue 0 or 1.
+ * announces that, waits for each peer's announcement and pulls block r from a_peers[r] (same
+ * layout) while it multiplies. `flags`: t5x_gemm_allgather_flag_words(world, rows_per_rank)
+ * uint32 of this GPU's memory, zero on entry and on exit. K % 32 == 0. epilogue 0 or 1.
  *
  * GEMM -> reduce-scatter: the bf16 partial product (+ R) is stored row block by row block to
- * c_peers[r], this rank's slot [rows_per_rank, ldc] of rank r's inbox; after a barrier the
- * owner adds its `world` slots with t5x_slot_sum_bf16. */
+ * c_peers[r], this rank's slot [rows_per_rank, ldc] of rank r's inbox; the kernel then raises
+ * this rank's "scattered" signal. The owner adds its `world` slots with
+ * t5x_slot_sum_wait_bf16 (sig = sig_local + 16), which first waits for every peer's signal of
+ * that epoch. Successive calls must alternate between two inboxes. */
+int t5x_gemm_allgather_flag_words(int world, int rows_per_rank);
 int t5x_gemm_allgather_bf16(void* A, const void* const* a_peers, int world, int rank,
                             int rows_per_rank, void* flags, const void* B, const void* B2,
                             void* C, int M, int N, int K, long long ldb, long long ldc,
                             int b_mn_major, int epilogue, void* H0, void* H1, long long ldh,
-                            void* stream);
+                            void* sig_local, void* const* sig_peers, unsigned int epoch,
+                            void* exit_count, void* stream);
 int t5x_gemm_reducescatter_bf16(const void* A, const void* B, void* const* c_peers, int world,
                                 int rank, int rows_per_rank, int M, int N, int K, long long lda,
                                 long long ldb, long long ldc, int a_mn_major, int b_mn_major,
-                                const void* R, long long ldr, void* stream);
+                                const void* R, long long ldr, void* sig_local,
+                                void* const* sig_peers, unsigned int epoch, void* exit_count,
+                                void* stream);
 int t5x_slot_sum_bf16(const void* slots, int num_slots, long long n, const void* residual,
                       void* dst, void* stream);
+int t5x_slot_sum_wait_bf16(const void* slots, int num_slots, long long n, const void* residual,
+                           void* dst, const void* sig, int world, int rank, unsigned int epoch,
+                           void* stream);
 
 /* Stream-ordered barrier over `world` ranks through signal pads (one per rank, as mapped
  * here; (channel + 1) * 16 uint32 each, zero at start). `epoch` >= 1 and increasing per

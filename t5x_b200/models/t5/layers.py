@@ -468,6 +468,7 @@ class MultiHeadDotProductAttention(nn.Module):
       h_sp, h_block = h_sp / math.sqrt(self.head_dim), None
     hd = (self.local_heads, self.head_dim)
     if kv_full is None:
+      tp_fused.fuse_weight_columns([self.query.kernel, self.key.kernel, self.value.kernel])
       q, k, v = tp_fused.all_gather_linears(
           h_sp, [self.query.kernel, self.key.kernel, self.value.kernel], block=h_block)
       lk = lq

@@ -43,6 +43,20 @@ def _sbh(t):
   return t.stride(0), t.stride(1), t.stride(2)
 
 
+def _packed_qkv(q, k, v) -> bool:
+  """True when q, k, v [B, L, H, D] are the three column blocks of one [B * L, 3 * H * D]
+  projection output (a fused q/k/v GEMM): their gradients are then written as the column
+  blocks of one buffer too, so that the projection's backward is a single GEMM over it."""
+  if q.shape != k.shape or q.shape != v.shape:
+    return False
+  b, l, h, d = q.shape
+  row = 3 * h * d
+  want = (l * row, row, d, 1)
+  step = h * d * q.element_size()
+  return (q.stride() == want and k.stride() == want and v.stride() == want and
+          k.data_ptr() == q.data_ptr() + step and v.data_ptr() == q.data_ptr() + 2 * step)
+
+
 class _FlashAttentionFn(torch.autograd.Function):
 
   @staticmethod
@@ -73,8 +87,13 @@ class _FlashAttentionFn(torch.autograd.Function):
     Lk = k.shape[1]
     do = do if _strides_ok(do) else do.contiguous()
     dq32 = torch.zeros((B, Lq, H, D), dtype=torch.float32, device=q.device)
-    dk = torch.empty((B, Lk, H, D), dtype=torch.bfloat16, device=q.device)
-    dv = torch.empty((B, Lk, H, D), dtype=torch.bfloat16, device=q.device)
+    packed = _packed_qkv(q, k, v)
+    if packed:
+      dqkv = torch.empty((B, Lq, 3, H, D), dtype=torch.bfloat16, device=q.device)
+      dq, dk, dv = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+    else:
+      dk = torch.empty((B, Lk, H, D), dtype=torch.bfloat16, device=q.device)
+      dv = torch.empty((B, Lk, H, D), dtype=torch.bfloat16, device=q.device)
     delta = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
     d_rel = torch.zeros_like(rel_bias) if rel_bias is not None else None
     nrel = rel_bias.shape[1] if rel_bias is not None else 0
@@ -85,7 +104,11 @@ class _FlashAttentionFn(torch.autograd.Function):
         native.ptr(d_rel), nrel, rel_off, native.ptr(key_mask), native.ptr(q_seg),
         native.ptr(kv_seg), int(causal), causal_off, native.stream_ptr())
     native._check(rc, "attention_bwd")
-    return dq32.to(torch.bfloat16), dk, dv, d_rel, None, None, None, None, None, None
+    if packed:
+      dq.copy_(dq32)
+    else:
+      dq = dq32.to(torch.bfloat16)
+    return dq, dk, dv, d_rel, None, None, None, None, None, None
 
 
 _BUCKET_CACHE: dict = {}

@@ -19,18 +19,30 @@ run inside the tensor-core kernels:
                           its `T` inbox slots in fp32.
 
 Backward of one is the other. Buffers that peers read or write live in one symmetric-memory
-arena per model group; flag barriers through its signal pads order the accesses: before a rank
-reuses bytes that peers read (or writes into a peer's inbox) every rank has finished the
-kernels that touched them.
+arena per model group. The kernels order their accesses themselves, through epoch-numbered
+signal words that every rank maps (`csrc/gemm_common.cuh`): an all-gather GEMM announces that
+its rank's rows are in place and waits for a peer's announcement before it reads from it; a
+reduce-scatter GEMM announces that all its stores have been performed and the kernel that sums
+the inbox slots waits for every peer's announcement. No barrier kernel runs between them.
+Two rules on the host keep reuse of memory safe:
+
+  * the inbox is double-buffered: call n writes the buffer call n - 2 used, and a rank can only
+    get to call n after its sum of call n - 1 has seen every peer finish GEMM n - 1, which
+    those peers ran after their sum of call n - 2;
+  * an arena block that peers may still be reading is not handed out again until this rank has
+    enqueued a slot sum (whose wait proves that every peer is past the GEMMs issued before it),
+    or a real barrier.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
 
+from t5x_b200.ops import comm
 from t5x_b200.parallel import state as pstate
 
 _ALIGN = 1024
@@ -61,9 +73,11 @@ class _Block:
     return [p + self.offset + extra_bytes for p in self.arena.buf.peer_ptrs]
 
   def release(self) -> None:
+    """Gives the bytes back. They become allocatable again once peers can no longer be
+    reading them (see `SymmetricArena.peers_are_past`)."""
     ar, self.arena = self.arena, None
     if ar is not None and self.generation == ar.generation:
-      ar._free(self.offset, self.size)
+      ar.quarantine.append((self.offset, self.size))
 
 
 class _Inbox:
@@ -88,22 +102,27 @@ class SymmetricArena:
   the same offset of the peer's mapping."""
 
   def __init__(self, nbytes: int, group):
-    from t5x_b200.ops import comm
     self.buf = comm.SymmetricBuffer(int(nbytes), torch.uint8, group)
     self.rank, self.world = self.buf.rank, self.buf.world
     self.nbytes = int(nbytes)
     self.free = [(0, self.nbytes)]
+    self.quarantine = []  # released blocks that peers may still be reading
     self.generation = 0   # bumped by end_step(); blocks of older generations are void
     self.allocations = 0  # blocks handed out so far (cross-checked over ranks in debug runs)
-    self.flags = torch.zeros(64, dtype=torch.int32, device=self.buf.tensor.device)
-    # True while a kernel that reads peers' memory has been enqueued since the last barrier:
-    # the next reuse of arena bytes must wait for every rank to get past it.
-    self.dirty = False
-    # The inbox of the reduce-scatter kernels is a buffer of its own (peers write it, only
-    # this rank reads it). True while this rank's sum over it is not yet ordered before the
-    # peers' next writes by a barrier.
-    self._inbox = None
-    self.inbox_busy = False
+    dev = self.buf.tensor.device
+    # arrival counters of the all-gather GEMM (zero between calls) and its exit counter
+    self.flags = torch.zeros(1 << 16, dtype=torch.int32, device=dev)
+    self.exit_count = torch.zeros(1, dtype=torch.int32, device=dev)
+    # epoch-numbered signal words, one array per rank, mapped by all ranks
+    self.sig = comm.SymmetricBuffer(64, torch.int32, group, dev)
+    self.sig.tensor.zero_()
+    torch.cuda.synchronize(dev)
+    dist.barrier(group=group)  # every rank's words are zero before anyone raises one
+    self.epoch = 0
+    # The inboxes of the reduce-scatter kernels are buffers of their own (peers write them,
+    # only this rank reads them), used alternately.
+    self._inboxes = [None, None]
+    self._inbox_turn = 0
     self._group = group
 
   def alloc(self, nbytes: int) -> _Block:
@@ -116,6 +135,10 @@ class SymmetricArena:
           self.free[i] = (off + size, sz - size)
         self.allocations += 1
         return _Block(self, off, size)
+    if self.quarantine:
+      # out of proven-free bytes: a real barrier proves the quarantined ones free
+      self.barrier()
+      return self.alloc(nbytes)
     raise RuntimeError(
         f"tensor-parallel arena exhausted ({size} bytes wanted); raise T5X_B200_TP_ARENA_GB")
 
@@ -130,15 +153,33 @@ class SymmetricArena:
         merged.append((off, sz))
     self.free = merged
 
+  def next_epoch(self) -> int:
+    """The epoch number of the next tensor-parallel GEMM (every rank counts the same calls)."""
+    self.epoch = (self.epoch + 1) & 0xFFFFFFFF
+    return self.epoch
+
+  def sig_local_ptr(self, kind: int) -> int:
+    return self.sig.tensor.data_ptr() + kind * 16 * 4
+
+  def peers_are_past(self) -> None:
+    """Called when a kernel has been enqueued whose wait proves that every peer has finished
+    the tensor-parallel GEMMs issued so far: released blocks may be handed out again to work
+    enqueued from here on."""
+    for off, size in self.quarantine:
+      self._free(off, size)
+    self.quarantine = []
+
   def end_step(self) -> None:
     """Called by the trainer between steps, when no activation of the step is alive any more:
-    every block still allocated (dropped without `release()`, or kept by an exception path) is
-    voided and the whole arena is free again. With `T5X_B200_TP_ARENA_CHECK=1` the ranks also
-    compare how many blocks they have handed out; a difference means their programs diverged
-    and peers would read each other's bytes at the wrong offsets."""
-    self.settle()
+    after a barrier every block still allocated (dropped without `release()`, or kept by an
+    exception path) is voided and the whole arena is free again. With
+    `T5X_B200_TP_ARENA_CHECK=1` the ranks also compare how many blocks they have handed out; a
+    difference means their programs diverged and peers would read each other's bytes at the
+    wrong offsets."""
+    self.barrier()
     self.generation += 1
     self.free = [(0, self.nbytes)]
+    self.quarantine = []
     if os.environ.get("T5X_B200_TP_ARENA_CHECK", "0") == "1" and dist.is_initialized():
       mine = torch.tensor([self.allocations], dtype=torch.int64, device=self.buf.tensor.device)
       every = [torch.zeros_like(mine) for _ in range(self.world)]
@@ -148,21 +189,24 @@ class SymmetricArena:
         raise RuntimeError(f"tensor-parallel arena: ranks handed out {counts} blocks; their "
                            "allocation sequences differ")
 
-  def inbox(self, nbytes: int) -> "_Inbox":
-    if self._inbox is None or self._inbox.tensor.numel() < nbytes:
-      from t5x_b200.ops import comm
-      self.barrier()  # nobody is still writing the buffer being replaced
-      self._inbox = comm.SymmetricBuffer(int(nbytes), torch.uint8, self._group)
-    return _Inbox(self, self._inbox)
+  def next_inbox(self, nbytes: int) -> "_Inbox":
+    """The inbox for the next reduce-scatter (the two buffers take turns). Growing them is a
+    collective allocation behind a barrier."""
+    if self._inboxes[0] is None or self._inboxes[0].tensor.numel() < nbytes:
+      self.barrier()  # nobody is still writing the buffers being replaced
+      self._inboxes = [comm.SymmetricBuffer(int(nbytes), torch.uint8, self._group),
+                       comm.SymmetricBuffer(int(nbytes), torch.uint8, self._group)]
+    self._inbox_turn ^= 1
+    return _Inbox(self, self._inboxes[self._inbox_turn])
 
   def barrier(self) -> None:
+    """A real barrier kernel over the group (step boundaries, buffer growth, arena pressure)."""
     self.buf.barrier(channel=0)
-    self.dirty = False
-    self.inbox_busy = False
+    self.peers_are_past()
 
   def settle(self) -> None:
-    """Barrier only if a peer-touching kernel is still unordered against what comes next."""
-    if self.dirty:
+    """Barrier if released blocks are still waiting for proof that peers are done with them."""
+    if self.quarantine:
       self.barrier()
 
 
@@ -189,17 +233,20 @@ def enabled() -> bool:
 # ---- kernel wrappers ----------------------------------------------------------------------
 def _native():
   from t5x_b200.ops import native
-  import ctypes
   if not getattr(_native, "_registered", False):
     vp, ci, ll = native.c_void_p, native.c_int, native.c_ll
     pp = ctypes.POINTER(vp)
+    cu = ctypes.c_uint
     native.register_signature(
         "t5x_gemm_allgather_bf16",
-        [vp, pp, ci, ci, ci, vp, vp, vp, vp, ci, ci, ci, ll, ll, ci, ci, vp, vp, ll, vp])
+        [vp, pp, ci, ci, ci, vp, vp, vp, vp, ci, ci, ci, ll, ll, ci, ci, vp, vp, ll, vp, pp, cu,
+         vp, vp])
+    native.register_signature("t5x_gemm_allgather_flag_words", [ci, ci])
     native.register_signature("t5x_slot_sum_bf16", [vp, ci, ll, vp, vp, vp])
+    native.register_signature("t5x_slot_sum_wait_bf16", [vp, ci, ll, vp, vp, vp, ci, ci, cu, vp])
     native.register_signature(
         "t5x_gemm_reducescatter_bf16",
-        [vp, vp, pp, ci, ci, ci, ci, ci, ci, ll, ll, ll, ci, ci, vp, ll, vp])
+        [vp, vp, pp, ci, ci, ci, ci, ci, ci, ll, ll, ll, ci, ci, vp, ll, vp, pp, cu, vp, vp])
     _native._registered = True
   return native
 
@@ -237,19 +284,22 @@ def gemm_allgather(block: _Block, M: int, K: int, b: torch.Tensor, *,
       h1 = h0 + N * 2
       ldh = save_h.stride(0)
   a = block.tensor((M, K))
+  if native.lib().t5x_gemm_allgather_flag_words(ar.world, M // ar.world) > ar.flags.numel():
+    raise RuntimeError(f"gemm_allgather: {M} rows need more arrival counters than the arena has")
   native._check(native.lib().t5x_gemm_allgather_bf16(
       a.data_ptr(), _ptr_array(block.peer_ptrs()), ar.world, ar.rank, M // ar.world,
       ar.flags.data_ptr(), b.data_ptr(), native.ptr(b2), out.data_ptr(), M, N, K, ldb,
-      out.stride(0), b_mn, 1 if b2 is not None else 0, h0, h1, ldh, native.stream_ptr()),
-      "gemm_allgather")
-  ar.dirty = True
+      out.stride(0), b_mn, 1 if b2 is not None else 0, h0, h1, ldh, ar.sig.tensor.data_ptr(),
+      _ptr_array(ar.sig.peer_ptrs), ar.next_epoch(), ar.exit_count.data_ptr(),
+      native.stream_ptr()), "gemm_allgather")
   return out
 
 
 def gemm_reducescatter(a: torch.Tensor, b: torch.Tensor, inbox: _Inbox, *,
-                       residual: Optional[torch.Tensor] = None) -> None:
+                       residual: Optional[torch.Tensor] = None) -> int:
   """Stores the bf16 partial product a [M, K] @ b [K, N] (+ residual [M, N]) of this rank
-  into slot `rank` of the owners' inboxes (`inbox`: [T, M / T, N] bf16 on every rank)."""
+  into slot `rank` of the owners' inboxes (`inbox`: [T, M / T, N] bf16 on every rank).
+  Returns the epoch whose "scattered" signals the sum over the slots has to wait for."""
   native = _native()
   ar = inbox.arena
   M, K = a.shape
@@ -262,9 +312,13 @@ def gemm_reducescatter(a: torch.Tensor, b: torch.Tensor, inbox: _Inbox, *,
   if residual is not None:
     assert residual.dtype == torch.bfloat16 and residual.stride(1) == 1
     r_ptr, ldr = residual.data_ptr(), residual.stride(0)
+  epoch = ar.next_epoch()
   native._check(native.lib().t5x_gemm_reducescatter_bf16(
       a.data_ptr(), b.data_ptr(), _ptr_array(inbox.peer_ptrs(slot)), ar.world, ar.rank, rows, M,
-      N, K, lda, ldb, N, a_mn, b_mn, r_ptr, ldr, native.stream_ptr()), "gemm_reducescatter")
+      N, K, lda, ldb, N, a_mn, b_mn, r_ptr, ldr, ar.sig.tensor.data_ptr(),
+      _ptr_array(ar.sig.peer_ptrs), epoch, ar.exit_count.data_ptr(), native.stream_ptr()),
+      "gemm_reducescatter")
+  return epoch
 
 
 # ---- building blocks ----------------------------------------------------------------------
@@ -273,21 +327,18 @@ def rows_buffer(m: int, k: int):
   rank's rows of it. A producer that writes its [m, k] result into `dst` saves the copy that
   `all_gather_linears(..., block=None)` would make."""
   ar = arena()
-  ar.settle()  # peers may still be reading the bytes this block reuses
-  blk = ar.alloc(m * ar.world * k * 2)
+  blk = ar.alloc(m * ar.world * k * 2)  # only bytes no peer can still be reading
   return blk, blk.tensor((m * ar.world, k))[ar.rank * m:(ar.rank + 1) * m]
 
 
 def _gather_block(rows: torch.Tensor, blk: Optional[_Block] = None) -> _Block:
-  """An arena block shaped [M, K] whose block of this rank holds `rows` ([M / T, K]), with
-  every rank past the point where its own rows are in place. `blk`: the block `rows` already
-  lives in (see `rows_buffer`)."""
-  ar = arena()
+  """An arena block shaped [M, K] whose block of this rank holds `rows` ([M / T, K]). `blk`:
+  the block `rows` already lives in (see `rows_buffer`). The all-gather GEMM that consumes
+  the block tells the peers that the rows are there."""
   m, k = rows.shape
   if blk is None:
     blk, dst = rows_buffer(m, k)
     dst.copy_(rows)
-  ar.barrier()
   return blk
 
 
@@ -300,24 +351,67 @@ def _reduce_scatter(a: torch.Tensor, b: torch.Tensor, residual: Optional[torch.T
   ar = arena()
   M, N = a.shape[0], b.shape[1]
   m = M // ar.world
-  inbox = ar.inbox(M * N * 2)
-  if ar.inbox_busy:
-    ar.barrier()  # every rank has finished summing what the inbox held before
-  gemm_reducescatter(a, b, inbox, residual=residual)
-  ar.barrier()  # every rank's rows have landed
+  inbox = ar.next_inbox(M * N * 2)
+  epoch = gemm_reducescatter(a, b, inbox, residual=residual)
   out = torch.empty((m, N), dtype=torch.bfloat16, device=a.device)
   if add_rows is not None:
     assert add_rows.dtype == torch.bfloat16 and add_rows.is_contiguous()
-  native._check(native.lib().t5x_slot_sum_bf16(
+  # the sum waits (inside the kernel) until every peer's rows have landed
+  native._check(native.lib().t5x_slot_sum_wait_bf16(
       inbox.tensor((ar.world, m, N)).data_ptr(), ar.world, m * N, native.ptr(add_rows),
-      out.data_ptr(), native.stream_ptr()), "slot_sum_bf16")
-  ar.inbox_busy = True
+      out.data_ptr(), ar.sig_local_ptr(1), ar.world, ar.rank, epoch, native.stream_ptr()),
+      "slot_sum_wait_bf16")
+  ar.peers_are_past()
   return out
 
 
 def _weight2d(w: torch.Tensor, k: int) -> torch.Tensor:
   from t5x_b200.ops import functional as F
   return F.compute_weight(w, torch.bfloat16).reshape(k, -1)
+
+
+def _column_blocks(ts: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
+  """If the 2-D tensors `ts` ([rows, n_i], unit inner stride) are consecutive column blocks of
+  one row-major matrix, that matrix [rows, sum n_i]; else None. Used to run the projections of
+  q, k and v (whose bf16 weights are kept side by side in one buffer) as one GEMM, and to use
+  their gradients, which the attention backward writes side by side, without a copy."""
+  t0 = ts[0]
+  if t0.dim() != 2 or t0.stride(1) != 1:
+    return None
+  ld, total = t0.stride(0), 0
+  for t in ts:
+    if (t.dim() != 2 or t.stride() != (ld, 1) or t.shape[0] != t0.shape[0] or
+        t.dtype != t0.dtype or t.data_ptr() != t0.data_ptr() + total * t0.element_size()):
+      return None
+    total += t.shape[1]
+  if total > ld:
+    return None
+  return torch.as_strided(t0, (t0.shape[0], total), (ld, 1))
+
+
+def fuse_weight_columns(params: Sequence[torch.Tensor]) -> bool:
+  """Puts the bf16 working copies (`p.bf16`) of 2-D parameters with equal row counts side by
+  side in one buffer, as strided views, so that `_column_blocks` finds them. The optimizer
+  kernels write working copies through their row stride, so the views stay current. Returns
+  False (and changes nothing) when a copy is missing or managed elsewhere (optimizer sharding
+  keeps the working copies in a buffer of its own)."""
+  bfs = [getattr(p, "bf16", None) for p in params]
+  if any(b is None or b.dim() != 2 for b in bfs) or \
+      any(getattr(p, "zero", None) is not None for p in params):
+    return False
+  if _column_blocks(bfs) is not None:
+    return True
+  with torch.no_grad():
+    k = bfs[0].shape[0]
+    widths = [b.shape[1] for b in bfs]
+    fused = torch.empty((k, sum(widths)), dtype=bfs[0].dtype, device=bfs[0].device)
+    col = 0
+    for p, b, n in zip(params, bfs, widths):
+      view = fused[:, col:col + n]
+      view.copy_(b)
+      p.bf16 = view
+      col += n
+  return True
 
 
 class _AllGatherLinearsFn(torch.autograd.Function):
@@ -337,9 +431,15 @@ class _AllGatherLinearsFn(torch.autograd.Function):
       ctx.h = torch.empty((M, 2 * ws[0].shape[1]), dtype=torch.bfloat16, device=h_sp.device)
       outs = [gemm_allgather(blk, M, k, ws[0], b2=ws[1], save_h=ctx.h)]
     else:
-      outs = [gemm_allgather(blk, M, k, ws[0])]
-      a_full = blk.tensor((M, k))
-      outs += [native.gemm(a_full, w) for w in ws[1:]]
+      fused = _column_blocks(ws) if len(ws) > 1 else None
+      if fused is not None:
+        # q | k | v side by side: one GEMM with three times the work to hide the gather behind
+        out = gemm_allgather(blk, M, k, fused)
+        outs = list(torch.split(out, [w.shape[1] for w in ws], dim=1))
+      else:
+        outs = [gemm_allgather(blk, M, k, ws[0])]
+        a_full = blk.tensor((M, k))
+        outs += [native.gemm(a_full, w) for w in ws[1:]]
     ctx.blk, ctx.weights, ctx.gated, ctx.shape = blk, weights, gated, (M, k)
     if not any(ctx.needs_input_grad):
       # no backward will come for this block: give the bytes back here (the next user of
@@ -361,7 +461,12 @@ class _AllGatherLinearsFn(torch.autograd.Function):
       native.gated_gelu_bwd_(douts[0].reshape(M, dff).contiguous(), dh)
       dys = [dh[:, :dff], dh[:, dff:]]
     else:
-      dys = [None if d is None else d.reshape(M, -1).contiguous() for d in douts]
+      dys = []
+      for d in douts:
+        if d is not None:
+          d = d.reshape(M, -1)
+          d = d if d.stride(1) == 1 else d.contiguous()
+        dys.append(d)
     dws = []
     for i, (w, dy) in enumerate(zip(weights, dys)):
       need = ctx.needs_input_grad[3 + i] and dy is not None
@@ -371,6 +476,13 @@ class _AllGatherLinearsFn(torch.autograd.Function):
     dh_sp = None
     if ctx.needs_input_grad[0]:
       live = [(dy, w) for dy, w in zip(dys, ws) if dy is not None]
+      fused_w = _column_blocks([w for _, w in live]) if len(live) > 1 else None
+      if fused_w is not None:
+        # dx = [dq | dk | dv] @ [Wq | Wk | Wv]^T as one reduce-scatter GEMM
+        dy_all = _column_blocks([dy for dy, _ in live])
+        if dy_all is None:
+          dy_all = torch.cat([dy for dy, _ in live], dim=1)
+        live = [(dy_all, fused_w)]
       partial = None
       for dy, w in live[:-1]:
         if partial is None:

@@ -99,11 +99,14 @@ def test_two_way_tensor_parallel_matches_single(tmp_path):
 
 def test_symmetric_arena_allocator_is_deterministic_and_coalesces():
   """The first-fit allocator of the fused tensor-parallel path: every rank runs the same
-  sequence, so offsets must depend on the sequence only; freed neighbours merge again."""
+  sequence, so offsets must depend on the sequence only; released blocks wait in quarantine
+  until peers are known to be done with them; freed neighbours merge again."""
   from t5x_b200.parallel import tp_fused
   ar = object.__new__(tp_fused.SymmetricArena)
   ar.nbytes, ar.free, ar.generation, ar.allocations = 1 << 20, [(0, 1 << 20)], 0, 0
-  ar.dirty, ar.world = False, 1
+  ar.quarantine, ar.world = [], 1
+  barriers = []
+  ar.barrier = lambda: (barriers.append(1), ar.peers_are_past())
   a = ar.alloc(1000)          # rounded up to the 1024-byte granule
   b = ar.alloc(5000)
   c = ar.alloc(1024)
@@ -111,25 +114,31 @@ def test_symmetric_arena_allocator_is_deterministic_and_coalesces():
   assert (b.offset, b.size) == (1024, 5120)
   assert c.offset == 6144
   b.release()
-  d = ar.alloc(2048)          # first fit: the hole left by b
-  assert d.offset == 1024
-  e = ar.alloc(4096)          # does not fit the remaining 3072-byte hole
-  assert e.offset == 7168
+  d = ar.alloc(2048)          # b's bytes may still be read by peers: not handed out yet
+  assert d.offset == 7168
+  ar.peers_are_past()         # e.g. a slot sum that waited for every peer has been enqueued
+  e = ar.alloc(2048)          # first fit: the hole left by b
+  assert e.offset == 1024
   for blk in (a, c, d, e):
     blk.release()
-  assert ar.free == [(0, 1 << 20)]
   b.release()                 # releasing twice is a no-op
+  ar.peers_are_past()
   assert ar.free == [(0, 1 << 20)]
   f = ar.alloc(1 << 20)
   with pytest.raises(RuntimeError, match="arena exhausted"):
     ar.alloc(1)
-  del f                       # dropping a block frees nothing: object lifetime differs by rank
-  assert ar.free == []
+  f.release()
+  assert not barriers
+  g = ar.alloc(4096)          # only quarantined bytes are left: a real barrier proves them free
+  assert barriers == [1] and g.offset == 0
+  del g                       # dropping a block frees nothing: object lifetime differs by rank
+  assert ar.free == [(4096, (1 << 20) - 4096)]
   ar.end_step()               # the step boundary voids whatever is still allocated
-  assert ar.free == [(0, 1 << 20)] and ar.allocations == 6
+  assert ar.free == [(0, 1 << 20)] and ar.allocations == 7
   h = ar.alloc(4096)
   ar.end_step()
   h.release()                 # a block of an earlier step is void: nothing is freed twice
+  ar.peers_are_past()
   assert ar.free == [(0, 1 << 20)]
 
 
