@@ -12,7 +12,10 @@
 //   dist_apply      : Adafactor parameter update whose bf16 result is stored to every rank's
 //                     working copy (the all-gather of updated weights fused into the update)
 //
-// Only plain ld/st are used on peer addresses: no TMA, no multimem.
+// Peer addresses are accessed with plain ld/st. When the caller also passes the NVSwitch
+// multicast address of the same buffers, the gradient sum is one `multimem.ld_reduce` per 16
+// bytes (the switch adds the ranks' copies and the owner receives 1/world of the bytes) and the
+// weight push one `multimem.st` (the switch fans the store out). No TMA is used on peer memory.
 #include "adafactor_common.cuh"
 #include "common.cuh"
 #include "t5x_b200.h"
@@ -39,6 +42,22 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
   return v;
+}
+
+// In-switch sum of the 16 bytes at `mc` (multicast address) over every rank's copy.
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+// One 8-byte store that the switch delivers to every rank's copy.
+__device__ __forceinline__ void multimem_st_b32x2(void* mc, uint32_t a, uint32_t b) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc),
+               "f"(__uint_as_float(a)), "f"(__uint_as_float(b))
+               : "memory");
 }
 
 // One CTA, one thread per peer. Slot layout inside a pad: pad[channel * kMaxPeers + writer].
@@ -137,7 +156,9 @@ static inline int ds_grid(const DsTiles& t) {
 // Adafactor phase 1 over the gradient summed across ranks. CTA tile: kDsTileR rows x
 // kDsTileC columns; a thread owns 4 adjacent columns and walks the rows, so column sums stay
 // in registers and row sums need one block reduction per row. Requires C % 4 == 0.
-template <int W>  // number of ranks known at compile time, or 0 for any `world`
+// W: number of ranks known at compile time, or 0 for any `world`; W = -1: grads.p[0] is the
+// multicast address and the switch performs the sum.
+template <int W>
 __global__ void __launch_bounds__(kDsThreads)
     dist_stats_kernel(PeerF32 grads, int world, float* __restrict__ g_out,
                       const float* __restrict__ p, float* __restrict__ rowsum,
@@ -158,7 +179,7 @@ __global__ void __launch_bounds__(kDsThreads)
   // All loads of RU rows (W gradient copies and the parameter each) are issued before the
   // first use, so a thread keeps RU * (W + 1) 16-byte requests in flight over NVLink / HBM.
   constexpr int RU = W == 0 ? 1 : (W <= 2 ? 4 : 2);
-  constexpr int WN = W == 0 ? 1 : W;
+  constexpr int WN = W <= 0 ? 1 : W;
   for (int rr = 0; rr < rows; rr += RU) {
     float4 v[RU][WN], pv[RU];
 #pragma unroll
@@ -177,6 +198,8 @@ __global__ void __launch_bounds__(kDsThreads)
             acc.w += t.w;
           }
         v[u][0] = acc;
+      } else if (W < 0) {
+        v[u][0] = on ? multimem_ld_reduce_f32x4(grads.p[0] + off) : make_float4(0.f, 0.f, 0.f, 0.f);
       } else {
 #pragma unroll
         for (int d = 0; d < WN; ++d)
@@ -245,7 +268,7 @@ __global__ void __launch_bounds__(kDsThreads)
                       const float* __restrict__ rf, const float* __restrict__ cf,
                       float* __restrict__ m, PeerBf16 out, int world,
                       const AdafactorScalars* __restrict__ scal, int R, int C, float n_global,
-                      AfHyper h, DsTiles tiles) {
+                      AfHyper h, DsTiles tiles, __nv_bfloat16* __restrict__ out_mc) {
   for (long long tile = blockIdx.x; tile < tiles.total; tile += gridDim.x) {
   const int b = static_cast<int>(tile / tiles.per_batch);
   const int in_b = static_cast<int>(tile - static_cast<long long>(b) * tiles.per_batch);
@@ -305,7 +328,10 @@ __global__ void __launch_bounds__(kDsThreads)
     uint2 packed;
     packed.x = *reinterpret_cast<uint32_t*>(&lo);
     packed.y = *reinterpret_cast<uint32_t*>(&hi);
-    for (int d = 0; d < world; ++d) *reinterpret_cast<uint2*>(out.p[d] + off) = packed;
+    if (out_mc != nullptr)
+      multimem_st_b32x2(out_mc + off, packed.x, packed.y);
+    else
+      for (int d = 0; d < world; ++d) *reinterpret_cast<uint2*>(out.p[d] + off) = packed;
   }
   }
   }
@@ -383,9 +409,22 @@ T5X_API void t5x_comm_set_max_ctas(int max_ctas) { g_comm_max_ctas = max_ctas < 
 // Adafactor phase 1 with the gradient summed over `world` ranks' copies (grads[d], same
 // layout as g_out, which receives the sum and may be this rank's own copy). Clears `scratch`
 // like t5x_adafactor_stats. Requires C % 4 == 0 and 16-byte aligned pointers.
+T5X_API int t5x_dist_adafactor_stats_mc(const void* p, const void* const* grads, int world,
+                                        const void* grads_mc, void* g_out, void* scratch,
+                                        int batch, int R, int C, float eps1, void* stream);
+
 T5X_API int t5x_dist_adafactor_stats(const void* p, const void* const* grads, int world,
                                      void* g_out, void* scratch, int batch, int R, int C,
                                      float eps1, void* stream) {
+  return t5x_dist_adafactor_stats_mc(p, grads, world, nullptr, g_out, scratch, batch, R, C, eps1,
+                                     stream);
+}
+
+// The same with `grads_mc`, the multicast address of the gradient buffers (or null): the sum
+// over ranks is then taken by the switch.
+T5X_API int t5x_dist_adafactor_stats_mc(const void* p, const void* const* grads, int world,
+                                        const void* grads_mc, void* g_out, void* scratch,
+                                        int batch, int R, int C, float eps1, void* stream) {
   if (batch <= 0 || R <= 0 || C <= 0) return 0;
   if (world < 1 || world > kMaxPeers || (C & 3)) return set_error("dist_adafactor_stats: bad shape");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -401,6 +440,12 @@ T5X_API int t5x_dist_adafactor_stats(const void* p, const void* const* grads, in
   auto kernel = world == 2 ? dist_stats_kernel<2>
               : world == 4 ? dist_stats_kernel<4>
               : world == 8 ? dist_stats_kernel<8> : dist_stats_kernel<0>;
+  if (grads_mc != nullptr) {
+    if (reinterpret_cast<uintptr_t>(grads_mc) & 15)
+      return set_error("dist_adafactor_stats: multicast address must be 16-byte aligned");
+    kernel = dist_stats_kernel<-1>;
+    ps.p[0] = static_cast<const float*>(grads_mc);
+  }
   kernel<<<ds_grid(tiles), kDsThreads, 0, st>>>(
       ps, world, static_cast<float*>(g_out), static_cast<const float*>(p), rowsum, colsum, scal,
       R, C, eps1, tiles);
@@ -410,11 +455,29 @@ T5X_API int t5x_dist_adafactor_stats(const void* p, const void* const* grads, in
 
 // Adafactor phase 4 storing the bf16 result into every rank's copy (bf16_out[d], contiguous
 // [batch, R, C] like p). Requires C % 4 == 0.
+T5X_API int t5x_dist_adafactor_apply_mc(void* p, const void* g, void* m, void* const* bf16_out,
+                                        int world, void* bf16_mc, void* scratch, int batch, int R,
+                                        int C, long long n_global, float lr, float eps2,
+                                        float clip_threshold, float weight_decay, float beta1,
+                                        float max_param_scale, int flags, void* stream);
+
 T5X_API int t5x_dist_adafactor_apply(void* p, const void* g, void* m, void* const* bf16_out,
                                      int world, void* scratch, int batch, int R, int C,
                                      long long n_global, float lr, float eps2,
                                      float clip_threshold, float weight_decay, float beta1,
                                      float max_param_scale, int flags, void* stream) {
+  return t5x_dist_adafactor_apply_mc(p, g, m, bf16_out, world, nullptr, scratch, batch, R, C,
+                                     n_global, lr, eps2, clip_threshold, weight_decay, beta1,
+                                     max_param_scale, flags, stream);
+}
+
+// The same with `bf16_mc`, the multicast address of the working-copy buffers (or null): one
+// store per 8 bytes then reaches every rank's copy through the switch.
+T5X_API int t5x_dist_adafactor_apply_mc(void* p, const void* g, void* m, void* const* bf16_out,
+                                        int world, void* bf16_mc, void* scratch, int batch, int R,
+                                        int C, long long n_global, float lr, float eps2,
+                                        float clip_threshold, float weight_decay, float beta1,
+                                        float max_param_scale, int flags, void* stream) {
   if (batch <= 0) return 0;
   if (world < 1 || world > kMaxPeers || (C & 3)) return set_error("dist_adafactor_apply: bad shape");
   PeerBf16 po;
@@ -427,7 +490,8 @@ T5X_API int t5x_dist_adafactor_apply(void* p, const void* g, void* m, void* cons
   const DsTiles tiles = ds_tiles(batch, R, C);
   dist_apply_kernel<<<ds_grid(tiles), kDsThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<float*>(p), static_cast<const float*>(g), rf, cf, static_cast<float*>(m), po,
-      world, scal, R, C, static_cast<float>(n_global), h, tiles);
+      world, scal, R, C, static_cast<float>(n_global), h, tiles,
+      static_cast<__nv_bfloat16*>(bf16_mc));
   count_launches(1);
   return comm_check("dist_adafactor_apply");
 }

@@ -464,7 +464,7 @@ class Adafactor(OptimizerDef):
     if zinfo is not None:
       from t5x_b200.ops import comm
       comm.dist_adafactor_stats_(param, zinfo.grad_ptrs(), grad, scratch, batch, R, C,
-                                 hp.epsilon1)
+                                 hp.epsilon1, grad_mc=zinfo.grad_mc())
     else:
       native.adafactor_stats_(param, grad, scratch, batch, R, C, hp.epsilon1)
     rows_sharded = sharded and shard_dim in row_dims
@@ -494,7 +494,7 @@ class Adafactor(OptimizerDef):
       scratch[o_scal:o_scal + 4 * batch].view(batch, 4)[:, 1] = us
     if zinfo is not None:
       comm.dist_adafactor_apply_(param, grad, m, zinfo.bf16_ptrs(), scratch, batch, R, C,
-                                 n_global, **common)
+                                 n_global, bf16_mc=zinfo.bf16_mc(), **common)
     else:
       native.adafactor_apply_(param, grad, m, bf, scratch, batch, R, C, n_global,
                               ld_bf16=ld_bf16, bf16_batch_stride=bbs, **common)

@@ -32,11 +32,23 @@ native.register_signature("t5x_dist_adafactor_apply",
                            c_ll, c_float, c_float, c_float, c_float, c_float, c_float, c_int,
                            c_void_p])
 
+native.register_signature("t5x_dist_adafactor_stats_mc",
+                          [c_void_p, _PP, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                           c_float, c_void_p])
+native.register_signature("t5x_dist_adafactor_apply_mc",
+                          [c_void_p, c_void_p, c_void_p, _PP, c_int, c_void_p, c_void_p, c_int,
+                           c_int, c_int, c_ll, c_float, c_float, c_float, c_float, c_float,
+                           c_float, c_int, c_void_p])
 native.register_signature("t5x_comm_set_max_ctas", [c_int])
 
 MAX_PEERS = 16
 # Polls (64 ns apart at least) a barrier waits before it gives up: about two seconds.
 DEFAULT_SPIN_LIMIT = 1 << 24
+
+
+def nvls_requested() -> bool:
+  """In-switch reduction / multicast for the sharded-optimizer exchange (`T5X_B200_NVLS=1`)."""
+  return os.environ.get("T5X_B200_NVLS", "0") == "1"
 
 
 def _ptr_array(ptrs: Sequence[int]):
@@ -48,9 +60,12 @@ class SymmetricBuffer:
 
   def __init__(self, numel: int, dtype: torch.dtype, group=None, device=None):
     import torch.distributed._symmetric_memory as symm_mem
-    # Plain peer loads/stores only: the switch multicast object is not needed, and leaving
-    # memory unbound from it keeps a rank's death from disturbing its peers' GPUs.
-    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    # By default memory stays unbound from the switch's multicast object (plain peer loads and
+    # stores only): a rank that dies then cannot disturb its peers' GPUs. `T5X_B200_NVLS=1`
+    # (set before the first buffer of the process is created) binds the buffers, and
+    # `multicast_ptr` is then the address on which `multimem` instructions reach all copies.
+    if not nvls_requested():
+      os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     group = group if group is not None else dist.group.WORLD
     device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
     self.group = group
@@ -63,7 +78,13 @@ class SymmetricBuffer:
     self.peer_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
     self.pad_ptrs: List[int] = [int(p) for p in self.handle.signal_pad_ptrs]
     self.itemsize = self.tensor.element_size()
+    self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0) \
+        if nvls_requested() else 0
     self._epochs = {}
+
+  def mc_ptr_at(self, offset_elems: int) -> int:
+    """Multicast address of element `offset_elems` (0 when the buffer is not bound)."""
+    return self.multicast_ptr + offset_elems * self.itemsize if self.multicast_ptr else 0
 
   def ptrs_at(self, offset_elems: int):
     """ctypes array of every rank's address of element `offset_elems`."""
@@ -102,18 +123,22 @@ def peer_push_bf16_(dst_ptrs, src: torch.Tensor, n: int, skip_rank: int = -1) ->
                 "peer_push_bf16")
 
 
-def dist_adafactor_stats_(p, grad_ptrs, g_out, scratch, batch, rows, cols, eps1) -> None:
-  native._check(native.lib().t5x_dist_adafactor_stats(
-      p.data_ptr(), grad_ptrs, len(grad_ptrs), g_out.data_ptr(), scratch.data_ptr(), batch, rows,
-      cols, eps1, native.stream_ptr()), "dist_adafactor_stats")
+def dist_adafactor_stats_(p, grad_ptrs, g_out, scratch, batch, rows, cols, eps1,
+                          grad_mc: int = 0) -> None:
+  """`grad_mc`: multicast address of the gradient (0: the owner loads every rank's copy)."""
+  native._check(native.lib().t5x_dist_adafactor_stats_mc(
+      p.data_ptr(), grad_ptrs, len(grad_ptrs), grad_mc, g_out.data_ptr(), scratch.data_ptr(),
+      batch, rows, cols, eps1, native.stream_ptr()), "dist_adafactor_stats")
 
 
 def dist_adafactor_apply_(p, g, m, bf16_ptrs, scratch, batch, rows, cols, n_global, *, lr, eps2,
-                          clip_threshold, weight_decay, beta1, max_param_scale, flags) -> None:
-  native._check(native.lib().t5x_dist_adafactor_apply(
-      p.data_ptr(), g.data_ptr(), native.ptr(m), bf16_ptrs, len(bf16_ptrs), scratch.data_ptr(),
-      batch, rows, cols, n_global, lr, eps2, clip_threshold, weight_decay, beta1,
-      max_param_scale, flags, native.stream_ptr()), "dist_adafactor_apply")
+                          clip_threshold, weight_decay, beta1, max_param_scale, flags,
+                          bf16_mc: int = 0) -> None:
+  """`bf16_mc`: multicast address of the working copies (0: one store per rank)."""
+  native._check(native.lib().t5x_dist_adafactor_apply_mc(
+      p.data_ptr(), g.data_ptr(), native.ptr(m), bf16_ptrs, len(bf16_ptrs), bf16_mc,
+      scratch.data_ptr(), batch, rows, cols, n_global, lr, eps2, clip_threshold, weight_decay,
+      beta1, max_param_scale, flags, native.stream_ptr()), "dist_adafactor_apply")
 
 
 def set_max_ctas(max_ctas: int) -> None:
