@@ -60,6 +60,21 @@ class ZeroInfo:
     return self.ctx.weights.mc_ptr_at(self.offset)
 
 
+# Parameters below this size stay replicated: their gradients are all-reduced (coalesced into
+# one small collective) and every rank applies the same update to its own fp32 copy.
+MIN_OWNED_NUMEL = 1 << 16
+
+
+def owned_by_one_rank(p) -> bool:
+  """Whether parameter `p` gets a single owner rank under optimizer sharding. Only the large
+  matrices do: the forward pass reads those through their bf16 working copies, which the
+  owner refreshes on every rank. Norm scales, relative-position tables and other small fp32
+  parameters are read by the forward pass in fp32 on every rank, so every rank keeps and
+  updates its own copy of them."""
+  return (isinstance(p, torch.Tensor) and p.is_cuda and p.dtype == torch.float32 and
+          p.dim() >= 2 and p.numel() >= MIN_OWNED_NUMEL)
+
+
 def assign_owners(sizes: Mapping[str, int], world: int) -> Dict[str, int]:
   """Largest-first greedy balancing of parameter sizes over ranks; deterministic."""
   load = [0] * world
@@ -80,8 +95,7 @@ class ZeroContext:
     self.group = group if group is not None else (st.data_group or dist.group.WORLD)
     self.rank = dist.get_rank(self.group)
     self.world = dist.get_world_size(self.group)
-    names = [k for k, p in params_flat.items()
-             if isinstance(p, torch.Tensor) and p.is_cuda and p.dtype == torch.float32]
+    names = [k for k, p in params_flat.items() if owned_by_one_rank(p)]
     sizes = {k: int(params_flat[k].numel()) for k in names}
     self.owners = assign_owners(sizes, self.world)
     offset = 0

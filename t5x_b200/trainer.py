@@ -295,6 +295,9 @@ def reduce_partial_gradients_over_model_axis(grads_flat, params_flat) -> None:
     off += n
 
 
+_COALESCE_MAX_NUMEL = 1 << 18  # gradients up to this size travel in one flattened all-reduce
+
+
 def reduce_gradients_over_data_axis(grads_flat: Mapping[str, torch.Tensor], params_flat) -> None:
   """Sum of gradients over data-parallel replicas (losses are sums, not means, so the global
   gradient is the sum; t5x/trainer.py:815-828). Expert-sharded parameters are reduced over
@@ -303,12 +306,25 @@ def reduce_gradients_over_data_axis(grads_flat: Mapping[str, torch.Tensor], para
   if st.world_size == 1:
     return
   if st.data_size * st.expert_size > 1 and st.data_group is not None:
+    small, small_numel = [], 0
     for k, g in grads_flat.items():
       if getattr(params_flat[k], "expert_sharded", False):
         continue
       if getattr(params_flat[k], "zero", None) is not None:
         continue  # summed by its owner inside the optimizer kernels
-      dist.all_reduce(g, group=st.data_group)
+      if g.dtype == torch.float32 and g.numel() <= _COALESCE_MAX_NUMEL:
+        small.append(g)
+        small_numel += g.numel()
+      else:
+        dist.all_reduce(g, group=st.data_group)
+    if small:
+      # norm scales, bias tables and the like: one collective for all of them
+      flat = torch.cat([g.reshape(-1) for g in small])
+      dist.all_reduce(flat, group=st.data_group)
+      off = 0
+      for g in small:
+        g.copy_(flat[off:off + g.numel()].view_as(g))
+        off += g.numel()
   from t5x_b200.parallel import zero
   ctx = zero.active()
   if ctx is not None:
