@@ -224,6 +224,12 @@ def measure_train(args, parallelism: str, steps: int, warmup: int, with_e2e: boo
   else:
     trainer = trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, n_micro)
   n_params = sum(int(np.prod(getattr(p, "global_shape", p.shape))) for p in module.parameters())
+  from t5x_b200.parallel import zero as zero_lib
+  zctx = zero_lib.active()
+  exchange = None
+  if zctx is not None:
+    exchange = ("NVSwitch multimem (in-switch gradient sum, multicast weight push)"
+                if zctx.nvls else "peer loads / stores over NVLink")
 
   # Tensor-parallel ranks all consume the global batch; data-parallel ranks each take a shard.
   lengths = {"inputs": args.inputs_length, "targets": args.targets_length}
@@ -330,6 +336,7 @@ def measure_train(args, parallelism: str, steps: int, warmup: int, with_e2e: boo
                  "global_batch": args.batch, "seq_len": args.inputs_length + args.targets_length,
                  "inputs_length": args.inputs_length, "targets_length": args.targets_length,
                  "parallelism": layout, "optimizer": "adafactor", "num_microbatches": n_micro,
+                 "gradient_exchange": exchange,
                  "l2": "no explicit flush: every step streams the full weights, gradients and "
                        "activations (tens of GB), far larger than the 126 MB L2",
                  "baseline_note": "vs_baseline divides by the reference's published A100 figure "

@@ -128,9 +128,74 @@ __global__ void __launch_bounds__(kCeThreads)
   }
 }
 
+// Merges the per-tile partials of the fused projection + cross-entropy forward
+// (t5x_gemm_ce_stats) into the per-row statistics t5x_ce_stats produces: one warp per row.
+__global__ void __launch_bounds__(256)
+    ce_merge_kernel(const float4* __restrict__ part, const int* __restrict__ arg,
+                    const float* __restrict__ target_logit, const long long* __restrict__ targets,
+                    float4* __restrict__ stats, float* __restrict__ arg_val,
+                    int* __restrict__ arg_idx, int rows, int tiles, int vocab_start,
+                    int vocab_local) {
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float mx = -3.0e38f, se = 0.f, sx = 0.f, best = -3.0e38f;
+  int best_idx = 0x7fffffff;
+  for (int t = lane; t < tiles; t += 32) {
+    const float4 v = part[static_cast<long long>(row) * tiles + t];
+    const float nm = fmaxf(mx, v.x);
+    se = se * __expf(mx - nm) + v.y * __expf(v.x - nm);
+    mx = nm;
+    sx += v.z;
+    const int idx = arg[static_cast<long long>(row) * tiles + t];
+    if (v.w > best || (v.w == best && idx < best_idx)) {
+      best = v.w;
+      best_idx = idx;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+    const float os = __shfl_xor_sync(0xffffffffu, se, o);
+    const float nm = fmaxf(mx, om);
+    se = se * __expf(mx - nm) + os * __expf(om - nm);
+    mx = nm;
+    sx += __shfl_xor_sync(0xffffffffu, sx, o);
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
+    if (ob > best || (ob == best && oi < best_idx)) {
+      best = ob;
+      best_idx = oi;
+    }
+  }
+  if (lane == 0) {
+    const long long t = targets[row] - vocab_start;
+    const float tl = (t >= 0 && t < vocab_local) ? target_logit[row] : 0.f;
+    stats[row] = make_float4(mx, se, tl, sx);
+    arg_val[row] = best;
+    arg_idx[row] = best_idx;
+  }
+}
+
 }  // namespace t5x
 
 using namespace t5x;
+
+// stats[rows] = (max, sum exp(x - max), target logit, sum x), arg_val / arg_idx = largest logit
+// and its vocabulary id, from the partials of t5x_gemm_ce_stats.
+T5X_API int t5x_ce_merge(const void* part, const void* arg, const void* target_logit,
+                         const void* targets, void* stats, void* arg_val, void* arg_idx, int rows,
+                         int tiles, int vocab_start, int vocab_local, void* stream) {
+  if (rows <= 0) return 0;
+  ce_merge_kernel<<<(rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float4*>(part), static_cast<const int*>(arg),
+      static_cast<const float*>(target_logit), static_cast<const long long*>(targets),
+      static_cast<float4*>(stats), static_cast<float*>(arg_val), static_cast<int*>(arg_idx), rows,
+      tiles, vocab_start, vocab_local);
+  count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("ce_merge: %s", cudaGetErrorString(e));
+  return 0;
+}
 
 T5X_API int t5x_ce_stats(const void* logits, int logits_fp32, const void* targets, void* stats,
                          void* arg_val, void* arg_idx, int rows, int vocab_local, long long ld,

@@ -10,7 +10,14 @@ constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
 constexpr int kKernelIdGemm = 1;
 
-enum GemmEpilogue : int { kEpiPlain = 0, kEpiGatedGelu = 1, kEpiResidual = 2 };
+enum GemmEpilogue : int {
+  kEpiPlain = 0,
+  kEpiGatedGelu = 1,
+  kEpiResidual = 2,
+  // The product is a logits matrix that is consumed in the epilogue and never stored:
+  kEpiCeStats = 3,  // per (row, column tile) softmax partials for the cross-entropy forward
+  kEpiCeGrad = 4,   // gradient of the cross-entropy w.r.t. the logits, written as bf16
+};
 
 struct GemmParams {
   int M, N, K, batch;
@@ -27,6 +34,15 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int mt_rot;  // the row-tile walk starts at this tile (tensor-parallel kernels); 0 otherwise
   int* status;
+  // Cross-entropy epilogues. Column c of the product is vocabulary entry ce_vocab_start + c.
+  const long long* ce_targets;  // [M] target ids
+  int ce_vocab_start;
+  float* ce_part;          // kEpiCeStats: [M, tiles_n, 4] = max, sum exp(x - max), sum x, largest x
+  int* ce_arg;             // kEpiCeStats: [M, tiles_n] column of the largest x
+  float* ce_target_logit;  // kEpiCeStats: [M], written by the tile that holds the target
+  const float* ce_lse;     // kEpiCeGrad: [M] log-sum-exp of the row over the whole vocabulary
+  const float* ce_row_scale;  // kEpiCeGrad: [M] upstream gradient of the row's loss
+  float ce_z, ce_conf, ce_low;  // z-loss factor, label-smoothing confidences
 };
 
 // Tensor-parallel extensions of the CTA-pair GEMM. The rows of A (all-gather) or of C
@@ -242,6 +258,88 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
         }
       }
     }
+  }
+}
+
+// Cross-entropy forward epilogue of one accumulator tile: the calling thread owns one row of
+// logits x = alpha * acc and folds the tile's BN columns into (max, sum exp(x - max), sum x,
+// largest x and its column), which a small kernel merges over the column tiles afterwards.
+// The logits themselves are never stored.
+template <int BN>
+__device__ __forceinline__ void gemm_epilogue_ce_stats(const GemmParams& p, uint32_t t_row, int m0,
+                                                       int n0, int nt, int q, int lane) {
+  const int row = m0 + q * 32 + lane;
+  const bool row_ok = row < p.M;
+  const long long tgt = row_ok ? p.ce_targets[row] - p.ce_vocab_start : -1;
+  float mx = -3.0e38f, se = 0.f, sx = 0.f, best = -3.0e38f;
+  int best_col = 0;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(t_row + c * 32, r);
+    tmem_ld_wait();
+    const int col = n0 + c * 32;
+    const int n_valid = p.N - col;
+    if (!row_ok || n_valid <= 0) continue;
+    float v[32];
+    float cm = -3.0e38f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      v[i] = __uint_as_float(r[i]) * p.alpha;
+      if (i < n_valid) {
+        cm = fmaxf(cm, v[i]);
+        sx += v[i];
+        if (v[i] > best) {
+          best = v[i];
+          best_col = col + i;
+        }
+        if (col + i == tgt) p.ce_target_logit[row] = v[i];
+      }
+    }
+    const float nm = fmaxf(mx, cm);
+    float add = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < n_valid) add += __expf(v[i] - nm);
+    se = se * __expf(mx - nm) + add;
+    mx = nm;
+  }
+  if (row_ok) {
+    float4* out = reinterpret_cast<float4*>(p.ce_part) + static_cast<long long>(row) * p.tiles_n + nt;
+    *out = make_float4(mx, se, sx, best);
+    p.ce_arg[static_cast<long long>(row) * p.tiles_n + nt] = best_col + p.ce_vocab_start;
+  }
+}
+
+// Cross-entropy backward epilogue: the logits tile is recomputed by the GEMM and turned into
+//   dlogits = row_scale * ((1 + 2 z lse) * exp(x - lse) - soft_target)        (bf16)
+// which the two gradient GEMMs of the projection read next. C is the bf16 [M, N] output.
+template <int BN>
+__device__ __forceinline__ void gemm_epilogue_ce_grad(const GemmParams& p, uint32_t t_row, int m0,
+                                                      int n0, int q, int lane, bool c_vec_ok) {
+  const int row = m0 + q * 32 + lane;
+  const bool row_ok = row < p.M;
+  const float lse = row_ok ? p.ce_lse[row] : 0.f;
+  const float g = row_ok ? p.ce_row_scale[row] : 0.f;
+  const float zf = 1.f + 2.f * p.ce_z * lse;
+  const long long tgt = row_ok ? p.ce_targets[row] - p.ce_vocab_start : -1;
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(t_row + c * 32, r);
+    tmem_ld_wait();
+    const int col = n0 + c * 32;
+    const int n_valid = p.N - col;
+    if (!row_ok || n_valid <= 0) continue;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float x = __uint_as_float(r[i]) * p.alpha;
+      const float soft = (col + i == tgt) ? p.ce_conf : p.ce_low;
+      v[i] = g == 0.f ? 0.f : g * (zf * __expf(x - lse) - soft);
+    }
+    store_row_bf16(out + col, v, n_valid, c_vec_ok);
   }
 }
 

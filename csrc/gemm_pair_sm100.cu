@@ -376,6 +376,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
       if (MODE == kTpReduceScatter)
         gemm_epilogue_tile_rs<BN, EPI>(p, tp, t_row, m0, n0, q, lane,
                                        staging + (warp - 2) * kRsStageBytesPerWarp);
+      else if (EPI == kEpiCeStats)
+        gemm_epilogue_ce_stats<BN>(p, t_row, m0, n0, nt, q, lane);
+      else if (EPI == kEpiCeGrad)
+        gemm_epilogue_ce_grad<BN>(p, t_row, m0, n0, q, lane, c_vec_ok);
       else
         gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok);
       tc_fence_before();
@@ -459,6 +463,12 @@ static int launch_pair_mode(int epilogue, const CUtensorMap* tA, const CUtensorM
       if (MODE == kTpAllGather) break;
       return launch_pair<kEpiResidual, MODE == kTpAllGather ? kTpNone : MODE>(
           tA, tB, tB2, p, tp, max_ctas, stream);
+    case kEpiCeStats:
+      if (MODE != kTpNone) break;
+      return launch_pair<kEpiCeStats, kTpNone>(tA, tB, tB2, p, tp, max_ctas, stream);
+    case kEpiCeGrad:
+      if (MODE != kTpNone) break;
+      return launch_pair<kEpiCeGrad, kTpNone>(tA, tB, tB2, p, tp, max_ctas, stream);
     default:
       break;
   }

@@ -216,7 +216,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok);
+      if (EPI == kEpiCeStats)
+        gemm_epilogue_ce_stats<BN>(p, t_row, m0, n0, nt, q, lane);
+      else if (EPI == kEpiCeGrad)
+        gemm_epilogue_ce_grad<BN>(p, t_row, m0, n0, q, lane, c_vec_ok);
+      else
+        gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
@@ -320,6 +325,19 @@ T5X_API int t5x_gemm_set_pair_mode(int mode) {
 }
 
 namespace t5x {
+// What the cross-entropy epilogues need besides the GEMM itself.
+struct GemmCe {
+  const long long* targets;
+  int vocab_start;
+  float* part;
+  int* arg;
+  float* target_logit;
+  const float* lse;
+  const float* row_scale;
+  float z, conf, low;
+};
+static thread_local const GemmCe* g_ce_extras = nullptr;  // set by the two entry points around gemm_impl
+
 static int gemm_impl(const void* A, const void* B, const void* B2, void* C, int M, int N,
                      int K, int batch, long long lda, long long ldb, long long ldc,
                      long long a_batch_stride, long long b_batch_stride,
@@ -354,6 +372,13 @@ static int gemm_impl(const void* A, const void* B, const void* B2, void* C, int 
   p.status = device_status_buffer();
   p.tiles_m = (M + kBM - 1) / kBM;
   p.mt_rot = 0;
+  p.ce_targets = nullptr;
+  p.ce_part = nullptr;
+  p.ce_arg = nullptr;
+  p.ce_target_logit = nullptr;
+  p.ce_lse = p.ce_row_scale = nullptr;
+  p.ce_vocab_start = 0;
+  p.ce_z = p.ce_conf = p.ce_low = 0.f;
 
   const CUtensorMap* tA = operand_map(A, a_mn_major, M, K, lda, a_batch_stride, batch, 128);
   const CUtensorMap* tB = operand_map(B, b_mn_major, N, K, ldb, b_batch_stride, batch, 128);
@@ -388,6 +413,27 @@ static int gemm_impl(const void* A, const void* B, const void* B2, void* C, int 
     return launch_gemm_pair(epilogue, tA, tB, tB2, p, max_ctas, st, tp, tp_mode);
   }
 
+  if (epilogue == kEpiCeStats || epilogue == kEpiCeGrad) {
+    const GemmCe* ce = g_ce_extras;
+    if (ce == nullptr || batch != 1) return set_error("cross-entropy epilogue: bad call");
+    p.ce_targets = ce->targets;
+    p.ce_vocab_start = ce->vocab_start;
+    p.ce_part = ce->part;
+    p.ce_arg = ce->arg;
+    p.ce_target_logit = ce->target_logit;
+    p.ce_lse = ce->lse;
+    p.ce_row_scale = ce->row_scale;
+    p.ce_z = ce->z;
+    p.ce_conf = ce->conf;
+    p.ce_low = ce->low;
+    p.tiles_n = (N + 255) / 256;
+    if (pair_mode != 0 && M >= 2 * kBM) {
+      p.tiles_m = pair_tiles_m;
+      return launch_gemm_pair(epilogue, tA, tB, tB, p, max_ctas, st);
+    }
+    return epilogue == kEpiCeStats ? launch_gemm<256, kEpiCeStats>(tA, tB, tB, p, max_ctas, st)
+                                   : launch_gemm<256, kEpiCeGrad>(tA, tB, tB, p, max_ctas, st);
+  }
   if (epilogue == kEpiGatedGelu) {
     if (out_fp32 || accumulate) return set_error("gated-GELU epilogue writes bf16 without accumulate");
     const CUtensorMap* tB2 = operand_map(B2, b_mn_major, N, K, ldb, b_batch_stride, batch, 128);
@@ -525,4 +571,61 @@ T5X_API int t5x_gemm_reducescatter_bf16(const void* A, const void* B, void* cons
   return gemm_impl(A, B, nullptr, nullptr, M, N, K, 1, lda, ldb, ldc, 0, 0, 0, a_mn_major,
                    b_mn_major, 0, 0, R ? kEpiResidual : kEpiPlain, R, ldr, 0, nullptr, nullptr, 0,
                    1.f, 0, stream, &tp, kTpReduceScatter);
+}
+
+// ---- logits projection fused with the cross-entropy: the [M, N] logits are never stored ----
+// Number of column tiles (partials per row) the forward produces for a vocabulary slice of N.
+T5X_API int t5x_gemm_ce_tiles(int N) { return (N + 255) / 256; }
+
+// Forward: logits = alpha * A[M, K] @ B[K, N] are folded, tile by tile in the GEMM epilogue,
+// into part[M, tiles, 4] (max, sum exp(x - max), sum x, largest x), arg[M, tiles] (vocabulary
+// id of the largest x) and target_logit[M] (written only if the row's target lies in
+// [vocab_start, vocab_start + N)). t5x_ce_merge turns the partials into per-row statistics.
+T5X_API int t5x_gemm_ce_stats(const void* A, const void* B, int M, int N, int K, long long lda,
+                              long long ldb, int a_mn_major, int b_mn_major, float alpha,
+                              const void* targets, int vocab_start, void* part, void* arg,
+                              void* target_logit, void* stream) {
+  using namespace t5x;
+  if (M <= 0 || N <= 0) return 0;
+  if (targets == nullptr || part == nullptr || arg == nullptr || target_logit == nullptr)
+    return set_error("gemm_ce_stats: null pointer");
+  GemmCe ce = {};
+  ce.targets = static_cast<const long long*>(targets);
+  ce.vocab_start = vocab_start;
+  ce.part = static_cast<float*>(part);
+  ce.arg = static_cast<int*>(arg);
+  ce.target_logit = static_cast<float*>(target_logit);
+  g_ce_extras = &ce;
+  const int rc = gemm_impl(A, B, nullptr, nullptr, M, N, K, 1, lda, ldb, 0, 0, 0, 0, a_mn_major,
+                           b_mn_major, 0, 0, kEpiCeStats, nullptr, 0, 0, nullptr, nullptr, 0,
+                           alpha, 0, stream, nullptr, 0);
+  g_ce_extras = nullptr;
+  return rc;
+}
+
+// Backward: recomputes the logits tiles and writes dlogits[M, N] (bf16, row stride ldd) =
+// row_scale * ((1 + 2 z lse) * softmax - soft targets), with lse[M] over the whole vocabulary.
+T5X_API int t5x_gemm_ce_grad(const void* A, const void* B, void* dlogits, long long ldd, int M,
+                             int N, int K, long long lda, long long ldb, int a_mn_major,
+                             int b_mn_major, float alpha, const void* targets, int vocab_start,
+                             const void* lse, const void* row_scale, float z_loss,
+                             float confidence, float low_confidence, void* stream) {
+  using namespace t5x;
+  if (M <= 0 || N <= 0) return 0;
+  if (targets == nullptr || lse == nullptr || row_scale == nullptr || dlogits == nullptr)
+    return set_error("gemm_ce_grad: null pointer");
+  GemmCe ce = {};
+  ce.targets = static_cast<const long long*>(targets);
+  ce.vocab_start = vocab_start;
+  ce.lse = static_cast<const float*>(lse);
+  ce.row_scale = static_cast<const float*>(row_scale);
+  ce.z = z_loss;
+  ce.conf = confidence;
+  ce.low = low_confidence;
+  g_ce_extras = &ce;
+  const int rc = gemm_impl(A, B, nullptr, dlogits, M, N, K, 1, lda, ldb, ldd, 0, 0, 0, a_mn_major,
+                           b_mn_major, 0, 0, kEpiCeGrad, nullptr, 0, 0, nullptr, nullptr, 0,
+                           alpha, 0, stream, nullptr, 0);
+  g_ce_extras = nullptr;
+  return rc;
 }

@@ -471,9 +471,11 @@ def _library_attention(q, k, v, bias, key_mask, causal, q_seg, kv_seg, extra_mas
 # Cross entropy with z-loss on top of the logits projection
 # ----------------------------------------------------------------------------
 class _LogitsCrossEntropyFn(torch.autograd.Function):
-  """per-token (loss, z_loss, correct) = CE(hidden @ W) without keeping fp32 logits alive
-  beyond this function: logits are produced by the GEMM, reduced, and turned into bf16
-  dlogits in place of a second softmax pass in backward."""
+  """per-token (loss, z_loss, correct) = CE(hidden @ W) with the [tokens, vocab] logits never
+  written to memory: the projection GEMM folds each accumulator tile into softmax partials in
+  its epilogue (forward), and backward runs the projection again with an epilogue that turns
+  each tile straight into bf16 dlogits for the two gradient GEMMs. The per-row log-sum-exp is
+  all that is kept between the passes (`T5X_B200_FUSED_CE=0` restores materialised logits)."""
 
   @staticmethod
   def forward(ctx, hidden, weight, targets, z_loss, label_smoothing, logits_scale):
@@ -483,9 +485,14 @@ class _LogitsCrossEntropyFn(torch.autograd.Function):
     if w.shape[0] != k:  # tied embedding [V, d]: logits = h @ E^T
       w = w.t()
     vocab = w.shape[1]
-    logits = native.gemm(h2, w, out_dtype=torch.float32, alpha=logits_scale)
     t2 = targets.reshape(-1)
-    stats, _, arg_idx = native.ce_stats(logits, t2)
+    fused = _fused_ce_enabled()
+    if fused:
+      logits = None
+      stats, _, arg_idx = native.gemm_ce_stats(h2, w, t2, alpha=logits_scale)
+    else:
+      logits = native.gemm(h2, w, out_dtype=torch.float32, alpha=logits_scale)
+      stats, _, arg_idx = native.ce_stats(logits, t2)
     lse = stats[:, 0] + torch.log(stats[:, 1])
     conf, low, norm_const = ref.label_smoothing_constants(vocab, label_smoothing)
     tl = stats[:, 2]
@@ -493,14 +500,19 @@ class _LogitsCrossEntropyFn(torch.autograd.Function):
     z = z_loss * lse * lse
     loss = lse - soft_dot + z - norm_const
     correct = (arg_idx.long() == t2)
-    ctx.save_for_backward(hidden, weight, t2, lse, logits)
+    if fused:
+      ctx.save_for_backward(hidden, weight, t2, lse)
+    else:
+      ctx.save_for_backward(hidden, weight, t2, lse, logits)
     ctx.cfg = (z_loss, conf, low, logits_scale)
     ctx.mark_non_differentiable(correct)
     return loss.view(targets.shape), z.view(targets.shape), correct.view(targets.shape)
 
   @staticmethod
   def backward(ctx, dloss, dz, _dcorrect):
-    hidden, weight, t2, lse, logits = ctx.saved_tensors
+    saved = ctx.saved_tensors
+    hidden, weight, t2, lse = saved[:4]
+    logits = saved[4] if len(saved) > 4 else None
     z_loss, conf, low, logits_scale = ctx.cfg
     k = hidden.shape[-1]
     h2 = hidden.reshape(-1, k)
@@ -511,7 +523,11 @@ class _LogitsCrossEntropyFn(torch.autograd.Function):
     # `loss` already contains the z term; a gradient arriving through the separate z output
     # (metrics only) is ignored, as in the reference's custom VJP (t5x/losses.py:98-124).
     row_scale = (dloss.reshape(-1).float() * logits_scale).contiguous()
-    dlogits = native.ce_grad(logits, t2, lse, row_scale, z_loss, conf, low)
+    if logits is None:
+      dlogits = native.gemm_ce_grad(h2, w, t2, lse.contiguous(), row_scale, z_loss, conf, low,
+                                    alpha=logits_scale)
+    else:
+      dlogits = native.ce_grad(logits, t2, lse, row_scale, z_loss, conf, low)
     dh = native.gemm(dlogits, w.t()).view(hidden.shape) if ctx.needs_input_grad[0] else None
     dw = None
     if ctx.needs_input_grad[1]:
@@ -526,6 +542,11 @@ class _LogitsCrossEntropyFn(torch.autograd.Function):
       else:
         dw = _accumulate_wgrad(weight, h2.t(), dlogits)
     return dh, dw, None, None, None, None
+
+
+def _fused_ce_enabled() -> bool:
+  import os
+  return os.environ.get("T5X_B200_FUSED_CE", "1") != "0"
 
 
 def logits_cross_entropy(hidden, weight, targets, *, z_loss: float = 0.0,

@@ -457,6 +457,73 @@ def ce_grad(logits, targets, lse, row_scale, z_loss, confidence, low_confidence,
   return out
 
 
+register_signature("t5x_gemm_ce_tiles", [c_int])
+register_signature("t5x_gemm_ce_stats", [c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_int,
+                                         c_int, c_float, c_void_p, c_int, c_void_p, c_void_p,
+                                         c_void_p, c_void_p])
+register_signature("t5x_gemm_ce_grad", [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int,
+                                        c_ll, c_ll, c_int, c_int, c_float, c_void_p, c_int,
+                                        c_void_p, c_void_p, c_float, c_float, c_float, c_void_p])
+register_signature("t5x_ce_merge", [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_void_p])
+
+
+def _b_layout(b: torch.Tensor):
+  """(mn_major, ld) of b as the [K, N] operand of the GEMM kernels."""
+  if b.stride(-2) == 1:
+    return 0, b.stride(-1)
+  if b.stride(-1) == 1:
+    return 1, b.stride(-2)
+  raise NativeError(f"b with strides {b.stride()} is neither row- nor column-major")
+
+
+def gemm_ce_stats(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, alpha: float = 1.0,
+                  vocab_start: int = 0):
+  """Cross-entropy statistics of logits = alpha * h[M, K] @ w[K, N] without storing the
+  logits: the GEMM epilogue folds every 256-column tile into softmax partials, which a second
+  small kernel merges. Returns what `ce_stats` returns: stats [M, 4] = (max, sum exp(x - max),
+  target logit, sum x), arg_val [M], arg_idx [M] (vocabulary id of the largest logit)."""
+  assert h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and targets.dtype == torch.int64
+  M, K = h.shape
+  N = w.shape[1]
+  a_mn, lda, _ = _mat_layout(h, M, K)
+  b_mn, ldb = _b_layout(w)
+  tiles = int(lib().t5x_gemm_ce_tiles(N))
+  dev = h.device
+  part = torch.empty((M, tiles, 4), dtype=torch.float32, device=dev)
+  arg = torch.empty((M, tiles), dtype=torch.int32, device=dev)
+  tlogit = torch.zeros(M, dtype=torch.float32, device=dev)
+  t = targets.contiguous()
+  _check(lib().t5x_gemm_ce_stats(h.data_ptr(), w.data_ptr(), M, N, K, lda, ldb, a_mn, b_mn,
+                                 float(alpha), t.data_ptr(), vocab_start, part.data_ptr(),
+                                 arg.data_ptr(), tlogit.data_ptr(), stream_ptr()), "gemm_ce_stats")
+  stats = torch.empty((M, 4), dtype=torch.float32, device=dev)
+  arg_val = torch.empty(M, dtype=torch.float32, device=dev)
+  arg_idx = torch.empty(M, dtype=torch.int32, device=dev)
+  _check(lib().t5x_ce_merge(part.data_ptr(), arg.data_ptr(), tlogit.data_ptr(), t.data_ptr(),
+                            stats.data_ptr(), arg_val.data_ptr(), arg_idx.data_ptr(), M, tiles,
+                            vocab_start, N, stream_ptr()), "ce_merge")
+  return stats, arg_val, arg_idx
+
+
+def gemm_ce_grad(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor,
+                 row_scale: torch.Tensor, z_loss: float, confidence: float,
+                 low_confidence: float, alpha: float = 1.0, vocab_start: int = 0) -> torch.Tensor:
+  """dlogits [M, N] (bf16) of the cross-entropy over logits = alpha * h @ w, with the logits
+  recomputed tile by tile inside the GEMM instead of read from memory."""
+  M, K = h.shape
+  N = w.shape[1]
+  a_mn, lda, _ = _mat_layout(h, M, K)
+  b_mn, ldb = _b_layout(w)
+  out = torch.empty((M, N), dtype=torch.bfloat16, device=h.device)
+  _check(lib().t5x_gemm_ce_grad(h.data_ptr(), w.data_ptr(), out.data_ptr(), out.stride(0), M, N,
+                                K, lda, ldb, a_mn, b_mn, float(alpha),
+                                targets.contiguous().data_ptr(), vocab_start,
+                                lse.contiguous().data_ptr(), row_scale.contiguous().data_ptr(),
+                                float(z_loss), float(confidence), float(low_confidence),
+                                stream_ptr()), "gemm_ce_grad")
+  return out
+
+
 # ----------------------------------------------------------------------------
 # Adafactor
 # ----------------------------------------------------------------------------

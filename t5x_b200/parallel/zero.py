@@ -54,15 +54,15 @@ class ZeroInfo:
 
   def grad_mc(self) -> int:
     """Multicast address of this parameter's gradient over all replicas (0 without NVLS)."""
-    return self.ctx.grads.mc_ptr_at(self.offset)
+    return self.ctx.grads.mc_ptr_at(self.offset) if self.ctx.nvls else 0
 
   def bf16_mc(self) -> int:
-    return self.ctx.weights.mc_ptr_at(self.offset)
+    return self.ctx.weights.mc_ptr_at(self.offset) if self.ctx.nvls else 0
 
 
 # Parameters below this size stay replicated: their gradients are all-reduced (coalesced into
 # one small collective) and every rank applies the same update to its own fp32 copy.
-MIN_OWNED_NUMEL = 1 << 16
+MIN_OWNED_NUMEL = 1 << 14
 
 
 def owned_by_one_rank(p) -> bool:
@@ -122,8 +122,11 @@ class ZeroContext:
     torch.cuda.synchronize(device)
     dist.barrier(group=self.group)
     owned = sum(sizes[k] for k in names if self.owners[k] == self.rank)
-    logging.info("optimizer sharding: rank %d/%d owns %.1f M of %.1f M parameters", self.rank,
-                 self.world, owned / 1e6, sum(sizes.values()) / 1e6)
+    # in-switch gradient sum / multicast weight push (T5X_B200_NVLS=1 and a fabric that has it)
+    self.nvls = bool(self.grads.multicast_ptr and self.weights.multicast_ptr)
+    logging.info("optimizer sharding: rank %d/%d owns %.1f M of %.1f M parameters%s", self.rank,
+                 self.world, owned / 1e6, sum(sizes.values()) / 1e6,
+                 ", exchange through NVSwitch multimem" if self.nvls else "")
 
   # -- overlap with backward ----------------------------------------------------------------
   # During the last microbatch of a step, the parameters of a transformer layer are final as

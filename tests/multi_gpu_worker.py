@@ -103,6 +103,7 @@ def case_train(out):
   bf = torch.cat([p.bf16.float().reshape(-1) for p in module.parameters()])
   ctx = zero.active()
   json.dump({"loss": float(summary["loss"].value), "sharded": ctx is not None,
+             "nvls": bool(getattr(ctx, "nvls", False)),
              "overlapped": len(getattr(ctx, "done_this_step", ())),
              "param_sum": float(flat.double().sum()), "param_abs": float(flat.double().abs().sum()),
              "bf16_abs": float(bf.double().abs().sum()),

@@ -60,6 +60,25 @@ def test_sharded_optimizer_matches_all_reduce(tmp_path):
     assert x == pytest.approx(y, rel=1e-2, abs=1e-4)
 
 
+def test_sharded_optimizer_through_the_switch_matches_peer_loads(tmp_path):
+  """The same three steps with the gradient sum taken by the NVSwitch (`multimem.ld_reduce`)
+  and the weights pushed by one multicast store, against the peer-load form. Skipped where the
+  fabric offers no multicast."""
+  _need_two()
+  switch = _run_ranks("train", tmp_path / "s", env={"T5X_B200_NVLS": "1"})
+  if not all(r["nvls"] for r in switch):
+    pytest.skip("no NVSwitch multicast on this box")
+  plain = _run_ranks("train", tmp_path / "p")
+  assert not any(r["nvls"] for r in plain)
+  assert abs(switch[0]["param_sum"] - switch[1]["param_sum"]) <= 1e-6 * switch[0]["param_abs"]
+  a, b = switch[0], plain[0]
+  assert a["loss"] == pytest.approx(b["loss"], rel=2e-3)
+  assert a["param_abs"] == pytest.approx(b["param_abs"], rel=1e-4)
+  assert a["bf16_abs"] == pytest.approx(a["param_abs"], rel=5e-3)
+  for x, y in zip(a["first"], b["first"]):
+    assert x == pytest.approx(y, rel=1e-2, abs=1e-4)
+
+
 def test_barrier_gives_up_when_a_peer_never_arrives():
   from t5x_b200.ops import comm, native
   pad = torch.zeros(256, dtype=torch.int32, device="cuda")
