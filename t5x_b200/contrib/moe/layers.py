@@ -183,6 +183,49 @@ class TokensChooseRouter(nn.Module):
             "flat_slot": _flat_slots(index, slot, capacity)}, metrics
 
 
+class ExpertsChooseRouter(nn.Module):
+  """Every expert picks its `capacity` highest-probability tokens ("experts choose" routing of
+  the Flaxformer MoE layers the reference builds on). Experts are always full, so there is no
+  load-balancing loss; a token may be processed by several experts or by none. The routing is
+  reported in the same form as `TokensChooseRouter` with one "choice" column per expert:
+  flat_slot[t, e] is the row of (expert e, position) in the dispatch buffer, or -1 when expert
+  e did not pick token t, and gate[t, e] the router probability of the picks."""
+
+  def __init__(self, emb_dim: int, num_experts: int, jitter_noise: float = 0.0, device=None):
+    super().__init__()
+    self.num_experts = num_experts
+    self.jitter_noise = jitter_noise
+    self.router_weights = RouterWeights(emb_dim, num_experts, device=device)
+
+  def forward(self, tokens: torch.Tensor, capacity: int, enable_dropout: bool = False):
+    x = tokens.float()
+    if enable_dropout and self.jitter_noise > 0:
+      x = x * torch.empty_like(x).uniform_(1.0 - self.jitter_noise, 1.0 + self.jitter_noise)
+    logits = x @ self.router_weights.w.kernel.float()
+    probs = torch.softmax(logits, dim=-1)                            # [T, E]
+    t, e = probs.shape
+    picks = min(capacity, t)
+    top_p, top_tok = torch.topk(probs.t(), picks, dim=1)             # [E, picks]
+    rows = (torch.arange(e, device=probs.device)[:, None] * capacity +
+            torch.arange(picks, device=probs.device)[None, :])       # slot row of (e, position)
+    cols = torch.arange(e, device=probs.device)[:, None].expand(e, picks)
+    flat_slot = torch.full((t, e), -1, dtype=torch.long, device=probs.device)
+    flat_slot[top_tok, cols] = rows
+    gate = torch.zeros_like(probs)
+    gate[top_tok, cols] = top_p
+    chosen = flat_slot >= 0
+    dispatched_somewhere = chosen.any(dim=1).float().sum()
+    metrics = {
+        "auxiliary_loss": torch.zeros((), dtype=torch.float32, device=probs.device),
+        "router_z_loss": router_z_loss(logits),
+        "fraction_tokens_left_behind": 1.0 - dispatched_somewhere / float(t),
+        "expert_usage": torch.as_tensor(float(picks) / float(capacity), device=probs.device),
+        "router_confidence": gate.sum() / dispatched_somewhere.clamp(min=1.0),
+    }
+    index = torch.arange(e, device=probs.device)[None, :].expand(t, e)
+    return {"expert_index": index, "flat_slot": flat_slot, "gate": gate}, metrics
+
+
 # ----------------------------------------------------------------------------
 # Dispatch / combine
 # ----------------------------------------------------------------------------
@@ -342,17 +385,24 @@ class MoeLayer(nn.Module):
                activations: Sequence[str] = ("gelu", "linear"), num_selected_experts: int = 1,
                capacity_factor: float = 1.25, eval_capacity_factor: Optional[float] = None,
                min_expert_capacity: int = 4, dropout_rate: float = 0.0, jitter_noise: float = 0.0,
-               dtype=torch.float32, device=None):
+               dtype=torch.float32, device=None, router_type: str = "tokens_choose"):
     super().__init__()
     self.num_experts = num_experts
     self.k = num_selected_experts
+    self.router_type = router_type
     self.capacity_factor = capacity_factor
     self.eval_capacity_factor = eval_capacity_factor or capacity_factor
     self.min_expert_capacity = min_expert_capacity
     self.dropout_rate = dropout_rate
     self.dtype = t5_layers.canonical_dtype(dtype)
-    self.router = TokensChooseRouter(emb_dim, num_experts, num_selected_experts, jitter_noise,
-                                     device=device)
+    if router_type == "tokens_choose":
+      self.router = TokensChooseRouter(emb_dim, num_experts, num_selected_experts, jitter_noise,
+                                       device=device)
+    elif router_type == "experts_choose":
+      self.router = ExpertsChooseRouter(emb_dim, num_experts, jitter_noise, device=device)
+    else:
+      raise ValueError(f"router_type must be 'tokens_choose' or 'experts_choose', got "
+                       f"{router_type!r}")
     self.expert = Experts(num_experts, emb_dim, mlp_dim, activations, dtype, device=device)
 
   def forward(self, inputs: torch.Tensor, residual: Optional[torch.Tensor] = None,

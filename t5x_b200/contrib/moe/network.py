@@ -26,6 +26,7 @@ class MoeT5Config(t5_network.T5Config):
   router_jitter_noise: float = 0.0
   sparse_layout: Union[str, Tuple[int, ...]] = "every_other"
   expert_mlp_dim: int = 0  # 0: same as mlp_dim
+  router_type: str = "tokens_choose"  # or "experts_choose"
 
 
 def is_sparse_layer(config: MoeT5Config, index: int) -> bool:
@@ -44,7 +45,8 @@ def _moe(config: MoeT5Config, device):
   return moe_layers.MoeLayer(
       c.emb_dim, c.expert_mlp_dim or c.mlp_dim, c.num_experts, c.mlp_activations,
       c.num_selected_experts, c.train_capacity_factor, c.eval_capacity_factor,
-      c.min_expert_capacity, c.dropout_rate, c.router_jitter_noise, c.dtype, device=device)
+      c.min_expert_capacity, c.dropout_rate, c.router_jitter_noise, c.dtype, device=device,
+      router_type=c.router_type)
 
 
 class Transformer(t5_network.Transformer):

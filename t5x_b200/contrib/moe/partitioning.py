@@ -128,8 +128,94 @@ class MoePjitPartitioner(base_partitioning.PjitPartitioner):
                                           self._world_size, self._local_rank)
     return self._mesh_cache
 
+  def get_data_layout(self, batch_size: Optional[int] = None,
+                      host_index: Optional[int] = None) -> base_partitioning.DataLayout:
+    """Data layout with both 'expert' and 'data' acting as data axes: shards are numbered
+    expert-major (shard id = data chunk + expert chunk * data chunks), and a process reads data
+    when it is the first replica of its (expert, data) block
+    (t5x/contrib/moe/partitioning.py:205-262)."""
+    if host_index is not None:
+      raise NotImplementedError("Explicit host_index is not yet implemented.")
+    chunker = self._local_chunker
+    mesh_shape = chunker.global_mesh.shape
+    data_mesh_size = mesh_shape["data"] * mesh_shape["expert"]
+    batch_size = batch_size or data_mesh_size
+    if batch_size % data_mesh_size:
+      raise ValueError(
+          f"Batch size ({batch_size}) must be divisible by entire data mesh size "
+          f"({data_mesh_size}). Note that for MoE, the data mesh spans both the \"expert\" and "
+          "\"data\" virtual mesh axes.")
+    num_shards = chunker.num_chunks["data"] * chunker.num_chunks["expert"]
+    if batch_size % num_shards:
+      raise ValueError(f"Batch size ({batch_size}) must be divisible by total number of shards "
+                       f"({num_shards}) across \"data\" and \"expert\" mesh axes.")
+    block = chunker.get_local_chunk_info(
+        (mesh_shape["expert"], batch_size // mesh_shape["expert"]), ("expert", "data"))
+    return base_partitioning.DataLayout(
+        batch_size=int(batch_size),
+        shard_id=int(chunker.chunk_ids["data"] +
+                     chunker.chunk_ids["expert"] * chunker.num_chunks["data"]),
+        num_shards=int(num_shards), is_first_host_in_replica_set=(block.replica_id == 0))
+
+  def get_logical_axes(self, train_state):
+    """Logical axes of the train state with 'expert' prepended to the optimizer slots that
+    the state filter names. Factored Adafactor does not carry the parameter's axis names over
+    to its `v_row` / `v_col` vectors, so for expert kernels (stacked [experts, ...]) those
+    vectors would otherwise look replicated although they have one slice per expert
+    (t5x/contrib/moe/partitioning.py:264-317)."""
+    logical_axes = train_state.as_logical_axes()
+    if not hasattr(train_state, "_optimizer"):
+      return logical_axes  # inference state: no optimizer slots
+    state_filter_fn = self._state_filter_fn or _infer_state_filter_fn(train_state)
+    if state_filter_fn is None:
+      return logical_axes
+    from t5x_b200 import optimizers
+    from t5x_b200.utils import tree as tree_utils
+    axes_opt = logical_axes._optimizer  # pylint: disable=protected-access
+    slots = tree_utils.flatten_dict(axes_opt.state.param_states,
+                                    is_leaf=lambda x: not isinstance(x, dict))
+    for path, axes in slots.items():
+      name = path if isinstance(path, str) else "/".join(str(k) for k in path)
+      if state_filter_fn(name):
+        slots[path] = ("expert",) + tuple(axes) if axes else ("expert",)
+    new_state = optimizers.OptimizerState(step=axes_opt.state.step,
+                                          param_states=tree_utils.unflatten_dict(slots))
+    return logical_axes.replace(_optimizer=axes_opt.replace(state=new_state))
+
   def partition(self, fn, in_axis_resources, out_axis_resources, static_argnums=(),
                 donate_argnums=()):
     return super().partition(fn, override_partition_specs(in_axis_resources),
                              override_partition_specs(out_axis_resources), static_argnums,
                              donate_argnums)
+
+
+
+def _infer_state_filter_fn(train_state):
+  """Which optimizer slots are sharded along 'expert' without saying so in their axis names:
+  for factored Adafactor the `v_row` / `v_col` vectors of expert kernels; for unfactored
+  Adafactor and for wrapped optax optimizers the slots inherit the parameter's names and
+  nothing needs overriding (t5x/contrib/moe/partitioning.py:506-581)."""
+  from t5x_b200 import adafactor, optimizers
+  from t5x_b200.contrib.moe import training_utils
+  opt_def = train_state._optimizer.optimizer_def  # pylint: disable=protected-access
+  if isinstance(opt_def, optimizers.MultiOptimizer):
+    subs = list(opt_def.sub_optimizers)
+    if not subs:
+      return None
+    if any(type(o) is not type(subs[0]) for o in subs):
+      raise ValueError("optimizers.MultiOptimizer is only supported in cases where all "
+                       "suboptimizers are of the same type.")
+    if isinstance(subs[0], adafactor.Adafactor) and \
+        any(o.hyper_params.factored != subs[0].hyper_params.factored for o in subs):
+      raise ValueError("If using adafactor.Adafactor as the suboptimizer in "
+                       "optimizers.MultiOptimizer, all suboptimizers must be either factored or "
+                       "unfactored (cannot use mixed factoring).")
+    opt_def = subs[0]
+  if isinstance(opt_def, optimizers.OptaxWrapper):
+    return None
+  if not isinstance(opt_def, adafactor.Adafactor):
+    raise ValueError("Unrecognized optimizer type. Expecting optimizers.OptaxWrapper or "
+                     f"adafactor.Adafactor. Received: {opt_def}")
+  if opt_def.hyper_params.factored:
+    return training_utils.match_fn(r".*expert.*/kernel/v_.*")
+  return None

@@ -220,3 +220,73 @@ def test_sparse_upcycling_broadcasts_dense_mlp(tmp_path):
   torch.testing.assert_close(
       restored.params["encoder"]["layers_0"]["mlp"]["wi_0"]["kernel"].detach(),
       dense.encoder.layers_0.mlp.wi_0.kernel.detach())
+
+
+def _moe_train_state(factored=True):
+  from t5x_b200 import adafactor, train_state as ts_lib
+  from t5x_b200.contrib.moe import adafactor_utils, models as moe_models, network as moe_network
+  from t5x_b200.data import vocabularies
+  cfg = moe_network.MoeT5Config(vocab_size=64, dtype="float32", emb_dim=128, num_heads=2,
+                                head_dim=16, mlp_dim=256, num_encoder_layers=2,
+                                num_decoder_layers=2, dropout_rate=0.0,
+                                mlp_activations=("gelu", "linear"), num_experts=4,
+                                num_selected_experts=1)
+  module = moe_network.Transformer(cfg)
+  v = vocabularies.PassThroughVocabulary(64)
+  opt = adafactor.Adafactor(factored=factored,
+                            logical_factor_rules=adafactor_utils.logical_factor_rules())
+  model = moe_models.MoeEncoderDecoderModel(module, v, v, opt)
+  return ts_lib.FlaxOptimTrainState.create(opt, model.get_initial_variables(None, None))
+
+
+def test_moe_partitioner_marks_factored_expert_slots_and_lays_out_data():
+  """The (data, expert, model) partitioner: factored Adafactor's v_row / v_col of expert
+  kernels get the 'expert' axis (the reference's state filter), dense slots do not; data
+  shards are numbered expert-major over the two data-like axes."""
+  from t5x_b200.contrib.moe import partitioning as mp
+  from t5x_b200.utils import tree
+  state = _moe_train_state()
+  part = mp.MoePjitPartitioner(num_expert_partitions=2, num_partitions=1, world_size=4,
+                               local_rank=3)
+  axes = tree.flatten_dict(part.get_mesh_axes(state).state_dict(),
+                           is_leaf=lambda x: not isinstance(x, dict))
+  expert_slot = "state/param_states/encoder/layers_1/mlp/expert/wi_0/kernel/"
+  dense_slot = "state/param_states/encoder/layers_0/mlp/wi_0/kernel/"
+  assert axes[expert_slot + "v_row"] == mp.PartitionSpec("expert",)
+  assert axes[expert_slot + "v_col"] == mp.PartitionSpec("expert",)
+  assert axes[dense_slot + "v_row"] is None
+  assert axes["target/encoder/layers_1/mlp/expert/wi_0/kernel"][0] == "expert"
+  # mesh data=2 x expert=2 x model=1: rank 3 is (data 1, expert 1) -> shard 1 + 1 * 2
+  layout = part.get_data_layout(16)
+  assert (layout.shard_id, layout.num_shards, layout.batch_size) == (3, 4, 16)
+  assert layout.is_first_host_in_replica_set
+  with pytest.raises(ValueError, match="entire data mesh size"):
+    part.get_data_layout(6)
+  # unfactored Adafactor: slots inherit the parameter's names, nothing to override
+  assert mp._infer_state_filter_fn(_moe_train_state(factored=False)) is None
+
+
+def test_experts_choose_router_fills_every_expert_with_its_best_tokens():
+  from t5x_b200.contrib.moe import layers
+  torch.manual_seed(0)
+  t, d, e, cap = 40, 16, 4, 6
+  router = layers.ExpertsChooseRouter(d, e)
+  tokens = torch.randn(t, d)
+  route, metrics = router(tokens, cap)
+  probs = torch.softmax(tokens @ router.router_weights.w.kernel.float(), -1)
+  fs, gate = route["flat_slot"], route["gate"]
+  for ex in range(e):
+    best = set(torch.topk(probs[:, ex], cap).indices.tolist())
+    picked = set(torch.nonzero(fs[:, ex] >= 0).squeeze(1).tolist())
+    assert picked == best
+    # its capacity rows of the dispatch buffer are all used, each once
+    assert sorted(fs[fs[:, ex] >= 0, ex].tolist()) == list(range(ex * cap, (ex + 1) * cap))
+    assert torch.allclose(gate[list(best), ex], probs[list(best), ex])
+  assert float(metrics["auxiliary_loss"]) == 0.0 and float(metrics["expert_usage"]) == 1.0
+  left = 1.0 - (fs >= 0).any(1).float().mean()
+  assert float(metrics["fraction_tokens_left_behind"]) == pytest.approx(float(left))
+  # the whole layer runs and is differentiable with this router
+  layer = layers.MoeLayer(d, 32, e, router_type="experts_choose", capacity_factor=1.0)
+  x = torch.randn(2, 20, d, requires_grad=True)
+  layer(x).sum().backward()
+  assert x.grad is not None and layer.router.router_weights.w.kernel.grad is not None
