@@ -230,8 +230,11 @@ class Adafactor(OptimizerDef):
                           tree_utils.unflatten_dict(states))
 
   # ---- update ----------------------------------------------------------------------------
-  def apply_param_gradient(self, step, hyper_params, param, state, grad, path):
-    """Updates `param` and `state` in place; returns them."""
+  def apply_param_gradient(self, step, hyper_params, param, state, grad, path,
+                           pre_reduced: bool = False):
+    """Updates `param` and `state` in place; returns them. `pre_reduced`: with the optimizer
+    sharded over the data axis, `grad` already holds the sum over replicas (global-norm
+    clipping needed it first), so the update only pushes the new weights."""
     hp = hyper_params
     assert hp.learning_rate is not None, "no learning rate provided."
     lr = float(hp.learning_rate)
@@ -245,8 +248,8 @@ class Adafactor(OptimizerDef):
     if isinstance(mbps, HParamMap):
       mbps = mbps[path]
     zinfo = getattr(param, "zero", None)
-    if zinfo is not None and self._fused_sharded_ok(param, state, grad, averaging_dims,
-                                                    factored_dims):
+    if zinfo is not None and not pre_reduced and \
+        self._fused_sharded_ok(param, state, grad, averaging_dims, factored_dims):
       # gradient reduction and weight broadcast happen inside the update kernels
       done = self._try_native(param, state, grad, path, lr, decay, bool(mbps),
                               weight_decay_rate, averaging_dims, factored_dims, zinfo=zinfo)
@@ -254,7 +257,8 @@ class Adafactor(OptimizerDef):
       return param, state
     if zinfo is not None:
       from t5x_b200.ops import comm
-      comm.peer_reduce_f32_(grad, zinfo.grad_ptrs(), zinfo.numel)
+      if not pre_reduced:
+        comm.peer_reduce_f32_(grad, zinfo.grad_ptrs(), zinfo.numel)
     if not self._try_native(param, state, grad, path, lr, decay, bool(mbps), weight_decay_rate,
                             averaging_dims, factored_dims):
       self._apply_torch(param, state, grad, lr, decay, bool(mbps), weight_decay_rate,
@@ -508,22 +512,40 @@ class Adafactor(OptimizerDef):
     saved_hp = self.hyper_params
     self.hyper_params = hyper_params
     try:
+      pre_reduced = False
       if hyper_params.global_norm_clip_threshold:
+        # The norm is that of the gradient summed over replicas. With the optimizer sharded
+        # over the data axis that sum exists on a parameter's owner only, so owners reduce
+        # their gradients here (the update below then skips its own reduction) and the
+        # squared norms are summed over the data axis; tensor-parallel shards are summed over
+        # the model axis, replicated parameters are counted once.
         thr = hyper_params.global_norm_clip_threshold
-        sq = torch.stack([(flat_g[k].float() ** 2).sum() for k in flat_p])
-        total = sq.sum()
         st = pstate.get()
+        counted = []
+        sums = torch.zeros(4, dtype=torch.float32, device=next(iter(flat_g.values())).device)
+        for k, p in flat_p.items():
+          zinfo = getattr(p, "zero", None)
+          if zinfo is not None:
+            if not zinfo.mine:
+              continue
+            from t5x_b200.ops import comm
+            comm.peer_reduce_f32_(flat_g[k], zinfo.grad_ptrs(), zinfo.numel)
+            pre_reduced = True
+          counted.append(k)
+          slot = 2 * (zinfo is not None) + (getattr(p, "shard_dim", None) is not None)
+          sums[slot] += (flat_g[k].float() ** 2).sum()
+        if any(getattr(p, "zero", None) is not None for p in flat_p.values()):
+          pre_reduced = True
+          dist.all_reduce(sums[2:], group=st.data_group)
         if st.model_size > 1:
-          # sharded params contribute their shard; replicated ones are counted once
-          rep = torch.stack([(flat_g[k].float() ** 2).sum() for k in flat_p
-                             if getattr(flat_p[k], "shard_dim", None) is None]).sum() \
-              if any(getattr(flat_p[k], "shard_dim", None) is None for k in flat_p) else 0.0
-          sh = total - rep
-          dist.all_reduce(sh, group=st.model_group)
-          total = sh + rep
+          sharded = sums[1] + sums[3]
+          dist.all_reduce(sharded, group=st.model_group)
+          total = sums[0] + sums[2] + sharded
+        else:
+          total = sums.sum()
         gn = torch.sqrt(total)
         scale = thr * torch.minimum(torch.tensor(1.0 / thr, device=gn.device), 1.0 / gn)
-        for k in flat_p:
+        for k in counted:
           flat_g[k].mul_(scale.to(flat_g[k].dtype))
       from t5x_b200.parallel import zero
       done = zero.done_this_step()
@@ -533,7 +555,8 @@ class Adafactor(OptimizerDef):
           continue  # its owner updates it and pushes the new bf16 weights here
         if k in done:
           continue  # already updated while the backward pass was running
-        self.apply_param_gradient(step, hyper_params, p, flat_s[k], flat_g[k], k)
+        self.apply_param_gradient(step, hyper_params, p, flat_s[k], flat_g[k], k,
+                                  pre_reduced=pre_reduced)
     finally:
       self.hyper_params = saved_hp
     return params, OptimizerState(step + 1, state.param_states)

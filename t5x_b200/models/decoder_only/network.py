@@ -22,6 +22,7 @@ from torch import nn
 from t5x_b200.models.t5 import layers
 from t5x_b200.models.t5.network import _dropout
 from t5x_b200.ops import functional as F
+from t5x_b200.ops import reference as ref
 from t5x_b200.parallel import state as pstate
 
 
@@ -109,19 +110,11 @@ class Decoder(nn.Module):
 
   @staticmethod
   def _prefix_lm_mask(decoder_target_tokens, decoder_causal_attention, decoder_segment_ids):
-    """[b,1,q,k] visibility for a prefix LM: causal, or both positions inside the prefix;
-    restricted to non-padding positions of the same packed segment
-    (the semantics of layers.make_decoder_mask, t5x/examples/t5/layers.py:842-924)."""
-    b, l = decoder_target_tokens.shape
-    pos = torch.arange(l, device=decoder_target_tokens.device)
-    vis = (pos[None, :] <= pos[:, None])[None].expand(b, l, l)
-    ca = decoder_causal_attention > 0
-    vis = vis | (ca[:, :, None] & ca[:, None, :])
-    valid = decoder_target_tokens > 0
-    vis = vis & valid[:, :, None] & valid[:, None, :]
-    if decoder_segment_ids is not None:
-      vis = vis & (decoder_segment_ids[:, :, None] == decoder_segment_ids[:, None, :])
-    return vis[:, None]
+    """Prefix-LM visibility: causal, or both positions inside the prefix; restricted to
+    non-padding positions of the same packed segment (the semantics of
+    layers.make_decoder_mask, t5x/examples/t5/layers.py:842-924), in factored form."""
+    return ref.PrefixLMMask(decoder_causal_attention > 0, decoder_target_tokens > 0,
+                            decoder_segment_ids)
 
   def hidden(self, decoder_input_tokens, decoder_target_tokens, decoder_segment_ids=None,
              decoder_positions=None, decoder_causal_attention=None, *, enable_dropout=True,

@@ -23,8 +23,24 @@ native.register_signature("t5x_attention_bwd", [c_void_p] * 10 + [c_int] * 4 + [
                           [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                            c_int, c_void_p])
 
-MAX_LK = 512
-MAX_LQ = 512
+native.register_signature("t5x_attention_fwd_stream", [c_void_p] * 5 + [c_int] * 5 + [c_ll] * 12 +
+                          [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                           c_void_p])
+
+# The short-range forward kernel keeps the scores of a whole key range in TMEM.
+CLASSIC_MAX_LK = 512
+CLASSIC_MAX_LQ = 512
+# The backward kernel keeps bias-gradient bins for the whole query range in shared memory.
+BWD_MAX_LQ = 4096
+
+
+def forward_kernel(Lq: int, Lk: int, D: int, prefix_lm: bool = False) -> str:
+  """'stream' (any length, head_dim 64 or 128) or 'classic' (head_dim 64, up to 512 x 512).
+  `T5X_B200_ATTN_FWD` forces one where both apply."""
+  import os
+  classic_ok = D == 64 and Lq <= CLASSIC_MAX_LQ and Lk <= CLASSIC_MAX_LK and not prefix_lm
+  want = os.environ.get("T5X_B200_ATTN_FWD", "stream")
+  return "classic" if (classic_ok and want == "classic") else "stream"
 
 
 def _strides_ok(t: torch.Tensor) -> bool:
@@ -34,8 +50,11 @@ def _strides_ok(t: torch.Tensor) -> bool:
 
 def flash_supported(q, k, v, explicit_bias, extra_mask) -> bool:
   """True when the sm_100a flash kernels cover this call."""
-  return (explicit_bias is None and extra_mask is None and q.shape[-1] == 64 and
-          k.shape[1] <= MAX_LK and q.shape[1] <= MAX_LQ and q.dtype == torch.bfloat16 and
+  prefix_lm = isinstance(extra_mask, ref.PrefixLMMask)
+  if prefix_lm and q.shape[1] != k.shape[1]:
+    return False
+  return (explicit_bias is None and (extra_mask is None or prefix_lm) and q.shape[-1] == 64 and
+          q.shape[1] <= BWD_MAX_LQ and q.dtype == torch.bfloat16 and
           k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16)
 
 
@@ -69,11 +88,16 @@ class _FlashAttentionFn(torch.autograd.Function):
     o = torch.empty((B, Lq, H, D), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
     nrel = rel_bias.shape[1] if rel_bias is not None else 0
-    rc = native.lib().t5x_attention_fwd(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, H, Lq, Lk,
-        *_sbh(q), *_sbh(k), *_sbh(v), *_sbh(o), native.ptr(rel_bias), nrel, rel_off,
-        native.ptr(key_mask), native.ptr(q_seg), native.ptr(kv_seg), int(causal), causal_off,
-        native.stream_ptr())
+    tail = (*_sbh(q), *_sbh(k), *_sbh(v), *_sbh(o), native.ptr(rel_bias), nrel, rel_off,
+            native.ptr(key_mask), native.ptr(q_seg), native.ptr(kv_seg), int(causal), causal_off,
+            native.stream_ptr())
+    if forward_kernel(Lq, Lk, D, int(causal) == 2) == "classic":
+      rc = native.lib().t5x_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                          lse.data_ptr(), B, H, Lq, Lk, *tail)
+    else:
+      rc = native.lib().t5x_attention_fwd_stream(q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                 o.data_ptr(), lse.data_ptr(), B, H, Lq, Lk, D,
+                                                 *tail)
     native._check(rc, "attention_fwd")
     ctx.save_for_backward(q, k, v, o, lse, rel_bias, key_mask, q_seg, kv_seg)
     ctx.cfg = (causal, causal_off, rel_off)
@@ -131,8 +155,11 @@ def _rel_buckets(Lq, Lk, q_offset, bidirectional, num_buckets, max_distance, dev
 def flash_attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None,
                     bidirectional: bool = True, num_buckets: int = 32, max_distance: int = 128,
                     key_mask: Optional[torch.Tensor] = None, causal: bool = False,
-                    q_segment_ids=None, kv_segment_ids=None, q_offset: int = 0) -> torch.Tensor:
-  """q [B,Lq,H,64], k/v [B,Lk,H,64] bf16 -> [B,Lq,H,64]."""
+                    q_segment_ids=None, kv_segment_ids=None, q_offset: int = 0,
+                    prefix_lm: Optional["ref.PrefixLMMask"] = None) -> torch.Tensor:
+  """q [B,Lq,H,D], k/v [B,Lk,H,D] bf16 -> [B,Lq,H,D], D = 64 (forward and backward) or 128
+  (forward). `prefix_lm`: prefix-LM visibility in factored form; it replaces `causal`,
+  `key_mask` and the segment ids (which it contains)."""
   B, Lq, H, D = q.shape
   Lk = k.shape[1]
   rel_bias = None
@@ -144,5 +171,11 @@ def flash_attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None,
   ks = kv_segment_ids.to(torch.int32).contiguous() if kv_segment_ids is not None else None
   if qs is None or ks is None:
     qs = ks = None
-  return _FlashAttentionFn.apply(q, k, v, rel_bias, km, qs, ks, bool(causal),
-                                 (Lk - Lq) if causal else 0, Lq - 1)
+  mode = int(bool(causal))
+  if prefix_lm is not None:
+    qs, ks = prefix_lm.token_codes()
+    valid = prefix_lm.valid.to(torch.uint8)
+    km = valid.contiguous() if km is None else (km & valid).contiguous()
+    mode = 2
+  return _FlashAttentionFn.apply(q, k, v, rel_bias, km, qs, ks, mode,
+                                 (Lk - Lq) if mode else 0, Lq - 1)

@@ -75,21 +75,34 @@ def bench_gemm(pair_modes=(0, 1)):
 
 
 def bench_attention():
+  """Forward (both kernels where the short-range one applies) and forward + backward times of
+  the flash-attention kernels with the T5 relative bias, against torch SDPA without a bias."""
+  import os
   from t5x_b200.ops import attention as attn
   rows = []
-  for (b, h, lq, lk) in [(16, 64, 512, 512), (16, 64, 114, 512), (16, 64, 114, 114)]:
-    q = torch.randn(b, lq, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    k = torch.randn(b, lk, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    v = torch.randn(b, lk, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+  shapes = [(16, 64, 512, 512, 64), (16, 64, 114, 512, 64), (16, 64, 114, 114, 64),
+            (4, 64, 2048, 2048, 64), (8, 32, 1024, 1024, 128)]
+  for (b, h, lq, lk, d) in shapes:
+    q = torch.randn(b, lq, h, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(b, lk, h, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(b, lk, h, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     table = torch.randn(h, 32, device="cuda")
     fwd = lambda: attn.flash_attention(q, k, v, bias_table=table, bidirectional=True)
-    ms_f = time_ms(fwd)
-    o = fwd()
-    do = torch.randn_like(o)
-    ms_fb = time_ms(lambda: torch.autograd.grad(fwd(), (q, k, v), do))
-    flops = 4.0 * b * h * lq * lk * 64
-    row = {"b": b, "h": h, "lq": lq, "lk": lk, "fwd_ms": round(ms_f, 3),
-           "fwd_tflops": round(flops / ms_f / 1e9, 1), "fwd_bwd_ms": round(ms_fb, 3)}
+    flops = 4.0 * b * h * lq * lk * d
+    row = {"b": b, "h": h, "lq": lq, "lk": lk, "d": d}
+    for kernel in ("stream", "classic"):
+      os.environ["T5X_B200_ATTN_FWD"] = kernel
+      if attn.forward_kernel(lq, lk, d) != kernel:
+        continue
+      with torch.no_grad():
+        ms = time_ms(fwd)
+      row[f"fwd_{kernel}_ms"] = round(ms, 3)
+      row[f"fwd_{kernel}_tflops"] = round(flops / ms / 1e9, 1)
+    os.environ.pop("T5X_B200_ATTN_FWD", None)
+    if d == 64:
+      o = fwd()
+      do = torch.randn_like(o)
+      row["fwd_bwd_ms"] = round(time_ms(lambda: torch.autograd.grad(fwd(), (q, k, v), do)), 3)
     qs, ks, vs = (t.detach().transpose(1, 2) for t in (q, k, v))
     row["sdpa_fwd_ms_no_bias"] = round(time_ms(
         lambda: torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, scale=1.0)), 3)

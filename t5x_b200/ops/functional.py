@@ -420,7 +420,8 @@ def attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None, bidirection
                                     num_buckets=num_buckets, max_distance=max_distance,
                                     key_mask=key_mask, causal=causal,
                                     q_segment_ids=q_segment_ids, kv_segment_ids=kv_segment_ids,
-                                    q_offset=q_offset)
+                                    q_offset=q_offset,
+                                    prefix_lm=extra_mask)  # None or a ref.PrefixLMMask
   bias = explicit_bias
   if bias_table is not None:
     rb = ref.relative_position_bias(bias_table.float(), q.shape[1], k.shape[1], bidirectional,

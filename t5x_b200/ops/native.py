@@ -770,3 +770,24 @@ def moe_router_bwd(x, w, k: int, capacity: int, fwd: dict, dgate: torch.Tensor,
       dgate.data_ptr(), fwd["stats"].data_ptr(), coef.data_ptr(), dlogits.data_ptr(), ptr(dx),
       d, dw.data_ptr(), dw_part.data_ptr(), stream_ptr()), "moe_router_bwd")
   return dx, dw
+
+
+# ----------------------------------------------------------------------------
+# AdamW
+# ----------------------------------------------------------------------------
+register_signature("t5x_adamw_step", [c_void_p, c_void_p, c_void_p, c_void_p,
+                                      ctypes.POINTER(c_void_p), c_int, c_void_p, c_ll, c_float,
+                                      c_float, c_float, c_float, c_float, c_float, c_int, c_void_p,
+                                      c_void_p])
+
+
+def adamw_step_(p, g, mu, nu, bf16_out_ptrs, bf16_mc: int = 0, *, lr, b1, b2, eps, eps_root,
+                weight_decay, step: int, clip_scale: Optional[torch.Tensor] = None) -> None:
+  """One fused AdamW step on a contiguous fp32 parameter (csrc/adamw.cu). `bf16_out_ptrs`: a
+  ctypes array of device pointers to the bf16 working copies that receive the new weights;
+  `clip_scale`: a one-element device tensor multiplying the gradient, or None."""
+  _check(lib().t5x_adamw_step(p.data_ptr(), g.data_ptr(), mu.data_ptr(), nu.data_ptr(),
+                              bf16_out_ptrs, len(bf16_out_ptrs), bf16_mc, p.numel(), float(lr),
+                              float(b1), float(b2), float(eps), float(eps_root),
+                              float(weight_decay), int(step), ptr(clip_scale), stream_ptr()),
+         "adamw_step")

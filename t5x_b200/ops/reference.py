@@ -69,6 +69,40 @@ def relative_position_bias(table: torch.Tensor, qlen: int, klen: int, bidirectio
   return table[:, buckets]  # [H, q, k]
 
 
+class PrefixLMMask:
+  """Visibility of a prefix LM in factored form: key k is visible to query q when
+  (k <= q, or both lie inside the prefix) and both are real tokens of the same packed segment
+  (the semantics of make_decoder_mask with decoder_causal_attention,
+  t5x/examples/t5/layers.py:842-924). `bool()` gives the dense [B, 1, L, L] mask, so the object
+  can stand wherever a dense `extra_mask` is accepted; the flash kernels use the per-token
+  vectors and never build the dense form."""
+
+  def __init__(self, in_prefix: torch.Tensor, valid: torch.Tensor,
+               segment_ids: Optional[torch.Tensor] = None):
+    self.in_prefix, self.valid, self.segment_ids = in_prefix.bool(), valid.bool(), segment_ids
+
+  def bool(self) -> torch.Tensor:
+    b, l = self.valid.shape
+    pos = torch.arange(l, device=self.valid.device)
+    vis = (pos[None, :] <= pos[:, None])[None].expand(b, l, l)
+    vis = vis | (self.in_prefix[:, :, None] & self.in_prefix[:, None, :])
+    vis = vis & self.valid[:, :, None] & self.valid[:, None, :]
+    if self.segment_ids is not None:
+      vis = vis & (self.segment_ids[:, :, None] == self.segment_ids[:, None, :])
+    return vis[:, None]
+
+  def token_codes(self):
+    """(query codes, key codes) int32 [B, L] for the kernels: the segment id (1 when unpacked)
+    in the low 30 bits, bit 30 set inside the prefix; padding queries carry a segment id that no
+    key has, so their rows see nothing."""
+    seg = self.segment_ids.to(torch.int32) if self.segment_ids is not None else \
+        torch.ones_like(self.valid, dtype=torch.int32)
+    pre = self.in_prefix.to(torch.int32) << 30
+    k_codes = seg | pre
+    q_codes = torch.where(self.valid, seg, torch.full_like(seg, 0x3FFFFFFE)) | pre
+    return q_codes.contiguous(), k_codes.contiguous()
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
               bias: Optional[torch.Tensor] = None, key_mask: Optional[torch.Tensor] = None,
               causal: bool = False, q_segment_ids: Optional[torch.Tensor] = None,

@@ -141,6 +141,9 @@ class GradientTransformation(NamedTuple):
   init: Callable[[Dict[str, torch.Tensor]], Any]
   update: Callable[..., Tuple[Dict[str, torch.Tensor], Any]]
   name: str = "transform"
+  # what the transformation was built with (read by OptaxWrapper to recognise chains that a
+  # fused kernel covers); for a chain: {"transforms": [...]}
+  hparams: Mapping[str, Any] = {}
 
 
 def _zeros_like_tree(params):
@@ -176,7 +179,8 @@ def scale_by_learning_rate(learning_rate, flip_sign=True) -> GradientTransformat
     lr = _lr(learning_rate, int(state["count"]))
     return {k: v * (sign * lr) for k, v in updates.items()}, {"count": state["count"] + 1}
 
-  return GradientTransformation(init, update, "scale_by_schedule")
+  return GradientTransformation(init, update, "scale_by_schedule",
+                                {"learning_rate": learning_rate, "flip_sign": flip_sign})
 
 
 def clip(max_delta: float) -> GradientTransformation:
@@ -193,7 +197,8 @@ def clip_by_global_norm(max_norm: float) -> GradientTransformation:
     # optax: scale only when g >= max_norm, i.e. factor = min(1, max_norm/g)
     return {k: v * factor for k, v in updates.items()}, state
 
-  return GradientTransformation(lambda p: {}, update, "clip_by_global_norm")
+  return GradientTransformation(lambda p: {}, update, "clip_by_global_norm",
+                                {"max_norm": max_norm})
 
 
 def trace(decay: float, nesterov: bool = False) -> GradientTransformation:
@@ -222,7 +227,8 @@ def scale_by_adam(b1=0.9, b2=0.999, eps=1e-8, eps_root=0.0) -> GradientTransform
     out = {k: (mu[k] / bc1) / (torch.sqrt(nu[k] / bc2 + eps_root) + eps) for k in updates}
     return out, {"count": count, "mu": mu, "nu": nu}
 
-  return GradientTransformation(init, update, "scale_by_adam")
+  return GradientTransformation(init, update, "scale_by_adam",
+                                {"b1": b1, "b2": b2, "eps": eps, "eps_root": eps_root})
 
 
 def scale_by_belief(b1=0.9, b2=0.999, eps=1e-16, eps_root=1e-16) -> GradientTransformation:
@@ -332,7 +338,8 @@ def add_decayed_weights(weight_decay: float, mask=None):
       raise ValueError("add_decayed_weights needs params")
     return {k: g + weight_decay * params[k].float() for k, g in updates.items()}, state
 
-  return GradientTransformation(lambda p: {}, update, "add_decayed_weights")
+  return GradientTransformation(lambda p: {}, update, "add_decayed_weights",
+                                {"weight_decay": weight_decay, "mask": mask})
 
 
 def scale_by_trust_ratio(min_norm=0.0, trust_coefficient=1.0, eps=0.0):
@@ -374,7 +381,7 @@ def chain_transforms(*transforms: GradientTransformation) -> GradientTransformat
       updates, new_state[str(i)] = t.update(updates, state[str(i)], params)
     return updates, new_state
 
-  return GradientTransformation(init, update, "chain")
+  return GradientTransformation(init, update, "chain", {"transforms": list(transforms)})
 
 
 # --- aliases with optax's signatures ------------------------------------------------------
@@ -460,6 +467,7 @@ class OptaxWrapper(OptimizerDef):
 
   def __init__(self, optax_optimizer: GradientTransformation):
     self.optax_optimizer = optax_optimizer
+    self.fused_plan = _fused_adamw_plan(optax_optimizer)
     super().__init__(hyper_params=None)
 
   def init_state(self, params):
@@ -500,6 +508,8 @@ class OptaxWrapper(OptimizerDef):
 
   def apply_gradient(self, hyper_params, params, state, grads):
     flat_p = tree_utils.flatten_dict(params)
+    if self.fused_plan is not None and _fused_adamw_usable(flat_p, grads):
+      return self._apply_fused_adamw(hyper_params, params, state, grads)
     flat_g = {k: v.float() for k, v in tree_utils.flatten_dict(grads).items()}
     opt_state = self._flat(state.param_states, flat_p.keys())
     _STEP_LEARNING_RATE[0] = (hyper_params or {}).get("learning_rate")
@@ -516,6 +526,74 @@ class OptaxWrapper(OptimizerDef):
           bf.copy_(p)
     return params, OptimizerState(step=state.step + 1, param_states=self._nest(new_opt_state))
 
+  def _apply_fused_adamw(self, hyper_params, params, state, grads):
+    """[clip_by_global_norm ->] scale_by_adam [-> add_decayed_weights] -> scale_by_learning_rate
+    as one native kernel per parameter (csrc/adamw.cu), with the same state layout as the
+    generic path. With the optimizer sharded over the data axis (`parallel/zero.py`) the owner
+    of a parameter first sums the replicas' gradients over NVLink, the clip factor is taken
+    from the norm of the summed gradients of all owners, and the update kernel stores the new
+    bf16 weights into every replica's working copy."""
+    from t5x_b200.ops import comm, native
+    from t5x_b200.parallel import state as pstate
+    plan = self.fused_plan
+    flat_p = tree_utils.flatten_dict(params)
+    flat_g = tree_utils.flatten_dict(grads)
+    opt_state = self._flat(state.param_states, flat_p.keys())
+    def at(path):
+      node = opt_state
+      for i in path:
+        node = node[str(i)]
+      return node
+
+    adam_state, lr_state = at(plan["adam_path"]), at(plan["lr_path"])
+    _STEP_LEARNING_RATE[0] = (hyper_params or {}).get("learning_rate")
+    try:
+      lr = float(_lr(plan["learning_rate"], int(lr_state["count"])))
+    finally:
+      _STEP_LEARNING_RATE[0] = None
+    step = int(adam_state["count"]) + 1
+    st = pstate.get()
+    with torch.no_grad():
+      mine, replicated = [], []
+      for k, p in flat_p.items():
+        z = getattr(p, "zero", None)
+        if z is None:
+          replicated.append(k)
+        elif z.mine:
+          comm.peer_reduce_f32_(flat_g[k], z.grad_ptrs(), z.numel)
+          mine.append(k)
+      clip_scale = None
+      if plan["max_norm"] is not None:
+        def sumsq(keys):
+          if not keys:
+            return torch.zeros((), dtype=torch.float32, device=st.device)
+          norms = torch._foreach_norm([flat_g[k] for k in keys])
+          return torch.stack(norms).float().pow(2).sum()
+        total = sumsq(mine)
+        if any(getattr(p, "zero", None) is not None for p in flat_p.values()):
+          import torch.distributed as dist
+          dist.all_reduce(total, group=st.data_group)
+        total = total + sumsq(replicated)
+        gnorm = torch.sqrt(total)
+        clip_scale = torch.clamp(plan["max_norm"] / (gnorm + 1e-16), max=1.0).float().reshape(1)
+      for k in mine + replicated:
+        p, g = flat_p[k], flat_g[k]
+        z = getattr(p, "zero", None)
+        bf = getattr(p, "bf16", None)
+        if z is not None:
+          outs, mc = z.bf16_ptrs(), z.bf16_mc()
+        elif bf is not None:
+          outs, mc = comm._ptr_array([bf.data_ptr()]), 0
+        else:
+          outs, mc = comm._ptr_array([]), 0
+        native.adamw_step_(p, g, adam_state["mu"][k], adam_state["nu"][k], outs, mc, lr=lr,
+                           b1=plan["b1"], b2=plan["b2"], eps=plan["eps"],
+                           eps_root=plan["eps_root"], weight_decay=plan["weight_decay"],
+                           step=step, clip_scale=clip_scale)
+    adam_state["count"] = adam_state["count"] + 1
+    lr_state["count"] = lr_state["count"] + 1
+    return params, OptimizerState(step=state.step + 1, param_states=self._nest(opt_state))
+
   def derive_logical_axes(self, optimizer, param_logical_axes):
     """Per-parameter moments inherit the parameter's axes; counters are replicated."""
     flat_axes = tree_utils.flatten_dict(param_logical_axes, is_leaf=lambda x: not isinstance(x, dict))
@@ -531,6 +609,67 @@ class OptaxWrapper(OptimizerDef):
 
     state_axes = OptimizerState(step=None, param_states=conv(optimizer.state.param_states))
     return Optimizer(optimizer.optimizer_def, state_axes, param_logical_axes)
+
+
+def _fused_adamw_plan(t: GradientTransformation):
+  """The hyper-parameters of an Adam / AdamW chain that the native kernel covers, or None:
+  [clip_by_global_norm,] scale_by_adam, [add_decayed_weights without a mask,]
+  scale_by_learning_rate (descending), possibly nested one level (`chain([clip, adamw(...)])`)."""
+  def flatten(x):
+    if x.name == "chain":
+      out = []
+      for sub in x.hparams.get("transforms", []):
+        out.extend(flatten(sub))
+      return out
+    return [x]
+
+  def index_paths(x, prefix=()):
+    if x.name == "chain":
+      out = []
+      for i, sub in enumerate(x.hparams.get("transforms", [])):
+        out.extend(index_paths(sub, prefix + (i,)))
+      return out
+    return [prefix]
+
+  if t.name != "chain":
+    return None
+  parts, paths = flatten(t), index_paths(t)
+  names = [x.name for x in parts]
+  want = [n for n in names if n != "clip_by_global_norm"]
+  if want not in (["scale_by_adam", "scale_by_schedule"],
+                  ["scale_by_adam", "add_decayed_weights", "scale_by_schedule"]):
+    return None
+  if names.count("clip_by_global_norm") > 1 or \
+      ("clip_by_global_norm" in names and names[0] != "clip_by_global_norm"):
+    return None
+  by = {x.name: x for x in parts}
+  wd = by.get("add_decayed_weights")
+  if wd is not None and wd.hparams.get("mask") is not None:
+    return None
+  if not by["scale_by_schedule"].hparams.get("flip_sign", True):
+    return None
+  adam = by["scale_by_adam"].hparams
+  return {"adam_path": paths[names.index("scale_by_adam")],
+          "lr_path": paths[names.index("scale_by_schedule")],
+          "learning_rate": by["scale_by_schedule"].hparams["learning_rate"],
+          "b1": adam["b1"], "b2": adam["b2"], "eps": adam["eps"], "eps_root": adam["eps_root"],
+          "weight_decay": wd.hparams["weight_decay"] if wd is not None else 0.0,
+          "max_norm": by["clip_by_global_norm"].hparams["max_norm"]
+          if "clip_by_global_norm" in by else None}
+
+
+def _fused_adamw_usable(flat_p, grads) -> bool:
+  flat_g = tree_utils.flatten_dict(grads)
+  for k, p in flat_p.items():
+    g = flat_g.get(k)
+    if not (isinstance(p, torch.Tensor) and p.is_cuda and p.dtype == torch.float32 and
+            isinstance(g, torch.Tensor) and g.is_cuda and g.dtype == torch.float32 and
+            g.is_contiguous()):
+      return False
+    z = getattr(p, "zero", None)
+    if (z is None or z.mine) and not p.is_contiguous():
+      return False
+  return True
 
 
 def wrap_optax_optimizer(optax_optimizer_fn):

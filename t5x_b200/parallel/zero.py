@@ -239,6 +239,9 @@ class ZeroContext:
   # -- step protocol -------------------------------------------------------------------------
   def gradients_complete(self) -> None:
     """Barrier after the last backward pass: every rank's gradient copy is final."""
+    if getattr(self, "_release_after_sync", False):
+      self._release_after_sync = False
+      self.release_replica_masters()
     self.end_overlap()
     self.grads.barrier(channel=0)
 
@@ -279,15 +282,37 @@ class ZeroContext:
     for k, p in self.params.items():
       dist.broadcast(p.data, src=ranks[self.owners[k]], group=self.group)
     if optimizer_state is not None:
-      from t5x_b200.utils import tree as tree_utils
-      flat = tree_utils.flatten_dict(optimizer_state)
-      by_param = {}
-      for path, v in flat.items():
-        if isinstance(v, torch.Tensor) and v.is_cuda:
-          by_param.setdefault(path[:-1], []).append(v)
-      for k in self.params:
-        for v in by_param.get(tuple(k) if not isinstance(k, tuple) else k, []):
-          dist.broadcast(v, src=ranks[self.owners[k]], group=self.group)
+      for k, leaves in state_leaves_by_param(self.params.keys(), optimizer_state).items():
+        for v in leaves:
+          if v.is_cuda:
+            dist.broadcast(v, src=ranks[self.owners[k]], group=self.group)
+
+
+def state_leaves_by_param(param_names, optimizer_state) -> Dict[str, List[torch.Tensor]]:
+  """The tensors of an optimizer-state tree that belong to each parameter. Two layouts occur:
+  Adafactor keeps a dict of slots under the parameter's path ('<param>/v_row'), optax-style
+  states keep a copy of the parameter tree under each moment ('1/0/mu/<param>'). A leaf belongs
+  to the parameter whose name is the head or the tail of its path; counters and other leaves
+  that match no parameter are left out (they are identical on every rank)."""
+  from t5x_b200.utils import tree as tree_utils
+  names = set(param_names)
+  out: Dict[str, List[torch.Tensor]] = {k: [] for k in names}
+  for path, v in tree_utils.flatten_dict(optimizer_state).items():
+    if not isinstance(v, torch.Tensor):
+      continue
+    parts = path.split("/")
+    for i in range(len(parts), 0, -1):
+      head = "/".join(parts[:i])
+      if head in names:
+        out[head].append(v)
+        break
+    else:
+      for i in range(1, len(parts)):
+        tail = "/".join(parts[i:])
+        if tail in names:
+          out[tail].append(v)
+          break
+  return out
 
 
 class LocalUpdateOverlap:

@@ -197,7 +197,9 @@ class LocalChunker:
   def get_local_chunk_info(self, global_shape: Tuple[int, ...],
                            mesh_axes: Sequence[Optional[str]]) -> LocalChunkInfo:
     block, used = [], set()
-    for extent, spec in zip(global_shape, mesh_axes):
+    # a spec shorter than the array's rank leaves the trailing dimensions whole
+    specs = list(mesh_axes) + [None] * (len(global_shape) - len(mesh_axes))
+    for extent, spec in zip(global_shape, specs):
       axes = self._as_axes(spec)
       if not axes:
         block.append(slice(None))

@@ -343,6 +343,9 @@ def build_flag_parser(description: str = ""):
   ap.add_argument("--process_index", type=int, default=None)
   ap.add_argument("--initialization_timeout", type=int, default=None)
   ap.add_argument("--seqio_additional_cache_dirs", action="append", default=[])
+  ap.add_argument("--profile_steps", default=None, metavar="FIRST:LAST",
+                  help="Record train steps FIRST..LAST-1 with torch.profiler into "
+                       "<model_dir>/profile/ (trace + kernels by device time).")
   return ap
 
 
@@ -374,6 +377,10 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
   logging.basicConfig(level=logging.INFO)
   argv = gin_utils.rewrite_gin_args(list(sys.argv[1:] if argv is None else argv))
   flags = build_flag_parser(__doc__).parse_args(argv)
+  if flags.profile_steps:
+    from t5x_b200.utils import profiling
+    profiling.parse_step_range(flags.profile_steps)  # fail on a malformed range before training
+    os.environ["T5X_B200_PROFILE_STEPS"] = flags.profile_steps
   init_distributed_from_flags(flags)
   gin.set_main_module(sys.modules[__name__])
   parse_gin_from_flags(flags, _DEFAULT_GIN_SEARCH_PATHS)

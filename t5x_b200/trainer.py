@@ -480,6 +480,7 @@ class BaseTrainer(abc.ABC):
     self._train_state_mutex = threading.RLock()
     self._train_state = train_state
     self.stop_training = False
+    self._summary_dir = summary_dir
     self.train_metrics_manager = MetricsManager("train", summary_dir=summary_dir)
     self.eval_metrics_managers = {
         n: MetricsManager(f"training_eval/{n}", summary_dir=summary_dir) for n in eval_names}
@@ -517,11 +518,13 @@ class BaseTrainer(abc.ABC):
       start_step = int(self.train_state.step)
     self.train_metrics_manager.start_duration_timer(block_on=self.train_state)
     last_log = time.time()
+    profiler = self._step_profiler()
     for step_num in range(start_step, start_step + num_steps):
       self._check_preemption()
       if time.time() - last_log > 10.0:
         logging.info("Training: step %d", step_num)
         last_log = time.time()
+      profiler.step_begin(step_num)
       if torch.cuda.is_available():
         torch.cuda.nvtx.range_push(f"train_step_{step_num}")
       with self._train_state_mutex:
@@ -530,10 +533,20 @@ class BaseTrainer(abc.ABC):
       if torch.cuda.is_available():
         torch.cuda.nvtx.range_pop()
       self._after_step()
+      profiler.step_end(step_num)
       metrics = metrics_update if metrics is None else merge_metrics(metrics, metrics_update)
+    profiler.finish()
     self._replicas_stale = True
     return self.train_metrics_manager.write_metrics_summary(metrics, start_step + num_steps,
                                                             num_steps)
+
+  def _step_profiler(self):
+    """The `--profile_steps a:b` capture (see `utils/profiling.py`); idle unless requested."""
+    if getattr(self, "_profiler", None) is None:
+      from t5x_b200.utils import profiling
+      self._profiler = profiling.StepProfiler.from_environment(
+          getattr(self, "_summary_dir", None), pstate.get().rank)
+    return self._profiler
 
   def request_preemption(self) -> None:
     """Called from a signal handler: asks the loop to stop at the next step boundary. The
@@ -671,33 +684,39 @@ class Trainer(BaseTrainer):
 
   def _maybe_shard_optimizer(self, train_state, weight_metrics_computer) -> None:
     """Shards the optimizer over the data axis (see `t5x_b200.parallel.zero`) when there is
-    more than one replica on GPUs and nothing needs the fully reduced gradient on every
-    rank (weight metrics, global-norm clipping). `T5X_B200_OPTIMIZER_SHARDING=0` keeps the
-    plain all-reduce."""
-    from t5x_b200 import adafactor
+    more than one replica on GPUs and nothing needs the fully reduced gradient on every rank
+    (weight metrics). Covered optimizers: Adafactor (with or without global-norm clipping) and
+    the optax-style Adam / AdamW chains that the fused kernel handles
+    (`OptaxWrapper.fused_plan`). The per-layer overlap with the backward pass is attached for
+    Adafactor without clipping only: a clip factor needs every gradient first.
+    `T5X_B200_OPTIMIZER_SHARDING=0` keeps the plain all-reduce."""
+    from t5x_b200 import adafactor, optimizers
     from t5x_b200.parallel import zero
     zero.disable_local_overlap()  # a previous trainer's registration does not apply to this one
     st = pstate.get()
     opt_def = getattr(getattr(train_state, "_optimizer", None), "optimizer_def", None)
+    is_adafactor = isinstance(opt_def, adafactor.Adafactor)
+    is_fused_adam = isinstance(opt_def, optimizers.OptaxWrapper) and \
+        opt_def.fused_plan is not None
     if (self._device.type != "cuda" or weight_metrics_computer is not None or
-        not isinstance(opt_def, adafactor.Adafactor) or
-        opt_def.hyper_params.global_norm_clip_threshold):
+        not (is_adafactor or is_fused_adam)):
       return
-    if st.world_size == 1 and getattr(self._model, "module", None) is not None and \
-        os.environ.get("T5X_B200_OVERLAP_GRAD_EXCHANGE", "1") != "0":
-      # one replica: nothing to exchange, but each layer's update can still run under the
-      # backward pass of the layers below it (registered after the buffers are attached)
-      self._local_overlap_args = (train_state, opt_def)
+    can_overlap = is_adafactor and not opt_def.hyper_params.global_norm_clip_threshold and \
+        getattr(self._model, "module", None) is not None and \
+        os.environ.get("T5X_B200_OVERLAP_GRAD_EXCHANGE", "1") != "0"
+    if st.world_size == 1:
+      if can_overlap:
+        # one replica: nothing to exchange, but each layer's update can still run under the
+        # backward pass of the layers below it (registered after the buffers are attached)
+        self._local_overlap_args = (train_state, opt_def)
       return
     if (os.environ.get("T5X_B200_OPTIMIZER_SHARDING", "1") == "0" or st.data_size <= 1 or
         st.expert_size > 1):
       return
     ctx = zero.enable(tree_utils.flatten_dict(train_state.params), st.data_group)
-    module = getattr(self._model, "module", None)
-    if ctx is not None and module is not None and \
-        os.environ.get("T5X_B200_OVERLAP_GRAD_EXCHANGE", "1") != "0":
+    if ctx is not None and can_overlap:
       slots = tree_utils.flatten_dict(train_state.param_states, is_leaf=adafactor._is_state_leaf)
-      ctx.attach_overlap(module, opt_def, lambda name: slots[name])
+      ctx.attach_overlap(self._model.module, opt_def, lambda name: slots[name])
 
   def _train_step(self, train_state, batch, step_num):
     step = int(step_num)

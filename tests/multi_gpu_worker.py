@@ -65,11 +65,19 @@ def _tiny_trainer(n_micro=2):
   torch.manual_seed(7)
   module = network.Transformer(cfg, device=st.device)
   vocab = vocabularies.PassThroughVocabulary(512)
-  opt = adafactor.Adafactor(decay_rate=0.8, step_offset=0,
-                            logical_factor_rules=adafactor.standard_logical_factor_rules())
+  kind = os.environ.get("T5X_TEST_OPTIMIZER", "adafactor")
+  if kind == "adamw_clip":
+    from t5x_b200 import optimizers
+    opt = optimizers.chain([optimizers.clip_by_global_norm(1.0),
+                            optimizers._adamw(1e-3, weight_decay=0.01)])
+  else:
+    opt = adafactor.Adafactor(decay_rate=0.8, step_offset=0,
+                              global_norm_clip_threshold=1.0 if kind == "adafactor_clip" else None,
+                              logical_factor_rules=adafactor.standard_logical_factor_rules())
   model = models.EncoderDecoderModel(module, vocab, vocab, opt, z_loss=1e-4)
   state = ts_lib.FlaxOptimTrainState.create(opt, model.get_initial_variables(None, None))
-  lr_fn = schedules.create_learning_rate_scheduler("constant", 0.01, 0)
+  lr_fn = schedules.create_learning_rate_scheduler("constant",
+                                                   1e-3 if kind == "adamw_clip" else 0.01, 0)
   return trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, n_micro), module
 
 
@@ -102,7 +110,12 @@ def case_train(out):
   flat = torch.cat([p.detach().float().reshape(-1) for p in module.parameters()])
   bf = torch.cat([p.bf16.float().reshape(-1) for p in module.parameters()])
   ctx = zero.active()
+  from t5x_b200.utils import tree as tree_utils
+  slots = [v.double().abs().sum() for v in
+           tree_utils.flatten_dict(trainer.train_state.param_states).values()
+           if isinstance(v, torch.Tensor) and v.is_cuda and v.numel() > 1]
   json.dump({"loss": float(summary["loss"].value), "sharded": ctx is not None,
+             "slot_abs": float(torch.stack(slots).sum()),
              "nvls": bool(getattr(ctx, "nvls", False)),
              "overlapped": len(getattr(ctx, "done_this_step", ())),
              "param_sum": float(flat.double().sum()), "param_abs": float(flat.double().abs().sum()),

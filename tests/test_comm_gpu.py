@@ -52,9 +52,32 @@ def test_sharded_optimizer_matches_all_reduce(tmp_path):
   for run in (sharded, plain):
     assert abs(run[0]["param_sum"] - run[1]["param_sum"]) <= 1e-6 * run[0]["param_abs"]
     assert run[0]["loss"] == pytest.approx(run[1]["loss"], rel=1e-6)
+    assert run[0]["slot_abs"] == pytest.approx(run[1]["slot_abs"], rel=1e-6)
   a, b = sharded[0], plain[0]
   assert a["loss"] == pytest.approx(b["loss"], rel=2e-3)
   assert a["param_abs"] == pytest.approx(b["param_abs"], rel=1e-4)
+  assert a["bf16_abs"] == pytest.approx(a["param_abs"], rel=5e-3)
+  for x, y in zip(a["first"], b["first"]):
+    assert x == pytest.approx(y, rel=1e-2, abs=1e-4)
+
+
+@pytest.mark.parametrize("kind", ["adamw_clip", "adafactor_clip"])
+def test_sharded_adamw_and_global_norm_clip_match_all_reduce(tmp_path, kind):
+  """Optimizers whose update needs the norm of the whole gradient: owners reduce first, the
+  squared norms are summed over the data axis, and the fused AdamW kernel (or Adafactor's own
+  kernels) then update and push. Optimizer slots agree between ranks after `sync_replicas`."""
+  _need_two()
+  env = {"T5X_TEST_OPTIMIZER": kind}
+  sharded = _run_ranks("train", tmp_path / "z", env=env)
+  plain = _run_ranks("train", tmp_path / "p", env={**env, "T5X_B200_OPTIMIZER_SHARDING": "0"})
+  assert all(r["sharded"] for r in sharded) and not any(r["sharded"] for r in plain)
+  for run in (sharded, plain):
+    assert abs(run[0]["param_sum"] - run[1]["param_sum"]) <= 1e-6 * run[0]["param_abs"]
+    assert run[0]["slot_abs"] == pytest.approx(run[1]["slot_abs"], rel=1e-6)
+  a, b = sharded[0], plain[0]
+  assert a["loss"] == pytest.approx(b["loss"], rel=2e-3)
+  assert a["param_abs"] == pytest.approx(b["param_abs"], rel=1e-4)
+  assert a["slot_abs"] == pytest.approx(b["slot_abs"], rel=1e-2)
   assert a["bf16_abs"] == pytest.approx(a["param_abs"], rel=5e-3)
   for x, y in zip(a["first"], b["first"]):
     assert x == pytest.approx(y, rel=1e-2, abs=1e-4)

@@ -123,3 +123,21 @@ def test_overlapped_update_skips_parameters_that_owe_a_model_axis_sum():
   assert ctx._final_names("layers_0") == ["w", "scale"]
   st.model_size = 2
   assert ctx._final_names("layers_0") == ["w"]
+
+
+def test_optimizer_slots_are_matched_to_their_parameters():
+  """`sync_replicas` broadcasts each slot from its parameter's owner: both state layouts
+  (slots under the parameter path; parameter tree under each moment) resolve, counters do not."""
+  from t5x_b200.parallel import zero
+  names = ["enc/mlp/kernel", "enc/norm/scale"]
+  adafactor_like = {"enc": {"mlp": {"kernel": {"v_row": torch.ones(2), "v_col": torch.ones(3),
+                                               "m": torch.zeros(1), "v": torch.zeros(1)}},
+                            "norm": {"scale": {"v": torch.ones(4)}}}}
+  got = zero.state_leaves_by_param(names, adafactor_like)
+  assert [len(got[n]) for n in names] == [4, 1]
+  tree = lambda: {"enc": {"mlp": {"kernel": torch.ones(2, 3)}, "norm": {"scale": torch.ones(4)}}}
+  optax_like = {"0": {}, "1": {"0": {"count": torch.tensor(3), "mu": tree(), "nu": tree()},
+                               "1": {}, "2": {"count": torch.tensor(3)}}}
+  got = zero.state_leaves_by_param(names, optax_like)
+  assert [len(got[n]) for n in names] == [2, 2]
+  assert all(v.shape == (2, 3) for v in got["enc/mlp/kernel"])

@@ -250,3 +250,16 @@ def test_same_seed_gives_the_same_losses(tmp_path):
   _run_train(str(tmp_path / "a"), 3, actions={"TRAIN": [a]})
   _run_train(str(tmp_path / "b"), 3, actions={"TRAIN": [b]})
   assert a.values == b.values and len(a.values) == 3
+
+
+def test_profile_steps_hook_writes_a_trace_for_the_requested_steps(tmp_path, monkeypatch):
+  from t5x_b200.utils import profiling
+  assert profiling.parse_step_range("2:4") == (2, 4) and profiling.parse_step_range("3") == (3, 4)
+  with pytest.raises(ValueError):
+    profiling.parse_step_range("4:2")
+  monkeypatch.setenv("T5X_B200_PROFILE_STEPS", "1:3")
+  model_dir = str(tmp_path / "run")
+  _run_train(model_dir, 4)
+  files = sorted(os.path.basename(p) for p in glob.glob(os.path.join(model_dir, "profile", "*")))
+  assert files == ["steps_1_3.rank0.kernels.txt", "steps_1_3.rank0.trace.json"]
+  assert os.path.getsize(os.path.join(model_dir, "profile", files[1])) > 1000

@@ -61,3 +61,38 @@ def test_loss_and_grads_match_cpu_fp32():
     cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
     worst = max(worst, 1 - cos)
     assert cos > 0.98, (k, cos)
+
+
+def _three_steps():
+  """Losses of three optimizer steps from a fixed seed, and a checksum of the final weights."""
+  from t5x_b200 import train_state as ts_lib, trainer as trainer_lib
+  from t5x_b200.parallel import state as pstate
+  from t5x_b200.utils import schedules
+  pstate.setup_mesh(model_size=1, device=torch.device("cuda"))
+  model = _build("cuda", "bfloat16")
+  state = ts_lib.FlaxOptimTrainState.create(model.optimizer_def,
+                                            model.get_initial_variables(None, None))
+  lr_fn = schedules.create_learning_rate_scheduler("constant", 0.01, 0)
+  trainer = trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, 2)
+  losses = []
+  batch = {k: v.cpu() for k, v in _batch("cuda").items()}
+  for step in range(3):
+    summary = trainer.train(iter([batch]), 1, start_step=step).result()
+    losses.append(float(summary["loss"].value))
+  flat = torch.cat([p.detach().float().reshape(-1) for p in model.module.parameters()])
+  trainer.close()
+  return losses, float(flat.double().abs().sum())
+
+
+def test_same_seed_twice_stays_within_a_stated_bound():
+  """Two runs from the same seed. The kernels are deterministic except where partial sums meet
+  in memory by atomic adds (weight gradients cut along K, dQ of the attention backward, the
+  Adafactor row / column sums): the order of those adds varies, so results agree to rounding
+  of fp32 sums, not bit for bit. Bound: 2e-4 relative on each of three losses, 1e-5 on the
+  weights' absolute sum."""
+  a_losses, a_sum = _three_steps()
+  b_losses, b_sum = _three_steps()
+  assert a_losses[0] != a_losses[2]  # the steps did change the model
+  for x, y in zip(a_losses, b_losses):
+    assert x == pytest.approx(y, rel=2e-4), (a_losses, b_losses)
+  assert a_sum == pytest.approx(b_sum, rel=1e-5)

@@ -296,3 +296,39 @@ def test_projection_fused_with_cross_entropy(N, rows, vocab, tied, smoothing, sc
   # and the two library paths agree with each other more tightly than with fp32
   assert rel(got[0], old[0]) < 1e-5
   assert rel(got[3], old[3]) < 6e-3 and rel(got[4], old[4]) < 6e-3
+
+
+def test_fused_adamw_matches_the_generic_chain():
+  """clip_by_global_norm -> adamw through the one-kernel path against the same chain evaluated
+  transformation by transformation with tensor ops (fp32 throughout), three steps."""
+  from t5x_b200 import optimizers
+
+  def run(fused):
+    torch.manual_seed(5)
+    params = {"a": {"kernel": torch.randn(384, 515, device="cuda")},
+              "b": {"scale": torch.randn(1027, device="cuda")}}
+    for leaf in (params["a"]["kernel"], params["b"]["scale"]):
+      leaf.bf16 = leaf.to(torch.bfloat16)
+    opt_def = optimizers.chain([optimizers.clip_by_global_norm(0.5),
+                                optimizers._adamw(3e-3, weight_decay=0.05)])
+    assert opt_def.fused_plan is not None
+    if not fused:
+      opt_def.fused_plan = None
+    opt = opt_def.create(params)
+    for step in range(3):
+      g = {"a": {"kernel": torch.randn(384, 515, device="cuda") * (step + 1)},
+           "b": {"scale": torch.randn(1027, device="cuda")}}
+      opt = opt.apply_gradient(g)
+    native.check_status()
+    adam = opt.state.param_states["1"]["0"]
+    return opt.target, adam
+
+  (pf, sf), (pg, sg) = run(True), run(False)
+  for path in (("a", "kernel"), ("b", "scale")):
+    f, g = pf[path[0]][path[1]], pg[path[0]][path[1]]
+    torch.testing.assert_close(f, g, rtol=2e-5, atol=2e-6)
+    torch.testing.assert_close(f.bf16.float(), f, rtol=8e-3, atol=1e-3)
+    for slot in ("mu", "nu"):
+      torch.testing.assert_close(sf[slot][path[0]][path[1]], sg[slot][path[0]][path[1]],
+                                 rtol=2e-5, atol=1e-7)
+  assert int(sf["count"]) == int(sg["count"]) == 3
