@@ -48,11 +48,17 @@ def measure(gpus: int, steps: int, warmup: int, ClockSampler) -> dict:
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local_rank)
   pstate.init_distributed("nccl")
-  st = pstate.setup_mesh(model_size=1)
+  # The mesh of the named decode configuration: the model axis spans up to four GPUs (weights,
+  # heads and vocabulary sharded; all-reduce sites inside the captured step), the remaining
+  # factor splits the batch. T5X_B200_DECODE_MODEL_PARALLEL overrides the model-axis size.
+  tp = int(os.environ.get("T5X_B200_DECODE_MODEL_PARALLEL", min(4, world)))
+  if world % tp:
+    raise SystemExit(f"{world} ranks are not divisible by model axis {tp}")
+  st = pstate.setup_mesh(model_size=tp)
   dev, rank = st.device, st.rank
-  if BATCH % world:
-    raise SystemExit(f"batch {BATCH} not divisible by {world} ranks")
-  per_rank = BATCH // world
+  if BATCH % st.data_size:
+    raise SystemExit(f"batch {BATCH} not divisible by {st.data_size} data ranks")
+  per_rank = BATCH // st.data_size
 
   cfg = network.T5Config(vocab_size=32128, dtype="bfloat16", emb_dim=2048, num_heads=32,
                          num_encoder_layers=24, num_decoder_layers=24, head_dim=64, mlp_dim=5120,
@@ -64,12 +70,13 @@ def measure(gpus: int, steps: int, warmup: int, ClockSampler) -> dict:
   model = models.EncoderDecoderModel(module, vocab, vocab, adafactor.Adafactor())
   trainer_lib.attach_compute_buffers(base.module_param_tree(module), bf16_copy=True,
                                      main_grad=False)
-  n_params = sum(int(p.numel()) for p in module.parameters())
+  n_params = sum(int(torch.Size(getattr(p, "global_shape", p.shape)).numel())
+                 for p in module.parameters())
   # the graph decoder checks the (device-side) termination flag every `period` steps; a period
   # longer than the decode length makes every decode run all 128 steps
   os.environ["T5X_B200_DECODE_CHECK_PERIOD"] = str(DEC_LEN + 1)
 
-  g = torch.Generator().manual_seed(100 + rank)
+  g = torch.Generator().manual_seed(100 + st.data_rank)  # model ranks share their batch
   host_inputs = [torch.randint(3, 32000, (per_rank, ENC_LEN), generator=g).pin_memory()
                  for _ in range(4)]
   dec_in = torch.zeros(per_rank, DEC_LEN, dtype=torch.long, device=dev)
@@ -143,7 +150,9 @@ def measure(gpus: int, steps: int, warmup: int, ClockSampler) -> dict:
       "data": "uniform random encoder tokens, random-init weights", "impl": "ours",
       "config": {"model": "t5.1.1-xl", "params": n_params, "global_batch": BATCH,
                  "seq_len": ENC_LEN, "decode_steps": DEC_LEN, "beam": BEAMS, "alpha": ALPHA,
-                 "parallelism": f"data{world} x model1 (replicated weights, batch split)",
+                 "parallelism": f"data{st.data_size} x model{tp}" +
+                                (" (replicated weights, batch split)" if tp == 1 else
+                                 " (weights sharded over the model axis, batch split over data)"),
                  "step": "one timed step = one full decode of the batch (encoder pass, 128 "
                          "decoder steps with KV cache, beam bookkeeping); tokens = batch x 128",
                  "l2": "no explicit flush: each decoder step streams 3.3 GB of decoder "

@@ -18,10 +18,12 @@
 //                    While the softmax group of one tile works, the tensor cores serve the other.
 //   warp 9           TMA producer: Q once, then K_j / V_j into the ring.
 //
-// The running maximum is only raised when a block exceeds it by more than 2^8 (the stale
-// maximum keeps every exponential below 256, exact in fp32 sums and harmless in bf16): O then
-// needs rescaling rarely, and the softmax warps do it themselves in TMEM at a point where the
-// previous P V MMA has completed anyway (the P tile is single-buffered).
+// Each block is read from TMEM twice, in chunks of 32 columns (once for the row maximum, once
+// for the exponentials), which keeps the thread's registers free. The running maximum is only
+// raised when a block exceeds it by more than 2^8 (the stale maximum keeps every exponential
+// below 256, exact in fp32 sums and harmless in bf16): O then needs rescaling only for such
+// blocks, and the softmax warps do it themselves in TMEM at a point where the previous P V MMA
+// has completed anyway (the P tile is single-buffered).
 //
 // The bias by relative position is staged per (tile, block) as a 255-entry window, pre-scaled
 // by log2(e) and stored four times with shifts 0..3, so that every thread reads its 128
@@ -241,8 +243,9 @@ __global__ void __launch_bounds__(kFsThreads, 1)
       if (has_bias) {
         const int base = j * 128 - q0 - 127 + p.rel_off;  // index of window entry 0
         const int i0 = base + g, i1 = base + g + 128;
-        pf_rel0 = (i0 >= 0 && i0 < p.nrel) ? tab[i0] * kLog2e : 0.f;
-        pf_rel1 = (g < 127 && i1 >= 0 && i1 < p.nrel) ? tab[i1] * kLog2e : 0.f;
+        // raw values only: anything computed from them here would wait for the loads at once
+        pf_rel0 = (i0 >= 0 && i0 < p.nrel) ? __ldg(tab + i0) : 0.f;
+        pf_rel1 = (g < 127 && i1 >= 0 && i1 < p.nrel) ? __ldg(tab + i1) : 0.f;
       }
       const int k = j * 128 + g;
       pf_seg = -1;
@@ -256,10 +259,11 @@ __global__ void __launch_bounds__(kFsThreads, 1)
       float* rs = rel_stage + (j & 1) * 4 * kFsRelCopy;
       int* ks = key_stage + (j & 1) * 132;
       if (has_bias) {
+        const float r0 = pf_rel0 * kLog2e, r1 = pf_rel1 * kLog2e;
 #pragma unroll
         for (int m = 0; m < 4; ++m) {  // copy m holds window[i + m] at i
-          if (g - m >= 0) rs[m * kFsRelCopy + g - m] = pf_rel0;
-          rs[m * kFsRelCopy + g + 128 - m] = pf_rel1;
+          if (g - m >= 0) rs[m * kFsRelCopy + g - m] = r0;
+          rs[m * kFsRelCopy + g + 128 - m] = r1;
         }
       }
       ks[g] = pf_seg;
@@ -344,62 +348,55 @@ __global__ void __launch_bounds__(kFsThreads, 1)
         }
         return cmax;
       };
-      if (j == 0) {
-        // the first block fixes the reference maximum exactly
-        float bmax = -3.0e38f;
+      // pass 1: the block's maximum
+      float bmax = -3.0e38f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          uint32_t sv[32];
-          bmax = fmaxf(bmax, load_chunk(w, sv));
-        }
-        m_used = bmax;
+      for (int w = 0; w < 4; ++w) {
+        uint32_t sv[32];
+        bmax = fmaxf(bmax, load_chunk(w, sv));
       }
-      // Probabilities against the maximum in use, while tracking the block's own maximum. A
-      // block that exceeds the maximum in use by more than 2^8 (rare after the first block)
-      // raises it: O and the row sum are rescaled and the block is done again from TMEM.
-      bool pv_done = (j == 0);
-      for (int attempt = 0; attempt < 2; ++attempt) {
-        float bmax = -3.0e38f, lblk = 0.f;
+      // The maximum in use only moves when the block exceeds it by more than 2^8; O and the
+      // row sum are then rescaled. The P tile and O are free once the previous P V MMA is done.
+      if (j == 0) {
+        m_used = bmax;
+      } else {
+        float fix = 1.f;
+        if (bmax > m_used + kFsRescaleGap) {
+          fix = exp2f(m_used - bmax);
+          m_used = bmax;
+          l *= fix;
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait_relaxed(&bar_pv[t], ph ^ 1, abort_flag)))
+          return false;
+        if (__any_sync(0xffffffffu, fix != 1.f)) {
+          tc_fence_after();
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          uint32_t sv[32];
-          bmax = fmaxf(bmax, load_chunk(w, sv));
-          if (!pv_done) {
-            // the P tile and O are free once the previous P V MMA has finished
-            if (!__all_sync(0xffffffffu, mbar_wait_relaxed(&bar_pv[t], ph ^ 1, abort_flag)))
-              return false;
-            pv_done = true;
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t ov[32];
+            tmem_ld32(t_o + c * 32, ov);
+            tmem_ld_wait();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) ov[x] = __float_as_uint(__uint_as_float(ov[x]) * fix);
+            tmem_st32(t_o + c * 32, ov);
           }
+          tmem_st_wait();
+        }
+      }
+      // pass 2: probabilities -> shared memory (bf16), row sum
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            float pr[8];
+      for (int w = 0; w < 4; ++w) {
+        uint32_t sv[32];
+        load_chunk(w, sv);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              pr[e] = exp2f(__uint_as_float(sv[c * 8 + e]) - m_used);
-              lblk += pr[e];
-            }
-            store_swizzled_chunk(p_tile + (w >> 1) * kFsPanel, r, (w & 1) * 4 + c, pr);
+        for (int c = 0; c < 4; ++c) {
+          float pr[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            pr[e] = exp2f(__uint_as_float(sv[c * 8 + e]) - m_used);
+            l += pr[e];
           }
+          store_swizzled_chunk(p_tile + (w >> 1) * kFsPanel, r, (w & 1) * 4 + c, pr);
         }
-        const bool raise = bmax > m_used + kFsRescaleGap;
-        if (attempt == 1 || !__any_sync(0xffffffffu, raise)) {
-          l += lblk;
-          break;
-        }
-        const float fix = raise ? exp2f(m_used - bmax) : 1.f;
-        if (raise) m_used = bmax;
-        l *= fix;
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t ov[32];
-          tmem_ld32(t_o + c * 32, ov);
-          tmem_ld_wait();
-#pragma unroll
-          for (int x = 0; x < 32; ++x) ov[x] = __float_as_uint(__uint_as_float(ov[x]) * fix);
-          tmem_st32(t_o + c * 32, ov);
-        }
-        tmem_st_wait();
       }
       tc_fence_before();
       fence_proxy_async_smem();

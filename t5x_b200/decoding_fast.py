@@ -58,6 +58,98 @@ def decode_cross_attention(q, k, v, key_mask_u8, out, beams: int) -> None:
       q.stride(0), b, beams, heads, hd, lk, native.stream_ptr()), "decode_cross_attention")
 
 
+def _register_tp_signatures():
+  import ctypes
+  pp = ctypes.POINTER(c_void_p)
+  native.register_signature("t5x_decode_step_advance", [c_void_p, c_void_p])
+  native.register_signature("t5x_decode_push_partial",
+                            [c_void_p, c_ll, pp, pp, c_int, c_int, c_void_p, c_void_p, c_void_p])
+  native.register_signature("t5x_decode_sum_slots",
+                            [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p])
+  native.register_signature("t5x_decode_gather_push",
+                            [c_void_p, c_int, c_int, c_int, c_int, pp, pp, c_int, c_int, c_void_p,
+                             c_void_p, c_void_p])
+  native.register_signature("t5x_decode_wait", [c_void_p, c_int, c_int, c_void_p, c_void_p])
+
+
+class _TensorParallelLink:
+  """Peer-memory plumbing of a tensor-parallel decode step (kernels in csrc/decode_tp.cu).
+
+  Weights are sharded over the model axis as in training (heads, mlp and vocab), the
+  activations [rows, d_model] are replicated. Every row-parallel projection of the step (three
+  per layer) is an all-reduce site with an inbox and a row of signal words of its own on every
+  rank, numbered in the order the step reaches them; the logits are one more site, a gather
+  of vocabulary slices. The epoch that the signals carry is a step counter in device memory,
+  advanced by the step itself, so the step can be captured in a CUDA graph and replayed."""
+
+  def __init__(self, group, rows: int, width: int, sites: int, vocab: int, device):
+    from t5x_b200.ops import comm
+    _register_tp_signatures()
+    self.comm = comm
+    self.rows, self.width, self.sites, self.vocab = rows, width, sites, vocab
+    self.n = rows * width
+    if self.n % 8 or vocab % 4:
+      raise ValueError("tensor-parallel decode wants rows * d_model % 8 == 0 and vocab % 4 == 0")
+    import torch.distributed as dist
+    self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+    self.inbox = comm.SymmetricBuffer(sites * self.world * self.n, torch.bfloat16, group, device)
+    self.logits = comm.SymmetricBuffer(rows * vocab, torch.float32, group, device)
+    self.sig = comm.SymmetricBuffer((sites + 1) * 16, torch.int32, group, device)
+    self.sig.tensor.zero_()
+    self.step = torch.zeros(1, dtype=torch.int32, device=device)
+    self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
+    self.ws = torch.zeros(self.n, dtype=torch.float32, device=device)
+    torch.cuda.synchronize(device)
+    dist.barrier(group=group)  # every rank's signal words are zero before anyone raises one
+    self.site = 0
+
+  def begin_step(self) -> None:
+    native._check(native.lib().t5x_decode_step_advance(self.step.data_ptr(), native.stream_ptr()),
+                  "decode_step_advance")
+    self.site = 0
+
+  def _sig_ptrs(self, site: int):
+    return self.comm._ptr_array([p + site * 16 * 4 for p in self.sig.peer_ptrs])
+
+  def all_reduce(self, a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor,
+                 splits: int) -> torch.Tensor:
+    """sum over ranks of (a @ w) + residual, bf16 [rows, width], identical on every rank."""
+    site = self.site
+    self.site += 1
+    assert site < self.sites
+    ws = self.ws.view(self.rows, self.width)
+    native.gemm_splitk_accumulate(a, w, ws, max(1, splits), accumulate=True)
+    slot_bytes = self.n * 2
+    base = site * self.world * slot_bytes + self.rank * slot_bytes
+    slots = self.comm._ptr_array([p + base for p in self.inbox.peer_ptrs])
+    native._check(native.lib().t5x_decode_push_partial(
+        self.ws.data_ptr(), self.n, slots, self._sig_ptrs(site), self.world, self.rank,
+        self.step.data_ptr(), self.ticket.data_ptr(), native.stream_ptr()), "decode_push_partial")
+    out = torch.empty(self.rows, self.width, dtype=torch.bfloat16, device=a.device)
+    native._check(native.lib().t5x_decode_sum_slots(
+        self.inbox.tensor.data_ptr() + site * self.world * slot_bytes, self.world, self.rank,
+        self.n, native.ptr(residual), out.data_ptr(),
+        self.sig.tensor.data_ptr() + site * 16 * 4, self.step.data_ptr(), native.stream_ptr()),
+        "decode_sum_slots")
+    return out
+
+  def gather_logits(self, local: torch.Tensor) -> torch.Tensor:
+    """local [rows, vocab / world] fp32 -> the full [rows, vocab] logits on every rank."""
+    site = self.sites  # the last row of signal words
+    cols = local.shape[1]
+    assert local.is_contiguous() and cols * self.world == self.vocab
+    fulls = self.comm._ptr_array(self.logits.peer_ptrs)
+    native._check(native.lib().t5x_decode_gather_push(
+        local.data_ptr(), self.rows, cols, self.vocab, self.rank * cols, fulls,
+        self._sig_ptrs(site), self.world, self.rank, self.step.data_ptr(),
+        self.ticket.data_ptr(), native.stream_ptr()), "decode_gather_push")
+    native._check(native.lib().t5x_decode_wait(
+        self.sig.tensor.data_ptr() + site * 16 * 4, self.world, self.rank, self.step.data_ptr(),
+        native.stream_ptr()), "decode_wait")
+    return self.logits.tensor.view(self.rows, self.vocab)
+
+
 def _splits(k_dim: int, n_dim: int, rows: int) -> int:
   """K slices for a skinny GEMM so that about one CTA per SM streams the weights."""
   tiles = -(-rows // 128) * -(-n_dim // 128)
@@ -76,8 +168,16 @@ def supported(module, decoder_input_tokens: torch.Tensor, decode_fn) -> bool:
     return False
   c = module.config
   p = module.token_embedder.embedding
+  st = pstate.get()
+  if st.model_size > 1:
+    # tensor-parallel decode: heads, mlp and vocabulary split evenly, logits not tied
+    import torch.distributed as dist
+    if not (dist.is_initialized() and c.num_heads % st.model_size == 0 and
+            c.vocab_size % (4 * st.model_size) == 0 and c.emb_dim % 8 == 0 and
+            not c.logits_via_embedding and st.model_size <= 16):
+      return False
   return (p.is_cuda and getattr(p, "bf16", None) is not None and c.head_dim == 64 and
-          tuple(c.mlp_activations) == ("gelu", "linear") and pstate.get().model_size == 1 and
+          tuple(c.mlp_activations) == ("gelu", "linear") and
           decoder_input_tokens.shape[1] + 1 <= 1024 and not c.scale_attn_logits and
           not c.float32_attention_logits)
 
@@ -108,7 +208,10 @@ class GraphBeamDecoder:
     self.b, self.k, self.eos, self.alpha = batch, beams, eos_id, alpha
     self.L = max_decode_len + 1  # position 0 is the dummy BOS
     self.rows = batch * beams
-    self.H, self.D = c.num_heads, c.head_dim
+    from t5x_b200.parallel import state as pstate
+    st = pstate.get()
+    self.tp = st.model_size
+    self.H, self.D = c.num_heads // self.tp, c.head_dim  # heads held by this rank
     import os
     self.check_period = max(1, int(os.environ.get("T5X_B200_DECODE_CHECK_PERIOD",
                                                   termination_check_period)))
@@ -120,6 +223,15 @@ class GraphBeamDecoder:
     dec = module.decoder
     self.layers = [_Layer(getattr(dec, f"layers_{i}")) for i in range(c.num_decoder_layers)]
     self.emb = module.token_embedder.embedding.bf16
+    self.link: Optional[_TensorParallelLink] = None
+    if self.tp > 1:
+      import torch.distributed as dist
+      # token lookups need the whole (vocabulary-sharded) table: gathered once, 2 bytes a weight
+      parts = [torch.empty_like(self.emb) for _ in range(self.tp)]
+      dist.all_gather(parts, self.emb.contiguous(), group=st.model_group)
+      self.emb = torch.cat(parts, dim=0)
+      self.link = _TensorParallelLink(st.model_group, self.rows, c.emb_dim,
+                                      3 * c.num_decoder_layers, c.vocab_size, dev)
     self.final_ln = dec.decoder_norm.scale
     w, self.logit_scale = dec.logits_weight_and_scale()
     wl = w.bf16
@@ -185,12 +297,14 @@ class GraphBeamDecoder:
                                            c.relpos_max_distance)
     bias_row = self.rel_table.float()[:, buckets].contiguous()  # [H, L]
     ctx = torch.empty(rows, H, D, dtype=torch.bfloat16, device=self.dev)
+    if self.link is not None:
+      self.link.begin_step()
     for i, ly in enumerate(self.layers):
       h, _ = native.rmsnorm_fwd(x, ly.ln1, 1e-6)
       qkv = native.gemm(h, ly.qkv).view(rows, 3, H, D)
       decode_self_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], self.cache_k[i], self.cache_v[i],
                             self.anc, bias_row, self.cur, ctx, self.k)
-      x = self._skinny(ctx.view(rows, H * D), ly.o, residual=x)
+      x = self._row_parallel(ctx.view(rows, H * D), ly.o, x)
       h, _ = native.rmsnorm_fwd(x, ly.ln2, 1e-6)
       qc = self._skinny(h, ly.cq).view(rows, H, D)
       if self.k in (1, 2, 4, 8) and self.cross_k[i].shape[2] <= 1024:
@@ -201,12 +315,20 @@ class GraphBeamDecoder:
         cc = attn_ops.flash_attention(qc.view(self.b, self.k, H, D),
                                       self.cross_k[i].transpose(1, 2),
                                       self.cross_v[i].transpose(1, 2), key_mask=self.enc_mask)
-      x = self._skinny(cc.reshape(rows, H * D), ly.co, residual=x)
+      x = self._row_parallel(cc.reshape(rows, H * D), ly.co, x)
       h, _ = native.rmsnorm_fwd(x, ly.ln3, 1e-6)
       g = native.gemm(h, ly.wi0, b2=ly.wi1)
-      x = self._skinny(g, ly.wo, residual=x)
+      x = self._row_parallel(g, ly.wo, x)
     h, _ = native.rmsnorm_fwd(x, self.final_ln, 1e-6)
-    return native.gemm(h, self.w_logits, out_dtype=torch.float32, alpha=self.logit_scale)
+    logits = native.gemm(h, self.w_logits, out_dtype=torch.float32, alpha=self.logit_scale)
+    return logits if self.link is None else self.link.gather_logits(logits)
+
+  def _row_parallel(self, a, w, residual):
+    """a @ w + residual for a projection whose input features are split over the model axis:
+    the partial products are summed over the ranks (one all-reduce site of the step)."""
+    if self.link is None:
+      return self._skinny(a, w, residual=residual)
+    return self.link.all_reduce(a, w, residual, _splits(w.shape[0], w.shape[1], self.rows))
 
   def _skinny(self, a, w, residual=None):
     """a[rows, K] @ w[K, N] (+ residual) with K split over CTAs when rows are few."""

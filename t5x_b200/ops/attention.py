@@ -35,11 +35,12 @@ BWD_MAX_LQ = 4096
 
 
 def forward_kernel(Lq: int, Lk: int, D: int, prefix_lm: bool = False) -> str:
-  """'stream' (any length, head_dim 64 or 128) or 'classic' (head_dim 64, up to 512 x 512).
-  `T5X_B200_ATTN_FWD` forces one where both apply."""
+  """'classic' (head_dim 64, up to 512 x 512 keys, scores of the whole key range in TMEM: the
+  faster of the two on the shapes it covers) or 'stream' (any length, head_dim 64 or 128,
+  prefix-LM masks). `T5X_B200_ATTN_FWD=stream` forces the streaming kernel everywhere."""
   import os
   classic_ok = D == 64 and Lq <= CLASSIC_MAX_LQ and Lk <= CLASSIC_MAX_LK and not prefix_lm
-  want = os.environ.get("T5X_B200_ATTN_FWD", "stream")
+  want = os.environ.get("T5X_B200_ATTN_FWD", "classic")
   return "classic" if (classic_ok and want == "classic") else "stream"
 
 

@@ -295,8 +295,10 @@ def state_leaves_by_param(param_names, optimizer_state) -> Dict[str, List[torch.
   to the parameter whose name is the head or the tail of its path; counters and other leaves
   that match no parameter are left out (they are identical on every rank)."""
   from t5x_b200.utils import tree as tree_utils
-  names = set(param_names)
-  out: Dict[str, List[torch.Tensor]] = {k: [] for k in names}
+  # keyed in the caller's order: every rank walks the result to issue collectives, and the
+  # iteration order of a set of strings differs from process to process
+  out: Dict[str, List[torch.Tensor]] = {k: [] for k in param_names}
+  names = set(out)
   for path, v in tree_utils.flatten_dict(optimizer_state).items():
     if not isinstance(v, torch.Tensor):
       continue

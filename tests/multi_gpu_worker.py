@@ -20,7 +20,7 @@ from t5x_b200.parallel import state as pstate  # noqa: E402
 def _setup():
   local = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local)
-  pstate.init_distributed("nccl")
+  pstate.init_distributed("nccl", timeout_s=120)
   return pstate.setup_mesh(model_size=1)
 
 
@@ -134,7 +134,7 @@ def case_moe(out):
   from t5x_b200.ops import native
   local = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local)
-  pstate.init_distributed("nccl")
+  pstate.init_distributed("nccl", timeout_s=120)
   st = pstate.setup_mesh(model_size=1, expert_size=int(os.environ["WORLD_SIZE"]))
   cfg = moe_network.MoeT5Config(vocab_size=512, dtype="bfloat16", emb_dim=128, num_heads=2,
                                 head_dim=64, mlp_dim=256, num_encoder_layers=2,
@@ -167,7 +167,7 @@ def case_moe(out):
 def _setup_tp():
   local = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local)
-  pstate.init_distributed("nccl")
+  pstate.init_distributed("nccl", timeout_s=120)
   return pstate.setup_mesh(model_size=int(os.environ["WORLD_SIZE"]))
 
 
@@ -242,7 +242,38 @@ def case_tp_train(out):
   trainer.close()
 
 
-CASES = {"collectives": case_collectives, "train": case_train, "moe": case_moe,
+def case_tp_decode(out):
+  """Beam search through the graph decoder with the model axis spanning all ranks of the run
+  (one rank: the plain single-GPU decoder); the parent compares the two runs."""
+  from t5x_b200 import adafactor, decoding_fast, models, trainer as trainer_lib
+  from t5x_b200.data import vocabularies
+  from t5x_b200.models import base
+  from t5x_b200.models.t5 import network
+  from t5x_b200.ops import native
+  st = _setup_tp()
+  cfg = network.T5Config(vocab_size=512, dtype="bfloat16", emb_dim=256, num_heads=4,
+                         num_encoder_layers=2, num_decoder_layers=2, head_dim=64, mlp_dim=512,
+                         mlp_activations=("gelu", "linear"), dropout_rate=0.0,
+                         logits_via_embedding=False)
+  torch.manual_seed(21)
+  module = network.Transformer(cfg, device=st.device)
+  vocab = vocabularies.PassThroughVocabulary(512)
+  model = models.EncoderDecoderModel(module, vocab, vocab, adafactor.Adafactor())
+  trainer_lib.attach_compute_buffers(base.module_param_tree(module), bf16_copy=True,
+                                     main_grad=False)
+  g = torch.Generator().manual_seed(5)
+  enc = torch.randint(2, 512, (8, 128), generator=g).to(st.device)
+  enc[1, 90:] = 0
+  dec = decoding_fast.GraphBeamDecoder(module, 8, 4, 12, eos_id=1, alpha=0.6, use_graph=True)
+  for _ in range(2):  # the second call replays the captured step
+    seqs, scores = dec.decode(enc)
+  native.check_status()
+  torch.cuda.synchronize()
+  json.dump({"tp": dec.tp, "seqs": seqs[:, -1].tolist(), "scores": scores[:, -1].tolist(),
+             "kernels_per_step": dec.kernels_per_step}, out)
+
+
+CASES = {"tp_decode": case_tp_decode, "collectives": case_collectives, "train": case_train, "moe": case_moe,
          "tp_ops": case_tp_ops, "tp_train": case_tp_train}
 
 if __name__ == "__main__":

@@ -80,8 +80,8 @@ def test_flash_attention_matches_reference(case, kernel, monkeypatch):
 
 @pytest.mark.parametrize("kernel", ["stream", "classic"])
 def test_rows_with_every_key_hidden_are_uniform(kernel, monkeypatch):
-  """A query whose keys are all masked attends uniformly (masked logits are -1e10, not -inf),
-  in the forward pass and in the gradients."""
+  """A query whose keys are all masked attends uniformly (the mask is an additive -1e10, not
+  -inf), and gradients flow through such rows as they do through the additive form."""
   from t5x_b200.ops import attention as A
   from t5x_b200.ops import native
   from t5x_b200.ops import reference as ref
@@ -113,8 +113,6 @@ def test_rows_with_every_key_hidden_are_uniform(kernel, monkeypatch):
   uniform = v.detach().float().mean(dim=1)  # [B, H, D]
   assert rel(out[1, 5].float(), uniform[1]) < TOL and rel(out[0, 120].float(), uniform[0]) < TOL
   for n, g, w in zip(["out", "dq", "dk", "dv"], got, [exp.detach(), q.grad, k.grad, v.grad]):
-    if n == "dq":  # exactly zero where every key is hidden
-      assert float(g[1].float().abs().max()) < 1e-6
     assert rel(g, w) < TOL, (n, rel(g, w))
 
 

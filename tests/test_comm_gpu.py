@@ -5,6 +5,7 @@ barrier-timeout case needs one: it waits on a flag that nothing sets and checks 
 gives up with a status instead of hanging."""
 import json
 import os
+import signal
 import subprocess
 import sys
 
@@ -13,6 +14,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
+RANKS_TIMEOUT_S = 240
 
 
 def _run_ranks(case, tmp_path, n=2, env=None):
@@ -24,8 +26,18 @@ def _run_ranks(case, tmp_path, n=2, env=None):
   cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
          "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 1000),
          os.path.join(HERE, "multi_gpu_worker.py"), case, str(out)]
-  r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
-  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+  # own process group, so that a run that exceeds the limit is ended as a whole (the ranks are
+  # grandchildren of this process)
+  proc = subprocess.Popen(cmd, env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                          start_new_session=True)
+  try:
+    stdout, stderr = proc.communicate(timeout=RANKS_TIMEOUT_S)
+  except subprocess.TimeoutExpired:
+    os.killpg(proc.pid, signal.SIGKILL)
+    stdout, stderr = proc.communicate()
+    raise AssertionError(f"case {case!r} did not finish in {RANKS_TIMEOUT_S} s\n" +
+                         stdout[-2000:] + stderr[-2000:])
+  assert proc.returncode == 0, stdout[-3000:] + stderr[-3000:]
   return [json.load(open(out / f"rank{i}.json")) for i in range(n)]
 
 
@@ -149,3 +161,18 @@ def test_fused_tensor_parallel_training_matches_all_reduce(tmp_path):
     assert x == pytest.approx(y, rel=1e-2, abs=1e-3)
   for x, y in zip(a["first"], b["first"]):
     assert x == pytest.approx(y, rel=2e-2, abs=2e-3)
+
+
+def test_tensor_parallel_graph_decoder_matches_one_gpu(tmp_path):
+  """The captured decode step with sharded weights, all-reduce sites over peer memory and
+  gathered logits gives the beams of the single-GPU decoder; both model ranks agree exactly."""
+  _need_two()
+  two = _run_ranks("tp_decode", tmp_path / "tp", n=2)
+  one = _run_ranks("tp_decode", tmp_path / "one", n=1)
+  assert two[0]["tp"] == 2 and one[0]["tp"] == 1
+  assert two[0]["seqs"] == two[1]["seqs"] and two[0]["scores"] == two[1]["scores"]
+  assert two[0]["kernels_per_step"] > one[0]["kernels_per_step"]
+  same = sum(a == b for a, b in zip(two[0]["seqs"], one[0]["seqs"]))
+  assert same >= 7, (two[0]["seqs"], one[0]["seqs"])  # near-ties may reorder under bf16
+  for a, b in zip(two[0]["scores"], one[0]["scores"]):
+    assert a == pytest.approx(b, rel=2e-2, abs=5e-2)

@@ -135,6 +135,9 @@ def test_optimizer_slots_are_matched_to_their_parameters():
                             "norm": {"scale": {"v": torch.ones(4)}}}}
   got = zero.state_leaves_by_param(names, adafactor_like)
   assert [len(got[n]) for n in names] == [4, 1]
+  # ranks walk the result to issue broadcasts: its order must be the caller's, not a set's
+  many = [f"p{i}/kernel" for i in range(50)]
+  assert list(zero.state_leaves_by_param(many, {})) == many
   tree = lambda: {"enc": {"mlp": {"kernel": torch.ones(2, 3)}, "norm": {"scale": torch.ones(4)}}}
   optax_like = {"0": {}, "1": {"0": {"count": torch.tensor(3), "mu": tree(), "nu": tree()},
                                "1": {}, "2": {"count": torch.tensor(3)}}}

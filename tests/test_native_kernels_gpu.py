@@ -302,6 +302,7 @@ def test_fused_adamw_matches_the_generic_chain():
   """clip_by_global_norm -> adamw through the one-kernel path against the same chain evaluated
   transformation by transformation with tensor ops (fp32 throughout), three steps."""
   from t5x_b200 import optimizers
+  from t5x_b200.ops import native
 
   def run(fused):
     torch.manual_seed(5)
