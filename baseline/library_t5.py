@@ -218,7 +218,10 @@ def run(args, ClockSampler, model_sizes, default_microbatches, baseline_tok_s_pe
   per_rank = args.batch // world
   # half the microbatch of the headline run: autograd keeps fp32 gradients, bf16 weight casts
   # and unfused activations alive, which needs the room
-  n_micro = args.microbatches or min(per_rank, 2 * default_microbatches(args.model, world))
+  # 8 sequences per microbatch at every rank count: plain autograd keeps fp32 logits and all
+  # attention probabilities alive, which is what bounds the microbatch here
+  n_micro = args.microbatches or min(per_rank, {1: 16, 2: 8, 4: 4}.get(world, 2)
+                                     if args.model == "xxl" else 1)
   rng = np.random.default_rng(100 + rank)
   host = []
   for _ in range(4):

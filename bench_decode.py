@@ -28,7 +28,7 @@ def run(args, ClockSampler) -> None:
     dist.destroy_process_group()
 
 
-def measure(gpus: int, steps: int, warmup: int, ClockSampler) -> dict:
+def measure(gpus: int, steps: int, warmup: int, ClockSampler, model_parallel: int = 0) -> dict:
   """Builds the XL model, times `steps` decodes of the batch (device-timed and end to end) and
   returns the result record (the same on every rank)."""
   import torch
@@ -48,10 +48,13 @@ def measure(gpus: int, steps: int, warmup: int, ClockSampler) -> dict:
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local_rank)
   pstate.init_distributed("nccl")
-  # The mesh of the named decode configuration: the model axis spans up to four GPUs (weights,
-  # heads and vocabulary sharded; all-reduce sites inside the captured step), the remaining
-  # factor splits the batch. T5X_B200_DECODE_MODEL_PARALLEL overrides the model-axis size.
-  tp = int(os.environ.get("T5X_B200_DECODE_MODEL_PARALLEL", min(4, world)))
+  # Default mesh: the batch split over all GPUs with replicated weights (the XL weights fit one
+  # GPU many times over, and a decode step of a few dozen rows is bound by latency, which the
+  # all-reduce sites of a model axis add to). `model_parallel` (or
+  # T5X_B200_DECODE_MODEL_PARALLEL) puts that many GPUs on a model axis instead: weights, heads
+  # and vocabulary sharded, all-reduce sites inside the captured step; the named decode
+  # configuration is data2 x model4.
+  tp = int(model_parallel or os.environ.get("T5X_B200_DECODE_MODEL_PARALLEL", 1))
   if world % tp:
     raise SystemExit(f"{world} ranks are not divisible by model axis {tp}")
   st = pstate.setup_mesh(model_size=tp)

@@ -351,19 +351,22 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 // Backward
 // ---------------------------------------------------------------------------------------
 // delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d]
+template <int D>
 __global__ void __launch_bounds__(256)
     attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
                       float* __restrict__ delta, int B, int H, int Lq, long long do_sb,
                       long long do_sl, long long do_sh, long long o_sb, long long o_sl,
                       long long o_sh) {
-  // eight lanes per (b, q, h): 64 elements -> one 16-byte load per lane and tensor; four items
-  // in flight per thread. Requires 16-byte aligned rows (strides multiples of 8 elements).
+  // D / 8 lanes per (b, q, h): one 16-byte load per lane and tensor; four items in flight per
+  // thread. Requires 16-byte aligned rows (strides multiples of 8 elements).
+  constexpr int kLanes = D / 8;           // 8 or 16
+  constexpr int kShift = (D == 64) ? 3 : 4;
   const long long total = static_cast<long long>(B) * Lq * H;
-  const int sub = threadIdx.x & 7;
-  const long long first = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 3;
-  const long long stride = (static_cast<long long>(gridDim.x) * blockDim.x) >> 3;
-  // the four 8-lane groups of a warp leave the loop together (the shuffles use the full mask)
-  const int group = (threadIdx.x & 31) >> 3;
+  const int sub = threadIdx.x & (kLanes - 1);
+  const long long first = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> kShift;
+  const long long stride = (static_cast<long long>(gridDim.x) * blockDim.x) >> kShift;
+  // the lane groups of a warp leave the loop together (the shuffles use the full mask)
+  const int group = (threadIdx.x & 31) >> kShift;
   for (long long w0 = first; w0 - group < total; w0 += 4 * stride) {
     uint4 a[4], c[4];
     long long out[4];
@@ -395,6 +398,7 @@ __global__ void __launch_bounds__(256)
           s += fa.x * fc.x + fa.y * fc.y;
         }
       }
+      if (kLanes == 16) s += __shfl_xor_sync(0xffffffffu, s, 8);
       s += __shfl_xor_sync(0xffffffffu, s, 4);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       s += __shfl_xor_sync(0xffffffffu, s, 1);
@@ -403,38 +407,49 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// head_dim 64: Q / dO double-buffered, the scores of the next query block are issued while the
+// softmax warps work, dQ partial tiles alternate between two TMEM buffers. head_dim 128: operand
+// tiles are twice as large and dK, dV take twice the TMEM columns, so Q / dO have one stage, dQ
+// reuses the columns of S^T and the query blocks run one after the other.
+template <int D>
 struct BwdSmem {
-  static constexpr int kTile = 128 * 128;
+  static constexpr int kTile = 128 * 128;  // bytes of a [128 x 64] bf16 panel
+  static constexpr int kPanels = D / 64;
+  static constexpr int kStages = (D == 64) ? 2 : 1;
   static constexpr int kK = 0;
-  static constexpr int kV = kTile;
-  static constexpr int kQ = 2 * kTile;        // 2 stages
-  static constexpr int kDO = 4 * kTile;       // 2 stages
-  static constexpr int kPT = 6 * kTile;       // P^T : 2 tiles (128 keys x 128 queries)
-  static constexpr int kDST = 8 * kTile;      // dS^T: 2 tiles
-  static constexpr int kVec = 10 * kTile;     // 2 stages x {lse[128], delta[128], qseg[128]}
+  static constexpr int kV = kK + kPanels * kTile;
+  static constexpr int kQ = kV + kPanels * kTile;                 // kStages x kPanels
+  static constexpr int kDO = kQ + kStages * kPanels * kTile;      // kStages x kPanels
+  static constexpr int kPT = kDO + kStages * kPanels * kTile;     // P^T : 2 panels (128 keys x 128 queries)
+  static constexpr int kDST = kPT + 2 * kTile;                    // dS^T: 2 panels
+  static constexpr int kVec = kDST + 2 * kTile;     // 2 stages x {lse[128], delta[128], qseg[128]}
   static constexpr int kRel = kVec + 2 * 3 * 128 * 4;   // bias by rel for the (i, j) pair: 2 x 256 floats
   static constexpr int kDRel = kRel + 2 * 256 * 4;      // d bias by rel accumulators: (Lq_pad + 128) floats
   static constexpr int kBars = kDRel + (4096 + 128) * 4;
   static constexpr int kTotal = kBars + 256 + 1024;
 };
 
+template <int D>
 __global__ void __launch_bounds__(kAttnThreads, 1)
     attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const AttnParams p) {
+  using Smem = BwdSmem<D>;
+  constexpr int kPanels = Smem::kPanels;
+  constexpr int kStageBytes = kPanels * Smem::kTile;  // one Q (or dO) stage
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sK = smem + BwdSmem::kK;
-  uint8_t* sV = smem + BwdSmem::kV;
-  uint8_t* sQ = smem + BwdSmem::kQ;
-  uint8_t* sDO = smem + BwdSmem::kDO;
-  uint8_t* sPT = smem + BwdSmem::kPT;
-  uint8_t* sDST = smem + BwdSmem::kDST;
-  float* sVec = reinterpret_cast<float*>(smem + BwdSmem::kVec);
-  float* sRelAll = reinterpret_cast<float*>(smem + BwdSmem::kRel);
-  float* sDRel = reinterpret_cast<float*>(smem + BwdSmem::kDRel);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::kBars);
+  uint8_t* sK = smem + Smem::kK;
+  uint8_t* sV = smem + Smem::kV;
+  uint8_t* sQ = smem + Smem::kQ;
+  uint8_t* sDO = smem + Smem::kDO;
+  uint8_t* sPT = smem + Smem::kPT;
+  uint8_t* sDST = smem + Smem::kDST;
+  float* sVec = reinterpret_cast<float*>(smem + Smem::kVec);
+  float* sRelAll = reinterpret_cast<float*>(smem + Smem::kRel);
+  float* sDRel = reinterpret_cast<float*>(smem + Smem::kDRel);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
   uint64_t* bar_kv = bars;          // 1
   uint64_t* bar_qdo = bars + 1;     // 2 (full, per stage)
   uint64_t* bar_free = bars + 3;    // 2 (stage consumed by the MMAs)
@@ -453,7 +468,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   // TMEM columns
   // dQ partial tiles alternate between two 64-column buffers, so that the tile of query block
   // i is read out while the MMAs of block i + 1 run.
-  constexpr int cS = 0, cDP = 128, cDQ = 256, cDK = 384, cDV = 448;
+  constexpr int cS = 0, cDP = 128;
+  constexpr int cDQ = (D == 64) ? 256 : 0;     // head_dim 128: dQ takes over the columns of S^T
+  constexpr int cDK = (D == 64) ? 384 : 256;
+  constexpr int cDV = (D == 64) ? 448 : 384;
+  constexpr int kColsPerPart = D / 4;          // output columns per thread of a row
 
   if (threadIdx.x == 0) {
     mbar_init(bar_kv, 1);
@@ -483,32 +502,67 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   if (warp == kCtrlWarp) {
     if (lane == 0) {
       bool ok = true;
-      mbar_expect_tx(bar_kv, 2 * BwdSmem::kTile);
-      tma_load_4d(sK, &tmK, bar_kv, 0, h, k0, b);
-      tma_load_4d(sV, &tmV, bar_kv, 0, h, k0, b);
-      for (int i = 0; i < nq && i < 2; ++i) {
-        mbar_expect_tx(&bar_qdo[i], 2 * BwdSmem::kTile);
-        tma_load_4d(sQ + i * BwdSmem::kTile, &tmQ, &bar_qdo[i], 0, h, i * 128, b);
-        tma_load_4d(sDO + i * BwdSmem::kTile, &tmDO, &bar_qdo[i], 0, h, i * 128, b);
+      mbar_expect_tx(bar_kv, 2 * kStageBytes);
+      for (int c = 0; c < kPanels; ++c) {
+        tma_load_4d(sK + c * Smem::kTile, &tmK, bar_kv, c * 64, h, k0, b);
+        tma_load_4d(sV + c * Smem::kTile, &tmV, bar_kv, c * 64, h, k0, b);
       }
-      const uint32_t idesc_kq = make_idesc_bf16(128, 128, 0, 0);   // [keys x queries], K = d
-      const uint32_t idesc_kd = make_idesc_bf16(128, 64, 0, 1);    // [keys x d], K = queries (B MN-major)
-      const uint32_t idesc_qd = make_idesc_bf16(128, 64, 1, 1);    // [queries x d], A and B MN-major
+      auto load_qdo = [&](int i, int st) {
+        mbar_expect_tx(&bar_qdo[st], 2 * kStageBytes);
+        for (int c = 0; c < kPanels; ++c) {
+          tma_load_4d(sQ + st * kStageBytes + c * Smem::kTile, &tmQ, &bar_qdo[st], c * 64, h,
+                      i * 128, b);
+          tma_load_4d(sDO + st * kStageBytes + c * Smem::kTile, &tmDO, &bar_qdo[st], c * 64, h,
+                      i * 128, b);
+        }
+      };
+      for (int i = 0; i < nq && i < Smem::kStages; ++i) load_qdo(i, i);
+      const uint32_t idesc_kq = make_idesc_bf16(128, 128, 0, 0);  // [keys x queries], K = d
+      const uint32_t idesc_kd = make_idesc_bf16(128, D, 0, 1);    // [keys x d], K = queries (B MN-major)
+      const uint32_t idesc_qd = make_idesc_bf16(128, D, 1, 1);    // [queries x d], A and B MN-major
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
       const uint32_t pta = smem_u32(sPT), dsta = smem_u32(sDST);
 
-      auto issue_scores = [&](int i) {  // S^T = K Q_i^T ; dP^T = V dO_i^T
-        const uint32_t qa = smem_u32(sQ + (i & 1) * BwdSmem::kTile);
-        const uint32_t doa = smem_u32(sDO + (i & 1) * BwdSmem::kTile);
+      auto issue_scores = [&](int st) {  // S^T = K Q_i^T ; dP^T = V dO_i^T
+        const uint32_t qa = smem_u32(sQ + st * kStageBytes);
+        const uint32_t doa = smem_u32(sDO + st * kStageBytes);
 #pragma unroll
-        for (int s = 0; s < 4; ++s)
-          umma_bf16(tmem_base + cS, make_smem_desc_sw128(ka + s * 32, 16, 1024),
-                    make_smem_desc_sw128(qa + s * 32, 16, 1024), idesc_kq, s != 0);
+        for (int s = 0; s < D / 16; ++s)
+          umma_bf16(tmem_base + cS,
+                    make_smem_desc_sw128(ka + (s >> 2) * Smem::kTile + (s & 3) * 32, 16, 1024),
+                    make_smem_desc_sw128(qa + (s >> 2) * Smem::kTile + (s & 3) * 32, 16, 1024),
+                    idesc_kq, s != 0);
 #pragma unroll
-        for (int s = 0; s < 4; ++s)
-          umma_bf16(tmem_base + cDP, make_smem_desc_sw128(va + s * 32, 16, 1024),
-                    make_smem_desc_sw128(doa + s * 32, 16, 1024), idesc_kq, s != 0);
+        for (int s = 0; s < D / 16; ++s)
+          umma_bf16(tmem_base + cDP,
+                    make_smem_desc_sw128(va + (s >> 2) * Smem::kTile + (s & 3) * 32, 16, 1024),
+                    make_smem_desc_sw128(doa + (s >> 2) * Smem::kTile + (s & 3) * 32, 16, 1024),
+                    idesc_kq, s != 0);
         umma_commit(bar_s);
+      };
+      // dV += P^T dO ; dK += dS^T Q ; dQ_i = dS K. The B operands hold d contiguous (MN-major):
+      // 64-channel groups are one panel apart, 16 rows of the K dimension 2048 bytes.
+      auto issue_grads = [&](int i, int st, int dq_col) {
+        const uint32_t qa = smem_u32(sQ + st * kStageBytes);
+        const uint32_t doa = smem_u32(sDO + st * kStageBytes);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          umma_bf16(tmem_base + cDV,
+                    make_smem_desc_sw128(pta + (s >> 2) * Smem::kTile + (s & 3) * 32, 16, 1024),
+                    make_smem_desc_sw128(doa + s * 2048, Smem::kTile, 1024), idesc_kd, (i | s) != 0);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          umma_bf16(tmem_base + cDK,
+                    make_smem_desc_sw128(dsta + (s >> 2) * Smem::kTile + (s & 3) * 32, 16, 1024),
+                    make_smem_desc_sw128(qa + s * 2048, Smem::kTile, 1024), idesc_kd, (i | s) != 0);
+        // A = dS (M = queries) read from the dS^T tiles as an MN-major operand: 64-query groups
+        // are kTile apart (LBO), 8-key groups 1024 B apart (SBO); K advances 16 keys = 2048 B.
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          umma_bf16(tmem_base + dq_col,
+                    make_smem_desc_sw128(dsta + s * 2048, Smem::kTile, 1024),
+                    make_smem_desc_sw128(ka + s * 2048, Smem::kTile, 1024), idesc_qd, s != 0);
+        umma_commit(bar_dq);
       };
 
       ok = mbar_wait(bar_kv, 0, abort_flag) && mbar_wait(&bar_qdo[0], 0, abort_flag);
@@ -516,60 +570,60 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         tc_fence_after();
         issue_scores(0);
       }
-      // Order per query block i: the scores of block i + 1 are issued as soon as the softmax
-      // warps hold those of block i in registers (bar_sfree), so they are computed while the
-      // warps do their arithmetic; the gradient MMAs of block i follow when P^T / dS^T are in
-      // shared memory (bar_p).
-      for (int i = 0; i < nq && ok; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
-        const uint32_t qa = smem_u32(sQ + st * BwdSmem::kTile);
-        const uint32_t doa = smem_u32(sDO + st * BwdSmem::kTile);
-        ok = mbar_wait(bar_sfree, i & 1, abort_flag);
-        if (ok && i + 1 < nq) {
-          ok = mbar_wait(&bar_qdo[(i + 1) & 1], ((i + 1) >> 1) & 1, abort_flag);
-          if (ok) {
-            tc_fence_after();
-            issue_scores(i + 1);
+      if constexpr (D == 64) {
+        // Order per query block i: the scores of block i + 1 are issued as soon as the softmax
+        // warps hold those of block i in registers (bar_sfree), so they are computed while the
+        // warps do their arithmetic; the gradient MMAs of block i follow when P^T / dS^T are
+        // in shared memory (bar_p).
+        for (int i = 0; i < nq && ok; ++i) {
+          const int st = i & 1;
+          const uint32_t ph = (i >> 1) & 1;
+          ok = mbar_wait(bar_sfree, i & 1, abort_flag);
+          if (ok && i + 1 < nq) {
+            ok = mbar_wait(&bar_qdo[(i + 1) & 1], ((i + 1) >> 1) & 1, abort_flag);
+            if (ok) {
+              tc_fence_after();
+              issue_scores((i + 1) & 1);
+            }
+          }
+          if (ok) ok = mbar_wait(bar_p, i & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_grads(i, st, cDQ + (i & 1) * 64);
+          umma_commit(&bar_free[st]);
+          // The softmax warps read dQ_{i-1} right after they signalled bar_p for block i; once
+          // they have, its buffer is free for dQ_{i+1}. (Waiting here, not before the next
+          // block's MMAs, keeps at most one completion of bar_dq_read ahead of this wait.)
+          if (i >= 1 && i + 1 < nq) {
+            ok = mbar_wait(bar_dq_read, (i - 1) & 1, abort_flag);
+            if (!ok) break;
+          }
+          // refill this stage with query block i + 2
+          if (i + 2 < nq) {
+            ok = mbar_wait(&bar_free[st], ph, abort_flag);
+            if (!ok) break;
+            load_qdo(i + 2, st);
           }
         }
-        if (ok) ok = mbar_wait(bar_p, i & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        // dV += P^T dO ; dK += dS^T Q ; dQ_i = dS K
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma_bf16(tmem_base + cDV,
-                    make_smem_desc_sw128(pta + (s >> 2) * BwdSmem::kTile + (s & 3) * 32, 16, 1024),
-                    make_smem_desc_sw128(doa + s * 2048, 8192, 1024), idesc_kd, (i | s) != 0);
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma_bf16(tmem_base + cDK,
-                    make_smem_desc_sw128(dsta + (s >> 2) * BwdSmem::kTile + (s & 3) * 32, 16, 1024),
-                    make_smem_desc_sw128(qa + s * 2048, 8192, 1024), idesc_kd, (i | s) != 0);
-        // A = dS (M = queries) read from the dS^T tiles as an MN-major operand: 64-query groups
-        // are kTile apart (LBO), 8-key groups 1024 B apart (SBO); K advances 16 keys = 2048 B.
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma_bf16(tmem_base + cDQ + (i & 1) * 64,
-                    make_smem_desc_sw128(dsta + s * 2048, BwdSmem::kTile, 1024),
-                    make_smem_desc_sw128(ka + s * 2048, 8192, 1024), idesc_qd, s != 0);
-        umma_commit(bar_dq);
-        umma_commit(&bar_free[st]);
-        // The softmax warps read dQ_{i-1} right after they signalled bar_p for block i; once
-        // they have, its buffer is free for dQ_{i+1}. (Waiting here, not before the next
-        // block's MMAs, keeps at most one completion of bar_dq_read ahead of this wait.)
-        if (i >= 1 && i + 1 < nq) {
-          ok = mbar_wait(bar_dq_read, (i - 1) & 1, abort_flag);
+      } else {
+        // One query block at a time: scores, softmax, gradient MMAs, dQ read-out (from the
+        // columns of S^T), then the next block's operands and scores.
+        for (int i = 0; i < nq && ok; ++i) {
+          ok = mbar_wait(bar_p, i & 1, abort_flag);
           if (!ok) break;
-        }
-        // refill this stage with query block i + 2
-        if (i + 2 < nq) {
-          ok = mbar_wait(&bar_free[st], ph, abort_flag);
-          if (!ok) break;
-          mbar_expect_tx(&bar_qdo[st], 2 * BwdSmem::kTile);
-          tma_load_4d(sQ + st * BwdSmem::kTile, &tmQ, &bar_qdo[st], 0, h, (i + 2) * 128, b);
-          tma_load_4d(sDO + st * BwdSmem::kTile, &tmDO, &bar_qdo[st], 0, h, (i + 2) * 128, b);
+          tc_fence_after();
+          issue_grads(i, 0, cDQ);
+          umma_commit(&bar_free[0]);
+          if (i + 1 < nq) {
+            ok = mbar_wait(&bar_free[0], i & 1, abort_flag);
+            if (!ok) break;
+            load_qdo(i + 1, 0);
+            ok = mbar_wait(bar_dq_read, i & 1, abort_flag) &&
+                 mbar_wait(&bar_qdo[0], (i + 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_scores(0);
+          }
         }
       }
       if (!ok) {
@@ -637,8 +691,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     };
 
     auto read_dq = [&](int blk, bool release) {
-      uint32_t v[16];
-      tmem_ld16(t_row + cDQ + (blk & 1) * 64 + part * 16, v);
+      uint32_t v[kColsPerPart];
+      if constexpr (D == 64) {
+        tmem_ld16(t_row + cDQ + (blk & 1) * 64 + part * 16, v);
+      } else {
+        tmem_ld32(t_row + cDQ + part * 32, v);
+      }
       tmem_ld_wait();
       if (release) {
         tc_fence_before();
@@ -647,9 +705,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
       const int q = blk * 128 + r;
       if (q < p.Lq) {
-        float* dst = p.dQ + ((static_cast<long long>(b) * p.Lq + q) * p.H + h) * kAttnD + part * 16;
+        float* dst = p.dQ + ((static_cast<long long>(b) * p.Lq + q) * p.H + h) * D +
+                     part * kColsPerPart;
 #pragma unroll
-        for (int x = 0; x < 16; x += 4)
+        for (int x = 0; x < kColsPerPart; x += 4)
           asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + x),
                        "f"(__uint_as_float(v[x])), "f"(__uint_as_float(v[x + 1])),
                        "f"(__uint_as_float(v[x + 2])), "f"(__uint_as_float(v[x + 3]))
@@ -693,8 +752,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       // interior tile with a key-only mask: the mask is one additive constant per thread
       // (-1e10 absorbs any score: |s| is far below the fp32 spacing at 1e10)
       const float madd = kvis ? 0.f : kMaskValue;
-      uint8_t* pt_tile = sPT + (part >> 1) * BwdSmem::kTile;
-      uint8_t* dst_tile = sDST + (part >> 1) * BwdSmem::kTile;
+      uint8_t* pt_tile = sPT + (part >> 1) * Smem::kTile;
+      uint8_t* dst_tile = sDST + (part >> 1) * Smem::kTile;
       // Bias gradient: dS[key r][query c] belongs to bin (r - c). Within the warp's 32 x 32
       // block (lane = key row, x = query column) lane L collects diagonal L and diagonal L - 32:
       // at column x it fetches the value of lane (L + x) mod 32, which lies on diagonal L when
@@ -756,8 +815,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             }
           }
         }
-        if (hc == 0 && i > 0) {
+        if (D == 64 && hc == 0 && i > 0) {
           // the gradient MMAs of block i - 1 still read P^T / dS^T; they also produce dQ_{i-1}
+          // (head_dim 128 has waited for them already, at the end of block i - 1)
           ok = mbar_wait_relaxed(bar_dq, (i - 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
@@ -780,11 +840,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       // dQ partial of the previous block (its MMAs were waited for above), while the MMAs of
       // this block run: rows are queries here (TMEM lane = query within the block), 16 columns
       // per thread.
-      if (i > 0) read_dq(i - 1, true);
+      if constexpr (D == 64) {
+        if (i > 0) read_dq(i - 1, true);
+      } else {
+        // dQ_i sits in the columns of S^T: out before the next block's scores may be issued
+        ok = mbar_wait_relaxed(bar_dq, i & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        read_dq(i, true);
+      }
       if (i + 1 < nq) publish_vectors(i + 1);  // other stage than the one block i used
       softmax_bar_sync();  // the vectors of block i+1 are complete; those of block i are dead
     }
-    if (ok) {
+    if (D == 64 && ok) {
       ok = mbar_wait_relaxed(bar_dq, (nq - 1) & 1, abort_flag);
       if (ok) {
         tc_fence_after();
@@ -793,14 +861,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
     if (ok) {
       // dK, dV accumulators are complete once the last bar_dq fired (same commit group).
-      uint32_t vk[16], vv[16];
-      tmem_ld16(t_row + cDK + part * 16, vk);
-      tmem_ld16(t_row + cDV + part * 16, vv);
-      tmem_ld_wait();
-      if (k_ok) {
-        const long long off = b * p.dk_sb + static_cast<long long>(k) * p.dk_sl + h * p.dk_sh + part * 16;
-        store16_bf16(p.dK + off, vk, 1.f);
-        store16_bf16(p.dV + off, vv, 1.f);
+#pragma unroll
+      for (int c = 0; c < kColsPerPart / 16; ++c) {
+        uint32_t vk[16], vv[16];
+        tmem_ld16(t_row + cDK + part * kColsPerPart + c * 16, vk);
+        tmem_ld16(t_row + cDV + part * kColsPerPart + c * 16, vv);
+        tmem_ld_wait();
+        if (k_ok) {
+          const long long off = b * p.dk_sb + static_cast<long long>(k) * p.dk_sl + h * p.dk_sh +
+                                part * kColsPerPart + c * 16;
+          store16_bf16(p.dK + off, vk, 1.f);
+          store16_bf16(p.dV + off, vv, 1.f);
+        }
       }
       softmax_bar_sync();
       if (p.d_rel_bias != nullptr) {
@@ -881,35 +953,60 @@ T5X_API int t5x_attention_fwd(const void* q, const void* k, const void* v, void*
   return 0;
 }
 
-// dq_f32 [B,Lq,H,64] fp32 contiguous, zero on entry. delta [B,H,Lq] fp32 scratch.
+namespace t5x {
+template <int D>
+static int launch_attention_bwd(const void* d_o, const void* o, void* delta, const CUtensorMap* tq,
+                                const CUtensorMap* tk, const CUtensorMap* tv,
+                                const CUtensorMap* tdo, const AttnParams& p, long long do_sb,
+                                long long do_sl, long long do_sh, long long o_sb, long long o_sl,
+                                long long o_sh, cudaStream_t st) {
+  long long items = static_cast<long long>(p.B) * p.Lq * p.H;
+  long long blocks = (items * (D / 8) / 4 + 255) / 256;
+  long long cap = static_cast<long long>(num_sms()) * 8;
+  attn_delta_kernel<D><<<static_cast<int>(blocks > cap ? cap : blocks), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(o),
+      static_cast<float*>(delta), p.B, p.H, p.Lq, do_sb, do_sl, do_sh, o_sb, o_sl, o_sh);
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         BwdSmem<D>::kTotal);
+    if (e != cudaSuccess) return set_error("attention_bwd attr: %s", cudaGetErrorString(e));
+    attr_set[dev] = true;
+  }
+  dim3 grid((p.Lk + 127) / 128, p.H, p.B);
+  attn_bwd_kernel<D><<<grid, kAttnThreads, BwdSmem<D>::kTotal, st>>>(*tq, *tk, *tv, *tdo, p);
+  count_launches(2);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("attention_bwd: %s", cudaGetErrorString(e));
+  return 0;
+}
+}  // namespace t5x
+
+// dq_f32 [B,Lq,H,D] fp32 contiguous, zero on entry. delta [B,H,Lq] fp32 scratch. D = 64 or 128.
 T5X_API int t5x_attention_bwd(const void* q, const void* k, const void* v, const void* o,
                               const void* d_o, const void* lse, void* delta, void* dq_f32, void* dk,
-                              void* dv, int B, int H, int Lq, int Lk, long long q_sb, long long q_sl,
-                              long long q_sh, long long k_sb, long long k_sl, long long k_sh,
-                              long long v_sb, long long v_sl, long long v_sh, long long o_sb,
-                              long long o_sl, long long o_sh, long long do_sb, long long do_sl,
-                              long long do_sh, long long dk_sb, long long dk_sl, long long dk_sh,
-                              const void* rel_bias, void* d_rel_bias, int nrel, int rel_off,
-                              const void* key_mask, const void* q_seg, const void* kv_seg,
-                              int causal, int causal_off, void* stream) {
+                              void* dv, int B, int H, int Lq, int Lk, int D, long long q_sb,
+                              long long q_sl, long long q_sh, long long k_sb, long long k_sl,
+                              long long k_sh, long long v_sb, long long v_sl, long long v_sh,
+                              long long o_sb, long long o_sl, long long o_sh, long long do_sb,
+                              long long do_sl, long long do_sh, long long dk_sb, long long dk_sl,
+                              long long dk_sh, const void* rel_bias, void* d_rel_bias, int nrel,
+                              int rel_off, const void* key_mask, const void* q_seg,
+                              const void* kv_seg, int causal, int causal_off, void* stream) {
   if (B <= 0 || H <= 0 || Lq <= 0 || Lk <= 0) return 0;
+  if (D != 64 && D != 128) return set_error("attention_bwd: head_dim %d not in {64, 128}", D);
   if (Lq > 4096) return set_error("attention_bwd: Lq=%d > 4096 is not covered by this kernel", Lq);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const CUtensorMap* tq = bhld_map(q, B, Lq, H, q_sb, q_sl, q_sh);
-  const CUtensorMap* tk = bhld_map(k, B, Lk, H, k_sb, k_sl, k_sh);
-  const CUtensorMap* tv = bhld_map(v, B, Lk, H, v_sb, v_sl, v_sh);
-  const CUtensorMap* tdo = bhld_map(d_o, B, Lq, H, do_sb, do_sl, do_sh);
+  const CUtensorMap* tq = bhld_map(q, B, Lq, H, q_sb, q_sl, q_sh, D);
+  const CUtensorMap* tk = bhld_map(k, B, Lk, H, k_sb, k_sl, k_sh, D);
+  const CUtensorMap* tv = bhld_map(v, B, Lk, H, v_sb, v_sl, v_sh, D);
+  const CUtensorMap* tdo = bhld_map(d_o, B, Lq, H, do_sb, do_sl, do_sh, D);
   if (!tq || !tk || !tv || !tdo) return -1;
-  {
-    if ((do_sb | do_sl | do_sh | o_sb | o_sl | o_sh) & 7)
-      return set_error("attention_bwd: dO / O strides must be multiples of 8 elements");
-    long long items = static_cast<long long>(B) * Lq * H;
-    long long blocks = (items * 8 / 4 + 255) / 256;
-    long long cap = static_cast<long long>(num_sms()) * 8;
-    attn_delta_kernel<<<static_cast<int>(blocks > cap ? cap : blocks), 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(o),
-        static_cast<float*>(delta), B, H, Lq, do_sb, do_sl, do_sh, o_sb, o_sl, o_sh);
-  }
+  if ((do_sb | do_sl | do_sh | o_sb | o_sl | o_sh | dk_sb | dk_sl | dk_sh) & 7)
+    return set_error("attention_bwd: dO / O / dK strides must be multiples of 8 elements");
   AttnParams p = {};
   p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk;
   p.rel_bias = static_cast<const float*>(rel_bias);
@@ -926,19 +1023,9 @@ T5X_API int t5x_attention_bwd(const void* q, const void* k, const void* v, const
   p.dV = static_cast<__nv_bfloat16*>(dv);
   p.dk_sb = dk_sb; p.dk_sl = dk_sl; p.dk_sh = dk_sh;
   p.status = device_status_buffer();
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         BwdSmem::kTotal);
-    if (e != cudaSuccess) return set_error("attention_bwd attr: %s", cudaGetErrorString(e));
-    attr_set[dev] = true;
-  }
-  dim3 grid((Lk + 127) / 128, H, B);
-  attn_bwd_kernel<<<grid, kAttnThreads, BwdSmem::kTotal, st>>>(*tq, *tk, *tv, *tdo, p);
-  count_launches(2);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return set_error("attention_bwd: %s", cudaGetErrorString(e));
-  return 0;
+  if (D == 128)
+    return launch_attention_bwd<128>(d_o, o, delta, tq, tk, tv, tdo, p, do_sb, do_sl, do_sh, o_sb,
+                                     o_sl, o_sh, st);
+  return launch_attention_bwd<64>(d_o, o, delta, tq, tk, tv, tdo, p, do_sb, do_sl, do_sh, o_sb,
+                                  o_sl, o_sh, st);
 }

@@ -3,10 +3,11 @@
 // (batch x beams) where latency, not bandwidth, decides.
 //
 // Every all-reduce site of the captured decode step has an inbox of its own on every rank
-// ([world][n] bf16) and a row of signal words of its own. The split-K GEMM leaves fp32 sums in
-// a workspace; `push_partial` rounds them to bf16, stores them into slot `rank` of every rank's
-// inbox (its own included), clears the workspace for the next GEMM, and, from the last CTA to
-// finish, raises this rank's signal word on every rank to the current step number.
+// ([world][n] fp32) and a row of signal words of its own. The split-K GEMM leaves fp32 sums in
+// a workspace; `push_partial` stores them (still fp32: a megabyte or two per site, and the sum
+// then rounds once, like the single-GPU step) into slot `rank` of every rank's inbox (its own
+// included), clears the workspace for the next GEMM, and, from the last CTA to finish, raises
+// this rank's signal word on every rank to the current step number.
 // `sum_slots` waits (bounded) until all ranks' words have reached the step number and adds the
 // slots and the residual in fp32, in the same order on every rank, so all ranks hold bit-identical
 // activations. The step number lives in device memory and is advanced by a kernel of the step
@@ -71,29 +72,13 @@ __global__ void decode_advance_kernel(unsigned int* step) {
   if (blockIdx.x == 0 && threadIdx.x == 0) *step += 1u;
 }
 
-// ws [n] fp32 -> bf16 into every rank's slot; ws cleared; last CTA signals.
-__global__ void __launch_bounds__(kDtThreads)
-    decode_push_partial_kernel(float* __restrict__ ws, long long n8, DtPeers slot, DtPeers sig,
-                               int world, int rank, const unsigned int* __restrict__ step,
-                               unsigned int* ticket) {
-  const long long stride = static_cast<long long>(gridDim.x) * kDtThreads;
-  for (long long i = blockIdx.x * static_cast<long long>(kDtThreads) + threadIdx.x; i < n8;
-       i += stride) {
-    float4* src = reinterpret_cast<float4*>(ws) + 2 * i;
-    const float4 a = src[0], b = src[1];
-    src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-    src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-    uint4 o;
-    __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
-    q[0] = __floats2bfloat162_rn(a.x, a.y);
-    q[1] = __floats2bfloat162_rn(a.z, a.w);
-    q[2] = __floats2bfloat162_rn(b.x, b.y);
-    q[3] = __floats2bfloat162_rn(b.z, b.w);
-    for (int d = 0; d < world; ++d) reinterpret_cast<uint4*>(slot.p[d])[i] = o;
-  }
-  __threadfence_system();
+// One arrival per CTA: the CTA barrier orders every thread's stores before thread 0's
+// system-scope fence (fences are cumulative), and the last CTA to arrive publishes the epoch.
+__device__ __forceinline__ void dt_publish(DtPeers sig, int world, int rank,
+                                           const unsigned int* step, unsigned int* ticket) {
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned int done = atomicAdd(ticket, 1u);
     if (done == gridDim.x - 1) {
       *ticket = 0u;
@@ -105,43 +90,47 @@ __global__ void __launch_bounds__(kDtThreads)
   }
 }
 
+// ws [n] fp32 -> every rank's slot; ws cleared; last CTA signals.
 __global__ void __launch_bounds__(kDtThreads)
-    decode_sum_slots_kernel(const __nv_bfloat16* __restrict__ inbox, int world, int rank,
-                            long long n8, const __nv_bfloat16* __restrict__ res,
-                            __nv_bfloat16* __restrict__ dst, const unsigned int* __restrict__ sig,
+    decode_push_partial_kernel(float* __restrict__ ws, long long n4, DtPeers slot, DtPeers sig,
+                               int world, int rank, const unsigned int* __restrict__ step,
+                               unsigned int* ticket) {
+  const long long stride = static_cast<long long>(gridDim.x) * kDtThreads;
+  for (long long i = blockIdx.x * static_cast<long long>(kDtThreads) + threadIdx.x; i < n4;
+       i += stride) {
+    float4* src = reinterpret_cast<float4*>(ws) + i;
+    const float4 a = *src;
+    *src = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int d = 0; d < world; ++d) reinterpret_cast<float4*>(slot.p[d])[i] = a;
+  }
+  dt_publish(sig, world, rank, step, ticket);
+}
+
+__global__ void __launch_bounds__(kDtThreads)
+    decode_sum_slots_kernel(const float* __restrict__ inbox, int world, int rank, long long n4,
+                            const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ dst,
+                            const unsigned int* __restrict__ sig,
                             const unsigned int* __restrict__ step, int* status) {
   if (!dt_wait_all(sig, world, rank, *step, status, kKernelIdDecodeSum)) return;
   const long long stride = static_cast<long long>(gridDim.x) * kDtThreads;
-  for (long long i = blockIdx.x * static_cast<long long>(kDtThreads) + threadIdx.x; i < n8;
+  for (long long i = blockIdx.x * static_cast<long long>(kDtThreads) + threadIdx.x; i < n4;
        i += stride) {
-    float acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (res != nullptr) {
-      const uint4 u = reinterpret_cast<const uint4*>(res)[i];
+      const uint2 u = reinterpret_cast<const uint2*>(res)[i];
       const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(p[j]);
-        acc[2 * j] = f.x;
-        acc[2 * j + 1] = f.y;
-      }
+      const float2 lo = __bfloat1622float2(p[0]), hi = __bfloat1622float2(p[1]);
+      acc = make_float4(lo.x, lo.y, hi.x, hi.y);
     }
     for (int s = 0; s < world; ++s) {
-      const uint4 u = reinterpret_cast<const uint4*>(inbox)[s * n8 + i];
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(p[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
-      }
+      const float4 v = reinterpret_cast<const float4*>(inbox)[s * n4 + i];
+      acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
     }
-    uint4 o;
+    uint2 o;
     __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) q[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    reinterpret_cast<uint4*>(dst)[i] = o;
+    q[0] = __floats2bfloat162_rn(acc.x, acc.y);
+    q[1] = __floats2bfloat162_rn(acc.z, acc.w);
+    reinterpret_cast<uint2*>(dst)[i] = o;
   }
 }
 
@@ -161,18 +150,7 @@ __global__ void __launch_bounds__(kDtThreads)
     for (int d = 0; d < world; ++d)
       *reinterpret_cast<float4*>(static_cast<float*>(full.p[d]) + off) = v;
   }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int done = atomicAdd(ticket, 1u);
-    if (done == gridDim.x - 1) {
-      *ticket = 0u;
-      __threadfence_system();
-      const unsigned int epoch = *step;
-      for (int d = 0; d < world; ++d)
-        dt_signal(static_cast<unsigned int*>(sig.p[d]) + rank, epoch);
-    }
-  }
+  dt_publish(sig, world, rank, step, ticket);
 }
 
 __global__ void decode_wait_kernel(const unsigned int* __restrict__ sig, int world, int rank,
@@ -182,7 +160,9 @@ __global__ void decode_wait_kernel(const unsigned int* __restrict__ sig, int wor
 
 int dt_grid(long long items) {
   long long blocks = (items + kDtThreads - 1) / kDtThreads;
-  const long long cap = static_cast<long long>(num_sms()) * 2;
+  // a few dozen CTAs move these few megabytes as fast as hundreds would, with far fewer
+  // arrivals to count before the signal goes out
+  const long long cap = 64;
   if (blocks > cap) blocks = cap;
   return static_cast<int>(blocks < 1 ? 1 : blocks);
 }
@@ -209,13 +189,13 @@ T5X_API int t5x_decode_step_advance(void* step, void* stream) {
   return 0;
 }
 
-// ws [n] fp32 (n a multiple of 8, cleared on return) -> bf16 into `slots[d]` (rank d's inbox slot
-// for this rank) for every d, then signal `sigs[d][rank] = *step`.
+// ws [n] fp32 (n a multiple of 4, cleared on return) -> `slots[d]` (rank d's fp32 inbox slot for
+// this rank) for every d, then signal `sigs[d][rank] = *step`.
 T5X_API int t5x_decode_push_partial(void* ws, long long n, void* const* slots, void* const* sigs,
                                     int world, int rank, const void* step, void* ticket,
                                     void* stream) {
   if (n <= 0) return 0;
-  if (n % 8 || world < 1 || world > kDtMaxPeers || rank < 0 || rank >= world)
+  if (n % 4 || world < 1 || world > kDtMaxPeers || rank < 0 || rank >= world)
     return set_error("decode_push_partial: bad arguments (n=%lld, world=%d)", n, world);
   if (ws == nullptr || step == nullptr || ticket == nullptr ||
       (reinterpret_cast<uintptr_t>(ws) & 15))
@@ -223,8 +203,8 @@ T5X_API int t5x_decode_push_partial(void* ws, long long n, void* const* slots, v
   DtPeers slot = {}, sig = {};
   if (!dt_peers(&slot, slots, world, 16) || !dt_peers(&sig, sigs, world, 4))
     return set_error("decode_push_partial: null or misaligned peer pointer");
-  decode_push_partial_kernel<<<dt_grid(n / 8), kDtThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<float*>(ws), n / 8, slot, sig, world, rank,
+  decode_push_partial_kernel<<<dt_grid(n / 4), kDtThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float*>(ws), n / 4, slot, sig, world, rank,
       static_cast<const unsigned int*>(step), static_cast<unsigned int*>(ticket));
   count_launches(1);
   cudaError_t e = cudaGetLastError();
@@ -232,18 +212,18 @@ T5X_API int t5x_decode_push_partial(void* ws, long long n, void* const* slots, v
   return 0;
 }
 
-// dst [n] bf16 = sum over the `world` slots of inbox ([world][n] bf16) + residual, after every
+// dst [n] bf16 = sum over the `world` slots of inbox ([world][n] fp32) + residual (bf16), after every
 // rank's signal word in `sig` ([world] words, local) has reached *step.
 T5X_API int t5x_decode_sum_slots(const void* inbox, int world, int rank, long long n,
                                  const void* residual, void* dst, const void* sig,
                                  const void* step, void* stream) {
   if (n <= 0) return 0;
-  if (n % 8 || world < 1 || world > kDtMaxPeers || rank < 0 || rank >= world)
+  if (n % 4 || world < 1 || world > kDtMaxPeers || rank < 0 || rank >= world)
     return set_error("decode_sum_slots: bad arguments (n=%lld, world=%d)", n, world);
   if (inbox == nullptr || dst == nullptr || sig == nullptr || step == nullptr)
     return set_error("decode_sum_slots: null pointer");
-  decode_sum_slots_kernel<<<dt_grid(n / 8), kDtThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(inbox), world, rank, n / 8,
+  decode_sum_slots_kernel<<<dt_grid(n / 4), kDtThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(inbox), world, rank, n / 4,
       static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(dst),
       static_cast<const unsigned int*>(sig), static_cast<const unsigned int*>(step),
       device_status_buffer());

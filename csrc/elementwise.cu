@@ -620,15 +620,18 @@ T5X_API int t5x_cast_f32_bf16(const void* src, void* dst, long long rows, int co
 
 
 // dst[i] = bf16(src[i] (+ residual[i])): finishes a split-K GEMM whose partial products were
-// added into an fp32 workspace.
+// added into an fp32 workspace. With kClear the workspace is left zero, ready for the next GEMM
+// that accumulates into it (no separate fill kernel).
 namespace t5x {
+template <bool kClear>
 __global__ void __launch_bounds__(256)
-    f32_to_bf16_residual_kernel(const float* __restrict__ src, const __nv_bfloat16* __restrict__ res,
+    f32_to_bf16_residual_kernel(float* __restrict__ src, const __nv_bfloat16* __restrict__ res,
                                 __nv_bfloat16* __restrict__ dst, long long n4) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
        i += stride) {
     float4 a = reinterpret_cast<const float4*>(src)[i];
+    if (kClear) reinterpret_cast<float4*>(src)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (res != nullptr) {
       const uint2 r = reinterpret_cast<const uint2*>(res)[i];
       const float2 r0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
@@ -656,13 +659,33 @@ T5X_API int t5x_f32_to_bf16_residual(const void* src, const void* residual, void
   long long blocks = (n4 + 255) / 256;
   const long long cap = static_cast<long long>(t5x::num_sms()) * 8;
   if (blocks > cap) blocks = cap;
-  t5x::f32_to_bf16_residual_kernel<<<static_cast<int>(blocks), 256, 0,
-                                     static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const float*>(src), static_cast<const __nv_bfloat16*>(residual),
+  t5x::f32_to_bf16_residual_kernel<false><<<static_cast<int>(blocks), 256, 0,
+                                            static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float*>(const_cast<void*>(src)), static_cast<const __nv_bfloat16*>(residual),
       static_cast<__nv_bfloat16*>(dst), n4);
   t5x::count_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return t5x::set_error("f32_to_bf16_residual: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// The same, and src[0..n) is zero afterwards.
+T5X_API int t5x_f32_to_bf16_residual_clear(void* src, const void* residual, void* dst, long long n,
+                                           void* stream) {
+  if (n <= 0) return 0;
+  if (n % 4) return t5x::set_error("f32_to_bf16_residual_clear: n must be a multiple of 4");
+  const long long n4 = n / 4;
+  long long blocks = (n4 + 255) / 256;
+  const long long cap = static_cast<long long>(t5x::num_sms()) * 8;
+  if (blocks > cap) blocks = cap;
+  t5x::f32_to_bf16_residual_kernel<true><<<static_cast<int>(blocks), 256, 0,
+                                           static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float*>(src), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<__nv_bfloat16*>(dst), n4);
+  t5x::count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return t5x::set_error("f32_to_bf16_residual_clear: %s", cudaGetErrorString(e));
   return 0;
 }
 

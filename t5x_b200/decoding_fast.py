@@ -93,7 +93,7 @@ class _TensorParallelLink:
       raise ValueError("tensor-parallel decode wants rows * d_model % 8 == 0 and vocab % 4 == 0")
     import torch.distributed as dist
     self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-    self.inbox = comm.SymmetricBuffer(sites * self.world * self.n, torch.bfloat16, group, device)
+    self.inbox = comm.SymmetricBuffer(sites * self.world * self.n, torch.float32, group, device)
     self.logits = comm.SymmetricBuffer(rows * vocab, torch.float32, group, device)
     self.sig = comm.SymmetricBuffer((sites + 1) * 16, torch.int32, group, device)
     self.sig.tensor.zero_()
@@ -120,7 +120,7 @@ class _TensorParallelLink:
     assert site < self.sites
     ws = self.ws.view(self.rows, self.width)
     native.gemm_splitk_accumulate(a, w, ws, max(1, splits), accumulate=True)
-    slot_bytes = self.n * 2
+    slot_bytes = self.n * 4
     base = site * self.world * slot_bytes + self.rank * slot_bytes
     slots = self.comm._ptr_array([p + base for p in self.inbox.peer_ptrs])
     native._check(native.lib().t5x_decode_push_partial(
@@ -285,6 +285,9 @@ class GraphBeamDecoder:
           .contiguous()
     self.enc_mask = (encoder_input_tokens > 0)
     self.enc_mask_u8 = self.enc_mask.to(torch.uint8).contiguous()
+    if self.tp > 1:
+      from t5x_b200.parallel import tp_fused
+      tp_fused.end_step()  # the encoder pass is over: its arena blocks are free again
 
   def _model_step(self) -> torch.Tensor:
     """Logits [rows, vocab] (fp32) of the token at position `cur` of every live beam."""
@@ -335,10 +338,11 @@ class GraphBeamDecoder:
     if self.rows > 512:
       return native.gemm(a, w, residual=residual)
     if self._ws is None:
-      self._ws = torch.empty(self.rows * max(self.c.emb_dim, self.H * self.D),
+      # zero once; every finishing kernel leaves what it read zero again
+      self._ws = torch.zeros(self.rows * max(self.c.emb_dim, self.H * self.D),
                              dtype=torch.float32, device=self.dev)
     return native.gemm_splitk(a, w, _splits(w.shape[0], w.shape[1], self.rows),
-                              residual=residual, workspace=self._ws)
+                              residual=residual, workspace=self._ws, workspace_is_clear=True)
 
   def _beam_step(self, flat_logits: torch.Tensor) -> None:
     """One step of the search state update. Beam widths 1, 2, 4 and 8 run the two native

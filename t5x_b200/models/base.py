@@ -373,6 +373,9 @@ class EncoderDecoderModel(BaseTransformerModel):
         logits = self._compute_logits(params, batch)
         onehot = torch.nn.functional.one_hot(targets, logits.shape[-1]).float()
         token_scores = -losses.cross_entropy_with_logits(logits, onehot, z_loss=0.0)[0] * weights
+      if token_scores.is_cuda:
+        from t5x_b200.parallel import tp_fused
+        tp_fused.end_step()
     sequence_scores = token_scores.sum(-1)
     if return_intermediates:
       intermediates = {"decoder": {"target_tokens": (targets,), "loss_weights": (weights,),

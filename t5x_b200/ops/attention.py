@@ -19,7 +19,7 @@ c_void_p, c_int, c_ll = native.c_void_p, native.c_int, native.c_ll
 native.register_signature("t5x_attention_fwd", [c_void_p] * 5 + [c_int] * 4 + [c_ll] * 12 +
                           [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                            c_void_p])
-native.register_signature("t5x_attention_bwd", [c_void_p] * 10 + [c_int] * 4 + [c_ll] * 18 +
+native.register_signature("t5x_attention_bwd", [c_void_p] * 10 + [c_int] * 5 + [c_ll] * 18 +
                           [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                            c_int, c_void_p])
 
@@ -54,8 +54,8 @@ def flash_supported(q, k, v, explicit_bias, extra_mask) -> bool:
   prefix_lm = isinstance(extra_mask, ref.PrefixLMMask)
   if prefix_lm and q.shape[1] != k.shape[1]:
     return False
-  return (explicit_bias is None and (extra_mask is None or prefix_lm) and q.shape[-1] == 64 and
-          q.shape[1] <= BWD_MAX_LQ and q.dtype == torch.bfloat16 and
+  return (explicit_bias is None and (extra_mask is None or prefix_lm) and
+          q.shape[-1] in (64, 128) and q.shape[1] <= BWD_MAX_LQ and q.dtype == torch.bfloat16 and
           k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16)
 
 
@@ -124,7 +124,8 @@ class _FlashAttentionFn(torch.autograd.Function):
     nrel = rel_bias.shape[1] if rel_bias is not None else 0
     rc = native.lib().t5x_attention_bwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
-        delta.data_ptr(), dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H, Lq, Lk, *_sbh(q),
+        delta.data_ptr(), dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H, Lq, Lk, D,
+        *_sbh(q),
         *_sbh(k), *_sbh(v), *_sbh(o), *_sbh(do), *_sbh(dk), native.ptr(rel_bias),
         native.ptr(d_rel), nrel, rel_off, native.ptr(key_mask), native.ptr(q_seg),
         native.ptr(kv_seg), int(causal), causal_off, native.stream_ptr())
@@ -158,8 +159,7 @@ def flash_attention(q, k, v, *, bias_table: Optional[torch.Tensor] = None,
                     key_mask: Optional[torch.Tensor] = None, causal: bool = False,
                     q_segment_ids=None, kv_segment_ids=None, q_offset: int = 0,
                     prefix_lm: Optional["ref.PrefixLMMask"] = None) -> torch.Tensor:
-  """q [B,Lq,H,D], k/v [B,Lk,H,D] bf16 -> [B,Lq,H,D], D = 64 (forward and backward) or 128
-  (forward). `prefix_lm`: prefix-LM visibility in factored form; it replaces `causal`,
+  """q [B,Lq,H,D], k/v [B,Lk,H,D] bf16 -> [B,Lq,H,D], D = 64 or 128. `prefix_lm`: prefix-LM visibility in factored form; it replaces `causal`,
   `key_mask` and the segment ids (which it contains)."""
   B, Lq, H, D = q.shape
   Lk = k.shape[1]

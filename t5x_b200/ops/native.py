@@ -278,11 +278,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None
 # ----------------------------------------------------------------------------
 def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, *,
                 residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                workspace: Optional[torch.Tensor] = None,
+                workspace_is_clear: bool = False) -> torch.Tensor:
   """out[M, N] (bf16) = a[M, K] @ b[K, N] (+ residual) with K cut into `splits` slices whose
   partial products are added atomically into an fp32 workspace. For skinny problems (decode
   steps: M of a few hundred rows) this puts `splits` times more CTAs on the weight stream
-  than one CTA per output tile would."""
+  than one CTA per output tile would. `workspace_is_clear`: the caller's workspace is zero on
+  entry and is left zero on return (the finishing kernel clears what it reads), so a sequence
+  of such GEMMs over one workspace needs no fill kernel at all."""
   M, K = a.shape
   N = b.shape[1]
   assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.stride(1) == 1
@@ -293,7 +296,9 @@ def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, *,
   ws = workspace if workspace is not None else torch.empty(M, N, dtype=torch.float32,
                                                            device=a.device)
   ws = ws.view(-1)[:M * N].view(M, N)
-  ws.zero_()
+  keep_clear = workspace_is_clear and workspace is not None
+  if not keep_clear:
+    ws.zero_()
   rc = lib().t5x_gemm_bf16(
       a.data_ptr(), b.data_ptr(), 0, ws.data_ptr(), M, N, ks, splits, a.stride(0), b.stride(0), N,
       ks, ks * b.stride(0), 0, 0, 1, 1, 2, EPI_PLAIN, 0, 0, 0, 0, 0, 0, 1.0, 0, stream_ptr())
@@ -302,9 +307,14 @@ def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, *,
     out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
   assert out.is_contiguous() and (residual is None or residual.is_contiguous())
   l = lib()
-  l.t5x_f32_to_bf16_residual.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_void_p]
-  _check(l.t5x_f32_to_bf16_residual(ws.data_ptr(), ptr(residual), out.data_ptr(), M * N,
-                                    stream_ptr()), "f32_to_bf16_residual")
+  if keep_clear:
+    l.t5x_f32_to_bf16_residual_clear.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_void_p]
+    _check(l.t5x_f32_to_bf16_residual_clear(ws.data_ptr(), ptr(residual), out.data_ptr(), M * N,
+                                            stream_ptr()), "f32_to_bf16_residual_clear")
+  else:
+    l.t5x_f32_to_bf16_residual.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_void_p]
+    _check(l.t5x_f32_to_bf16_residual(ws.data_ptr(), ptr(residual), out.data_ptr(), M * N,
+                                      stream_ptr()), "f32_to_bf16_residual")
   return out
 
 

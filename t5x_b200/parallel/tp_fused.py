@@ -222,6 +222,14 @@ def arena() -> SymmetricArena:
   return _ARENA
 
 
+def end_step() -> None:
+  """Between forward passes that no trainer step follows (evaluation, scoring, the encoder pass
+  of a decode): gives all bytes of the arena back, at a point every rank reaches in the same
+  order. A training loop does this once per step (`Trainer._after_step`)."""
+  if _ARENA is not None:
+    _ARENA.end_step()
+
+
 def enabled() -> bool:
   """Fused tensor-parallel kernels run on GPUs when the model axis has more than one rank
   (`T5X_B200_TP_FUSED=0` keeps the all-reduce form of `t5x_b200.parallel.tp`)."""

@@ -621,6 +621,9 @@ class BaseTrainer(abc.ABC):
         num_steps += 1
         with torch.no_grad():
           mu = self._eval_step(train_state, _to_device_batch(batch, self._device))
+        if self._device.type == "cuda":
+          from t5x_b200.parallel import tp_fused
+          tp_fused.end_step()
         metrics = mu if metrics is None else merge_metrics(metrics, mu)
       _assert_equal_across_ranks(num_steps, "eval step mismatch across ranks")
       if metrics is None:

@@ -257,6 +257,10 @@ def case_tp_decode(out):
                          logits_via_embedding=False)
   torch.manual_seed(21)
   module = network.Transformer(cfg, device=st.device)
+  with torch.no_grad():
+    # sharper next-token distributions than a random initialisation gives: near-ties between
+    # candidates would otherwise let bf16 rounding differences reorder the beams
+    module.decoder.logits_dense.kernel.mul_(8.0)
   vocab = vocabularies.PassThroughVocabulary(512)
   model = models.EncoderDecoderModel(module, vocab, vocab, adafactor.Adafactor())
   trainer_lib.attach_compute_buffers(base.module_param_tree(module), bf16_copy=True,

@@ -116,28 +116,37 @@ def test_rows_with_every_key_hidden_are_uniform(kernel, monkeypatch):
     assert rel(g, w) < TOL, (n, rel(g, w))
 
 
-@pytest.mark.parametrize("shape", [(2, 3, 200, 200, True), (1, 2, 130, 1100, False)])
-def test_streaming_forward_with_head_dim_128(shape):
-  """head_dim 128 (T5 1.0 3B / 11B): forward output and log-sum-exp against fp32."""
+@pytest.mark.parametrize("shape", [(2, 3, 200, 200, True), (1, 2, 130, 1100, False),
+                                   (2, 2, 384, 256, False)])
+def test_head_dim_128_forward_and_backward(shape):
+  """head_dim 128 (T5 1.0 3B / 11B): the streaming forward and the one-block-at-a-time
+  backward against fp32, with bias, padding mask and (first case) causal masking."""
   from t5x_b200.ops import attention as A
   from t5x_b200.ops import native
   from t5x_b200.ops import reference as ref
   B, H, Lq, Lk, causal = shape
   torch.manual_seed(2)
-  q = (torch.randn(B, Lq, H, 128, device="cuda") * 0.3).bfloat16()
-  k = (torch.randn(B, Lk, H, 128, device="cuda") * 0.3).bfloat16()
-  v = torch.randn(B, Lk, H, 128, device="cuda").bfloat16()
-  table = torch.randn(H, 32, device="cuda") * 0.5
+  q = (torch.randn(B, Lq, H, 128, device="cuda") * 0.3).bfloat16().requires_grad_(True)
+  k = (torch.randn(B, Lk, H, 128, device="cuda") * 0.3).bfloat16().requires_grad_(True)
+  v = torch.randn(B, Lk, H, 128, device="cuda").bfloat16().requires_grad_(True)
+  table = (torch.randn(H, 32, device="cuda") * 0.5).requires_grad_(True)
   lens = torch.randint(Lk // 2, Lk + 1, (B,), device="cuda")
   key_mask = torch.arange(Lk, device="cuda")[None, :] < lens[:, None]
-  with torch.no_grad():
-    out = A.flash_attention(q, k, v, bias_table=table, bidirectional=not causal,
-                            key_mask=key_mask, causal=causal)
-    native.check_status()
-    exp = ref.attention(q.float(), k.float(), v.float(),
-                        bias=ref.relative_position_bias(table, Lq, Lk, not causal),
-                        key_mask=key_mask, causal=causal)
-  assert rel(out, exp) < TOL
+  do = torch.randn(B, Lq, H, 128, device="cuda").bfloat16()
+  assert A.flash_supported(q, k, v, None, None)
+  out = A.flash_attention(q, k, v, bias_table=table, bidirectional=not causal,
+                          key_mask=key_mask, causal=causal)
+  out.backward(do)
+  native.check_status()
+  got = [out.detach(), q.grad.clone(), k.grad.clone(), v.grad.clone(), table.grad.clone()]
+  q.grad = k.grad = v.grad = table.grad = None
+  exp = ref.attention(q.float(), k.float(), v.float(),
+                      bias=ref.relative_position_bias(table, Lq, Lk, not causal),
+                      key_mask=key_mask, causal=causal)
+  exp.backward(do.float())
+  for n, g, w in zip(["out", "dq", "dk", "dv", "dbias"], got,
+                     [exp.detach(), q.grad, k.grad, v.grad, table.grad]):
+    assert rel(g, w) < TOL, (n, rel(g, w))
 
 
 @pytest.mark.parametrize("length", [96, 300, 1100])

@@ -98,6 +98,14 @@ def test_gemm_splitk(shape):
   scale = ref.abs().max()
   assert (out.float() - ref).abs().max() / scale < 1e-2
   assert (out_r.float() - (ref + r.float())).abs().max() / scale < 2e-2
+  # a shared workspace that starts clear stays clear: two GEMMs back to back, no fill between
+  ws = torch.zeros(M * N + 64, dtype=torch.float32, device="cuda")
+  first = native.gemm_splitk(a, w, S, workspace=ws, workspace_is_clear=True)
+  second = native.gemm_splitk(a, w, S, residual=r, workspace=ws, workspace_is_clear=True)
+  native.check_status()
+  assert float(ws.abs().max()) == 0.0
+  assert (first.float() - ref).abs().max() / scale < 1e-2
+  assert (second.float() - (ref + r.float())).abs().max() / scale < 2e-2
 
 
 @pytest.mark.parametrize("use_graph", [False, True])

@@ -51,16 +51,16 @@ def test_loss_and_grads_match_cpu_fp32():
   lg.backward()
   native.check_status()
   assert native.launch_count() > before
-  assert abs(float(lg) - float(lc)) / abs(float(lc)) < 2e-2
+  assert abs(float(lg) - float(lc)) / abs(float(lc)) < 1e-3
   from t5x_b200.utils import tree
   fc, fg = tree.flatten_dict(pc), tree.flatten_dict(pg)
   grads = trainer_lib._collect_grads(fg)
-  worst = 0.0
+  # every gradient tensor within 3 % of the fp32 one in relative norm (bf16 activations and
+  # weights against fp32 ones: about 1.7 % on the worst tensor of this model)
   for k in fc:
     a, b = grads[k].float().cpu(), fc[k].grad.float()
-    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
-    worst = max(worst, 1 - cos)
-    assert cos > 0.98, (k, cos)
+    err = float((a - b).norm() / (b.norm() + 1e-12))
+    assert err < 3e-2, (k, err)
 
 
 def _three_steps():
@@ -96,3 +96,45 @@ def test_same_seed_twice_stays_within_a_stated_bound():
   for x, y in zip(a_losses, b_losses):
     assert x == pytest.approx(y, rel=2e-4), (a_losses, b_losses)
   assert a_sum == pytest.approx(b_sum, rel=1e-5)
+
+
+def test_training_shapes_never_reach_the_library_attention(monkeypatch):
+  """Forward + backward of the model families at the shapes their configurations use
+  (head_dim 64 at 512 keys, head_dim 128, 1024-token inputs, a packed prefix LM) stay on the
+  flash kernels: the library fallback with a materialised [b, h, q, k] bias raises here."""
+  from t5x_b200.models import base
+  from t5x_b200.models.decoder_only import network as lm_network
+  from t5x_b200.models.t5 import network
+  from t5x_b200.ops import functional as F
+  from t5x_b200.ops import native
+  from t5x_b200 import trainer as trainer_lib
+
+  def boom(*a, **k):
+    raise AssertionError("library attention reached")
+  monkeypatch.setattr(F, "_library_attention", boom)
+  torch.manual_seed(0)
+  for head_dim, le, ld in [(64, 512, 114), (128, 256, 64), (64, 1024, 229)]:
+    cfg = network.T5Config(vocab_size=512, dtype="bfloat16", emb_dim=256, num_heads=2,
+                           num_encoder_layers=1, num_decoder_layers=1, head_dim=head_dim,
+                           mlp_dim=256, mlp_activations=("gelu", "linear"), dropout_rate=0.1)
+    module = network.Transformer(cfg, device="cuda")
+    trainer_lib.attach_compute_buffers(base.module_param_tree(module), bf16_copy=True,
+                                       main_grad=True)
+    enc = torch.randint(1, 512, (2, le), device="cuda")
+    dec = torch.randint(1, 512, (2, ld), device="cuda")
+    hidden = module(enc, dec, dec, enable_dropout=True, return_hidden=True)
+    hidden.float().sum().backward()
+  cfg = lm_network.TransformerConfig(vocab_size=512, dtype="bfloat16", emb_dim=256, num_heads=2,
+                                     num_layers=1, head_dim=64, mlp_dim=256,
+                                     mlp_activations=("gelu", "linear"), dropout_rate=0.0)
+  lm = lm_network.DecoderWrapper(cfg, device="cuda") if hasattr(lm_network, "DecoderWrapper") \
+      else lm_network.Decoder(cfg, device="cuda")
+  trainer_lib.attach_compute_buffers(base.module_param_tree(lm), bf16_copy=True, main_grad=True)
+  tok = torch.randint(1, 512, (2, 640), device="cuda")
+  pos = torch.arange(640, device="cuda")
+  seg = torch.where(pos < 320, 1, 2)[None].expand(2, 640).contiguous()
+  prefix = ((pos % 320) < 100)[None].expand(2, 640).long().contiguous()
+  out = lm(tok, tok, decoder_segment_ids=seg, decoder_causal_attention=prefix,
+           enable_dropout=False, return_hidden=True)
+  out.float().sum().backward()
+  native.check_status()
