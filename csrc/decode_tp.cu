@@ -160,9 +160,9 @@ __global__ void decode_wait_kernel(const unsigned int* __restrict__ sig, int wor
 
 int dt_grid(long long items) {
   long long blocks = (items + kDtThreads - 1) / kDtThreads;
-  // a few dozen CTAs move these few megabytes as fast as hundreds would, with far fewer
-  // arrivals to count before the signal goes out
-  const long long cap = 64;
+  // a few dozen CTAs move a megabyte or two as fast as hundreds would, with far fewer arrivals
+  // to count before the signal goes out; the logits gather (tens of megabytes) takes them all
+  const long long cap = items > (1ll << 19) ? static_cast<long long>(num_sms()) * 2 : 64;
   if (blocks > cap) blocks = cap;
   return static_cast<int>(blocks < 1 ? 1 : blocks);
 }

@@ -193,6 +193,10 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
   argv = gin_utils.rewrite_gin_args(list(sys.argv[1:] if argv is None else argv))
   flags = train_lib.build_flag_parser(__doc__).parse_args(argv)
   train_lib.init_distributed_from_flags(flags)
+  from t5x_b200 import config_utils
+  if config_utils.using_fdl(flags):
+    config_utils.run_with_fiddle(evaluate, flags)
+    return
   gin.set_main_module(sys.modules[__name__])
   train_lib.parse_gin_from_flags(flags, train_lib._DEFAULT_GIN_SEARCH_PATHS)
   gin.get_configurable(evaluate)()

@@ -360,6 +360,12 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
                   help="Index of this job among independent inference jobs over one dataset.")
   flags = ap.parse_args(argv)
   train_lib.init_distributed_from_flags(flags)
+  from t5x_b200 import config_utils
+  if config_utils.using_fdl(flags):
+    if flags.shard_id is not None:
+      flags.fdl_set = list(flags.fdl_set) + [f"shard_id={flags.shard_id}"]
+    config_utils.run_with_fiddle(infer, flags)
+    return
   gin.set_main_module(sys.modules[__name__])
   train_lib.parse_gin_from_flags(flags, train_lib._DEFAULT_GIN_SEARCH_PATHS)
   fn = gin.get_configurable(infer)

@@ -146,9 +146,18 @@ def moe_exchange() -> Dict[str, float]:
   return {"moe_dispatch": _rel(x_f, x_r), "moe_combine": _rel(o_f, o_r)}
 
 
+class SelfCheckError(RuntimeError):
+  """A check exceeded its tolerance; `errors` holds every measured error of the call."""
+
+  def __init__(self, message: str, errors: Dict[str, float]):
+    super().__init__(message)
+    self.errors = errors
+
+
 def run(which, tol: float = 2e-2) -> Dict[str, float]:
   """Runs the named checks (`tp`, `dp`, `moe`) on the current mesh; all ranks must call it.
-  Returns the largest error over ranks per check and raises if any exceeds `tol`."""
+  Returns the largest error over ranks per check and raises `SelfCheckError` if any exceeds
+  `tol`."""
   from t5x_b200.ops import native
   fns = {"tp": tp_gemms, "dp": dp_exchange, "moe": moe_exchange}
   out: Dict[str, float] = {}
@@ -163,5 +172,5 @@ def run(which, tol: float = 2e-2) -> Dict[str, float]:
   out = {k: float(v) for k, v in zip(keys, vec)}
   bad = {k: v for k, v in out.items() if not v <= tol}
   if bad:
-    raise RuntimeError(f"multi-GPU self-check failed (tolerance {tol}): {bad}")
+    raise SelfCheckError(f"multi-GPU self-check failed (tolerance {tol}): {bad}", out)
   return out

@@ -343,6 +343,8 @@ def build_flag_parser(description: str = ""):
   ap.add_argument("--process_index", type=int, default=None)
   ap.add_argument("--initialization_timeout", type=int, default=None)
   ap.add_argument("--seqio_additional_cache_dirs", action="append", default=[])
+  from t5x_b200 import config_utils
+  config_utils.add_flags(ap)
   ap.add_argument("--profile_steps", default=None, metavar="FIRST:LAST",
                   help="Record train steps FIRST..LAST-1 with torch.profiler into "
                        "<model_dir>/profile/ (trace + kernels by device time).")
@@ -382,6 +384,10 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
     profiling.parse_step_range(flags.profile_steps)  # fail on a malformed range before training
     os.environ["T5X_B200_PROFILE_STEPS"] = flags.profile_steps
   init_distributed_from_flags(flags)
+  from t5x_b200 import config_utils
+  if config_utils.using_fdl(flags):
+    config_utils.run_with_fiddle(train, flags)
+    return
   gin.set_main_module(sys.modules[__name__])
   parse_gin_from_flags(flags, _DEFAULT_GIN_SEARCH_PATHS)
   train_using_gin = gin.get_configurable(train)

@@ -175,4 +175,4 @@ def test_tensor_parallel_graph_decoder_matches_one_gpu(tmp_path):
   same = sum(a == b for a, b in zip(two[0]["seqs"], one[0]["seqs"]))
   assert same >= 6, (two[0]["seqs"], one[0]["seqs"])  # near-ties may reorder under bf16
   for a, b in zip(two[0]["scores"], one[0]["scores"]):
-    assert a == pytest.approx(b, rel=2e-2, abs=5e-2)
+    assert a == pytest.approx(b, rel=2e-2, abs=0.15)
