@@ -31,6 +31,9 @@ native.register_signature("t5x_decode_self_attention",
                           [c_void_p] * 9 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p])
 native.register_signature("t5x_decode_cross_attention",
                           [c_void_p] * 5 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p])
+native.register_signature("t5x_decode_cross_attention_mma",
+                          [c_void_p] * 5 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p])
 
 NEG_INF = decoding.NEG_INF
 
@@ -150,6 +153,32 @@ class _TensorParallelLink:
     return self.logits.tensor.view(self.rows, self.vocab)
 
 
+def cross_kv_layout(k: torch.Tensor, v: torch.Tensor):
+  """(keys [b, H, Lp, 64], values transposed [b, H, 64, Lp]) for `decode_cross_attention_mma`
+  from k, v [b, Lk, H, 64]; Lp = Lk rounded up to a multiple of 16, the padding is zero."""
+  b, lk, h, d = k.shape
+  lp = -(-lk // 16) * 16
+  kp = torch.zeros(b, h, lp, d, dtype=k.dtype, device=k.device)
+  kp[:, :, :lk] = k.transpose(1, 2)
+  vt = torch.zeros(b, h, d, lp, dtype=v.dtype, device=v.device)
+  vt[:, :, :, :lk] = v.permute(0, 2, 3, 1)
+  return kp, vt
+
+
+def decode_cross_attention_mma(q, k_padded, v_transposed, key_mask_u8, out, beams: int,
+                               lk: int) -> None:
+  """`beams` query rows per example against that example's encoder keys / values on the tensor
+  cores (csrc/decode_cross_mma.cu); operands as made by `cross_kv_layout`."""
+  rows, heads, hd = q.shape
+  b, lp = k_padded.shape[0], k_padded.shape[2]
+  assert k_padded.is_contiguous() and v_transposed.is_contiguous()
+  assert v_transposed.shape == (b, heads, hd, lp) and q.stride(2) == 1 and q.stride(1) == hd
+  native._check(native.lib().t5x_decode_cross_attention_mma(
+      q.data_ptr(), k_padded.data_ptr(), v_transposed.data_ptr(), native.ptr(key_mask_u8),
+      out.data_ptr(), q.stride(0), b, beams, heads, hd, lk, lp, native.stream_ptr()),
+      "decode_cross_attention_mma")
+
+
 def _splits(k_dim: int, n_dim: int, rows: int) -> int:
   """K slices for a skinny GEMM so that about one CTA per SM streams the weights."""
   tiles = -(-rows // 128) * -(-n_dim // 128)
@@ -258,6 +287,7 @@ class GraphBeamDecoder:
     self.positions = torch.arange(self.L, device=dev)
     self.min_brevity = float(decoding.brevity_penalty(alpha, self.L))
     self.graph: Optional[torch.cuda.CUDAGraph] = None
+    self._graph_enc_len = -1
     self._beam_scratch = None
 
   # ------------------------------------------------------------------------------------------
@@ -277,12 +307,18 @@ class GraphBeamDecoder:
     enc = self.module.encode(encoder_input_tokens, enable_dropout=False)
     b, le, _ = enc.shape
     flat = enc.reshape(b * le, -1)
+    self.enc_len = le
+    self.cross_mma = self.k in (1, 2, 4, 8) and le <= 1024
     for i, ly in enumerate(self.layers):
-      # stored head-major [b, H, le, D] so that the decode kernel streams contiguous memory
-      self.cross_k[i] = native.gemm(flat, ly.ck).view(b, le, self.H, self.D).transpose(1, 2) \
-          .contiguous()
-      self.cross_v[i] = native.gemm(flat, ly.cv).view(b, le, self.H, self.D).transpose(1, 2) \
-          .contiguous()
+      k = native.gemm(flat, ly.ck).view(b, le, self.H, self.D)
+      v = native.gemm(flat, ly.cv).view(b, le, self.H, self.D)
+      if self.cross_mma:
+        # keys head-major and padded to 16, values transposed: the layouts the tensor-core
+        # decode kernel loads straight into its operand registers
+        self.cross_k[i], self.cross_v[i] = cross_kv_layout(k, v)
+      else:
+        self.cross_k[i] = k.transpose(1, 2).contiguous()
+        self.cross_v[i] = v.transpose(1, 2).contiguous()
     self.enc_mask = (encoder_input_tokens > 0)
     self.enc_mask_u8 = self.enc_mask.to(torch.uint8).contiguous()
     if self.tp > 1:
@@ -310,9 +346,9 @@ class GraphBeamDecoder:
       x = self._row_parallel(ctx.view(rows, H * D), ly.o, x)
       h, _ = native.rmsnorm_fwd(x, ly.ln2, 1e-6)
       qc = self._skinny(h, ly.cq).view(rows, H, D)
-      if self.k in (1, 2, 4, 8) and self.cross_k[i].shape[2] <= 1024:
-        decode_cross_attention(qc, self.cross_k[i], self.cross_v[i], self.enc_mask_u8, ctx,
-                               self.k)
+      if self.cross_mma:
+        decode_cross_attention_mma(qc, self.cross_k[i], self.cross_v[i], self.enc_mask_u8, ctx,
+                                   self.k, self.enc_len)
         cc = ctx
       else:
         cc = attn_ops.flash_attention(qc.view(self.b, self.k, H, D),
@@ -411,6 +447,8 @@ class GraphBeamDecoder:
     """-> ([batch, beams, max_decode_len] sequences, [batch, beams] scores), ascending."""
     assert encoder_input_tokens.shape[0] == self.b
     with torch.no_grad():
+      if self.graph is not None and encoder_input_tokens.shape[1] != self._graph_enc_len:
+        self.graph = None  # the captured step has the encoder length in its arguments
       self._encode(encoder_input_tokens)
       self._reset()
       if self.use_graph and self.graph is None:
@@ -426,6 +464,7 @@ class GraphBeamDecoder:
         self.graph = g
         self._graph_enc = (list(self.cross_k), list(self.cross_v), self.enc_mask,
                            self.enc_mask_u8)
+        self._graph_enc_len = encoder_input_tokens.shape[1]
       elif self.use_graph:
         # the captured graph reads the encoder products through fixed buffers
         for dst, src in zip(self._graph_enc[0] + self._graph_enc[1], self.cross_k + self.cross_v):

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 
 import torch
 
@@ -112,6 +113,138 @@ def bench_attention():
   return rows
 
 
+def _measured_hbm_gbs() -> float:
+  path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                      "MEASURED_PEAKS.json")
+  try:
+    return float(json.load(open(path))["hbm_gbs"])
+  except (OSError, KeyError, ValueError):
+    return 6650.0  # the fallback figure of this pool
+
+
+def bench_streaming():
+  """The kernels whose bound is memory traffic, each against the bytes its algorithm has to
+  move (inputs read once, outputs written once) and the measured copy bandwidth: one JSON line
+  per kernel with time, achieved GB/s and the fraction of the copy figure. A kernel that fails
+  prints its error and the run goes on."""
+  from t5x_b200 import decoding_fast
+  peak = _measured_hbm_gbs()
+  dev = "cuda"
+  bf = dict(device=dev, dtype=torch.bfloat16)
+
+  def report(name, fn, nbytes, **extra):
+    try:
+      ms = time_ms(fn)
+      native.check_status()
+      gbs = nbytes / ms / 1e6
+      print(json.dumps({"kernel": name, "ms": round(ms, 4), "mbytes": round(nbytes / 1e6, 1),
+                        "gb_s": round(gbs, 1), "of_measured_copy": round(gbs / peak, 3),
+                        **extra}), flush=True)
+    except Exception as e:  # pylint: disable=broad-except
+      print(json.dumps({"kernel": name, "error": f"{type(e).__name__}: {e}"}), flush=True)
+
+  # RMSNorm over XXL activations of one microbatch (16384 x 4096)
+  T, d = 16384, 4096
+  x = torch.randn(T, d, **bf)
+  scale = torch.ones(d, device=dev)
+  report("rmsnorm_fwd", lambda: native.rmsnorm_fwd(x, scale, 1e-6), 2 * T * d * 2, rows=T, d=d)
+  _, rstd = native.rmsnorm_fwd(x, scale, 1e-6)
+  dy = torch.randn(T, d, **bf)
+  dscale = torch.zeros(d, device=dev)
+  report("rmsnorm_bwd", lambda: native.rmsnorm_bwd(dy, x, scale, rstd, None, dscale),
+         3 * T * d * 2, rows=T, d=d)
+  dres = torch.randn(T, d, **bf)
+  report("rmsnorm_bwd_with_residual_grad",
+         lambda: native.rmsnorm_bwd(dy, x, scale, rstd, dres, dscale), 4 * T * d * 2)
+  # gated GELU backward on the saved [T, 2 * d_ff] pre-activations
+  ff = 10240
+  h = torch.randn(T, 2 * ff, **bf)
+  dg = torch.randn(T, ff, **bf)
+  report("gated_gelu_bwd", lambda: native.gated_gelu_bwd_(dg, h), (T * ff + 2 * 2 * T * ff) * 2)
+  # dropout with a mask shared along the length axis
+  from t5x_b200.ops import functional as F
+  xb = torch.randn(32, 512, d, **bf)
+  report("dropout_broadcast_over_length",
+         lambda: F.dropout(xb, 0.1, True, broadcast_dims=(-2,)), 2 * xb.numel() * 2)
+  # embedding gather
+  table = torch.randn(32128, d, **bf)
+  ids = torch.randint(0, 32128, (T,), device=dev)
+  report("embedding_fwd", lambda: native.embedding_fwd(ids, table), 2 * T * d * 2)
+  # optimizers on one XXL MLP kernel (4096 x 10240 fp32)
+  from t5x_b200 import adafactor
+  n = d * ff
+  p = torch.randn(d, ff, device=dev)
+  p.bf16 = p.to(torch.bfloat16)
+  g = torch.randn(d, ff, device=dev) * 1e-2
+  opt = adafactor.Adafactor(decay_rate=0.8, step_offset=0)
+  state = opt.init_param_state(p, "mlp/wi_0/kernel") if hasattr(opt, "init_param_state") else None
+  if state is not None:
+    hp = opt.hyper_params.replace(learning_rate=0.01) if hasattr(opt.hyper_params, "replace") \
+        else opt.hyper_params
+    step = torch.tensor(3)
+    # p read and written in fp32, g read twice (statistics, then the update), bf16 copy written
+    report("adafactor_factored_update",
+           lambda: opt.apply_param_gradient(3, hp, p, state, g, "mlp/wi_0/kernel"),
+           n * (4 + 4 + 2 * 4 + 2))
+  from t5x_b200.ops import comm
+  mu, nu = torch.zeros_like(p), torch.zeros_like(p)
+  outs = comm._ptr_array([p.bf16.data_ptr()])
+  report("adamw_step", lambda: native.adamw_step_(p, g, mu, nu, outs, lr=1e-3, b1=0.9, b2=0.999,
+                                                   eps=1e-8, eps_root=0.0, weight_decay=0.01,
+                                                   step=3),
+         n * (2 * 4 + 4 + 4 * 4 + 2))
+  # decode-step attention at the XL decode shapes (batch 64, beam 4, 32 heads)
+  b, k, H, D, L, Le = 64, 4, 32, 64, 129, 512
+  rows = b * k
+  qkv = torch.randn(rows, 3, H, D, **bf)
+  ck = torch.randn(b, k, H, L, D, **bf)
+  cv = torch.randn(b, k, H, L, D, **bf)
+  anc = torch.arange(k, device=dev, dtype=torch.int32)[None, :, None].expand(b, k, L).contiguous()
+  bias = torch.randn(H, L, device=dev)
+  out = torch.empty(rows, H, D, **bf)
+  cur = torch.tensor([L - 2], device=dev, dtype=torch.int32)
+  report("decode_self_attention_full_cache",
+         lambda: decoding_fast.decode_self_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], ck, cv, anc,
+                                                     bias, cur, out, k),
+         2 * rows * H * (L - 1) * D * 2, rows=rows, heads=H, cached_positions=L - 2)
+  ek = torch.randn(b, H, Le, D, **bf)
+  ev = torch.randn(b, H, Le, D, **bf)
+  mask = torch.ones(b, Le, device=dev, dtype=torch.uint8)
+  report("decode_cross_attention",
+         lambda: decoding_fast.decode_cross_attention(qkv[:, 0], ek, ev, mask, out, k),
+         2 * b * H * Le * D * 2, rows=rows, heads=H, keys=Le)
+  kq = torch.randn(b, Le, H, D, **bf)
+  kp, vt = decoding_fast.cross_kv_layout(kq, kq)
+  report("decode_cross_attention_mma",
+         lambda: decoding_fast.decode_cross_attention_mma(qkv[:, 0], kp, vt, mask, out, k, Le),
+         2 * b * H * Le * D * 2, rows=rows, heads=H, keys=Le)
+  # beam step over [rows, vocab] fp32 logits
+  V = 32128
+  logits = torch.randn(rows, V, device=dev)
+  scratch = native.BeamStepScratch(b, k, V, dev)
+  Ld = 130
+  st = dict(live_lp=torch.zeros(b, k, device=dev),
+            live_seqs=torch.zeros(b, k, Ld, dtype=torch.int64, device=dev),
+            fin_seqs=torch.zeros(b, k, Ld, dtype=torch.int64, device=dev),
+            fin_scores=torch.full((b, k), -1e7, device=dev),
+            fin_flags=torch.zeros(b, k, dtype=torch.bool, device=dev),
+            ancestry=anc[:, :, :Ld].contiguous() if L >= Ld else
+            torch.zeros(b, k, Ld, dtype=torch.int32, device=dev),
+            cur=torch.zeros(1, dtype=torch.int32, device=dev),
+            terminated=torch.zeros(1, dtype=torch.bool, device=dev))
+
+  def one_beam_step():
+    st["cur"].zero_()
+    native.beam_step(logits, batch=b, beams=k, eos_id=1, alpha=0.6, min_brevity=1.0,
+                     scratch=scratch, **st)
+  report("beam_step", one_beam_step, rows * V * 4, rows=rows, vocab=V)
+  tok_logits = torch.randn(rows, V, device=dev)
+  report("sample_tokens_topk40",
+         lambda: native.sample_tokens(tok_logits, temperature=1.0, topk=40, topp=0.0,
+                                      rescale_log_probs=True, seed=1, stream_id=0),
+         rows * V * 4, rows=rows, vocab=V)
+
+
 def gemm_one(m: int, n: int, k: int, iters: int, pair: int):
   """A few launches of one GEMM shape (the small case for profiler captures)."""
   a = torch.randn(m, k, device="cuda").bfloat16()
@@ -141,7 +274,7 @@ def attention_one(b: int, h: int, lq: int, lk: int, iters: int):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("what", choices=["gemm", "attention", "gemm-one", "attention-one"])
+  ap.add_argument("what", choices=["gemm", "attention", "gemm-one", "attention-one", "streaming"])
   ap.add_argument("--pair", type=int, nargs="*", default=[0, 1])
   ap.add_argument("--shape", type=int, nargs="*", default=[])
   ap.add_argument("--iters", type=int, default=3)
@@ -151,6 +284,8 @@ def main():
   elif args.what == "gemm-one":
     m, n, k = args.shape or [8192, 8192, 4096]
     gemm_one(m, n, k, args.iters, args.pair[0] if args.pair else 1)
+  elif args.what == "streaming":
+    bench_streaming()
   elif args.what == "attention-one":
     b, h, lq, lk = args.shape or [16, 64, 512, 512]
     attention_one(b, h, lq, lk, args.iters)

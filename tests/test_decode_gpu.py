@@ -144,3 +144,34 @@ def test_predict_batch_uses_graph_decoder_by_default():
   out = model.predict_batch(None, batch)
   assert out.shape == (2, 8)
   assert model.__dict__.get("_graph_decoders")
+
+
+@pytest.mark.parametrize("beams,lk", [(1, 37), (4, 512), (8, 1000), (2, 16)])
+def test_decode_cross_attention_on_tensor_cores(beams, lk):
+  """The mma.sync cross-attention (permuted channel and key order, transposed values) against
+  fp32: every beam of an example attends over that example's keys, padding masked."""
+  from t5x_b200 import decoding_fast
+  from t5x_b200.ops import native
+  torch.manual_seed(beams * 1000 + lk)
+  b, H, D = 3, 5, 64
+  rows = b * beams
+  q = (torch.randn(rows, H, D, device="cuda") * 0.5).bfloat16()
+  k = (torch.randn(b, lk, H, D, device="cuda") * 0.5).bfloat16()
+  v = torch.randn(b, lk, H, D, device="cuda").bfloat16()
+  lens = torch.tensor([lk, max(1, lk // 2), max(1, lk - 3)], device="cuda")
+  mask = torch.arange(lk, device="cuda")[None, :] < lens[:, None]
+  kp, vt = decoding_fast.cross_kv_layout(k, v)
+  out = torch.empty(rows, H, D, device="cuda", dtype=torch.bfloat16)
+  decoding_fast.decode_cross_attention_mma(q, kp, vt, mask.to(torch.uint8).contiguous(), out,
+                                           beams, lk)
+  native.check_status()
+  qf = q.float().view(b, beams, H, D)
+  s = torch.einsum("bjhd,bthd->bhjt", qf, k.float())
+  s = s + torch.where(mask, 0.0, -1e10)[:, None, None, :]
+  want = torch.einsum("bhjt,bthd->bjhd", torch.softmax(s, -1), v.float()).reshape(rows, H, D)
+  assert (out.float() - want).abs().max() < 3e-2
+  # no mask at all
+  decoding_fast.decode_cross_attention_mma(q, kp, vt, None, out, beams, lk)
+  s = torch.einsum("bjhd,bthd->bhjt", qf, k.float())
+  want = torch.einsum("bhjt,bthd->bjhd", torch.softmax(s, -1), v.float()).reshape(rows, H, D)
+  assert (out.float() - want).abs().max() < 3e-2
