@@ -454,25 +454,51 @@ def main() -> None:
   out = measure_train_or_halve(args, args.parallelism, args.steps, args.warmup, not args.skip_e2e)
   if selfcheck is not None:
     out["selfcheck"] = selfcheck
-  if extras and world > 1 and args.parallelism == "dp":
+  # The records beyond the headline one. A phase that raises is reported under its key and ends
+  # the extras on every rank (the ranks agree through the host control group), so that the
+  # headline measurement above is printed whatever happens to them.
+  keys = ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "e2e", "clocks",
+          "gpu_launches", "config", "peak_memory_gb")
+  dec_steps = min(max(args.steps, 3), 5)
+
+  def named_mesh_train():
     nm = measure_train_or_halve(args, "tp", min(max(args.steps, 5), 8), 3, not args.skip_e2e)
-    out["named_mesh"] = {k: nm[k] for k in ("value", "unit", "ms_per_step", "steps", "warmup",
-                                            "e2e", "clocks", "gpu_launches", "final_loss",
-                                            "peak_memory_gb")}
-    out["named_mesh"]["parallelism"] = nm["config"]["parallelism"]
-    out["named_mesh"]["num_microbatches"] = nm["config"]["num_microbatches"]
-  if extras:
+    rec = {k: nm[k] for k in ("value", "unit", "ms_per_step", "steps", "warmup", "e2e", "clocks",
+                              "gpu_launches", "final_loss", "peak_memory_gb")}
+    rec["parallelism"] = nm["config"]["parallelism"]
+    rec["num_microbatches"] = nm["config"]["num_microbatches"]
+    return rec
+
+  def decode(model_parallel):
     import bench_decode
-    dec = bench_decode.measure(world, min(max(args.steps, 3), 5), 3, ClockSampler)
-    keys = ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "e2e", "clocks",
-            "gpu_launches", "config", "peak_memory_gb")
-    out["decode"] = {k: dec[k] for k in keys}
-    if world > 1:
-      # the named decode mesh: a model axis of up to four GPUs, the rest splits the batch
+    dec = bench_decode.measure(world, dec_steps, 3, ClockSampler, model_parallel=model_parallel)
+    return {k: dec[k] for k in keys}
+
+  phases = []
+  if extras and world > 1 and args.parallelism == "dp":
+    phases.append(("named_mesh", named_mesh_train))
+  if extras:
+    phases.append(("decode", lambda: decode(1)))
+    # the named decode mesh (a model axis of up to four GPUs, the rest splits the batch)
+    named = os.environ.get("T5X_B200_BENCH_DECODE_NAMED_MESH", "1" if world > 1 else "0")
+    if world > 1 and named == "1":
+      phases.append(("decode_named_mesh", lambda: decode(min(4, world))))
+  for name, phase in phases:
+    failure = None
+    try:
+      out[name] = phase()
+    except Exception as e:  # pylint: disable=broad-except
+      failure = f"{type(e).__name__}: {e}"[:500]
+      out[name] = {"failed": failure}
+    try:
       _teardown()
-      dec = bench_decode.measure(world, min(max(args.steps, 3), 5), 3, ClockSampler,
-                                 model_parallel=min(4, world))
-      out["decode_named_mesh"] = {k: dec[k] for k in keys}
+      stop = pstate.host_any(failure is not None)
+    except Exception:  # pylint: disable=broad-except
+      stop = True
+    if stop:
+      if failure is None:
+        out[name + "_note"] = "a later phase was skipped: this phase failed on another rank"
+      break
   if rank == 0:
     print(json.dumps(out))
   if world > 1:

@@ -13,14 +13,18 @@
 //     permuted: lane (g, t) (g = lane / 4, t = lane % 4) holds channels 16t .. 16t+15 of "its"
 //     key row (two 16-byte loads) and of its beam's query, and MMA step s uses channels
 //     16t + 4s .. 16t + 4s + 3 as its k positions {2t, 2t+1, 2t+8, 2t+9};
-//   * which key sits in which column of a score tile is free too: in a chunk of 16 keys, tile
-//     0 column n holds key 4(n/2) + n%2 and tile 1 column n holds key 4(n/2) + 2 + n%2, so the
-//     four probabilities that lane t carries into the second product (k positions 2t, 2t+1,
-//     2t+8, 2t+9) belong to the adjacent keys 4t .. 4t+3;
-//   * the values are stored transposed ([example, head, channel, key]), so those four keys of
-//     channel g are one 8-byte load.
-// Scores stay in registers between the two products (Lk <= 1024: 64 values per lane), the row
-// maximum and sum cross the four warps through shared memory, and the partial outputs of the
+//   * which key sits in which column of a score tile is free too: a chunk of 32 keys is four
+//     score tiles (half u = 0, 1; tile = 0, 1), and column n of tile (u, tile) holds key
+//     8(n/2) + 4u + 2 tile + n%2, so the four probabilities that lane t carries into the second
+//     product of half u (k positions 2t, 2t+1, 2t+8, 2t+9) belong to the adjacent keys
+//     8t + 4u .. 8t + 4u + 3;
+//   * the values are stored transposed ([example, head, channel, key]), so the eight keys
+//     8t .. 8t+7 of channel g are one 16-byte load: a warp instruction reads 64 contiguous
+//     bytes of each of 8 channel rows.
+// Key rows are requested two chunks (64 keys) ahead of their use, so that enough bytes are in
+// flight. Scores stay in registers between the two products (Lk <=
+// 1024: 32 values per lane), the row
+// maximum and sum cross the eight warps through shared memory, and the partial outputs of the
 // warps are added there at the end. Masked keys take the additive -1e10 of the reference.
 #include "common.cuh"
 #include "t5x_b200.h"
@@ -28,10 +32,10 @@
 namespace t5x {
 namespace {
 
-constexpr int kXmWarps = 4;
+constexpr int kXmWarps = 8;
 constexpr int kXmThreads = kXmWarps * 32;
 constexpr int kXmMaxKeys = 1024;
-constexpr int kXmMaxChunks = kXmMaxKeys / 16 / kXmWarps;  // 16-key chunks per warp
+constexpr int kXmMaxChunks = kXmMaxKeys / 32 / kXmWarps;  // 32-key chunks per warp
 constexpr float kXmMasked = -1e10f;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -48,9 +52,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
-// key of column n of score tile `tile` (0 or 1) within a 16-key chunk
-__device__ __forceinline__ int key_of_column(int tile, int n) {
-  return 4 * (n >> 1) + 2 * tile + (n & 1);
+// key of column n of score tile (half u, tile) within a 32-key chunk
+__device__ __forceinline__ int key_of_column(int u, int tile, int n) {
+  return 8 * (n >> 1) + 4 * u + 2 * tile + (n & 1);
 }
 
 template <int BEAMS>
@@ -84,52 +88,53 @@ __global__ void __launch_bounds__(kXmThreads)
     qa[4] = hi.x, qa[5] = hi.y, qa[6] = hi.z, qa[7] = hi.w;
   }
 
-  // ---- scores: chunks of 16 keys; every warp takes a contiguous run of chunks ----
-  const int nchunks = Lp / 16;
+  // ---- scores: chunks of 32 keys; every warp takes a contiguous run of chunks ----
+  const int nchunks = Lp / 32;
   const int per_warp = (nchunks + kXmWarps - 1) / kXmWarps;
   const int first = warp * per_warp;
   const int mine = max(0, min(per_warp, nchunks - first));
-  float sc[kXmMaxChunks][4];  // per chunk: tile 0 columns (2t, 2t+1), tile 1 columns (2t, 2t+1)
+  float sc[kXmMaxChunks][2][4];  // [chunk][half]: tile 0 columns (2t, 2t+1), tile 1 columns (2t, 2t+1)
   float mx = -3.0e38f;
-  constexpr int kBatch = 4;  // chunks whose key rows are requested before any is used
+  constexpr int kBatch = 2;  // chunks whose key rows are requested before any is used
 #pragma unroll
   for (int i0 = 0; i0 < kXmMaxChunks; i0 += kBatch) {
     if (i0 >= mine) break;
-    uint4 kr[kBatch][2][2];
+    uint4 kr[kBatch][4][2];
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-      const int base = (first + min(i0 + u, mine - 1)) * 16;
+    for (int c = 0; c < kBatch; ++c) {
+      const int base = (first + min(i0 + c, mine - 1)) * 32;
 #pragma unroll
-      for (int tile = 0; tile < 2; ++tile) {
-        const int key = base + key_of_column(tile, g);  // the key row this lane group loads
+      for (int ut = 0; ut < 4; ++ut) {
+        const int key = base + key_of_column(ut >> 1, ut & 1, g);  // the row this lane group loads
         const uint4* src =
             reinterpret_cast<const uint4*>(kb + static_cast<long long>(key) * 64 + 16 * t);
-        kr[u][tile][0] = src[0];
-        kr[u][tile][1] = src[1];
+        kr[c][ut][0] = src[0];
+        kr[c][ut][1] = src[1];
       }
     }
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-      const int i = i0 + u;
+    for (int c = 0; c < kBatch; ++c) {
+      const int i = i0 + c;
       if (i >= mine) break;
-      const int base = (first + i) * 16;
+      const int base = (first + i) * 32;
 #pragma unroll
-      for (int tile = 0; tile < 2; ++tile) {
-        const uint4 lo = kr[u][tile][0], hi = kr[u][tile][1];
+      for (int ut = 0; ut < 4; ++ut) {
+        const int u = ut >> 1, tile = ut & 1;
+        const uint4 lo = kr[c][ut][0], hi = kr[c][ut][1];
         const uint32_t r[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int s = 0; s < 4; ++s)
-          mma_bf16_16816(c, qa[2 * s], 0u, qa[2 * s + 1], 0u, r[2 * s], r[2 * s + 1]);
-        // c[0], c[1]: beam g, columns 2t and 2t+1 of this tile
+        for (int s_ = 0; s_ < 4; ++s_)
+          mma_bf16_16816(acc4, qa[2 * s_], 0u, qa[2 * s_ + 1], 0u, r[2 * s_], r[2 * s_ + 1]);
+        // acc4[0], acc4[1]: beam g, columns 2t and 2t+1 of this tile
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int kk = base + key_of_column(tile, 2 * t + e);
-          float v = c[e];
+          const int kk = base + key_of_column(u, tile, 2 * t + e);
+          float v = acc4[e];
           const bool exists = kk < Lk;
           if (exists && km != nullptr && km[kk] == 0) v = kXmMasked;
           if (!exists) v = -3.0e38f;  // padding of the key range: weight exactly zero
-          sc[i][2 * tile + e] = v;
+          sc[i][u][2 * tile + e] = v;
           if (exists) mx = fmaxf(mx, v);
         }
       }
@@ -140,7 +145,9 @@ __global__ void __launch_bounds__(kXmThreads)
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
   if (t == 0) s_max[warp][g] = mx;
   __syncthreads();
-  mx = fmaxf(fmaxf(s_max[0][g], s_max[1][g]), fmaxf(s_max[2][g], s_max[3][g]));
+  mx = s_max[0][g];
+#pragma unroll
+  for (int w = 1; w < kXmWarps; ++w) mx = fmaxf(mx, s_max[w][g]);
 
   // ---- probabilities and the value product ----
   float acc[8][4];
@@ -149,33 +156,30 @@ __global__ void __launch_bounds__(kXmThreads)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
   float sum = 0.f;
-  constexpr int kVBatch = 2;  // chunks whose value pieces are requested together
 #pragma unroll
-  for (int i0 = 0; i0 < kXmMaxChunks; i0 += kVBatch) {
-    if (i0 >= mine) break;
-    uint2 vv[kVBatch][8];
+  for (int i = 0; i < kXmMaxChunks; ++i) {
+    if (i >= mine) break;
+    const int base = (first + i) * 32;
+    uint4 vv[8];
 #pragma unroll
-    for (int u = 0; u < kVBatch; ++u) {
-      const int base = (first + min(i0 + u, mine - 1)) * 16;
+    for (int n = 0; n < 8; ++n)
+      vv[n] = *reinterpret_cast<const uint4*>(
+          vb + static_cast<long long>(n * 8 + g) * Lp + base + 8 * t);
 #pragma unroll
-      for (int n = 0; n < 8; ++n)
-        vv[u][n] = *reinterpret_cast<const uint2*>(
-            vb + static_cast<long long>(n * 8 + g) * Lp + base + 4 * t);
-    }
-#pragma unroll
-    for (int u = 0; u < kVBatch; ++u) {
-      const int i = i0 + u;
-      if (i >= mine) break;
+    for (int u = 0; u < 2; ++u) {
       float pr[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        pr[e] = __expf(sc[i][e] - mx);
+        pr[e] = __expf(sc[i][u][e] - mx);
         sum += pr[e];
       }
-      // A operand: k positions (2t, 2t+1) <- tile 0, (2t+8, 2t+9) <- tile 1: keys base + 4t .. + 3
+      // A operand of half u: k positions (2t, 2t+1) <- tile 0, (2t+8, 2t+9) <- tile 1, i.e. keys
+      // base + 8t + 4u .. + 3: the low (u = 0) or high (u = 1) half of the 16 bytes loaded
       const uint32_t pa0 = pack2(pr[0], pr[1]), pa2 = pack2(pr[2], pr[3]);
 #pragma unroll
-      for (int n = 0; n < 8; ++n) mma_bf16_16816(acc[n], pa0, 0u, pa2, 0u, vv[u][n].x, vv[u][n].y);
+      for (int n = 0; n < 8; ++n)
+        mma_bf16_16816(acc[n], pa0, 0u, pa2, 0u, u == 0 ? vv[n].x : vv[n].z,
+                       u == 0 ? vv[n].y : vv[n].w);
     }
   }
   sum += __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -190,8 +194,12 @@ __global__ void __launch_bounds__(kXmThreads)
   __syncthreads();
   for (int i = threadIdx.x; i < BEAMS * 64; i += kXmThreads) {
     const int j = i >> 6, d = i & 63;
-    const float tot = (s_out[0][j][d] + s_out[1][j][d]) + (s_out[2][j][d] + s_out[3][j][d]);
-    const float den = (s_sum[0][j] + s_sum[1][j]) + (s_sum[2][j] + s_sum[3][j]);
+    float tot = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < kXmWarps; ++w) {
+      tot += s_out[w][j][d];
+      den += s_sum[w][j];
+    }
     out[((static_cast<long long>(b) * BEAMS + j) * H + h) * 64 + d] = __float2bfloat16(tot / den);
   }
 }
@@ -202,7 +210,7 @@ __global__ void __launch_bounds__(kXmThreads)
 using namespace t5x;
 
 // q: [batch * beams, heads, 64] bf16 with row stride q_ld; k: [batch, heads, Lp, 64] bf16;
-// vt: [batch, heads, 64, Lp] bf16 (values transposed); Lp = Lk rounded up to a multiple of 16
+// vt: [batch, heads, 64, Lp] bf16 (values transposed); Lp = Lk rounded up to a multiple of 32
 // (the padding may hold anything finite); key_mask: [batch, Lk] uint8 (0 = padding) or null;
 // out: [batch * beams, heads, 64] contiguous. beams in {1, 2, 4, 8}, Lk <= 1024.
 T5X_API int t5x_decode_cross_attention_mma(const void* q, const void* k, const void* vt,
@@ -211,11 +219,11 @@ T5X_API int t5x_decode_cross_attention_mma(const void* q, const void* k, const v
                                            int Lp, void* stream) {
   if (batch <= 0) return 0;
   if (head_dim != 64) return set_error("decode_cross_attention_mma: head_dim must be 64");
-  if (Lk < 1 || Lk > kXmMaxKeys || Lp < Lk || Lp % 16 || Lp > kXmMaxKeys)
-    return set_error("decode_cross_attention_mma: need 1 <= Lk <= Lp <= %d, Lp %% 16 == 0",
+  if (Lk < 1 || Lk > kXmMaxKeys || Lp < Lk || Lp % 32 || Lp > kXmMaxKeys)
+    return set_error("decode_cross_attention_mma: need 1 <= Lk <= Lp <= %d, Lp %% 32 == 0",
                      kXmMaxKeys);
   if (q_ld % 8 || (reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) & 15 ||
-      (reinterpret_cast<uintptr_t>(vt) & 7))
+      (reinterpret_cast<uintptr_t>(vt) & 15))
     return set_error("decode_cross_attention_mma: misaligned operand");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const dim3 grid(batch * heads);

@@ -76,6 +76,56 @@ __global__ void __launch_bounds__(kDropThreads)
   }
 }
 
+// The common case (mask shared along the length axis or not shared at all, col_group == 1):
+// a thread owns 8 adjacent columns and walks down a tile of rows; the mask of those columns
+// depends on the row only through its group, so it is drawn once per group and tile (two Philox
+// blocks for 8 columns) instead of once per element, and no division is left in the loop.
+constexpr int kDropTileRows = 32;
+
+__global__ void __launch_bounds__(kDropThreads)
+    dropout_coltile_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                           const DropParams p) {
+  const int vec_per_row = p.C / 8;
+  const int v = blockIdx.x * kDropThreads + threadIdx.x;
+  if (v >= vec_per_row) return;
+  const int c0 = v * 8;
+  const long long r_begin = static_cast<long long>(blockIdx.y) * kDropTileRows;
+  const long long r_end = min(p.R, r_begin + kDropTileRows);
+  long long group = (r_begin + p.row_offset) / p.group_rows;
+  long long left_in_group = p.group_rows - (r_begin + p.row_offset - group * p.group_rows);
+  uint32_t keep_bits = 0;
+  bool have = false;
+  for (long long r = r_begin; r < r_end; ++r) {
+    if (!have) {
+      const unsigned long long key0 =
+          static_cast<unsigned long long>(group) * p.key_cols + static_cast<unsigned long long>(c0);
+      // c0 is a multiple of 8 and key_cols == C is one too: the 8 keys are two whole blocks
+      const Philox4 a = philox4x32_10(p.seed, p.stream, key0 >> 2);
+      const Philox4 b = philox4x32_10(p.seed, p.stream, (key0 >> 2) + 1);
+      const uint32_t bits[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      keep_bits = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) keep_bits |= ((bits[j] >> 8) < p.keep_threshold ? 1u : 0u) << j;
+      have = true;
+    }
+    uint4 u = *reinterpret_cast<const uint4*>(x + r * p.ldx + c0);
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(h[j]);
+      f.x = ((keep_bits >> (2 * j)) & 1u) ? f.x * p.inv_keep : 0.f;
+      f.y = ((keep_bits >> (2 * j + 1)) & 1u) ? f.y * p.inv_keep : 0.f;
+      h[j] = __floats2bfloat162_rn(f.x, f.y);
+    }
+    *reinterpret_cast<uint4*>(y + r * p.ldy + c0) = u;
+    if (--left_in_group == 0) {
+      ++group;
+      left_in_group = p.group_rows;
+      have = false;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kDropThreads)
     dropout_scalar_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                           const DropParams p) {
@@ -128,7 +178,12 @@ T5X_API int t5x_dropout_bf16(const void* x, void* y, long long R, int C, long lo
   long long blocks = (work + kDropThreads - 1) / kDropThreads;
   const long long cap = static_cast<long long>(num_sms()) * 8;
   if (blocks > cap) blocks = cap;
-  if (vec)
+  const long long row_tiles = (R + kDropTileRows - 1) / kDropTileRows;
+  if (vec && col_group == 1 && row_tiles <= 65535) {
+    const dim3 grid((C / 8 + kDropThreads - 1) / kDropThreads, static_cast<unsigned>(row_tiles));
+    dropout_coltile_kernel<<<grid, kDropThreads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), p);
+  } else if (vec)
     dropout_vec_kernel<<<static_cast<unsigned>(blocks), kDropThreads, 0, st>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), p);
   else

@@ -155,9 +155,9 @@ class _TensorParallelLink:
 
 def cross_kv_layout(k: torch.Tensor, v: torch.Tensor):
   """(keys [b, H, Lp, 64], values transposed [b, H, 64, Lp]) for `decode_cross_attention_mma`
-  from k, v [b, Lk, H, 64]; Lp = Lk rounded up to a multiple of 16, the padding is zero."""
+  from k, v [b, Lk, H, 64]; Lp = Lk rounded up to a multiple of 32, the padding is zero."""
   b, lk, h, d = k.shape
-  lp = -(-lk // 16) * 16
+  lp = -(-lk // 32) * 32
   kp = torch.zeros(b, h, lp, d, dtype=k.dtype, device=k.device)
   kp[:, :, :lk] = k.transpose(1, 2)
   vt = torch.zeros(b, h, d, lp, dtype=v.dtype, device=v.device)

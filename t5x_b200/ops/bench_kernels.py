@@ -245,6 +245,32 @@ def bench_streaming():
          rows * V * 4, rows=rows, vocab=V)
 
 
+def bench_skinny():
+  """The decode-step GEMMs of T5.1.1-XL (256 rows = batch 64 x beam 4): this library's GEMM
+  plain and with K cut into slices, against cuBLAS (torch.matmul), and against the time the
+  weights alone need at the measured copy bandwidth."""
+  peak = _measured_hbm_gbs()
+  rows = 256
+  for name, K, N in [("qkv", 2048, 6144), ("attn_out", 2048, 2048), ("wi_0 (half of the pair)",
+                                                                      2048, 5120),
+                     ("wo", 5120, 2048), ("logits", 2048, 32128)]:
+    a = torch.randn(rows, K, device="cuda").bfloat16()
+    w = (torch.randn(K, N, device="cuda") * 0.02).bfloat16()
+    row = {"gemm": name, "M": rows, "K": K, "N": N,
+           "weight_stream_us": round(K * N * 2 / peak / 1e3, 2)}
+    row["plain_us"] = round(time_ms(lambda: native.gemm(a, w)) * 1e3, 2)
+    ws = torch.zeros(rows * N, dtype=torch.float32, device="cuda")
+    for s_ in (2, 4, 5, 8):
+      if K % s_ or (K // s_) % 64:
+        continue
+      row[f"splitk{s_}_us"] = round(time_ms(
+          lambda: native.gemm_splitk(a, w, s_, workspace=ws, workspace_is_clear=True)) * 1e3, 2)
+    out = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    row["cublas_us"] = round(time_ms(lambda: torch.matmul(a, w, out=out)) * 1e3, 2)
+    print(json.dumps(row), flush=True)
+  native.check_status()
+
+
 def gemm_one(m: int, n: int, k: int, iters: int, pair: int):
   """A few launches of one GEMM shape (the small case for profiler captures)."""
   a = torch.randn(m, k, device="cuda").bfloat16()
@@ -274,7 +300,7 @@ def attention_one(b: int, h: int, lq: int, lk: int, iters: int):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("what", choices=["gemm", "attention", "gemm-one", "attention-one", "streaming"])
+  ap.add_argument("what", choices=["gemm", "attention", "gemm-one", "attention-one", "streaming", "skinny"])
   ap.add_argument("--pair", type=int, nargs="*", default=[0, 1])
   ap.add_argument("--shape", type=int, nargs="*", default=[])
   ap.add_argument("--iters", type=int, default=3)
@@ -286,6 +312,8 @@ def main():
     gemm_one(m, n, k, args.iters, args.pair[0] if args.pair else 1)
   elif args.what == "streaming":
     bench_streaming()
+  elif args.what == "skinny":
+    bench_skinny()
   elif args.what == "attention-one":
     b, h, lq, lk = args.shape or [16, 64, 512, 512]
     attention_one(b, h, lq, lk, args.iters)
