@@ -689,6 +689,82 @@ T5X_API int t5x_f32_to_bf16_residual_clear(void* src, const void* residual, void
   return 0;
 }
 
+// Finishes a split-K GEMM and applies the RMSNorm that follows it, one CTA per row:
+//   x[row] = bf16(ws[row] + residual[row]);  ws[row] = 0;  h[row] = x[row] * rstd * scale
+// with rstd taken from the rounded x, exactly as the separate norm kernel would see it. For the
+// decode step, where every residual projection is followed by a norm: one launch instead of two.
+namespace t5x {
+__global__ void __launch_bounds__(kNormThreads)
+    finish_residual_rmsnorm_kernel(float* __restrict__ ws, const __nv_bfloat16* __restrict__ res,
+                                   const float* __restrict__ scale, __nv_bfloat16* __restrict__ x,
+                                   __nv_bfloat16* __restrict__ h, int d, float eps) {
+  __shared__ float red[32];
+  const int nvec = d / 8;
+  const long long row = blockIdx.x;
+  float vals[kNormMaxVec][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      float4* src = reinterpret_cast<float4*>(ws + row * d) + 2 * v;
+      const float4 a = src[0], b = src[1];
+      src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      if (res != nullptr) {
+        float r[8];
+        unpack8(reinterpret_cast<const Bf16x8*>(res + row * d)[v], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += r[j];
+      }
+      const Bf16x8 packed = pack8(f);
+      reinterpret_cast<Bf16x8*>(x + row * d)[v] = packed;
+      unpack8(packed, vals[i]);  // the norm sees the rounded values
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+    }
+  }
+  const float tot = block_sum(ss, red);
+  const float rstd = rsqrtf(tot / static_cast<float>(d) + eps);
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      const float4 s0 = reinterpret_cast<const float4*>(scale)[2 * v];
+      const float4 s1 = reinterpret_cast<const float4*>(scale)[2 * v + 1];
+      const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * sc[j];
+      reinterpret_cast<Bf16x8*>(h + row * d)[v] = pack8(o);
+    }
+  }
+}
+}  // namespace t5x
+
+// ws [rows, d] fp32 (cleared on return), residual [rows, d] bf16 or null, scale [d] fp32 ->
+// x [rows, d] bf16 and h = rmsnorm(x) [rows, d] bf16. d a multiple of 8, d <= 8192.
+T5X_API int t5x_finish_residual_rmsnorm(void* ws, const void* residual, const void* scale,
+                                        void* x, void* h, int rows, int d, float eps,
+                                        void* stream) {
+  using namespace t5x;
+  if (rows <= 0) return 0;
+  if (d % 8 || d > kNormThreads * 8 * kNormMaxVec)
+    return set_error("finish_residual_rmsnorm: d=%d must be a multiple of 8 and <= %d", d,
+                     kNormThreads * 8 * kNormMaxVec);
+  if (ws == nullptr || scale == nullptr || x == nullptr || h == nullptr)
+    return set_error("finish_residual_rmsnorm: null pointer");
+  finish_residual_rmsnorm_kernel<<<rows, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float*>(ws), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<const float*>(scale), static_cast<__nv_bfloat16*>(x),
+      static_cast<__nv_bfloat16*>(h), d, eps);
+  count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("finish_residual_rmsnorm: %s", cudaGetErrorString(e));
+  return 0;
+}
+
 // dst[i] = bf16(sum over s of slots[s * n + i] (+ residual[i])) with fp32 accumulation: the
 // owner's side of the tensor-parallel reduce-scatter (`slots` is its inbox, one slot per rank).
 namespace t5x {

@@ -31,6 +31,9 @@ native.register_signature("t5x_decode_self_attention",
                           [c_void_p] * 9 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p])
 native.register_signature("t5x_decode_cross_attention",
                           [c_void_p] * 5 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p])
+native.register_signature("t5x_decode_self_attention_mma",
+                          [c_void_p] * 9 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p])
 native.register_signature("t5x_decode_cross_attention_mma",
                           [c_void_p] * 5 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_void_p])
@@ -49,6 +52,28 @@ def decode_self_attention(q, k_new, v_new, cache_k, cache_v, ancestry, bias_row,
       ancestry.data_ptr(), native.ptr(bias_row), cur_index.data_ptr(), out.data_ptr(),
       q.stride(0), rows, beams, heads, hd, cache_k.shape[3], native.stream_ptr()),
       "decode_self_attention")
+
+
+def self_mma_supported(beams: int, max_len: int) -> bool:
+  """Whether `decode_self_attention_mma` covers this search (its chunk budget is 32 chunks of
+  32 positions over all beams)."""
+  return beams in (1, 2, 4, 8) and beams * (-(-max_len // 32)) <= 32 and max_len <= 1024
+
+
+def decode_self_attention_mma(q, k_new, v_new, cache_k, cache_vt, ancestry, bias_row, cur_index,
+                              out, beams: int, max_len: int) -> None:
+  """One decode step of self-attention over an ancestry-indexed cache on the tensor cores
+  (csrc/decode_self_mma.cu): cache_k [b, beams, H, Lc, 64], cache_vt [b, beams, H, 64, Lc]."""
+  rows, heads, hd = q.shape
+  lc = cache_k.shape[3]
+  assert q.stride(2) == 1 and q.stride(1) == hd and k_new.stride() == q.stride() and \
+      v_new.stride() == q.stride()
+  assert cache_k.is_contiguous() and cache_vt.is_contiguous() and cache_vt.shape[4] == lc
+  native._check(native.lib().t5x_decode_self_attention_mma(
+      q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), cache_k.data_ptr(), cache_vt.data_ptr(),
+      ancestry.data_ptr(), native.ptr(bias_row), cur_index.data_ptr(), out.data_ptr(),
+      q.stride(0), rows // beams, beams, heads, hd, max_len, lc, native.stream_ptr()),
+      "decode_self_attention_mma")
 
 
 def decode_cross_attention(q, k, v, key_mask_u8, out, beams: int) -> None:
@@ -267,9 +292,19 @@ class GraphBeamDecoder:
     self.w_logits = wl if wl.shape[0] == c.emb_dim else wl.t()
     self.rel_table = dec.relpos_bias.rel_embedding
     bf = dict(dtype=torch.bfloat16, device=dev)
-    # [batch, beam slot, head, position, dim]: one (slot, head) history is contiguous
-    self.cache_k = [torch.zeros(batch, beams, self.H, self.L, self.D, **bf) for _ in self.layers]
-    self.cache_v = [torch.zeros(batch, beams, self.H, self.L, self.D, **bf) for _ in self.layers]
+    # [batch, beam slot, head, position, dim]: one (slot, head) history is contiguous. For the
+    # tensor-core kernel the cache is padded to a multiple of 32 positions and the values are
+    # kept transposed ([..., dim, position]).
+    self.self_mma = self_mma_supported(beams, self.L)
+    if self.self_mma:
+      lc = -(-self.L // 32) * 32
+      self.cache_k = [torch.zeros(batch, beams, self.H, lc, self.D, **bf) for _ in self.layers]
+      self.cache_v = [torch.zeros(batch, beams, self.H, self.D, lc, **bf) for _ in self.layers]
+    else:
+      self.cache_k = [torch.zeros(batch, beams, self.H, self.L, self.D, **bf)
+                      for _ in self.layers]
+      self.cache_v = [torch.zeros(batch, beams, self.H, self.L, self.D, **bf)
+                      for _ in self.layers]
     self.cross_k: List[Optional[torch.Tensor]] = [None] * len(self.layers)
     self.cross_v: List[Optional[torch.Tensor]] = [None] * len(self.layers)
     self.enc_mask = None
@@ -338,13 +373,21 @@ class GraphBeamDecoder:
     ctx = torch.empty(rows, H, D, dtype=torch.bfloat16, device=self.dev)
     if self.link is not None:
       self.link.begin_step()
+    norms = [(ly.ln1, ly.ln2, ly.ln3) for ly in self.layers]
+    h, _ = native.rmsnorm_fwd(x, norms[0][0], 1e-6)
     for i, ly in enumerate(self.layers):
-      h, _ = native.rmsnorm_fwd(x, ly.ln1, 1e-6)
+      # every residual projection is followed by a norm: `_row_parallel` returns both the new
+      # residual stream and its normed form (one finishing kernel on the single-GPU path)
+      next_ln1 = norms[i + 1][0] if i + 1 < len(self.layers) else self.final_ln
       qkv = native.gemm(h, ly.qkv).view(rows, 3, H, D)
-      decode_self_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], self.cache_k[i], self.cache_v[i],
-                            self.anc, bias_row, self.cur, ctx, self.k)
-      x = self._row_parallel(ctx.view(rows, H * D), ly.o, x)
-      h, _ = native.rmsnorm_fwd(x, ly.ln2, 1e-6)
+      if self.self_mma:
+        decode_self_attention_mma(qkv[:, 0], qkv[:, 1], qkv[:, 2], self.cache_k[i],
+                                  self.cache_v[i], self.anc, bias_row, self.cur, ctx, self.k,
+                                  self.L)
+      else:
+        decode_self_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], self.cache_k[i], self.cache_v[i],
+                              self.anc, bias_row, self.cur, ctx, self.k)
+      x, h = self._row_parallel(ctx.view(rows, H * D), ly.o, x, ly.ln2)
       qc = self._skinny(h, ly.cq).view(rows, H, D)
       if self.cross_mma:
         decode_cross_attention_mma(qc, self.cross_k[i], self.cross_v[i], self.enc_mask_u8, ctx,
@@ -354,31 +397,40 @@ class GraphBeamDecoder:
         cc = attn_ops.flash_attention(qc.view(self.b, self.k, H, D),
                                       self.cross_k[i].transpose(1, 2),
                                       self.cross_v[i].transpose(1, 2), key_mask=self.enc_mask)
-      x = self._row_parallel(cc.reshape(rows, H * D), ly.co, x)
-      h, _ = native.rmsnorm_fwd(x, ly.ln3, 1e-6)
+      x, h = self._row_parallel(cc.reshape(rows, H * D), ly.co, x, ly.ln3)
       g = native.gemm(h, ly.wi0, b2=ly.wi1)
-      x = self._row_parallel(g, ly.wo, x)
-    h, _ = native.rmsnorm_fwd(x, self.final_ln, 1e-6)
+      x, h = self._row_parallel(g, ly.wo, x, next_ln1)
     logits = native.gemm(h, self.w_logits, out_dtype=torch.float32, alpha=self.logit_scale)
     return logits if self.link is None else self.link.gather_logits(logits)
 
-  def _row_parallel(self, a, w, residual):
-    """a @ w + residual for a projection whose input features are split over the model axis:
-    the partial products are summed over the ranks (one all-reduce site of the step)."""
-    if self.link is None:
-      return self._skinny(a, w, residual=residual)
-    return self.link.all_reduce(a, w, residual, _splits(w.shape[0], w.shape[1], self.rows))
+  def _row_parallel(self, a, w, residual, next_norm_scale):
+    """(x, h): x = a @ w + residual and h = rmsnorm(x) * next_norm_scale, for a projection whose
+    input features may be split over the model axis (the partial products are then summed
+    over the ranks: one all-reduce site of the step)."""
+    if self.link is not None:
+      x = self.link.all_reduce(a, w, residual, _splits(w.shape[0], w.shape[1], self.rows))
+      return x, native.rmsnorm_fwd(x, next_norm_scale, 1e-6)[0]
+    if self.rows > 512:
+      x = native.gemm(a, w, residual=residual)
+      return x, native.rmsnorm_fwd(x, next_norm_scale, 1e-6)[0]
+    return native.gemm_splitk_norm(a, w, _splits(w.shape[0], w.shape[1], self.rows),
+                                   residual=residual, scale=next_norm_scale, eps=1e-6,
+                                   workspace=self._workspace())
 
   def _skinny(self, a, w, residual=None):
     """a[rows, K] @ w[K, N] (+ residual) with K split over CTAs when rows are few."""
     if self.rows > 512:
       return native.gemm(a, w, residual=residual)
+    return native.gemm_splitk(a, w, _splits(w.shape[0], w.shape[1], self.rows),
+                              residual=residual, workspace=self._workspace(),
+                              workspace_is_clear=True)
+
+  def _workspace(self) -> torch.Tensor:
     if self._ws is None:
       # zero once; every finishing kernel leaves what it read zero again
       self._ws = torch.zeros(self.rows * max(self.c.emb_dim, self.H * self.D),
                              dtype=torch.float32, device=self.dev)
-    return native.gemm_splitk(a, w, _splits(w.shape[0], w.shape[1], self.rows),
-                              residual=residual, workspace=self._ws, workspace_is_clear=True)
+    return self._ws
 
   def _beam_step(self, flat_logits: torch.Tensor) -> None:
     """One step of the search state update. Beam widths 1, 2, 4 and 8 run the two native

@@ -318,6 +318,36 @@ def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, *,
   return out
 
 
+def gemm_splitk_norm(a: torch.Tensor, b: torch.Tensor, splits: int, *, residual: torch.Tensor,
+                     scale: torch.Tensor, eps: float, workspace: torch.Tensor):
+  """(x, h): x = a @ b + residual (bf16), h = rmsnorm(x) * scale, with K cut into `splits`
+  slices added atomically into `workspace` (fp32, zero on entry, zero again on return) and one
+  finishing kernel per row doing the residual add, the rounding and the norm. Falls back to
+  the separate kernels when the shape does not split."""
+  M, K = a.shape
+  N = b.shape[1]
+  if splits <= 1 or K % splits or (K // splits) % 64 or N % 8 or N > 8192 or b.stride(1) != 1:
+    x = gemm_splitk(a, b, splits, residual=residual, workspace=workspace,
+                    workspace_is_clear=True)
+    return x, rmsnorm_fwd(x, scale, eps)[0]
+  ks = K // splits
+  ws = workspace.view(-1)[:M * N].view(M, N)
+  rc = lib().t5x_gemm_bf16(
+      a.data_ptr(), b.data_ptr(), 0, ws.data_ptr(), M, N, ks, splits, a.stride(0), b.stride(0), N,
+      ks, ks * b.stride(0), 0, 0, 1, 1, 2, EPI_PLAIN, 0, 0, 0, 0, 0, 0, 1.0, 0, stream_ptr())
+  _check(rc, "gemm_splitk")
+  x = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+  h = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+  assert residual is None or residual.is_contiguous()
+  l = lib()
+  l.t5x_finish_residual_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_int, c_int, c_float, c_void_p]
+  _check(l.t5x_finish_residual_rmsnorm(ws.data_ptr(), ptr(residual), scale.data_ptr(),
+                                       x.data_ptr(), h.data_ptr(), M, N, float(eps),
+                                       stream_ptr()), "finish_residual_rmsnorm")
+  return x, h
+
+
 def wgrad_splits(M: int, N: int, K: int) -> int:
   """How many K slices a weight-gradient GEMM [M, K] @ [K, N] should be cut into: 1 unless
   the output has too few tiles to occupy the SMs and K is long (small models: a 768 x 768

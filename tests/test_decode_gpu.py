@@ -175,3 +175,43 @@ def test_decode_cross_attention_on_tensor_cores(beams, lk):
   s = torch.einsum("bjhd,bthd->bhjt", qf, k.float())
   want = torch.einsum("bhjt,bthd->bjhd", torch.softmax(s, -1), v.float()).reshape(rows, H, D)
   assert (out.float() - want).abs().max() < 3e-2
+
+
+@pytest.mark.parametrize("beams,cur", [(4, 17), (4, 0), (8, 70), (1, 40), (2, 95)])
+def test_decode_self_attention_on_tensor_cores(beams, cur):
+  """The mma.sync self-attention over the ancestry-indexed cache (transposed value cache, keys
+  of all slots multiplied and masked by ownership) against the dense fp32 statement; the new
+  key row / value column land in the row's own slot."""
+  from t5x_b200 import decoding_fast
+  from t5x_b200.ops import native
+  torch.manual_seed(beams * 100 + cur)
+  b, L, H, D = 3, 100, 2, 64
+  lc = -(-L // 32) * 32
+  assert decoding_fast.self_mma_supported(beams, L)
+  rows = b * beams
+  cache_k = torch.zeros(b, beams, H, lc, D, device="cuda", dtype=torch.bfloat16)
+  cache_vt = torch.zeros(b, beams, H, D, lc, device="cuda", dtype=torch.bfloat16)
+  hist_k = (torch.randn(b, beams, L, H, D, device="cuda") * 0.5).bfloat16()
+  hist_v = torch.randn(b, beams, L, H, D, device="cuda").bfloat16()
+  # every (slot, position) holds something, also beyond `cur` (stale entries of an earlier
+  # decode must not matter); a beam's history at position t lives in slot anc[b, j, t]
+  cache_k[:, :, :, :L] = hist_k.permute(0, 1, 3, 2, 4)
+  cache_vt[:, :, :, :, :L] = hist_v.permute(0, 1, 3, 4, 2)
+  anc = torch.randint(0, beams, (b, beams, L), device="cuda", dtype=torch.int32)
+  qkv = (torch.randn(rows, 3, H, D, device="cuda") * 0.5).bfloat16()
+  bias = torch.randn(H, L, device="cuda")
+  out = torch.empty(rows, H, D, device="cuda", dtype=torch.bfloat16)
+  cur_t = torch.tensor([cur], device="cuda", dtype=torch.int32)
+  decoding_fast.decode_self_attention_mma(qkv[:, 0], qkv[:, 1], qkv[:, 2], cache_k, cache_vt, anc,
+                                          bias, cur_t, out, beams, L)
+  native.check_status()
+  torch.cuda.synchronize()
+  for r in range(rows):
+    bb, j = divmod(r, beams)
+    ks = torch.stack([hist_k[bb, anc[bb, j, t], t] for t in range(cur)] + [qkv[r, 1]]).float()
+    vs = torch.stack([hist_v[bb, anc[bb, j, t], t] for t in range(cur)] + [qkv[r, 2]]).float()
+    s = torch.einsum("hd,thd->ht", qkv[r, 0].float(), ks) + bias[:, :cur + 1]
+    o = torch.einsum("ht,thd->hd", torch.softmax(s, -1), vs)
+    assert (out[r].float() - o).abs().max() < 3e-2, (r, (out[r].float() - o).abs().max())
+    assert torch.equal(cache_k[bb, j, :, cur], qkv[r, 1])
+    assert torch.equal(cache_vt[bb, j, :, :, cur], qkv[r, 2])
