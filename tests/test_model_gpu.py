@@ -7,13 +7,15 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _build(device, dtype):
+def _build(device, dtype, **config_overrides):
   from t5x_b200 import adafactor, models
   from t5x_b200.data import vocabularies
   from t5x_b200.models.t5 import network
-  cfg = network.T5Config(vocab_size=2048, dtype=dtype, emb_dim=256, num_heads=4,
-                         num_encoder_layers=2, num_decoder_layers=2, head_dim=64, mlp_dim=512,
-                         mlp_activations=("gelu", "linear"), dropout_rate=0.0)
+  options = dict(vocab_size=2048, dtype=dtype, emb_dim=256, num_heads=4, num_encoder_layers=2,
+                 num_decoder_layers=2, head_dim=64, mlp_dim=512,
+                 mlp_activations=("gelu", "linear"), dropout_rate=0.0)
+  options.update(config_overrides)
+  cfg = network.T5Config(**options)
   torch.manual_seed(0)
   module = network.Transformer(cfg, device=device)
   vocab = vocabularies.PassThroughVocabulary(2048)
@@ -138,3 +140,26 @@ def test_training_shapes_never_reach_the_library_attention(monkeypatch):
            enable_dropout=False, return_hidden=True)
   out.float().sum().backward()
   native.check_status()
+
+
+@pytest.mark.parametrize("overrides,smoothing", [(dict(scale_attn_logits=True), 0.0),
+                                                 (dict(head_dim=128, num_heads=2), 0.0),
+                                                 (dict(), 0.1)])
+def test_loss_of_model_variants_matches_cpu_fp32(overrides, smoothing):
+  """The GPU-contrib query scaling (`scale_attn_logits`), head_dim 128 and label smoothing through
+  the fused projection + cross-entropy: bf16 CUDA loss against the fp32 CPU statement."""
+  from t5x_b200 import trainer as trainer_lib
+  from t5x_b200.models import base
+  from t5x_b200.ops import native
+  cpu_model = _build("cpu", "float32", **overrides)
+  gpu_model = _build("cuda", "bfloat16", **overrides)
+  gpu_model.module.load_state_dict(cpu_model.module.state_dict())
+  for m in (cpu_model, gpu_model):
+    m._label_smoothing = smoothing
+  pg = base.module_param_tree(gpu_model.module)
+  trainer_lib.attach_compute_buffers(pg, bf16_copy=True, main_grad=True)
+  lc, _ = cpu_model.loss_fn(base.module_param_tree(cpu_model.module), _batch("cpu"), None)
+  lg, _ = gpu_model.loss_fn(pg, _batch("cuda"), None)
+  lg.backward()
+  native.check_status()
+  assert abs(float(lg) - float(lc)) / abs(float(lc)) < 2e-3

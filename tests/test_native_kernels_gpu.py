@@ -333,3 +333,48 @@ def test_fused_adamw_matches_the_generic_chain():
       torch.testing.assert_close(sf[slot][path[0]][path[1]], sg[slot][path[0]][path[1]],
                                  rtol=2e-5, atol=1e-7)
   assert int(sf["count"]) == int(sg["count"]) == 3
+
+
+@pytest.mark.parametrize("options", [
+    dict(beta1=0.9),
+    dict(weight_decay_rate=0.01, multiply_by_parameter_scale=False),
+    dict(beta1=0.9, weight_decay_rate=0.02, max_parameter_scale=0.04),
+    dict(factored=False, beta1=0.5),
+    dict(skip_nan_updates=True),
+    dict(global_norm_clip_threshold=0.05),
+])
+def test_adafactor_options_on_gpu_match_the_cpu_statement(options):
+  """The optimizer with momentum, weight decay, a parameter-scale ceiling, NaN skipping and
+  global-norm clipping: three steps through the native kernels against the same class on CPU
+  tensors (plain tensor ops)."""
+  from t5x_b200 import adafactor
+  torch.manual_seed(11)
+  shapes = {"dense": {"kernel": (256, 384)}, "norm": {"scale": (384,)},
+            "embed": {"table": (130, 256)}}
+  init = {k: {n: torch.randn(s) * 0.05 for n, s in v.items()} for k, v in shapes.items()}
+  grads = [{k: {n: torch.randn(s) * 0.02 for n, s in v.items()} for k, v in shapes.items()}
+           for _ in range(3)]
+  if options.get("skip_nan_updates"):
+    grads[1]["dense"]["kernel"][3, 7] = float("nan")
+
+  def run(device):
+    params = {k: {n: t.clone().to(device) for n, t in v.items()} for k, v in init.items()}
+    opt = adafactor.Adafactor(decay_rate=0.8, step_offset=0, **options).create(params)
+    for g in grads:
+      g_dev = {k: {n: t.clone().to(device) for n, t in v.items()} for k, v in g.items()}
+      opt = opt.apply_gradient(g_dev, learning_rate=0.01)
+    return opt
+
+  cpu, gpu = run("cpu"), run("cuda")
+  from t5x_b200.ops import native
+  native.check_status()
+  for k, v in shapes.items():
+    for n in v:
+      a, b = gpu.target[k][n].float().cpu(), cpu.target[k][n].float()
+      if options.get("skip_nan_updates"):
+        assert not torch.isnan(a).any()
+      assert rel(a, b) < 2e-5, (k, n, rel(a, b))
+      for slot, val in cpu.state.param_states[k][n].items():
+        got = gpu.state.param_states[k][n][slot].float().cpu()
+        if val.numel() > 1:
+          assert rel(got, val.float()) < 2e-5, (k, n, slot)
