@@ -160,7 +160,8 @@ def measure_train_or_halve(args, parallelism: str, steps: int, warmup: int, e2e:
     if args.microbatches:
       raise
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    first = default_microbatches(args.model, 2 if parallelism == "tp" else world)
+    first = (4 if args.model == "xxl" else 1) if parallelism == "tp" else \
+        default_microbatches(args.model, world)
   _teardown()
   args.microbatches = 2 * first
   try:
@@ -235,7 +236,7 @@ def measure_train(args, parallelism: str, steps: int, warmup: int, with_e2e: boo
                                        loss_normalizing_factor=None)
   state = ts_lib.FlaxOptimTrainState.create(opt, model.get_initial_variables(None, None))
   # tensor-parallel ranks all work on the same microbatch: 32 sequences at a time for XXL
-  n_micro = args.microbatches or (default_microbatches(args.model, 2) if parallelism == "tp"
+  n_micro = args.microbatches or ((4 if args.model == "xxl" else 1) if parallelism == "tp"
                                   else default_microbatches(args.model, world))
   lr_fn = schedules.create_learning_rate_scheduler("constant * rsqrt_decay", 1.0, 10000)
   if moe:

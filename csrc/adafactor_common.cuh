@@ -24,7 +24,13 @@ __device__ __forceinline__ float af_update_scale(const AdafactorScalars& s, floa
     if (h.use_max_scale) ps = fminf(ps, h.max_param_scale);
     scale *= ps;
   }
-  if (h.use_clip) scale /= fmaxf(1.f, sqrtf(s.usq / n) / h.clip_threshold);
+  if (h.use_clip) {
+    // a NaN anywhere in the update makes its RMS NaN, and max(1, NaN) is NaN in the reference
+    // (jnp.maximum): the whole parameter's update is then NaN and, with skip_nan_updates, the
+    // whole parameter keeps its value. fmaxf alone would drop the NaN.
+    const float rms = sqrtf(s.usq / n) / h.clip_threshold;
+    scale /= isnan(rms) ? rms : fmaxf(1.f, rms);
+  }
   return scale;
 }
 

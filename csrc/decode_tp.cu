@@ -134,6 +134,70 @@ __global__ void __launch_bounds__(kDtThreads)
   }
 }
 
+// The same sum, one CTA per row, followed by the RMSNorm that every residual projection of the
+// decode step feeds: x = bf16(sum + residual), h = x * rsqrt(mean(x^2) + eps) * scale, with the
+// statistics taken from the rounded x as the separate norm kernel would see it.
+constexpr int kDtNormMaxVec = 8;  // float4 pieces per thread: d <= 256 * 4 * 8 = 8192
+
+__global__ void __launch_bounds__(kDtThreads)
+    decode_sum_slots_norm_kernel(const float* __restrict__ inbox, int world, int rank, int d,
+                                 long long n, const __nv_bfloat16* __restrict__ res,
+                                 const float* __restrict__ scale, float eps,
+                                 __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ h,
+                                 const unsigned int* __restrict__ sig,
+                                 const unsigned int* __restrict__ step, int* status) {
+  __shared__ float red[kDtThreads / 32];
+  if (!dt_wait_all(sig, world, rank, *step, status, kKernelIdDecodeSum)) return;
+  const long long row = blockIdx.x;
+  const int nvec = d / 4;
+  float4 vals[kDtNormMaxVec];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kDtNormMaxVec; ++i) {
+    const int v = threadIdx.x + i * kDtThreads;
+    if (v < nvec) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (res != nullptr) {
+        const uint2 u = reinterpret_cast<const uint2*>(res + row * d)[v];
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+        const float2 lo = __bfloat1622float2(p[0]), hi = __bfloat1622float2(p[1]);
+        acc = make_float4(lo.x, lo.y, hi.x, hi.y);
+      }
+      for (int s = 0; s < world; ++s) {
+        const float4 t = reinterpret_cast<const float4*>(inbox + s * n + row * d)[v];
+        acc.x += t.x, acc.y += t.y, acc.z += t.z, acc.w += t.w;
+      }
+      uint2 o;
+      __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+      q[0] = __floats2bfloat162_rn(acc.x, acc.y);
+      q[1] = __floats2bfloat162_rn(acc.z, acc.w);
+      reinterpret_cast<uint2*>(x + row * d)[v] = o;
+      const float2 lo = __bfloat1622float2(q[0]), hi = __bfloat1622float2(q[1]);
+      vals[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
+      ss += lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < kDtThreads / 32; ++w) tot += red[w];
+  const float rstd = rsqrtf(tot / static_cast<float>(d) + eps);
+#pragma unroll
+  for (int i = 0; i < kDtNormMaxVec; ++i) {
+    const int v = threadIdx.x + i * kDtThreads;
+    if (v < nvec) {
+      const float4 sc = reinterpret_cast<const float4*>(scale)[v];
+      uint2 o;
+      __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+      q[0] = __floats2bfloat162_rn(vals[i].x * rstd * sc.x, vals[i].y * rstd * sc.y);
+      q[1] = __floats2bfloat162_rn(vals[i].z * rstd * sc.z, vals[i].w * rstd * sc.w);
+      reinterpret_cast<uint2*>(h + row * d)[v] = o;
+    }
+  }
+}
+
 // src [rows, cols] fp32 (this rank's vocabulary slice) -> columns [col0, col0 + cols) of every
 // rank's [rows, ld] buffer; last CTA signals.
 __global__ void __launch_bounds__(kDtThreads)
@@ -230,6 +294,31 @@ T5X_API int t5x_decode_sum_slots(const void* inbox, int world, int rank, long lo
   count_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("decode_sum_slots: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// x [rows, d] bf16 = sum over the `world` slots of inbox ([world][rows * d] fp32) + residual, and
+// h [rows, d] = rmsnorm(x) * scale, after every rank's signal word has reached *step.
+// d a multiple of 4, d <= 8192.
+T5X_API int t5x_decode_sum_slots_norm(const void* inbox, int world, int rank, int rows, int d,
+                                      const void* residual, const void* scale, float eps, void* x,
+                                      void* h, const void* sig, const void* step, void* stream) {
+  if (rows <= 0) return 0;
+  if (d % 4 || d > kDtThreads * 4 * kDtNormMaxVec || world < 1 || world > kDtMaxPeers ||
+      rank < 0 || rank >= world)
+    return set_error("decode_sum_slots_norm: bad arguments (d=%d, world=%d)", d, world);
+  if (inbox == nullptr || scale == nullptr || x == nullptr || h == nullptr || sig == nullptr ||
+      step == nullptr)
+    return set_error("decode_sum_slots_norm: null pointer");
+  decode_sum_slots_norm_kernel<<<rows, kDtThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(inbox), world, rank, d, static_cast<long long>(rows) * d,
+      static_cast<const __nv_bfloat16*>(residual), static_cast<const float*>(scale), eps,
+      static_cast<__nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(h),
+      static_cast<const unsigned int*>(sig), static_cast<const unsigned int*>(step),
+      device_status_buffer());
+  count_launches(1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("decode_sum_slots_norm: %s", cudaGetErrorString(e));
   return 0;
 }
 

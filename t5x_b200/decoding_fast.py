@@ -95,6 +95,9 @@ def _register_tp_signatures():
   native.register_signature("t5x_decode_sum_slots",
                             [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p])
+  native.register_signature("t5x_decode_sum_slots_norm",
+                            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                             native.c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
   native.register_signature("t5x_decode_gather_push",
                             [c_void_p, c_int, c_int, c_int, c_int, pp, pp, c_int, c_int, c_void_p,
                              c_void_p, c_void_p])
@@ -140,9 +143,10 @@ class _TensorParallelLink:
   def _sig_ptrs(self, site: int):
     return self.comm._ptr_array([p + site * 16 * 4 for p in self.sig.peer_ptrs])
 
-  def all_reduce(self, a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor,
-                 splits: int) -> torch.Tensor:
-    """sum over ranks of (a @ w) + residual, bf16 [rows, width], identical on every rank."""
+  def all_reduce(self, a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, splits: int,
+                 norm_scale: Optional[torch.Tensor] = None, eps: float = 1e-6):
+    """x = sum over ranks of (a @ w) + residual, bf16 [rows, width], identical on every rank.
+    With `norm_scale` returns (x, rmsnorm(x) * norm_scale) from one kernel."""
     site = self.site
     self.site += 1
     assert site < self.sites
@@ -155,11 +159,20 @@ class _TensorParallelLink:
         self.ws.data_ptr(), self.n, slots, self._sig_ptrs(site), self.world, self.rank,
         self.step.data_ptr(), self.ticket.data_ptr(), native.stream_ptr()), "decode_push_partial")
     out = torch.empty(self.rows, self.width, dtype=torch.bfloat16, device=a.device)
+    inbox = self.inbox.tensor.data_ptr() + site * self.world * slot_bytes
+    sig = self.sig.tensor.data_ptr() + site * 16 * 4
+    if norm_scale is not None and self.width % 4 == 0 and self.width <= 8192:
+      normed = torch.empty_like(out)
+      native._check(native.lib().t5x_decode_sum_slots_norm(
+          inbox, self.world, self.rank, self.rows, self.width, native.ptr(residual),
+          norm_scale.data_ptr(), float(eps), out.data_ptr(), normed.data_ptr(), sig,
+          self.step.data_ptr(), native.stream_ptr()), "decode_sum_slots_norm")
+      return out, normed
     native._check(native.lib().t5x_decode_sum_slots(
-        self.inbox.tensor.data_ptr() + site * self.world * slot_bytes, self.world, self.rank,
-        self.n, native.ptr(residual), out.data_ptr(),
-        self.sig.tensor.data_ptr() + site * 16 * 4, self.step.data_ptr(), native.stream_ptr()),
-        "decode_sum_slots")
+        inbox, self.world, self.rank, self.n, native.ptr(residual), out.data_ptr(), sig,
+        self.step.data_ptr(), native.stream_ptr()), "decode_sum_slots")
+    if norm_scale is not None:
+      return out, native.rmsnorm_fwd(out, norm_scale, eps)[0]
     return out
 
   def gather_logits(self, local: torch.Tensor) -> torch.Tensor:
@@ -295,7 +308,11 @@ class GraphBeamDecoder:
     # [batch, beam slot, head, position, dim]: one (slot, head) history is contiguous. For the
     # tensor-core kernel the cache is padded to a multiple of 32 positions and the values are
     # kept transposed ([..., dim, position]).
-    self.self_mma = self_mma_supported(beams, self.L)
+    # measured slower than the one-warp-per-row kernel (95 against 75 us per layer at the XL
+    # decode shape: the work of an example and head does not fill a CTA of eight warps), so it
+    # is opt-in
+    self.self_mma = self_mma_supported(beams, self.L) and \
+        os.environ.get("T5X_B200_DECODE_SELF_MMA", "0") == "1"
     if self.self_mma:
       lc = -(-self.L // 32) * 32
       self.cache_k = [torch.zeros(batch, beams, self.H, lc, self.D, **bf) for _ in self.layers]
@@ -408,8 +425,8 @@ class GraphBeamDecoder:
     input features may be split over the model axis (the partial products are then summed
     over the ranks: one all-reduce site of the step)."""
     if self.link is not None:
-      x = self.link.all_reduce(a, w, residual, _splits(w.shape[0], w.shape[1], self.rows))
-      return x, native.rmsnorm_fwd(x, next_norm_scale, 1e-6)[0]
+      return self.link.all_reduce(a, w, residual, _splits(w.shape[0], w.shape[1], self.rows),
+                                  norm_scale=next_norm_scale)
     if self.rows > 512:
       x = native.gemm(a, w, residual=residual)
       return x, native.rmsnorm_fwd(x, next_norm_scale, 1e-6)[0]

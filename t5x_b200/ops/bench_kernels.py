@@ -207,6 +207,13 @@ def bench_streaming():
          lambda: decoding_fast.decode_self_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], ck, cv, anc,
                                                      bias, cur, out, k),
          2 * rows * H * (L - 1) * D * 2, rows=rows, heads=H, cached_positions=L - 2)
+  lc = -(-L // 32) * 32
+  ck2 = torch.randn(b, k, H, lc, D, **bf)
+  cvt = torch.randn(b, k, H, D, lc, **bf)
+  report("decode_self_attention_mma_full_cache",
+         lambda: decoding_fast.decode_self_attention_mma(qkv[:, 0], qkv[:, 1], qkv[:, 2], ck2, cvt,
+                                                         anc, bias, cur, out, k, L),
+         2 * rows * H * (L - 1) * D * 2, rows=rows, heads=H, cached_positions=L - 2)
   ek = torch.randn(b, H, Le, D, **bf)
   ev = torch.randn(b, H, Le, D, **bf)
   mask = torch.ones(b, Le, device=dev, dtype=torch.uint8)
