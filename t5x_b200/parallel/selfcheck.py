@@ -77,6 +77,9 @@ def _tiny_step(sharded: bool):
                               logical_factor_rules=adafactor.standard_logical_factor_rules())
     model = models.EncoderDecoderModel(module, vocab, vocab, opt, z_loss=1e-4)
     state = ts_lib.FlaxOptimTrainState.create(opt, model.get_initial_variables(None, None))
+    # taken before the trainer exists: with the optimizer sharded, a rank holds no fp32 master
+    # of the parameters it does not own until `sync_replicas` brings them back
+    before = torch.cat([p.detach().float().reshape(-1) for p in module.parameters()])
     trainer = trainer_lib.Trainer(model, state, None, [], None, None, 0, lambda s: 0.01, 2)
     per = 4
     g = torch.Generator().manual_seed(3)
@@ -87,7 +90,6 @@ def _tiny_step(sharded: bool):
     sl = slice(st.data_rank * per, (st.data_rank + 1) * per)
     batch = {"encoder_input_tokens": enc[sl], "decoder_input_tokens": dec_in[sl],
              "decoder_target_tokens": dec[sl], "decoder_loss_weights": torch.ones(per, 64)}
-    before = torch.cat([p.detach().float().reshape(-1) for p in module.parameters()])
     with torch.enable_grad():
       trainer.train(iter([batch, batch]), 2, start_step=0).result()
     trainer.sync_replicas()

@@ -479,6 +479,18 @@ class PjitPartitioner(BasePjitPartitioner):
   def logical_axis_rules(self):
     return self._logical_axis_rules
 
+  @property
+  def partitions_parameters_over_data(self) -> bool:
+    """True when the rules place a parameter axis on the 'data' mesh axis
+    (`parameter_partitioning_dims=2`: 'embed' -> 'data', t5x/partitioning.py:584-604). The
+    trainer enacts that as optimizer sharding by ownership over the data axis: each replica
+    holds the fp32 master, the optimizer slots and the update of its share of the parameters."""
+    for logical, mesh_axis in self._logical_axis_rules:
+      axes = mesh_axis if isinstance(mesh_axis, (tuple, list)) else (mesh_axis,)
+      if logical == "embed" and "data" in axes:
+        return True
+    return False
+
   use_shardy_partitioner = False
 
   def partition(self, fn, in_axis_resources, out_axis_resources, static_argnums=(),

@@ -713,8 +713,12 @@ class Trainer(BaseTrainer):
         # backward pass of the layers below it (registered after the buffers are attached)
         self._local_overlap_args = (train_state, opt_def)
       return
-    if (os.environ.get("T5X_B200_OPTIMIZER_SHARDING", "1") == "0" or st.data_size <= 1 or
-        st.expert_size > 1):
+    # A partitioner whose rules shard parameters over 'data' (parameter_partitioning_dims=2) asks
+    # for this layout by itself; otherwise it is the default, which the environment can turn off.
+    asked = bool(getattr(self._partitioner, "partitions_parameters_over_data", False))
+    if st.data_size <= 1 or st.expert_size > 1:
+      return
+    if not asked and os.environ.get("T5X_B200_OPTIMIZER_SHARDING", "1") == "0":
       return
     ctx = zero.enable(tree_utils.flatten_dict(train_state.params), st.data_group)
     if ctx is not None and can_overlap:

@@ -277,7 +277,14 @@ def case_tp_decode(out):
              "kernels_per_step": dec.kernels_per_step}, out)
 
 
-CASES = {"tp_decode": case_tp_decode, "collectives": case_collectives, "train": case_train, "moe": case_moe,
+def case_selfcheck(out):
+  """The data-axis checks that the benchmark runs on its own mesh before it reports a number."""
+  from t5x_b200.parallel import selfcheck
+  _setup()
+  json.dump(selfcheck.run(["dp"]), out)
+
+
+CASES = {"selfcheck": case_selfcheck, "tp_decode": case_tp_decode, "collectives": case_collectives, "train": case_train, "moe": case_moe,
          "tp_ops": case_tp_ops, "tp_train": case_tp_train}
 
 if __name__ == "__main__":

@@ -114,6 +114,14 @@ def test_sharded_optimizer_through_the_switch_matches_peer_loads(tmp_path):
     assert x == pytest.approx(y, rel=1e-2, abs=1e-4)
 
 
+def test_data_axis_selfcheck_passes(tmp_path):
+  """`selfcheck.run` raises when an error exceeds its tolerance; here it must not."""
+  _need_two()
+  for res in _run_ranks("selfcheck", tmp_path):
+    assert res["peer_reduce"] < 1e-5
+    assert res["sharded_adafactor_vs_allreduce"] < 2e-2
+
+
 def test_barrier_gives_up_when_a_peer_never_arrives():
   from t5x_b200.ops import comm, native
   pad = torch.zeros(256, dtype=torch.int32, device="cuda")

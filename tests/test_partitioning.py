@@ -118,3 +118,17 @@ def test_data_layout():
   with pytest.raises(ValueError):
     part.get_data_layout(30)
   assert part.data_partition_spec == P("data")
+
+
+def test_parameter_partitioning_over_data_is_visible_to_the_trainer():
+  """`parameter_partitioning_dims=2` puts 'embed' on the data axis: the partitioner reports it,
+  and the trainer turns that into optimizer sharding over the data axis."""
+  from t5x_b200 import partitioning
+  one = partitioning.PjitPartitioner(
+      num_partitions=1, logical_axis_rules=partitioning.standard_logical_axis_rules(
+          parameter_partitioning_dims=1))
+  two = partitioning.PjitPartitioner(
+      num_partitions=1, logical_axis_rules=partitioning.standard_logical_axis_rules(
+          parameter_partitioning_dims=2))
+  assert not one.partitions_parameters_over_data
+  assert two.partitions_parameters_over_data
