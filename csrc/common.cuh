@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 namespace t5x {
 
 // ---------------------------------------------------------------------------
@@ -393,6 +395,23 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Programmatic dependent launch. A kernel launched with the stream-serialisation attribute
+// (`launch_chained` below) may become resident while the kernel before it on the stream is
+// still running: everything it does before `chain_wait()` overlaps that kernel's tail
+// (barrier initialisation, TMEM allocation, descriptor prefetch, loads of constant weights).
+// `chain_wait()` returns once the preceding kernel has completed and its writes are visible;
+// every thread calls it before its first read of data that an earlier kernel wrote and before
+// its first global write. `chain_release()` lets the kernel after this one start becoming
+// resident once every CTA of this grid has called it (or exited). Both are no-ops in a kernel
+// launched the ordinary way.
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 }  // namespace t5x
 
 // ---------------------------------------------------------------------------
@@ -411,4 +430,25 @@ const CUtensorMap* get_tensor_map(const void* base, int elem_bytes, int rank, co
 int* device_status_buffer();  // per-device status words (zero on success)
 void count_launches(int n);     // bookkeeping: kernels launched by this library
 int num_sms();
+bool chained_launches();  // t5x_set_chained_launches: overlap each kernel's prologue with its predecessor
+bool chained_launches_constant_b();  // level 2: GEMM B operands are constant weights
+
+// Launches `kernel`; with chained launches switched on, as a programmatic dependent of the
+// kernel before it on `stream`. Only kernels that call `chain_wait()` before touching data of
+// earlier kernels may be launched through this.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launches() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 }  // namespace t5x

@@ -60,6 +60,8 @@ __global__ void __launch_bounds__(kDecWarps * 32)
   __shared__ float sprob[kDecWarps][kDecMaxLen];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * kDecWarps + warp;  // (row, head)
+  chain_release();
+  chain_wait();  // q / k / v, the ancestry table and the position come from earlier kernels
   if (item >= rows * H) return;
   const int row = item / H, h = item - row * H;
   const int b = row / beams;
@@ -341,15 +343,16 @@ T5X_API int t5x_decode_self_attention(const void* q, const void* k_new, const vo
   if (beams <= 0 || rows % beams) return set_error("decode_self_attention: rows %% beams != 0");
   if (in_ld % 8) return set_error("decode_self_attention: input row stride must be a multiple of 8");
   const int items = rows * heads;
-  decode_self_attention_kernel<<<(items + kDecWarps - 1) / kDecWarps, kDecWarps * 32, 0,
-                                 static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_new),
-      static_cast<const __nv_bfloat16*>(v_new), static_cast<__nv_bfloat16*>(cache_k),
-      static_cast<__nv_bfloat16*>(cache_v), static_cast<const int*>(ancestry),
-      static_cast<const float*>(bias_row), static_cast<const int*>(cur_index),
-      static_cast<__nv_bfloat16*>(out), in_ld, rows, beams, heads, max_len);
+  cudaError_t e = launch_chained(
+      decode_self_attention_kernel, dim3((items + kDecWarps - 1) / kDecWarps), dim3(kDecWarps * 32),
+      0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(q),
+      static_cast<const __nv_bfloat16*>(k_new), static_cast<const __nv_bfloat16*>(v_new),
+      static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v),
+      static_cast<const int*>(ancestry), static_cast<const float*>(bias_row),
+      static_cast<const int*>(cur_index), static_cast<__nv_bfloat16*>(out), in_ld, rows, beams,
+      heads, max_len);
   count_launches(1);
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("decode_self_attention: %s", cudaGetErrorString(e));
   return 0;
 }

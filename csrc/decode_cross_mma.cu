@@ -76,6 +76,15 @@ __global__ void __launch_bounds__(kXmThreads)
   const __nv_bfloat16* vb = vt + bh * 64 * Lp;
   const uint8_t* km = key_mask == nullptr ? nullptr : key_mask + static_cast<long long>(b) * Lk;
 
+  // Keys and values are encoder products, constant while decoding: this CTA's part of them is
+  // pulled toward L2 while the kernel before this one (which produces q) may still be running.
+  chain_release();
+  for (int line = threadIdx.x; line < Lp; line += kXmThreads) {  // Lp x 128 bytes each
+    prefetch_l2(reinterpret_cast<const char*>(kb) + static_cast<long long>(line) * 128);
+    prefetch_l2(reinterpret_cast<const char*>(vb) + static_cast<long long>(line) * 128);
+  }
+  chain_wait();
+
   // A operand of the score product: this lane's 16 channels of beam g (zero rows beyond the beams)
   uint32_t qa[8];
 #pragma unroll
@@ -232,24 +241,25 @@ T5X_API int t5x_decode_cross_attention_mma(const void* q, const void* k, const v
   auto vp = static_cast<const __nv_bfloat16*>(vt);
   auto mp = static_cast<const uint8_t*>(key_mask);
   auto op = static_cast<__nv_bfloat16*>(out);
+  cudaError_t le = cudaSuccess;
   switch (beams) {
     case 1:
-      decode_cross_mma_kernel<1><<<grid, kXmThreads, 0, st>>>(qp, kp, vp, mp, op, q_ld, heads, Lk, Lp);
+      le = launch_chained(decode_cross_mma_kernel<1>, grid, dim3(kXmThreads), 0, st, qp, kp, vp, mp, op, q_ld, heads, Lk, Lp);
       break;
     case 2:
-      decode_cross_mma_kernel<2><<<grid, kXmThreads, 0, st>>>(qp, kp, vp, mp, op, q_ld, heads, Lk, Lp);
+      le = launch_chained(decode_cross_mma_kernel<2>, grid, dim3(kXmThreads), 0, st, qp, kp, vp, mp, op, q_ld, heads, Lk, Lp);
       break;
     case 4:
-      decode_cross_mma_kernel<4><<<grid, kXmThreads, 0, st>>>(qp, kp, vp, mp, op, q_ld, heads, Lk, Lp);
+      le = launch_chained(decode_cross_mma_kernel<4>, grid, dim3(kXmThreads), 0, st, qp, kp, vp, mp, op, q_ld, heads, Lk, Lp);
       break;
     case 8:
-      decode_cross_mma_kernel<8><<<grid, kXmThreads, 0, st>>>(qp, kp, vp, mp, op, q_ld, heads, Lk, Lp);
+      le = launch_chained(decode_cross_mma_kernel<8>, grid, dim3(kXmThreads), 0, st, qp, kp, vp, mp, op, q_ld, heads, Lk, Lp);
       break;
     default:
       return set_error("decode_cross_attention_mma: beams must be 1, 2, 4 or 8 (got %d)", beams);
   }
   count_launches(1);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = le != cudaSuccess ? le : cudaGetLastError();
   if (e != cudaSuccess) return set_error("decode_cross_attention_mma: %s", cudaGetErrorString(e));
   return 0;
 }

@@ -628,6 +628,8 @@ __global__ void __launch_bounds__(256)
     f32_to_bf16_residual_kernel(float* __restrict__ src, const __nv_bfloat16* __restrict__ res,
                                 __nv_bfloat16* __restrict__ dst, long long n4) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  chain_release();
+  chain_wait();  // the sums in src come from the kernel before this one
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
        i += stride) {
     float4 a = reinterpret_cast<const float4*>(src)[i];
@@ -659,12 +661,12 @@ T5X_API int t5x_f32_to_bf16_residual(const void* src, const void* residual, void
   long long blocks = (n4 + 255) / 256;
   const long long cap = static_cast<long long>(t5x::num_sms()) * 8;
   if (blocks > cap) blocks = cap;
-  t5x::f32_to_bf16_residual_kernel<false><<<static_cast<int>(blocks), 256, 0,
-                                            static_cast<cudaStream_t>(stream)>>>(
-      static_cast<float*>(const_cast<void*>(src)), static_cast<const __nv_bfloat16*>(residual),
-      static_cast<__nv_bfloat16*>(dst), n4);
+  cudaError_t e = t5x::launch_chained(
+      t5x::f32_to_bf16_residual_kernel<false>, dim3(static_cast<int>(blocks)), dim3(256), 0,
+      static_cast<cudaStream_t>(stream), static_cast<float*>(const_cast<void*>(src)),
+      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(dst), n4);
   t5x::count_launches(1);
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return t5x::set_error("f32_to_bf16_residual: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -678,12 +680,12 @@ T5X_API int t5x_f32_to_bf16_residual_clear(void* src, const void* residual, void
   long long blocks = (n4 + 255) / 256;
   const long long cap = static_cast<long long>(t5x::num_sms()) * 8;
   if (blocks > cap) blocks = cap;
-  t5x::f32_to_bf16_residual_kernel<true><<<static_cast<int>(blocks), 256, 0,
-                                           static_cast<cudaStream_t>(stream)>>>(
-      static_cast<float*>(src), static_cast<const __nv_bfloat16*>(residual),
-      static_cast<__nv_bfloat16*>(dst), n4);
+  cudaError_t e = t5x::launch_chained(
+      t5x::f32_to_bf16_residual_kernel<true>, dim3(static_cast<int>(blocks)), dim3(256), 0,
+      static_cast<cudaStream_t>(stream), static_cast<float*>(src),
+      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(dst), n4);
   t5x::count_launches(1);
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess)
     return t5x::set_error("f32_to_bf16_residual_clear: %s", cudaGetErrorString(e));
   return 0;
@@ -703,6 +705,8 @@ __global__ void __launch_bounds__(kNormThreads)
   const long long row = blockIdx.x;
   float vals[kNormMaxVec][8];
   float ss = 0.f;
+  chain_release();
+  chain_wait();  // the sums in ws come from the kernel before this one
 #pragma unroll
   for (int i = 0; i < kNormMaxVec; ++i) {
     const int v = threadIdx.x + i * kNormThreads;
@@ -755,12 +759,13 @@ T5X_API int t5x_finish_residual_rmsnorm(void* ws, const void* residual, const vo
                      kNormThreads * 8 * kNormMaxVec);
   if (ws == nullptr || scale == nullptr || x == nullptr || h == nullptr)
     return set_error("finish_residual_rmsnorm: null pointer");
-  finish_residual_rmsnorm_kernel<<<rows, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<float*>(ws), static_cast<const __nv_bfloat16*>(residual),
-      static_cast<const float*>(scale), static_cast<__nv_bfloat16*>(x),
-      static_cast<__nv_bfloat16*>(h), d, eps);
+  cudaError_t e = launch_chained(
+      finish_residual_rmsnorm_kernel, dim3(rows), dim3(kNormThreads), 0,
+      static_cast<cudaStream_t>(stream), static_cast<float*>(ws),
+      static_cast<const __nv_bfloat16*>(residual), static_cast<const float*>(scale),
+      static_cast<__nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(h), d, eps);
   count_launches(1);
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("finish_residual_rmsnorm: %s", cudaGetErrorString(e));
   return 0;
 }

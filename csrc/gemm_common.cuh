@@ -33,6 +33,7 @@ struct GemmParams {
   float alpha;
   int tiles_m, tiles_n;
   int mt_rot;  // the row-tile walk starts at this tile (tensor-parallel kernels); 0 otherwise
+  int b_constant;  // B is not written by any kernel in flight: it may be loaded before chain_wait()
   int* status;
   // Cross-entropy epilogues. Column c of the product is vocabulary entry ce_vocab_start + c.
   const long long* ce_targets;  // [M] target ids

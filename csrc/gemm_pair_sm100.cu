@@ -90,6 +90,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
+  chain_release();  // the next kernel on the stream may set itself up behind this one
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
@@ -125,18 +126,62 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
     if (lane == 0) {
+      auto load_a = [&](int stage, int k0, int m0, int b) {
+        const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
+        uint8_t* a_dst = sA + stage * kPairABytes;
+        if (!p.a_mn) {
+          tma_load_3d_pair(a_dst, &tmA, bar, k0, m0, b);  // box {64 k, 128 m, 1}
+        } else {
+#pragma unroll
+          for (int j = 0; j < kBM / 64; ++j)  // box {64 m, 64 k, 1}
+            tma_load_3d_pair(a_dst + j * 8192, &tmA, bar, m0 + 64 * j, k0, b);
+        }
+      };
+      auto load_b = [&](int stage, const CUtensorMap* tb, int k0, int n0, int b) {
+        const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
+        uint8_t* b_dst = sB + stage * kPairBBytes;
+        if (!p.b_mn) {
+          tma_load_3d_pair(b_dst, tb, bar, k0, n0, b);  // box {64 k, 128 n, 1}
+        } else {
+#pragma unroll
+          for (int j = 0; j < (BN / 2) / 64; ++j)  // box {64 n, 64 k, 1}
+            tma_load_3d_pair(b_dst + j * 8192, tb, bar, n0 + 64 * j, k0, b);
+        }
+      };
+      // this CTA's 128 B columns of tile column nt: its half of the tile, or (gated) the same
+      // 128 columns of wi_0 for the even CTA and of wi_1 for the odd one
+      auto b_col = [&](int nt) {
+        const int n_tile = nt * kTileN;
+        return (EPI == kEpiGatedGelu) ? n_tile : n_tile + static_cast<int>(cta) * (BN / 2);
+      };
+      const CUtensorMap* tb = (EPI == kEpiGatedGelu && cta == 1) ? &tmB2 : &tmB;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // B is constant (weights that no kernel in flight writes): the B halves of the first
+      // stages are requested before the wait for the preceding kernel, the A halves after it.
+      int preloaded = 0;
+      if (MODE == kTpNone && p.b_constant && pair < total_tiles) {
+        int b, mt, nt;
+        gemm_tile_coords(p, pair, tiles_per_batch, b, mt, nt);
+        preloaded = min(kStages, num_kb);
+        for (int kb = 0; kb < preloaded; ++kb) {
+          if (cta == 0) mbar_expect_tx(&full[kb], 2 * kPairStageBytes);
+          load_b(kb, tb, kb * kBK, b_col(nt), b);
+        }
+        chain_wait();
+        for (int kb = 0; kb < preloaded; ++kb)
+          load_a(kb, kb * kBK, mt * (2 * kBM) + static_cast<int>(cta) * kBM, b);
+        if (preloaded == kStages) phase = 1;
+        else stage = preloaded;
+      } else {
+        chain_wait();
+      }
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
         int b, mt, nt;
         gemm_tile_coords(p, tile, tiles_per_batch, b, mt, nt);
         const int m0 = mt * (2 * kBM) + static_cast<int>(cta) * kBM;
-        const int n_tile = nt * kTileN;
-        // this CTA's 128 B columns: its half of the tile, or (gated) the same 128 columns of
-        // wi_0 for the even CTA and of wi_1 for the odd one
-        const int n0 = (EPI == kEpiGatedGelu) ? n_tile : n_tile + static_cast<int>(cta) * (BN / 2);
-        const CUtensorMap* tb = (EPI == kEpiGatedGelu && cta == 1) ? &tmB2 : &tmB;
+        const int n0 = b_col(nt);
         if (MODE == kTpAllGather && m0 < p.M) {
           // the rows of this CTA's A tile: wait for the row groups of other ranks among them
           const int m_end = min(m0 + kBM, p.M);  // exclusive
@@ -173,7 +218,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
           if (!ok) break;
           fence_proxy_async_all();  // the bulk stores that wrote A, before this TMA reads it
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = preloaded; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             report_status(p.status, kStatusTimeoutProducer, kKernelIdGemmPair, tile, kb);
             *abort_flag = 1;
@@ -181,29 +226,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
             break;
           }
           if (cta == 0) mbar_expect_tx(&full[stage], 2 * kPairStageBytes);
-          const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
-          uint8_t* a_dst = sA + stage * kPairABytes;
-          uint8_t* b_dst = sB + stage * kPairBBytes;
           const int k0 = kb * kBK;
-          if (!p.a_mn) {
-            tma_load_3d_pair(a_dst, &tmA, bar, k0, m0, b);  // box {64 k, 128 m, 1}
-          } else {
-#pragma unroll
-            for (int j = 0; j < kBM / 64; ++j)  // box {64 m, 64 k, 1}
-              tma_load_3d_pair(a_dst + j * 8192, &tmA, bar, m0 + 64 * j, k0, b);
-          }
-          if (!p.b_mn) {
-            tma_load_3d_pair(b_dst, tb, bar, k0, n0, b);  // box {64 k, 128 n, 1}
-          } else {
-#pragma unroll
-            for (int j = 0; j < (BN / 2) / 64; ++j)  // box {64 n, 64 k, 1}
-              tma_load_3d_pair(b_dst + j * 8192, tb, bar, n0 + 64 * j, k0, b);
-          }
+          load_a(stage, k0, m0, b);
+          load_b(stage, tb, k0, n0, b);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
+        preloaded = 0;
       }
     }
   } else if (warp == 1) {
@@ -356,6 +387,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
     const int q = warp & 3;
     int local = 0;
     bool ok = true;
+    chain_wait();  // the epilogue reads residuals and writes C
     const bool c_vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
     const uint32_t drained = mapa_shared(smem_u32(&tmem_empty[0]), 0);
     for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++local) {
@@ -440,10 +472,19 @@ static int launch_pair(const CUtensorMap* tA, const CUtensorMap* tB, const CUten
   int pairs = num_sms() / 2;
   if (max_ctas > 0) pairs = std::min(pairs, std::max(1, max_ctas / 2));
   pairs = std::max(1, std::min(pairs, total));
-  gemm_pair_kernel<EPI, MODE><<<2 * pairs, pair_threads<MODE>(), pair_smem<MODE>(), stream>>>(
-      *tA, *tB, *tB2, p, tp);
+  cudaError_t e;
+  if (MODE == kTpNone) {
+    p.b_constant = chained_launches_constant_b() ? 1 : 0;
+    e = launch_chained(gemm_pair_kernel<EPI, MODE>, dim3(2 * pairs), dim3(pair_threads<MODE>()),
+                       pair_smem<MODE>(), stream, *tA, *tB, *tB2, p, tp);
+  } else {
+    // kernels that wait for other ranks are launched the ordinary way
+    gemm_pair_kernel<EPI, MODE><<<2 * pairs, pair_threads<MODE>(), pair_smem<MODE>(), stream>>>(
+        *tA, *tB, *tB2, p, tp);
+    e = cudaSuccess;
+  }
   count_launches(1);
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("gemm_pair launch: %s", cudaGetErrorString(e));
   return 0;
 }

@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  chain_release();  // the next kernel on the stream may set itself up behind this one
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
@@ -88,15 +89,69 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
+      auto load_a = [&](int stage, int k0, int m0, int b) {
+        uint8_t* a_dst = sA + stage * S::kABytes;
+        if (!p.a_mn) {
+          tma_load_3d(a_dst, &tmA, &full[stage], k0, m0, b);  // box {64, 128, 1}
+        } else {
+#pragma unroll
+          for (int j = 0; j < kBM / 64; ++j)  // box {64 (m), 64 (k), 1}
+            tma_load_3d(a_dst + j * 8192, &tmA, &full[stage], m0 + 64 * j, k0, b);
+        }
+      };
+      auto load_b = [&](int stage, int k0, int n0, int b) {
+        uint8_t* b_dst = sB + stage * S::kBBytes;
+        if (EPI == kEpiGatedGelu) {
+          constexpr int kHalf = BN / 2;  // 128 columns of each of wi_0 and wi_1
+          if (!p.b_mn) {
+            tma_load_3d(b_dst, &tmB, &full[stage], k0, n0, b);
+            tma_load_3d(b_dst + kHalf * 128, &tmB2, &full[stage], k0, n0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kHalf / 64; ++j) {
+              tma_load_3d(b_dst + j * 8192, &tmB, &full[stage], n0 + 64 * j, k0, b);
+              tma_load_3d(b_dst + (kHalf / 64 + j) * 8192, &tmB2, &full[stage], n0 + 64 * j, k0, b);
+            }
+          }
+        } else {
+          if (!p.b_mn) {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)  // box {64, 128, 1}
+              tma_load_3d(b_dst + j * 16384, &tmB, &full[stage], k0, n0 + 128 * j, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)  // box {64 (n), 64 (k), 1}
+              tma_load_3d(b_dst + j * 8192, &tmB, &full[stage], n0 + 64 * j, k0, b);
+          }
+        }
+      };
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // B is constant (weights that no kernel in flight writes): the B halves of the first
+      // stages are requested before the wait for the preceding kernel, the A halves after it.
+      int preloaded = 0;
+      if (p.b_constant && blockIdx.x < total_tiles) {
+        int b, mt, nt;
+        gemm_tile_coords(p, blockIdx.x, tiles_per_batch, b, mt, nt);
+        preloaded = min(kStages, num_kb);
+        for (int kb = 0; kb < preloaded; ++kb) {
+          mbar_expect_tx(&full[kb], S::kStageBytes);
+          load_b(kb, kb * kBK, nt * kTileN, b);
+        }
+        chain_wait();
+        for (int kb = 0; kb < preloaded; ++kb) load_a(kb, kb * kBK, mt * kBM, b);
+        if (preloaded == kStages) phase = 1;
+        else stage = preloaded;
+      } else {
+        chain_wait();
+      }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int b, mt, nt;
         gemm_tile_coords(p, tile, tiles_per_batch, b, mt, nt);
         const int m0 = mt * kBM;
         const int n0 = nt * kTileN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = preloaded; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             report_status(p.status, kStatusTimeoutProducer, kKernelIdGemm, tile, kb);
             *abort_flag = 1;
@@ -104,45 +159,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           mbar_expect_tx(&full[stage], S::kStageBytes);
-          uint8_t* a_dst = sA + stage * S::kABytes;
-          uint8_t* b_dst = sB + stage * S::kBBytes;
           const int k0 = kb * kBK;
-          if (!p.a_mn) {
-            tma_load_3d(a_dst, &tmA, &full[stage], k0, m0, b);  // box {64, 128, 1}
-          } else {
-#pragma unroll
-            for (int j = 0; j < kBM / 64; ++j)  // box {64 (m), 64 (k), 1}
-              tma_load_3d(a_dst + j * 8192, &tmA, &full[stage], m0 + 64 * j, k0, b);
-          }
-          if (EPI == kEpiGatedGelu) {
-            constexpr int kHalf = BN / 2;  // 128 columns of each of wi_0 and wi_1
-            if (!p.b_mn) {
-              tma_load_3d(b_dst, &tmB, &full[stage], k0, n0, b);
-              tma_load_3d(b_dst + kHalf * 128, &tmB2, &full[stage], k0, n0, b);
-            } else {
-#pragma unroll
-              for (int j = 0; j < kHalf / 64; ++j) {
-                tma_load_3d(b_dst + j * 8192, &tmB, &full[stage], n0 + 64 * j, k0, b);
-                tma_load_3d(b_dst + (kHalf / 64 + j) * 8192, &tmB2, &full[stage], n0 + 64 * j, k0,
-                            b);
-              }
-            }
-          } else {
-            if (!p.b_mn) {
-#pragma unroll
-              for (int j = 0; j < BN / 128; ++j)  // box {64, 128, 1}
-                tma_load_3d(b_dst + j * 16384, &tmB, &full[stage], k0, n0 + 128 * j, b);
-            } else {
-#pragma unroll
-              for (int j = 0; j < BN / 64; ++j)  // box {64 (n), 64 (k), 1}
-                tma_load_3d(b_dst + j * 8192, &tmB, &full[stage], n0 + 64 * j, k0, b);
-            }
-          }
+          load_a(stage, k0, m0, b);
+          load_b(stage, k0, n0, b);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
+        preloaded = 0;
       }
     }
   } else if (warp == 1) {
@@ -200,6 +225,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int q = warp & 3;  // TMEM lanes [32q, 32q+32) belong to warps with id % 4 == q
     int local = 0;
     bool ok = true;
+    chain_wait();  // the epilogue reads residuals and writes C
     const bool c_vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
       const int acc = local & 1;
@@ -259,9 +285,11 @@ static int launch_gemm(const CUtensorMap* tA, const CUtensorMap* tB, const CUten
   int grid = std::min(total, num_sms());
   if (max_ctas > 0) grid = std::min(grid, max_ctas);
   if (grid <= 0) return 0;
-  gemm_bf16_kernel<BN, EPI><<<grid, kGemmThreads, S::kTotal, stream>>>(*tA, *tB, *tB2, p);
+  p.b_constant = chained_launches_constant_b() ? 1 : 0;
+  cudaError_t e = launch_chained(gemm_bf16_kernel<BN, EPI>, dim3(grid), dim3(kGemmThreads),
+                                 S::kTotal, stream, *tA, *tB, *tB2, p);
   count_launches(1);
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("gemm launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -372,6 +400,7 @@ static int gemm_impl(const void* A, const void* B, const void* B2, void* C, int 
   p.status = device_status_buffer();
   p.tiles_m = (M + kBM - 1) / kBM;
   p.mt_rot = 0;
+  p.b_constant = 0;
   p.ce_targets = nullptr;
   p.ce_part = nullptr;
   p.ce_arg = nullptr;

@@ -189,5 +189,19 @@ T5X_API int t5x_status_copy_async(int* host_dst, void* stream) {
 // Number of kernels this library has launched in this process (all devices).
 T5X_API long long t5x_launch_count() { return t5x::launches(); }
 
+namespace t5x {
+static thread_local int g_chained = 0;  // per host thread: only the caller's launches change
+bool chained_launches() { return g_chained != 0; }
+bool chained_launches_constant_b() { return g_chained == 2; }
+}  // namespace t5x
+// Applies to the calling host thread. 0 (default): ordinary launches. 1: kernels that support it are launched as programmatic
+// dependents of their predecessor on the stream (their prologue overlaps its tail). 2: as 1,
+// and the caller promises that the B operand of every GEMM it issues is constant (weights that
+// no kernel in flight writes), so that the GEMMs request B before they wait for the predecessor.
+T5X_API int t5x_set_chained_launches(int level) {
+  t5x::g_chained = level < 0 ? 0 : (level > 2 ? 2 : level);
+  return 0;
+}
+
 T5X_API int t5x_num_sms() { return t5x::num_sms(); }
 T5X_API int t5x_abi_version() { return 1; }

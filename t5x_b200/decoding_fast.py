@@ -283,6 +283,9 @@ class GraphBeamDecoder:
     self.check_period = max(1, int(os.environ.get("T5X_B200_DECODE_CHECK_PERIOD",
                                                   termination_check_period)))
     self.replays = 0           # graph replays so far
+    # programmatic dependent launches inside the step (`native.chained_launches`); the
+    # tensor-parallel step keeps ordinary launches: its kernels wait for other ranks
+    self.chain_level = int(os.environ.get("T5X_B200_DECODE_CHAIN", "0")) if self.tp == 1 else 0
     self.kernels_per_step = 0  # this library's kernels inside one captured step
     self.use_graph = use_graph
     dev = module.token_embedder.embedding.device
@@ -509,7 +512,11 @@ class GraphBeamDecoder:
     self.terminated.copy_((worst_fin > best_live).all().view(1))
 
   def _step(self):
-    self._beam_step(self._model_step())
+    if self.chain_level:
+      with native.chained_launches(self.chain_level):
+        self._beam_step(self._model_step())
+    else:
+      self._beam_step(self._model_step())
 
   # ------------------------------------------------------------------------------------------
   def decode(self, encoder_input_tokens: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:

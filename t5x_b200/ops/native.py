@@ -127,6 +127,28 @@ def launch_count() -> int:
   return int(lib().t5x_launch_count())
 
 
+class chained_launches:
+  """Context: kernels of this library that support it are launched as programmatic dependents
+  of the kernel before them on the stream, so that their set-up (barriers, TMEM, descriptor
+  fetches) overlaps that kernel's tail. Level 2 also promises that the B operand of every GEMM
+  issued inside is a constant weight, which those GEMMs then request before they wait for
+  their predecessor. For sequences of short kernels (a decode step); captured into CUDA graphs
+  as programmatic dependencies. Applies to the calling thread."""
+
+  def __init__(self, level: int = 2):
+    self.level = int(level)
+
+  def __enter__(self):
+    l = lib()
+    l.t5x_set_chained_launches.argtypes = [c_int]
+    l.t5x_set_chained_launches(self.level)
+    return self
+
+  def __exit__(self, *exc):
+    lib().t5x_set_chained_launches(0)
+    return False
+
+
 def use_native(t: torch.Tensor) -> bool:
   """Native kernels run for CUDA tensors; on a GPU the library is mandatory."""
   return t.is_cuda

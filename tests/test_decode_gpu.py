@@ -7,15 +7,21 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _model(layers=2, emb=128, heads=2, vocab=512):
+def _model(layers=2, emb=128, heads=2, vocab=512, sharp=False):
   from t5x_b200 import adafactor, models, trainer as trainer_lib
   from t5x_b200.data import vocabularies
   from t5x_b200.models.t5 import network
   cfg = network.T5Config(vocab_size=vocab, dtype="bfloat16", emb_dim=emb, num_heads=heads,
                          num_encoder_layers=layers, num_decoder_layers=layers, head_dim=64,
-                         mlp_dim=256, mlp_activations=("gelu", "linear"), dropout_rate=0.0)
+                         mlp_dim=256, mlp_activations=("gelu", "linear"), dropout_rate=0.0,
+                         logits_via_embedding=not sharp)
   torch.manual_seed(5)
   module = network.Transformer(cfg, device=torch.device("cuda"))
+  if sharp:
+    with torch.no_grad():
+      # sharper next-token distributions than a random initialisation gives: near-ties between
+      # candidates would otherwise let bf16 rounding differences reorder the beams
+      module.decoder.logits_dense.kernel.mul_(8.0)
   v = vocabularies.PassThroughVocabulary(vocab)
   model = models.EncoderDecoderModel(module, v, v, adafactor.Adafactor())
   from t5x_b200.models import base
@@ -134,6 +140,60 @@ def test_graph_beam_decoder_matches_reference_beam_search(use_graph):
   torch.testing.assert_close(scores[:, -1], ref_aux["scores"][:, -1], rtol=2e-2, atol=5e-2)
   agree = (seqs[:, -1] == ref_seqs[:, -1]).float().mean()
   assert agree > 0.9, (seqs[:, -1], ref_seqs[:, -1])
+
+
+@pytest.mark.parametrize("beams", [1, 2, 8])
+def test_graph_beam_decoder_at_other_beam_widths(beams):
+  from t5x_b200 import decoding_fast
+  model = _model(sharp=True)
+  torch.manual_seed(2)
+  b, le, ld = 4, 24, 10
+  enc = torch.randint(2, 512, (b, le), device="cuda")
+  enc[2, 11:] = 0
+  batch = {"encoder_input_tokens": enc,
+           "decoder_input_tokens": torch.zeros(b, ld, dtype=torch.long, device="cuda")}
+  os.environ["T5X_B200_GRAPH_DECODE"] = "0"
+  try:
+    ref_seqs, ref_aux = model.predict_batch_with_aux(None, batch, return_all_decodes=True,
+                                                     num_decodes=beams)
+  finally:
+    os.environ.pop("T5X_B200_GRAPH_DECODE")
+  dec = decoding_fast.GraphBeamDecoder(model.module, b, beams, ld, eos_id=1, alpha=0.6)
+  seqs, scores = dec.decode(enc)
+  assert seqs.shape == ref_seqs.shape == (b, beams, ld)
+  torch.testing.assert_close(scores[:, -1], ref_aux["scores"][:, -1], rtol=2e-2, atol=0.15)
+  agree = (seqs[:, -1] == ref_seqs[:, -1]).float().mean()
+  assert agree > 0.85, (seqs[:, -1], ref_seqs[:, -1])
+
+
+def test_termination_check_period_changes_when_the_loop_ends_not_what_it_returns():
+  """The host looks at the device's 'all batches finished' flag every `period` steps only.
+  With an end-of-sequence id that the model emits early, a short period leaves the loop
+  sooner; the hypotheses and scores are those of a run that never looks."""
+  from t5x_b200 import decoding_fast
+  model = _model(sharp=True)
+  torch.manual_seed(3)
+  b, le, ld, beams = 2, 16, 24, 4
+  enc = torch.randint(2, 512, (b, le), device="cuda")
+  probe = decoding_fast.GraphBeamDecoder(model.module, b, beams, ld, eos_id=1, alpha=0.6,
+                                         termination_check_period=10 ** 6)
+  seqs, _ = probe.decode(enc)
+  early = seqs[:, -1, 1:4].reshape(-1)
+  eos = int(torch.mode(early[early > 1]).values)  # a token that it emits early
+  runs = {}
+  for period in (10 ** 6, 1, 3, 8):
+    dec = decoding_fast.GraphBeamDecoder(model.module, b, beams, ld, eos_id=eos, alpha=0.6,
+                                         termination_check_period=period)
+    out = dec.decode(enc)
+    runs[period] = (out, dec.replays)
+  (want_seqs, want_scores), full = runs[10 ** 6]
+  assert full == ld
+  for period in (1, 3, 8):
+    (got_seqs, got_scores), n = runs[period]
+    assert n <= full and (n == full or n % period == 0)
+    torch.testing.assert_close(got_scores, want_scores)
+    assert torch.equal(got_seqs, want_seqs)
+  assert runs[1][1] <= runs[3][1] + 2 and runs[1][1] <= runs[8][1]
 
 
 def test_predict_batch_uses_graph_decoder_by_default():
