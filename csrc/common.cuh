@@ -404,6 +404,12 @@ __device__ __forceinline__ float warp_max(float v) {
 // its first global write. `chain_release()` lets the kernel after this one start becoming
 // resident once every CTA of this grid has called it (or exited). Both are no-ops in a kernel
 // launched the ordinary way.
+// Nanosecond timer shared by all SMs (for the optional per-CTA phase trace of the GEMM).
+__device__ __forceinline__ long long global_timer_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }

@@ -9,6 +9,11 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
 constexpr int kKernelIdGemm = 1;
+constexpr int kGemmTraceSlots = 8;
+#define T5X_GEMM_TRACE(slot)                                                              \
+  do {                                                                                    \
+    if (p.trace != nullptr) p.trace[blockIdx.x * kGemmTraceSlots + (slot)] = global_timer_ns(); \
+  } while (0)
 
 enum GemmEpilogue : int {
   kEpiPlain = 0,
@@ -34,6 +39,10 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int mt_rot;  // the row-tile walk starts at this tile (tensor-parallel kernels); 0 otherwise
   int b_constant;  // B is not written by any kernel in flight: it may be loaded before chain_wait()
+  // Optional phase trace (t5x_gemm_set_trace): 8 timestamps per CTA for its first tile: entry,
+  // set-up done, first loads issued, first operands landed, last MMA issued, accumulator
+  // complete, epilogue done, exit. Null in normal use.
+  long long* trace;
   int* status;
   // Cross-entropy epilogues. Column c of the product is vocabulary entry ce_vocab_start + c.
   const long long* ce_targets;  // [M] target ids
@@ -138,6 +147,73 @@ __device__ __forceinline__ void load_row_bf16(const __nv_bfloat16* src, float* v
   }
 }
 
+// Coalesced epilogue stores. A lane holds 32 consecutive columns of ONE accumulator row, so a
+// store straight from registers sends 16-byte pieces of 32 different rows per warp
+// instruction: 32 separate 128-byte lines each time, which the load/store unit serialises (a
+// 128 x 128 fp32 tile of split-K atomics took 7 us that way). Instead the warp parks its
+// 32 x 32 block in shared memory (`stage`: 4 KB of this warp, 16-byte chunks XOR-swizzled by
+// row so that neither side has bank conflicts) and writes it out as whole row segments:
+// four rows of 128 bytes (fp32) or eight rows of 64 bytes (bf16) per instruction.
+constexpr int kEpiStageBytesPerWarp = 32 * 128;
+
+// v: this lane's row (32 floats). out: &C[first row of the warp's block][first column], fp32.
+// mode 0: plain store, 2: atomic add. Rows >= rows_valid are skipped. All lanes must call it.
+__device__ __forceinline__ void staged_store_f32(float* stage, const float (&v)[32], float* out,
+                                                 long long ldc, int rows_valid, int lane,
+                                                 int mode) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<float4*>(stage + lane * 32 + ((c ^ (lane & 7)) * 4)) =
+        make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  __syncwarp();
+  const int c = lane & 7;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int row = j * 4 + (lane >> 3);
+    const float4 o = *reinterpret_cast<const float4*>(stage + row * 32 + ((c ^ (row & 7)) * 4));
+    if (row < rows_valid) {
+      float4* dst = reinterpret_cast<float4*>(out + static_cast<long long>(row) * ldc + c * 4);
+      if (mode == 2)
+        atomicAdd(dst, o);
+      else
+        *dst = o;
+    }
+  }
+  __syncwarp();
+}
+
+// The same for a bf16 output: the staged block is 32 rows x 64 bytes (the first half of each
+// 128-byte staging row), written out as eight 64-byte row segments per instruction.
+__device__ __forceinline__ void staged_store_bf16(float* stage, const float (&v)[32],
+                                                  __nv_bfloat16* out, long long ldc,
+                                                  int rows_valid, int lane) {
+  uint4* st4 = reinterpret_cast<uint4*>(stage);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[c * 8 + 0], v[c * 8 + 1]);
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(v[c * 8 + 2], v[c * 8 + 3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[c * 8 + 4], v[c * 8 + 5]);
+    __nv_bfloat162 p3 = __floats2bfloat162_rn(v[c * 8 + 6], v[c * 8 + 7]);
+    uint4 u;
+    u.x = *reinterpret_cast<uint32_t*>(&p0);
+    u.y = *reinterpret_cast<uint32_t*>(&p1);
+    u.z = *reinterpret_cast<uint32_t*>(&p2);
+    u.w = *reinterpret_cast<uint32_t*>(&p3);
+    // row `lane`, 16-byte chunk c of 4, swizzled over the 8 chunk slots of the 128-byte row
+    st4[lane * 8 + ((c ^ (lane & 7)))] = u;
+  }
+  __syncwarp();
+  const int c = lane & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int row = j * 8 + (lane >> 2);
+    const uint4 u = st4[row * 8 + (c ^ (row & 7))];
+    if (row < rows_valid)
+      *reinterpret_cast<uint4*>(out + static_cast<long long>(row) * ldc + c * 8) = u;
+  }
+  __syncwarp();
+}
+
 // Tile order: groups of kRasterGroup row tiles are walked column by column, so that the tiles
 // in flight at one time (one per SM or SM pair) share a few A row blocks and a few B column
 // blocks instead of one A block and every B block; the operands of a wave then fit in L2.
@@ -165,9 +241,10 @@ __device__ __forceinline__ void gemm_tile_coords(const GemmParams& p, int tile, 
 template <int BN, int EPI>
 __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t t_row, int m0,
                                                    int n0, int b, int q, int lane,
-                                                   bool c_vec_ok) {
+                                                   bool c_vec_ok, float* stage = nullptr) {
   const int row = m0 + q * 32 + lane;
   const bool row_ok = row < p.M;
+  const int rows_valid = p.M - (m0 + q * 32);  // of this warp's 32 rows (may exceed 32 or be <= 0)
 
   if (EPI == kEpiGatedGelu) {
     constexpr int kHalf = BN / 2;
@@ -205,6 +282,33 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
       tmem_ld_wait();
       const int col = n0 + c * 32;
       const int n_valid = p.N - col;
+      // whole 32-column blocks go out through the staging buffer (warp-uniform condition)
+      const bool staged = stage != nullptr && n_valid >= 32 && rows_valid > 0 &&
+                          p.accumulate != 1 &&
+                          (p.out_fp32 ? (p.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
+                                      : c_vec_ok);
+      if (staged) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        if (EPI == kEpiResidual && row_ok) {
+          float rr[32];
+          const bool rv = (p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+          load_row_bf16(p.R + b * p.r_batch_stride + static_cast<long long>(row) * p.ldr + col,
+                        rr, n_valid, rv);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += rr[i];
+        }
+        const long long first = b * p.c_batch_stride +
+                                static_cast<long long>(m0 + q * 32) * p.ldc + col;
+        if (p.out_fp32)
+          staged_store_f32(stage, v, reinterpret_cast<float*>(p.C) + first, p.ldc, rows_valid,
+                           lane, p.accumulate);
+        else
+          staged_store_bf16(stage, v, reinterpret_cast<__nv_bfloat16*>(p.C) + first, p.ldc,
+                            rows_valid, lane);
+        continue;
+      }
       if (row_ok && n_valid > 0) {
         float v[32];
 #pragma unroll

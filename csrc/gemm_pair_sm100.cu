@@ -56,7 +56,7 @@ template <int MODE>
 constexpr int pair_smem() {
   return MODE == kTpAllGather       ? kPairSmemTotal + kTpStageBytes
          : MODE == kTpReduceScatter ? kPairSmemTotal + 4 * kRsStageBytesPerWarp
-                                    : kPairSmemTotal;
+                                    : kPairSmemTotal + 4 * kEpiStageBytesPerWarp;
 }
 static_assert(kPairSmemTotal + 4 * kRsStageBytesPerWarp <= 232448, "shared memory per CTA");
 
@@ -413,7 +413,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<MODE>()
       else if (EPI == kEpiCeGrad)
         gemm_epilogue_ce_grad<BN>(p, t_row, m0, n0, q, lane, c_vec_ok);
       else
-        gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok);
+        gemm_epilogue_tile<BN, EPI>(
+            p, t_row, m0, n0, b, q, lane, c_vec_ok,
+            MODE == kTpNone
+                ? reinterpret_cast<float*>(staging + (warp - 2) * kEpiStageBytesPerWarp)
+                : nullptr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(drained + acc * 8);

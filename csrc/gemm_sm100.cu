@@ -22,6 +22,8 @@
 
 namespace t5x {
 
+static thread_local long long* g_gemm_trace = nullptr;  // t5x_gemm_set_trace
+
 template <int BN>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
@@ -29,7 +31,9 @@ struct GemmSmem {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kBarrierBytes = 1024;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 align slack
+  static constexpr int kEpiStageBytes = 4 * kEpiStageBytesPerWarp;  // coalesced epilogue stores
+  static constexpr int kTotal =
+      kStages * kStageBytes + kBarrierBytes + kEpiStageBytes + 1024;  // +1024 align slack
 };
 
 template <int BN, int EPI>
@@ -53,12 +57,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* tmem_empty = bars + 2 * kStages + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* epi_stage = reinterpret_cast<float*>(smem + kStages * S::kStageBytes + S::kBarrierBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   chain_release();  // the next kernel on the stream may set itself up behind this one
   if (threadIdx.x == 0) {
+    T5X_GEMM_TRACE(0);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -81,6 +87,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) T5X_GEMM_TRACE(1);
 
   const int num_kb = (p.K + kBK - 1) / kBK;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
@@ -141,6 +148,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         chain_wait();
         for (int kb = 0; kb < preloaded; ++kb) load_a(kb, kb * kBK, mt * kBM, b);
+        T5X_GEMM_TRACE(2);
         if (preloaded == kStages) phase = 1;
         else stage = preloaded;
       } else {
@@ -162,6 +170,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const int k0 = kb * kBK;
           load_a(stage, k0, m0, b);
           load_b(stage, k0, n0, b);
+          if (tile == blockIdx.x && kb == 0) T5X_GEMM_TRACE(2);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -203,6 +212,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           tc_fence_after();
+          if (local == 0 && kb == 0) T5X_GEMM_TRACE(3);
           const uint32_t a_addr = smem_u32(sA + stage * S::kABytes);
           const uint32_t b_addr = smem_u32(sB + stage * S::kBBytes);
 #pragma unroll
@@ -218,6 +228,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
         if (ok) umma_commit(&tmem_full[acc]);
+        if (local == 0) T5X_GEMM_TRACE(4);
       }
     }
   } else {
@@ -241,16 +252,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         break;
       }
       tc_fence_after();
+      if (local == 0 && warp == 2 && lane == 0) T5X_GEMM_TRACE(5);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       if (EPI == kEpiCeStats)
         gemm_epilogue_ce_stats<BN>(p, t_row, m0, n0, nt, q, lane);
       else if (EPI == kEpiCeGrad)
         gemm_epilogue_ce_grad<BN>(p, t_row, m0, n0, q, lane, c_vec_ok);
       else
-        gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok);
+        gemm_epilogue_tile<BN, EPI>(p, t_row, m0, n0, b, q, lane, c_vec_ok,
+                                    epi_stage + (warp - 2) * (kEpiStageBytesPerWarp / 4));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (local == 0 && warp == 2 && lane == 0) T5X_GEMM_TRACE(6);
     }
   }
 
@@ -265,6 +279,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+    if (lane == 0) T5X_GEMM_TRACE(7);
   }
 }
 
@@ -286,6 +301,7 @@ static int launch_gemm(const CUtensorMap* tA, const CUtensorMap* tB, const CUten
   if (max_ctas > 0) grid = std::min(grid, max_ctas);
   if (grid <= 0) return 0;
   p.b_constant = chained_launches_constant_b() ? 1 : 0;
+  p.trace = g_gemm_trace;
   cudaError_t e = launch_chained(gemm_bf16_kernel<BN, EPI>, dim3(grid), dim3(kGemmThreads),
                                  S::kTotal, stream, *tA, *tB, *tB2, p);
   count_launches(1);
@@ -401,6 +417,7 @@ static int gemm_impl(const void* A, const void* B, const void* B2, void* C, int 
   p.tiles_m = (M + kBM - 1) / kBM;
   p.mt_rot = 0;
   p.b_constant = 0;
+  p.trace = nullptr;
   p.ce_targets = nullptr;
   p.ce_part = nullptr;
   p.ce_arg = nullptr;
@@ -500,6 +517,15 @@ static int gemm_impl(const void* A, const void* B, const void* B2, void* C, int 
                    : launch_gemm<128, kEpiPlain>(tA, tB, tB, p, max_ctas, st);
 }
 }  // namespace t5x
+
+// Phase trace of the one-CTA-per-tile GEMM for profiling: while `buffer` (device memory, 8
+// int64 per CTA of the largest grid, i.e. 8 x the number of SMs) is set, every such GEMM
+// launched from the calling thread records nanosecond timestamps of its first tile's phases
+// (see GemmParams::trace). Null switches it off.
+T5X_API int t5x_gemm_set_trace(void* buffer) {
+  t5x::g_gemm_trace = static_cast<long long*>(buffer);
+  return 0;
+}
 
 T5X_API int t5x_gemm_bf16(const void* A, const void* B, const void* B2, void* C, int M, int N,
                           int K, int batch, long long lda, long long ldb, long long ldc,

@@ -252,30 +252,110 @@ def bench_streaming():
          rows * V * 4, rows=rows, vocab=V)
 
 
+def _graph_us(fns, reps: int = 5) -> float:
+  """Microseconds per call of `fns` replayed as one CUDA graph (median of `reps` replays): the
+  way the decode step issues them, free of the host's launch cost."""
+  for f in fns:
+    f()
+  torch.cuda.synchronize()
+  g = torch.cuda.CUDAGraph()
+  with torch.cuda.graph(g):
+    for f in fns:
+      f()
+  g.replay()
+  torch.cuda.synchronize()
+  times = []
+  for _ in range(reps):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    times.append(e0.elapsed_time(e1))
+  return sorted(times)[len(times) // 2] * 1e3 / len(fns)
+
+
 def bench_skinny():
   """The decode-step GEMMs of T5.1.1-XL (256 rows = batch 64 x beam 4): this library's GEMM
-  plain and with K cut into slices, against cuBLAS (torch.matmul), and against the time the
-  weights alone need at the measured copy bandwidth."""
+  plain and with K cut into slices (with the finishing kernel that adds the residual and applies
+  the next norm), against cuBLAS (torch.matmul), and against the time the weights alone need at
+  the measured copy bandwidth. Each figure is the time per GEMM inside a CUDA graph of 20
+  GEMMs over 20 different weight matrices (more bytes than L2 holds, so the weights are cold)."""
   peak = _measured_hbm_gbs()
-  rows = 256
-  for name, K, N in [("qkv", 2048, 6144), ("attn_out", 2048, 2048), ("wi_0 (half of the pair)",
-                                                                      2048, 5120),
-                     ("wo", 5120, 2048), ("logits", 2048, 32128)]:
+  rows, nw = 256, 20
+  for name, K, N in [("qkv", 2048, 6144), ("attn_out", 2048, 2048), ("wo", 5120, 2048)]:
     a = torch.randn(rows, K, device="cuda").bfloat16()
-    w = (torch.randn(K, N, device="cuda") * 0.02).bfloat16()
+    wts = [(torch.randn(K, N, device="cuda") * 0.02).bfloat16() for _ in range(nw)]
+    res = torch.randn(rows, N, device="cuda").bfloat16()
+    scale = torch.ones(N, device="cuda")
+    out = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    ws = torch.zeros(rows * N, dtype=torch.float32, device="cuda")
     row = {"gemm": name, "M": rows, "K": K, "N": N,
            "weight_stream_us": round(K * N * 2 / peak / 1e3, 2)}
-    row["plain_us"] = round(time_ms(lambda: native.gemm(a, w)) * 1e3, 2)
-    ws = torch.zeros(rows * N, dtype=torch.float32, device="cuda")
-    for s_ in (2, 4, 5, 8):
+    row["plain_us"] = round(_graph_us([(lambda w=w: native.gemm(a, w, out=out)) for w in wts]), 2)
+    for s_ in (2, 4, 8):
       if K % s_ or (K // s_) % 64:
         continue
-      row[f"splitk{s_}_us"] = round(time_ms(
-          lambda: native.gemm_splitk(a, w, s_, workspace=ws, workspace_is_clear=True)) * 1e3, 2)
-    out = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
-    row["cublas_us"] = round(time_ms(lambda: torch.matmul(a, w, out=out)) * 1e3, 2)
+      row[f"splitk{s_}_norm_us"] = round(_graph_us(
+          [(lambda w=w: native.gemm_splitk_norm(a, w, s_, residual=res, scale=scale, eps=1e-6,
+                                                workspace=ws)) for w in wts]), 2)
+    row["cublas_us"] = round(_graph_us([(lambda w=w: torch.matmul(a, w, out=out)) for w in wts]), 2)
     print(json.dumps(row), flush=True)
+  K, N = 2048, 5120
+  a = torch.randn(rows, K, device="cuda").bfloat16()
+  w0 = [(torch.randn(K, N, device="cuda") * 0.02).bfloat16() for _ in range(nw)]
+  w1 = [(torch.randn(K, N, device="cuda") * 0.02).bfloat16() for _ in range(nw)]
+  print(json.dumps({
+      "gemm": "wi_0 | wi_1 with gated GELU", "M": rows, "K": K, "N": N,
+      "weight_stream_us": round(2 * K * N * 2 / peak / 1e3, 2),
+      "fused_us": round(_graph_us([(lambda i=i: native.gemm(a, w0[i], b2=w1[i]))
+                                   for i in range(nw)]), 2),
+      "cublas_two_gemms_us": round(_graph_us(
+          [(lambda i=i: (torch.matmul(a, w0[i]), torch.matmul(a, w1[i]))) for i in range(nw)]), 2)}))
   native.check_status()
+
+
+def gemm_trace(m: int, n: int, k: int, splits: int):
+  """Where the time of one small GEMM goes: per-CTA timestamps of the phases of its first tile
+  (`t5x_gemm_set_trace`), in microseconds after the first CTA's entry; median and maximum over
+  the CTAs. The weights are cold (fresh matrix after an L2 flush), the activations warm."""
+  import ctypes
+  a = torch.randn(m, k, device="cuda").bfloat16()
+  ws = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+  sms = torch.cuda.get_device_properties(0).multi_processor_count
+  trace = torch.zeros(sms * 8, dtype=torch.int64, device="cuda")
+  l = native.lib()
+  l.t5x_gemm_set_trace.argtypes = [ctypes.c_void_p]
+  names = ["entry", "setup_done", "first_loads_issued", "first_operands_landed", "last_mma_issued",
+           "accumulator_complete", "epilogue_done", "exit"]
+  native.gemm_set_pair_mode(0)
+  rows = []
+  for it in range(4):
+    w = (torch.randn(k, n, device="cuda") * 0.02).bfloat16()
+    _flush_l2()
+    native.gemm(a, a.t()[:, :64].contiguous())  # keeps the activations in L2 after the flush
+    torch.cuda.synchronize()
+    trace.zero_()
+    l.t5x_gemm_set_trace(trace.data_ptr())
+    try:
+      if splits > 1:
+        native.gemm_splitk(a, w, splits, workspace=ws, workspace_is_clear=True)
+      else:
+        native.gemm(a, w)
+    finally:
+      l.t5x_gemm_set_trace(None)
+    torch.cuda.synchronize()
+    t = trace.view(sms, 8).cpu()
+    t = t[t[:, 0] > 0]
+    if it == 0 or not len(t):
+      continue  # first launch: descriptor encoding and attribute set-up
+    rel = (t - t[:, 0].min()).double() / 1e3
+    rows.append({"ctas": int(len(t)),
+                 **{nm: [round(float(rel[:, i].median()), 2), round(float(rel[:, i].max()), 2)]
+                    for i, nm in enumerate(names)}})
+  native.check_status()
+  for r in rows:
+    print(json.dumps({"M": m, "N": n, "K": k, "splits": splits, "us_median_max": r}))
 
 
 def gemm_one(m: int, n: int, k: int, iters: int, pair: int):
@@ -307,7 +387,9 @@ def attention_one(b: int, h: int, lq: int, lk: int, iters: int):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("what", choices=["gemm", "attention", "gemm-one", "attention-one", "streaming", "skinny"])
+  ap.add_argument("what", choices=["gemm", "attention", "gemm-one", "attention-one", "streaming", "skinny",
+                                   "gemm-trace"])
+  ap.add_argument("--splits", type=int, default=4)
   ap.add_argument("--pair", type=int, nargs="*", default=[0, 1])
   ap.add_argument("--shape", type=int, nargs="*", default=[])
   ap.add_argument("--iters", type=int, default=3)
@@ -321,6 +403,9 @@ def main():
     bench_streaming()
   elif args.what == "skinny":
     bench_skinny()
+  elif args.what == "gemm-trace":
+    m, n, k = args.shape or [256, 2048, 2048]
+    gemm_trace(m, n, k, args.splits)
   elif args.what == "attention-one":
     b, h, lq, lk = args.shape or [16, 64, 512, 512]
     attention_one(b, h, lq, lk, args.iters)

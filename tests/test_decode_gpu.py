@@ -162,8 +162,12 @@ def test_graph_beam_decoder_at_other_beam_widths(beams):
   seqs, scores = dec.decode(enc)
   assert seqs.shape == ref_seqs.shape == (b, beams, ld)
   torch.testing.assert_close(scores[:, -1], ref_aux["scores"][:, -1], rtol=2e-2, atol=0.15)
-  agree = (seqs[:, -1] == ref_seqs[:, -1]).float().mean()
-  assert agree > 0.85, (seqs[:, -1], ref_seqs[:, -1])
+  # the two paths round differently (bf16 kernels): where the best hypotheses differ, they must
+  # be a near-tie, and most examples must agree outright
+  same = (seqs[:, -1] == ref_seqs[:, -1]).all(dim=1)
+  gap = (scores[:, -1] - ref_aux["scores"][:, -1]).abs()
+  assert bool(((same) | (gap < 0.1)).all()), (seqs[:, -1], ref_seqs[:, -1], gap)
+  assert int(same.sum()) >= b // 2, (seqs[:, -1], ref_seqs[:, -1])
 
 
 def test_termination_check_period_changes_when_the_loop_ends_not_what_it_returns():
