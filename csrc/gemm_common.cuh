@@ -10,6 +10,7 @@ constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
 constexpr int kKernelIdGemm = 1;
 constexpr int kGemmTraceSlots = 8;
+long long* gemm_trace_buffer();  // host: the calling thread's trace buffer, or null
 #define T5X_GEMM_TRACE(slot)                                                              \
   do {                                                                                    \
     if (p.trace != nullptr) p.trace[blockIdx.x * kGemmTraceSlots + (slot)] = global_timer_ns(); \

@@ -23,6 +23,7 @@
 namespace t5x {
 
 static thread_local long long* g_gemm_trace = nullptr;  // t5x_gemm_set_trace
+long long* gemm_trace_buffer() { return g_gemm_trace; }
 
 template <int BN>
 struct GemmSmem {

@@ -264,7 +264,8 @@ class Adafactor(OptimizerDef):
       self._apply_torch(param, state, grad, lr, decay, bool(mbps), weight_decay_rate,
                         averaging_dims, factored_dims)
     if zinfo is not None:
-      comm.peer_push_bf16_(zinfo.bf16_ptrs(), param.bf16, zinfo.numel, skip_rank=zinfo.ctx.rank)
+      comm.peer_push_bf16_(zinfo.bf16_ptrs(), param.bf16, zinfo.numel,
+                           skip_rank=zinfo.push_skip_rank())
     return param, state
 
   def _fused_sharded_ok(self, param, state, grad, averaging_dims, factored_dims) -> bool:

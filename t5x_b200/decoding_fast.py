@@ -236,6 +236,9 @@ def supported(module, decoder_input_tokens: torch.Tensor, decode_fn) -> bool:
   c = module.config
   p = module.token_embedder.embedding
   st = pstate.get()
+  zctx = getattr(getattr(p, "zero", None), "ctx", None)
+  if zctx is not None and getattr(zctx, "shard_weights", False):
+    return False  # layer weights live on their owners; the module's own forward gathers them
   if st.model_size > 1:
     # tensor-parallel decode: heads, mlp and vocabulary split evenly, logits not tied
     import torch.distributed as dist
@@ -286,6 +289,9 @@ class GraphBeamDecoder:
     # programmatic dependent launches inside the step (`native.chained_launches`); the
     # tensor-parallel step keeps ordinary launches: its kernels wait for other ranks
     self.chain_level = int(os.environ.get("T5X_B200_DECODE_CHAIN", "0")) if self.tp == 1 else 0
+    # residual projections through the cluster split-K GEMM (sum over K slices in distributed
+    # shared memory) instead of fp32 atomics into a workspace plus a finishing kernel
+    self.cluster_gemm = os.environ.get("T5X_B200_DECODE_CLUSTER_GEMM", "1") != "0"
     self.kernels_per_step = 0  # this library's kernels inside one captured step
     self.use_graph = use_graph
     dev = module.token_embedder.embedding.device
@@ -433,6 +439,10 @@ class GraphBeamDecoder:
     if self.rows > 512:
       x = native.gemm(a, w, residual=residual)
       return x, native.rmsnorm_fwd(x, next_norm_scale, 1e-6)[0]
+    if self.cluster_gemm:
+      x = native.gemm_skinny(a, w, residual=residual)
+      if x is not None:
+        return x, native.rmsnorm_fwd(x, next_norm_scale, 1e-6)[0]
     return native.gemm_splitk_norm(a, w, _splits(w.shape[0], w.shape[1], self.rows),
                                    residual=residual, scale=next_norm_scale, eps=1e-6,
                                    workspace=self._workspace())
@@ -441,6 +451,10 @@ class GraphBeamDecoder:
     """a[rows, K] @ w[K, N] (+ residual) with K split over CTAs when rows are few."""
     if self.rows > 512:
       return native.gemm(a, w, residual=residual)
+    if self.cluster_gemm:
+      x = native.gemm_skinny(a, w, residual=residual)
+      if x is not None:
+        return x
     return native.gemm_splitk(a, w, _splits(w.shape[0], w.shape[1], self.rows),
                               residual=residual, workspace=self._workspace(),
                               workspace_is_clear=True)

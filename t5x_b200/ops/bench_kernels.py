@@ -299,6 +299,15 @@ def bench_skinny():
       row[f"splitk{s_}_norm_us"] = round(_graph_us(
           [(lambda w=w: native.gemm_splitk_norm(a, w, s_, residual=res, scale=scale, eps=1e-6,
                                                 workspace=ws)) for w in wts]), 2)
+    if native.gemm_skinny_splits(rows, N, K) > 0:
+      # K split over a cluster, partial products added through distributed shared memory
+      row["cluster_splits"] = native.gemm_skinny_splits(rows, N, K)
+      row["cluster_us"] = round(_graph_us(
+          [(lambda w=w: native.gemm_skinny(a, w, residual=res, out=out)) for w in wts]), 2)
+      hn = torch.empty_like(out)
+      row["cluster_norm_us"] = round(_graph_us(
+          [(lambda w=w: native.rmsnorm_fwd(native.gemm_skinny(a, w, residual=res, out=out), scale,
+                                           1e-6, out=hn)) for w in wts]), 2)
     row["cublas_us"] = round(_graph_us([(lambda w=w: torch.matmul(a, w, out=out)) for w in wts]), 2)
     print(json.dumps(row), flush=True)
   K, N = 2048, 5120
@@ -328,6 +337,9 @@ def gemm_trace(m: int, n: int, k: int, splits: int):
   l.t5x_gemm_set_trace.argtypes = [ctypes.c_void_p]
   names = ["entry", "setup_done", "first_loads_issued", "first_operands_landed", "last_mma_issued",
            "accumulator_complete", "epilogue_done", "exit"]
+  if splits == 0:  # the cluster split-K kernel records its own phases
+    names = ["entry", "setup_done", "first_loads_issued", "first_operands_landed",
+             "accumulator_complete", "tile_parked", "peer_rows_received", "rows_stored"]
   native.gemm_set_pair_mode(0)
   rows = []
   for it in range(4):
@@ -338,7 +350,9 @@ def gemm_trace(m: int, n: int, k: int, splits: int):
     trace.zero_()
     l.t5x_gemm_set_trace(trace.data_ptr())
     try:
-      if splits > 1:
+      if splits == 0:
+        native.gemm_skinny(a, w)
+      elif splits > 1:
         native.gemm_splitk(a, w, splits, workspace=ws, workspace_is_clear=True)
       else:
         native.gemm(a, w)
@@ -389,7 +403,8 @@ def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("what", choices=["gemm", "attention", "gemm-one", "attention-one", "streaming", "skinny",
                                    "gemm-trace"])
-  ap.add_argument("--splits", type=int, default=4)
+  ap.add_argument("--splits", type=int, default=4,
+                  help="gemm-trace: K slices of the atomic split-K path; 1: plain; 0: the cluster kernel")
   ap.add_argument("--pair", type=int, nargs="*", default=[0, 1])
   ap.add_argument("--shape", type=int, nargs="*", default=[])
   ap.add_argument("--iters", type=int, default=3)

@@ -116,6 +116,13 @@ def peer_reduce_f32_(dst: torch.Tensor, src_ptrs, n: int) -> None:
                                                  native.stream_ptr()), "peer_reduce_f32")
 
 
+def peer_copy_bf16_(dst_ptr: int, src_ptr: int, n: int) -> None:
+  """Copies n bf16 elements between raw addresses (either may be another rank's memory as
+  mapped here; plain loads and stores)."""
+  native._check(native.lib().t5x_peer_push_bf16(_ptr_array([dst_ptr]), c_void_p(int(src_ptr)), 1,
+                                                -1, n, native.stream_ptr()), "peer_copy_bf16")
+
+
 def peer_push_bf16_(dst_ptrs, src: torch.Tensor, n: int, skip_rank: int = -1) -> None:
   """Stores src[:n] (bf16) to every rank's array at `dst_ptrs` except `skip_rank`."""
   native._check(native.lib().t5x_peer_push_bf16(dst_ptrs, src.data_ptr(), len(dst_ptrs),

@@ -340,6 +340,50 @@ def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, *,
   return out
 
 
+def gemm_skinny_splits(M: int, N: int, K: int) -> int:
+  """Cluster size `gemm_skinny` would use for this shape; 0 when it does not cover it."""
+  l = lib()
+  l.t5x_gemm_skinny_splits.argtypes = [c_int, c_int, c_int]
+  return int(l.t5x_gemm_skinny_splits(M, N, K))
+
+
+def gemm_skinny(a: torch.Tensor, b: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, splits: Optional[int] = None,
+                alpha: float = 1.0) -> Optional[torch.Tensor]:
+  """out[M, N] (bf16) = alpha * a[M, K] @ b[K, N] (+ residual) for few rows: K is cut over the
+  CTAs of a thread-block cluster, which add their partial products through distributed shared
+  memory and store finished bf16 rows (no workspace, no second kernel). `b` may be row-major
+  [K, N] or a transposed view of a row-major [N, K] matrix. Returns None when the shape is not
+  covered (N % 128, K % 64, more tiles than SMs); callers then use `gemm` / `gemm_splitk`."""
+  M, K = a.shape
+  N = b.shape[1]
+  if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.stride(1) != 1 or M == 0:
+    return None
+  if b.stride(1) == 1:
+    b_mn, ldb = 1, b.stride(0)
+  elif b.stride(0) == 1:
+    b_mn, ldb = 0, b.stride(1)
+  else:
+    return None
+  s = gemm_skinny_splits(M, N, K) if splits is None else int(splits)
+  if s <= 0 or a.stride(0) % 8 or ldb % 8 or (a.data_ptr() | b.data_ptr()) & 15:
+    return None
+  if residual is not None and (residual.stride(1) != 1 or residual.stride(0) % 4 or
+                               residual.dtype != torch.bfloat16):
+    return None
+  if out is None:
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+  assert out.stride(1) == 1 and out.stride(0) % 4 == 0 and out.dtype == torch.bfloat16
+  l = lib()
+  l.t5x_gemm_skinny_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                     c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_float, c_void_p]
+  _check(l.t5x_gemm_skinny_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), ptr(residual), M, N, K,
+                                a.stride(0), ldb, out.stride(0),
+                                residual.stride(0) if residual is not None else 0, b_mn, s,
+                                float(alpha), stream_ptr()), "gemm_skinny")
+  return out
+
+
 def gemm_splitk_norm(a: torch.Tensor, b: torch.Tensor, splits: int, *, residual: torch.Tensor,
                      scale: torch.Tensor, eps: float, workspace: torch.Tensor):
   """(x, h): x = a @ b + residual (bf16), h = rmsnorm(x) * scale, with K cut into `splits`

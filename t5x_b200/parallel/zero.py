@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import logging
 import os
+import re
 from typing import Dict, List, Mapping, Optional
 
 import numpy as np
@@ -33,14 +34,23 @@ import torch.distributed as dist
 from t5x_b200.parallel import state as pstate
 
 _ALIGN = 128  # elements; keeps every parameter's offset 256-byte aligned in both buffers
+_LAYER_RE = re.compile(r"(.*\.)?layers_\d+")  # the transformer layers of a stack
 
 
 class ZeroInfo:
-  """Per-parameter record: where it lives in the symmetric buffers and who updates it."""
-  __slots__ = ("ctx", "offset", "numel", "owner")
+  """Per-parameter record: where it lives in the symmetric buffers and who updates it.
 
-  def __init__(self, ctx, offset: int, numel: int, owner: int):
+  `offset` locates the fp32 gradient (every rank holds a full copy). `w_offset` locates the
+  bf16 working weights: for a replicated parameter the same place on every rank; for a
+  `streamed` one (weights sharded over the data axis) the place in the OWNER's buffer, the only
+  copy that persists between uses."""
+  __slots__ = ("ctx", "offset", "numel", "owner", "w_offset", "streamed")
+
+  def __init__(self, ctx, offset: int, numel: int, owner: int, w_offset: Optional[int] = None,
+               streamed: bool = False):
     self.ctx, self.offset, self.numel, self.owner = ctx, offset, numel, owner
+    self.w_offset = offset if w_offset is None else w_offset
+    self.streamed = streamed
 
   @property
   def mine(self) -> bool:
@@ -50,14 +60,31 @@ class ZeroInfo:
     return self.ctx.grads.ptrs_at(self.offset)
 
   def bf16_ptrs(self):
-    return self.ctx.weights.ptrs_at(self.offset)
+    """Where the owner's update kernel stores the new bf16 weights: every replica's working
+    copy, or the owner's own shard only when the weights are sharded."""
+    if self.streamed:
+      from t5x_b200.ops import comm
+      return comm._ptr_array([self.owner_weight_ptr()])
+    return self.ctx.weights.ptrs_at(self.w_offset)
+
+  def owner_weight_ptr(self) -> int:
+    w = self.ctx.weights
+    return w.peer_ptrs[self.owner] + self.w_offset * w.itemsize
+
+  def push_skip_rank(self) -> int:
+    """`skip_rank` for a separate push of the owner's `p.bf16`: its own replica when weights
+    are replicated; none when they are sharded (`p.bf16` is then a transient gather slot and
+    the single destination is the owner's shard)."""
+    return -1 if self.streamed else self.ctx.rank
 
   def grad_mc(self) -> int:
     """Multicast address of this parameter's gradient over all replicas (0 without NVLS)."""
     return self.ctx.grads.mc_ptr_at(self.offset) if self.ctx.nvls else 0
 
   def bf16_mc(self) -> int:
-    return self.ctx.weights.mc_ptr_at(self.offset) if self.ctx.nvls else 0
+    if self.streamed:
+      return 0
+    return self.ctx.weights.mc_ptr_at(self.w_offset) if self.ctx.nvls else 0
 
 
 # Parameters below this size stay replicated: their gradients are all-reduced (coalesced into
@@ -89,7 +116,8 @@ def assign_owners(sizes: Mapping[str, int], world: int) -> Dict[str, int]:
 class ZeroContext:
   """Symmetric gradient / weight buffers for a flat {name: fp32 parameter} mapping."""
 
-  def __init__(self, params_flat: Mapping[str, torch.Tensor], group=None):
+  def __init__(self, params_flat: Mapping[str, torch.Tensor], group=None,
+               module: Optional[torch.nn.Module] = None, shard_weights: bool = False):
     from t5x_b200.ops import comm
     st = pstate.get()
     self.group = group if group is not None else (st.data_group or dist.group.WORLD)
@@ -97,25 +125,81 @@ class ZeroContext:
     self.world = dist.get_world_size(self.group)
     names = [k for k, p in params_flat.items() if owned_by_one_rank(p)]
     sizes = {k: int(params_flat[k].numel()) for k in names}
+    padded = {k: -(-sizes[k] // _ALIGN) * _ALIGN for k in names}
     self.owners = assign_owners(sizes, self.world)
+    device = params_flat[names[0]].device
+    # Weights sharded over the data axis: the parameters of the transformer layers keep their
+    # bf16 working copy on the owner only; everything else (embedding, output projection)
+    # stays replicated. `layer_names[j]` lists the streamed parameters of the j-th layer in
+    # execution order.
+    self.layer_names: List[List[str]] = []
+    self._layer_modules: List[torch.nn.Module] = []
+    if shard_weights and module is not None:
+      by_id = {id(params_flat[k]): k for k in names}
+      for mod_name, mod in module.named_modules():
+        if _LAYER_RE.fullmatch(mod_name):
+          ks = [by_id[id(q)] for q in mod.parameters(recurse=True) if id(q) in by_id]
+          if ks:
+            self.layer_names.append(ks)
+            self._layer_modules.append(mod)
+    streamed = {k: j for j, ks in enumerate(self.layer_names) for k in ks}
+    self.shard_weights = bool(streamed)
+    # gradients: a full fp32 copy on every rank, same layout everywhere
     offset = 0
+    g_off = {}
+    for k in names:
+      g_off[k] = offset
+      offset += padded[k]
+    self.total = max(offset, _ALIGN)
+    # weights: the replicated ones first (same place on every rank), then each rank's own
+    # streamed parameters; the region is as large as the fullest rank needs
+    w_off, w_cursor = {}, 0
+    for k in names:
+      if k not in streamed:
+        w_off[k] = w_cursor
+        w_cursor += padded[k]
+    own_cursor = [w_cursor] * self.world
+    for k in names:
+      if k in streamed:
+        r = self.owners[k]
+        w_off[k] = own_cursor[r]
+        own_cursor[r] += padded[k]
+    self.weights_total = max(max(own_cursor), _ALIGN)
     self.infos: Dict[str, ZeroInfo] = {}
     for k in names:
-      self.infos[k] = ZeroInfo(self, offset, sizes[k], self.owners[k])
-      offset += -(-sizes[k] // _ALIGN) * _ALIGN
-    self.total = max(offset, _ALIGN)
-    device = params_flat[names[0]].device
+      self.infos[k] = ZeroInfo(self, g_off[k], sizes[k], self.owners[k], w_off[k], k in streamed)
     self.grads = comm.SymmetricBuffer(self.total, torch.float32, self.group, device)
-    self.weights = comm.SymmetricBuffer(self.total, torch.bfloat16, self.group, device)
+    self.weights = comm.SymmetricBuffer(self.weights_total, torch.bfloat16, self.group, device)
+    # two gather slots, each as large as the largest layer: layer j is gathered into slot j % 2
+    self._slots: List[torch.Tensor] = []
+    self._slot_off: Dict[str, int] = {}
+    if self.shard_weights:
+      most = 0
+      for ks in self.layer_names:
+        cursor = 0
+        for k in ks:
+          self._slot_off[k] = cursor
+          cursor += padded[k]
+        most = max(most, cursor)
+      self._slots = [torch.empty(most, dtype=torch.bfloat16, device=device) for _ in range(2)]
     for k in names:
       p, info = params_flat[k], self.infos[k]
       g = self.grads.tensor[info.offset:info.offset + info.numel].view(p.shape)
-      w = self.weights.tensor[info.offset:info.offset + info.numel].view(p.shape)
       old = getattr(p, "bf16", None)
-      w.copy_(old if old is not None else p.detach())
+      src = old if old is not None else p.detach()
+      if info.streamed:
+        if info.mine:  # the persistent copy
+          self.weights.tensor[info.w_offset:info.w_offset + info.numel].view(p.shape).copy_(src)
+        so = self._slot_off[k]
+        w = self._slots[streamed[k] % 2][so:so + info.numel].view(p.shape)
+      else:
+        w = self.weights.tensor[info.w_offset:info.w_offset + info.numel].view(p.shape)
+        w.copy_(src)
       g.zero_()
       p.bf16, p.main_grad, p.grad_ready, p.zero = w, g, False, info
     self.params = {k: params_flat[k] for k in names}
+    if self.shard_weights:
+      self._attach_weight_streaming()
     self._masters_released = False
     if os.environ.get("T5X_B200_ZERO_SHARD_MASTERS", "1") != "0":
       self.release_replica_masters()
@@ -124,9 +208,84 @@ class ZeroContext:
     owned = sum(sizes[k] for k in names if self.owners[k] == self.rank)
     # in-switch gradient sum / multicast weight push (T5X_B200_NVLS=1 and a fabric that has it)
     self.nvls = bool(self.grads.multicast_ptr and self.weights.multicast_ptr)
-    logging.info("optimizer sharding: rank %d/%d owns %.1f M of %.1f M parameters%s", self.rank,
+    logging.info("optimizer sharding: rank %d/%d owns %.1f M of %.1f M parameters%s%s", self.rank,
                  self.world, owned / 1e6, sum(sizes.values()) / 1e6,
-                 ", exchange through NVSwitch multimem" if self.nvls else "")
+                 ", exchange through NVSwitch multimem" if self.nvls else "",
+                 (f", bf16 weights of {len(self.layer_names)} layers sharded "
+                  f"({self.weights_total / 1e6:.1f} M resident + 2 slots of "
+                  f"{self._slots[0].numel() / 1e6:.1f} M)") if self.shard_weights else "")
+
+  # -- weights sharded over the data axis -----------------------------------------------------
+  # The forward and backward pass of layer j read its weights from gather slot j % 2. Before
+  # the layer runs (module pre-hooks), a side stream copies each of its parameters from the
+  # owner's shard (peer loads over NVLink, or a local copy on the owner) into the slot, and the
+  # layer after it (before it, in the backward pass) is requested at once into the other slot,
+  # so that the copy runs under the current layer's kernels. A gather first waits for
+  # everything enqueued on the compute stream so far: that covers the previous user of the
+  # slot and, at the start of a step, the barrier after the owners' updates. Slots are
+  # invalidated whenever the owners have written new weights.
+  def _attach_weight_streaming(self) -> None:
+    self._gather_stream = torch.cuda.Stream(device=self.grads.tensor.device)
+    self._slot_holds: List[Optional[int]] = [None, None]
+    self._slot_ready: List[Optional[torch.cuda.Event]] = [None, None]
+    n = len(self._layer_modules)
+    self._stream_hooks = []
+    for j, mod in enumerate(self._layer_modules):
+      self._stream_hooks.append(mod.register_forward_pre_hook(
+          lambda m, args, j=j: self._layer_begins(j, j + 1 if j + 1 < n else None)))
+      self._stream_hooks.append(mod.register_full_backward_pre_hook(
+          lambda m, gout, j=j: self._layer_begins(j, j - 1 if j > 0 else None)))
+
+  def detach_weight_streaming(self) -> None:
+    """Removes the gather hooks and gives every streamed parameter a full private bf16 copy
+    again (taken from the owners), so that the module keeps working without this context."""
+    if not self.shard_weights:
+      return
+    for h in self._stream_hooks:
+      h.remove()
+    self._stream_hooks = []
+    from t5x_b200.ops import comm
+    torch.cuda.current_stream().wait_stream(self._gather_stream)
+    for ks in self.layer_names:
+      for k in ks:
+        p, info = self.params[k], self.infos[k]
+        full = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
+        comm.peer_copy_bf16_(full.data_ptr(), info.owner_weight_ptr(), info.numel)
+        p.bf16 = full
+    self.shard_weights = False
+    torch.cuda.synchronize()
+    dist.barrier(group=self.group)  # nobody frees its shard while a peer still copies from it
+
+  def _gather(self, j: int) -> None:
+    from t5x_b200.ops import comm
+    slot = j % 2
+    if self._slot_holds[slot] == j:
+      return
+    main = torch.cuda.current_stream()
+    fence = torch.cuda.Event()
+    fence.record(main)
+    with torch.cuda.stream(self._gather_stream):
+      self._gather_stream.wait_event(fence)
+      buf = self._slots[slot]
+      for k in self.layer_names[j]:
+        info = self.infos[k]
+        dst = buf.data_ptr() + self._slot_off[k] * buf.element_size()
+        comm.peer_copy_bf16_(dst, info.owner_weight_ptr(), info.numel)
+      ready = torch.cuda.Event()
+      ready.record(self._gather_stream)
+    self._slot_holds[slot] = j
+    self._slot_ready[slot] = ready
+
+  def _layer_begins(self, j: int, then: Optional[int]) -> None:
+    self._gather(j)
+    torch.cuda.current_stream().wait_event(self._slot_ready[j % 2])
+    if then is not None:
+      self._gather(then)
+
+  def weights_changed(self) -> None:
+    """The owners have stored new weights: what the gather slots hold is stale."""
+    if self.shard_weights:
+      self._slot_holds = [None, None]
 
   # -- overlap with backward ----------------------------------------------------------------
   # During the last microbatch of a step, the parameters of a transformer layer are final as
@@ -249,6 +408,7 @@ class ZeroContext:
     """Barrier after the update: all weight pushes have landed and no rank still reads
     another's gradients."""
     self.grads.barrier(channel=1)
+    self.weights_changed()
 
   # -- fp32 masters live on their owner only ------------------------------------------------
   # Forward and backward read the bf16 working copies and write the gradient buffers; the fp32
@@ -410,17 +570,23 @@ def active() -> Optional[ZeroContext]:
   return _ACTIVE
 
 
-def enable(params_flat: Mapping[str, torch.Tensor], group=None) -> Optional[ZeroContext]:
-  """Shards the optimizer over the data axis if it has more than one replica on GPUs."""
+def enable(params_flat: Mapping[str, torch.Tensor], group=None,
+           module: Optional[torch.nn.Module] = None,
+           shard_weights: bool = False) -> Optional[ZeroContext]:
+  """Shards the optimizer over the data axis if it has more than one replica on GPUs. With
+  `shard_weights` (and the model's `module`, whose `layers_N` sub-modules delimit the units of
+  gathering) the bf16 working weights of the transformer layers are sharded as well."""
   global _ACTIVE
   st = pstate.get()
   if not dist.is_initialized() or st.data_size <= 1 or st.device.type != "cuda":
     return None
-  _ACTIVE = ZeroContext(params_flat, group)
+  _ACTIVE = ZeroContext(params_flat, group, module=module, shard_weights=shard_weights)
   return _ACTIVE
 
 
 def disable() -> None:
   global _ACTIVE, _LOCAL
+  if _ACTIVE is not None and getattr(_ACTIVE, "shard_weights", False):
+    _ACTIVE.detach_weight_streaming()
   _ACTIVE = None
   _LOCAL = None

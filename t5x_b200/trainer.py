@@ -688,7 +688,9 @@ class Trainer(BaseTrainer):
   def _maybe_shard_optimizer(self, train_state, weight_metrics_computer) -> None:
     """Shards the optimizer over the data axis (see `t5x_b200.parallel.zero`) when there is
     more than one replica on GPUs and nothing needs the fully reduced gradient on every rank
-    (weight metrics). Covered optimizers: Adafactor (with or without global-norm clipping) and
+    (weight metrics). A partitioner whose rules put a parameter axis on 'data', or
+    `T5X_B200_ZERO_SHARD_WEIGHTS=1`, shards the bf16 working weights of the transformer layers
+    too: each layer's weights are gathered from their owners just before the layer runs. Covered optimizers: Adafactor (with or without global-norm clipping) and
     the optax-style Adam / AdamW chains that the fused kernel handles
     (`OptaxWrapper.fused_plan`). The per-layer overlap with the backward pass is attached for
     Adafactor without clipping only: a clip factor needs every gradient first.
@@ -720,7 +722,13 @@ class Trainer(BaseTrainer):
       return
     if not asked and os.environ.get("T5X_B200_OPTIMIZER_SHARDING", "1") == "0":
       return
-    ctx = zero.enable(tree_utils.flatten_dict(train_state.params), st.data_group)
+    # bf16 working weights sharded as well (the reference's parameter_partitioning_dims=2 shards
+    # the parameters themselves): when the partitioner's rules ask for it or the environment
+    # does; not combined with a model axis, whose fused kernels lay the weights out themselves
+    shard_weights = (asked or os.environ.get("T5X_B200_ZERO_SHARD_WEIGHTS", "0") == "1") and \
+        st.model_size == 1 and getattr(self._model, "module", None) is not None
+    ctx = zero.enable(tree_utils.flatten_dict(train_state.params), st.data_group,
+                      module=getattr(self._model, "module", None), shard_weights=shard_weights)
     if ctx is not None and can_overlap:
       slots = tree_utils.flatten_dict(train_state.param_states, is_leaf=adafactor._is_state_leaf)
       ctx.attach_overlap(self._model.module, opt_def, lambda name: slots[name])

@@ -107,9 +107,14 @@ def case_train(out):
   trainer.sync_replicas()
   native.check_status()
   torch.cuda.synchronize()
+  ctx = zero.active()
+  weights_sharded = bool(getattr(ctx, "shard_weights", False))
+  weight_elems = (int(getattr(ctx, "weights_total", 0)), int(getattr(ctx, "total", 0)))
+  overlapped = len(getattr(ctx, "done_this_step", ()))
+  if weights_sharded:
+    zero.disable()  # every rank gets full bf16 copies back from the owners
   flat = torch.cat([p.detach().float().reshape(-1) for p in module.parameters()])
   bf = torch.cat([p.bf16.float().reshape(-1) for p in module.parameters()])
-  ctx = zero.active()
   from t5x_b200.utils import tree as tree_utils
   slots = [v.double().abs().sum() for v in
            tree_utils.flatten_dict(trainer.train_state.param_states).values()
@@ -117,7 +122,8 @@ def case_train(out):
   json.dump({"loss": float(summary["loss"].value), "sharded": ctx is not None,
              "slot_abs": float(torch.stack(slots).sum()),
              "nvls": bool(getattr(ctx, "nvls", False)),
-             "overlapped": len(getattr(ctx, "done_this_step", ())),
+             "overlapped": overlapped, "weights_sharded": weights_sharded,
+             "weight_elems": weight_elems,
              "param_sum": float(flat.double().sum()), "param_abs": float(flat.double().abs().sum()),
              "bf16_abs": float(bf.double().abs().sum()),
              "first": flat[:8].tolist()}, out)

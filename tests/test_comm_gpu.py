@@ -73,6 +73,27 @@ def test_sharded_optimizer_matches_all_reduce(tmp_path):
     assert x == pytest.approx(y, rel=1e-2, abs=1e-4)
 
 
+def test_sharded_weights_match_replicated_weights(tmp_path):
+  """bf16 working weights of the transformer layers kept on their owners only and gathered
+  layer by layer (T5X_B200_ZERO_SHARD_WEIGHTS=1) train exactly like replicated weights: the
+  same kernels see the same operands."""
+  _need_two()
+  sharded = _run_ranks("train", tmp_path / "w", env={"T5X_B200_ZERO_SHARD_WEIGHTS": "1"})
+  plain = _run_ranks("train", tmp_path / "p")
+  assert all(r["weights_sharded"] for r in sharded) and not any(r["weights_sharded"] for r in plain)
+  # the persistent weight buffer shrinks: replicated part + this rank's share of the layers
+  assert sharded[0]["weight_elems"][0] < 0.8 * sharded[0]["weight_elems"][1]
+  assert plain[0]["weight_elems"][0] == plain[0]["weight_elems"][1]
+  assert sharded[0]["overlapped"] > 0
+  for a, b in zip(sharded, plain):
+    assert a["loss"] == pytest.approx(b["loss"], rel=1e-5)
+    assert a["param_abs"] == pytest.approx(b["param_abs"], rel=1e-6)
+    assert a["bf16_abs"] == pytest.approx(b["bf16_abs"], rel=1e-6)
+    assert a["slot_abs"] == pytest.approx(b["slot_abs"], rel=1e-5)
+    for x, y in zip(a["first"], b["first"]):
+      assert x == pytest.approx(y, rel=1e-4, abs=1e-6)
+
+
 @pytest.mark.parametrize("kind", ["adamw_clip", "adafactor_clip"])
 def test_sharded_adamw_and_global_norm_clip_match_all_reduce(tmp_path, kind):
   """Optimizers whose update needs the norm of the whole gradient: owners reduce first, the

@@ -114,6 +114,47 @@ def test_gemm_splitk(shape):
   assert (second.float() - (ref + r.float())).abs().max() / scale < 2e-2
 
 
+@pytest.mark.parametrize("m,k,n,splits,transposed,with_res", [
+    (256, 2048, 2048, None, False, True), (256, 5120, 2048, None, False, True),
+    (64, 512, 1024, 8, False, False), (200, 1024, 256, 4, False, True),
+    (256, 2048, 2048, 1, False, True), (128, 256, 128, 2, True, True),
+    (37, 128, 384, 2, True, False), (256, 2048, 2048, 2, False, False)])
+def test_gemm_skinny_cluster_split_k(m, k, n, splits, transposed, with_res):
+  """The cluster split-K GEMM (partial products added through distributed shared memory)
+  against an fp32 matmul, for every cluster size, both weight layouts and a row tail."""
+  from t5x_b200.ops import native
+  torch.manual_seed(m + k + n)
+  a = torch.randn(m, k, device="cuda").bfloat16()
+  if transposed:
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16().t()
+  else:
+    w = (torch.randn(k, n, device="cuda") * 0.05).bfloat16()
+  res = torch.randn(m, n, device="cuda").bfloat16() if with_res else None
+  if splits is None:
+    assert native.gemm_skinny_splits(m, n, k) in (2, 4, 8)
+  out = native.gemm_skinny(a, w, residual=res, splits=splits)
+  assert out is not None
+  native.check_status()
+  ref = a.float() @ w.float()
+  if res is not None:
+    ref = ref + res.float()
+  err = (out.float() - ref).abs().max() / ref.abs().max()
+  assert err < 8e-3, err
+  # twice in a row over the same buffers: nothing is left behind between launches
+  out2 = native.gemm_skinny(a, w, residual=res, splits=splits)
+  assert torch.equal(out, out2)
+
+
+def test_gemm_skinny_declines_shapes_it_does_not_cover():
+  from t5x_b200.ops import native
+  assert native.gemm_skinny_splits(256, 2000, 2048) == 0     # N % 128
+  assert native.gemm_skinny_splits(256, 2048, 2000) == 0     # K % 64
+  assert native.gemm_skinny_splits(4096, 32128 // 128 * 128, 2048) == 0  # more tiles than SMs
+  a = torch.randn(16, 100, device="cuda").bfloat16()
+  w = torch.randn(100, 128, device="cuda").bfloat16()
+  assert native.gemm_skinny(a, w) is None
+
+
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_graph_beam_decoder_matches_reference_beam_search(use_graph):
   from t5x_b200 import decoding_fast
