@@ -331,6 +331,12 @@ def measure_train(args, parallelism: str, steps: int, warmup: int, with_e2e: boo
            "d2h_bytes_per_step": d2h_bytes}
   trainer.close()
   peak_gb = torch.cuda.max_memory_allocated() / 2 ** 30
+  # memory held on the device at the end of the run, symmetric (peer-mapped) buffers included,
+  # which the caching allocator's statistics do not see
+  free_b, total_b = torch.cuda.mem_get_info()
+  device_used_gb = (total_b - free_b) / 2 ** 30
+  weights_sharded = os.environ.get("T5X_B200_ZERO_SHARD_WEIGHTS", "0") == "1" and world > 1 and \
+      parallelism != "tp" and not moe
   host_iter.close() if hasattr(host_iter, "close") else None
   del trainer, state, model, module, resident, futures
   _teardown()
@@ -342,7 +348,8 @@ def measure_train(args, parallelism: str, steps: int, warmup: int, with_e2e: boo
         " (all-gather / reduce-scatter inside the GEMM kernels, row-sharded residual stream)"
         if world > 1 else "")
   else:
-    layout = f"data{world} x model1" + (", optimizer sharded over data" if world > 1 else "")
+    layout = f"data{world} x model1" + (", optimizer sharded over data" if world > 1 else "") + (
+        ", bf16 layer weights sharded over data" if weights_sharded else "")
   return {
       "metric": ("Switch-Base-8 train tokens/s" if moe else
                  f"T5.1.1-{args.model.upper()} train tokens/s"),
@@ -364,7 +371,7 @@ def measure_train(args, parallelism: str, steps: int, warmup: int, with_e2e: boo
                  "baseline_note": "vs_baseline divides by the reference's published A100 figure "
                                   "scaled per GPU (1346 seq/s * 640 tok / 512 GPUs = 1682.5 tok/s/GPU)"},
       "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": last_loss,
-      "peak_memory_gb": peak_gb,
+      "peak_memory_gb": peak_gb, "device_memory_used_gb": device_used_gb,
   }
 
 
