@@ -65,25 +65,54 @@ class WeightMetricsComputer:
   def _rms(x):
     return torch.sqrt(torch.mean(x.float() ** 2))
 
+  @staticmethod
+  def holds(p) -> bool:
+    """Whether this rank contributes parameter `p` to the metrics. With the optimizer sharded
+    over the data axis, the reduced gradient, the fp32 weights and hence the update of a
+    parameter exist on its owner only; replicated parameters are counted by data rank 0."""
+    z = getattr(p, "zero", None)
+    if z is not None:
+      return z.mine
+    from t5x_b200.parallel import zero
+    return zero.active() is None or pstate.get().data_rank == 0
+
   def compute_metrics(self, gradients, old_params, new_train_state) -> MutableMapping[str, Any]:
+    """`old_params` needs entries only for the parameters this rank `holds`."""
     flat_g = tree_utils.flatten_dict(gradients)
     flat_old = tree_utils.flatten_dict(old_params)
     flat_new = tree_utils.flatten_dict(new_train_state.params)
+    names = list(flat_g)
+    first = next(iter(flat_new.values()))
+    # per parameter: sum g^2, sum w^2, sum (w - w_old)^2, max |w|
+    stats = torch.zeros(len(names), 4, dtype=torch.float32, device=first.device)
+    for i, k in enumerate(names):
+      new = flat_new[k].detach()
+      if not self.holds(flat_new[k]):
+        continue
+      upd = new.float() - flat_old[k].float()
+      stats[i, 0] = (flat_g[k].float() ** 2).sum()
+      stats[i, 1] = (new.float() ** 2).sum()
+      stats[i, 2] = (upd ** 2).sum()
+      stats[i, 3] = new.abs().max()
+    from t5x_b200.parallel import zero
+    if zero.active() is not None:
+      st = pstate.get()
+      sums, tops = stats[:, :3].contiguous(), stats[:, 3].contiguous()
+      dist.all_reduce(sums, group=st.data_group)
+      dist.all_reduce(tops, op=dist.ReduceOp.MAX, group=st.data_group)
+      stats = torch.cat([sums, tops[:, None]], dim=1)
     out = {}
-    gsq = psq = usq = 0.0
-    for k, g in flat_g.items():
-      new, old = flat_new[k].detach(), flat_old[k]
-      upd = new.float() - old.float()
-      out[f"weight_rms/{k}"] = metrics_lib.AveragePerStep.from_model_output(self._rms(new))
-      out[f"weight_gradient_rms/{k}"] = metrics_lib.AveragePerStep.from_model_output(self._rms(g))
-      out[f"weight_update_rms/{k}"] = metrics_lib.AveragePerStep.from_model_output(self._rms(upd))
-      out[f"weight_max/{k}"] = metrics_lib.AveragePerStep.from_model_output(new.abs().max())
-      gsq = gsq + (g.float() ** 2).sum()
-      psq = psq + (new.float() ** 2).sum()
-      usq = usq + (upd ** 2).sum()
-    out["weight_gradient_norm"] = metrics_lib.AveragePerStep.from_model_output(torch.sqrt(gsq))
-    out["weight_norm"] = metrics_lib.AveragePerStep.from_model_output(torch.sqrt(psq))
-    out["weight_update_norm"] = metrics_lib.AveragePerStep.from_model_output(torch.sqrt(usq))
+    for i, k in enumerate(names):
+      n = float(max(flat_new[k].numel(), 1))
+      avg = metrics_lib.AveragePerStep.from_model_output
+      out[f"weight_rms/{k}"] = avg(torch.sqrt(stats[i, 1] / n))
+      out[f"weight_gradient_rms/{k}"] = avg(torch.sqrt(stats[i, 0] / n))
+      out[f"weight_update_rms/{k}"] = avg(torch.sqrt(stats[i, 2] / n))
+      out[f"weight_max/{k}"] = avg(stats[i, 3])
+    total = stats[:, :3].sum(dim=0)
+    out["weight_gradient_norm"] = metrics_lib.AveragePerStep.from_model_output(torch.sqrt(total[0]))
+    out["weight_norm"] = metrics_lib.AveragePerStep.from_model_output(torch.sqrt(total[1]))
+    out["weight_update_norm"] = metrics_lib.AveragePerStep.from_model_output(torch.sqrt(total[2]))
     return out
 
 
@@ -415,7 +444,8 @@ def apply_grads(train_state, grad_accum, metrics: MetricMapType, learning_rate,
   old_params = None
   if weight_metrics_computer is not None:
     old_params = {k: v.detach().clone()
-                  for k, v in tree_utils.flatten_dict(train_state.params).items()}
+                  for k, v in tree_utils.flatten_dict(train_state.params).items()
+                  if weight_metrics_computer.holds(v)}
   with torch.no_grad():
     new_train_state = train_state.apply_gradient(grad_accum, learning_rate=learning_rate,
                                                  **(other_state_variables or {}))
@@ -687,8 +717,7 @@ class Trainer(BaseTrainer):
 
   def _maybe_shard_optimizer(self, train_state, weight_metrics_computer) -> None:
     """Shards the optimizer over the data axis (see `t5x_b200.parallel.zero`) when there is
-    more than one replica on GPUs and nothing needs the fully reduced gradient on every rank
-    (weight metrics). A partitioner whose rules put a parameter axis on 'data', or
+    more than one replica on GPUs (weight metrics are then gathered from the owners). A partitioner whose rules put a parameter axis on 'data', or
     `T5X_B200_ZERO_SHARD_WEIGHTS=1`, shards the bf16 working weights of the transformer layers
     too: each layer's weights are gathered from their owners just before the layer runs. Covered optimizers: Adafactor (with or without global-norm clipping) and
     the optax-style Adam / AdamW chains that the fused kernel handles
@@ -703,11 +732,12 @@ class Trainer(BaseTrainer):
     is_adafactor = isinstance(opt_def, adafactor.Adafactor)
     is_fused_adam = isinstance(opt_def, optimizers.OptaxWrapper) and \
         opt_def.fused_plan is not None
-    if (self._device.type != "cuda" or weight_metrics_computer is not None or
-        not (is_adafactor or is_fused_adam)):
+    if self._device.type != "cuda" or not (is_adafactor or is_fused_adam):
       return
+    # weight metrics compare the weights before and after the update: the updates then all run
+    # after the backward pass (no overlap), and each rank reports the parameters it owns
     can_overlap = is_adafactor and not opt_def.hyper_params.global_norm_clip_threshold and \
-        getattr(self._model, "module", None) is not None and \
+        getattr(self._model, "module", None) is not None and weight_metrics_computer is None and \
         os.environ.get("T5X_B200_OVERLAP_GRAD_EXCHANGE", "1") != "0"
     if st.world_size == 1:
       if can_overlap:

@@ -78,7 +78,9 @@ def _tiny_trainer(n_micro=2):
   state = ts_lib.FlaxOptimTrainState.create(opt, model.get_initial_variables(None, None))
   lr_fn = schedules.create_learning_rate_scheduler("constant",
                                                    1e-3 if kind == "adamw_clip" else 0.01, 0)
-  return trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, n_micro), module
+  wmc = trainer_lib.WeightMetricsComputer() if os.environ.get("T5X_TEST_WEIGHT_METRICS") else None
+  return trainer_lib.Trainer(model, state, None, [], None, None, 0, lr_fn, n_micro,
+                             weight_metrics_computer=wmc), module
 
 
 def _batches(rank, world, steps, per_rank=8):
@@ -119,7 +121,12 @@ def case_train(out):
   slots = [v.double().abs().sum() for v in
            tree_utils.flatten_dict(trainer.train_state.param_states).values()
            if isinstance(v, torch.Tensor) and v.is_cuda and v.numel() > 1]
+  weight_metrics = {k: float(v.value) for k, v in summary.items()
+                    if k in ("weight_norm", "weight_update_norm", "weight_gradient_norm") or
+                    k.startswith(("weight_update_rms/encoder/layers_1/mlp/wo",
+                                  "weight_max/decoder/layers_0/self_attention/query"))}
   json.dump({"loss": float(summary["loss"].value), "sharded": ctx is not None,
+             "weight_metrics": weight_metrics,
              "slot_abs": float(torch.stack(slots).sum()),
              "nvls": bool(getattr(ctx, "nvls", False)),
              "overlapped": overlapped, "weights_sharded": weights_sharded,

@@ -94,6 +94,21 @@ def test_sharded_weights_match_replicated_weights(tmp_path):
       assert x == pytest.approx(y, rel=1e-4, abs=1e-6)
 
 
+def test_weight_metrics_under_the_sharded_optimizer(tmp_path):
+  """Weight / gradient / update norms keep the optimizer sharded: each rank reports the
+  parameters it owns and the ranks add up; the figures match the all-reduce run."""
+  _need_two()
+  env = {"T5X_TEST_WEIGHT_METRICS": "1"}
+  sharded = _run_ranks("train", tmp_path / "z", env=env)
+  plain = _run_ranks("train", tmp_path / "p", env={**env, "T5X_B200_OPTIMIZER_SHARDING": "0"})
+  assert all(r["sharded"] for r in sharded) and not any(r["sharded"] for r in plain)
+  assert len(sharded[0]["weight_metrics"]) >= 5
+  for r in sharded[1:]:
+    assert r["weight_metrics"] == pytest.approx(sharded[0]["weight_metrics"], rel=1e-6)
+  for k, v in plain[0]["weight_metrics"].items():
+    assert sharded[0]["weight_metrics"][k] == pytest.approx(v, rel=2e-3), k
+
+
 @pytest.mark.parametrize("kind", ["adamw_clip", "adafactor_clip"])
 def test_sharded_adamw_and_global_norm_clip_match_all_reduce(tmp_path, kind):
   """Optimizers whose update needs the norm of the whole gradient: owners reduce first, the
