@@ -158,7 +158,8 @@ __device__ __forceinline__ void load_row_bf16(const __nv_bfloat16* src, float* v
 constexpr int kEpiStageBytesPerWarp = 32 * 128;
 
 // v: this lane's row (32 floats). out: &C[first row of the warp's block][first column], fp32.
-// mode 0: plain store, 2: atomic add. Rows >= rows_valid are skipped. All lanes must call it.
+// mode 0: plain store, 1: add to what is there (one writer per element), 2: atomic add.
+// Rows >= rows_valid are skipped. All lanes must call it.
 __device__ __forceinline__ void staged_store_f32(float* stage, const float (&v)[32], float* out,
                                                  long long ldc, int rows_valid, int lane,
                                                  int mode) {
@@ -174,10 +175,14 @@ __device__ __forceinline__ void staged_store_f32(float* stage, const float (&v)[
     const float4 o = *reinterpret_cast<const float4*>(stage + row * 32 + ((c ^ (row & 7)) * 4));
     if (row < rows_valid) {
       float4* dst = reinterpret_cast<float4*>(out + static_cast<long long>(row) * ldc + c * 4);
-      if (mode == 2)
+      if (mode == 2) {
         atomicAdd(dst, o);
-      else
+      } else if (mode == 1) {
+        const float4 old = *dst;
+        *dst = make_float4(o.x + old.x, o.y + old.y, o.z + old.z, o.w + old.w);
+      } else {
         *dst = o;
+      }
     }
   }
   __syncwarp();
@@ -285,9 +290,8 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
       const int n_valid = p.N - col;
       // whole 32-column blocks go out through the staging buffer (warp-uniform condition)
       const bool staged = stage != nullptr && n_valid >= 32 && rows_valid > 0 &&
-                          p.accumulate != 1 &&
                           (p.out_fp32 ? (p.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
-                                      : c_vec_ok);
+                                      : (c_vec_ok && p.accumulate == 0));
       if (staged) {
         float v[32];
 #pragma unroll
