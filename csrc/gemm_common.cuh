@@ -264,6 +264,29 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
       tmem_ld_wait();
       const int col = n0 + c * 32;
       const int n_valid = p.N - col;
+      const bool hv16 = p.H0 == nullptr ||
+                        ((p.ldh % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.H0) |
+                                               reinterpret_cast<uintptr_t>(p.H1)) & 15) == 0);
+      if (stage != nullptr && n_valid >= 32 && rows_valid > 0 && c_vec_ok && hv16) {
+        // whole 32-column blocks: row-contiguous stores through the staging block
+        float g[32], h0[32], h1[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          h0[i] = __uint_as_float(r0[i]);
+          h1[i] = __uint_as_float(r1[i]);
+          g[i] = gelu_tanh(h0[i]) * h1[i];
+        }
+        const long long first_row = m0 + q * 32;
+        staged_store_bf16(stage, g,
+                          reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.c_batch_stride +
+                              first_row * p.ldc + col,
+                          p.ldc, rows_valid, lane);
+        if (p.H0 != nullptr) {
+          staged_store_bf16(stage, h0, p.H0 + first_row * p.ldh + col, p.ldh, rows_valid, lane);
+          staged_store_bf16(stage, h1, p.H1 + first_row * p.ldh + col, p.ldh, rows_valid, lane);
+        }
+        continue;
+      }
       if (row_ok && n_valid > 0) {
         float g[32], h0[32], h1[32];
 #pragma unroll

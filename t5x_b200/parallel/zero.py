@@ -113,6 +113,35 @@ def assign_owners(sizes: Mapping[str, int], world: int) -> Dict[str, int]:
   return owners
 
 
+def plan_buffers(names, sizes: Mapping[str, int], owners: Mapping[str, int], streamed,
+                 world: int):
+  """Element offsets of every owned parameter in the two symmetric buffers.
+
+  Gradients: a full fp32 copy on every rank, the same layout everywhere. Weights (bf16): the
+  replicated parameters first, at the same place on every rank, then each rank's own
+  `streamed` parameters (the only persistent copy of those); the buffer is as large as the
+  fullest rank needs. Returns (grad offsets, grad elements, weight offsets, weight elements);
+  a streamed parameter's weight offset is the one in its OWNER's buffer. Every offset is a
+  multiple of `_ALIGN` elements."""
+  pad = lambda n: -(-n // _ALIGN) * _ALIGN
+  g_off, cursor = {}, 0
+  for k in names:
+    g_off[k] = cursor
+    cursor += pad(sizes[k])
+  grad_total = max(cursor, _ALIGN)
+  w_off, cursor = {}, 0
+  for k in names:
+    if k not in streamed:
+      w_off[k] = cursor
+      cursor += pad(sizes[k])
+  own = [cursor] * world
+  for k in names:
+    if k in streamed:
+      w_off[k] = own[owners[k]]
+      own[owners[k]] += pad(sizes[k])
+  return g_off, grad_total, w_off, max(max(own), _ALIGN)
+
+
 class ZeroContext:
   """Symmetric gradient / weight buffers for a flat {name: fp32 parameter} mapping."""
 
@@ -144,27 +173,8 @@ class ZeroContext:
             self._layer_modules.append(mod)
     streamed = {k: j for j, ks in enumerate(self.layer_names) for k in ks}
     self.shard_weights = bool(streamed)
-    # gradients: a full fp32 copy on every rank, same layout everywhere
-    offset = 0
-    g_off = {}
-    for k in names:
-      g_off[k] = offset
-      offset += padded[k]
-    self.total = max(offset, _ALIGN)
-    # weights: the replicated ones first (same place on every rank), then each rank's own
-    # streamed parameters; the region is as large as the fullest rank needs
-    w_off, w_cursor = {}, 0
-    for k in names:
-      if k not in streamed:
-        w_off[k] = w_cursor
-        w_cursor += padded[k]
-    own_cursor = [w_cursor] * self.world
-    for k in names:
-      if k in streamed:
-        r = self.owners[k]
-        w_off[k] = own_cursor[r]
-        own_cursor[r] += padded[k]
-    self.weights_total = max(max(own_cursor), _ALIGN)
+    g_off, self.total, w_off, self.weights_total = plan_buffers(
+        names, sizes, self.owners, set(streamed), self.world)
     self.infos: Dict[str, ZeroInfo] = {}
     for k in names:
       self.infos[k] = ZeroInfo(self, g_off[k], sizes[k], self.owners[k], w_off[k], k in streamed)

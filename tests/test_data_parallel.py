@@ -144,3 +144,35 @@ def test_optimizer_slots_are_matched_to_their_parameters():
   got = zero.state_leaves_by_param(names, optax_like)
   assert [len(got[n]) for n in names] == [2, 2]
   assert all(v.shape == (2, 3) for v in got["enc/mlp/kernel"])
+
+
+def test_buffer_plan_for_sharded_weights():
+  """Layout of the symmetric buffers: gradients replicated in full; weights replicated for the
+  resident parameters and, for the streamed ones, packed per owner without overlap."""
+  from t5x_b200.parallel import zero
+  sizes = {"emb": 65536, "l0/q": 16384, "l0/wi": 32768 + 5, "l1/q": 16384, "l1/wi": 32768,
+           "logits": 70000}
+  names = list(sizes)
+  world = 3
+  owners = zero.assign_owners(sizes, world)
+  assert sorted(set(owners.values())) == [0, 1, 2]
+  streamed = {k for k in names if k.startswith("l")}
+  g_off, g_total, w_off, w_total = zero.plan_buffers(names, sizes, owners, streamed, world)
+  pad = lambda n: -(-n // 128) * 128
+  assert g_total == sum(pad(n) for n in sizes.values())
+  assert all(off % 128 == 0 for off in list(g_off.values()) + list(w_off.values()))
+  # gradient ranges do not overlap
+  spans = sorted((g_off[k], g_off[k] + sizes[k]) for k in names)
+  assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+  # resident weights sit first and at the same place for everyone; every owner's streamed
+  # parameters follow without overlapping each other or the resident part
+  resident_end = max(w_off[k] + pad(sizes[k]) for k in names if k not in streamed)
+  for r in range(world):
+    mine = sorted((w_off[k], w_off[k] + sizes[k]) for k in streamed if owners[k] == r)
+    assert all(a[0] >= resident_end for a in mine)
+    assert all(a[1] <= b[0] for a, b in zip(mine, mine[1:]))
+    assert all(a[1] <= w_total for a in mine)
+  assert w_total < g_total  # that is the point of sharding them
+  # nothing streamed: both buffers have the same layout
+  g2, t2, w2, wt2 = zero.plan_buffers(names, sizes, owners, set(), world)
+  assert w2 == g2 and wt2 == t2
