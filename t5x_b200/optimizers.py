@@ -333,10 +333,21 @@ def scale_by_lion(b1=0.9, b2=0.99):
 
 
 def add_decayed_weights(weight_decay: float, mask=None):
+  """`mask`: None (decay everything), a tree of booleans shaped like the parameters, or a
+  callable that maps the parameter tree to such a tree; only entries that are true decay."""
+  def selected(params):
+    if mask is None:
+      return None
+    m = mask(tree_utils.unflatten_dict(dict(params))) if callable(mask) else mask
+    flat = tree_utils.flatten_dict(m) if isinstance(m, Mapping) else m
+    return {k: bool(v) for k, v in flat.items()}
+
   def update(updates, state, params=None):
     if params is None:
       raise ValueError("add_decayed_weights needs params")
-    return {k: g + weight_decay * params[k].float() for k, g in updates.items()}, state
+    keep = selected(params)
+    return {k: (g + weight_decay * params[k].float()) if keep is None or keep.get(k, False) else g
+            for k, g in updates.items()}, state
 
   return GradientTransformation(lambda p: {}, update, "add_decayed_weights",
                                 {"weight_decay": weight_decay, "mask": mask})
