@@ -241,6 +241,27 @@ def test_termination_check_period_changes_when_the_loop_ends_not_what_it_returns
   assert runs[1][1] <= runs[3][1] + 2 and runs[1][1] <= runs[8][1]
 
 
+@pytest.mark.parametrize("level", [1, 2])
+def test_chained_launches_do_not_change_the_decode(level, monkeypatch):
+  """Programmatic dependent launches (each kernel set up behind its predecessor, level 2 also
+  requesting the constant weights ahead of the wait) give bit-identical beams and scores."""
+  from t5x_b200 import decoding_fast
+  model = _model(sharp=True)
+  torch.manual_seed(4)
+  enc = torch.randint(2, 512, (3, 20), device="cuda")
+  plain = decoding_fast.GraphBeamDecoder(model.module, 3, 4, 12, eos_id=1, alpha=0.6)
+  want_seqs, want_scores = plain.decode(enc)
+  monkeypatch.setenv("T5X_B200_DECODE_CHAIN", str(level))
+  chained = decoding_fast.GraphBeamDecoder(model.module, 3, 4, 12, eos_id=1, alpha=0.6)
+  assert chained.chain_level == level
+  for _ in range(2):  # eager warm-up + capture, then replay
+    got_seqs, got_scores = chained.decode(enc)
+  from t5x_b200.ops import native
+  native.check_status()
+  assert torch.equal(got_seqs, want_seqs)
+  torch.testing.assert_close(got_scores, want_scores, rtol=0, atol=0)
+
+
 def test_predict_batch_uses_graph_decoder_by_default():
   model = _model()
   enc = torch.randint(2, 512, (2, 16), device="cuda")
