@@ -201,8 +201,8 @@ def _reshape_attn(name_path, value, heads: int, kv: int, to_3d: bool):
 
 def stack_layers(params: Mapping[str, Any], num_heads: int, head_dim: int, scan_axis: int = 1):
   """Per-layer parameter tree -> the scanned layout of the reference: `encoder/layers_i/...`
-  become `encoder/encoder/...` with a new `layers` axis at `scan_axis` (position 0 for
-  vectors that have fewer dims), attention kernels become 3-D. Works on numpy arrays or
+  become `encoder/encoder/...` with a new `layers` axis at `scan_axis` (a norm scale [embed]
+  becomes [embed, layers] for axis 1), attention kernels become 3-D. Works on numpy arrays or
   tensors (anything with reshape and stackable by torch/numpy)."""
   import numpy as np
 

@@ -234,8 +234,12 @@ def dropout(x: torch.Tensor, rate: float, training: bool, broadcast_dims=(),
   """Dropout whose mask is shared along `broadcast_dims` (flax nn.Dropout semantics)."""
   if not training or rate == 0.0:
     return x
-  if generator is None:
-    generator = _dropout_generator(x.device)
+  if generator is None and dropout_seed() is not None:
+    # one generator per call, keyed by (step seed, call number): a block that is recomputed in
+    # the backward pass (rematerialisation) restores the call counter and so draws the masks
+    # of its first pass again, as the in-kernel generator on the GPU does
+    generator = torch.Generator(device=x.device)
+    generator.manual_seed((dropout_seed() * 1000003 + next_dropout_site()) % (2 ** 63 - 1))
   shape = list(x.shape)
   for d in broadcast_dims:
     shape[d] = 1
