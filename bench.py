@@ -491,8 +491,27 @@ def main() -> None:
     named = os.environ.get("T5X_B200_BENCH_DECODE_NAMED_MESH", "1" if world > 1 else "0")
     if world > 1 and named == "1":
       phases.append(("decode_named_mesh", lambda: decode(min(4, world))))
+  # A phase that neither returns nor raises (ranks stuck in a rendezvous, say) must not cost the
+  # headline record: past the deadline every rank's watchdog ends its own process, rank 0 after
+  # printing what has been measured so far. The headline above is complete by now.
+  deadline_s = float(os.environ.get("T5X_B200_BENCH_EXTRAS_DEADLINE_S", "420"))
+  done = threading.Event()
+  current = ["(none)"]
+
+  def watchdog():
+    if done.wait(deadline_s):
+      return
+    if rank == 0:
+      out.setdefault(current[0], {"failed": f"no result within {deadline_s:.0f} s; run ended "
+                                            "by the bench's watchdog"})
+      print(json.dumps(out), flush=True)
+    os._exit(0)
+
+  if phases:
+    threading.Thread(target=watchdog, daemon=True).start()
   for name, phase in phases:
     failure = None
+    current[0] = name
     try:
       out[name] = phase()
     except Exception as e:  # pylint: disable=broad-except
@@ -507,8 +526,9 @@ def main() -> None:
       if failure is None:
         out[name + "_note"] = "a later phase was skipped: this phase failed on another rank"
       break
+  done.set()
   if rank == 0:
-    print(json.dumps(out))
+    print(json.dumps(out), flush=True)
   if world > 1:
     dist.barrier()
     dist.destroy_process_group()
