@@ -375,6 +375,23 @@ def measure_train(args, parallelism: str, steps: int, warmup: int, with_e2e: boo
   }
 
 
+class Watchdog:
+  """Calls `on_deadline` from a daemon thread unless `finish()` comes within `seconds`."""
+
+  def __init__(self, seconds: float, on_deadline):
+    self._seconds, self._on_deadline = seconds, on_deadline
+    self._done = threading.Event()
+
+  def start(self) -> None:
+    def run():
+      if not self._done.wait(self._seconds):
+        self._on_deadline()
+    threading.Thread(target=run, daemon=True).start()
+
+  def finish(self) -> None:
+    self._done.set()
+
+
 def run_selfcheck(world: int) -> dict:
   """Errors of the fused multi-GPU kernels against library collectives on this box; each
   family is checked on the mesh it serves. A family that exceeds the tolerance (or raises) is
@@ -495,20 +512,18 @@ def main() -> None:
   # headline record: past the deadline every rank's watchdog ends its own process, rank 0 after
   # printing what has been measured so far. The headline above is complete by now.
   deadline_s = float(os.environ.get("T5X_B200_BENCH_EXTRAS_DEADLINE_S", "420"))
-  done = threading.Event()
   current = ["(none)"]
 
-  def watchdog():
-    if done.wait(deadline_s):
-      return
+  def on_deadline():
     if rank == 0:
       out.setdefault(current[0], {"failed": f"no result within {deadline_s:.0f} s; run ended "
                                             "by the bench's watchdog"})
       print(json.dumps(out), flush=True)
     os._exit(0)
 
+  watchdog = Watchdog(deadline_s, on_deadline)
   if phases:
-    threading.Thread(target=watchdog, daemon=True).start()
+    watchdog.start()
   for name, phase in phases:
     failure = None
     current[0] = name
@@ -526,7 +541,7 @@ def main() -> None:
       if failure is None:
         out[name + "_note"] = "a later phase was skipped: this phase failed on another rank"
       break
-  done.set()
+  watchdog.finish()
   if rank == 0:
     print(json.dumps(out), flush=True)
   if world > 1:
