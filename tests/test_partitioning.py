@@ -132,3 +132,44 @@ def test_parameter_partitioning_over_data_is_visible_to_the_trainer():
           parameter_partitioning_dims=2))
   assert not one.partitions_parameters_over_data
   assert two.partitions_parameters_over_data
+
+
+def _mesh_worker(rank, world, port, out_dir):
+  import json
+  import os
+  import torch.distributed as dist
+  from t5x_b200.parallel import state as pstate
+  os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                    WORLD_SIZE=str(world))
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  st = pstate.setup_mesh(model_size=2)
+  import torch
+  one = torch.tensor([float(rank)])
+  model_sum, data_sum = one.clone(), one.clone()
+  dist.all_reduce(model_sum, group=st.model_group)
+  dist.all_reduce(data_sum, group=st.data_group)
+  with open(os.path.join(out_dir, f"{rank}.json"), "w") as f:
+    json.dump({"data": [st.data_size, st.data_rank], "model": [st.model_size, st.model_rank],
+               "model_ranks": dist.get_process_group_ranks(st.model_group),
+               "data_ranks": dist.get_process_group_ranks(st.data_group),
+               "model_sum": float(model_sum), "data_sum": float(data_sum)}, f)
+  dist.destroy_process_group()
+
+
+def test_four_ranks_as_data2_x_model2(tmp_path):
+  """Model groups are consecutive ranks, data groups stride over them; collectives on one
+  axis touch only that axis."""
+  import json
+  import socket
+  import torch.multiprocessing as mp
+  with socket.socket() as s:
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+  mp.spawn(_mesh_worker, args=(4, port, str(tmp_path)), nprocs=4, join=True)
+  got = [json.load(open(tmp_path / f"{r}.json")) for r in range(4)]
+  assert [g["model_ranks"] for g in got] == [[0, 1], [0, 1], [2, 3], [2, 3]]
+  assert [g["data_ranks"] for g in got] == [[0, 2], [1, 3], [0, 2], [1, 3]]
+  assert [g["data"] for g in got] == [[2, 0], [2, 0], [2, 1], [2, 1]]
+  assert [g["model"] for g in got] == [[2, 0], [2, 1], [2, 0], [2, 1]]
+  assert [g["model_sum"] for g in got] == [1.0, 1.0, 5.0, 5.0]
+  assert [g["data_sum"] for g in got] == [2.0, 4.0, 2.0, 4.0]
