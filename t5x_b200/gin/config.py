@@ -652,9 +652,12 @@ def parse_config(bindings, skip_unknown: bool = False, _filename: Optional[str] 
     if not indented:
       block_selector = None
     stmt = line.strip()
-    # gather continuation lines
-    while not _balanced(stmt) and i < len(lines):
-      stmt += "\n" + _strip_comment(lines[i])
+    # gather continuation lines: an open bracket or a trailing backslash
+    while i < len(lines) and (stmt.endswith("\\") or not _balanced(stmt)):
+      if stmt.endswith("\\"):
+        stmt = stmt[:-1].rstrip() + " " + _strip_comment(lines[i]).strip()
+      else:
+        stmt += "\n" + _strip_comment(lines[i])
       i += 1
     if stmt.startswith("import ") or stmt.startswith("from "):
       _do_import(" ".join(stmt.split()), imports, skip_unknown)
