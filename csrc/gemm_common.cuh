@@ -158,11 +158,13 @@ __device__ __forceinline__ void load_row_bf16(const __nv_bfloat16* src, float* v
 constexpr int kEpiStageBytesPerWarp = 32 * 128;
 
 // v: this lane's row (32 floats). out: &C[first row of the warp's block][first column], fp32.
-// mode 0: plain store, 1: add to what is there (one writer per element), 2: atomic add.
-// Rows >= rows_valid are skipped. All lanes must call it.
+// MODE 0: plain store, 1: add to what is there (one writer per element), 2: atomic add; a
+// template argument so that every variant is straight-line code (with the mode as a run-time
+// value the atomic variant ran almost four times slower). Rows >= rows_valid are skipped. All
+// lanes must call it.
+template <int MODE>
 __device__ __forceinline__ void staged_store_f32(float* stage, const float (&v)[32], float* out,
-                                                 long long ldc, int rows_valid, int lane,
-                                                 int mode) {
+                                                 long long ldc, int rows_valid, int lane) {
 #pragma unroll
   for (int c = 0; c < 8; ++c)
     *reinterpret_cast<float4*>(stage + lane * 32 + ((c ^ (lane & 7)) * 4)) =
@@ -175,9 +177,9 @@ __device__ __forceinline__ void staged_store_f32(float* stage, const float (&v)[
     const float4 o = *reinterpret_cast<const float4*>(stage + row * 32 + ((c ^ (row & 7)) * 4));
     if (row < rows_valid) {
       float4* dst = reinterpret_cast<float4*>(out + static_cast<long long>(row) * ldc + c * 4);
-      if (mode == 2) {
+      if (MODE == 2) {
         atomicAdd(dst, o);
-      } else if (mode == 1) {
+      } else if (MODE == 1) {
         const float4 old = *dst;
         *dst = make_float4(o.x + old.x, o.y + old.y, o.z + old.z, o.w + old.w);
       } else {
@@ -329,10 +331,15 @@ __device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, uint32_t
         }
         const long long first = b * p.c_batch_stride +
                                 static_cast<long long>(m0 + q * 32) * p.ldc + col;
-        if (p.out_fp32)
-          staged_store_f32(stage, v, reinterpret_cast<float*>(p.C) + first, p.ldc, rows_valid,
-                           lane, p.accumulate);
-        else
+        if (p.out_fp32) {
+          float* dst = reinterpret_cast<float*>(p.C) + first;
+          if (p.accumulate == 2)
+            staged_store_f32<2>(stage, v, dst, p.ldc, rows_valid, lane);
+          else if (p.accumulate == 1)
+            staged_store_f32<1>(stage, v, dst, p.ldc, rows_valid, lane);
+          else
+            staged_store_f32<0>(stage, v, dst, p.ldc, rows_valid, lane);
+        } else
           staged_store_bf16(stage, v, reinterpret_cast<__nv_bfloat16*>(p.C) + first, p.ldc,
                             rows_valid, lane);
         continue;

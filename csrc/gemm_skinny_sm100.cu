@@ -286,6 +286,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         *abort_flag = 1;
       }
       if (threadIdx.x == 64) T5X_GEMM_TRACE(6);
+      // This CTA has everything that was sent to it: it arrives at the closing cluster barrier
+      // now and waits for it only before leaving, so that the sum and the stores below do not
+      // hold the other CTAs up.
+      tc_fence_before();
+      cluster_arrive();
       if (got && acc_ok) {
         const bool c_vec = (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 7) == 0);
 #pragma unroll
@@ -322,11 +327,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
     }
+    else {
+      cluster_arrive();  // warps 0 and 1 take no part in the exchange
+    }
     // No CTA leaves while a peer may still write into its `recv`, signal its barrier or read
-    // its ring (the source of the outgoing copies): every CTA has waited for all of its
-    // incoming bytes before it arrives here, so past this barrier every copy is complete.
-    tc_fence_before();
-    cluster_sync_all();
+    // its ring (the source of the outgoing copies): every CTA arrives only after it has all of
+    // its incoming bytes, so once the barrier completes every copy is complete.
+    cluster_wait();
   } else if (warp >= 2 && acc_ok) {
     // one CTA per tile: the ordinary epilogue, rows straight from TMEM through a staging
     // block in the (free) operand ring
