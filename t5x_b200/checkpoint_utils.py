@@ -9,6 +9,7 @@ import shutil
 from typing import Any, Optional
 
 from t5x_b200.io import msgpack_io
+from t5x_b200.io import orbax_tree
 
 _PINNED_CHECKPOINT_FILENAME = "PINNED"
 _TS_KEYS = {"driver", "kvstore", "metadata"}
@@ -80,7 +81,8 @@ def detect_checkpoint_type(checkpoint_path: str,
   TensorStore specs) or a TensorFlow checkpoint (t5x/checkpoint_utils.py:101-250)."""
   found = None
   d = checkpoint_path if os.path.isdir(checkpoint_path) else os.path.dirname(checkpoint_path)
-  if _contains_ocdbt(checkpoint_path) or os.path.isdir(os.path.join(d, "state")):
+  if _contains_ocdbt(checkpoint_path) or os.path.isdir(os.path.join(d, "state")) or \
+      orbax_tree.find_state_dir(d) is not None:
     found = CheckpointTypes.ORBAX
   else:
     f = checkpoint_path if os.path.isfile(checkpoint_path) else os.path.join(d, "checkpoint")

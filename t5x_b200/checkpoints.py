@@ -37,6 +37,7 @@ from t5x_b200 import checkpoints_utils
 from t5x_b200 import partitioning
 from t5x_b200 import state_utils
 from t5x_b200.io import msgpack_io
+from t5x_b200.io import orbax_tree
 from t5x_b200.io import zarr_io
 from t5x_b200.parallel import state as pstate
 from t5x_b200.utils import tree as tree_utils
@@ -422,17 +423,30 @@ class Checkpointer:
       ckpt_path = os.path.join(ckpt_path, "checkpoint")
     else:
       ckpt_dir = os.path.dirname(ckpt_path)
-    if not os.path.exists(ckpt_path) or os.path.isdir(ckpt_path):
-      raise CheckpointReadError(f"Path is not a valid T5X checkpoint: {ckpt_path}")
-    logging.info("Restoring from checkpoint: %s", ckpt_path)
-    try:
-      with open(ckpt_path, "rb") as fp:
-        raw = fp.read()
-      ckpt_contents = msgpack_io.msgpack_restore(raw)
-      if not isinstance(ckpt_contents, Mapping) or "optimizer" not in ckpt_contents:
-        raise ValueError("no 'optimizer' entry")
-    except Exception as e:
-      raise CheckpointReadError(f"Checkpoint index {ckpt_path} is damaged: {e}") from e
+    tree_dir = orbax_tree.find_state_dir(ckpt_dir)
+    if tree_dir is not None:
+      # One zarr directory per leaf plus a placeholder / metadata file: the layout of the
+      # reference's Orbax manager (t5x/checkpoints.py:2386-2510).
+      logging.info("Restoring from PyTree checkpoint directory: %s", tree_dir)
+      try:
+        ckpt_contents = {"version": VERSION, "optimizer": _orbax_state_dict(tree_dir)}
+      except NotImplementedError:
+        raise
+      except Exception as e:
+        raise CheckpointReadError(f"Checkpoint tree {tree_dir} is damaged: {e}") from e
+      ckpt_dir = tree_dir
+    else:
+      if not os.path.exists(ckpt_path) or os.path.isdir(ckpt_path):
+        raise CheckpointReadError(f"Path is not a valid T5X checkpoint: {ckpt_path}")
+      logging.info("Restoring from checkpoint: %s", ckpt_path)
+      try:
+        with open(ckpt_path, "rb") as fp:
+          raw = fp.read()
+        ckpt_contents = msgpack_io.msgpack_restore(raw)
+        if not isinstance(ckpt_contents, Mapping) or "optimizer" not in ckpt_contents:
+          raise ValueError("no 'optimizer' entry")
+      except Exception as e:
+        raise CheckpointReadError(f"Checkpoint index {ckpt_path} is damaged: {e}") from e
     ckpt_state_dict = self._get_optimizer_state_dict(ckpt_contents, state_transformation_fns)
     written_infos = self._parameter_infos
     target_sd = self._train_state.state_dict()
@@ -467,7 +481,7 @@ class Checkpointer:
         if isinstance(e, CheckpointReadError):
           raise
         raise CheckpointReadError(
-            f"Array {'/'.join(map(str, name))} of checkpoint {ckpt_dir} cannot be read "
+            f"Array {name} of checkpoint {ckpt_dir} cannot be read "
             f"({type(e).__name__}: {e})") from e
     state_dict = tree_utils.unflatten_dict(restored)
     if self._dataset_iterator is not None and self._dataset_ckpt_name:
@@ -494,7 +508,11 @@ class Checkpointer:
       per = gshape[sdim] // st.model_size
       region = tuple(slice(st.model_rank * per, (st.model_rank + 1) * per) if i == sdim
                      else slice(None) for i in range(len(gshape)))
-    if _is_spec(ckpt_leaf):
+    if isinstance(ckpt_leaf, orbax_tree.ArrayRef):
+      def get():
+        want = _np_dtype(target.dtype) if hasattr(target, "dtype") else None
+        return ckpt_leaf.read(region, dtype=rd, expected_shape=gshape, expected_dtype=want)
+    elif _is_spec(ckpt_leaf):
       def get():
         return _read_ts(ckpt_leaf, ckpt_dir, gshape, region, rd, version, name)
     else:
@@ -571,6 +589,42 @@ def _read_ts(spec: Mapping[str, Any], ckpt_dir: str, expected_shape, region, res
   return z.read(region, dtype=restore_dtype)
 
 
+def _orbax_state_dict(tree_dir: str):
+  """Tree of a PyTree checkpoint directory as a state dict: sequences become dicts keyed
+  '0', '1', ... (the form `state_dict()` gives them) and a bare dataclass dump with an
+  `_optimizer` entry is unwrapped to its {'state', 'target'} part."""
+  def as_dicts(node):
+    if isinstance(node, Mapping):
+      return {str(k): as_dicts(v) for k, v in node.items()}
+    if isinstance(node, (list, tuple)):
+      return {str(i): as_dicts(v) for i, v in enumerate(node)}
+    return node
+  tree = as_dicts(orbax_tree.load_tree(tree_dir))
+  if "_optimizer" in tree and "target" not in tree:
+    extra = {k: v for k, v in tree.items() if k == "flax_mutables" and v}
+    tree = dict(tree["_optimizer"], **extra)
+  return tree
+
+
+def save_state_as_orbax_tree(train_state, checkpoints_dir: str, compressor=None) -> str:
+  """Writes `train_state.state_dict()` under `<checkpoints_dir>/checkpoint_<step>/state/` in
+  the one-directory-per-array PyTree layout (where the reference's Orbax manager puts its
+  state item, t5x/checkpoints.py:2336-2384). A single-process export for interchange: arrays
+  must be whole on this rank. Returns the checkpoint directory."""
+  step = int(_to_numpy(train_state.step))
+  final_dir = get_checkpoint_dir(checkpoints_dir, step)
+  tmp_dir = final_dir + f".tmp-{int(time.time())}"
+  flat = tree_utils.flatten_dict(train_state.state_dict(), keep_empty_nodes=True)
+  tree = tree_utils.unflatten_dict(
+      {k: (v if v is None or (isinstance(v, Mapping) and not v) else _to_numpy(_maybe_get(v)))
+       for k, v in flat.items()})
+  orbax_tree.save_tree(os.path.join(tmp_dir, "state"), tree, compressor)
+  if os.path.exists(final_dir):
+    checkpoint_utils.remove_checkpoint_dir(final_dir)
+  os.rename(tmp_dir, final_dir)
+  return final_dir
+
+
 def _get_optimizer_state_dict(ckpt_contents, optimizer_state, state_transformation_fns):
   """Checkpoint's optimizer dict after version checks and restore transformations
   (t5x/checkpoints.py:1637-1659)."""
@@ -614,17 +668,32 @@ def load_t5x_checkpoint(path: str, step: Optional[int] = None,
                         remap: bool = True, restore_dtype=None, lazy_parameters: bool = False):
   """Reads a whole checkpoint into a nested dict without needing the model or optimizer
   (t5x/checkpoints.py:1835-1958)."""
-  ckpt_file = find_checkpoint(path, step)
-  ckpt_dir = os.path.dirname(ckpt_file)
-  with open(ckpt_file, "rb") as fp:
-    contents = msgpack_io.msgpack_restore(fp.read())
+  tree_dir = None
+  if os.path.isdir(path):
+    cand = path if step is None else get_checkpoint_dir(path, step)
+    if step is None and orbax_tree.find_state_dir(cand) is None and latest_step(path) is not None:
+      cand = get_checkpoint_dir(path, latest_step(path))
+    tree_dir = orbax_tree.find_state_dir(cand)
+  if tree_dir is not None:
+    ckpt_dir = tree_dir
+    contents = {"version": VERSION, "optimizer": _orbax_state_dict(tree_dir)}
+  else:
+    ckpt_file = find_checkpoint(path, step)
+    ckpt_dir = os.path.dirname(ckpt_file)
+    with open(ckpt_file, "rb") as fp:
+      contents = msgpack_io.msgpack_restore(fp.read())
   version = contents.get("version", 0)
   state_dict = _get_optimizer_state_dict(contents, {}, state_transformation_fns)
   rd = _np_dtype(restore_dtype)
   flat = state_utils.flatten_state_dict(state_dict, keep_empty_nodes=True)
   out = {}
   for name, leaf in flat.items():
-    if _is_spec(leaf):
+    if isinstance(leaf, orbax_tree.ArrayRef):
+      dt = rd if name.split("/")[0] == "target" else None
+      get = functools.partial(leaf.read, None, dt)
+      out[name] = LazyArray(leaf.shape or (), dt or leaf.dtype or "float32", get) \
+          if lazy_parameters else get()
+    elif _is_spec(leaf):
       dt = rd if name.split("/")[0] == "target" else None
       shape = tuple(leaf.get("metadata", {}).get("shape", ()))
       get = functools.partial(_read_ts, leaf, ckpt_dir, None, None, dt, version, name)
@@ -710,8 +779,9 @@ class SaveBestCheckpointer(Checkpointer):
 class OrbaxCheckpointManagerInterface:
   """The checkpoint-manager call surface `train()` drives (t5x/checkpoints.py:2211-2550):
   `should_save / save / restore / wait_until_finished / close`, save period and explicit steps,
-  keep / keep-best policy. Arrays are stored in the native T5X format (the published
-  interchange format) rather than OCDBT."""
+  keep / keep-best policy. Saves use the native T5X format (the published interchange
+  format); restores also read Orbax PyTree directories that are not OCDBT-packed
+  (`io/orbax_tree.py`)."""
 
   def __init__(self, directory: str, train_state, partitioner, dataset_iterator=None,
                save_dtype=None, restore_dtype=None, keep: Optional[int] = None, period: int = 1,

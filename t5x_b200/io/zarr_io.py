@@ -200,7 +200,7 @@ class ZarrArray:
     """Reads `region` (default: everything), optionally cast to `dtype`."""
     if not self.shape:
       c = self._read_chunk(())
-      out = np.asarray(self._fill() if c is None else c.reshape(()))
+      out = np.array(self._fill() if c is None else c.reshape(()))
       return out.astype(dtype) if dtype is not None else out
     bounds = self._norm(region, self.shape)
     out = np.empty(tuple(b - a for a, b in bounds), self.dtype)
