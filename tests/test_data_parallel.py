@@ -176,3 +176,37 @@ def test_buffer_plan_for_sharded_weights():
   # nothing streamed: both buffers have the same layout
   g2, t2, w2, wt2 = zero.plan_buffers(names, sizes, owners, set(), world)
   assert w2 == g2 and wt2 == t2
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_owner_plan_of_an_xxl_shaped_model(world):
+  """The ownership plan on the parameter list of T5.1.1-XXL (shapes only, no storage): owners
+  are balanced, every offset is aligned, nothing overlaps, and sharding the layer weights cuts
+  the weight buffer to about the replicated part plus 1/world of the layers."""
+  from t5x_b200.models.t5 import network
+  from t5x_b200.parallel import zero
+  cfg = network.T5Config(vocab_size=32128, dtype="bfloat16", emb_dim=4096, num_heads=64,
+                         num_encoder_layers=24, num_decoder_layers=24, head_dim=64,
+                         mlp_dim=10240, mlp_activations=("gelu", "linear"), dropout_rate=0.0)
+  with torch.device("meta"):
+    module = network.Transformer(cfg)
+  sizes = {n: p.numel() for n, p in module.named_parameters()}
+  names = list(sizes)
+  total = sum(sizes.values())
+  assert 11.0e9 < total < 11.6e9
+  owners = zero.assign_owners(sizes, world)
+  load = [sum(sizes[k] for k in names if owners[k] == r) for r in range(world)]
+  assert max(load) - min(load) <= 0.02 * total / world
+  streamed = {k for k in names if zero._LAYER_RE.search(k)}
+  assert len(streamed) >= 48 * 6
+  g_off, g_total, w_off, w_total = zero.plan_buffers(names, sizes, owners, streamed, world)
+  assert all(o % zero._ALIGN == 0 for o in list(g_off.values()) + list(w_off.values()))
+  assert total <= g_total <= total + zero._ALIGN * len(names)
+  spans = sorted((g_off[k], g_off[k] + sizes[k]) for k in names)
+  assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+  resident = sum(sizes[k] for k in names if k not in streamed)
+  layers = total - resident
+  assert w_total <= resident + 1.05 * layers / world + zero._ALIGN * len(names)
+  for r in range(world):
+    mine = sorted((w_off[k], w_off[k] + sizes[k]) for k in streamed if owners[k] == r)
+    assert all(a[1] <= b[0] for a, b in zip(mine, mine[1:])) and mine[-1][1] <= w_total
