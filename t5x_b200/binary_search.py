@@ -14,16 +14,18 @@ import torch
 
 def int32_bsearch(batch_shape, predicate: Callable[[torch.Tensor], torch.Tensor],
                   device=None) -> torch.Tensor:
-  """Largest int32 `x` per batch element with predicate(x) true, assuming the predicate is
-  monotone (true up to some threshold) (t5x/binary_search.py:28-71)."""
-  # Decide the sign bit first, then the remaining 31 bits from the top.
+  """Largest int32 per batch element for which `predicate` is False. The predicate must be
+  monotone: False for every value up to a per-element threshold, True above it. Always True
+  gives the smallest int32, always False the largest (t5x/binary_search.py:28-71)."""
+  # Decide the sign first, then the remaining 31 bits from the top: a bit stays set while the
+  # candidate that has it is still on the False side.
   zero = torch.zeros(batch_shape, dtype=torch.int64, device=device)
-  nonneg = predicate(zero.to(torch.int32))
-  current = torch.where(nonneg, zero, torch.full_like(zero, -(2 ** 31)))
+  negative = predicate(zero.to(torch.int32)).bool()
+  current = torch.where(negative, torch.full_like(zero, -(2 ** 31)), zero)
   for bit in range(30, -1, -1):
     cand = current + (1 << bit)
-    ok = predicate(cand.to(torch.int32))
-    current = torch.where(ok, cand, current)
+    above = predicate(cand.to(torch.int32)).bool()
+    current = torch.where(above, current, cand)
   return current.to(torch.int32)
 
 
@@ -40,7 +42,8 @@ def _monotonic_float32_to_int32(x: torch.Tensor) -> torch.Tensor:
 
 def float32_bsearch(batch_shape, predicate: Callable[[torch.Tensor], torch.Tensor],
                     device=None) -> torch.Tensor:
-  """Largest float32 per batch element for which the monotone predicate holds
+  """Largest float32, in the total order of bit patterns, per batch element for which the
+  monotone `predicate` (False up to a threshold, True above it) is False
   (t5x/binary_search.py:121-164)."""
   res = int32_bsearch(batch_shape, lambda i: predicate(_monotonic_int32_to_float32(i)),
                       device=device)

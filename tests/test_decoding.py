@@ -118,7 +118,7 @@ def test_topp_mask_keeps_smallest_nucleus(p):
 
 def test_float_bsearch_finds_threshold():
   target = torch.tensor([-3.5, 0.0, 12.25])
-  found = binary_search.float32_bsearch((3,), lambda x: x <= target)
+  found = binary_search.float32_bsearch((3,), lambda x: x > target)
   torch.testing.assert_close(found, target)
 
 
