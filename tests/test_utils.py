@@ -262,3 +262,49 @@ def test_tree_helpers():
   assert list(tree.tree_leaves({"a": 1, "b": {"c": 2, "d": (3, 4)}},
                                is_leaf=lambda x: not isinstance(x, dict))) == [1, 2, (3, 4)]
   assert core.flatten_dict_string_keys({"x": {"y": 5}}) == {"x/y": 5}
+
+
+def test_orbax_tree_checkpoints_restore_through_the_initializer_and_the_manager(tmp_path):
+  """A checkpoint directory in Orbax's PyTree layout (`checkpoint_<step>/state/<array dirs>`)
+  restores through the same user-level calls as a native one: latest / specific modes of the
+  initializer, and the checkpoint manager built for a training run."""
+  model, part = _model(), partitioning.PjitPartitioner(num_partitions=1)
+  init = _initializer(model, part)
+  key = "encoder/layers_0/mlp/wo/kernel"
+  state = init.from_scratch(init_rng=11)
+  base = tree.flatten_dict(state.params)[key].detach().clone()
+  ckpt_dir = tmp_path / "orbax_ckpts"
+  for step in (3, 6):
+    with torch.no_grad():
+      for p in tree.flatten_dict(state.params).values():
+        p.add_(1.0)
+    checkpoints.save_state_as_orbax_tree(state.replace_step(step), str(ckpt_dir))
+  assert sorted(os.listdir(ckpt_dir)) == ["checkpoint_3", "checkpoint_6"]
+  assert not (ckpt_dir / "checkpoint_6" / "checkpoint").exists()   # no native index file
+
+  with torch.no_grad():
+    for p in tree.flatten_dict(state.params).values():
+      p.zero_()
+  latest = init.from_checkpoint([core.RestoreCheckpointConfig(path=str(ckpt_dir), mode="latest")])
+  assert int(latest.step) == 6
+  torch.testing.assert_close(tree.flatten_dict(latest.params)[key], base + 2.0)
+  specific = init.from_checkpoint([core.RestoreCheckpointConfig(
+      path=str(ckpt_dir / "checkpoint_3"), mode="specific")])
+  assert int(specific.step) == 3
+  torch.testing.assert_close(tree.flatten_dict(specific.params)[key], base + 1.0)
+
+  restore_cfg = core.RestoreCheckpointConfig(path=str(ckpt_dir), mode="latest")
+  save_cfg = core.SaveCheckpointConfig(period=2, keep=1)
+  model_dir = tmp_path / "run"
+  restored, manager = core.create_checkpoint_manager_and_restore(
+      init, part, restore_cfg, str(ckpt_dir / "checkpoint_6"), 0, save_checkpoint_cfg=save_cfg,
+      model_dir=str(model_dir))
+  assert int(restored.step) == 6
+  torch.testing.assert_close(tree.flatten_dict(restored.params)[key], base + 2.0)
+  # the run then saves in the native format, which restores as well
+  manager.save(restored.replace_step(8))
+  manager.wait_until_finished()
+  assert (model_dir / "checkpoint_8" / "checkpoint").exists()
+  again = init.from_checkpoint([core.RestoreCheckpointConfig(path=str(model_dir), mode="latest")])
+  assert int(again.step) == 8
+  manager.close()
