@@ -15,6 +15,7 @@ from typing import Any, Optional
 import numpy as np
 
 from t5x_b200 import checkpoints
+from t5x_b200.io import orbax_tree
 from t5x_b200.parallel import state as pstate
 
 
@@ -41,7 +42,9 @@ class UpcycleCheckpointer(checkpoints.Checkpointer):
     n_local = local_shape[0]
 
     def get():
-      if checkpoints._is_spec(ckpt_leaf):
+      if isinstance(ckpt_leaf, orbax_tree.ArrayRef):
+        dense = ckpt_leaf.read(None, dtype=rd, expected_shape=stored)
+      elif checkpoints._is_spec(ckpt_leaf):
         dense = checkpoints._read_ts(ckpt_leaf, ckpt_dir, stored, None, rd, version, name)
       else:
         dense = np.asarray(ckpt_leaf)
@@ -57,6 +60,8 @@ class UpcycleCheckpointer(checkpoints.Checkpointer):
 
 
 def _stored_shape(ckpt_leaf, ckpt_dir):
+  if isinstance(ckpt_leaf, orbax_tree.ArrayRef):
+    return ckpt_leaf.shape
   if checkpoints._is_spec(ckpt_leaf):
     from t5x_b200.io import zarr_io
     return tuple(zarr_io.ZarrArray.open(checkpoints._spec_path(ckpt_leaf, ckpt_dir)).shape)
